@@ -1,0 +1,89 @@
+// Shared helpers for the sm_100a kernels behind the C ABI in include/akv_b200.h.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+
+#define AKV_EXPORT extern "C" __attribute__((visibility("default")))
+
+// Element types accepted for float inputs/outputs (akv_dtype in the header).
+enum { AKV_F16 = 0, AKV_BF16 = 1, AKV_F32 = 2 };
+// Integer index types for block tables / context lengths.
+enum { AKV_I32 = 0, AKV_I64 = 1 };
+
+// Error codes returned by every entry point (0 = success, >0 = cudaError_t).
+enum {
+  AKV_OK = 0,
+  AKV_ERR_ARG = -1,        // bad argument (message in akv_last_error)
+  AKV_ERR_UNSUPPORTED = -2,
+  AKV_ERR_WORKSPACE = -3,  // workspace too small
+};
+
+namespace akv {
+
+char* error_buffer();  // thread-local, 512 bytes (defined in api.cu)
+
+inline int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(error_buffer(), 512, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+inline int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    return fail((int)e, "%s: %s", what, cudaGetErrorString(e));
+  }
+  return AKV_OK;
+}
+
+inline bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
+
+inline int packed_bytes(int head_dim, int bits) { return head_dim * bits / 8; }
+
+inline int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+__device__ __forceinline__ float load_as_float(const void* p, int dtype, int64_t i) {
+  if (dtype == AKV_F16) return __half2float(reinterpret_cast<const __half*>(p)[i]);
+  if (dtype == AKV_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+  return reinterpret_cast<const float*>(p)[i];
+}
+
+__device__ __forceinline__ void store_from_float(void* p, int dtype, int64_t i, float v) {
+  if (dtype == AKV_F16) reinterpret_cast<__half*>(p)[i] = __float2half_rn(v);
+  else if (dtype == AKV_BF16) reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+  else reinterpret_cast<float*>(p)[i] = v;
+}
+
+__device__ __forceinline__ int64_t load_index(const void* p, int itype, int64_t i) {
+  return itype == AKV_I64 ? reinterpret_cast<const int64_t*>(p)[i]
+                          : (int64_t)reinterpret_cast<const int32_t*>(p)[i];
+}
+
+// Code k (0-based) of an MSB-first packed row with `bits` bits per code
+// (byte format of packing.py:13-98 in the reference).
+__device__ __forceinline__ int extract_code(const uint8_t* row, int k, int bits, int row_bytes) {
+  int bit = k * bits;
+  int byte = bit >> 3;
+  int hi = row[byte];
+  int lo = (byte + 1 < row_bytes) ? row[byte + 1] : 0;
+  int w = (hi << 8) | lo;
+  return (w >> (16 - bits - (bit & 7))) & ((1 << bits) - 1);
+}
+
+}  // namespace akv

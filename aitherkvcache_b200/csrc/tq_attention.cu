@@ -1,0 +1,646 @@
+// Paged decode attention over a TurboQuant-packed KV cache, computed in the
+// rotated domain without materialising K/V (reference semantics:
+// aither_kvcache/fused_attention.py:91-185; dispatcher :538-748).
+//
+//   q_rot = R q                                   (akv_qrot_kernel, once per call)
+//   s_t   = n^K_t * (q_rot . c[idxK_t]) * scale   (split-K kernels below)
+//   acc   = sum_t softmax(s)_t * n^V_t * c[idxV_t]
+//   out   = R^T (acc / l)                          (akv_merge_kernel: LSE merge of the
+//                                                   split partials + inverse rotation)
+//
+// Two split-K kernels write the same partial format (m in log2 units, l, acc[D]):
+//   * tq_attn_mma_kernel  - head_dim 128, 4-bit codes, up to 8 query heads per KV
+//     head, block_size a multiple of 16.  One warp per (KV head, 16-token tile);
+//     codes are turned into fp16 MMA fragments by a shared-memory table lookup
+//     (one lookup per code pair) and both products run on mma.sync m16n8k16 with
+//     the 4..8 query heads of the group in the N dimension, so every K/V byte is
+//     read once for the whole GQA group.
+//   * tq_attn_generic_kernel - any power-of-two head_dim in [32, 256], 2/3/4 bits,
+//     any GQA ratio.  Scalar; lanes own dims.
+#include "common.cuh"
+#include <math_constants.h>
+
+namespace akv {
+
+struct AttnArgs {
+  const uint8_t* k_packed; const uint8_t* v_packed;
+  int64_t kp_sb, kp_sp, kp_sh;   // bytes: block, position, head
+  int64_t vp_sb, vp_sp, vp_sh;
+  const float* k_norms; const float* v_norms;
+  int64_t kn_sb, kn_sp, kn_sh;   // floats
+  int64_t vn_sb, vn_sp, vn_sh;
+  const void* block_tables; int bt_dtype; int64_t bt_stride;
+  const void* context_lens; int cl_dtype;
+  int num_seqs, num_q_heads, num_kv_heads, head_dim, block_size, max_blocks_per_seq;
+  int64_t num_blocks;            // physical blocks in the cache (for clamping)
+  int bits;
+  int blocks_per_split, num_splits, warps_per_head, num_parts;
+  const float* qrot;             // [S][QH][D] float32, already multiplied by scale*log2(e)
+  const float* centroids;
+  float* part_acc;               // [S][QH][NP][D]
+  float* part_ml;                // [S][QH][NP][2]
+};
+
+__device__ __forceinline__ int64_t phys_block(const AttnArgs& a, int seq, int blk) {
+  int64_t b = load_index(a.block_tables, a.bt_dtype, (int64_t)seq * a.bt_stride + blk);
+  if (b < 0) b = 0;
+  if (b >= a.num_blocks) b = a.num_blocks - 1;
+  return b;
+}
+
+// ---------------------------------------------------------------------------
+// q_rot[s][qh][i] = premul * sum_j R[i][j] q[s][qh][j]   (rot_t[j*D+i] = R[i][j])
+// ---------------------------------------------------------------------------
+__global__ void akv_qrot_kernel(const void* __restrict__ q, int q_dtype, int64_t q_ss, int64_t q_sh,
+                                int num_q_heads, int D, const float* __restrict__ rot_t,
+                                float premul, float* __restrict__ qrot) {
+  extern __shared__ float qs[];
+  int s = blockIdx.x / num_q_heads, qh = blockIdx.x % num_q_heads;
+  for (int j = threadIdx.x; j < D; j += blockDim.x)
+    qs[j] = load_as_float(q, q_dtype, s * q_ss + qh * q_sh + j);
+  __syncthreads();
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < D; ++j) acc = __fmaf_rn(rot_t[(int64_t)j * D + i], qs[j], acc);
+    qrot[(int64_t)blockIdx.x * D + i] = acc * premul;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// LSE merge of `np` partials per (seq, q head) followed by out = R^T (acc / l).
+// Part p of row r: acc at acc + r*acc_row + p*acc_part (+ d), ml at ml + r*ml_row + p*ml_part.
+// n_valid (optional, per sequence via context_lens): only parts < n_valid are read.
+// mode MERGE_ROTATE: out = R^T (acc / l); MERGE_NORMALIZE: out = acc / l;
+// MERGE_RAW: the merged, un-normalised (m, l, acc) goes to raw_out as [row][D+2]
+// for a later cross-device merge.
+// ---------------------------------------------------------------------------
+enum { MERGE_ROTATE = 0, MERGE_NORMALIZE = 1, MERGE_RAW = 2 };
+
+struct MergeArgs {
+  int mode;
+  const float* acc; int64_t acc_row, acc_part;
+  const float* ml; int64_t ml_row, ml_part;
+  int np;
+  const void* context_lens; int cl_dtype; int num_q_heads;
+  int tokens_per_split, warps_per_head;   // used when context_lens != nullptr
+  int D;
+  const float* rot;              // R row-major (MERGE_ROTATE only)
+  void* out; int out_dtype; int64_t out_ss, out_sh;
+  float* raw_out;
+};
+
+__global__ void akv_merge_kernel(MergeArgs a) {
+  extern __shared__ float sm[];   // [D]
+  const int row = blockIdx.x;
+  const int seq = row / a.num_q_heads, qh = row % a.num_q_heads;
+  int np = a.np;
+  if (a.context_lens != nullptr) {
+    int64_t ctx = load_index(a.context_lens, a.cl_dtype, seq);
+    int64_t splits = (ctx + a.tokens_per_split - 1) / a.tokens_per_split;
+    int64_t v = splits * a.warps_per_head;
+    np = (int)(v < np ? v : np);
+  }
+  const float* ml = a.ml + (int64_t)row * a.ml_row;
+  float M = -CUDART_INF_F;
+  for (int p = 0; p < np; ++p) {
+    float l = ml[p * a.ml_part + 1];
+    if (l > 0.f) M = fmaxf(M, ml[p * a.ml_part]);
+  }
+  float L = 0.f;
+  for (int p = 0; p < np; ++p) {
+    float l = ml[p * a.ml_part + 1];
+    if (l > 0.f) L += l * exp2f(ml[p * a.ml_part] - M);
+  }
+  const float* acc = a.acc + (int64_t)row * a.acc_row;
+  for (int d = threadIdx.x; d < a.D; d += blockDim.x) {
+    float o = 0.f;
+    for (int p = 0; p < np; ++p) {
+      float l = ml[p * a.ml_part + 1];
+      if (l > 0.f) o += acc[(int64_t)p * a.acc_part + d] * exp2f(ml[p * a.ml_part] - M);
+    }
+    if (a.mode == MERGE_RAW) {
+      a.raw_out[(int64_t)row * (a.D + 2) + 2 + d] = o;
+    } else {
+      const float v = (L > 0.f) ? o / L : 0.f;
+      if (a.mode == MERGE_NORMALIZE) store_from_float(a.out, a.out_dtype, seq * a.out_ss + qh * a.out_sh + d, v);
+      else sm[d] = v;
+    }
+  }
+  if (a.mode == MERGE_RAW) {
+    if (threadIdx.x == 0) {
+      a.raw_out[(int64_t)row * (a.D + 2)] = M;
+      a.raw_out[(int64_t)row * (a.D + 2) + 1] = L;
+    }
+    return;
+  }
+  if (a.mode == MERGE_NORMALIZE) return;
+  __syncthreads();
+  for (int j = threadIdx.x; j < a.D; j += blockDim.x) {
+    float x = 0.f;
+    for (int i = 0; i < a.D; ++i) x = __fmaf_rn(sm[i], a.rot[(int64_t)i * a.D + j], x);
+    store_from_float(a.out, a.out_dtype, seq * a.out_ss + qh * a.out_sh + j, x);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Generic split-K kernel.  grid = (splits, kv heads, seqs), 4 warps; warp j takes
+// blocks j, j+4, ... of the split; lane owns D/32 consecutive dims.
+// ---------------------------------------------------------------------------
+constexpr int GEN_WARPS = 4;
+constexpr int GEN_QCH = 4;   // query heads processed per pass over the tokens
+
+__global__ void __launch_bounds__(GEN_WARPS * 32)
+tq_attn_generic_kernel(AttnArgs a) {
+  const int split = blockIdx.x, h = blockIdx.y, seq = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int D = a.head_dim, bits = a.bits, pd = D * bits / 8;
+  const int dpl = D / 32;
+  const int G = a.num_q_heads / a.num_kv_heads;
+  const int64_t ctx = load_index(a.context_lens, a.cl_dtype, seq);
+  const int bs = a.block_size;
+  const int64_t nblk = (ctx + bs - 1) / bs;
+  const int64_t blk_begin = (int64_t)split * a.blocks_per_split;
+  if (blk_begin >= nblk) return;
+  const int64_t blk_end = (blk_begin + a.blocks_per_split < nblk) ? blk_begin + a.blocks_per_split : nblk;
+  const int part = split * GEN_WARPS + warp;
+  __shared__ float cent[16];
+  if (threadIdx.x < (1 << bits)) cent[threadIdx.x] = a.centroids[threadIdx.x];
+  __syncthreads();
+
+  for (int g0 = 0; g0 < G; g0 += GEN_QCH) {
+    const int ng = (G - g0 < GEN_QCH) ? G - g0 : GEN_QCH;
+    float q[GEN_QCH][8], acc[GEN_QCH][8], m[GEN_QCH], l[GEN_QCH];
+#pragma unroll
+    for (int gi = 0; gi < GEN_QCH; ++gi) {
+      m[gi] = -CUDART_INF_F; l[gi] = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        acc[gi][k] = 0.f;
+        q[gi][k] = (gi < ng && k < dpl)
+            ? a.qrot[((int64_t)seq * a.num_q_heads + h * G + g0 + gi) * D + lane * dpl + k] : 0.f;
+      }
+    }
+    for (int64_t blk = blk_begin + warp; blk < blk_end; blk += GEN_WARPS) {
+      const int64_t pb = phys_block(a, seq, (int)blk);
+      const int ntok = (int)((ctx - blk * bs < bs) ? ctx - blk * bs : bs);
+      for (int t = 0; t < ntok; ++t) {
+        const uint8_t* krow = a.k_packed + pb * a.kp_sb + t * a.kp_sp + h * a.kp_sh;
+        const uint8_t* vrow = a.v_packed + pb * a.vp_sb + t * a.vp_sp + h * a.vp_sh;
+        const float nk = a.k_norms[pb * a.kn_sb + t * a.kn_sp + h * a.kn_sh];
+        const float nv = a.v_norms[pb * a.vn_sb + t * a.vn_sp + h * a.vn_sh];
+        float kc[8], vc[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          if (k < dpl) {
+            kc[k] = cent[extract_code(krow, lane * dpl + k, bits, pd)];
+            vc[k] = cent[extract_code(vrow, lane * dpl + k, bits, pd)] * nv;
+          } else { kc[k] = 0.f; vc[k] = 0.f; }
+        }
+#pragma unroll
+        for (int gi = 0; gi < GEN_QCH; ++gi) {
+          if (gi >= ng) continue;
+          float d = 0.f;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) d = __fmaf_rn(q[gi][k], kc[k], d);
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+          const float s = d * nk;
+          const float mn = fmaxf(m[gi], s);
+          const float alpha = exp2f(m[gi] - mn);
+          const float p = exp2f(s - mn);
+          l[gi] = l[gi] * alpha + p;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) acc[gi][k] = __fmaf_rn(p, vc[k], acc[gi][k] * alpha);
+          m[gi] = mn;
+        }
+      }
+    }
+    for (int gi = 0; gi < ng; ++gi) {
+      const int64_t row = (int64_t)seq * a.num_q_heads + h * G + g0 + gi;
+      float* pa = a.part_acc + (row * a.num_parts + part) * D;
+      for (int k = 0; k < dpl; ++k) pa[lane * dpl + k] = acc[gi][k];
+      if (lane == 0) {
+        a.part_ml[(row * a.num_parts + part) * 2] = m[gi];
+        a.part_ml[(row * a.num_parts + part) * 2 + 1] = l[gi];
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Tensor-core split-K kernel (head_dim 128, 4-bit).
+// ---------------------------------------------------------------------------
+constexpr int LUT_STRIDE = 256;                 // bytes between table entries
+constexpr int LUT_BYTES = 256 * LUT_STRIDE;     // 64 KB: entry e, lane l at e*256 + l*4
+
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(y) : "r"(x));
+  return y;
+}
+
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Table lookup: byte `k` of `w` selects the entry; the result is
+// half2(c[byte >> 4], c[byte & 15]).  lanebase = lane * 4.
+template <int K>
+__device__ __forceinline__ uint32_t lut4(const unsigned char* lut, uint32_t w, uint32_t lanebase) {
+  uint32_t addr = __byte_perm(w, lanebase, 0x7604 + (K << 4));
+  return *reinterpret_cast<const uint32_t*>(lut + addr);
+}
+
+template <bool VEC16>
+__device__ __forceinline__ uint4 load16(const uint8_t* p) {
+  if (VEC16) return *reinterpret_cast<const uint4*>(p);
+  const uint32_t* q = reinterpret_cast<const uint32_t*>(p);
+  return make_uint4(q[0], q[1], q[2], q[3]);
+}
+template <bool VEC16>
+__device__ __forceinline__ uint2 load8(const uint8_t* p) {
+  if (VEC16) return *reinterpret_cast<const uint2*>(p);
+  const uint32_t* q = reinterpret_cast<const uint32_t*>(p);
+  return make_uint2(q[0], q[1]);
+}
+
+struct TileData {
+  uint4 kA, kB;          // K codes of tokens g and g+8, bytes 16t..16t+15
+  uint2 v0, v1, v2, v3;  // V codes of tokens 2t, 2t+1, 2t+8, 2t+9, bytes 8g..8g+7
+  float nkA, nkB, nvA, nvB;
+};
+
+template <bool VEC16>
+__device__ __forceinline__ void load_tile(const AttnArgs& a, int seq, int h, int tile,
+                                          int tiles_per_block, int g, int t, TileData& d) {
+  const int blk = tile / tiles_per_block;
+  const int tok0 = (tile - blk * tiles_per_block) * 16;
+  const int64_t pb = phys_block(a, seq, blk);
+  const uint8_t* kb = a.k_packed + pb * a.kp_sb + h * a.kp_sh + 16 * t;
+  d.kA = load16<VEC16>(kb + (int64_t)(tok0 + g) * a.kp_sp);
+  d.kB = load16<VEC16>(kb + (int64_t)(tok0 + g + 8) * a.kp_sp);
+  const uint8_t* vb = a.v_packed + pb * a.vp_sb + h * a.vp_sh + 8 * g;
+  d.v0 = load8<VEC16>(vb + (int64_t)(tok0 + 2 * t) * a.vp_sp);
+  d.v1 = load8<VEC16>(vb + (int64_t)(tok0 + 2 * t + 1) * a.vp_sp);
+  d.v2 = load8<VEC16>(vb + (int64_t)(tok0 + 2 * t + 8) * a.vp_sp);
+  d.v3 = load8<VEC16>(vb + (int64_t)(tok0 + 2 * t + 9) * a.vp_sp);
+  const float* kn = a.k_norms + pb * a.kn_sb + h * a.kn_sh;
+  const float* vn = a.v_norms + pb * a.vn_sb + h * a.vn_sh;
+  d.nkA = kn[(int64_t)(tok0 + g) * a.kn_sp];
+  d.nkB = kn[(int64_t)(tok0 + g + 8) * a.kn_sp];
+  d.nvA = vn[(int64_t)(tok0 + g) * a.vn_sp];
+  d.nvB = vn[(int64_t)(tok0 + g + 8) * a.vn_sp];
+}
+
+template <bool VEC16>
+__global__ void __launch_bounds__(256, 2)
+tq_attn_mma_kernel(AttnArgs a) {
+  extern __shared__ __align__(16) unsigned char lut[];
+  const int split = blockIdx.x, hg = blockIdx.y, seq = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int64_t ctx = load_index(a.context_lens, a.cl_dtype, seq);
+  const int tpb = a.block_size / 16;
+  const int64_t tiles_total = (ctx + 15) / 16;
+  const int64_t tile_begin = (int64_t)split * a.blocks_per_split * tpb;
+  if (tile_begin >= tiles_total) return;   // uniform for the CTA
+  int64_t tile_end = tile_begin + (int64_t)a.blocks_per_split * tpb;
+  if (tile_end > tiles_total) tile_end = tiles_total;
+
+  // table: entry e -> half2(c[e >> 4], c[e & 15]), one copy per lane (bank = lane)
+  for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x) {
+    const int e = i >> 5, l = i & 31;   // a warp fills one entry: 32 distinct banks
+    *reinterpret_cast<uint32_t*>(lut + e * LUT_STRIDE + l * 4) =
+        pack_half2(a.centroids[e >> 4], a.centroids[e & 15]);
+  }
+  __syncthreads();
+
+  const int wph = a.warps_per_head;
+  const int hl = warp / wph, wj = warp - hl * wph;
+  const int h = hg * 8 + hl;
+  if (h >= a.num_kv_heads) return;
+  const int G = a.num_q_heads / a.num_kv_heads;
+  const uint32_t lanebase = lane * 4;
+
+  // query fragments (B operand of the score product): thread (g,t) holds
+  // q_rot[qh = g][32t .. 32t+31]; k-tile kk uses dims 32t+4kk .. 32t+4kk+3.
+  uint32_t bq[8][2];
+  {
+    const float* qp = a.qrot + ((int64_t)seq * a.num_q_heads + h * G + (g < G ? g : 0)) * 128 + 32 * t;
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      float4 f = *reinterpret_cast<const float4*>(qp + 4 * kk);
+      if (g >= G) f = make_float4(0.f, 0.f, 0.f, 0.f);
+      bq[kk][0] = pack_half2(f.x, f.y);
+      bq[kk][1] = pack_half2(f.z, f.w);
+    }
+  }
+
+  float o[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+  float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
+
+  int64_t tile = tile_begin + wj;
+  TileData cur;
+  if (tile < tile_end) load_tile<VEC16>(a, seq, h, (int)tile, tpb, g, t, cur);
+  for (; tile < tile_end; tile += wph) {
+    TileData nxt = cur;
+    if (tile + wph < tile_end) load_tile<VEC16>(a, seq, h, (int)(tile + wph), tpb, g, t, nxt);
+
+    // ---- scores: S^T[16 tokens][8 q heads] ----
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    {
+      const uint32_t wa[4] = {cur.kA.x, cur.kA.y, cur.kA.z, cur.kA.w};
+      const uint32_t wb[4] = {cur.kB.x, cur.kB.y, cur.kB.z, cur.kB.w};
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        mma16816(s, lut4<0>(lut, wa[w], lanebase), lut4<0>(lut, wb[w], lanebase),
+                 lut4<1>(lut, wa[w], lanebase), lut4<1>(lut, wb[w], lanebase),
+                 bq[2 * w][0], bq[2 * w][1]);
+        mma16816(s, lut4<2>(lut, wa[w], lanebase), lut4<2>(lut, wb[w], lanebase),
+                 lut4<3>(lut, wa[w], lanebase), lut4<3>(lut, wb[w], lanebase),
+                 bq[2 * w + 1][0], bq[2 * w + 1][1]);
+      }
+    }
+    const int64_t tokA = tile * 16 + g;
+    const bool okA = tokA < ctx, okB = tokA + 8 < ctx;
+    s[0] = okA ? s[0] * cur.nkA : -CUDART_INF_F;
+    s[1] = okA ? s[1] * cur.nkA : -CUDART_INF_F;
+    s[2] = okB ? s[2] * cur.nkB : -CUDART_INF_F;
+    s[3] = okB ? s[3] * cur.nkB : -CUDART_INF_F;
+
+    // ---- online softmax over the 16 tokens (columns 2t, 2t+1 of this thread) ----
+    float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
+#pragma unroll
+    for (int off = 4; off < 32; off <<= 1) {
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+    }
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    const float al0 = exp2f(m0 - mn0), al1 = exp2f(m1 - mn1);
+    m0 = mn0; m1 = mn1;
+    const float p0 = exp2f(s[0] - mn0), p1 = exp2f(s[1] - mn1);
+    const float p2 = exp2f(s[2] - mn0), p3 = exp2f(s[3] - mn1);
+    l0 = l0 * al0 + p0 + p2;
+    l1 = l1 * al1 + p1 + p3;
+    if (__any_sync(0xffffffffu, (al0 != 1.f) | (al1 != 1.f))) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { o[j][0] *= al0; o[j][1] *= al1; o[j][2] *= al0; o[j][3] *= al1; }
+    }
+    // weights times value norms, transposed into the B-operand layout
+    const uint32_t h01 = pack_half2(okA ? p0 * cur.nvA : 0.f, okA ? p1 * cur.nvA : 0.f);
+    const uint32_t h23 = pack_half2(okB ? p2 * cur.nvB : 0.f, okB ? p3 * cur.nvB : 0.f);
+    const uint32_t pb0 = movmatrix_trans(h01);
+    const uint32_t pb1 = movmatrix_trans(h23);
+
+    // ---- values: O^T[128 dims][8 q heads] += V^T P^T ----
+    {
+      const uint32_t va[2] = {cur.v0.x, cur.v0.y}, vb[2] = {cur.v1.x, cur.v1.y};
+      const uint32_t vc[2] = {cur.v2.x, cur.v2.y}, vd[2] = {cur.v3.x, cur.v3.y};
+#pragma unroll
+      for (int w = 0; w < 2; ++w) {
+        const uint32_t x01 = (va[w] & 0xF0F0F0F0u) | ((vb[w] >> 4) & 0x0F0F0F0Fu);
+        const uint32_t y01 = ((va[w] << 4) & 0xF0F0F0F0u) | (vb[w] & 0x0F0F0F0Fu);
+        const uint32_t x23 = (vc[w] & 0xF0F0F0F0u) | ((vd[w] >> 4) & 0x0F0F0F0Fu);
+        const uint32_t y23 = ((vc[w] << 4) & 0xF0F0F0F0u) | (vd[w] & 0x0F0F0F0Fu);
+        mma16816(o[4 * w + 0], lut4<0>(lut, x01, lanebase), lut4<0>(lut, y01, lanebase),
+                 lut4<0>(lut, x23, lanebase), lut4<0>(lut, y23, lanebase), pb0, pb1);
+        mma16816(o[4 * w + 1], lut4<1>(lut, x01, lanebase), lut4<1>(lut, y01, lanebase),
+                 lut4<1>(lut, x23, lanebase), lut4<1>(lut, y23, lanebase), pb0, pb1);
+        mma16816(o[4 * w + 2], lut4<2>(lut, x01, lanebase), lut4<2>(lut, y01, lanebase),
+                 lut4<2>(lut, x23, lanebase), lut4<2>(lut, y23, lanebase), pb0, pb1);
+        mma16816(o[4 * w + 3], lut4<3>(lut, x01, lanebase), lut4<3>(lut, y01, lanebase),
+                 lut4<3>(lut, x23, lanebase), lut4<3>(lut, y23, lanebase), pb0, pb1);
+      }
+    }
+    cur = nxt;
+  }
+
+  // ---- partial for this warp ----
+#pragma unroll
+  for (int off = 4; off < 32; off <<= 1) {
+    l0 += __shfl_xor_sync(0xffffffffu, l0, off);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+  }
+  const int part = split * wph + wj;
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const int qg = 2 * t + e;
+    if (qg >= G) continue;
+    const int64_t row = (int64_t)seq * a.num_q_heads + h * G + qg;
+    float* pa = a.part_acc + (row * a.num_parts + part) * 128;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)   // M-tile j: row g -> dim 16g+2j, row g+8 -> dim 16g+2j+1
+      *reinterpret_cast<float2*>(pa + 16 * g + 2 * j) = make_float2(o[j][e], o[j][2 + e]);
+    if (g == 0) {
+      a.part_ml[(row * a.num_parts + part) * 2] = e ? m1 : m0;
+      a.part_ml[(row * a.num_parts + part) * 2 + 1] = e ? l1 : l0;
+    }
+  }
+}
+
+static inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+struct Plan {
+  bool mma;
+  int blocks_per_split, num_splits, warps_per_head, num_parts;
+  size_t off_qrot, off_acc, off_ml, total;
+};
+
+static Plan make_plan(int num_seqs, int num_q_heads, int num_kv_heads, int head_dim, int bits,
+                      int block_size, int max_blocks_per_seq, int blocks_per_split) {
+  Plan p;
+  const int G = num_q_heads / num_kv_heads;
+  p.mma = (head_dim == 128 && bits == 4 && G >= 1 && G <= 8 && block_size % 16 == 0);
+  if (blocks_per_split <= 0) blocks_per_split = (32 * 16 + block_size - 1) / block_size;  // ~512 tokens
+  if (blocks_per_split > max_blocks_per_seq) blocks_per_split = max_blocks_per_seq > 0 ? max_blocks_per_seq : 1;
+  p.blocks_per_split = blocks_per_split;
+  p.num_splits = max_blocks_per_seq > 0 ? (max_blocks_per_seq + blocks_per_split - 1) / blocks_per_split : 1;
+  if (p.mma) {
+    int nh = num_kv_heads < 8 ? num_kv_heads : 8;
+    p.warps_per_head = 8 / nh;
+  } else {
+    p.warps_per_head = GEN_WARPS;
+  }
+  p.num_parts = p.num_splits * p.warps_per_head;
+  size_t rows = (size_t)num_seqs * num_q_heads;
+  p.off_qrot = 0;
+  p.off_acc = align256(rows * head_dim * sizeof(float));
+  p.off_ml = p.off_acc + align256(rows * p.num_parts * head_dim * sizeof(float));
+  p.total = p.off_ml + align256(rows * p.num_parts * 2 * sizeof(float));
+  return p;
+}
+
+}  // namespace akv
+
+using namespace akv;
+
+// Field-for-field mirror of akv_tq_attn_params in include/akv_b200.h.
+struct akv_tq_attn_params {
+  const void* query; int q_dtype; int64_t q_stride_seq, q_stride_head;
+  const uint8_t* k_packed; int64_t kp_stride_blk, kp_stride_pos, kp_stride_head;
+  const float* k_norms; int64_t kn_stride_blk, kn_stride_pos, kn_stride_head;
+  const uint8_t* v_packed; int64_t vp_stride_blk, vp_stride_pos, vp_stride_head;
+  const float* v_norms; int64_t vn_stride_blk, vn_stride_pos, vn_stride_head;
+  const void* block_tables; int bt_dtype; int64_t bt_stride_seq;
+  const void* context_lens; int cl_dtype;
+  int num_seqs, num_q_heads, num_kv_heads, head_dim, block_size, max_blocks_per_seq;
+  int64_t num_blocks;
+  int bits;
+  const float* rotation; const float* rotation_t; const float* centroids;
+  float scale;
+  void* out; int out_dtype; int64_t out_stride_seq, out_stride_head;
+  float* raw_out;            // if non-null: write merged (m, l, acc) instead of `out`
+  void* workspace; size_t workspace_bytes;
+  int blocks_per_split;      // 0 = default
+  void* stream;
+  void* ev_kernel_start;     // optional cudaEvent_t recorded right before / after the
+  void* ev_kernel_stop;      // split-K kernel (for per-kernel timing); may be null
+};
+
+AKV_EXPORT size_t akv_tq_paged_attn_workspace_bytes(int num_seqs, int num_q_heads, int num_kv_heads,
+                                                    int head_dim, int bits, int block_size,
+                                                    int max_blocks_per_seq, int blocks_per_split) {
+  if (num_seqs <= 0 || num_q_heads <= 0 || num_kv_heads <= 0) return 0;
+  return make_plan(num_seqs, num_q_heads, num_kv_heads, head_dim, bits, block_size,
+                   max_blocks_per_seq, blocks_per_split).total;
+}
+
+namespace akv {
+int run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t workspace_bytes);
+}
+
+int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t workspace_bytes) {
+  if (!p) return fail(AKV_ERR_ARG, "null params");
+  if (p->bits != 2 && p->bits != 3 && p->bits != 4)
+    return fail(AKV_ERR_ARG, "Supported bit-widths: 2, 3, 4. Got %d", p->bits);
+  const int D = p->head_dim;
+  if (!is_pow2(D) || D < 32 || D > 256)
+    return fail(AKV_ERR_ARG, "paged attention needs a power-of-two head_dim in [32, 256], got %d", D);
+  if (p->num_seqs < 0 || p->num_q_heads <= 0 || p->num_kv_heads <= 0 ||
+      p->num_q_heads % p->num_kv_heads != 0 || p->block_size <= 0 || p->max_blocks_per_seq < 0)
+    return fail(AKV_ERR_ARG, "paged attention: bad sizes");
+  if (p->num_seqs == 0) return AKV_OK;
+  if (!p->query || !p->k_packed || !p->v_packed || !p->k_norms || !p->v_norms || !p->block_tables ||
+      !p->context_lens || !p->rotation_t || !p->centroids || (!p->raw_out && (!p->out || !p->rotation)))
+    return fail(AKV_ERR_ARG, "paged attention: null pointer");
+  if (p->num_blocks <= 0) return fail(AKV_ERR_ARG, "paged attention: num_blocks must be > 0");
+  cudaStream_t st = (cudaStream_t)p->stream;
+  Plan plan = make_plan(p->num_seqs, p->num_q_heads, p->num_kv_heads, D, p->bits, p->block_size,
+                        p->max_blocks_per_seq, p->blocks_per_split);
+  if (workspace == nullptr || workspace_bytes < plan.total)
+    return fail(AKV_ERR_WORKSPACE, "workspace too small: need %zu bytes, got %zu", plan.total, workspace_bytes);
+  char* ws = reinterpret_cast<char*>(workspace);
+  float* qrot = reinterpret_cast<float*>(ws + plan.off_qrot);
+  float* part_acc = reinterpret_cast<float*>(ws + plan.off_acc);
+  float* part_ml = reinterpret_cast<float*>(ws + plan.off_ml);
+  const int rows = p->num_seqs * p->num_q_heads;
+
+  akv_qrot_kernel<<<rows, D < 128 ? D : 128, D * sizeof(float), st>>>(
+      p->query, p->q_dtype, p->q_stride_seq, p->q_stride_head, p->num_q_heads, D, p->rotation_t,
+      p->scale * 1.4426950408889634f, qrot);
+  if (int rc = check_launch("akv_qrot_kernel")) return rc;
+
+  AttnArgs a{};
+  a.k_packed = p->k_packed; a.v_packed = p->v_packed;
+  a.kp_sb = p->kp_stride_blk; a.kp_sp = p->kp_stride_pos; a.kp_sh = p->kp_stride_head;
+  a.vp_sb = p->vp_stride_blk; a.vp_sp = p->vp_stride_pos; a.vp_sh = p->vp_stride_head;
+  a.k_norms = p->k_norms; a.v_norms = p->v_norms;
+  a.kn_sb = p->kn_stride_blk; a.kn_sp = p->kn_stride_pos; a.kn_sh = p->kn_stride_head;
+  a.vn_sb = p->vn_stride_blk; a.vn_sp = p->vn_stride_pos; a.vn_sh = p->vn_stride_head;
+  a.block_tables = p->block_tables; a.bt_dtype = p->bt_dtype; a.bt_stride = p->bt_stride_seq;
+  a.context_lens = p->context_lens; a.cl_dtype = p->cl_dtype;
+  a.num_seqs = p->num_seqs; a.num_q_heads = p->num_q_heads; a.num_kv_heads = p->num_kv_heads;
+  a.head_dim = D; a.block_size = p->block_size; a.max_blocks_per_seq = p->max_blocks_per_seq;
+  a.num_blocks = p->num_blocks; a.bits = p->bits;
+  a.blocks_per_split = plan.blocks_per_split; a.num_splits = plan.num_splits;
+  a.warps_per_head = plan.warps_per_head; a.num_parts = plan.num_parts;
+  a.qrot = qrot; a.centroids = p->centroids; a.part_acc = part_acc; a.part_ml = part_ml;
+
+  if (p->ev_kernel_start) cudaEventRecord((cudaEvent_t)p->ev_kernel_start, st);
+  if (p->max_blocks_per_seq > 0) {
+    bool mma = plan.mma && (p->kp_stride_blk % 4 == 0) && (p->kp_stride_pos % 4 == 0) &&
+               (p->kp_stride_head % 4 == 0) && (p->vp_stride_blk % 4 == 0) &&
+               (p->vp_stride_pos % 4 == 0) && (p->vp_stride_head % 4 == 0) &&
+               (reinterpret_cast<uintptr_t>(p->k_packed) % 4 == 0) &&
+               (reinterpret_cast<uintptr_t>(p->v_packed) % 4 == 0);
+    if (plan.mma && !mma)
+      return fail(AKV_ERR_UNSUPPORTED, "packed cache rows must be 4-byte aligned");
+    if (mma) {
+      bool vec16 = (p->kp_stride_blk % 16 == 0) && (p->kp_stride_pos % 16 == 0) &&
+                   (p->kp_stride_head % 16 == 0) && (p->vp_stride_blk % 16 == 0) &&
+                   (p->vp_stride_pos % 16 == 0) && (p->vp_stride_head % 16 == 0) &&
+                   (reinterpret_cast<uintptr_t>(p->k_packed) % 16 == 0) &&
+                   (reinterpret_cast<uintptr_t>(p->v_packed) % 16 == 0);
+      int nh = p->num_kv_heads < 8 ? p->num_kv_heads : 8;
+      dim3 grid(plan.num_splits, (p->num_kv_heads + 7) / 8, p->num_seqs);
+      dim3 block(32 * nh * plan.warps_per_head);
+      auto kern = vec16 ? tq_attn_mma_kernel<true> : tq_attn_mma_kernel<false>;
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LUT_BYTES);
+      if (e != cudaSuccess) return fail((int)e, "attention: smem attribute: %s", cudaGetErrorString(e));
+      kern<<<grid, block, LUT_BYTES, st>>>(a);
+      if (int rc = check_launch("tq_attn_mma_kernel")) return rc;
+    } else {
+      dim3 grid(plan.num_splits, p->num_kv_heads, p->num_seqs);
+      tq_attn_generic_kernel<<<grid, GEN_WARPS * 32, 0, st>>>(a);
+      if (int rc = check_launch("tq_attn_generic_kernel")) return rc;
+    }
+  }
+
+  if (p->ev_kernel_stop) cudaEventRecord((cudaEvent_t)p->ev_kernel_stop, st);
+
+  MergeArgs mg{};
+  mg.acc = part_acc; mg.acc_row = (int64_t)plan.num_parts * D; mg.acc_part = D;
+  mg.ml = part_ml; mg.ml_row = (int64_t)plan.num_parts * 2; mg.ml_part = 2;
+  mg.np = p->max_blocks_per_seq > 0 ? plan.num_parts : 0;
+  mg.context_lens = p->context_lens; mg.cl_dtype = p->cl_dtype; mg.num_q_heads = p->num_q_heads;
+  mg.tokens_per_split = plan.blocks_per_split * p->block_size; mg.warps_per_head = plan.warps_per_head;
+  mg.D = D;
+  mg.mode = p->raw_out ? MERGE_RAW : MERGE_ROTATE;
+  mg.rot = p->rotation;
+  mg.out = p->out; mg.out_dtype = p->out_dtype; mg.out_ss = p->out_stride_seq; mg.out_sh = p->out_stride_head;
+  mg.raw_out = p->raw_out;
+  akv_merge_kernel<<<rows, D < 128 ? D : 128, D * sizeof(float), st>>>(mg);
+  return check_launch("akv_merge_kernel");
+}
+
+AKV_EXPORT int akv_tq_paged_attn(const akv_tq_attn_params* p) {
+  if (!p) return fail(AKV_ERR_ARG, "null params");
+  return run_tq_attn(p, p->workspace, p->workspace_bytes);
+}
+
+// Merge `num_parts` raw partials laid out [part][row][D+2] (m in log2 units, l,
+// acc[D]) - e.g. the all-gathered raw_out of several devices - and write
+// out = R^T (acc / l), or out = acc / l when `rotation` is null.
+AKV_EXPORT int akv_lse_merge(const float* parts, int num_parts, int num_seqs, int num_q_heads,
+                             int head_dim, const float* rotation, void* out, int out_dtype,
+                             int64_t out_stride_seq, int64_t out_stride_head, void* stream) {
+  if (num_parts <= 0 || num_seqs < 0 || num_q_heads <= 0 || head_dim <= 0 || head_dim > 1024)
+    return fail(AKV_ERR_ARG, "akv_lse_merge: bad sizes");
+  if (num_seqs == 0) return AKV_OK;
+  if (!parts || !out) return fail(AKV_ERR_ARG, "akv_lse_merge: null pointer");
+  const int rows = num_seqs * num_q_heads;
+  MergeArgs mg{};
+  mg.acc = parts + 2; mg.acc_row = head_dim + 2; mg.acc_part = (int64_t)rows * (head_dim + 2);
+  mg.ml = parts; mg.ml_row = head_dim + 2; mg.ml_part = (int64_t)rows * (head_dim + 2);
+  mg.np = num_parts;
+  mg.context_lens = nullptr; mg.num_q_heads = num_q_heads;
+  mg.D = head_dim;
+  mg.mode = rotation ? MERGE_ROTATE : MERGE_NORMALIZE;
+  mg.rot = rotation;
+  mg.out = out; mg.out_dtype = out_dtype; mg.out_ss = out_stride_seq; mg.out_sh = out_stride_head;
+  akv_merge_kernel<<<rows, head_dim < 128 ? head_dim : 128, head_dim * sizeof(float),
+                     (cudaStream_t)stream>>>(mg);
+  return check_launch("akv_merge_kernel");
+}

@@ -1,0 +1,141 @@
+"""Paged decode attention that reads the TurboQuant-packed cache directly.
+
+Interface of the reference's ``TQPagedAttention`` (``aither_kvcache/fused_attention.py``
+:538-748).  The query is rotated once, scores and the value sum are formed in the
+rotated domain from the packed codes, and the result is rotated back; no fp16 K/V is
+materialised.  All of it - rotation, split-K partials, log-sum-exp merge, inverse
+rotation - runs in the kernels behind ``akv_tq_paged_attn``.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+
+class TQPagedAttention:
+    """``attn = TQPagedAttention(tq, num_query_heads); out = attn.forward(...)``."""
+
+    # Kept for interface compatibility.  The reference switches to split-K above
+    # SPLITK_THRESHOLD blocks; here every call is split-K and only the split size
+    # is tunable (AITHER_TQ_SPLITK_BLOCKS = KV blocks per work item, 0 = default).
+    SPLITK_THRESHOLD = int(os.environ.get("AITHER_TQ_SPLITK_THRESHOLD", "64"))
+    SPLITK_NUM_SPLITS = int(os.environ.get("AITHER_TQ_SPLITK_SPLITS", "16"))
+    SPLITK_BLOCKS = int(os.environ.get("AITHER_TQ_SPLITK_BLOCKS", "0"))
+
+    def __init__(self, tq, num_query_heads: int, block_selector=None):
+        if block_selector is not None:
+            raise NotImplementedError("sparse block selection is not part of this build")
+        self.rotation = tq.rotation
+        self.rotation_T = getattr(tq, "rotation_T", None)
+        if self.rotation_T is None:
+            self.rotation_T = tq.rotation.t().contiguous()
+        self.centroids = tq.centroids
+        self.scale = 1.0 / math.sqrt(tq.head_dim)
+        self.head_dim = tq.head_dim
+        self.num_levels = tq.num_levels
+        self.bits = tq.bits
+        self.packed_dim = tq._packed_dim
+        self.num_query_heads = num_query_heads
+        self._workspace: Optional[torch.Tensor] = None
+
+    def _get_workspace(self, nbytes: int, device) -> torch.Tensor:
+        ws = self._workspace
+        if ws is None or ws.numel() < nbytes or ws.device != device:
+            ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+            self._workspace = ws
+        return ws
+
+    def forward(
+        self,
+        query: torch.Tensor,           # [num_seqs, num_query_heads, head_dim]
+        k_packed: torch.Tensor,        # [num_blocks, block_size, num_kv_heads, packed_dim] uint8
+        k_norms: torch.Tensor,         # [num_blocks, block_size, num_kv_heads] float32
+        v_packed: torch.Tensor,
+        v_norms: torch.Tensor,
+        block_tables: torch.Tensor,    # [num_seqs, max_blocks_per_seq] int32/int64
+        context_lens: torch.Tensor,    # [num_seqs] int32/int64
+        block_size: int = 16,
+        num_kv_heads: Optional[int] = None,
+        out: Optional[torch.Tensor] = None,
+        raw_out: Optional[torch.Tensor] = None,
+        scale: Optional[float] = None,
+        kernel_events=None,
+    ) -> torch.Tensor:
+        """Returns [num_seqs, num_query_heads, head_dim] in ``query.dtype``.
+
+        With ``raw_out`` (float32 [num_seqs*num_query_heads, head_dim+2]) the call writes the
+        un-normalised partial (m, l, acc) instead, for merging across devices.
+        ``scale`` defaults to 1/sqrt(head_dim).  ``kernel_events`` is an optional pair of
+        ``torch.cuda.Event(enable_timing=True)`` recorded around the split-K kernel alone.
+        """
+        if num_kv_heads is None:
+            num_kv_heads = k_packed.shape[2]
+        dev = _lib.require_cuda(query, k_packed, k_norms, v_packed, v_norms, block_tables, context_lens)
+        num_seqs, num_q_heads, head_dim = query.shape
+        assert head_dim == self.head_dim and num_q_heads == self.num_query_heads
+        assert k_packed.shape[1] == block_size, "block_size does not match the cache"
+        if query.dtype not in _lib._FLOAT_CODES:
+            query = query.float()
+        if query.stride(-1) != 1:
+            query = query.contiguous()
+        for name, t in (("k_packed", k_packed), ("v_packed", v_packed)):
+            if t.dtype != torch.uint8 or t.stride(-1) != 1:
+                raise ValueError(f"{name} must be uint8 with a contiguous last dimension")
+        if k_norms.dtype != torch.float32 or v_norms.dtype != torch.float32:
+            raise TypeError("norm tensors must be float32")
+        if block_tables.stride(-1) != 1:
+            block_tables = block_tables.contiguous()
+        context_lens = context_lens.contiguous()
+        max_blocks = block_tables.shape[1] if block_tables.dim() == 2 else 0
+        if out is None and raw_out is None:
+            out = torch.empty(num_seqs, num_q_heads, head_dim, dtype=query.dtype, device=dev)
+
+        L = _lib.lib()
+        nbytes = L.akv_tq_paged_attn_workspace_bytes(num_seqs, num_q_heads, num_kv_heads, head_dim,
+                                                     self.bits, block_size, max_blocks, self.SPLITK_BLOCKS)
+        ws = self._get_workspace(nbytes, dev)
+        p = _lib.TQAttnParams()
+        p.query, p.q_dtype = query.data_ptr(), _lib.float_code(query)
+        p.q_stride_seq, p.q_stride_head = query.stride(0), query.stride(1)
+        p.k_packed = k_packed.data_ptr()
+        p.kp_stride_blk, p.kp_stride_pos, p.kp_stride_head = k_packed.stride(0), k_packed.stride(1), k_packed.stride(2)
+        p.k_norms = k_norms.data_ptr()
+        p.kn_stride_blk, p.kn_stride_pos, p.kn_stride_head = k_norms.stride(0), k_norms.stride(1), k_norms.stride(2)
+        p.v_packed = v_packed.data_ptr()
+        p.vp_stride_blk, p.vp_stride_pos, p.vp_stride_head = v_packed.stride(0), v_packed.stride(1), v_packed.stride(2)
+        p.v_norms = v_norms.data_ptr()
+        p.vn_stride_blk, p.vn_stride_pos, p.vn_stride_head = v_norms.stride(0), v_norms.stride(1), v_norms.stride(2)
+        p.block_tables, p.bt_dtype = block_tables.data_ptr(), _lib.index_code(block_tables)
+        p.bt_stride_seq = block_tables.stride(0) if block_tables.dim() == 2 else 0
+        p.context_lens, p.cl_dtype = context_lens.data_ptr(), _lib.index_code(context_lens)
+        p.num_seqs, p.num_q_heads, p.num_kv_heads, p.head_dim = num_seqs, num_q_heads, num_kv_heads, head_dim
+        p.block_size, p.max_blocks_per_seq, p.num_blocks = block_size, max_blocks, k_packed.shape[0]
+        p.bits = self.bits
+        p.rotation, p.rotation_t, p.centroids = (self.rotation.data_ptr(), self.rotation_T.data_ptr(),
+                                                 self.centroids.data_ptr())
+        p.scale = self.scale if scale is None else float(scale)
+        if kernel_events is not None:
+            for ev in kernel_events:      # torch creates the CUDA event on first record
+                if not ev.cuda_event:
+                    ev.record(torch.cuda.current_stream(dev))
+            p.ev_kernel_start, p.ev_kernel_stop = kernel_events[0].cuda_event, kernel_events[1].cuda_event
+        if raw_out is not None:
+            assert raw_out.dtype == torch.float32 and raw_out.is_contiguous()
+            assert raw_out.numel() == num_seqs * num_q_heads * (head_dim + 2)
+            p.raw_out = raw_out.data_ptr()
+        else:
+            p.out, p.out_dtype = out.data_ptr(), _lib.float_code(out)
+            p.out_stride_seq, p.out_stride_head = out.stride(0), out.stride(1)
+        p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+        p.blocks_per_split = self.SPLITK_BLOCKS
+        p.stream = _lib.stream_ptr(dev)
+        with torch.cuda.device(dev):
+            rc = L.akv_tq_paged_attn(ctypes.byref(p))
+        _lib.check(rc, "akv_tq_paged_attn")
+        return raw_out if raw_out is not None else out

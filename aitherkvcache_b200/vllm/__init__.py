@@ -1,0 +1,3 @@
+"""Serving-side surface: the ``tq::decode_step`` / ``tq::hybrid_decode_step`` custom ops
+and the vLLM ``CUSTOM`` attention backend, wired to the sm_100a kernels."""
+from .ops import decode_step, init_quantizer, register_custom_ops  # noqa: F401

@@ -1,0 +1,359 @@
+#!/usr/bin/env python
+"""Benchmark of the headline path: paged decode attention over a tq-t4nc (4-bit
+TurboQuant) KV cache.
+
+Workload (BASELINE.json configs[1]): 16 sequences, context lengths uniform in
+[4096, 32768] (torch CPU generator, seed 1), 32 query / 8 KV heads, head_dim 128,
+block_size 16, block tables a random permutation of the physical blocks, K and V
+N(0,1) fp16 encoded to 4-bit codes + float32 norms, one fp16 query token per sequence.
+
+A step is one decode-attention pass over the whole batch.
+  value : KV-tokens/s with everything resident in HBM (CUDA events around the K timed steps)
+  e2e   : the same through the serving op tq::decode_step with HOST inputs - every step copies
+          query, new K/V token, slot mapping, block table and sequence lengths from pinned host
+          memory, encodes the new token into the cache, attends, and copies the output back.
+  roofline : algorithmic packed-KV bytes / duration of the split-K kernel alone (events recorded
+          around that launch inside the library).
+With --gpus N (torchrun) every rank runs its own batch of 16 sequences (batched decode shards by
+sequence, no collective): weak scaling.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+H_KV, H_Q, D, BS, BITS = 8, 32, 128, 16, 4
+NUM_SEQS = 16
+PD = D * BITS // 8
+METRIC = "paged TQ4 decode-attn KV-tokens/s"
+UNIT = "KV-tokens/s"
+WORKLOAD = ("paged decode attention, tq-t4nc cache: 16 seqs, ctx U[4096,32768] seed 1, 32Q/8KV heads, "
+            "head_dim 128, block_size 16, permuted block tables")
+
+
+def context_lengths(rank=0):
+    g = torch.Generator().manual_seed(1 + 1000 * rank)
+    return torch.randint(4096, 32769, (NUM_SEQS,), generator=g)
+
+
+def peak_hbm():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:
+        return 6650.0, "fallback (6.65 TB/s)"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu, self.proc, self.path = gpu_index, None, None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1])); mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for n, v in zip(names, f[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out = {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                   "samples": len(sm)}
+        return out
+
+
+def build_cache(tq, ctx, device, seed, replicas):
+    """Encode N(0,1) fp16 K/V into `replicas` paged caches with permuted block tables (on the GPU)."""
+    from aitherkvcache_b200 import fused_tq4_kv_update
+    nblk = [(int(c) + BS - 1) // BS for c in ctx]
+    total = sum(nblk)
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(total, generator=g)
+    bt = torch.zeros(NUM_SEQS, max(nblk), dtype=torch.int32)
+    p = 0
+    for s, n in enumerate(nblk):
+        bt[s, :n] = perm[p:p + n].to(torch.int32)
+        p += n
+    caches = []
+    gg = torch.Generator(device=device).manual_seed(seed)
+    for _ in range(replicas):
+        kp = torch.zeros(total, BS, H_KV, PD, dtype=torch.uint8, device=device)
+        vp = torch.zeros_like(kp)
+        kn = torch.zeros(total, BS, H_KV, device=device)
+        vn = torch.zeros_like(kn)
+        for s, n in enumerate(nblk):
+            blocks = bt[s, :n].to(device).long()
+            slots = (blocks[:, None] * BS + torch.arange(BS, device=device)[None, :]).reshape(-1)[:int(ctx[s])]
+            for packed, norms in ((kp, kn), (vp, vn)):
+                x = torch.randn(int(ctx[s]), H_KV, D, generator=gg, device=device, dtype=torch.float32).half()
+                fused_tq4_kv_update(x, slots, packed, norms, tq.rotation, tq.boundaries_inner, BS,
+                                    rotation_t=tq.rotation_T)
+        caches.append((kp, kn, vp, vn))
+    return caches, bt.to(device), total
+
+
+def cpu_baseline(tq, cache, bt, ctx, q, budget_s=10.0):
+    """Oracle (numpy port of the reference torch path: decode -> fp16 -> dense attention) timed on
+    the host, one sequence after another until the time budget is spent."""
+    from oracle import tq as otq
+    try:
+        from threadpoolctl import threadpool_info
+        threads = max([p.get("num_threads", 1) for p in threadpool_info()] or [1])
+    except Exception:
+        threads = os.cpu_count() or 1
+    kp, kn, vp, vn = cache
+    R = tq.rotation.cpu().numpy()
+    cent = tq.centroids.cpu().numpy()
+    btc = bt.cpu().numpy()
+    order = np.argsort(ctx.numpy())           # shortest first, so several sequences fit the budget
+    done_tokens, elapsed, used = 0, 0.0, []
+    for s in order:
+        c = int(ctx[s])
+        nb = (c + BS - 1) // BS
+        blocks = torch.from_numpy(btc[s, :nb].astype(np.int64)).to(kp.device)
+        # gather this sequence's blocks on the device and hand the oracle a compact copy
+        sub = [t[blocks].cpu().numpy() for t in (kp, kn, vp, vn)]
+        local_bt = np.arange(nb, dtype=np.int32)[None, :]
+        t0 = time.perf_counter()
+        otq.paged_attention_decode_sdpa(q[s:s + 1].cpu().numpy(), sub[0], sub[1], sub[2], sub[3], local_bt,
+                                        np.asarray([c]), R, cent, BITS, 1.0 / math.sqrt(D), BS)
+        elapsed += time.perf_counter() - t0
+        done_tokens += c
+        used.append(int(s))
+        if elapsed >= budget_s:
+            break
+    return {"value": done_tokens / elapsed, "unit": UNIT, "cores": int(threads), "kind": "port",
+            "sample": f"{len(used)} of {NUM_SEQS} sequences ({done_tokens} KV-tokens, shortest first), "
+                      f"{elapsed:.1f} s of numpy decode->fp16->attention"}, done_tokens, elapsed
+
+
+def run_reference(args, rank, world):
+    """--impl reference: the oracle port of the reference's CPU torch path on the host cores."""
+    if rank != 0:
+        return
+    # the CPU arm needs the packed cache; build it with the product encoder if a GPU is present,
+    # otherwise with the oracle encoder on a reduced batch.
+    from oracle import tq as otq
+    ctx = context_lengths(0)
+    info = None
+    steps_done, tok, el = 0, 0, 0.0
+    if torch.cuda.is_available():
+        from aitherkvcache_b200 import TurboQuant
+        dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+        torch.cuda.set_device(dev)
+        tq = TurboQuant(head_dim=D, bits=BITS, device=str(dev))
+        caches, bt, _ = build_cache(tq, ctx, dev, seed=1, replicas=1)
+        q = torch.randn(NUM_SEQS, H_Q, D, generator=torch.Generator().manual_seed(2)).half()
+        budget = max(2.0, min(10.0, 120.0 / max(1, args.steps + args.warmup)))
+        for i in range(args.warmup + args.steps):
+            info, t, e = cpu_baseline(tq, caches[0], bt, ctx, q, budget_s=budget)
+            if i >= args.warmup:
+                tok += t; el += e; steps_done += 1
+    else:
+        raise SystemExit("bench.py --impl reference needs the packed cache built on a GPU")
+    value = tok / el
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * el / steps_done,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": {"workload": WORKLOAD, "sample": info["sample"]},
+            "cpu_baseline": dict(info, value=value),
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--replicas", type=int, default=2, help="cache copies cycled through (L2 defeat)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch.distributed as dist
+    from aitherkvcache_b200 import TQPagedAttention, TurboQuant
+    from aitherkvcache_b200.vllm import ops
+
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    tq = TurboQuant(head_dim=D, bits=BITS, device=str(dev))
+    ctx = context_lengths(rank)
+    total_ctx = int(ctx.sum())
+    caches, bt, total_blocks = build_cache(tq, ctx, dev, seed=1 + rank, replicas=args.replicas)
+    ctx_dev = ctx.to(torch.int32).to(dev)
+    q_host = torch.randn(NUM_SEQS, H_Q, D, generator=torch.Generator().manual_seed(2 + rank)).half()
+    q = q_host.to(dev)
+    attn = TQPagedAttention(tq, H_Q)
+    out = torch.empty(NUM_SEQS, H_Q, D, dtype=torch.float16, device=dev)
+    kv_bytes = total_ctx * H_KV * 2 * (PD + 4)          # algorithmic packed-KV bytes per step
+
+    def step(i, events=None):
+        kp, kn, vp, vn = caches[i % len(caches)]
+        attn.forward(q, kp, kn, vp, vn, bt, ctx_dev, out=out, kernel_events=events)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing ------------------------------------------------
+    for i in range(args.warmup):
+        step(i)
+    kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i, kev[i])
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    ms_total = e0.elapsed_time(e1)
+    kernel_ms = float(np.mean([a.elapsed_time(b) for a, b in kev]))
+
+    # ---- end to end through tq::decode_step with host buffers ---------------------
+    ops.register_custom_ops()
+    ops._quantizers[D] = tq
+    kv_cache = torch.zeros(total_blocks, 2, BS, H_KV, PD, dtype=torch.uint8, device=dev)
+    kv_cache[:, 0] = caches[0][0]
+    kv_cache[:, 1] = caches[0][2]
+    k_norms = caches[0][1].unsqueeze(0).contiguous()
+    v_norms = caches[0][3].unsqueeze(0).contiguous()
+    gen = torch.Generator().manual_seed(3 + rank)
+    host = {
+        "query": q_host.pin_memory(),
+        "key": torch.randn(NUM_SEQS, H_KV, D, generator=gen).half().pin_memory(),
+        "value": torch.randn(NUM_SEQS, H_KV, D, generator=gen).half().pin_memory(),
+        # the new token overwrites the last context position of each sequence
+        "slot_mapping": torch.stack([bt[s, (int(ctx[s]) - 1) // BS].cpu().long() * BS + (int(ctx[s]) - 1) % BS
+                                     for s in range(NUM_SEQS)]).pin_memory(),
+        "block_table": bt.cpu().pin_memory(),
+        "seq_lens": ctx.to(torch.int32).pin_memory(),
+    }
+    out_host = torch.empty(NUM_SEQS, H_Q, D, dtype=torch.float16).pin_memory()
+    out_dev = torch.empty(NUM_SEQS, H_Q, D, dtype=torch.float16, device=dev)
+    h2d = sum(t.numel() * t.element_size() for t in host.values())
+    d2h = out_host.numel() * out_host.element_size()
+
+    def e2e_step():
+        d = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
+        res = torch.ops.tq.decode_step(d["query"], d["key"], d["value"], kv_cache, out_dev, k_norms, v_norms,
+                                       d["slot_mapping"], d["block_table"], d["seq_lens"], 0, H_Q, H_KV, D,
+                                       1.0 / math.sqrt(D), NUM_SEQS)
+        out_host.copy_(res, non_blocking=True)
+        torch.cuda.current_stream().synchronize()     # the caller reads the result every step
+
+    for _ in range(args.warmup):
+        e2e_step()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    f1.record()
+    barrier()
+    e2e_ms = f0.elapsed_time(f1)
+
+    times = torch.tensor([ms_total, e2e_ms, float(total_ctx)], dtype=torch.float64, device=dev)
+    if world > 1:
+        mx = times.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = times.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        ms_total, e2e_ms, job_ctx = float(mx[0]), float(mx[1]), float(sm[2])
+    else:
+        job_ctx = float(total_ctx)
+
+    if rank == 0:
+        peak, peak_src = peak_hbm()
+        achieved = kv_bytes / (kernel_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": job_ctx * args.steps / (ms_total * 1e-3), "unit": UNIT,
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16 mma / f32 accumulate over u8 4-bit codes", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "kv_tokens_per_gpu": total_ctx, "packed_kv_bytes_per_step": kv_bytes,
+                       "l2_policy": f"inputs larger than L2: {args.replicas} cache replicas of {kv_bytes / 1e6:.0f} MB "
+                                    "cycled between steps",
+                       "parallelism": f"dp{world} (sequences sharded, no collective)"},
+            "e2e": {"value": job_ctx * args.steps / (e2e_ms * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps,
+                    "api": "torch.ops.tq.decode_step (encode new token + attention), host pinned buffers"},
+            "gpu_launches": 3 * args.steps,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "kernel": "tq_attn_mma_kernel",
+                         "kernel_ms": kernel_ms, "peak_source": peak_src,
+                         "frac_of_8TBs_nominal": achieved / 8000.0},
+            "clocks": clocks,
+        }
+        if not args.no_cpu_baseline and world == 1:
+            info, _, _ = cpu_baseline(tq, caches[0], bt, ctx, q)
+            line["cpu_baseline"] = info
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,132 @@
+/*
+ * C ABI of libakv_b200.so: sm_100a kernels for the compressed-KV hot path of
+ * aither-kvcache (TurboQuant encode / decode / paged cache write / paged decode
+ * attention, the hybrid tq35 codec, TriAttention's spectral codec).
+ *
+ * The reference has no C interface for this path: its callers reach Triton
+ * kernels and torch op chains from Python.  Each entry point below names the
+ * reference function it stands in for (paths inside the reference project).
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless said otherwise; `stream` is a
+ *     cudaStream_t (NULL = the legacy default stream).  Calls only enqueue
+ *     work; nothing synchronises the host.
+ *   - Sizes are element counts, strides are in elements of the pointed-to type
+ *     (bytes for uint8_t), rows are row-major.
+ *   - Return value: 0 on success, a positive cudaError_t if a launch failed,
+ *     a negative AKV_ERR_* for rejected arguments.  akv_last_error() returns
+ *     the message of the last failure on the calling thread.
+ *   - Nothing here allocates device memory except where a function says so;
+ *     scratch space is passed in as `workspace`.
+ */
+#ifndef AKV_B200_H
+#define AKV_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of floating-point tensors */
+enum { AKV_F16 = 0, AKV_BF16 = 1, AKV_F32 = 2 };
+/* element types of index tensors (block tables, context lengths) */
+enum { AKV_I32 = 0, AKV_I64 = 1 };
+/* negative return codes */
+enum { AKV_OK = 0, AKV_ERR_ARG = -1, AKV_ERR_UNSUPPORTED = -2, AKV_ERR_WORKSPACE = -3 };
+
+int akv_version(void);
+const char* akv_last_error(void);
+/* major*10+minor of the current device (100 on B200), negative if none */
+int akv_device_arch(void);
+
+/* ------------------------------------------------------------------------
+ * Uniform TurboQuant codec
+ * ---------------------------------------------------------------------- */
+
+/* Replaces TurboQuant.encode (aither_kvcache/quantizer.py:122-166, with
+ * _pytorch_encode :203-207 and the Triton kernels of triton_ops.py:26-57,92-126).
+ *   x            [n_rows, head_dim], rows x_row_stride elements apart
+ *   rotation_t   [head_dim, head_dim] float32, rotation_t[j][i] = R[i][j]
+ *   boundaries   [2^bits - 1] float32, ascending
+ *   packed       [n_rows, head_dim*bits/8] MSB-first codes (packing.py:13-98)
+ *   norms        [n_rows] float32 L2 norms
+ * bits in {2,3,4}; head_dim a power of two in [8, 1024]. */
+int akv_tq_encode(const void* x, int x_dtype, int64_t n_rows, int64_t x_row_stride,
+                  int head_dim, int bits, const float* rotation_t, const float* boundaries,
+                  uint8_t* packed, int64_t packed_row_stride, float* norms, void* stream);
+
+/* Replaces TurboQuant.decode (quantizer.py:168-197, _pytorch_decode :209-212,
+ * triton_ops.py:59-86,128-159).  out is [n_rows, head_dim] contiguous of
+ * out_dtype; rotation is R row-major; centroids has 2^bits entries. */
+int akv_tq_decode(const uint8_t* packed, int64_t packed_row_stride, const float* norms,
+                  int64_t n_rows, int head_dim, int bits, const float* rotation,
+                  const float* centroids, void* out, int out_dtype, void* stream);
+
+/* Replaces fused_tq4_kv_update (aither_kvcache/fused_kv_update.py:300-405; Triton
+ * kernel :49-213; torch path :220-293) and, for 3/2-bit, encode + index-put
+ * (vllm/hooks.py:487-497).  Token t, head h is written to
+ * out_packed[slot/block_size][slot%block_size][h] where slot = slot_mapping[t];
+ * tokens with slot < 0 or slot/block_size >= max_blocks are skipped. */
+int akv_tq_kv_update(const void* x, int x_dtype, int64_t num_tokens, int num_kv_heads,
+                     int head_dim, int64_t x_stride_tok, int64_t x_stride_head,
+                     const int64_t* slot_mapping, uint8_t* out_packed, int64_t p_stride_blk,
+                     int64_t p_stride_pos, int64_t p_stride_head, float* out_norms,
+                     int64_t n_stride_blk, int64_t n_stride_pos, int64_t n_stride_head, int bits,
+                     const float* rotation_t, const float* boundaries, int block_size,
+                     int64_t max_blocks, void* stream);
+
+/* Paged decode attention over the packed cache.  Replaces
+ * TQPagedAttention.forward (aither_kvcache/fused_attention.py:594-748: the
+ * pre-rotation sgemm, _tq_paged_attn_fused_4bit :204-356, _tq_splitk_phase1
+ * :368-477, _tq_splitk_reduce :479-531 and the inverse-rotation sgemm), with the
+ * semantics of TQPagedAttentionRef.forward (:91-185).
+ *   query        [num_seqs, num_q_heads, head_dim]
+ *   k/v_packed   [num_blocks, block_size, num_kv_heads, head_dim*bits/8] (strided views allowed)
+ *   k/v_norms    [num_blocks, block_size, num_kv_heads] float32
+ *   block_tables [num_seqs, max_blocks_per_seq]; context_lens [num_seqs]
+ *   out          [num_seqs, num_q_heads, head_dim]; sequences with context 0 give zeros
+ * If raw_out is non-NULL the call instead writes, per (seq, q head), the
+ * un-normalised partial [m (log2 units), l, acc[head_dim]] in the rotated domain
+ * (float32, [num_seqs*num_q_heads, head_dim+2]) for merging across devices with
+ * akv_lse_merge; `out` and `rotation` may then be NULL. */
+typedef struct akv_tq_attn_params {
+  const void* query; int q_dtype; int64_t q_stride_seq, q_stride_head;
+  const uint8_t* k_packed; int64_t kp_stride_blk, kp_stride_pos, kp_stride_head;
+  const float* k_norms; int64_t kn_stride_blk, kn_stride_pos, kn_stride_head;
+  const uint8_t* v_packed; int64_t vp_stride_blk, vp_stride_pos, vp_stride_head;
+  const float* v_norms; int64_t vn_stride_blk, vn_stride_pos, vn_stride_head;
+  const void* block_tables; int bt_dtype; int64_t bt_stride_seq;
+  const void* context_lens; int cl_dtype;
+  int num_seqs, num_q_heads, num_kv_heads, head_dim, block_size, max_blocks_per_seq;
+  int64_t num_blocks;
+  int bits;
+  const float* rotation; const float* rotation_t; const float* centroids;
+  float scale;
+  void* out; int out_dtype; int64_t out_stride_seq, out_stride_head;
+  float* raw_out;
+  void* workspace; size_t workspace_bytes;
+  int blocks_per_split;   /* KV blocks per split-K work item; 0 = library default */
+  void* stream;
+  void* ev_kernel_start;  /* optional cudaEvent_t pair recorded around the split-K kernel, */
+  void* ev_kernel_stop;   /* so a caller can time that kernel alone; NULL = off */
+} akv_tq_attn_params;
+
+size_t akv_tq_paged_attn_workspace_bytes(int num_seqs, int num_q_heads, int num_kv_heads,
+                                         int head_dim, int bits, int block_size,
+                                         int max_blocks_per_seq, int blocks_per_split);
+int akv_tq_paged_attn(const akv_tq_attn_params* params);
+
+/* Log-sum-exp merge of partial attention results, the arithmetic of
+ * _tq_splitk_reduce (fused_attention.py:479-531) applied across devices.
+ *   parts [num_parts, num_seqs*num_q_heads, head_dim+2] float32 as written to raw_out
+ * out = R^T (acc / l) when rotation is given, acc / l when it is NULL. */
+int akv_lse_merge(const float* parts, int num_parts, int num_seqs, int num_q_heads, int head_dim,
+                  const float* rotation, void* out, int out_dtype, int64_t out_stride_seq,
+                  int64_t out_stride_head, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AKV_B200_H */

@@ -1,0 +1,324 @@
+"""GPU parity of the uniform TurboQuant kernels (through the C ABI) against the
+oracle and the reference-generated fixtures."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import load_golden
+from helpers import make_paged_cache, ordered_fp16, to_cuda
+from oracle import tq as otq
+
+pytestmark = pytest.mark.gpu
+
+BITS = (4, 3, 2)
+
+
+def _tq(d, bits, golden=None, **kw):
+    from aitherkvcache_b200 import TurboQuant
+    tq = TurboQuant(head_dim=d, bits=bits, device="cuda", **kw)
+    if golden is not None:
+        # the QR-based rotation depends on the host's LAPACK build; compare with the
+        # fixture's matrix and then use the fixture's so that codes can be compared bit for bit
+        assert np.abs(tq.rotation.cpu().numpy() - golden["rotation"]).max() < 1e-5
+        tq.rotation = torch.from_numpy(golden["rotation"]).cuda()
+        assert np.array_equal(tq.centroids.cpu().numpy(), golden["centroids"])
+        assert np.array_equal(tq.boundaries_inner.cpu().numpy(), golden["boundaries"])
+    return tq
+
+
+def _check_codes(packed, x, ref_packed, g, d, bits, exact_rows=None):
+    """Codes equal to ref except where the float64 rotated coordinate is within 1e-6 of a boundary."""
+    _, _, margin = otq.encode(x, g["rotation"], g["boundaries"], bits, return_margin=True)
+    a = otq.unpack(packed, d, bits)
+    b = otq.unpack(ref_packed, d, bits)
+    diff = a != b
+    near = margin.reshape(diff.shape) < 1e-6
+    assert not (diff & ~near).any(), f"{(diff & ~near).sum()} codes differ away from a boundary"
+    return float(diff.mean()), float(near.mean())
+
+
+@pytest.mark.parametrize("d", (128, 64))
+@pytest.mark.parametrize("bits", BITS)
+@pytest.mark.parametrize("which", ("f16", "bf16", "f32"))
+def test_encode_golden(d, bits, which):
+    g = load_golden(f"tq_d{d}_b{bits}.npz")
+    tq = _tq(d, bits, g)
+    if which == "f16":
+        x = torch.from_numpy(g["x"]); ref_p, ref_n = g["packed"], g["norms"]
+    elif which == "bf16":
+        x = torch.from_numpy(g["x_bf16_as_f32"]).bfloat16(); ref_p, ref_n = g["packed_bf16"], g["norms_bf16"]
+    else:
+        x = torch.from_numpy(g["x_f32"]); ref_p, ref_n = g["packed_f32"], g["norms_f32"]
+    packed, norms = tq.encode(x.cuda())
+    assert packed.dtype == torch.uint8 and norms.dtype == torch.float32
+    assert packed.shape == (x.shape[0], d * bits // 8) and norms.shape == (x.shape[0],)
+    assert np.array_equal(norms.cpu().numpy().view(np.uint32), ref_n.view(np.uint32)), "norms must be bit-equal"
+    mism, near = _check_codes(packed.cpu().numpy(), x.float().numpy(), ref_p, g, d, bits)
+    assert mism <= near
+    if which == "f16":   # hand-made rows (zero vector, one-hot, huge, tiny) are exact
+        assert np.array_equal(packed.cpu().numpy()[-7:], ref_p[-7:])
+
+
+@pytest.mark.parametrize("bits", BITS)
+def test_encode_config0_shape_vs_oracle(bits):
+    """[4, 1024, 8, 128] fp16 N(0,1), seed 0: the roundtrip configuration of the benchmark."""
+    g = load_golden(f"tq_d128_b{bits}.npz")
+    tq = _tq(128, bits, g)
+    torch.manual_seed(0)
+    x = torch.randn(4, 1024, 8, 128).half()
+    packed, norms = tq.encode(x.cuda())
+    assert packed.shape == (4, 1024, 8, 128 * bits // 8) and norms.shape == (4, 1024, 8)
+    op, on, margin = otq.encode(x.numpy(), g["rotation"], g["boundaries"], bits, return_margin=True)
+    assert np.array_equal(norms.cpu().numpy().view(np.uint32), on.view(np.uint32))
+    diff = otq.unpack(packed.cpu().numpy(), 128, bits) != otq.unpack(op, 128, bits)
+    near = margin < 1e-6
+    assert not (diff & ~near).any()
+    assert near.mean() < 2e-4
+    # the first 1024 vectors are also in the reference fixture
+    assert np.array_equal(norms.cpu().numpy().reshape(-1)[:1024].view(np.uint32), g["norms"][:1024].view(np.uint32))
+    dec = tq.decode(packed, norms).float().cpu()
+    cos = torch.nn.functional.cosine_similarity(dec.reshape(-1, 128), x.float().reshape(-1, 128), dim=-1)
+    assert cos.mean().item() > {4: 0.99, 3: 0.975, 2: 0.93}[bits]
+
+
+@pytest.mark.parametrize("d", (128, 64))
+@pytest.mark.parametrize("bits", BITS)
+def test_decode_golden(d, bits):
+    g = load_golden(f"tq_d{d}_b{bits}.npz")
+    tq = _tq(d, bits, g)
+    dec = tq.decode(torch.from_numpy(g["packed"]).cuda(), torch.from_numpy(g["norms"]).cuda())
+    assert dec.dtype == torch.float16 and dec.shape == g["decoded"].shape
+    dec = dec.cpu().numpy()
+    ref = g["decoded"]
+    fin = np.isfinite(ref.astype(np.float32))
+    assert np.array_equal(np.isfinite(dec.astype(np.float32)), fin)
+    ulp = np.abs(ordered_fp16(dec[fin]) - ordered_fp16(ref[fin]))
+    abs_err = np.abs(dec.astype(np.float32) - ref.astype(np.float32))[fin]
+    noise = (1e-6 * np.broadcast_to(g["norms"][:, None], ref.shape))[fin]
+    assert ((ulp <= 1) | (abs_err <= noise)).all()
+    assert (ulp != 0).mean() < 2e-3
+
+
+@pytest.mark.parametrize("d,bits", [(256, 4), (32, 3), (16, 2), (512, 4)])
+def test_generic_head_dims_vs_oracle(d, bits):
+    tq = _tq(d, bits)
+    R = tq.rotation.cpu().numpy()
+    x = torch.randn(333, d, generator=torch.Generator().manual_seed(d)).half()
+    packed, norms = tq.encode(x.cuda())
+    op, on, margin = otq.encode(x.numpy(), R, tq.boundaries_inner.cpu().numpy(), bits, return_margin=True)
+    if d >= 32:
+        assert np.array_equal(norms.cpu().numpy().view(np.uint32), on.view(np.uint32))
+    else:
+        assert np.allclose(norms.cpu().numpy(), on, rtol=1e-6)
+    diff = otq.unpack(packed.cpu().numpy(), d, bits) != otq.unpack(op, d, bits)
+    assert not (diff & ~(margin < 1e-6)).any()
+    dec = tq.decode(packed, norms).cpu().numpy().astype(np.float32)
+    ref = otq.decode_f32(op, on, R, tq.centroids.cpu().numpy(), bits)
+    assert np.abs(dec - ref).max() <= 2e-3 * max(1.0, np.abs(ref).max())
+
+
+def test_shapes_and_errors():
+    tq = _tq(128, 4)
+    x = torch.randn(2, 3, 5, 128, device="cuda", dtype=torch.float16)
+    p, n = tq.encode(x)
+    assert p.shape == (2, 3, 5, 64) and n.shape == (2, 3, 5)
+    assert tq.decode(p, n).shape == (2, 3, 5, 128)
+    p1, n1 = tq.encode(x[0, 0, 0])
+    assert p1.shape == (64,) and n1.dim() == 0
+    assert torch.equal(p1, p[0, 0, 0]) and torch.equal(n1, n[0, 0, 0])
+    # strided rows
+    wide = torch.randn(10, 256, device="cuda", dtype=torch.float16)
+    ps, ns = tq.encode(wide[:, :128])
+    pc, nc = tq.encode(wide[:, :128].contiguous())
+    assert torch.equal(ps, pc) and torch.equal(ns, nc)
+    pe, ne = tq.encode(torch.empty(0, 128, device="cuda", dtype=torch.float16))
+    assert pe.shape == (0, 64) and ne.shape == (0,)
+    z = torch.zeros(1, 128, device="cuda")
+    pz, nz = tq.encode(z)
+    assert nz.item() == 0.0 and (pz == 0x77).all()
+    assert torch.isfinite(tq.decode(pz, nz)).all() and (tq.decode(pz, nz) == 0).all()
+    with pytest.raises(AssertionError):
+        tq.encode(torch.randn(4, 64, device="cuda"))
+    with pytest.raises(RuntimeError):
+        tq.encode(torch.randn(4, 128))
+    from aitherkvcache_b200 import TurboQuant
+    with pytest.raises(ValueError):
+        TurboQuant(head_dim=128, bits=5)
+    with pytest.raises(ValueError):
+        TurboQuant(head_dim=100, bits=4)
+    # norm accuracy as in the reference's tests (1e-3)
+    xf = torch.randn(100, 128, device="cuda") * 5
+    _, nn = tq.encode(xf)
+    assert torch.allclose(nn, xf.norm(dim=-1), atol=1e-3)
+
+
+def test_validate_and_mse_bounds():
+    for bits in BITS:
+        tq = _tq(128, bits)
+        r = tq.validate(num_vectors=20000)
+        assert r["mse_theory_lower"] <= r["mse"] <= r["mse_theory_upper"]
+
+
+def test_paged_write_golden():
+    from aitherkvcache_b200 import fused_tq4_kv_update
+    g = load_golden("paged_write_b4.npz")
+    t = load_golden("tq_d128_b4.npz")
+    tq = _tq(128, 4, t)
+    outp = torch.full(g["out_packed"].shape, 0xAB, dtype=torch.uint8, device="cuda")
+    outn = torch.full(g["out_norms"].shape, -7.0, device="cuda")
+    fused_tq4_kv_update(torch.from_numpy(g["x"]).cuda(), torch.from_numpy(g["slot_mapping"]).cuda(), outp, outn,
+                        tq.rotation, tq.boundaries_inner, int(g["block_size"]), int(g["max_blocks"]))
+    assert np.array_equal(outn.cpu().numpy().view(np.uint32), g["out_norms"].view(np.uint32))
+    assert np.array_equal(outp.cpu().numpy(), g["out_packed"])
+
+
+@pytest.mark.parametrize("bits", BITS)
+def test_paged_write_strided_cache_vs_oracle(bits):
+    """Write into kv_cache[:, 0/1, :, :, :pd] views of a [blocks, 2, bs, H, pd+4] uint8 tensor."""
+    from aitherkvcache_b200 import fused_tq4_kv_update
+    t = load_golden(f"tq_d128_b{bits}.npz")
+    tq = _tq(128, bits, t)
+    pd = 128 * bits // 8
+    nblk, bs, H, T = 9, 16, 8, 100
+    gen = torch.Generator().manual_seed(5)
+    key = torch.randn(T, H, 128, generator=gen).half()
+    slots = torch.randperm(nblk * bs, generator=gen)[:T].to(torch.int64)
+    slots[7] = -1
+    kv = torch.zeros(nblk, 2, bs, H, pd + 4, dtype=torch.uint8, device="cuda")
+    norms = torch.zeros(nblk, bs, H, device="cuda")
+    fused_tq4_kv_update(key.cuda(), slots.cuda(), kv[:, 0, :, :, :pd], norms, tq.rotation,
+                        tq.boundaries_inner, bs, nblk)
+    refp = np.zeros((nblk, bs, H, pd), np.uint8)
+    refn = np.zeros((nblk, bs, H), np.float32)
+    otq.paged_kv_update(key.numpy(), slots.numpy(), refp, refn, t["rotation"], t["boundaries"], bits, bs, nblk)
+    assert np.array_equal(norms.cpu().numpy().view(np.uint32), refn.view(np.uint32))
+    got = kv[:, 0, :, :, :pd].cpu().numpy()
+    assert (got != refp).mean() < 1e-4
+    assert (kv[:, 1] == 0).all() and (kv[:, 0, :, :, pd:] == 0).all()
+
+
+def _attn(tq, qh):
+    from aitherkvcache_b200 import TQPagedAttention
+    return TQPagedAttention(tq, qh)
+
+
+@pytest.mark.parametrize("bits", BITS)
+@pytest.mark.parametrize("idx_dtype", (torch.int32, torch.int64))
+def test_paged_attention_golden(bits, idx_dtype):
+    g = load_golden(f"paged_attn_b{bits}.npz")
+    t = load_golden(f"tq_d128_b{bits}.npz")
+    tq = _tq(128, bits, t)
+    c = to_cuda(g, ["query", "k_packed", "k_norms", "v_packed", "v_norms", "block_tables", "context_lens"])
+    out = _attn(tq, 8).forward(c["query"], c["k_packed"], c["k_norms"], c["v_packed"], c["v_norms"],
+                               c["block_tables"].to(idx_dtype), c["context_lens"].to(idx_dtype))
+    assert out.dtype == torch.float16 and out.shape == (7, 8, 128)
+    out = out.float().cpu().numpy()
+    assert (out[0] == 0).all(), "zero context gives zeros"
+    assert np.abs(out - g["out_rotated_domain"].astype(np.float32)).max() < 2e-3
+    assert np.abs(out - g["out_decode_sdpa"].astype(np.float32)).max() < 2e-3
+
+
+@pytest.mark.parametrize("bits,H,QH,ctx", [
+    (4, 8, 32, [1500, 17, 4096, 333]),       # benchmark head layout, several splits
+    (4, 2, 16, [700, 64]),                    # GQA 8:1, 4 warps per head
+    (4, 4, 4, [100, 48, 1]),                  # the reference tests' layout (no GQA)
+    (3, 8, 32, [600, 31]),
+    (2, 8, 32, [600, 129]),
+])
+def test_paged_attention_vs_oracle(bits, H, QH, ctx):
+    t = load_golden(f"tq_d128_b{bits}.npz")
+    tq = _tq(128, bits, t)
+    d = make_paged_cache(100 + bits + H, ctx, H, 128, bits, t["rotation"], t["boundaries"])
+    q = torch.randn(len(ctx), QH, 128, generator=torch.Generator().manual_seed(9)).half()
+    c = to_cuda(d, ["k_packed", "k_norms", "v_packed", "v_norms", "block_tables", "context_lens"])
+    out = _attn(tq, QH).forward(q.cuda(), c["k_packed"], c["k_norms"], c["v_packed"], c["v_norms"],
+                                c["block_tables"], c["context_lens"]).float().cpu().numpy()
+    ref = otq.paged_attention_rotated(q.numpy(), d["k_packed"], d["k_norms"], d["v_packed"], d["v_norms"],
+                                      d["block_tables"], d["context_lens"], t["rotation"], t["centroids"],
+                                      bits, 1.0 / math.sqrt(128))
+    assert np.abs(out - ref).max() < 2e-3    # fp16 output, tolerance of the benchmark spec
+    sdpa = otq.paged_attention_decode_sdpa(q.numpy(), d["k_packed"], d["k_norms"], d["v_packed"], d["v_norms"],
+                                           d["block_tables"], d["context_lens"], t["rotation"], t["centroids"],
+                                           bits, 1.0 / math.sqrt(128))
+    assert np.abs(out - sdpa.astype(np.float32)).max() < 2e-3
+
+
+def test_paged_attention_strided_cache_and_query_dtypes():
+    """kv_cache[:, 0/1, ..., :pd] views (row pitch pd+4) and bf16 / fp32 queries."""
+    bits, H, QH, ctx = 4, 8, 32, [200, 95]
+    t = load_golden("tq_d128_b4.npz")
+    tq = _tq(128, bits, t)
+    d = make_paged_cache(77, ctx, H, 128, bits, t["rotation"], t["boundaries"])
+    nb = d["k_packed"].shape[0]
+    kv = torch.zeros(nb, 2, 16, H, 68, dtype=torch.uint8, device="cuda")
+    kv[:, 0, :, :, :64] = torch.from_numpy(d["k_packed"]).cuda()
+    kv[:, 1, :, :, :64] = torch.from_numpy(d["v_packed"]).cuda()
+    c = to_cuda(d, ["k_norms", "v_norms", "block_tables", "context_lens"])
+    q = torch.randn(len(ctx), QH, 128, generator=torch.Generator().manual_seed(3))
+    ref = otq.paged_attention_rotated(q.numpy(), d["k_packed"], d["k_norms"], d["v_packed"], d["v_norms"],
+                                      d["block_tables"], d["context_lens"], t["rotation"], t["centroids"],
+                                      bits, 1.0 / math.sqrt(128))
+    out = _attn(tq, QH).forward(q.cuda(), kv[:, 0, :, :, :64], c["k_norms"], kv[:, 1, :, :, :64], c["v_norms"],
+                                c["block_tables"], c["context_lens"])
+    assert out.dtype == torch.float32
+    assert np.abs(out.cpu().numpy() - ref).max() < 1e-3
+    qb = q.bfloat16()
+    refb = otq.paged_attention_rotated(qb.float().numpy(), d["k_packed"], d["k_norms"], d["v_packed"],
+                                       d["v_norms"], d["block_tables"], d["context_lens"], t["rotation"],
+                                       t["centroids"], bits, 1.0 / math.sqrt(128))
+    outb = _attn(tq, QH).forward(qb.cuda(), kv[:, 0, :, :, :64], c["k_norms"], kv[:, 1, :, :, :64],
+                                 c["v_norms"], c["block_tables"], c["context_lens"])
+    assert outb.dtype == torch.bfloat16
+    assert np.abs(outb.float().cpu().numpy() - refb).max() < 8e-3   # bf16 output rounding
+
+
+def test_paged_attention_head_dim_64_and_large_norms():
+    bits, H, QH, ctx = 4, 4, 8, [70, 16]
+    t = load_golden("tq_d64_b4.npz")
+    tq = _tq(64, bits, t)
+    d = make_paged_cache(5, ctx, H, 64, bits, t["rotation"], t["boundaries"], k_scale=20.0)
+    q = torch.randn(len(ctx), QH, 64, generator=torch.Generator().manual_seed(4)).half()
+    c = to_cuda(d, ["k_packed", "k_norms", "v_packed", "v_norms", "block_tables", "context_lens"])
+    out = _attn(tq, QH).forward(q.cuda(), c["k_packed"], c["k_norms"], c["v_packed"], c["v_norms"],
+                                c["block_tables"], c["context_lens"]).float().cpu().numpy()
+    ref = otq.paged_attention_rotated(q.numpy(), d["k_packed"], d["k_norms"], d["v_packed"], d["v_norms"],
+                                      d["block_tables"], d["context_lens"], t["rotation"], t["centroids"],
+                                      bits, 1.0 / math.sqrt(64))
+    assert np.isfinite(out).all()
+    assert np.abs(out - ref).max() < 4e-3   # peaky softmax: outputs are O(1), fp16 ulp there is 1e-3
+
+
+def test_split_context_raw_partials_merge():
+    """Two halves of every context, as two devices would hold them, merged by akv_lse_merge."""
+    from aitherkvcache_b200 import _lib
+    bits, H, QH, ctx = 4, 8, 32, [640, 96, 33]
+    t = load_golden("tq_d128_b4.npz")
+    tq = _tq(128, bits, t)
+    d = make_paged_cache(21, ctx, H, 128, bits, t["rotation"], t["boundaries"])
+    q = torch.randn(len(ctx), QH, 128, generator=torch.Generator().manual_seed(1)).half().cuda()
+    c = to_cuda(d, ["k_packed", "k_norms", "v_packed", "v_norms", "block_tables", "context_lens"])
+    attn = _attn(tq, QH)
+    full = attn.forward(q, c["k_packed"], c["k_norms"], c["v_packed"], c["v_norms"], c["block_tables"],
+                        c["context_lens"])
+    # rank 0: first 16*k tokens; rank 1: the rest (block tables shifted left); one rank may be empty
+    parts = torch.zeros(2, len(ctx) * QH, 130, device="cuda")
+    bt = c["block_tables"]
+    cl = c["context_lens"]
+    first = torch.tensor([320, 96, 16], device="cuda")
+    attn.forward(q, c["k_packed"], c["k_norms"], c["v_packed"], c["v_norms"], bt, torch.minimum(cl, first),
+                 raw_out=parts[0])
+    bt2 = torch.zeros_like(bt)
+    for s, f in enumerate(first.tolist()):
+        nb = f // 16
+        bt2[s, :bt.shape[1] - nb] = bt[s, nb:]
+    attn.forward(q, c["k_packed"], c["k_norms"], c["v_packed"], c["v_norms"], bt2,
+                 torch.clamp(cl - first, min=0), raw_out=parts[1])
+    assert parts[1].reshape(3, QH, 130)[1, :, 1].abs().max().item() == 0.0    # empty range: l == 0
+    out = torch.empty_like(full)
+    rc = _lib.lib().akv_lse_merge(parts.data_ptr(), 2, len(ctx), QH, 128, tq.rotation.data_ptr(),
+                                  out.data_ptr(), _lib.AKV_F16, out.stride(0), out.stride(1),
+                                  torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "akv_lse_merge")
+    assert (out.float() - full.float()).abs().max().item() < 1e-3
