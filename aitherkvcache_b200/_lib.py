@@ -57,6 +57,8 @@ _SIGNATURES = {
                                  c_i64, c_vp, c_i64, c_i64, c_i64, c_int, c_vp, c_vp, c_int, c_i64, c_vp]),
     "akv_tq_paged_attn_workspace_bytes": (C.c_size_t, [c_int] * 8),
     "akv_tq_paged_attn": (c_int, [C.POINTER(TQAttnParams)]),
+    "akv_tq_paged_attn_static_scratch_bytes": (C.c_size_t, []),
+    "akv_tq_paged_attn_static": (c_int, [C.POINTER(TQAttnParams)]),
     "akv_lse_merge": (c_int, [c_vp, c_int, c_int, c_int, c_int, c_vp, c_vp, c_int, c_i64, c_i64, c_vp]),
 }
 

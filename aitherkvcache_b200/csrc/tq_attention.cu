@@ -620,6 +620,87 @@ AKV_EXPORT int akv_tq_paged_attn(const akv_tq_attn_params* p) {
   return run_tq_attn(p, p->workspace, p->workspace_bytes);
 }
 
+// ---------------------------------------------------------------------------
+// Allocation-free variant of akv_tq_paged_attn.
+//
+// Some callers are not allowed to allocate device memory around the call: a
+// serving engine that has already handed every free byte to its KV-cache pool,
+// or a plugin that runs inside someone else's memory plan and may not touch
+// cudaMalloc (nor torch's caching allocator).  For them the split-K scratch -
+// rotated queries plus the (m, l, acc) partials - lives in a fixed array that is
+// part of the loaded library image, so each GPU that loads the library holds
+// AKV_STATIC_SCRATCH_BYTES of it until the process exits.
+//
+// In host code `g_static_scratch` is only a handle for the symbol, not a device
+// address; the address every kernel receives comes from cudaGetSymbolAddress,
+// asked once per device with that device current.
+// ---------------------------------------------------------------------------
+#define AKV_STATIC_SCRATCH_BYTES (8u << 20)
+static __device__ __align__(256) unsigned char g_static_scratch[AKV_STATIC_SCRATCH_BYTES];
+
+namespace akv {
+static int static_scratch_ptr(void** out) {
+  constexpr int kMaxDevices = 64;
+  static void* ptrs[kMaxDevices] = {nullptr};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail((int)e, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(AKV_ERR_UNSUPPORTED, "device index %d out of range", dev);
+  void* p = __atomic_load_n(&ptrs[dev], __ATOMIC_ACQUIRE);
+  if (p == nullptr) {
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(e != cudaSuccess ? (int)e : AKV_ERR_UNSUPPORTED, "cudaGetSymbolAddress(static scratch): %s",
+                  cudaGetErrorString(e));
+    __atomic_store_n(&ptrs[dev], p, __ATOMIC_RELEASE);   // same value from any thread
+  }
+  *out = p;
+  return AKV_OK;
+}
+}  // namespace akv
+
+AKV_EXPORT size_t akv_tq_paged_attn_static_scratch_bytes(void) { return AKV_STATIC_SCRATCH_BYTES; }
+
+// Same arguments and results as akv_tq_paged_attn; params->workspace and
+// params->workspace_bytes are ignored.  If params->blocks_per_split is 0 the
+// split size is grown until the partials fit the static array; a problem that
+// does not fit even with one split per sequence (or an explicit
+// blocks_per_split that needs more) is rejected with AKV_ERR_WORKSPACE.
+//
+// The first call on a device looks up the array's address; make that call
+// before any stream capture starts.  All calls on a device share the array and
+// it keeps whatever the previous call left (nothing in it needs to start at
+// zero: every partial that is read has been written by the same call), so two
+// calls that may overlap on the GPU - different streams, or graphs replayed
+// concurrently - race on it; serialise them.
+AKV_EXPORT int akv_tq_paged_attn_static(const akv_tq_attn_params* p) {
+  if (!p) return fail(AKV_ERR_ARG, "null params");
+  if (p->num_seqs <= 0 || p->num_q_heads <= 0 || p->num_kv_heads <= 0 || p->block_size <= 0 ||
+      p->max_blocks_per_seq < 0)
+    return run_tq_attn(p, nullptr, 0);   // reports the argument error (or returns for 0 sequences)
+  akv_tq_attn_params q = *p;
+  int bps = p->blocks_per_split;
+  Plan plan = make_plan(p->num_seqs, p->num_q_heads, p->num_kv_heads, p->head_dim, p->bits,
+                        p->block_size, p->max_blocks_per_seq, bps);
+  if (bps <= 0) {
+    bps = plan.blocks_per_split;
+    while (plan.total > AKV_STATIC_SCRATCH_BYTES && plan.num_splits > 1) {
+      bps *= 2;
+      plan = make_plan(p->num_seqs, p->num_q_heads, p->num_kv_heads, p->head_dim, p->bits,
+                       p->block_size, p->max_blocks_per_seq, bps);
+    }
+    q.blocks_per_split = plan.blocks_per_split;
+  }
+  if (plan.total > AKV_STATIC_SCRATCH_BYTES)
+    return fail(AKV_ERR_WORKSPACE,
+                "akv_tq_paged_attn_static: needs %zu bytes of scratch but the built-in array holds %u "
+                "(num_seqs*num_q_heads = %d rows, %d partials each); use akv_tq_paged_attn with a workspace",
+                plan.total, (unsigned)AKV_STATIC_SCRATCH_BYTES, p->num_seqs * p->num_q_heads, plan.num_parts);
+  void* scratch = nullptr;
+  if (int rc = static_scratch_ptr(&scratch)) return rc;
+  return run_tq_attn(&q, scratch, AKV_STATIC_SCRATCH_BYTES);
+}
+
 // Merge `num_parts` raw partials laid out [part][row][D+2] (m in log2 units, l,
 // acc[D]) - e.g. the all-gathered raw_out of several devices - and write
 // out = R^T (acc / l), or out = acc / l when `rotation` is null.

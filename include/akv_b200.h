@@ -118,6 +118,20 @@ size_t akv_tq_paged_attn_workspace_bytes(int num_seqs, int num_q_heads, int num_
                                          int max_blocks_per_seq, int blocks_per_split);
 int akv_tq_paged_attn(const akv_tq_attn_params* params);
 
+/* akv_tq_paged_attn without a caller-supplied workspace and without any device
+ * allocation.  It has no counterpart in the reference.  It is for callers that
+ * cannot allocate around the call - an engine whose memory is fully committed to
+ * its KV-cache pool, a plugin that must stay out of the host program's
+ * allocator.  The scratch is a fixed array inside the library image
+ * (akv_tq_paged_attn_static_scratch_bytes(), 8 MiB per GPU, held until exit);
+ * params->workspace / workspace_bytes are ignored.  With blocks_per_split == 0
+ * the split size is grown until the partials fit; problems that still do not fit
+ * return AKV_ERR_WORKSPACE.  The first call on each device resolves the array's
+ * address and should happen before any stream capture.  Calls on one device share
+ * the array: calls that can overlap on the GPU race and must be serialised. */
+size_t akv_tq_paged_attn_static_scratch_bytes(void);
+int akv_tq_paged_attn_static(const akv_tq_attn_params* params);
+
 /* Log-sum-exp merge of partial attention results, the arithmetic of
  * _tq_splitk_reduce (fused_attention.py:479-531) applied across devices.
  *   parts [num_parts, num_seqs*num_q_heads, head_dim+2] float32 as written to raw_out
