@@ -20,6 +20,12 @@
 #include "common.cuh"
 #include <math_constants.h>
 
+// 1: one norm load per lane, broadcast by shuffles; 0: four norm loads per thread.
+// Measured equal on B200; the shuffle form spills less.
+#ifndef AKV_NORM_SHFL
+#define AKV_NORM_SHFL 1
+#endif
+
 namespace akv {
 
 struct AttnArgs {
@@ -274,32 +280,135 @@ __device__ __forceinline__ uint2 load8(const uint8_t* p) {
   return make_uint2(q[0], q[1]);
 }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Per-thread packed data of one 16-token tile of one KV head.
 struct TileData {
   uint4 kA, kB;          // K codes of tokens g and g+8, bytes 16t..16t+15
   uint2 v0, v1, v2, v3;  // V codes of tokens 2t, 2t+1, 2t+8, 2t+9, bytes 8g..8g+7
-  float nkA, nkB, nvA, nvB;
+#if AKV_NORM_SHFL
+  float nrm;             // lanes 0..15: K norm of token `lane`; lanes 16..31: V norm of token lane-16
+#else
+  float nkA, nkB, nvA, nvB;   // norms of tokens g, g+8
+#endif
+};
+
+// Byte / element offsets that do not change from tile to tile (block_size 16: one tile per block).
+struct ThreadOffsets {
+  int kA, kB, v0, v1, v2, v3;   // from the block's base in k_packed / v_packed
+  int nrm;                      // from the block's base in k_norms (lanes 0..15) or v_norms
+  int nkA, nkB, nvA, nvB;
 };
 
 template <bool VEC16>
-__device__ __forceinline__ void load_tile(const AttnArgs& a, int seq, int h, int tile,
-                                          int tiles_per_block, int g, int t, TileData& d) {
-  const int blk = tile / tiles_per_block;
-  const int tok0 = (tile - blk * tiles_per_block) * 16;
-  const int64_t pb = phys_block(a, seq, blk);
-  const uint8_t* kb = a.k_packed + pb * a.kp_sb + h * a.kp_sh + 16 * t;
-  d.kA = load16<VEC16>(kb + (int64_t)(tok0 + g) * a.kp_sp);
-  d.kB = load16<VEC16>(kb + (int64_t)(tok0 + g + 8) * a.kp_sp);
-  const uint8_t* vb = a.v_packed + pb * a.vp_sb + h * a.vp_sh + 8 * g;
-  d.v0 = load8<VEC16>(vb + (int64_t)(tok0 + 2 * t) * a.vp_sp);
-  d.v1 = load8<VEC16>(vb + (int64_t)(tok0 + 2 * t + 1) * a.vp_sp);
-  d.v2 = load8<VEC16>(vb + (int64_t)(tok0 + 2 * t + 8) * a.vp_sp);
-  d.v3 = load8<VEC16>(vb + (int64_t)(tok0 + 2 * t + 9) * a.vp_sp);
-  const float* kn = a.k_norms + pb * a.kn_sb + h * a.kn_sh;
-  const float* vn = a.v_norms + pb * a.vn_sb + h * a.vn_sh;
-  d.nkA = kn[(int64_t)(tok0 + g) * a.kn_sp];
-  d.nkB = kn[(int64_t)(tok0 + g + 8) * a.kn_sp];
-  d.nvA = vn[(int64_t)(tok0 + g) * a.vn_sp];
-  d.nvB = vn[(int64_t)(tok0 + g + 8) * a.vn_sp];
+__device__ __forceinline__ void load_tile(const AttnArgs& a, const ThreadOffsets& off, int64_t pb,
+                                          int tok0, int lane, TileData& d) {
+  const uint8_t* kb = a.k_packed + pb * a.kp_sb + (int64_t)tok0 * a.kp_sp;
+  const uint8_t* vb = a.v_packed + pb * a.vp_sb + (int64_t)tok0 * a.vp_sp;
+  d.kA = load16<VEC16>(kb + off.kA);
+  d.kB = load16<VEC16>(kb + off.kB);
+  d.v0 = load8<VEC16>(vb + off.v0);
+  d.v1 = load8<VEC16>(vb + off.v1);
+  d.v2 = load8<VEC16>(vb + off.v2);
+  d.v3 = load8<VEC16>(vb + off.v3);
+#if AKV_NORM_SHFL
+  const float* nb = (lane < 16) ? a.k_norms + pb * a.kn_sb + (int64_t)tok0 * a.kn_sp
+                                : a.v_norms + pb * a.vn_sb + (int64_t)tok0 * a.vn_sp;
+  d.nrm = nb[off.nrm];
+#else
+  const float* kn = a.k_norms + pb * a.kn_sb + (int64_t)tok0 * a.kn_sp;
+  const float* vn = a.v_norms + pb * a.vn_sb + (int64_t)tok0 * a.vn_sp;
+  d.nkA = kn[off.nkA]; d.nkB = kn[off.nkB]; d.nvA = vn[off.nvA]; d.nvB = vn[off.nvB];
+#endif
+}
+
+struct SoftmaxState {
+  float m0, m1, l0, l1;   // running max (log2 units) and sum for q-head columns 2t, 2t+1
+};
+
+// One 16-token tile: scores, online softmax, value accumulation.
+// `n_valid` (1..16) masks the tail of the last tile of a sequence.
+__device__ __forceinline__ void process_tile(const unsigned char* lut, uint32_t lanebase, int g,
+                                             const uint32_t (&bq)[8][2], const TileData& cur,
+                                             int n_valid, float (&o)[8][4], SoftmaxState& st) {
+  // ---- scores: S^T[16 tokens][8 q heads], two independent accumulation chains ----
+  float s[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};
+  {
+    const uint32_t wa[4] = {cur.kA.x, cur.kA.y, cur.kA.z, cur.kA.w};
+    const uint32_t wb[4] = {cur.kB.x, cur.kB.y, cur.kB.z, cur.kB.w};
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      mma16816(s, lut4<0>(lut, wa[w], lanebase), lut4<0>(lut, wb[w], lanebase),
+               lut4<1>(lut, wa[w], lanebase), lut4<1>(lut, wb[w], lanebase),
+               bq[2 * w][0], bq[2 * w][1]);
+      mma16816(s2, lut4<2>(lut, wa[w], lanebase), lut4<2>(lut, wb[w], lanebase),
+               lut4<3>(lut, wa[w], lanebase), lut4<3>(lut, wb[w], lanebase),
+               bq[2 * w + 1][0], bq[2 * w + 1][1]);
+    }
+  }
+#if AKV_NORM_SHFL
+  const float nkA = __shfl_sync(0xffffffffu, cur.nrm, g);
+  const float nkB = __shfl_sync(0xffffffffu, cur.nrm, g + 8);
+  float nvA = __shfl_sync(0xffffffffu, cur.nrm, g + 16);
+  float nvB = __shfl_sync(0xffffffffu, cur.nrm, g + 24);
+#else
+  const float nkA = cur.nkA, nkB = cur.nkB;
+  float nvA = cur.nvA, nvB = cur.nvB;
+#endif
+  s[0] = (s[0] + s2[0]) * nkA;
+  s[1] = (s[1] + s2[1]) * nkA;
+  s[2] = (s[2] + s2[2]) * nkB;
+  s[3] = (s[3] + s2[3]) * nkB;
+  if (n_valid < 16) {   // warp-uniform: only the last tile of a sequence
+    if (g >= n_valid) { s[0] = -CUDART_INF_F; s[1] = -CUDART_INF_F; nvA = 0.f; }
+    if (g + 8 >= n_valid) { s[2] = -CUDART_INF_F; s[3] = -CUDART_INF_F; nvB = 0.f; }
+  }
+
+  // ---- online softmax over the 16 tokens (columns 2t, 2t+1 of this thread) ----
+  float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
+#pragma unroll
+  for (int off = 4; off < 32; off <<= 1) {
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+  }
+  const float mn0 = fmaxf(st.m0, mx0), mn1 = fmaxf(st.m1, mx1);
+  if (__any_sync(0xffffffffu, (mn0 != st.m0) | (mn1 != st.m1))) {
+    const float al0 = ex2_approx(st.m0 - mn0), al1 = ex2_approx(st.m1 - mn1);
+    st.l0 *= al0; st.l1 *= al1;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { o[j][0] *= al0; o[j][1] *= al1; o[j][2] *= al0; o[j][3] *= al1; }
+    st.m0 = mn0; st.m1 = mn1;
+  }
+  const float p0 = ex2_approx(s[0] - mn0), p1 = ex2_approx(s[1] - mn1);
+  const float p2 = ex2_approx(s[2] - mn0), p3 = ex2_approx(s[3] - mn1);
+  st.l0 += p0 + p2;
+  st.l1 += p1 + p3;
+  // weights times value norms, transposed into the B-operand layout
+  const uint32_t pb0 = movmatrix_trans(pack_half2(p0 * nvA, p1 * nvA));
+  const uint32_t pb1 = movmatrix_trans(pack_half2(p2 * nvB, p3 * nvB));
+
+  // ---- values: O^T[128 dims][8 q heads] += V^T P^T ----
+  const uint32_t va[2] = {cur.v0.x, cur.v0.y}, vb[2] = {cur.v1.x, cur.v1.y};
+  const uint32_t vc[2] = {cur.v2.x, cur.v2.y}, vd[2] = {cur.v3.x, cur.v3.y};
+#pragma unroll
+  for (int w = 0; w < 2; ++w) {
+    const uint32_t x01 = (va[w] & 0xF0F0F0F0u) | ((vb[w] >> 4) & 0x0F0F0F0Fu);
+    const uint32_t y01 = ((va[w] << 4) & 0xF0F0F0F0u) | (vb[w] & 0x0F0F0F0Fu);
+    const uint32_t x23 = (vc[w] & 0xF0F0F0F0u) | ((vd[w] >> 4) & 0x0F0F0F0Fu);
+    const uint32_t y23 = ((vc[w] << 4) & 0xF0F0F0F0u) | (vd[w] & 0x0F0F0F0Fu);
+    mma16816(o[4 * w + 0], lut4<0>(lut, x01, lanebase), lut4<0>(lut, y01, lanebase),
+             lut4<0>(lut, x23, lanebase), lut4<0>(lut, y23, lanebase), pb0, pb1);
+    mma16816(o[4 * w + 1], lut4<1>(lut, x01, lanebase), lut4<1>(lut, y01, lanebase),
+             lut4<1>(lut, x23, lanebase), lut4<1>(lut, y23, lanebase), pb0, pb1);
+    mma16816(o[4 * w + 2], lut4<2>(lut, x01, lanebase), lut4<2>(lut, y01, lanebase),
+             lut4<2>(lut, x23, lanebase), lut4<2>(lut, y23, lanebase), pb0, pb1);
+    mma16816(o[4 * w + 3], lut4<3>(lut, x01, lanebase), lut4<3>(lut, y01, lanebase),
+             lut4<3>(lut, x23, lanebase), lut4<3>(lut, y23, lanebase), pb0, pb1);
+  }
 }
 
 template <bool VEC16>
@@ -346,92 +455,63 @@ tq_attn_mma_kernel(AttnArgs a) {
     }
   }
 
+  ThreadOffsets off;
+  off.kA = (int)(g * a.kp_sp + h * a.kp_sh + 16 * t);
+  off.kB = (int)(off.kA + 8 * a.kp_sp);
+  off.v0 = (int)(2 * t * a.vp_sp + h * a.vp_sh + 8 * g);
+  off.v1 = (int)(off.v0 + a.vp_sp);
+  off.v2 = (int)(off.v0 + 8 * a.vp_sp);
+  off.v3 = (int)(off.v0 + 9 * a.vp_sp);
+  off.nkA = (int)(g * a.kn_sp + h * a.kn_sh); off.nkB = (int)(off.nkA + 8 * a.kn_sp);
+  off.nvA = (int)(g * a.vn_sp + h * a.vn_sh); off.nvB = (int)(off.nvA + 8 * a.vn_sp);
+  off.nrm = (lane < 16) ? (int)(lane * a.kn_sp + h * a.kn_sh) : (int)((lane - 16) * a.vn_sp + h * a.vn_sh);
+
   float o[8][4];
 #pragma unroll
   for (int j = 0; j < 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
-  float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
+  SoftmaxState st{-CUDART_INF_F, -CUDART_INF_F, 0.f, 0.f};
 
-  int64_t tile = tile_begin + wj;
-  TileData cur;
-  if (tile < tile_end) load_tile<VEC16>(a, seq, h, (int)tile, tpb, g, t, cur);
-  for (; tile < tile_end; tile += wph) {
-    TileData nxt = cur;
-    if (tile + wph < tile_end) load_tile<VEC16>(a, seq, h, (int)(tile + wph), tpb, g, t, nxt);
-
-    // ---- scores: S^T[16 tokens][8 q heads] ----
-    float s[4] = {0.f, 0.f, 0.f, 0.f};
+  // This warp's tiles: tile_begin + wj, + wph, ...  Block ids are fetched 32 tiles at
+  // a time (lane i holds the block of the i-th tile of the batch) and broadcast.
+  const int64_t first = tile_begin + wj;
+  const int n_tiles = first < tile_end ? (int)((tile_end - first + wph - 1) / wph) : 0;
+  for (int base = 0; base < n_tiles; base += 32) {
+    const int cnt = n_tiles - base < 32 ? n_tiles - base : 32;
+    int64_t my_pb = 0;
+    if (lane < cnt) my_pb = phys_block(a, seq, (int)((first + (int64_t)(base + lane) * wph) / tpb));
+    TileData buf0, buf1;
     {
-      const uint32_t wa[4] = {cur.kA.x, cur.kA.y, cur.kA.z, cur.kA.w};
-      const uint32_t wb[4] = {cur.kB.x, cur.kB.y, cur.kB.z, cur.kB.w};
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        mma16816(s, lut4<0>(lut, wa[w], lanebase), lut4<0>(lut, wb[w], lanebase),
-                 lut4<1>(lut, wa[w], lanebase), lut4<1>(lut, wb[w], lanebase),
-                 bq[2 * w][0], bq[2 * w][1]);
-        mma16816(s, lut4<2>(lut, wa[w], lanebase), lut4<2>(lut, wb[w], lanebase),
-                 lut4<3>(lut, wa[w], lanebase), lut4<3>(lut, wb[w], lanebase),
-                 bq[2 * w + 1][0], bq[2 * w + 1][1]);
+      const int64_t tile = first + (int64_t)base * wph;
+      load_tile<VEC16>(a, off, __shfl_sync(0xffffffffu, my_pb, 0), (int)(tile % tpb) * 16, lane, buf0);
+    }
+#pragma unroll 1
+    for (int i = 0; i < cnt; i += 2) {
+      const int64_t tile = first + (int64_t)(base + i) * wph;
+      if (i + 1 < cnt) {
+        const int64_t pb = __shfl_sync(0xffffffffu, my_pb, i + 1);
+        load_tile<VEC16>(a, off, pb, (int)((tile + wph) % tpb) * 16, lane, buf1);
+      }
+      {
+        const int64_t rem = ctx - tile * 16;
+        process_tile(lut, lanebase, g, bq, buf0, rem < 16 ? (int)rem : 16, o, st);
+      }
+      if (i + 1 < cnt) {
+        if (i + 2 < cnt) {
+          const int64_t pb = __shfl_sync(0xffffffffu, my_pb, i + 2);
+          load_tile<VEC16>(a, off, pb, (int)((tile + 2 * wph) % tpb) * 16, lane, buf0);
+        }
+        const int64_t rem = ctx - (tile + wph) * 16;
+        process_tile(lut, lanebase, g, bq, buf1, rem < 16 ? (int)rem : 16, o, st);
       }
     }
-    const int64_t tokA = tile * 16 + g;
-    const bool okA = tokA < ctx, okB = tokA + 8 < ctx;
-    s[0] = okA ? s[0] * cur.nkA : -CUDART_INF_F;
-    s[1] = okA ? s[1] * cur.nkA : -CUDART_INF_F;
-    s[2] = okB ? s[2] * cur.nkB : -CUDART_INF_F;
-    s[3] = okB ? s[3] * cur.nkB : -CUDART_INF_F;
-
-    // ---- online softmax over the 16 tokens (columns 2t, 2t+1 of this thread) ----
-    float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
-#pragma unroll
-    for (int off = 4; off < 32; off <<= 1) {
-      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
-      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
-    }
-    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-    const float al0 = exp2f(m0 - mn0), al1 = exp2f(m1 - mn1);
-    m0 = mn0; m1 = mn1;
-    const float p0 = exp2f(s[0] - mn0), p1 = exp2f(s[1] - mn1);
-    const float p2 = exp2f(s[2] - mn0), p3 = exp2f(s[3] - mn1);
-    l0 = l0 * al0 + p0 + p2;
-    l1 = l1 * al1 + p1 + p3;
-    if (__any_sync(0xffffffffu, (al0 != 1.f) | (al1 != 1.f))) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) { o[j][0] *= al0; o[j][1] *= al1; o[j][2] *= al0; o[j][3] *= al1; }
-    }
-    // weights times value norms, transposed into the B-operand layout
-    const uint32_t h01 = pack_half2(okA ? p0 * cur.nvA : 0.f, okA ? p1 * cur.nvA : 0.f);
-    const uint32_t h23 = pack_half2(okB ? p2 * cur.nvB : 0.f, okB ? p3 * cur.nvB : 0.f);
-    const uint32_t pb0 = movmatrix_trans(h01);
-    const uint32_t pb1 = movmatrix_trans(h23);
-
-    // ---- values: O^T[128 dims][8 q heads] += V^T P^T ----
-    {
-      const uint32_t va[2] = {cur.v0.x, cur.v0.y}, vb[2] = {cur.v1.x, cur.v1.y};
-      const uint32_t vc[2] = {cur.v2.x, cur.v2.y}, vd[2] = {cur.v3.x, cur.v3.y};
-#pragma unroll
-      for (int w = 0; w < 2; ++w) {
-        const uint32_t x01 = (va[w] & 0xF0F0F0F0u) | ((vb[w] >> 4) & 0x0F0F0F0Fu);
-        const uint32_t y01 = ((va[w] << 4) & 0xF0F0F0F0u) | (vb[w] & 0x0F0F0F0Fu);
-        const uint32_t x23 = (vc[w] & 0xF0F0F0F0u) | ((vd[w] >> 4) & 0x0F0F0F0Fu);
-        const uint32_t y23 = ((vc[w] << 4) & 0xF0F0F0F0u) | (vd[w] & 0x0F0F0F0Fu);
-        mma16816(o[4 * w + 0], lut4<0>(lut, x01, lanebase), lut4<0>(lut, y01, lanebase),
-                 lut4<0>(lut, x23, lanebase), lut4<0>(lut, y23, lanebase), pb0, pb1);
-        mma16816(o[4 * w + 1], lut4<1>(lut, x01, lanebase), lut4<1>(lut, y01, lanebase),
-                 lut4<1>(lut, x23, lanebase), lut4<1>(lut, y23, lanebase), pb0, pb1);
-        mma16816(o[4 * w + 2], lut4<2>(lut, x01, lanebase), lut4<2>(lut, y01, lanebase),
-                 lut4<2>(lut, x23, lanebase), lut4<2>(lut, y23, lanebase), pb0, pb1);
-        mma16816(o[4 * w + 3], lut4<3>(lut, x01, lanebase), lut4<3>(lut, y01, lanebase),
-                 lut4<3>(lut, x23, lanebase), lut4<3>(lut, y23, lanebase), pb0, pb1);
-      }
-    }
-    cur = nxt;
   }
 
   // ---- partial for this warp ----
+  float l0 = st.l0, l1 = st.l1;
 #pragma unroll
-  for (int off = 4; off < 32; off <<= 1) {
-    l0 += __shfl_xor_sync(0xffffffffu, l0, off);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+  for (int offs = 4; offs < 32; offs <<= 1) {
+    l0 += __shfl_xor_sync(0xffffffffu, l0, offs);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, offs);
   }
   const int part = split * wph + wj;
 #pragma unroll
@@ -444,11 +524,12 @@ tq_attn_mma_kernel(AttnArgs a) {
     for (int j = 0; j < 8; ++j)   // M-tile j: row g -> dim 16g+2j, row g+8 -> dim 16g+2j+1
       *reinterpret_cast<float2*>(pa + 16 * g + 2 * j) = make_float2(o[j][e], o[j][2 + e]);
     if (g == 0) {
-      a.part_ml[(row * a.num_parts + part) * 2] = e ? m1 : m0;
+      a.part_ml[(row * a.num_parts + part) * 2] = e ? st.m1 : st.m0;
       a.part_ml[(row * a.num_parts + part) * 2 + 1] = e ? l1 : l0;
     }
   }
 }
+
 
 static inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
@@ -463,7 +544,7 @@ static Plan make_plan(int num_seqs, int num_q_heads, int num_kv_heads, int head_
   Plan p;
   const int G = num_q_heads / num_kv_heads;
   p.mma = (head_dim == 128 && bits == 4 && G >= 1 && G <= 8 && block_size % 16 == 0);
-  if (blocks_per_split <= 0) blocks_per_split = (32 * 16 + block_size - 1) / block_size;  // ~512 tokens
+  if (blocks_per_split <= 0) blocks_per_split = (64 * 16 + block_size - 1) / block_size;  // ~1024 tokens
   if (blocks_per_split > max_blocks_per_seq) blocks_per_split = max_blocks_per_seq > 0 ? max_blocks_per_seq : 1;
   p.blocks_per_split = blocks_per_split;
   p.num_splits = max_blocks_per_seq > 0 ? (max_blocks_per_seq + blocks_per_split - 1) / blocks_per_split : 1;

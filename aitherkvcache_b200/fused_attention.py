@@ -43,6 +43,52 @@ class TQPagedAttention:
         self.packed_dim = tq._packed_dim
         self.num_query_heads = num_query_heads
         self._workspace: Optional[torch.Tensor] = None
+        self._params = None
+        self._params_key = None
+
+    def _build_params(self, dev, query, k_packed, k_norms, v_packed, v_norms, block_tables, context_lens,
+                      block_size, num_kv_heads, out, raw_out, scale) -> "_lib.TQAttnParams":
+        num_seqs, num_q_heads, head_dim = query.shape
+        for name, t in (("k_packed", k_packed), ("v_packed", v_packed)):
+            if t.dtype != torch.uint8 or t.stride(-1) != 1:
+                raise ValueError(f"{name} must be uint8 with a contiguous last dimension")
+        if k_norms.dtype != torch.float32 or v_norms.dtype != torch.float32:
+            raise TypeError("norm tensors must be float32")
+        max_blocks = block_tables.shape[1] if block_tables.dim() == 2 else 0
+        L = _lib.lib()
+        nbytes = L.akv_tq_paged_attn_workspace_bytes(num_seqs, num_q_heads, num_kv_heads, head_dim,
+                                                     self.bits, block_size, max_blocks, self.SPLITK_BLOCKS)
+        ws = self._get_workspace(nbytes, dev)
+        p = _lib.TQAttnParams()
+        p.query, p.q_dtype = query.data_ptr(), _lib.float_code(query)
+        p.q_stride_seq, p.q_stride_head = query.stride(0), query.stride(1)
+        p.k_packed = k_packed.data_ptr()
+        p.kp_stride_blk, p.kp_stride_pos, p.kp_stride_head = k_packed.stride(0), k_packed.stride(1), k_packed.stride(2)
+        p.k_norms = k_norms.data_ptr()
+        p.kn_stride_blk, p.kn_stride_pos, p.kn_stride_head = k_norms.stride(0), k_norms.stride(1), k_norms.stride(2)
+        p.v_packed = v_packed.data_ptr()
+        p.vp_stride_blk, p.vp_stride_pos, p.vp_stride_head = v_packed.stride(0), v_packed.stride(1), v_packed.stride(2)
+        p.v_norms = v_norms.data_ptr()
+        p.vn_stride_blk, p.vn_stride_pos, p.vn_stride_head = v_norms.stride(0), v_norms.stride(1), v_norms.stride(2)
+        p.block_tables, p.bt_dtype = block_tables.data_ptr(), _lib.index_code(block_tables)
+        p.bt_stride_seq = block_tables.stride(0) if block_tables.dim() == 2 else 0
+        p.context_lens, p.cl_dtype = context_lens.data_ptr(), _lib.index_code(context_lens)
+        p.num_seqs, p.num_q_heads, p.num_kv_heads, p.head_dim = num_seqs, num_q_heads, num_kv_heads, head_dim
+        p.block_size, p.max_blocks_per_seq, p.num_blocks = block_size, max_blocks, k_packed.shape[0]
+        p.bits = self.bits
+        p.rotation, p.rotation_t, p.centroids = (self.rotation.data_ptr(), self.rotation_T.data_ptr(),
+                                                 self.centroids.data_ptr())
+        p.scale = self.scale if scale is None else float(scale)
+        if raw_out is not None:
+            assert raw_out.dtype == torch.float32 and raw_out.is_contiguous()
+            assert raw_out.numel() == num_seqs * num_q_heads * (head_dim + 2)
+            p.raw_out = raw_out.data_ptr()
+        else:
+            p.out, p.out_dtype = out.data_ptr(), _lib.float_code(out)
+            p.out_stride_seq, p.out_stride_head = out.stride(0), out.stride(1)
+        p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+        p.blocks_per_split = self.SPLITK_BLOCKS
+        return p
 
     def _get_workspace(self, nbytes: int, device) -> torch.Tensor:
         ws = self._workspace
@@ -84,58 +130,32 @@ class TQPagedAttention:
             query = query.float()
         if query.stride(-1) != 1:
             query = query.contiguous()
-        for name, t in (("k_packed", k_packed), ("v_packed", v_packed)):
-            if t.dtype != torch.uint8 or t.stride(-1) != 1:
-                raise ValueError(f"{name} must be uint8 with a contiguous last dimension")
-        if k_norms.dtype != torch.float32 or v_norms.dtype != torch.float32:
-            raise TypeError("norm tensors must be float32")
         if block_tables.stride(-1) != 1:
             block_tables = block_tables.contiguous()
         context_lens = context_lens.contiguous()
-        max_blocks = block_tables.shape[1] if block_tables.dim() == 2 else 0
         if out is None and raw_out is None:
             out = torch.empty(num_seqs, num_q_heads, head_dim, dtype=query.dtype, device=dev)
+        target = raw_out if raw_out is not None else out
 
-        L = _lib.lib()
-        nbytes = L.akv_tq_paged_attn_workspace_bytes(num_seqs, num_q_heads, num_kv_heads, head_dim,
-                                                     self.bits, block_size, max_blocks, self.SPLITK_BLOCKS)
-        ws = self._get_workspace(nbytes, dev)
-        p = _lib.TQAttnParams()
-        p.query, p.q_dtype = query.data_ptr(), _lib.float_code(query)
-        p.q_stride_seq, p.q_stride_head = query.stride(0), query.stride(1)
-        p.k_packed = k_packed.data_ptr()
-        p.kp_stride_blk, p.kp_stride_pos, p.kp_stride_head = k_packed.stride(0), k_packed.stride(1), k_packed.stride(2)
-        p.k_norms = k_norms.data_ptr()
-        p.kn_stride_blk, p.kn_stride_pos, p.kn_stride_head = k_norms.stride(0), k_norms.stride(1), k_norms.stride(2)
-        p.v_packed = v_packed.data_ptr()
-        p.vp_stride_blk, p.vp_stride_pos, p.vp_stride_head = v_packed.stride(0), v_packed.stride(1), v_packed.stride(2)
-        p.v_norms = v_norms.data_ptr()
-        p.vn_stride_blk, p.vn_stride_pos, p.vn_stride_head = v_norms.stride(0), v_norms.stride(1), v_norms.stride(2)
-        p.block_tables, p.bt_dtype = block_tables.data_ptr(), _lib.index_code(block_tables)
-        p.bt_stride_seq = block_tables.stride(0) if block_tables.dim() == 2 else 0
-        p.context_lens, p.cl_dtype = context_lens.data_ptr(), _lib.index_code(context_lens)
-        p.num_seqs, p.num_q_heads, p.num_kv_heads, p.head_dim = num_seqs, num_q_heads, num_kv_heads, head_dim
-        p.block_size, p.max_blocks_per_seq, p.num_blocks = block_size, max_blocks, k_packed.shape[0]
-        p.bits = self.bits
-        p.rotation, p.rotation_t, p.centroids = (self.rotation.data_ptr(), self.rotation_T.data_ptr(),
-                                                 self.centroids.data_ptr())
-        p.scale = self.scale if scale is None else float(scale)
+        # The argument block only depends on pointers, shapes and strides: reuse it while
+        # the caller keeps passing the same buffers (the steady state of a decode loop).
+        tensors = (query, k_packed, k_norms, v_packed, v_norms, block_tables, context_lens, target)
+        key = tuple((t.data_ptr(), t.shape, t.stride(), t.dtype) for t in tensors) + (
+            block_size, num_kv_heads, raw_out is not None, scale, self.SPLITK_BLOCKS)
+        p = self._params if key == self._params_key else None
+        if p is None:
+            p = self._build_params(dev, query, k_packed, k_norms, v_packed, v_norms, block_tables,
+                                   context_lens, block_size, num_kv_heads, out, raw_out, scale)
+            self._params, self._params_key = p, key
+        p.stream = _lib.stream_ptr(dev)
         if kernel_events is not None:
             for ev in kernel_events:      # torch creates the CUDA event on first record
                 if not ev.cuda_event:
                     ev.record(torch.cuda.current_stream(dev))
             p.ev_kernel_start, p.ev_kernel_stop = kernel_events[0].cuda_event, kernel_events[1].cuda_event
-        if raw_out is not None:
-            assert raw_out.dtype == torch.float32 and raw_out.is_contiguous()
-            assert raw_out.numel() == num_seqs * num_q_heads * (head_dim + 2)
-            p.raw_out = raw_out.data_ptr()
         else:
-            p.out, p.out_dtype = out.data_ptr(), _lib.float_code(out)
-            p.out_stride_seq, p.out_stride_head = out.stride(0), out.stride(1)
-        p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
-        p.blocks_per_split = self.SPLITK_BLOCKS
-        p.stream = _lib.stream_ptr(dev)
+            p.ev_kernel_start = p.ev_kernel_stop = None
         with torch.cuda.device(dev):
-            rc = L.akv_tq_paged_attn(ctypes.byref(p))
+            rc = _lib.lib().akv_tq_paged_attn(ctypes.byref(p))
         _lib.check(rc, "akv_tq_paged_attn")
         return raw_out if raw_out is not None else out
