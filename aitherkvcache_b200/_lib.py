@@ -47,6 +47,36 @@ class TQAttnParams(C.Structure):
     ]
 
 
+class HybridTables(C.Structure):
+    """Mirror of ``akv_hybrid_tables``."""
+    _fields_ = [
+        ("head_dim", c_int), ("packed_dim", c_int),
+        ("group_index", c_vp), ("num_index_heads", c_int),
+        ("had_signs", c_vp), ("qjl_signs", c_vp), ("centroids", c_vp), ("boundaries", c_vp),
+        ("qjl_scale0", c_f), ("qjl_scale1", c_f),
+    ]
+
+
+class HybridAttnParams(C.Structure):
+    """Mirror of ``akv_hybrid_attn_params``."""
+    _fields_ = [
+        ("query", c_vp), ("q_dtype", c_int), ("q_stride_seq", c_i64), ("q_stride_head", c_i64),
+        ("k_cache", c_vp), ("k_stride_blk", c_i64), ("k_stride_pos", c_i64), ("k_stride_head", c_i64),
+        ("v_cache", c_vp), ("v_stride_blk", c_i64), ("v_stride_pos", c_i64), ("v_stride_head", c_i64),
+        ("block_tables", c_vp), ("bt_dtype", c_int), ("bt_stride_seq", c_i64),
+        ("context_lens", c_vp), ("cl_dtype", c_int),
+        ("num_seqs", c_int), ("num_q_heads", c_int), ("num_kv_heads", c_int), ("block_size", c_int),
+        ("max_blocks_per_seq", c_int),
+        ("num_blocks", c_i64),
+        ("tables", C.POINTER(HybridTables)),
+        ("scale", c_f),
+        ("out", c_vp), ("out_dtype", c_int), ("out_stride_seq", c_i64), ("out_stride_head", c_i64),
+        ("workspace", c_vp), ("workspace_bytes", C.c_size_t),
+        ("blocks_per_split", c_int),
+        ("stream", c_vp),
+    ]
+
+
 _SIGNATURES = {
     "akv_version": (c_int, []),
     "akv_last_error": (C.c_char_p, []),
@@ -59,6 +89,10 @@ _SIGNATURES = {
     "akv_tq_paged_attn": (c_int, [C.POINTER(TQAttnParams)]),
     "akv_tq_paged_attn_static_scratch_bytes": (C.c_size_t, []),
     "akv_tq_paged_attn_static": (c_int, [C.POINTER(TQAttnParams)]),
+    "akv_hybrid_encode": (c_int, [c_vp, c_int, c_i64, c_i64, C.POINTER(HybridTables), c_vp, c_i64, c_vp]),
+    "akv_hybrid_decode": (c_int, [c_vp, c_i64, c_i64, C.POINTER(HybridTables), c_vp, c_int, c_vp]),
+    "akv_hybrid_paged_attn_workspace_bytes": (C.c_size_t, [c_int] * 5),
+    "akv_hybrid_paged_attn": (c_int, [C.POINTER(HybridAttnParams)]),
     "akv_lse_merge": (c_int, [c_vp, c_int, c_int, c_int, c_int, c_vp, c_vp, c_int, c_i64, c_i64, c_vp]),
 }
 

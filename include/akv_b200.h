@@ -140,6 +140,58 @@ int akv_lse_merge(const float* parts, int num_parts, int num_seqs, int num_q_hea
                   const float* rotation, void* out, int out_dtype, int64_t out_stride_seq,
                   int64_t out_stride_head, void* stream);
 
+/* ------------------------------------------------------------------------
+ * Hybrid split-group codec (tq35 / tq25, head_dim 128)
+ * ---------------------------------------------------------------------- */
+
+/* Tables of one HybridTurboQuant instance (aither_kvcache/hybrid_quantizer.py:486-547,
+ * calibrate/calibrate_uniform :553-603).  All arrays live on the device.
+ *   group_index [num_index_heads][head_dim] int32: the dims of group 0, then of group 1
+ *   had_signs / qjl_signs [head_dim]: +-1, group 0 then group 1
+ *   centroids / boundaries [16]: group 0 in [0..8), group 1 in [8..16) (unused tail ignored)
+ * packed_dim selects the mode: 64 = tq35, 44 = tq25. */
+typedef struct akv_hybrid_tables {
+  int head_dim, packed_dim;
+  const int* group_index; int num_index_heads;
+  const float* had_signs; const float* qjl_signs;
+  const float* centroids; const float* boundaries;
+  float qjl_scale0, qjl_scale1;
+} akv_hybrid_tables;
+
+/* Replaces HybridTurboQuant.encode (hybrid_quantizer.py:616-779): x [n_rows, 128] ->
+ * packed [n_rows, packed_dim] (codes | residual sign bits | fp16 norm | fp16 residual norm,
+ * per group).  Row n uses index head n % num_index_heads. */
+int akv_hybrid_encode(const void* x, int x_dtype, int64_t n_rows, int64_t x_row_stride,
+                      const akv_hybrid_tables* tables, uint8_t* packed, int64_t packed_row_stride,
+                      void* stream);
+
+/* Replaces HybridTurboQuant.decode (hybrid_quantizer.py:785-933): out [n_rows, 128] contiguous. */
+int akv_hybrid_decode(const uint8_t* packed, int64_t packed_row_stride, int64_t n_rows,
+                      const akv_hybrid_tables* tables, void* out, int out_dtype, void* stream);
+
+/* Paged decode attention over tq35 records without reconstructing K/V.  Replaces the
+ * decompress-then-SDPA body of tq::hybrid_decode_step (vllm/hooks.py:297-345).
+ *   k_cache / v_cache [num_blocks, block_size, num_kv_heads, 64] uint8 (strided views allowed) */
+typedef struct akv_hybrid_attn_params {
+  const void* query; int q_dtype; int64_t q_stride_seq, q_stride_head;
+  const uint8_t* k_cache; int64_t k_stride_blk, k_stride_pos, k_stride_head;
+  const uint8_t* v_cache; int64_t v_stride_blk, v_stride_pos, v_stride_head;
+  const void* block_tables; int bt_dtype; int64_t bt_stride_seq;
+  const void* context_lens; int cl_dtype;
+  int num_seqs, num_q_heads, num_kv_heads, block_size, max_blocks_per_seq;
+  int64_t num_blocks;
+  const akv_hybrid_tables* tables;   /* HOST pointer to the struct; its arrays are device arrays */
+  float scale;
+  void* out; int out_dtype; int64_t out_stride_seq, out_stride_head;
+  void* workspace; size_t workspace_bytes;
+  int blocks_per_split;
+  void* stream;
+} akv_hybrid_attn_params;
+
+size_t akv_hybrid_paged_attn_workspace_bytes(int num_seqs, int num_q_heads, int block_size,
+                                             int max_blocks_per_seq, int blocks_per_split);
+int akv_hybrid_paged_attn(const akv_hybrid_attn_params* params);
+
 #ifdef __cplusplus
 }
 #endif
