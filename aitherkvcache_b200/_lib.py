@@ -77,6 +77,27 @@ class HybridAttnParams(C.Structure):
     ]
 
 
+class TriDecodeParams(C.Structure):
+    """Mirror of ``akv_tri_decode_params``."""
+    _fields_ = [
+        ("query", c_vp), ("q_dtype", c_int), ("q_stride_batch", c_i64), ("q_stride_head", c_i64),
+        ("k_indices", c_vp), ("k_packed", c_vp), ("k_scales", c_vp),
+        ("v_indices", c_vp), ("v_packed", c_vp), ("v_scales", c_vp),
+        ("batch", c_int), ("seq_len", c_int), ("num_kv_heads", c_int), ("num_q_heads", c_int),
+        ("head_dim", c_int), ("num_freqs", c_int),
+        ("key_positions", c_vp), ("key_pos_start", c_i64),
+        ("query_pos", c_vp), ("query_pos_default", c_i64),
+        ("theta", c_vp),
+        ("scale", c_f),
+        ("out", c_vp), ("raw_out", c_vp),
+        ("workspace", c_vp), ("workspace_bytes", C.c_size_t),
+        ("tokens_per_split", c_int),
+        ("stream", c_vp),
+        ("ev_kernel_start", c_vp), ("ev_kernel_stop", c_vp),
+        ("scores_out", c_vp),
+    ]
+
+
 _SIGNATURES = {
     "akv_version": (c_int, []),
     "akv_last_error": (C.c_char_p, []),
@@ -93,6 +114,9 @@ _SIGNATURES = {
     "akv_hybrid_decode": (c_int, [c_vp, c_i64, c_i64, C.POINTER(HybridTables), c_vp, c_int, c_vp]),
     "akv_hybrid_paged_attn_workspace_bytes": (C.c_size_t, [c_int] * 5),
     "akv_hybrid_paged_attn": (c_int, [C.POINTER(HybridAttnParams)]),
+    "akv_tri_encode": (c_int, [c_vp, c_int, c_i64, c_i64, c_int, c_int, c_vp, c_vp, c_vp, c_vp]),
+    "akv_tri_decode_workspace_bytes": (C.c_size_t, [c_int] * 4),
+    "akv_tri_decode_step": (c_int, [C.POINTER(TriDecodeParams)]),
     "akv_lse_merge": (c_int, [c_vp, c_int, c_int, c_int, c_int, c_vp, c_vp, c_int, c_i64, c_i64, c_vp]),
 }
 

@@ -86,4 +86,22 @@ __device__ __forceinline__ int extract_code(const uint8_t* row, int k, int bits,
   return (w >> (16 - bits - (bit & 7))) & ((1 << bits) - 1);
 }
 
+// LSE merge of split partials (kernel and launcher live in tq_attention.cu).
+enum { MERGE_ROTATE = 0, MERGE_NORMALIZE = 1, MERGE_RAW = 2 };
+
+struct MergeArgs {
+  int mode;
+  const float* acc; int64_t acc_row, acc_part;
+  const float* ml; int64_t ml_row, ml_part;
+  int np;
+  const void* context_lens; int cl_dtype; int num_q_heads;
+  int tokens_per_split, warps_per_head;   // used when context_lens != nullptr
+  int D;
+  const float* rot;              // R row-major (MERGE_ROTATE only)
+  void* out; int out_dtype; int64_t out_ss, out_sh;
+  float* raw_out;
+};
+
+int launch_merge(const MergeArgs& a, int rows, cudaStream_t st);
+
 }  // namespace akv

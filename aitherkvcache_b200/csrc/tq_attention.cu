@@ -80,21 +80,6 @@ __global__ void akv_qrot_kernel(const void* __restrict__ q, int q_dtype, int64_t
 // MERGE_RAW: the merged, un-normalised (m, l, acc) goes to raw_out as [row][D+2]
 // for a later cross-device merge.
 // ---------------------------------------------------------------------------
-enum { MERGE_ROTATE = 0, MERGE_NORMALIZE = 1, MERGE_RAW = 2 };
-
-struct MergeArgs {
-  int mode;
-  const float* acc; int64_t acc_row, acc_part;
-  const float* ml; int64_t ml_row, ml_part;
-  int np;
-  const void* context_lens; int cl_dtype; int num_q_heads;
-  int tokens_per_split, warps_per_head;   // used when context_lens != nullptr
-  int D;
-  const float* rot;              // R row-major (MERGE_ROTATE only)
-  void* out; int out_dtype; int64_t out_ss, out_sh;
-  float* raw_out;
-};
-
 __global__ void akv_merge_kernel(MergeArgs a) {
   extern __shared__ float sm[];   // [D]
   const int row = blockIdx.x;
@@ -146,6 +131,11 @@ __global__ void akv_merge_kernel(MergeArgs a) {
     for (int i = 0; i < a.D; ++i) x = __fmaf_rn(sm[i], a.rot[(int64_t)i * a.D + j], x);
     store_from_float(a.out, a.out_dtype, seq * a.out_ss + qh * a.out_sh + j, x);
   }
+}
+
+int launch_merge(const MergeArgs& a, int rows, cudaStream_t st) {
+  akv_merge_kernel<<<rows, a.D < 128 ? a.D : 128, a.D * sizeof(float), st>>>(a);
+  return check_launch("akv_merge_kernel");
 }
 
 // ---------------------------------------------------------------------------

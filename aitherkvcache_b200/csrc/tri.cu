@@ -1,0 +1,443 @@
+// TriAttention: spectral KV codec (top-F RoPE pairs, int4 coefficients) and the
+// trig-series decode step.
+//
+// Reference: aither_kvcache/triattention/encoder.py:73-149 (encode),
+// scorer.py:84-208 (scores), attention.py:186-280 (softmax + scattered value sum).
+//
+// decode step, per (batch, kv head), for every cached token:
+//   k0,k1   = dequantised pair coefficients of the F retained pairs
+//   phi     = float32( float(pos_k) - float(pos_q) ) * theta[pair]      (same float32 product
+//             as the reference; reduced mod 2*pi with a three-term Cody-Waite step)
+//   k'      = the pair rotated by phi: (k0 cos - k1 sin, k1 cos + k0 sin)
+//   score_h = scale * sum_f ( q_h[2i] k'_0 + q_h[2i+1] k'_1 )
+// which equals the reference's c*cos + s*sin series.  The rotated sparse keys and the
+// sparse values of a 32-token tile are written into dense fp16 tiles in shared memory
+// (zero elsewhere) and both products run on mma.sync m16n8k16, the 4..8 query heads of the
+// GQA group in the N dimension; softmax is online over tiles, partials (m, l, acc) are
+// merged by the common LSE merge kernel.
+#include "common.cuh"
+#include <math_constants.h>
+
+namespace akv {
+
+// ---------------------------------------------------------------------------
+// encode: one thread per vector
+// ---------------------------------------------------------------------------
+constexpr int TE_THREADS = 64;
+constexpr int TE_LD = 129;
+
+template <int F>
+__global__ void __launch_bounds__(TE_THREADS)
+tri_encode_kernel(const void* __restrict__ x, int x_dtype, int64_t n_rows, int64_t x_row_stride,
+                  uint8_t* __restrict__ indices, uint8_t* __restrict__ packed, __half* __restrict__ scales) {
+  constexpr int D = 128, P = 64;
+  __shared__ float xs[TE_THREADS * TE_LD];
+  const int tid = threadIdx.x;
+  const int64_t row0 = (int64_t)blockIdx.x * TE_THREADS;
+  for (int e = tid; e < TE_THREADS * D; e += TE_THREADS) {
+    const int r = e / D, c = e % D;
+    const int64_t n = row0 + r;
+    xs[r * TE_LD + c] = (n < n_rows) ? load_as_float(x, x_dtype, n * x_row_stride + c) : 0.f;
+  }
+  __syncthreads();
+  const int64_t n = row0 + tid;
+  if (n >= n_rows) return;
+  const float* v = xs + tid * TE_LD;
+  float e[P];
+#pragma unroll
+  for (int i = 0; i < P; ++i) e[i] = __fadd_rn(__fmul_rn(v[2 * i], v[2 * i]), __fmul_rn(v[2 * i + 1], v[2 * i + 1]));
+  // F rounds of arg-max; ties go to the lower pair id
+  unsigned long long mask = 0ull;
+  for (int r = 0; r < F; ++r) {
+    float best = -1.f;
+    int bi = 0;
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+      const bool taken = (mask >> i) & 1ull;
+      if (!taken && e[i] > best) { best = e[i]; bi = i; }
+    }
+    mask |= 1ull << bi;
+  }
+  int ids[F];
+  int c = 0;
+  for (int i = 0; i < P && c < F; ++i)
+    if ((mask >> i) & 1ull) ids[c++] = i;
+  float amax = 0.f;
+  for (int f = 0; f < F; ++f) {
+    amax = fmaxf(amax, fabsf(v[2 * ids[f]]));
+    amax = fmaxf(amax, fabsf(v[2 * ids[f] + 1]));
+  }
+  const float scale = fmaxf(amax, 1e-8f);
+  uint8_t oi[F], op[F];
+  for (int f = 0; f < F; ++f) {
+    float q0 = rintf(__fmul_rn(__fadd_rn(__fdiv_rn(v[2 * ids[f]], scale), 1.0f), 7.5f));
+    float q1 = rintf(__fmul_rn(__fadd_rn(__fdiv_rn(v[2 * ids[f] + 1], scale), 1.0f), 7.5f));
+    q0 = fminf(fmaxf(q0, 0.f), 15.f);
+    q1 = fminf(fmaxf(q1, 0.f), 15.f);
+    oi[f] = (uint8_t)ids[f];
+    op[f] = (uint8_t)(((int)q0 << 4) | (int)q1);
+  }
+  for (int f = 0; f < F; ++f) {
+    indices[n * F + f] = oi[f];
+    packed[n * F + f] = op[f];
+  }
+  scales[n] = __float2half_rn(scale);
+}
+
+// ---------------------------------------------------------------------------
+// decode step
+// ---------------------------------------------------------------------------
+struct TriArgs {
+  const uint8_t* k_idx; const uint8_t* k_packed; const __half* k_scales;
+  const uint8_t* v_idx; const uint8_t* v_packed; const __half* v_scales;
+  int B, S, KVH, QH, F;
+  const void* query; int q_dtype; int64_t q_sb, q_sh;   // [B,QH,128]
+  const int64_t* key_positions;   // [B,S] or null: position = key_pos_start + s
+  int64_t key_pos_start;
+  const int64_t* query_pos;       // [B] or null: query_pos_default
+  int64_t query_pos_default;
+  const float* theta;             // [64]
+  float premul;                   // scale * log2(e)
+  int tokens_per_split, num_parts;
+  float* part_acc;                // [B*QH][NP][128]
+  float* part_ml;                 // [B*QH][NP][2]
+  float* scores_out;              // optional [B][QH][S] pre-softmax logits (natural units)
+};
+
+constexpr int TD_WARPS = 4;
+constexpr int TD_LD = 136;                       // halves per row of the dense tiles (272 B: conflict-free ldmatrix)
+constexpr int TD_TILE_HALVES = 32 * TD_LD;
+constexpr size_t TD_SMEM = (size_t)TD_WARPS * 2 * TD_TILE_HALVES * sizeof(__half);
+
+__device__ __forceinline__ void mma16816_tri(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const __half* p) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const __half* p) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+__device__ __forceinline__ uint32_t movmatrix_trans_tri(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(y) : "r"(x));
+  return y;
+}
+
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__device__ __forceinline__ float ex2a(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// sin and cos of a float32 phase of magnitude up to ~2e5 rad: subtract n * 2*pi with 2*pi split
+// into three float32 terms (FMA keeps each product exact), then the hardware approximations
+// on the reduced argument in [-pi, pi] (absolute error ~5e-7).
+__device__ __forceinline__ void sincos_reduced(float phi, float& s, float& c) {
+  const float n = rintf(phi * 0.15915494309189535f);
+  float r = __fmaf_rn(-n, 6.2831854820251465f, phi);
+  r = __fmaf_rn(-n, -1.7484555314695172e-07f, r);
+  r = __fmaf_rn(-n, -6.8604980400235275e-15f, r);
+  s = __sinf(r);
+  c = __cosf(r);
+}
+
+template <int F>
+__global__ void __launch_bounds__(TD_WARPS * 32)
+tri_decode_kernel(TriArgs a) {
+  extern __shared__ __align__(16) __half tiles[];
+  __shared__ float s_theta[64];
+  __shared__ float s_deq[16];
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  if (threadIdx.x < 64) s_theta[threadIdx.x] = a.theta[threadIdx.x];
+  if (threadIdx.x < 16) s_deq[threadIdx.x] = __fsub_rn(__fdiv_rn((float)threadIdx.x, 7.5f), 1.0f);
+  __syncthreads();
+  __half* kt = tiles + (size_t)warp * 2 * TD_TILE_HALVES;   // [32 tokens][TD_LD]: rotated keys, dense
+  __half* vt = kt + TD_TILE_HALVES;                          // [32 tokens][TD_LD]: values, dense
+  const int G = a.QH / a.KVH;
+
+  // query fragments: B operand [k = dim][n = q head of the group]
+  uint32_t bq[8][2];
+  {
+    const int qh = kvh * G + (g < G ? g : 0);
+    const int64_t base = (int64_t)b * a.q_sb + (int64_t)qh * a.q_sh;
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      float f0 = load_as_float(a.query, a.q_dtype, base + 16 * kk + 2 * t) * a.premul;
+      float f1 = load_as_float(a.query, a.q_dtype, base + 16 * kk + 2 * t + 1) * a.premul;
+      float f2 = load_as_float(a.query, a.q_dtype, base + 16 * kk + 2 * t + 8) * a.premul;
+      float f3 = load_as_float(a.query, a.q_dtype, base + 16 * kk + 2 * t + 9) * a.premul;
+      if (g >= G) { f0 = f1 = f2 = f3 = 0.f; }
+      bq[kk][0] = pack_h2(f0, f1);
+      bq[kk][1] = pack_h2(f2, f3);
+    }
+  }
+  const float qpos = (float)(a.query_pos ? a.query_pos[b] : a.query_pos_default);
+
+  float o[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+  float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
+
+  const int s_begin = split * a.tokens_per_split;
+  int s_end = s_begin + a.tokens_per_split;
+  if (s_end > a.S) s_end = a.S;
+  for (int s0 = s_begin + warp * 32; s0 < s_end; s0 += TD_WARPS * 32) {
+    const int s = s0 + lane;
+    const bool valid = s < s_end;
+    // ---- zero this lane's rows of both tiles ----
+    {
+      uint4 z = make_uint4(0, 0, 0, 0);
+      uint4* rk = reinterpret_cast<uint4*>(kt + lane * TD_LD);
+      uint4* rv = reinterpret_cast<uint4*>(vt + lane * TD_LD);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) { rk[i] = z; rv[i] = z; }
+    }
+    if (valid) {
+      const int64_t rec = ((int64_t)b * a.S + s) * a.KVH + kvh;
+      const float kpos = (float)(a.key_positions ? a.key_positions[(int64_t)b * a.S + s] : a.key_pos_start + s);
+      const float delta = __fsub_rn(kpos, qpos);
+      const float ks = __half2float(a.k_scales[rec]);
+      const float vs = __half2float(a.v_scales[rec]);
+      const uint8_t* ki = a.k_idx + rec * F;
+      const uint8_t* kp = a.k_packed + rec * F;
+      const uint8_t* vi = a.v_idx + rec * F;
+      const uint8_t* vp = a.v_packed + rec * F;
+      __half2* krow = reinterpret_cast<__half2*>(kt + lane * TD_LD);
+      __half2* vrow = reinterpret_cast<__half2*>(vt + lane * TD_LD);
+#pragma unroll
+      for (int f = 0; f < F; ++f) {
+        const int id = ki[f] & 63, pk = kp[f];
+        const float k0 = __fmul_rn(s_deq[pk >> 4], ks), k1 = __fmul_rn(s_deq[pk & 15], ks);
+        float sn, cs;
+        sincos_reduced(__fmul_rn(delta, s_theta[id]), sn, cs);
+        krow[id] = __floats2half2_rn(k0 * cs - k1 * sn, k1 * cs + k0 * sn);
+        const int idv = vi[f] & 63, pv = vp[f];
+        vrow[idv] = __floats2half2_rn(__fmul_rn(s_deq[pv >> 4], vs), __fmul_rn(s_deq[pv & 15], vs));
+      }
+    }
+    __syncwarp();
+
+    // ---- scores for the two 16-token halves: S^T[tokens][q heads] ----
+    float sc[2][4];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {
+      sc[mt][0] = sc[mt][1] = sc[mt][2] = sc[mt][3] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        uint32_t af[4];
+        ldmatrix_x4(af, kt + (mt * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * TD_LD + kk * 16 + 8 * (lane >> 4));
+        mma16816_tri(sc[mt], af, bq[kk][0], bq[kk][1]);
+      }
+    }
+    const int rem = s_end - s0;    // tokens of this tile that exist
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {
+      if (mt * 16 + g >= rem) { sc[mt][0] = -CUDART_INF_F; sc[mt][1] = -CUDART_INF_F; }
+      if (mt * 16 + g + 8 >= rem) { sc[mt][2] = -CUDART_INF_F; sc[mt][3] = -CUDART_INF_F; }
+    }
+    if (a.scores_out != nullptr) {
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int tok = mt * 16 + g + 8 * (e >> 1), qg = 2 * t + (e & 1);
+          if (tok < rem && qg < G)
+            a.scores_out[((int64_t)b * a.QH + kvh * G + qg) * a.S + s0 + tok] = sc[mt][e] * 0.6931471805599453f;
+        }
+    }
+    float mx0 = fmaxf(fmaxf(sc[0][0], sc[0][2]), fmaxf(sc[1][0], sc[1][2]));
+    float mx1 = fmaxf(fmaxf(sc[0][1], sc[0][3]), fmaxf(sc[1][1], sc[1][3]));
+#pragma unroll
+    for (int off = 4; off < 32; off <<= 1) {
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+    }
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    const float al0 = ex2a(m0 - mn0), al1 = ex2a(m1 - mn1);
+    m0 = mn0; m1 = mn1;
+    l0 *= al0; l1 *= al1;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { o[j][0] *= al0; o[j][1] *= al1; o[j][2] *= al0; o[j][3] *= al1; }
+    uint32_t pb[2][2];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {
+      const float p0 = ex2a(sc[mt][0] - mn0), p1 = ex2a(sc[mt][1] - mn1);
+      const float p2 = ex2a(sc[mt][2] - mn0), p3 = ex2a(sc[mt][3] - mn1);
+      l0 += p0 + p2;
+      l1 += p1 + p3;
+      pb[mt][0] = movmatrix_trans_tri(pack_h2(p0, p1));
+      pb[mt][1] = movmatrix_trans_tri(pack_h2(p2, p3));
+    }
+    // ---- values: O^T[dims][q heads] += V^T P^T ----
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        uint32_t af[4];
+        ldmatrix_x4_trans(af, vt + (mt * 16 + (lane & 7) + 8 * (lane >> 4)) * TD_LD + j * 16 + 8 * ((lane >> 3) & 1));
+        mma16816_tri(o[j], af, pb[mt][0], pb[mt][1]);
+      }
+    }
+    __syncwarp();
+  }
+
+#pragma unroll
+  for (int off = 4; off < 32; off <<= 1) {
+    l0 += __shfl_xor_sync(0xffffffffu, l0, off);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+  }
+  const int part = split * TD_WARPS + warp;
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const int qg = 2 * t + e;
+    if (qg >= G) continue;
+    const int64_t row = (int64_t)b * a.QH + kvh * G + qg;
+    float* pa = a.part_acc + (row * a.num_parts + part) * 128;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {   // M-tile j: rows g, g+8 -> dims 16j+g, 16j+g+8
+      pa[16 * j + g] = o[j][e];
+      pa[16 * j + g + 8] = o[j][2 + e];
+    }
+    if (g == 0) {
+      a.part_ml[(row * a.num_parts + part) * 2] = e ? m1 : m0;
+      a.part_ml[(row * a.num_parts + part) * 2 + 1] = e ? l1 : l0;
+    }
+  }
+}
+
+static void tri_plan(int B, int QH, int S, int tps_in, int* tps, int* parts, size_t* off_ml, size_t* total) {
+  int tp = tps_in > 0 ? tps_in : 2048;
+  if (tp > S) tp = S > 0 ? S : 1;
+  tp = (tp + 31) / 32 * 32;
+  const int splits = S > 0 ? (S + tp - 1) / tp : 1;
+  *tps = tp;
+  *parts = splits * TD_WARPS;
+  const size_t rows = (size_t)B * QH;
+  auto al = [](size_t v) { return (v + 255) & ~(size_t)255; };
+  *off_ml = al(rows * (size_t)*parts * 128 * sizeof(float));
+  *total = *off_ml + al(rows * (size_t)*parts * 2 * sizeof(float));
+}
+
+}  // namespace akv
+
+using namespace akv;
+
+AKV_EXPORT int akv_tri_encode(const void* x, int x_dtype, int64_t n_rows, int64_t x_row_stride, int head_dim,
+                              int num_freqs, uint8_t* indices, uint8_t* packed, void* scales_f16, void* stream) {
+  if (head_dim != 128) return fail(AKV_ERR_UNSUPPORTED, "tri encode is built for head_dim 128, got %d", head_dim);
+  if (n_rows < 0) return fail(AKV_ERR_ARG, "n_rows < 0");
+  if (n_rows == 0) return AKV_OK;
+  if (!x || !indices || !packed || !scales_f16) return fail(AKV_ERR_ARG, "akv_tri_encode: null pointer");
+  if (x_dtype < AKV_F16 || x_dtype > AKV_F32) return fail(AKV_ERR_ARG, "bad x_dtype %d", x_dtype);
+  const int grid = (int)((n_rows + TE_THREADS - 1) / TE_THREADS);
+  cudaStream_t st = (cudaStream_t)stream;
+  __half* sc = reinterpret_cast<__half*>(scales_f16);
+  switch (num_freqs) {
+    case 8: tri_encode_kernel<8><<<grid, TE_THREADS, 0, st>>>(x, x_dtype, n_rows, x_row_stride, indices, packed, sc); break;
+    case 12: tri_encode_kernel<12><<<grid, TE_THREADS, 0, st>>>(x, x_dtype, n_rows, x_row_stride, indices, packed, sc); break;
+    case 16: tri_encode_kernel<16><<<grid, TE_THREADS, 0, st>>>(x, x_dtype, n_rows, x_row_stride, indices, packed, sc); break;
+    default: return fail(AKV_ERR_UNSUPPORTED, "tri encode: num_freqs must be 8, 12 or 16, got %d", num_freqs);
+  }
+  return check_launch("tri_encode_kernel");
+}
+
+// Mirror of akv_tri_decode_params in include/akv_b200.h.
+struct akv_tri_decode_params {
+  const void* query; int q_dtype; int64_t q_stride_batch, q_stride_head;
+  const uint8_t* k_indices; const uint8_t* k_packed; const void* k_scales;
+  const uint8_t* v_indices; const uint8_t* v_packed; const void* v_scales;
+  int batch, seq_len, num_kv_heads, num_q_heads, head_dim, num_freqs;
+  const int64_t* key_positions; int64_t key_pos_start;
+  const int64_t* query_pos; int64_t query_pos_default;
+  const float* theta;
+  float scale;
+  float* out;          // [batch, num_q_heads, head_dim] float32, or NULL with raw_out
+  float* raw_out;      // [batch*num_q_heads, head_dim+2]: un-normalised (m, l, acc)
+  void* workspace; size_t workspace_bytes;
+  int tokens_per_split;
+  void* stream;
+  void* ev_kernel_start; void* ev_kernel_stop;
+  float* scores_out;
+};
+
+AKV_EXPORT size_t akv_tri_decode_workspace_bytes(int batch, int num_q_heads, int seq_len, int tokens_per_split) {
+  if (batch <= 0 || num_q_heads <= 0) return 0;
+  int tps, parts; size_t off_ml, total;
+  tri_plan(batch, num_q_heads, seq_len, tokens_per_split, &tps, &parts, &off_ml, &total);
+  return total;
+}
+
+AKV_EXPORT int akv_tri_decode_step(const akv_tri_decode_params* p) {
+  if (!p) return fail(AKV_ERR_ARG, "null params");
+  if (p->head_dim != 128) return fail(AKV_ERR_UNSUPPORTED, "tri decode is built for head_dim 128");
+  if (p->num_freqs != 8 && p->num_freqs != 12 && p->num_freqs != 16)
+    return fail(AKV_ERR_UNSUPPORTED, "tri decode: num_freqs must be 8, 12 or 16");
+  if (p->batch < 0 || p->seq_len < 0 || p->num_kv_heads <= 0 || p->num_q_heads <= 0 ||
+      p->num_q_heads % p->num_kv_heads)
+    return fail(AKV_ERR_ARG, "tri decode: bad sizes");
+  const int G = p->num_q_heads / p->num_kv_heads;
+  if (G > 8) return fail(AKV_ERR_UNSUPPORTED, "tri decode: at most 8 query heads per KV head");
+  if (p->batch == 0) return AKV_OK;
+  if (!p->query || !p->theta || (!p->out && !p->raw_out) ||
+      (p->seq_len > 0 && (!p->k_indices || !p->k_packed || !p->k_scales || !p->v_indices || !p->v_packed || !p->v_scales)))
+    return fail(AKV_ERR_ARG, "tri decode: null pointer");
+  int tps, parts; size_t off_ml, total;
+  tri_plan(p->batch, p->num_q_heads, p->seq_len, p->tokens_per_split, &tps, &parts, &off_ml, &total);
+  if (!p->workspace || p->workspace_bytes < total)
+    return fail(AKV_ERR_WORKSPACE, "workspace too small: need %zu bytes, got %zu", total, p->workspace_bytes);
+  char* ws = reinterpret_cast<char*>(p->workspace);
+  cudaStream_t st = (cudaStream_t)p->stream;
+  TriArgs a{};
+  a.k_idx = p->k_indices; a.k_packed = p->k_packed; a.k_scales = reinterpret_cast<const __half*>(p->k_scales);
+  a.v_idx = p->v_indices; a.v_packed = p->v_packed; a.v_scales = reinterpret_cast<const __half*>(p->v_scales);
+  a.B = p->batch; a.S = p->seq_len; a.KVH = p->num_kv_heads; a.QH = p->num_q_heads; a.F = p->num_freqs;
+  a.query = p->query; a.q_dtype = p->q_dtype; a.q_sb = p->q_stride_batch; a.q_sh = p->q_stride_head;
+  a.key_positions = p->key_positions; a.key_pos_start = p->key_pos_start;
+  a.query_pos = p->query_pos; a.query_pos_default = p->query_pos_default;
+  a.theta = p->theta; a.premul = p->scale * 1.4426950408889634f;
+  a.tokens_per_split = tps; a.num_parts = parts;
+  a.part_acc = reinterpret_cast<float*>(ws); a.part_ml = reinterpret_cast<float*>(ws + off_ml);
+  a.scores_out = p->scores_out;
+  if (p->ev_kernel_start) cudaEventRecord((cudaEvent_t)p->ev_kernel_start, st);
+  if (p->seq_len > 0) {
+    dim3 grid(parts / TD_WARPS, p->num_kv_heads, p->batch);
+    cudaError_t e = cudaSuccess;
+#define AKV_TRI(FF)                                                                                  \
+    e = cudaFuncSetAttribute(tri_decode_kernel<FF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TD_SMEM); \
+    if (e == cudaSuccess) tri_decode_kernel<FF><<<grid, TD_WARPS * 32, TD_SMEM, st>>>(a);
+    if (p->num_freqs == 8) { AKV_TRI(8) } else if (p->num_freqs == 12) { AKV_TRI(12) } else { AKV_TRI(16) }
+#undef AKV_TRI
+    if (e != cudaSuccess) return fail((int)e, "tri decode: smem attribute: %s", cudaGetErrorString(e));
+    if (int rc = check_launch("tri_decode_kernel")) return rc;
+  }
+  if (p->ev_kernel_stop) cudaEventRecord((cudaEvent_t)p->ev_kernel_stop, st);
+  const int rows = p->batch * p->num_q_heads;
+  MergeArgs mg{};
+  mg.mode = p->raw_out ? MERGE_RAW : MERGE_NORMALIZE;
+  mg.acc = a.part_acc; mg.acc_row = (int64_t)parts * 128; mg.acc_part = 128;
+  mg.ml = a.part_ml; mg.ml_row = (int64_t)parts * 2; mg.ml_part = 2;
+  mg.np = p->seq_len > 0 ? parts : 0;
+  mg.context_lens = nullptr; mg.num_q_heads = p->num_q_heads;
+  mg.D = 128; mg.rot = nullptr;
+  mg.out = p->out; mg.out_dtype = AKV_F32; mg.out_ss = (int64_t)p->num_q_heads * 128; mg.out_sh = 128;
+  mg.raw_out = p->raw_out;
+  return launch_merge(mg, rows, st);
+}

@@ -192,6 +192,49 @@ size_t akv_hybrid_paged_attn_workspace_bytes(int num_seqs, int num_q_heads, int 
                                              int max_blocks_per_seq, int blocks_per_split);
 int akv_hybrid_paged_attn(const akv_hybrid_attn_params* params);
 
+/* ------------------------------------------------------------------------
+ * TriAttention spectral codec (head_dim 128, int4 coefficients, pre-RoPE keys)
+ * ---------------------------------------------------------------------- */
+
+/* Replaces SpectralKVEncoder.encode (aither_kvcache/triattention/encoder.py:73-149, coeff_bits 4;
+ * called twice by TriAttention.encode_kv, attention.py:96-112).  Per vector: the num_freqs
+ * (8, 12 or 16) RoPE pairs of largest energy in ascending order, their two coefficients
+ * quantised to 4 bits against the largest magnitude, and that magnitude as fp16.
+ *   indices, packed [n_rows, num_freqs] uint8; scales [n_rows] fp16. */
+int akv_tri_encode(const void* x, int x_dtype, int64_t n_rows, int64_t x_row_stride, int head_dim,
+                   int num_freqs, uint8_t* indices, uint8_t* packed, void* scales_f16, void* stream);
+
+/* Replaces TriAttention.decode_step (attention.py:186-280) = TrigSeriesScorer.score
+ * (scorer.py:115-208) + softmax + _accumulate_values.
+ *   query [batch, num_q_heads, 128]; k_ / v_ indices, packed [batch, seq_len, num_kv_heads, F] uint8,
+ *   scales [batch, seq_len, num_kv_heads] fp16; theta [64] float32 RoPE frequencies.
+ *   key_positions [batch, seq_len] int64 or NULL (position = key_pos_start + index);
+ *   query_pos [batch] int64 or NULL (query_pos_default).
+ * out is float32 [batch, num_q_heads, 128].  With raw_out the un-normalised partial
+ * (m in log2 units, l, acc[128]) per (batch, q head) is written instead, so that key ranges held
+ * by different devices can be merged with akv_lse_merge(rotation = NULL). */
+typedef struct akv_tri_decode_params {
+  const void* query; int q_dtype; int64_t q_stride_batch, q_stride_head;
+  const uint8_t* k_indices; const uint8_t* k_packed; const void* k_scales;
+  const uint8_t* v_indices; const uint8_t* v_packed; const void* v_scales;
+  int batch, seq_len, num_kv_heads, num_q_heads, head_dim, num_freqs;
+  const int64_t* key_positions; int64_t key_pos_start;
+  const int64_t* query_pos; int64_t query_pos_default;
+  const float* theta;
+  float scale;
+  float* out;
+  float* raw_out;
+  void* workspace; size_t workspace_bytes;
+  int tokens_per_split;   /* 0 = library default */
+  void* stream;
+  void* ev_kernel_start; void* ev_kernel_stop;   /* optional cudaEvent_t pair around the main kernel */
+  float* scores_out;      /* optional [batch, num_q_heads, seq_len] float32: the pre-softmax scores
+                             (what TrigSeriesScorer.score returns); NULL = not written */
+} akv_tri_decode_params;
+
+size_t akv_tri_decode_workspace_bytes(int batch, int num_q_heads, int seq_len, int tokens_per_split);
+int akv_tri_decode_step(const akv_tri_decode_params* params);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,111 @@
+"""GPU parity of the TriAttention kernels against reference fixtures and the oracle."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import load_golden
+from oracle import tri as otri
+
+pytestmark = pytest.mark.gpu
+
+
+def _tri(kvh=2, qh=8, f=12):
+    from aitherkvcache_b200.triattention import TriAttention, TriAttentionConfig
+    cfg = TriAttentionConfig(head_dim=128, num_freqs=f, coeff_bits=4, num_kv_heads=kvh, num_query_heads=qh,
+                             rope_base=1_000_000.0)
+    return TriAttention(cfg, device="cuda")
+
+
+def _enc_to_cuda(g, side):
+    from aitherkvcache_b200.triattention import SpectralEncoding
+    return SpectralEncoding(torch.from_numpy(g[f"{side}_indices"]).cuda(), torch.from_numpy(g[f"{side}_packed"]).cuda(),
+                            torch.from_numpy(g[f"{side}_scales"]).cuda())
+
+
+def test_encode_matches_reference():
+    g = load_golden("tri_f12_int4.npz")
+    tri = _tri()
+    assert np.array_equal(tri._theta.cpu().numpy().view(np.uint32), g["theta"].view(np.uint32))
+    k_enc, v_enc = tri.encode_kv(torch.from_numpy(g["keys"]).cuda(), torch.from_numpy(g["values"]).cuda())
+    for side, enc, x in (("k", k_enc, g["keys"]), ("v", v_enc, g["values"])):
+        assert enc.indices.dtype == torch.uint8 and enc.packed.dtype == torch.uint8 and enc.scales.dtype == torch.float16
+        assert enc.indices.shape == (2, 200, 2, 12) and enc.scales.shape == (2, 200, 2)
+        clear = otri.rank_gap(x, 12) > 0        # top-F set unambiguous
+        assert clear.mean() > 0.999
+        assert np.array_equal(enc.indices.cpu().numpy()[clear], g[f"{side}_indices"][clear])
+        assert np.array_equal(enc.packed.cpu().numpy()[clear], g[f"{side}_packed"][clear])
+        assert np.array_equal(enc.scales.cpu().numpy()[clear].view(np.uint16), g[f"{side}_scales"][clear].view(np.uint16))
+
+
+def test_decode_step_matches_reference():
+    g = load_golden("tri_f12_int4.npz")
+    tri = _tri()
+    k_enc, v_enc = _enc_to_cuda(g, "k"), _enc_to_cuda(g, "v")
+    q = torch.from_numpy(g["query"]).cuda()
+    out = tri.decode_step(q, k_enc, v_enc)
+    assert out.dtype == torch.float32 and out.shape == (2, 8, 128)
+    assert np.abs(out.cpu().numpy() - g["out_default"]).max() < 2e-3
+    qpos, kpos = torch.from_numpy(g["query_pos"]).cuda(), torch.from_numpy(g["key_positions"]).cuda()
+    out = tri.decode_step(q, k_enc, v_enc, qpos, kpos)
+    assert np.abs(out.cpu().numpy() - g["out_far"]).max() < 2e-3
+    from aitherkvcache_b200.triattention import TrigSeriesScorer
+    sc = TrigSeriesScorer(tri.config, device="cuda").score(q, k_enc, qpos, kpos)
+    assert sc.shape == (2, 8, 200)
+    assert np.abs(sc.cpu().numpy() - g["scores_far"]).max() < 5e-3     # fp16 operands of the score product
+
+
+def _synthetic(B, S, H, seed=2):
+    g = torch.Generator().manual_seed(seed)
+    s_i = torch.exp(-torch.arange(64, dtype=torch.float32) / 16.0)
+    scale = torch.stack([s_i[torch.randperm(64, generator=g)] for _ in range(H)])
+    keys = (torch.randn(B, S, H, 64, 2, generator=g) * scale[None, None, :, :, None]).reshape(B, S, H, 128).half()
+    values = torch.randn(B, S, H, 128, generator=g).half()
+    return keys, values, g
+
+
+@pytest.mark.parametrize("S", (1, 31, 32, 33, 2500))
+def test_decode_step_vs_oracle_long_positions(S):
+    """Benchmark head layout (32Q/8KV), keys at the far end of a 128K context."""
+    B, H, QH = 2, 8, 32
+    tri = _tri(H, QH)
+    keys, values, g = _synthetic(B, S, H)
+    q = torch.randn(B, QH, 128, generator=g).half()
+    k_enc, v_enc = tri.encode_kv(keys.cuda(), values.cuda())
+    kpos = torch.arange(131072 - S, 131072).unsqueeze(0).expand(B, -1).contiguous()
+    qpos = torch.full((B,), 131072)
+    out = tri.decode_step(q.cuda(), k_enc, v_enc, qpos.cuda(), kpos.cuda()).cpu().numpy()
+    k_np = tuple(t.cpu().numpy() for t in k_enc)
+    v_np = tuple(t.cpu().numpy() for t in v_enc)
+    ref = otri.decode_step(q.numpy(), k_np, v_np, tri._theta.cpu().numpy(), qpos.numpy(), kpos.numpy())
+    assert np.abs(out - ref).max() < 2e-3
+    # the encoder against the oracle on the same data
+    oi, op, osc = otri.encode(keys.numpy(), 12)
+    clear = otri.rank_gap(keys.numpy(), 12) > 0
+    assert np.array_equal(k_np[0][clear], oi[clear]) and np.array_equal(k_np[1][clear], op[clear])
+    assert np.array_equal(k_np[2][clear].view(np.uint16), osc[clear].view(np.uint16))
+
+
+def test_split_ranges_merge_like_devices():
+    """Key range split in contiguous parts, raw partials merged by akv_lse_merge (one part empty)."""
+    from aitherkvcache_b200 import _lib
+    from aitherkvcache_b200.triattention import SpectralEncoding
+    B, S, H, QH = 2, 1000, 8, 32
+    tri = _tri(H, QH)
+    keys, values, g = _synthetic(B, S, H, seed=5)
+    q = torch.randn(B, QH, 128, generator=g).half().cuda()
+    k_enc, v_enc = tri.encode_kv(keys.cuda(), values.cuda())
+    full = tri.decode_step(q, k_enc, v_enc)
+    bounds = [0, 400, 400, 1000]            # rank 1 holds nothing
+    parts = []
+    for r in range(3):
+        lo, hi = bounds[r], bounds[r + 1]
+        sl = lambda e: SpectralEncoding(e.indices[:, lo:hi].contiguous(), e.packed[:, lo:hi].contiguous(),   # noqa: E731
+                                        e.scales[:, lo:hi].contiguous())
+        parts.append(tri.decode_step_partial(q, sl(k_enc), sl(v_enc), key_pos_start=lo, query_pos_default=S))
+    stacked = torch.stack(parts).contiguous()
+    assert stacked[1, :, 1].abs().max().item() == 0.0
+    out = torch.empty(B, QH, 128, dtype=torch.float32, device="cuda")
+    rc = _lib.lib().akv_lse_merge(stacked.data_ptr(), 3, B, QH, 128, None, out.data_ptr(), _lib.AKV_F32,
+                                  out.stride(0), out.stride(1), torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "akv_lse_merge")
+    assert (out - full).abs().max().item() < 1e-4
