@@ -70,3 +70,24 @@ def test_packing_helpers_match_oracle(bits):
     assert p.dtype == torch.uint8 and p.shape[-1] == packing.packed_size(128, bits)
     assert np.array_equal(p.numpy(), otq.pack(idx.numpy(), bits))
     assert torch.equal(unpack(p, 128).long(), idx)
+
+
+def test_vllm_backend_surface():
+    """Class attributes and statics of the CUSTOM backend (needs vLLM importable; no GPU)."""
+    pytest.importorskip("vllm")
+    from aitherkvcache_b200.vllm import backend
+    B = backend.TurboQuantBackend
+    assert B.get_name() == "CUSTOM"
+    assert B.accept_output_buffer is True and B.forward_includes_kv_cache_update is False
+    assert B.get_kv_cache_shape(10, 16, 8, 128, "auto") == (10, 2, 16, 8, 128)
+    assert {"tq-t4nc", "tq-t3nc", "tq-t2nc"} <= set(B.supported_kv_cache_dtypes)
+    assert 128 in B.get_supported_head_sizes()
+    impl = B.get_impl_cls()
+    assert hasattr(impl, "forward") and hasattr(impl, "do_kv_cache_update")
+    assert backend.bits_from_env_or_dtype("tq-t3nc") == 3
+
+
+def test_kv_cache_dtype_table():
+    import aitherkvcache_b200 as a
+    assert a.KV_CACHE_DTYPES["tq-t4nc"] == {"kind": "uniform", "bits": 4}
+    assert a.KV_CACHE_DTYPES["tq-t35nc"]["mode"] == "tq35"
