@@ -163,7 +163,9 @@ tri_decode_kernel(TriArgs a) {
   extern __shared__ __align__(16) __half tiles[];
   __shared__ float s_theta[64];
   __shared__ float s_deq[16];
-  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  // kv head is the fastest grid index: the heads of a token range are interleaved at F-byte
+  // granularity in memory, so CTAs that run together share DRAM sectors through L2
+  const int kvh = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   if (threadIdx.x < 64) s_theta[threadIdx.x] = a.theta[threadIdx.x];
@@ -216,20 +218,26 @@ tri_decode_kernel(TriArgs a) {
       const float delta = __fsub_rn(kpos, qpos);
       const float ks = __half2float(a.k_scales[rec]);
       const float vs = __half2float(a.v_scales[rec]);
-      const uint8_t* ki = a.k_idx + rec * F;
-      const uint8_t* kp = a.k_packed + rec * F;
-      const uint8_t* vi = a.v_idx + rec * F;
-      const uint8_t* vp = a.v_packed + rec * F;
+      // F bytes per array and token (F is a multiple of 4): word loads, bytes taken by shifts
+      uint32_t kiw[F / 4], kpw[F / 4], viw[F / 4], vpw[F / 4];
+#pragma unroll
+      for (int w = 0; w < F / 4; ++w) {
+        kiw[w] = reinterpret_cast<const uint32_t*>(a.k_idx + rec * F)[w];
+        kpw[w] = reinterpret_cast<const uint32_t*>(a.k_packed + rec * F)[w];
+        viw[w] = reinterpret_cast<const uint32_t*>(a.v_idx + rec * F)[w];
+        vpw[w] = reinterpret_cast<const uint32_t*>(a.v_packed + rec * F)[w];
+      }
       __half2* krow = reinterpret_cast<__half2*>(kt + lane * TD_LD);
       __half2* vrow = reinterpret_cast<__half2*>(vt + lane * TD_LD);
 #pragma unroll
       for (int f = 0; f < F; ++f) {
-        const int id = ki[f] & 63, pk = kp[f];
+        const int sh = 8 * (f & 3);
+        const int id = (kiw[f >> 2] >> sh) & 63, pk = (kpw[f >> 2] >> sh) & 255;
         const float k0 = __fmul_rn(s_deq[pk >> 4], ks), k1 = __fmul_rn(s_deq[pk & 15], ks);
         float sn, cs;
         sincos_reduced(__fmul_rn(delta, s_theta[id]), sn, cs);
         krow[id] = __floats2half2_rn(k0 * cs - k1 * sn, k1 * cs + k0 * sn);
-        const int idv = vi[f] & 63, pv = vp[f];
+        const int idv = (viw[f >> 2] >> sh) & 63, pv = (vpw[f >> 2] >> sh) & 255;
         vrow[idv] = __floats2half2_rn(__fmul_rn(s_deq[pv >> 4], vs), __fmul_rn(s_deq[pv & 15], vs));
       }
     }
@@ -418,7 +426,7 @@ AKV_EXPORT int akv_tri_decode_step(const akv_tri_decode_params* p) {
   a.scores_out = p->scores_out;
   if (p->ev_kernel_start) cudaEventRecord((cudaEvent_t)p->ev_kernel_start, st);
   if (p->seq_len > 0) {
-    dim3 grid(parts / TD_WARPS, p->num_kv_heads, p->batch);
+    dim3 grid(p->num_kv_heads, parts / TD_WARPS, p->batch);
     cudaError_t e = cudaSuccess;
 #define AKV_TRI(FF)                                                                                  \
     e = cudaFuncSetAttribute(tri_decode_kernel<FF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TD_SMEM); \
