@@ -9,7 +9,7 @@
 //                                                   split partials + inverse rotation)
 //
 // Two split-K kernels write the same partial format (m in log2 units, l, acc[D]):
-//   * tq_attn_mma_kernel  - head_dim 128, 4-bit codes, up to 8 query heads per KV
+//   * tq_attn_mma_kernel  - head_dim 128, 4/3/2-bit codes, up to 8 query heads per KV
 //     head, block_size a multiple of 16.  One warp per (KV head, 16-token tile);
 //     codes are turned into fp16 MMA fragments by a shared-memory table lookup
 //     (one lookup per code pair) and both products run on mma.sync m16n8k16 with
@@ -224,7 +224,7 @@ tq_attn_generic_kernel(AttnArgs a) {
 }
 
 // ---------------------------------------------------------------------------
-// Tensor-core split-K kernel (head_dim 128, 4-bit).
+// Tensor-core split-K kernel (head_dim 128).
 // ---------------------------------------------------------------------------
 constexpr int LUT_STRIDE = 256;                 // bytes between table entries
 constexpr int LUT_BYTES = 256 * LUT_STRIDE;     // 64 KB: entry e, lane l at e*256 + l*4
@@ -276,10 +276,13 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-// Per-thread packed data of one 16-token tile of one KV head.
+// Per-thread packed data of one 16-token tile of one KV head.  With `BITS` bits per code a
+// thread holds, for the score product, dims 32t..32t+31 of tokens g and g+8 (4*BITS bytes each)
+// and, for the value product, dims 16g..16g+15 of tokens 2t, 2t+1, 2t+8, 2t+9 (2*BITS bytes each).
+template <int BITS>
 struct TileData {
-  uint4 kA, kB;          // K codes of tokens g and g+8, bytes 16t..16t+15
-  uint2 v0, v1, v2, v3;  // V codes of tokens 2t, 2t+1, 2t+8, 2t+9, bytes 8g..8g+7
+  uint32_t kA[BITS], kB[BITS];   // little-endian words of the K bytes
+  uint32_t v[4][2];              // V bytes of the four tokens (3-bit: 6 bytes, 2-bit: 4 bytes)
 #if AKV_NORM_SHFL
   float nrm;             // lanes 0..15: K norm of token `lane`; lanes 16..31: V norm of token lane-16
 #else
@@ -294,17 +297,43 @@ struct ThreadOffsets {
   int nkA, nkB, nvA, nvB;
 };
 
-template <bool VEC16>
+template <int BITS, bool VEC16>
+__device__ __forceinline__ void load_k(const uint8_t* p, uint32_t (&w)[BITS]) {
+  if constexpr (BITS == 4 && VEC16) {
+    const uint4 q = *reinterpret_cast<const uint4*>(p);
+    w[0] = q.x; w[1] = q.y; w[2] = q.z; w[3] = q.w;
+  } else {
+#pragma unroll
+    for (int i = 0; i < BITS; ++i) w[i] = reinterpret_cast<const uint32_t*>(p)[i];
+  }
+}
+
+template <int BITS, bool VEC16>
+__device__ __forceinline__ void load_v(const uint8_t* p, uint32_t (&w)[2]) {
+  if constexpr (BITS == 4) {
+    if (VEC16) { const uint2 q = *reinterpret_cast<const uint2*>(p); w[0] = q.x; w[1] = q.y; }
+    else { w[0] = reinterpret_cast<const uint32_t*>(p)[0]; w[1] = reinterpret_cast<const uint32_t*>(p)[1]; }
+  } else if constexpr (BITS == 3) {   // 6 bytes at a 2-byte aligned address
+    const uint16_t* h = reinterpret_cast<const uint16_t*>(p);
+    w[0] = (uint32_t)h[0] | ((uint32_t)h[1] << 16);
+    w[1] = h[2];
+  } else {
+    w[0] = *reinterpret_cast<const uint32_t*>(p);
+    w[1] = 0;
+  }
+}
+
+template <int BITS, bool VEC16>
 __device__ __forceinline__ void load_tile(const AttnArgs& a, const ThreadOffsets& off, int64_t pb,
-                                          int tok0, int lane, TileData& d) {
+                                          int tok0, int lane, TileData<BITS>& d) {
   const uint8_t* kb = a.k_packed + pb * a.kp_sb + (int64_t)tok0 * a.kp_sp;
   const uint8_t* vb = a.v_packed + pb * a.vp_sb + (int64_t)tok0 * a.vp_sp;
-  d.kA = load16<VEC16>(kb + off.kA);
-  d.kB = load16<VEC16>(kb + off.kB);
-  d.v0 = load8<VEC16>(vb + off.v0);
-  d.v1 = load8<VEC16>(vb + off.v1);
-  d.v2 = load8<VEC16>(vb + off.v2);
-  d.v3 = load8<VEC16>(vb + off.v3);
+  load_k<BITS, VEC16>(kb + off.kA, d.kA);
+  load_k<BITS, VEC16>(kb + off.kB, d.kB);
+  load_v<BITS, VEC16>(vb + off.v0, d.v[0]);
+  load_v<BITS, VEC16>(vb + off.v1, d.v[1]);
+  load_v<BITS, VEC16>(vb + off.v2, d.v[2]);
+  load_v<BITS, VEC16>(vb + off.v3, d.v[3]);
 #if AKV_NORM_SHFL
   const float* nb = (lane < 16) ? a.k_norms + pb * a.kn_sb + (int64_t)tok0 * a.kn_sp
                                 : a.v_norms + pb * a.vn_sb + (int64_t)tok0 * a.vn_sp;
@@ -320,24 +349,102 @@ struct SoftmaxState {
   float m0, m1, l0, l1;   // running max (log2 units) and sum for q-head columns 2t, 2t+1
 };
 
+// ---- code -> fp16 fragment lookups for 3 and 2 bits ----
+// 3-bit table: entry e (two codes, 6 bits) -> half2(c[e >> 3], c[e & 7]) at e*128 + lane*4.
+// 2-bit table: entry e (four codes, one byte) -> 4 halves at e*256 + lane*8.
+constexpr int LUT3_STRIDE = 128;
+
+// Pair P of an MSB-first 3-bit stream held as big-endian words B[0], B[1], ...
+template <int P>
+__device__ __forceinline__ uint32_t lut3(const unsigned char* lut, const uint32_t* B, uint32_t lanebase) {
+  constexpr int o = 6 * P, w = o >> 5, pos = o & 31;
+  uint32_t x;
+  if constexpr (pos <= 26) x = B[w] >> (26 - pos);
+  else x = __funnelshift_r(B[w + 1], B[w], 58 - pos);
+  const uint32_t addr = ((x & 63u) << 7) | lanebase;
+  return *reinterpret_cast<const uint32_t*>(lut + addr);
+}
+
+template <int K>
+__device__ __forceinline__ uint2 lut2(const unsigned char* lut, uint32_t w, uint32_t lanebase8) {
+  const uint32_t addr = __byte_perm(w, lanebase8, 0x7604 + (K << 4));
+  return *reinterpret_cast<const uint2*>(lut + addr);
+}
+
+__device__ __forceinline__ uint32_t bswap32(uint32_t w) { return __byte_perm(w, 0, 0x0123); }
+
+// Natural-order fragments of one token's K bytes: n[p] = half2(dim 32t+2p, dim 32t+2p+1), p = 0..15.
+template <int BITS>
+__device__ __forceinline__ void k_natural(const unsigned char* lut, const uint32_t (&w)[BITS], uint32_t lanebase,
+                                          uint32_t (&n)[16]) {
+  if constexpr (BITS == 3) {
+    const uint32_t B[3] = {bswap32(w[0]), bswap32(w[1]), bswap32(w[2])};
+    n[0] = lut3<0>(lut, B, lanebase);   n[1] = lut3<1>(lut, B, lanebase);   n[2] = lut3<2>(lut, B, lanebase);
+    n[3] = lut3<3>(lut, B, lanebase);   n[4] = lut3<4>(lut, B, lanebase);   n[5] = lut3<5>(lut, B, lanebase);
+    n[6] = lut3<6>(lut, B, lanebase);   n[7] = lut3<7>(lut, B, lanebase);   n[8] = lut3<8>(lut, B, lanebase);
+    n[9] = lut3<9>(lut, B, lanebase);   n[10] = lut3<10>(lut, B, lanebase); n[11] = lut3<11>(lut, B, lanebase);
+    n[12] = lut3<12>(lut, B, lanebase); n[13] = lut3<13>(lut, B, lanebase); n[14] = lut3<14>(lut, B, lanebase);
+    n[15] = lut3<15>(lut, B, lanebase);
+  } else {   // 2 bits: byte b holds dims 32t+4b .. 32t+4b+3
+    const uint32_t lb8 = lanebase * 2;
+    uint2 r;
+    r = lut2<0>(lut, w[0], lb8); n[0] = r.x;  n[1] = r.y;
+    r = lut2<1>(lut, w[0], lb8); n[2] = r.x;  n[3] = r.y;
+    r = lut2<2>(lut, w[0], lb8); n[4] = r.x;  n[5] = r.y;
+    r = lut2<3>(lut, w[0], lb8); n[6] = r.x;  n[7] = r.y;
+    r = lut2<0>(lut, w[1], lb8); n[8] = r.x;  n[9] = r.y;
+    r = lut2<1>(lut, w[1], lb8); n[10] = r.x; n[11] = r.y;
+    r = lut2<2>(lut, w[1], lb8); n[12] = r.x; n[13] = r.y;
+    r = lut2<3>(lut, w[1], lb8); n[14] = r.x; n[15] = r.y;
+  }
+}
+
+// Natural-order fragments of one token's V bytes: n[j] = half2(dim 16g+2j, dim 16g+2j+1), j = 0..7.
+template <int BITS>
+__device__ __forceinline__ void v_natural(const unsigned char* lut, const uint32_t (&w)[2], uint32_t lanebase,
+                                          uint32_t (&n)[8]) {
+  if constexpr (BITS == 3) {
+    // bytes b0..b5 of the stream: w[0] = b0 | b1<<8 | b2<<16 | b3<<24, w[1] = b4 | b5<<8
+    const uint32_t B[2] = {bswap32(w[0]), __byte_perm(w[1], 0, 0x0144)};   // b4 b5 0 0 (big-endian)
+    n[0] = lut3<0>(lut, B, lanebase); n[1] = lut3<1>(lut, B, lanebase); n[2] = lut3<2>(lut, B, lanebase);
+    n[3] = lut3<3>(lut, B, lanebase); n[4] = lut3<4>(lut, B, lanebase); n[5] = lut3<5>(lut, B, lanebase);
+    n[6] = lut3<6>(lut, B, lanebase); n[7] = lut3<7>(lut, B, lanebase);
+  } else {
+    const uint32_t lb8 = lanebase * 2;
+    uint2 r;
+    r = lut2<0>(lut, w[0], lb8); n[0] = r.x; n[1] = r.y;
+    r = lut2<1>(lut, w[0], lb8); n[2] = r.x; n[3] = r.y;
+    r = lut2<2>(lut, w[0], lb8); n[4] = r.x; n[5] = r.y;
+    r = lut2<3>(lut, w[0], lb8); n[6] = r.x; n[7] = r.y;
+  }
+}
+
 // One 16-token tile: scores, online softmax, value accumulation.
 // `n_valid` (1..16) masks the tail of the last tile of a sequence.
+template <int BITS>
 __device__ __forceinline__ void process_tile(const unsigned char* lut, uint32_t lanebase, int g,
-                                             const uint32_t (&bq)[8][2], const TileData& cur,
+                                             const uint32_t (&bq)[8][2], const TileData<BITS>& cur,
                                              int n_valid, float (&o)[8][4], SoftmaxState& st) {
   // ---- scores: S^T[16 tokens][8 q heads], two independent accumulation chains ----
   float s[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};
-  {
-    const uint32_t wa[4] = {cur.kA.x, cur.kA.y, cur.kA.z, cur.kA.w};
-    const uint32_t wb[4] = {cur.kB.x, cur.kB.y, cur.kB.z, cur.kB.w};
+  if constexpr (BITS == 4) {
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
-      mma16816(s, lut4<0>(lut, wa[w], lanebase), lut4<0>(lut, wb[w], lanebase),
-               lut4<1>(lut, wa[w], lanebase), lut4<1>(lut, wb[w], lanebase),
+      mma16816(s, lut4<0>(lut, cur.kA[w], lanebase), lut4<0>(lut, cur.kB[w], lanebase),
+               lut4<1>(lut, cur.kA[w], lanebase), lut4<1>(lut, cur.kB[w], lanebase),
                bq[2 * w][0], bq[2 * w][1]);
-      mma16816(s2, lut4<2>(lut, wa[w], lanebase), lut4<2>(lut, wb[w], lanebase),
-               lut4<3>(lut, wa[w], lanebase), lut4<3>(lut, wb[w], lanebase),
+      mma16816(s2, lut4<2>(lut, cur.kA[w], lanebase), lut4<2>(lut, cur.kB[w], lanebase),
+               lut4<3>(lut, cur.kA[w], lanebase), lut4<3>(lut, cur.kB[w], lanebase),
                bq[2 * w + 1][0], bq[2 * w + 1][1]);
+    }
+  } else {
+    uint32_t na[16], nb[16];
+    k_natural<BITS>(lut, cur.kA, lanebase, na);
+    k_natural<BITS>(lut, cur.kB, lanebase, nb);
+#pragma unroll
+    for (int kk = 0; kk < 8; kk += 2) {
+      mma16816(s, na[2 * kk], nb[2 * kk], na[2 * kk + 1], nb[2 * kk + 1], bq[kk][0], bq[kk][1]);
+      mma16816(s2, na[2 * kk + 2], nb[2 * kk + 2], na[2 * kk + 3], nb[2 * kk + 3], bq[kk + 1][0], bq[kk + 1][1]);
     }
   }
 #if AKV_NORM_SHFL
@@ -382,26 +489,39 @@ __device__ __forceinline__ void process_tile(const unsigned char* lut, uint32_t 
   const uint32_t pb1 = movmatrix_trans(pack_half2(p2 * nvB, p3 * nvB));
 
   // ---- values: O^T[128 dims][8 q heads] += V^T P^T ----
-  const uint32_t va[2] = {cur.v0.x, cur.v0.y}, vb[2] = {cur.v1.x, cur.v1.y};
-  const uint32_t vc[2] = {cur.v2.x, cur.v2.y}, vd[2] = {cur.v3.x, cur.v3.y};
+  if constexpr (BITS == 4) {
 #pragma unroll
-  for (int w = 0; w < 2; ++w) {
-    const uint32_t x01 = (va[w] & 0xF0F0F0F0u) | ((vb[w] >> 4) & 0x0F0F0F0Fu);
-    const uint32_t y01 = ((va[w] << 4) & 0xF0F0F0F0u) | (vb[w] & 0x0F0F0F0Fu);
-    const uint32_t x23 = (vc[w] & 0xF0F0F0F0u) | ((vd[w] >> 4) & 0x0F0F0F0Fu);
-    const uint32_t y23 = ((vc[w] << 4) & 0xF0F0F0F0u) | (vd[w] & 0x0F0F0F0Fu);
-    mma16816(o[4 * w + 0], lut4<0>(lut, x01, lanebase), lut4<0>(lut, y01, lanebase),
-             lut4<0>(lut, x23, lanebase), lut4<0>(lut, y23, lanebase), pb0, pb1);
-    mma16816(o[4 * w + 1], lut4<1>(lut, x01, lanebase), lut4<1>(lut, y01, lanebase),
-             lut4<1>(lut, x23, lanebase), lut4<1>(lut, y23, lanebase), pb0, pb1);
-    mma16816(o[4 * w + 2], lut4<2>(lut, x01, lanebase), lut4<2>(lut, y01, lanebase),
-             lut4<2>(lut, x23, lanebase), lut4<2>(lut, y23, lanebase), pb0, pb1);
-    mma16816(o[4 * w + 3], lut4<3>(lut, x01, lanebase), lut4<3>(lut, y01, lanebase),
-             lut4<3>(lut, x23, lanebase), lut4<3>(lut, y23, lanebase), pb0, pb1);
+    for (int w = 0; w < 2; ++w) {
+      const uint32_t va = cur.v[0][w], vb = cur.v[1][w], vc = cur.v[2][w], vd = cur.v[3][w];
+      // index byte = (code of the first token) << 4 | (code of the second token), same dim
+      const uint32_t x01 = (va & 0xF0F0F0F0u) | ((vb >> 4) & 0x0F0F0F0Fu);
+      const uint32_t y01 = ((va << 4) & 0xF0F0F0F0u) | (vb & 0x0F0F0F0Fu);
+      const uint32_t x23 = (vc & 0xF0F0F0F0u) | ((vd >> 4) & 0x0F0F0F0Fu);
+      const uint32_t y23 = ((vc << 4) & 0xF0F0F0F0u) | (vd & 0x0F0F0F0Fu);
+      mma16816(o[4 * w + 0], lut4<0>(lut, x01, lanebase), lut4<0>(lut, y01, lanebase),
+               lut4<0>(lut, x23, lanebase), lut4<0>(lut, y23, lanebase), pb0, pb1);
+      mma16816(o[4 * w + 1], lut4<1>(lut, x01, lanebase), lut4<1>(lut, y01, lanebase),
+               lut4<1>(lut, x23, lanebase), lut4<1>(lut, y23, lanebase), pb0, pb1);
+      mma16816(o[4 * w + 2], lut4<2>(lut, x01, lanebase), lut4<2>(lut, y01, lanebase),
+               lut4<2>(lut, x23, lanebase), lut4<2>(lut, y23, lanebase), pb0, pb1);
+      mma16816(o[4 * w + 3], lut4<3>(lut, x01, lanebase), lut4<3>(lut, y01, lanebase),
+               lut4<3>(lut, x23, lanebase), lut4<3>(lut, y23, lanebase), pb0, pb1);
+    }
+  } else {
+    // dequantise each token in natural order, then pair the same dim of two tokens
+    uint32_t n0[8], n1[8], n2[8], n3[8];
+    v_natural<BITS>(lut, cur.v[0], lanebase, n0);
+    v_natural<BITS>(lut, cur.v[1], lanebase, n1);
+    v_natural<BITS>(lut, cur.v[2], lanebase, n2);
+    v_natural<BITS>(lut, cur.v[3], lanebase, n3);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      mma16816(o[j], __byte_perm(n0[j], n1[j], 0x5410), __byte_perm(n0[j], n1[j], 0x7632),
+               __byte_perm(n2[j], n3[j], 0x5410), __byte_perm(n2[j], n3[j], 0x7632), pb0, pb1);
   }
 }
 
-template <bool VEC16>
+template <int BITS, bool VEC16>
 __global__ void __launch_bounds__(256, 2)
 tq_attn_mma_kernel(AttnArgs a) {
   extern __shared__ __align__(16) unsigned char lut[];
@@ -416,11 +536,26 @@ tq_attn_mma_kernel(AttnArgs a) {
   int64_t tile_end = tile_begin + (int64_t)a.blocks_per_split * tpb;
   if (tile_end > tiles_total) tile_end = tiles_total;
 
-  // table: entry e -> half2(c[e >> 4], c[e & 15]), one copy per lane (bank = lane)
-  for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x) {
-    const int e = i >> 5, l = i & 31;   // a warp fills one entry: 32 distinct banks
-    *reinterpret_cast<uint32_t*>(lut + e * LUT_STRIDE + l * 4) =
-        pack_half2(a.centroids[e >> 4], a.centroids[e & 15]);
+  // lookup table, one copy per lane (bank = lane); a warp fills one entry
+  if constexpr (BITS == 4) {          // byte -> half2(c[hi nibble], c[lo nibble])
+    for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x) {
+      const int e = i >> 5, l = i & 31;
+      *reinterpret_cast<uint32_t*>(lut + e * LUT_STRIDE + l * 4) =
+          pack_half2(a.centroids[e >> 4], a.centroids[e & 15]);
+    }
+  } else if constexpr (BITS == 3) {   // 6 bits -> half2(c[hi 3 bits], c[lo 3 bits])
+    for (int i = threadIdx.x; i < 64 * 32; i += blockDim.x) {
+      const int e = i >> 5, l = i & 31;
+      *reinterpret_cast<uint32_t*>(lut + e * LUT3_STRIDE + l * 4) =
+          pack_half2(a.centroids[e >> 3], a.centroids[e & 7]);
+    }
+  } else {                            // byte -> four halves
+    for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x) {
+      const int e = i >> 5, l = i & 31;
+      *reinterpret_cast<uint2*>(lut + e * LUT_STRIDE + l * 8) =
+          make_uint2(pack_half2(a.centroids[e >> 6], a.centroids[(e >> 4) & 3]),
+                     pack_half2(a.centroids[(e >> 2) & 3], a.centroids[e & 3]));
+    }
   }
   __syncthreads();
 
@@ -446,9 +581,9 @@ tq_attn_mma_kernel(AttnArgs a) {
   }
 
   ThreadOffsets off;
-  off.kA = (int)(g * a.kp_sp + h * a.kp_sh + 16 * t);
+  off.kA = (int)(g * a.kp_sp + h * a.kp_sh + 4 * BITS * t);
   off.kB = (int)(off.kA + 8 * a.kp_sp);
-  off.v0 = (int)(2 * t * a.vp_sp + h * a.vp_sh + 8 * g);
+  off.v0 = (int)(2 * t * a.vp_sp + h * a.vp_sh + 2 * BITS * g);
   off.v1 = (int)(off.v0 + a.vp_sp);
   off.v2 = (int)(off.v0 + 8 * a.vp_sp);
   off.v3 = (int)(off.v0 + 9 * a.vp_sp);
@@ -469,29 +604,29 @@ tq_attn_mma_kernel(AttnArgs a) {
     const int cnt = n_tiles - base < 32 ? n_tiles - base : 32;
     int64_t my_pb = 0;
     if (lane < cnt) my_pb = phys_block(a, seq, (int)((first + (int64_t)(base + lane) * wph) / tpb));
-    TileData buf0, buf1;
+    TileData<BITS> buf0, buf1;
     {
       const int64_t tile = first + (int64_t)base * wph;
-      load_tile<VEC16>(a, off, __shfl_sync(0xffffffffu, my_pb, 0), (int)(tile % tpb) * 16, lane, buf0);
+      load_tile<BITS, VEC16>(a, off, __shfl_sync(0xffffffffu, my_pb, 0), (int)(tile % tpb) * 16, lane, buf0);
     }
 #pragma unroll 1
     for (int i = 0; i < cnt; i += 2) {
       const int64_t tile = first + (int64_t)(base + i) * wph;
       if (i + 1 < cnt) {
         const int64_t pb = __shfl_sync(0xffffffffu, my_pb, i + 1);
-        load_tile<VEC16>(a, off, pb, (int)((tile + wph) % tpb) * 16, lane, buf1);
+        load_tile<BITS, VEC16>(a, off, pb, (int)((tile + wph) % tpb) * 16, lane, buf1);
       }
       {
         const int64_t rem = ctx - tile * 16;
-        process_tile(lut, lanebase, g, bq, buf0, rem < 16 ? (int)rem : 16, o, st);
+        process_tile<BITS>(lut, lanebase, g, bq, buf0, rem < 16 ? (int)rem : 16, o, st);
       }
       if (i + 1 < cnt) {
         if (i + 2 < cnt) {
           const int64_t pb = __shfl_sync(0xffffffffu, my_pb, i + 2);
-          load_tile<VEC16>(a, off, pb, (int)((tile + 2 * wph) % tpb) * 16, lane, buf0);
+          load_tile<BITS, VEC16>(a, off, pb, (int)((tile + 2 * wph) % tpb) * 16, lane, buf0);
         }
         const int64_t rem = ctx - (tile + wph) * 16;
-        process_tile(lut, lanebase, g, bq, buf1, rem < 16 ? (int)rem : 16, o, st);
+        process_tile<BITS>(lut, lanebase, g, bq, buf1, rem < 16 ? (int)rem : 16, o, st);
       }
     }
   }
@@ -533,7 +668,7 @@ static Plan make_plan(int num_seqs, int num_q_heads, int num_kv_heads, int head_
                       int block_size, int max_blocks_per_seq, int blocks_per_split) {
   Plan p;
   const int G = num_q_heads / num_kv_heads;
-  p.mma = (head_dim == 128 && bits == 4 && G >= 1 && G <= 8 && block_size % 16 == 0);
+  p.mma = (head_dim == 128 && G >= 1 && G <= 8 && block_size % 16 == 0);
   if (blocks_per_split <= 0) blocks_per_split = (64 * 16 + block_size - 1) / block_size;  // ~1024 tokens
   if (blocks_per_split > max_blocks_per_seq) blocks_per_split = max_blocks_per_seq > 0 ? max_blocks_per_seq : 1;
   p.blocks_per_split = blocks_per_split;
@@ -657,10 +792,14 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
       int nh = p->num_kv_heads < 8 ? p->num_kv_heads : 8;
       dim3 grid(plan.num_splits, (p->num_kv_heads + 7) / 8, p->num_seqs);
       dim3 block(32 * nh * plan.warps_per_head);
-      auto kern = vec16 ? tq_attn_mma_kernel<true> : tq_attn_mma_kernel<false>;
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LUT_BYTES);
+      void (*kern)(AttnArgs) = nullptr;
+      int lut_bytes = LUT_BYTES;
+      if (p->bits == 4) kern = vec16 ? tq_attn_mma_kernel<4, true> : tq_attn_mma_kernel<4, false>;
+      else if (p->bits == 3) { kern = tq_attn_mma_kernel<3, false>; lut_bytes = 64 * LUT3_STRIDE; }
+      else kern = tq_attn_mma_kernel<2, false>;
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, lut_bytes);
       if (e != cudaSuccess) return fail((int)e, "attention: smem attribute: %s", cudaGetErrorString(e));
-      kern<<<grid, block, LUT_BYTES, st>>>(a);
+      kern<<<grid, block, lut_bytes, st>>>(a);
       if (int rc = check_launch("tq_attn_mma_kernel")) return rc;
     } else {
       dim3 grid(plan.num_splits, p->num_kv_heads, p->num_seqs);
