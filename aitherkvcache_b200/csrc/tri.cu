@@ -104,10 +104,8 @@ struct TriArgs {
   float* scores_out;              // optional [B][QH][S] pre-softmax logits (natural units)
 };
 
-constexpr int TD_WARPS = 4;
 constexpr int TD_LD = 136;                       // halves per row of the dense tiles (272 B: conflict-free ldmatrix)
 constexpr int TD_TILE_HALVES = 32 * TD_LD;
-constexpr size_t TD_SMEM = (size_t)TD_WARPS * 2 * TD_TILE_HALVES * sizeof(__half);
 
 __device__ __forceinline__ void mma16816_tri(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -157,23 +155,86 @@ __device__ __forceinline__ void sincos_reduced(float phi, float& s, float& c) {
   c = __cosf(r);
 }
 
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" :: "r"(d), "l"(gsrc));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
+
+// Shared-memory plan of one CTA (nh <= 8 KV heads, one warp each):
+//   dense tile per warp  [32 tokens][TD_LD halves]   (rotated keys, then values; all-zero between uses)
+//   two staging buffers  4 arrays x [nh][32 tokens][F bytes] + 2 x [32 tokens][nh] fp16 scales
 template <int F>
-__global__ void __launch_bounds__(TD_WARPS * 32)
+struct TriSmem {
+  static constexpr int WORDS = F / 4;                       // words per record
+  static constexpr int ARR = 8 * 32 * WORDS;                // words per staged array (8 heads)
+  static constexpr int STAGE_WORDS = 4 * ARR + 2 * 128;     // + scales: 2 x 32 x 8 halves = 2 x 128 words
+  static constexpr size_t bytes(int nh) { return (size_t)nh * TD_TILE_HALVES * 2 + 2 * STAGE_WORDS * 4; }
+};
+
+template <int F>
+__device__ __forceinline__ void tri_stage_load(const TriArgs& a, uint32_t* stage, int b, int hg0, int nh,
+                                               int s0, int s_end) {
+  using SM = TriSmem<F>;
+  const int row_words = nh * SM::WORDS;                     // words per token of this head group
+  const int total = 32 * row_words;
+  const uint8_t* const srcs[4] = {a.k_idx, a.k_packed, a.v_idx, a.v_packed};
+  for (int i = threadIdx.x; i < total; i += blockDim.x) {
+    const int tok = i / row_words, j = i - tok * row_words;
+    if (s0 + tok >= s_end) continue;
+    const int head = j / SM::WORDS, wj = j - head * SM::WORDS;
+    const int64_t g_off = (((int64_t)b * a.S + s0 + tok) * a.KVH + hg0) * F + 4 * j;
+    const int s_off = (head * 32 + tok) * SM::WORDS + wj;
+#pragma unroll
+    for (int arr = 0; arr < 4; ++arr) cp_async4(stage + arr * SM::ARR + s_off, srcs[arr] + g_off);
+  }
+  // scales, staged as [tok][8] halves: pairs of heads by 4-byte async copies when the layout
+  // allows it, single halves through registers otherwise
+  __half* sk = reinterpret_cast<__half*>(stage + 4 * SM::ARR);
+  __half* sv = sk + 256;
+  if (((nh | a.KVH) & 1) == 0) {
+    const int hp = nh / 2;
+    for (int i = threadIdx.x; i < 32 * hp; i += blockDim.x) {
+      const int tok = i / hp, pr = i - tok * hp;
+      if (s0 + tok >= s_end) continue;
+      const int64_t rec = ((int64_t)b * a.S + s0 + tok) * a.KVH + hg0 + 2 * pr;
+      cp_async4(sk + tok * 8 + 2 * pr, a.k_scales + rec);
+      cp_async4(sv + tok * 8 + 2 * pr, a.v_scales + rec);
+    }
+  } else {
+    for (int i = threadIdx.x; i < 32 * nh; i += blockDim.x) {
+      const int tok = i / nh, head = i - tok * nh;
+      if (s0 + tok >= s_end) continue;
+      const int64_t rec = ((int64_t)b * a.S + s0 + tok) * a.KVH + hg0 + head;
+      sk[tok * 8 + head] = a.k_scales[rec];
+      sv[tok * 8 + head] = a.v_scales[rec];
+    }
+  }
+}
+
+template <int F>
+__global__ void __launch_bounds__(256, 2)
 tri_decode_kernel(TriArgs a) {
-  extern __shared__ __align__(16) __half tiles[];
+  using SM = TriSmem<F>;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ float s_theta[64];
-  __shared__ float s_deq[16];
-  // kv head is the fastest grid index: the heads of a token range are interleaved at F-byte
-  // granularity in memory, so CTAs that run together share DRAM sectors through L2
-  const int kvh = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
+  const int hg = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
+  const int hg0 = hg * 8;
+  const int nh = (a.KVH - hg0 < 8) ? a.KVH - hg0 : 8;        // heads (= warps) of this CTA
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   if (threadIdx.x < 64) s_theta[threadIdx.x] = a.theta[threadIdx.x];
-  if (threadIdx.x < 16) s_deq[threadIdx.x] = __fsub_rn(__fdiv_rn((float)threadIdx.x, 7.5f), 1.0f);
-  __syncthreads();
-  __half* kt = tiles + (size_t)warp * 2 * TD_TILE_HALVES;   // [32 tokens][TD_LD]: rotated keys, dense
-  __half* vt = kt + TD_TILE_HALVES;                          // [32 tokens][TD_LD]: values, dense
+  __half* tile = reinterpret_cast<__half*>(smem_raw) + (size_t)warp * TD_TILE_HALVES;
+  uint32_t* stage0 = reinterpret_cast<uint32_t*>(smem_raw + (size_t)nh * TD_TILE_HALVES * 2);
+  const int kvh = hg0 + warp;
   const int G = a.QH / a.KVH;
+
+  {   // the dense tile starts (and is left after every use) all zero
+    uint4* row = reinterpret_cast<uint4*>(tile + lane * TD_LD);
+#pragma unroll
+    for (int i = 0; i < 17; ++i) row[i] = make_uint4(0, 0, 0, 0);
+  }
 
   // query fragments: B operand [k = dim][n = q head of the group]
   uint32_t bq[8][2];
@@ -201,44 +262,49 @@ tri_decode_kernel(TriArgs a) {
   const int s_begin = split * a.tokens_per_split;
   int s_end = s_begin + a.tokens_per_split;
   if (s_end > a.S) s_end = a.S;
-  for (int s0 = s_begin + warp * 32; s0 < s_end; s0 += TD_WARPS * 32) {
+  const int n_iter = (s_end - s_begin + 31) / 32;
+
+  tri_stage_load<F>(a, stage0, b, hg0, nh, s_begin, s_end);
+  cp_async_commit();
+  for (int it = 0; it < n_iter; ++it) {
+    const int s0 = s_begin + it * 32;
+    uint32_t* st = stage0 + (it & 1) * SM::STAGE_WORDS;
+    cp_async_wait_all();
+    __syncthreads();            // stage `it` is complete; everyone is done with stage it-1
+    if (it + 1 < n_iter) tri_stage_load<F>(a, stage0 + ((it + 1) & 1) * SM::STAGE_WORDS, b, hg0, nh, s0 + 32, s_end);
+    cp_async_commit();
+
     const int s = s0 + lane;
     const bool valid = s < s_end;
-    // ---- zero this lane's rows of both tiles ----
-    {
-      uint4 z = make_uint4(0, 0, 0, 0);
-      uint4* rk = reinterpret_cast<uint4*>(kt + lane * TD_LD);
-      uint4* rv = reinterpret_cast<uint4*>(vt + lane * TD_LD);
-#pragma unroll
-      for (int i = 0; i < 16; ++i) { rk[i] = z; rv[i] = z; }
-    }
+    uint32_t kiw[SM::WORDS], kpw[SM::WORDS], viw[SM::WORDS], vpw[SM::WORDS];
+    float ks = 0.f, vs = 0.f, delta = 0.f;
     if (valid) {
-      const int64_t rec = ((int64_t)b * a.S + s) * a.KVH + kvh;
-      const float kpos = (float)(a.key_positions ? a.key_positions[(int64_t)b * a.S + s] : a.key_pos_start + s);
-      const float delta = __fsub_rn(kpos, qpos);
-      const float ks = __half2float(a.k_scales[rec]);
-      const float vs = __half2float(a.v_scales[rec]);
-      // F bytes per array and token (F is a multiple of 4): word loads, bytes taken by shifts
-      uint32_t kiw[F / 4], kpw[F / 4], viw[F / 4], vpw[F / 4];
+      const int r = (warp * 32 + lane) * SM::WORDS;
 #pragma unroll
-      for (int w = 0; w < F / 4; ++w) {
-        kiw[w] = reinterpret_cast<const uint32_t*>(a.k_idx + rec * F)[w];
-        kpw[w] = reinterpret_cast<const uint32_t*>(a.k_packed + rec * F)[w];
-        viw[w] = reinterpret_cast<const uint32_t*>(a.v_idx + rec * F)[w];
-        vpw[w] = reinterpret_cast<const uint32_t*>(a.v_packed + rec * F)[w];
+      for (int w = 0; w < SM::WORDS; ++w) {
+        kiw[w] = st[r + w];
+        kpw[w] = st[SM::ARR + r + w];
+        viw[w] = st[2 * SM::ARR + r + w];
+        vpw[w] = st[3 * SM::ARR + r + w];
       }
-      __half2* krow = reinterpret_cast<__half2*>(kt + lane * TD_LD);
-      __half2* vrow = reinterpret_cast<__half2*>(vt + lane * TD_LD);
+      const __half* sk = reinterpret_cast<const __half*>(st + 4 * SM::ARR);
+      ks = __half2float(sk[lane * 8 + warp]);
+      vs = __half2float(sk[256 + lane * 8 + warp]);
+      const float kpos = (float)(a.key_positions ? a.key_positions[(int64_t)b * a.S + s] : a.key_pos_start + s);
+      delta = __fsub_rn(kpos, qpos);
+    }
+    __half2* row = reinterpret_cast<__half2*>(tile + lane * TD_LD);
+    // ---- rotated keys into the dense tile ----
+    if (valid) {
+      const float ka = ks * 0.13333334f;       // (n / 7.5 - 1) * scale = n * (scale / 7.5) - scale
 #pragma unroll
       for (int f = 0; f < F; ++f) {
         const int sh = 8 * (f & 3);
         const int id = (kiw[f >> 2] >> sh) & 63, pk = (kpw[f >> 2] >> sh) & 255;
-        const float k0 = __fmul_rn(s_deq[pk >> 4], ks), k1 = __fmul_rn(s_deq[pk & 15], ks);
+        const float k0 = __fmaf_rn((float)(pk >> 4), ka, -ks), k1 = __fmaf_rn((float)(pk & 15), ka, -ks);
         float sn, cs;
         sincos_reduced(__fmul_rn(delta, s_theta[id]), sn, cs);
-        krow[id] = __floats2half2_rn(k0 * cs - k1 * sn, k1 * cs + k0 * sn);
-        const int idv = (viw[f >> 2] >> sh) & 63, pv = (vpw[f >> 2] >> sh) & 255;
-        vrow[idv] = __floats2half2_rn(__fmul_rn(s_deq[pv >> 4], vs), __fmul_rn(s_deq[pv & 15], vs));
+        row[id] = __floats2half2_rn(k0 * cs - k1 * sn, k1 * cs + k0 * sn);
       }
     }
     __syncwarp();
@@ -251,16 +317,24 @@ tri_decode_kernel(TriArgs a) {
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk) {
         uint32_t af[4];
-        ldmatrix_x4(af, kt + (mt * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * TD_LD + kk * 16 + 8 * (lane >> 4));
+        ldmatrix_x4(af, tile + (mt * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * TD_LD + kk * 16 + 8 * (lane >> 4));
         mma16816_tri(sc[mt], af, bq[kk][0], bq[kk][1]);
       }
     }
-    const int rem = s_end - s0;    // tokens of this tile that exist
+    __syncwarp();
+    // ---- take the keys out again, put the values in ----
+    if (valid) {
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt) {
-      if (mt * 16 + g >= rem) { sc[mt][0] = -CUDART_INF_F; sc[mt][1] = -CUDART_INF_F; }
-      if (mt * 16 + g + 8 >= rem) { sc[mt][2] = -CUDART_INF_F; sc[mt][3] = -CUDART_INF_F; }
+      for (int f = 0; f < F; ++f) row[(kiw[f >> 2] >> (8 * (f & 3))) & 63] = __floats2half2_rn(0.f, 0.f);
+      const float va = vs * 0.13333334f;
+#pragma unroll
+      for (int f = 0; f < F; ++f) {
+        const int sh = 8 * (f & 3);
+        const int idv = (viw[f >> 2] >> sh) & 63, pv = (vpw[f >> 2] >> sh) & 255;
+        row[idv] = __floats2half2_rn(__fmaf_rn((float)(pv >> 4), va, -vs), __fmaf_rn((float)(pv & 15), va, -vs));
+      }
     }
+    const int rem = s_end - s0;    // tokens of this tile that exist
     if (a.scores_out != nullptr) {
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt)
@@ -271,6 +345,11 @@ tri_decode_kernel(TriArgs a) {
             a.scores_out[((int64_t)b * a.QH + kvh * G + qg) * a.S + s0 + tok] = sc[mt][e] * 0.6931471805599453f;
         }
     }
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {
+      if (mt * 16 + g >= rem) { sc[mt][0] = -CUDART_INF_F; sc[mt][1] = -CUDART_INF_F; }
+      if (mt * 16 + g + 8 >= rem) { sc[mt][2] = -CUDART_INF_F; sc[mt][3] = -CUDART_INF_F; }
+    }
     float mx0 = fmaxf(fmaxf(sc[0][0], sc[0][2]), fmaxf(sc[1][0], sc[1][2]));
     float mx1 = fmaxf(fmaxf(sc[0][1], sc[0][3]), fmaxf(sc[1][1], sc[1][3]));
 #pragma unroll
@@ -279,11 +358,13 @@ tri_decode_kernel(TriArgs a) {
       mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
     }
     const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-    const float al0 = ex2a(m0 - mn0), al1 = ex2a(m1 - mn1);
-    m0 = mn0; m1 = mn1;
-    l0 *= al0; l1 *= al1;
+    if (__any_sync(0xffffffffu, (mn0 != m0) | (mn1 != m1))) {
+      const float al0 = ex2a(m0 - mn0), al1 = ex2a(m1 - mn1);
+      l0 *= al0; l1 *= al1;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) { o[j][0] *= al0; o[j][1] *= al1; o[j][2] *= al0; o[j][3] *= al1; }
+      for (int j = 0; j < 8; ++j) { o[j][0] *= al0; o[j][1] *= al1; o[j][2] *= al0; o[j][3] *= al1; }
+      m0 = mn0; m1 = mn1;
+    }
     uint32_t pb[2][2];
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt) {
@@ -294,17 +375,22 @@ tri_decode_kernel(TriArgs a) {
       pb[mt][0] = movmatrix_trans_tri(pack_h2(p0, p1));
       pb[mt][1] = movmatrix_trans_tri(pack_h2(p2, p3));
     }
+    __syncwarp();
     // ---- values: O^T[dims][q heads] += V^T P^T ----
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
         uint32_t af[4];
-        ldmatrix_x4_trans(af, vt + (mt * 16 + (lane & 7) + 8 * (lane >> 4)) * TD_LD + j * 16 + 8 * ((lane >> 3) & 1));
+        ldmatrix_x4_trans(af, tile + (mt * 16 + (lane & 7) + 8 * (lane >> 4)) * TD_LD + j * 16 + 8 * ((lane >> 3) & 1));
         mma16816_tri(o[j], af, pb[mt][0], pb[mt][1]);
       }
     }
     __syncwarp();
+    if (valid) {
+#pragma unroll
+      for (int f = 0; f < F; ++f) row[(viw[f >> 2] >> (8 * (f & 3))) & 63] = __floats2half2_rn(0.f, 0.f);
+    }
   }
 
 #pragma unroll
@@ -312,32 +398,32 @@ tri_decode_kernel(TriArgs a) {
     l0 += __shfl_xor_sync(0xffffffffu, l0, off);
     l1 += __shfl_xor_sync(0xffffffffu, l1, off);
   }
-  const int part = split * TD_WARPS + warp;
+  const int part = split;
 #pragma unroll
   for (int e = 0; e < 2; ++e) {
     const int qg = 2 * t + e;
     if (qg >= G) continue;
-    const int64_t row = (int64_t)b * a.QH + kvh * G + qg;
-    float* pa = a.part_acc + (row * a.num_parts + part) * 128;
+    const int64_t rowi = (int64_t)b * a.QH + kvh * G + qg;
+    float* pa = a.part_acc + (rowi * a.num_parts + part) * 128;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {   // M-tile j: rows g, g+8 -> dims 16j+g, 16j+g+8
       pa[16 * j + g] = o[j][e];
       pa[16 * j + g + 8] = o[j][2 + e];
     }
     if (g == 0) {
-      a.part_ml[(row * a.num_parts + part) * 2] = e ? m1 : m0;
-      a.part_ml[(row * a.num_parts + part) * 2 + 1] = e ? l1 : l0;
+      a.part_ml[(rowi * a.num_parts + part) * 2] = e ? m1 : m0;
+      a.part_ml[(rowi * a.num_parts + part) * 2 + 1] = e ? l1 : l0;
     }
   }
 }
 
 static void tri_plan(int B, int QH, int S, int tps_in, int* tps, int* parts, size_t* off_ml, size_t* total) {
-  int tp = tps_in > 0 ? tps_in : 2048;
+  int tp = tps_in > 0 ? tps_in : 1024;
   if (tp > S) tp = S > 0 ? S : 1;
   tp = (tp + 31) / 32 * 32;
   const int splits = S > 0 ? (S + tp - 1) / tp : 1;
   *tps = tp;
-  *parts = splits * TD_WARPS;
+  *parts = splits;
   const size_t rows = (size_t)B * QH;
   auto al = [](size_t v) { return (v + 255) & ~(size_t)255; };
   *off_ml = al(rows * (size_t)*parts * 128 * sizeof(float));
@@ -426,11 +512,13 @@ AKV_EXPORT int akv_tri_decode_step(const akv_tri_decode_params* p) {
   a.scores_out = p->scores_out;
   if (p->ev_kernel_start) cudaEventRecord((cudaEvent_t)p->ev_kernel_start, st);
   if (p->seq_len > 0) {
-    dim3 grid(p->num_kv_heads, parts / TD_WARPS, p->batch);
+    const int nh = p->num_kv_heads < 8 ? p->num_kv_heads : 8;
+    dim3 grid((p->num_kv_heads + 7) / 8, parts, p->batch);
     cudaError_t e = cudaSuccess;
 #define AKV_TRI(FF)                                                                                  \
-    e = cudaFuncSetAttribute(tri_decode_kernel<FF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TD_SMEM); \
-    if (e == cudaSuccess) tri_decode_kernel<FF><<<grid, TD_WARPS * 32, TD_SMEM, st>>>(a);
+    e = cudaFuncSetAttribute(tri_decode_kernel<FF>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
+                             (int)TriSmem<FF>::bytes(8));                                                \
+    if (e == cudaSuccess) tri_decode_kernel<FF><<<grid, 32 * nh, TriSmem<FF>::bytes(nh), st>>>(a);
     if (p->num_freqs == 8) { AKV_TRI(8) } else if (p->num_freqs == 12) { AKV_TRI(12) } else { AKV_TRI(16) }
 #undef AKV_TRI
     if (e != cudaSuccess) return fail((int)e, "tri decode: smem attribute: %s", cudaGetErrorString(e));
