@@ -19,6 +19,7 @@
 //     any GQA ratio.  Scalar; lanes own dims.
 #include "common.cuh"
 #include <math_constants.h>
+#include <stdlib.h>
 
 // 1: one norm load per lane, broadcast by shuffles; 0: four norm loads per thread.
 // Measured equal on B200; the shuffle form spills less.
@@ -66,9 +67,15 @@ __global__ void akv_qrot_kernel(const void* __restrict__ q, int q_dtype, int64_t
     qs[j] = load_as_float(q, q_dtype, s * q_ss + qh * q_sh + j);
   __syncthreads();
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
-    float acc = 0.f;
-    for (int j = 0; j < D; ++j) acc = __fmaf_rn(rot_t[(int64_t)j * D + i], qs[j], acc);
-    qrot[(int64_t)blockIdx.x * D + i] = acc * premul;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < D; j += 16) {      // 16 loads in flight per round (the matrix sits in L2)
+      float r[16];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) r[k] = rot_t[(int64_t)(j + k) * D + i];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) acc[k & 3] = __fmaf_rn(r[k], qs[j + k], acc[k & 3]);
+    }
+    qrot[(int64_t)blockIdx.x * D + i] = ((acc[0] + acc[1]) + (acc[2] + acc[3])) * premul;
   }
 }
 
@@ -81,7 +88,9 @@ __global__ void akv_qrot_kernel(const void* __restrict__ q, int q_dtype, int64_t
 // for a later cross-device merge.
 // ---------------------------------------------------------------------------
 __global__ void akv_merge_kernel(MergeArgs a) {
-  extern __shared__ float sm[];   // [D]
+  extern __shared__ float sm[];   // [D] merged vector, then [np] weights
+  float* wts = sm + a.D;
+  __shared__ float s_red[2];
   const int row = blockIdx.x;
   const int seq = row / a.num_q_heads, qh = row % a.num_q_heads;
   int np = a.np;
@@ -92,23 +101,45 @@ __global__ void akv_merge_kernel(MergeArgs a) {
     np = (int)(v < np ? v : np);
   }
   const float* ml = a.ml + (int64_t)row * a.ml_row;
-  float M = -CUDART_INF_F;
-  for (int p = 0; p < np; ++p) {
-    float l = ml[p * a.ml_part + 1];
-    if (l > 0.f) M = fmaxf(M, ml[p * a.ml_part]);
+  // weights w_p = 2^(m_p - M) for parts with l_p > 0 (first warp), L = sum l_p w_p
+  if (threadIdx.x < 32) {
+    float M = -CUDART_INF_F;
+    for (int p = threadIdx.x; p < np; p += 32)
+      if (ml[(int64_t)p * a.ml_part + 1] > 0.f) M = fmaxf(M, ml[(int64_t)p * a.ml_part]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    float L = 0.f;
+    for (int p = threadIdx.x; p < np; p += 32) {
+      const float l = ml[(int64_t)p * a.ml_part + 1];
+      const float w = (l > 0.f) ? exp2f(ml[(int64_t)p * a.ml_part] - M) : 0.f;
+      wts[p] = w;
+      L += l * w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+    if (threadIdx.x == 0) { s_red[0] = M; s_red[1] = L; }
   }
-  float L = 0.f;
-  for (int p = 0; p < np; ++p) {
-    float l = ml[p * a.ml_part + 1];
-    if (l > 0.f) L += l * exp2f(ml[p * a.ml_part] - M);
-  }
+  __syncthreads();
+  const float M = s_red[0], L = s_red[1];
   const float* acc = a.acc + (int64_t)row * a.acc_row;
   for (int d = threadIdx.x; d < a.D; d += blockDim.x) {
-    float o = 0.f;
-    for (int p = 0; p < np; ++p) {
-      float l = ml[p * a.ml_part + 1];
-      if (l > 0.f) o += acc[(int64_t)p * a.acc_part + d] * exp2f(ml[p * a.ml_part] - M);
+    float o4[4] = {0.f, 0.f, 0.f, 0.f};    // independent chains so the loads overlap
+    int p = 0;
+    for (; p + 8 <= np; p += 8) {          // 8 loads in flight per round
+      float v[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] = acc[(int64_t)(p + k) * a.acc_part + d];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float w = wts[p + k];
+        o4[k & 3] = (w != 0.f) ? __fmaf_rn(v[k], w, o4[k & 3]) : o4[k & 3];
+      }
     }
+    for (; p < np; ++p) {
+      const float w = wts[p];
+      if (w != 0.f) o4[0] = __fmaf_rn(acc[(int64_t)p * a.acc_part + d], w, o4[0]);
+    }
+    const float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
     if (a.mode == MERGE_RAW) {
       a.raw_out[(int64_t)row * (a.D + 2) + 2 + d] = o;
     } else {
@@ -127,14 +158,20 @@ __global__ void akv_merge_kernel(MergeArgs a) {
   if (a.mode == MERGE_NORMALIZE) return;
   __syncthreads();
   for (int j = threadIdx.x; j < a.D; j += blockDim.x) {
-    float x = 0.f;
-    for (int i = 0; i < a.D; ++i) x = __fmaf_rn(sm[i], a.rot[(int64_t)i * a.D + j], x);
-    store_from_float(a.out, a.out_dtype, seq * a.out_ss + qh * a.out_sh + j, x);
+    float x4[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int i = 0; i < a.D; i += 16) {
+      float r[16];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) r[k] = a.rot[(int64_t)(i + k) * a.D + j];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) x4[k & 3] = __fmaf_rn(sm[i + k], r[k], x4[k & 3]);
+    }
+    store_from_float(a.out, a.out_dtype, seq * a.out_ss + qh * a.out_sh + j, (x4[0] + x4[1]) + (x4[2] + x4[3]));
   }
 }
 
 int launch_merge(const MergeArgs& a, int rows, cudaStream_t st) {
-  akv_merge_kernel<<<rows, a.D < 128 ? a.D : 128, a.D * sizeof(float), st>>>(a);
+  akv_merge_kernel<<<rows, a.D < 128 ? (a.D < 32 ? 32 : a.D) : 128, (a.D + (a.np > 0 ? a.np : 1)) * sizeof(float), st>>>(a);
   return check_launch("akv_merge_kernel");
 }
 
@@ -656,6 +693,173 @@ tq_attn_mma_kernel(AttnArgs a) {
 }
 
 
+// ---------------------------------------------------------------------------
+// Pipelined variant for the common cache layout (4-bit, 8 KV heads per CTA, block_size 16,
+// token rows of 8 x 64 contiguous bytes, norms [block][16][heads] contiguous).
+//
+// A CTA of 16 warps streams whole 16-token blocks (8 KB of K codes, 8 KB of V codes, 2 x 512 B
+// of norms) into a 4-stage shared-memory ring with 16-byte asynchronous copies, two blocks per
+// stage; warp (head, j) consumes block j of every stage.  Copies are written through an XOR
+// swizzle so that the fragment reads below are free of bank conflicts:
+//   K: 64-byte head slot h is stored at slot h ^ (token & 1)      (two token rows per 128-bit read phase)
+//   V: 32-byte slot s is stored at slot s ^ ((token >> 1) & 3)    (four token rows per 64-bit read phase)
+// ---------------------------------------------------------------------------
+constexpr int PIPE_STAGES = 4;
+constexpr int PIPE_STAGE_BYTES = 2 * 8192 + 2 * 8192 + 4 * 512;       // K, V, norms of two blocks
+constexpr int PIPE_SMEM = LUT_BYTES + PIPE_STAGES * PIPE_STAGE_BYTES;  // 204800
+constexpr int PIPE_MAX_BLOCKS = 256;                                   // blocks per split
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" :: "r"(d), "l"(gsrc));
+}
+
+__global__ void __launch_bounds__(512, 1)
+tq4_attn_pipe_kernel(AttnArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ int s_pb[PIPE_MAX_BLOCKS];
+  unsigned char* lut = smem;
+  unsigned char* ring = smem + LUT_BYTES;
+  const int split = blockIdx.x, hg = blockIdx.y, seq = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int64_t ctx = load_index(a.context_lens, a.cl_dtype, seq);
+  const int64_t nblk = (ctx + 15) / 16;
+  const int64_t blk_begin = (int64_t)split * a.blocks_per_split;
+  if (blk_begin >= nblk) return;   // uniform for the CTA
+  const int nb = (int)((blk_begin + a.blocks_per_split < nblk ? blk_begin + a.blocks_per_split : nblk) - blk_begin);
+  const int n_ss = (nb + 1) / 2;
+
+  for (int i = tid; i < nb; i += 512) s_pb[i] = (int)phys_block(a, seq, (int)(blk_begin + i));
+  for (int i = tid; i < 256 * 32; i += 512) {
+    const int e = i >> 5, l = i & 31;
+    *reinterpret_cast<uint32_t*>(lut + e * LUT_STRIDE + l * 4) =
+        pack_half2(a.centroids[e >> 4], a.centroids[e & 15]);
+  }
+  __syncthreads();
+
+  // producer role of this thread: one 16-byte chunk of K and of V per block
+  const int c_tok = tid >> 5, c_r = tid & 31;
+  const int k_dst = c_tok * 512 + (((c_r >> 2) ^ (c_tok & 1)) << 6) + (c_r & 3) * 16;
+  const int v_dst = c_tok * 512 + (((c_r >> 1) ^ ((c_tok >> 1) & 3)) << 5) + (c_r & 1) * 16;
+  const int64_t k_src = (int64_t)c_tok * a.kp_sp + hg * 512 + c_r * 16;
+  const int64_t v_src = (int64_t)c_tok * a.vp_sp + hg * 512 + c_r * 16;
+  auto issue = [&](int ss) {
+    unsigned char* st = ring + (ss % PIPE_STAGES) * PIPE_STAGE_BYTES;
+#pragma unroll
+    for (int b2 = 0; b2 < 2; ++b2) {
+      const int bi = 2 * ss + b2;
+      if (bi >= nb) break;
+      const int64_t pb = s_pb[bi];
+      cp_async16(st + b2 * 8192 + k_dst, a.k_packed + pb * a.kp_sb + k_src);
+      cp_async16(st + 16384 + b2 * 8192 + v_dst, a.v_packed + pb * a.vp_sb + v_src);
+    }
+    if (tid < 128) {   // norms: 32 chunks of 16 bytes per (K|V, block)
+      const int which = tid >> 5, ch = tid & 31, b2 = which & 1;
+      const int bi = 2 * ss + b2;
+      if (bi < nb) {
+        const int64_t pb = s_pb[bi];
+        const int tok = ch >> 1, half = ch & 1;
+        const float* src = (which < 2)
+            ? a.k_norms + pb * a.kn_sb + (int64_t)tok * a.kn_sp + hg * 8 + half * 4
+            : a.v_norms + pb * a.vn_sb + (int64_t)tok * a.vn_sp + hg * 8 + half * 4;
+        cp_async16(st + 32768 + which * 512 + ch * 16, src);
+      }
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
+  };
+
+  const int hl = warp & 7, wj = warp >> 3;
+  const int h = hg * 8 + hl;
+  const int G = a.num_q_heads / a.num_kv_heads;
+  const uint32_t lanebase = lane * 4;
+  uint32_t bq[8][2];
+  {
+    const float* qp = a.qrot + ((int64_t)seq * a.num_q_heads + h * G + (g < G ? g : 0)) * 128 + 32 * t;
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      float4 f = *reinterpret_cast<const float4*>(qp + 4 * kk);
+      if (g >= G) f = make_float4(0.f, 0.f, 0.f, 0.f);
+      bq[kk][0] = pack_half2(f.x, f.y);
+      bq[kk][1] = pack_half2(f.z, f.w);
+    }
+  }
+  // consumer offsets inside a stage
+  const int kA_off = wj * 8192 + g * 512 + ((hl ^ (g & 1)) << 6) + 16 * t;          // token g (g+8: +4096)
+  int v_off[4];
+  {
+    const int toks[4] = {2 * t, 2 * t + 1, 2 * t + 8, 2 * t + 9};
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      v_off[i] = 16384 + wj * 8192 + toks[i] * 512 + (((2 * hl + (g >> 2)) ^ ((toks[i] >> 1) & 3)) << 5) + (g & 3) * 8;
+  }
+  const int n_off = 32768 + (lane < 16 ? wj * 512 + (lane * 8 + hl) * 4 : 1024 + wj * 512 + ((lane - 16) * 8 + hl) * 4);
+
+  float o[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+  SoftmaxState st{-CUDART_INF_F, -CUDART_INF_F, 0.f, 0.f};
+
+#pragma unroll
+  for (int ss = 0; ss < PIPE_STAGES - 1; ++ss) {
+    if (ss < n_ss) issue(ss);
+    else asm volatile("cp.async.commit_group;\n" ::);
+  }
+  for (int it = 0; it < n_ss; ++it) {
+    asm volatile("cp.async.wait_group %0;\n" :: "n"(PIPE_STAGES - 2) : "memory");
+    __syncthreads();                 // stage `it` has landed; stage it-1 is free again
+    if (it + PIPE_STAGES - 1 < n_ss) issue(it + PIPE_STAGES - 1);
+    else asm volatile("cp.async.commit_group;\n" ::);
+    const int bi = 2 * it + wj;
+    if (bi < nb) {
+      const unsigned char* sb = ring + (it % PIPE_STAGES) * PIPE_STAGE_BYTES;
+      TileData<4> cur;
+      const uint4 ka = *reinterpret_cast<const uint4*>(sb + kA_off);
+      const uint4 kb = *reinterpret_cast<const uint4*>(sb + kA_off + 4096);
+      cur.kA[0] = ka.x; cur.kA[1] = ka.y; cur.kA[2] = ka.z; cur.kA[3] = ka.w;
+      cur.kB[0] = kb.x; cur.kB[1] = kb.y; cur.kB[2] = kb.z; cur.kB[3] = kb.w;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint2 v = *reinterpret_cast<const uint2*>(sb + v_off[i]);
+        cur.v[i][0] = v.x; cur.v[i][1] = v.y;
+      }
+#if AKV_NORM_SHFL
+      cur.nrm = *reinterpret_cast<const float*>(sb + n_off);
+#else
+      cur.nkA = *reinterpret_cast<const float*>(sb + 32768 + wj * 512 + (g * 8 + hl) * 4);
+      cur.nkB = *reinterpret_cast<const float*>(sb + 32768 + wj * 512 + ((g + 8) * 8 + hl) * 4);
+      cur.nvA = *reinterpret_cast<const float*>(sb + 33792 + wj * 512 + (g * 8 + hl) * 4);
+      cur.nvB = *reinterpret_cast<const float*>(sb + 33792 + wj * 512 + ((g + 8) * 8 + hl) * 4);
+#endif
+      const int64_t rem = ctx - (blk_begin + bi) * 16;
+      process_tile<4>(lut, lanebase, g, bq, cur, rem < 16 ? (int)rem : 16, o, st);
+    }
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+
+  float l0 = st.l0, l1 = st.l1;
+#pragma unroll
+  for (int offs = 4; offs < 32; offs <<= 1) {
+    l0 += __shfl_xor_sync(0xffffffffu, l0, offs);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, offs);
+  }
+  const int part = split * 2 + wj;
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const int qg = 2 * t + e;
+    if (qg >= G) continue;
+    const int64_t row = (int64_t)seq * a.num_q_heads + h * G + qg;
+    float* pa = a.part_acc + (row * a.num_parts + part) * 128;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      *reinterpret_cast<float2*>(pa + 16 * g + 2 * j) = make_float2(o[j][e], o[j][2 + e]);
+    if (g == 0) {
+      a.part_ml[(row * a.num_parts + part) * 2] = e ? st.m1 : st.m0;
+      a.part_ml[(row * a.num_parts + part) * 2 + 1] = e ? l1 : l0;
+    }
+  }
+}
+
 static inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 struct Plan {
@@ -680,11 +884,13 @@ static Plan make_plan(int num_seqs, int num_q_heads, int num_kv_heads, int head_
     p.warps_per_head = GEN_WARPS;
   }
   p.num_parts = p.num_splits * p.warps_per_head;
+  // the pipelined 4-bit kernel writes two partials per split; size the buffers for either kernel
+  const size_t parts_alloc = (size_t)p.num_splits * (p.warps_per_head > 2 ? p.warps_per_head : 2);
   size_t rows = (size_t)num_seqs * num_q_heads;
   p.off_qrot = 0;
   p.off_acc = align256(rows * head_dim * sizeof(float));
-  p.off_ml = p.off_acc + align256(rows * p.num_parts * head_dim * sizeof(float));
-  p.total = p.off_ml + align256(rows * p.num_parts * 2 * sizeof(float));
+  p.off_ml = p.off_acc + align256(rows * parts_alloc * head_dim * sizeof(float));
+  p.total = p.off_ml + align256(rows * parts_alloc * 2 * sizeof(float));
   return p;
 }
 
@@ -789,6 +995,25 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
                    (p->vp_stride_pos % 16 == 0) && (p->vp_stride_head % 16 == 0) &&
                    (reinterpret_cast<uintptr_t>(p->k_packed) % 16 == 0) &&
                    (reinterpret_cast<uintptr_t>(p->v_packed) % 16 == 0);
+      static const bool no_pipe = getenv("AKV_NO_PIPE") != nullptr;
+      const bool pipe = !no_pipe && vec16 && p->bits == 4 && p->block_size == 16 && p->num_kv_heads % 8 == 0 &&
+                        p->kp_stride_head == 64 && p->vp_stride_head == 64 && p->kn_stride_head == 1 &&
+                        p->vn_stride_head == 1 && p->kn_stride_pos % 4 == 0 && p->vn_stride_pos % 4 == 0 &&
+                        p->kn_stride_blk % 4 == 0 && p->vn_stride_blk % 4 == 0 &&
+                        reinterpret_cast<uintptr_t>(p->k_norms) % 16 == 0 &&
+                        reinterpret_cast<uintptr_t>(p->v_norms) % 16 == 0 &&
+                        plan.blocks_per_split <= PIPE_MAX_BLOCKS;
+      if (pipe) {
+        a.warps_per_head = 2;
+        a.num_parts = plan.num_splits * 2;
+        plan.warps_per_head = 2;
+        plan.num_parts = a.num_parts;
+        cudaError_t e = cudaFuncSetAttribute(tq4_attn_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PIPE_SMEM);
+        if (e != cudaSuccess) return fail((int)e, "attention: smem attribute: %s", cudaGetErrorString(e));
+        dim3 grid(plan.num_splits, p->num_kv_heads / 8, p->num_seqs);
+        tq4_attn_pipe_kernel<<<grid, 512, PIPE_SMEM, st>>>(a);
+        if (int rc = check_launch("tq4_attn_pipe_kernel")) return rc;
+      } else {
       int nh = p->num_kv_heads < 8 ? p->num_kv_heads : 8;
       dim3 grid(plan.num_splits, (p->num_kv_heads + 7) / 8, p->num_seqs);
       dim3 block(32 * nh * plan.warps_per_head);
@@ -801,6 +1026,7 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
       if (e != cudaSuccess) return fail((int)e, "attention: smem attribute: %s", cudaGetErrorString(e));
       kern<<<grid, block, lut_bytes, st>>>(a);
       if (int rc = check_launch("tq_attn_mma_kernel")) return rc;
+      }
     } else {
       dim3 grid(plan.num_splits, p->num_kv_heads, p->num_seqs);
       tq_attn_generic_kernel<<<grid, GEN_WARPS * 32, 0, st>>>(a);
@@ -821,8 +1047,7 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
   mg.rot = p->rotation;
   mg.out = p->out; mg.out_dtype = p->out_dtype; mg.out_ss = p->out_stride_seq; mg.out_sh = p->out_stride_head;
   mg.raw_out = p->raw_out;
-  akv_merge_kernel<<<rows, D < 128 ? D : 128, D * sizeof(float), st>>>(mg);
-  return check_launch("akv_merge_kernel");
+  return launch_merge(mg, rows, st);
 }
 
 AKV_EXPORT int akv_tq_paged_attn(const akv_tq_attn_params* p) {
@@ -917,7 +1142,8 @@ AKV_EXPORT int akv_tq_paged_attn_static(const akv_tq_attn_params* p) {
 AKV_EXPORT int akv_lse_merge(const float* parts, int num_parts, int num_seqs, int num_q_heads,
                              int head_dim, const float* rotation, void* out, int out_dtype,
                              int64_t out_stride_seq, int64_t out_stride_head, void* stream) {
-  if (num_parts <= 0 || num_seqs < 0 || num_q_heads <= 0 || head_dim <= 0 || head_dim > 1024)
+  if (num_parts <= 0 || num_seqs < 0 || num_q_heads <= 0 || head_dim <= 0 || head_dim > 1024 ||
+      (rotation != nullptr && head_dim % 16 != 0))
     return fail(AKV_ERR_ARG, "akv_lse_merge: bad sizes");
   if (num_seqs == 0) return AKV_OK;
   if (!parts || !out) return fail(AKV_ERR_ARG, "akv_lse_merge: null pointer");
@@ -931,7 +1157,5 @@ AKV_EXPORT int akv_lse_merge(const float* parts, int num_parts, int num_seqs, in
   mg.mode = rotation ? MERGE_ROTATE : MERGE_NORMALIZE;
   mg.rot = rotation;
   mg.out = out; mg.out_dtype = out_dtype; mg.out_ss = out_stride_seq; mg.out_sh = out_stride_head;
-  akv_merge_kernel<<<rows, head_dim < 128 ? head_dim : 128, head_dim * sizeof(float),
-                     (cudaStream_t)stream>>>(mg);
-  return check_launch("akv_merge_kernel");
+  return launch_merge(mg, rows, (cudaStream_t)stream);
 }

@@ -308,32 +308,43 @@ tq_decode_tiled_kernel(const uint8_t* __restrict__ packed, int64_t p_stride_row,
 __global__ void __launch_bounds__(128)
 tq_encode_generic_kernel(RowMap m, int64_t n_rows, int D, int bits, const float* __restrict__ rot_t,
                          const float* __restrict__ boundaries) {
+  // one CTA per vector: thread o produces outputs o, o+128, ...
   extern __shared__ __align__(16) float smem_f[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float* u = smem_f + warp * (D + D / 4 + 16);
-  uint8_t* codes = reinterpret_cast<uint8_t*>(u + D);
+  float* u = smem_f;                                        // [D]
+  uint8_t* codes = reinterpret_cast<uint8_t*>(u + D);       // [D]
+  __shared__ float s_nrm;
+  const int tid = threadIdx.x;
   const int nb = (1 << bits) - 1;
   const int pd = D * bits / 8;
-  for (int64_t n = (int64_t)blockIdx.x * 4 + warp; n < n_rows; n += (int64_t)gridDim.x * 4) {
+  for (int64_t n = blockIdx.x; n < n_rows; n += gridDim.x) {
     RowAddr a = map_row(m, n);
-    for (int i = lane; i < D; i += 32) u[i] = load_as_float(a.src_base, m.x_dtype, a.src_off + i);
-    __syncwarp();
-    float tot = sumsq_8lane(u, D, lane & 7, 0xffffffffu);
-    float nrm = __fsqrt_rn(tot);
-    float den = __fadd_rn(nrm, 1e-10f);
-    __syncwarp();
-    for (int i = lane; i < D; i += 32) u[i] = __fdiv_rn(u[i], den);
-    __syncwarp();
-    for (int o = lane; o < D; o += 32) {
-      float y = 0.f;
-      for (int j = 0; j < D; ++j) y = __fmaf_rn(u[j], rot_t[(int64_t)j * D + o], y);
+    for (int i = tid; i < D; i += 128) u[i] = load_as_float(a.src_base, m.x_dtype, a.src_off + i);
+    __syncthreads();
+    if (tid < 32) {
+      float tot = sumsq_8lane(u, D, tid & 7, 0xffffffffu);
+      if (tid == 0) s_nrm = __fsqrt_rn(tot);
+    }
+    __syncthreads();
+    const float nrm = s_nrm;
+    const float den = __fadd_rn(nrm, 1e-10f);
+    for (int i = tid; i < D; i += 128) u[i] = __fdiv_rn(u[i], den);
+    __syncthreads();
+    for (int o = tid; o < D; o += 128) {
+      float y = 0.f;      // one chain in the order j = 0..D-1 (bit-identical to the tiled kernel)
+      for (int j0 = 0; j0 < D; j0 += 8) {    // 8 loads in flight per round (D is a multiple of 8)
+        float r[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) r[k] = rot_t[(int64_t)(j0 + k) * D + o];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) y = __fmaf_rn(u[j0 + k], r[k], y);
+      }
       int c = 0;
       for (int k = 0; k < nb; ++k) c += (boundaries[k] < y) ? 1 : 0;
       codes[o] = (uint8_t)c;
     }
-    __syncwarp();
+    __syncthreads();
     if (a.dst != nullptr) {
-      for (int bi = lane; bi < pd; bi += 32) {
+      for (int bi = tid; bi < pd; bi += 128) {
         int val = 0;
         for (int bit = 0; bit < 8; ++bit) {
           int pos = bi * 8 + bit;
@@ -342,9 +353,9 @@ tq_encode_generic_kernel(RowMap m, int64_t n_rows, int D, int bits, const float*
         }
         a.dst[bi] = (uint8_t)val;
       }
-      if (lane == 0) *a.dst_norm = nrm;
+      if (tid == 0) *a.dst_norm = nrm;
     }
-    __syncwarp();
+    __syncthreads();
   }
 }
 
@@ -364,7 +375,13 @@ tq_decode_generic_kernel(const uint8_t* __restrict__ packed, int64_t p_stride_ro
     float nrm = norms[n];
     for (int j = lane; j < D; j += 32) {
       float x = 0.f;
-      for (int i = 0; i < D; ++i) x = __fmaf_rn(yh[i], rot[(int64_t)i * D + j], x);
+      for (int i0 = 0; i0 < D; i0 += 8) {
+        float r[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) r[k] = rot[(int64_t)(i0 + k) * D + j];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) x = __fmaf_rn(yh[i0 + k], r[k], x);
+      }
       store_from_float(out, out_dtype, n * D + j, __fmul_rn(x, nrm));
     }
     __syncwarp();
@@ -400,13 +417,13 @@ int launch_decode_tiled(const uint8_t* packed, int64_t ps, const float* norms, i
 static int encode_dispatch(const RowMap& m, int64_t n_rows, int D, int bits, const float* rot_t,
                            const float* bnd, cudaStream_t st) {
   if (n_rows == 0) return AKV_OK;
+  // small batches (a decode step) are not worth filling 64 KB of shared memory per CTA
 #define AKV_ENC(DD, BB) \
-  if (D == DD && bits == BB) return launch_encode_tiled<DD, BB>(m, n_rows, rot_t, bnd, st);
+  if (D == DD && bits == BB && n_rows >= 2048) return launch_encode_tiled<DD, BB>(m, n_rows, rot_t, bnd, st);
   AKV_ENC(128, 4) AKV_ENC(128, 3) AKV_ENC(128, 2) AKV_ENC(64, 4) AKV_ENC(64, 3) AKV_ENC(64, 2)
 #undef AKV_ENC
-  size_t smem = 4 * (size_t)(D + D / 4 + 16) * sizeof(float);
-  int64_t blocks = (n_rows + 3) / 4;
-  int grid = (int)(blocks < 8 * sm_count() ? blocks : 8 * sm_count());
+  size_t smem = (size_t)(D + D / 4 + 16) * sizeof(float);
+  int grid = (int)(n_rows < 16 * sm_count() ? n_rows : 16 * sm_count());
   tq_encode_generic_kernel<<<grid, 128, smem, st>>>(m, n_rows, D, bits, rot_t, bnd);
   return check_launch("tq_encode_generic_kernel");
 }
