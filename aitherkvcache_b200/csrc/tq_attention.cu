@@ -718,6 +718,7 @@ __global__ void __launch_bounds__(512, 1)
 tq4_attn_pipe_kernel(AttnArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int s_pb[PIPE_MAX_BLOCKS];
+  __shared__ float s_cent[16];
   unsigned char* lut = smem;
   unsigned char* ring = smem + LUT_BYTES;
   const int split = blockIdx.x, hg = blockIdx.y, seq = blockIdx.z;
@@ -731,11 +732,7 @@ tq4_attn_pipe_kernel(AttnArgs a) {
   const int n_ss = (nb + 1) / 2;
 
   for (int i = tid; i < nb; i += 512) s_pb[i] = (int)phys_block(a, seq, (int)(blk_begin + i));
-  for (int i = tid; i < 256 * 32; i += 512) {
-    const int e = i >> 5, l = i & 31;
-    *reinterpret_cast<uint32_t*>(lut + e * LUT_STRIDE + l * 4) =
-        pack_half2(a.centroids[e >> 4], a.centroids[e & 15]);
-  }
+  if (tid < 16) s_cent[tid] = a.centroids[tid];
   __syncthreads();
 
   // producer role of this thread: one 16-byte chunk of K and of V per block
@@ -769,6 +766,17 @@ tq4_attn_pipe_kernel(AttnArgs a) {
     asm volatile("cp.async.commit_group;\n" ::);
   };
 
+  // start the copies first; the table fill and the query loads below overlap their latency
+#pragma unroll
+  for (int ss = 0; ss < PIPE_STAGES - 1; ++ss) {
+    if (ss < n_ss) issue(ss);
+    else asm volatile("cp.async.commit_group;\n" ::);
+  }
+  for (int i = tid; i < 256 * 32; i += 512) {
+    const int e = i >> 5, l = i & 31;
+    *reinterpret_cast<uint32_t*>(lut + e * LUT_STRIDE + l * 4) = pack_half2(s_cent[e >> 4], s_cent[e & 15]);
+  }
+
   const int hl = warp & 7, wj = warp >> 3;
   const int h = hg * 8 + hl;
   const int G = a.num_q_heads / a.num_kv_heads;
@@ -776,12 +784,14 @@ tq4_attn_pipe_kernel(AttnArgs a) {
   uint32_t bq[8][2];
   {
     const float* qp = a.qrot + ((int64_t)seq * a.num_q_heads + h * G + (g < G ? g : 0)) * 128 + 32 * t;
+    float4 f[8];
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) f[kk] = *reinterpret_cast<const float4*>(qp + 4 * kk);
 #pragma unroll
     for (int kk = 0; kk < 8; ++kk) {
-      float4 f = *reinterpret_cast<const float4*>(qp + 4 * kk);
-      if (g >= G) f = make_float4(0.f, 0.f, 0.f, 0.f);
-      bq[kk][0] = pack_half2(f.x, f.y);
-      bq[kk][1] = pack_half2(f.z, f.w);
+      if (g >= G) f[kk] = make_float4(0.f, 0.f, 0.f, 0.f);
+      bq[kk][0] = pack_half2(f[kk].x, f[kk].y);
+      bq[kk][1] = pack_half2(f[kk].z, f[kk].w);
     }
   }
   // consumer offsets inside a stage
@@ -800,11 +810,6 @@ tq4_attn_pipe_kernel(AttnArgs a) {
   for (int j = 0; j < 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
   SoftmaxState st{-CUDART_INF_F, -CUDART_INF_F, 0.f, 0.f};
 
-#pragma unroll
-  for (int ss = 0; ss < PIPE_STAGES - 1; ++ss) {
-    if (ss < n_ss) issue(ss);
-    else asm volatile("cp.async.commit_group;\n" ::);
-  }
   for (int it = 0; it < n_ss; ++it) {
     asm volatile("cp.async.wait_group %0;\n" :: "n"(PIPE_STAGES - 2) : "memory");
     __syncthreads();                 // stage `it` has landed; stage it-1 is free again
@@ -843,7 +848,34 @@ tq4_attn_pipe_kernel(AttnArgs a) {
     l0 += __shfl_xor_sync(0xffffffffu, l0, offs);
     l1 += __shfl_xor_sync(0xffffffffu, l1, offs);
   }
-  const int part = split * 2 + wj;
+  // the two warps of a head combine their partials through shared memory (the ring is free now)
+  __syncthreads();
+  float* xch = reinterpret_cast<float*>(ring) + (hl * 32 + lane) * 37;   // 36 floats + 1 pad
+  if (wj == 1) {
+    xch[0] = st.m0; xch[1] = st.m1; xch[2] = l0; xch[3] = l1;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { xch[4 + 4 * j] = o[j][0]; xch[5 + 4 * j] = o[j][1]; xch[6 + 4 * j] = o[j][2]; xch[7 + 4 * j] = o[j][3]; }
+  }
+  __syncthreads();
+  if (wj == 1) return;
+  {
+    const float om0 = xch[0], om1 = xch[1];
+    const float mn0 = fmaxf(st.m0, om0), mn1 = fmaxf(st.m1, om1);
+    // a side that saw no token has m = -inf and l = 0: its weight is 0
+    const float a0 = (st.m0 == mn0) ? 1.f : ex2_approx(st.m0 - mn0), b0 = (om0 == mn0) ? 1.f : ex2_approx(om0 - mn0);
+    const float a1 = (st.m1 == mn1) ? 1.f : ex2_approx(st.m1 - mn1), b1 = (om1 == mn1) ? 1.f : ex2_approx(om1 - mn1);
+    l0 = l0 * a0 + xch[2] * b0;
+    l1 = l1 * a1 + xch[3] * b1;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      o[j][0] = o[j][0] * a0 + xch[4 + 4 * j] * b0;
+      o[j][1] = o[j][1] * a1 + xch[5 + 4 * j] * b1;
+      o[j][2] = o[j][2] * a0 + xch[6 + 4 * j] * b0;
+      o[j][3] = o[j][3] * a1 + xch[7 + 4 * j] * b1;
+    }
+    st.m0 = mn0; st.m1 = mn1;
+  }
+  const int part = split;
 #pragma unroll
   for (int e = 0; e < 2; ++e) {
     const int qg = 2 * t + e;
@@ -884,8 +916,7 @@ static Plan make_plan(int num_seqs, int num_q_heads, int num_kv_heads, int head_
     p.warps_per_head = GEN_WARPS;
   }
   p.num_parts = p.num_splits * p.warps_per_head;
-  // the pipelined 4-bit kernel writes two partials per split; size the buffers for either kernel
-  const size_t parts_alloc = (size_t)p.num_splits * (p.warps_per_head > 2 ? p.warps_per_head : 2);
+  const size_t parts_alloc = (size_t)p.num_parts;
   size_t rows = (size_t)num_seqs * num_q_heads;
   p.off_qrot = 0;
   p.off_acc = align256(rows * head_dim * sizeof(float));
@@ -1004,10 +1035,6 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
                         reinterpret_cast<uintptr_t>(p->v_norms) % 16 == 0 &&
                         plan.blocks_per_split <= PIPE_MAX_BLOCKS;
       if (pipe) {
-        a.warps_per_head = 2;
-        a.num_parts = plan.num_splits * 2;
-        plan.warps_per_head = 2;
-        plan.num_parts = a.num_parts;
         cudaError_t e = cudaFuncSetAttribute(tq4_attn_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PIPE_SMEM);
         if (e != cudaSuccess) return fail((int)e, "attention: smem attribute: %s", cudaGetErrorString(e));
         dim3 grid(plan.num_splits, p->num_kv_heads / 8, p->num_seqs);
