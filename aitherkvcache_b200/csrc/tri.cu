@@ -168,7 +168,9 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 template <int F>
 struct TriSmem {
   static constexpr int WORDS = F / 4;                       // words per record
-  static constexpr int ARR = 8 * 32 * WORDS;                // words per staged array (8 heads)
+  static constexpr int HEAD = 32 * WORDS + WORDS;            // words per head, padded so that the async
+                                                            // copies of one token row hit distinct banks
+  static constexpr int ARR = 8 * HEAD;                      // words per staged array (8 heads)
   static constexpr int STAGE_WORDS = 4 * ARR + 2 * 128;     // + scales: 2 x 32 x 8 halves = 2 x 128 words
   static constexpr size_t bytes(int nh) { return (size_t)nh * TD_TILE_HALVES * 2 + 2 * STAGE_WORDS * 4; }
 };
@@ -185,7 +187,7 @@ __device__ __forceinline__ void tri_stage_load(const TriArgs& a, uint32_t* stage
     if (s0 + tok >= s_end) continue;
     const int head = j / SM::WORDS, wj = j - head * SM::WORDS;
     const int64_t g_off = (((int64_t)b * a.S + s0 + tok) * a.KVH + hg0) * F + 4 * j;
-    const int s_off = (head * 32 + tok) * SM::WORDS + wj;
+    const int s_off = head * SM::HEAD + tok * SM::WORDS + wj;
 #pragma unroll
     for (int arr = 0; arr < 4; ++arr) cp_async4(stage + arr * SM::ARR + s_off, srcs[arr] + g_off);
   }
@@ -279,7 +281,7 @@ tri_decode_kernel(TriArgs a) {
     uint32_t kiw[SM::WORDS], kpw[SM::WORDS], viw[SM::WORDS], vpw[SM::WORDS];
     float ks = 0.f, vs = 0.f, delta = 0.f;
     if (valid) {
-      const int r = (warp * 32 + lane) * SM::WORDS;
+      const int r = warp * SM::HEAD + lane * SM::WORDS;
 #pragma unroll
       for (int w = 0; w < SM::WORDS; ++w) {
         kiw[w] = st[r + w];
