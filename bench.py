@@ -43,6 +43,9 @@ WORKLOAD = ("paged decode attention, tq-t4nc cache: 16 seqs, ctx U[4096,32768] s
             "head_dim 128, block_size 16, permuted block tables")
 
 
+NCU_TRAFFIC_BYTES = 276_980_480 + 8_485_120     # read + write per launch (ncu, rank-0 workload)
+
+
 def context_lengths(rank=0):
     g = torch.Generator().manual_seed(1 + 1000 * rank)
     return torch.randint(4096, 32769, (NUM_SEQS,), generator=g)
@@ -561,8 +564,11 @@ def main():
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps,
                     "api": "torch.ops.tq.decode_step (encode new token + attention), host pinned buffers"},
             "gpu_launches": 3 * args.steps,
+            # traffic: dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this
+            # workload, from the ncu capture summarised in profiles/tq4_attn_pipe_kernel_config1.md
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None, "kernel": "tq_attn_mma_kernel",
+                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES if world == 1 else None,
+                         "algorithmic_bytes": kv_bytes, "kernel": "tq4_attn_pipe_kernel",
                          "kernel_ms": kernel_ms, "peak_source": peak_src,
                          "frac_of_8TBs_nominal": achieved / 8000.0},
             "clocks": clocks,
