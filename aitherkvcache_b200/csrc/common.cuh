@@ -100,6 +100,7 @@ struct MergeArgs {
   const float* rot;              // R row-major (MERGE_ROTATE only)
   void* out; int out_dtype; int64_t out_ss, out_sh;
   float* raw_out;
+  const int* part_counts;       // optional [num_seqs]: number of valid parts of each sequence
 };
 
 int launch_merge(const MergeArgs& a, int rows, cudaStream_t st);

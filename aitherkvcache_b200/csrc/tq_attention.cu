@@ -21,10 +21,16 @@
 #include <math_constants.h>
 #include <stdlib.h>
 
-// 1: one norm load per lane, broadcast by shuffles; 0: four norm loads per thread.
-// Measured equal on B200; the shuffle form spills less.
+// 1: one norm load per lane, broadcast by shuffles; 0: four norm loads per thread (slightly faster
+// in the shared-memory-staged kernels).
+#ifndef AKV_MMA_SEP
+#define AKV_MMA_SEP 0
+#endif
+#ifndef AKV_LDS_NOVOL
+#define AKV_LDS_NOVOL 0
+#endif
 #ifndef AKV_NORM_SHFL
-#define AKV_NORM_SHFL 1
+#define AKV_NORM_SHFL 0
 #endif
 
 namespace akv {
@@ -46,6 +52,9 @@ struct AttnArgs {
   const float* centroids;
   float* part_acc;               // [S][QH][NP][D]
   float* part_ml;                // [S][QH][NP][2]
+  // stream-K plan (persistent kernel): [0..S] prefix of per-sequence stage counts, [S+1] stages per
+  // CTA, then first CTA [S], part count [S], block count [S]
+  int* sk;
 };
 
 __device__ __forceinline__ int64_t phys_block(const AttnArgs& a, int seq, int blk) {
@@ -58,10 +67,55 @@ __device__ __forceinline__ int64_t phys_block(const AttnArgs& a, int seq, int bl
 // ---------------------------------------------------------------------------
 // q_rot[s][qh][i] = premul * sum_j R[i][j] q[s][qh][j]   (rot_t[j*D+i] = R[i][j])
 // ---------------------------------------------------------------------------
+// Stream-K plan: sequence s contributes ceil(blocks_s / 2) two-block stages; the stages of all
+// sequences, laid end to end, are cut into `grid` equal ranges, one per persistent CTA.
+struct StreamKPlanArgs {
+  const void* context_lens; int cl_dtype; int num_seqs; int block_size; int grid;
+  int* sk;    // nullptr: no plan wanted
+};
+
+__device__ void streamk_plan(const StreamKPlanArgs& p) {
+  __shared__ int s_part[128];
+  __shared__ int s_total;
+  const int S = p.num_seqs, tid = threadIdx.x, nthr = blockDim.x;
+  const int per = (S + nthr - 1) / nthr;
+  const int s0 = tid * per, s1 = (s0 + per < S) ? s0 + per : S;
+  int local = 0;
+  for (int s = s0; s < s1; ++s) {
+    const int64_t ctx = load_index(p.context_lens, p.cl_dtype, s);
+    const int nb = (int)((ctx + p.block_size - 1) / p.block_size);
+    p.sk[3 * S + 2 + s] = nb;
+    local += (nb + 1) / 2;
+  }
+  s_part[tid] = local;
+  __syncthreads();
+  if (tid == 0) {
+    int run = 0;
+    for (int i = 0; i < nthr; ++i) { const int v = s_part[i]; s_part[i] = run; run += v; }
+    s_total = run;
+  }
+  __syncthreads();
+  const int T = s_total;
+  const int chunk = T > 0 ? (T + p.grid - 1) / p.grid : 1;
+  int run = s_part[tid];
+  for (int s = s0; s < s1; ++s) {
+    const int cnt = (p.sk[3 * S + 2 + s] + 1) / 2;
+    p.sk[s] = run;
+    p.sk[S + 2 + s] = cnt > 0 ? run / chunk : 0;
+    p.sk[2 * S + 2 + s] = cnt > 0 ? 2 * ((run + cnt - 1) / chunk - run / chunk + 1) : 0;
+    run += cnt;
+  }
+  if (tid == 0) { p.sk[S] = T; p.sk[S + 1] = chunk; }
+}
+
 __global__ void akv_qrot_kernel(const void* __restrict__ q, int q_dtype, int64_t q_ss, int64_t q_sh,
                                 int num_q_heads, int D, const float* __restrict__ rot_t,
-                                float premul, float* __restrict__ qrot) {
+                                float premul, float* __restrict__ qrot, int rows, StreamKPlanArgs plan) {
   extern __shared__ float qs[];
+  if ((int)blockIdx.x == rows) {   // the extra block computes the stream-K plan
+    streamk_plan(plan);
+    return;
+  }
   int s = blockIdx.x / num_q_heads, qh = blockIdx.x % num_q_heads;
   for (int j = threadIdx.x; j < D; j += blockDim.x)
     qs[j] = load_as_float(q, q_dtype, s * q_ss + qh * q_sh + j);
@@ -94,7 +148,9 @@ __global__ void akv_merge_kernel(MergeArgs a) {
   const int row = blockIdx.x;
   const int seq = row / a.num_q_heads, qh = row % a.num_q_heads;
   int np = a.np;
-  if (a.context_lens != nullptr) {
+  if (a.part_counts != nullptr) {
+    np = a.part_counts[seq] < np ? a.part_counts[seq] : np;
+  } else if (a.context_lens != nullptr) {
     int64_t ctx = load_index(a.context_lens, a.cl_dtype, seq);
     int64_t splits = (ctx + a.tokens_per_split - 1) / a.tokens_per_split;
     int64_t v = splits * a.warps_per_head;
@@ -268,6 +324,14 @@ constexpr int LUT_BYTES = 256 * LUT_STRIDE;     // 64 KB: entry e, lane l at e*2
 
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1) {
+#if AKV_MMA_SEP
+  float e0, e1, e2, e3;
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};\n"
+      : "=f"(e0), "=f"(e1), "=f"(e2), "=f"(e3)
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(d[0]), "f"(d[1]), "f"(d[2]), "f"(d[3]));
+  d[0] = e0; d[1] = e1; d[2] = e2; d[3] = e3;
+  return;
+#endif
   asm volatile(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
       "{%0,%1,%2,%3};\n"
@@ -288,10 +352,33 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
 
 // Table lookup: byte `k` of `w` selects the entry; the result is
 // half2(c[byte >> 4], c[byte & 15]).  lanebase = lane * 4.
+// All table reads go through explicit 32-bit shared-space addresses: `lut` is the table's address
+// in the shared window (not a generic pointer), so a lookup is one PRMT, one add and one LDS.
+using lut_t = uint32_t;
+
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+#if AKV_LDS_NOVOL
+  asm("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+#else
+  asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+#endif
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
 template <int K>
-__device__ __forceinline__ uint32_t lut4(const unsigned char* lut, uint32_t w, uint32_t lanebase) {
-  uint32_t addr = __byte_perm(w, lanebase, 0x7604 + (K << 4));
-  return *reinterpret_cast<const uint32_t*>(lut + addr);
+__device__ __forceinline__ uint32_t lut4(lut_t lut, uint32_t w, uint32_t lanebase) {
+  return lds32(lut + __byte_perm(w, lanebase, 0x7604 + (K << 4)));
 }
 
 template <bool VEC16>
@@ -393,26 +480,24 @@ constexpr int LUT3_STRIDE = 128;
 
 // Pair P of an MSB-first 3-bit stream held as big-endian words B[0], B[1], ...
 template <int P>
-__device__ __forceinline__ uint32_t lut3(const unsigned char* lut, const uint32_t* B, uint32_t lanebase) {
+__device__ __forceinline__ uint32_t lut3(lut_t lut, const uint32_t* B, uint32_t lanebase) {
   constexpr int o = 6 * P, w = o >> 5, pos = o & 31;
   uint32_t x;
   if constexpr (pos <= 26) x = B[w] >> (26 - pos);
   else x = __funnelshift_r(B[w + 1], B[w], 58 - pos);
-  const uint32_t addr = ((x & 63u) << 7) | lanebase;
-  return *reinterpret_cast<const uint32_t*>(lut + addr);
+  return lds32(lut + (((x & 63u) << 7) | lanebase));
 }
 
 template <int K>
-__device__ __forceinline__ uint2 lut2(const unsigned char* lut, uint32_t w, uint32_t lanebase8) {
-  const uint32_t addr = __byte_perm(w, lanebase8, 0x7604 + (K << 4));
-  return *reinterpret_cast<const uint2*>(lut + addr);
+__device__ __forceinline__ uint2 lut2(lut_t lut, uint32_t w, uint32_t lanebase8) {
+  return lds64(lut + __byte_perm(w, lanebase8, 0x7604 + (K << 4)));
 }
 
 __device__ __forceinline__ uint32_t bswap32(uint32_t w) { return __byte_perm(w, 0, 0x0123); }
 
 // Natural-order fragments of one token's K bytes: n[p] = half2(dim 32t+2p, dim 32t+2p+1), p = 0..15.
 template <int BITS>
-__device__ __forceinline__ void k_natural(const unsigned char* lut, const uint32_t (&w)[BITS], uint32_t lanebase,
+__device__ __forceinline__ void k_natural(lut_t lut, const uint32_t (&w)[BITS], uint32_t lanebase,
                                           uint32_t (&n)[16]) {
   if constexpr (BITS == 3) {
     const uint32_t B[3] = {bswap32(w[0]), bswap32(w[1]), bswap32(w[2])};
@@ -438,7 +523,7 @@ __device__ __forceinline__ void k_natural(const unsigned char* lut, const uint32
 
 // Natural-order fragments of one token's V bytes: n[j] = half2(dim 16g+2j, dim 16g+2j+1), j = 0..7.
 template <int BITS>
-__device__ __forceinline__ void v_natural(const unsigned char* lut, const uint32_t (&w)[2], uint32_t lanebase,
+__device__ __forceinline__ void v_natural(lut_t lut, const uint32_t (&w)[2], uint32_t lanebase,
                                           uint32_t (&n)[8]) {
   if constexpr (BITS == 3) {
     // bytes b0..b5 of the stream: w[0] = b0 | b1<<8 | b2<<16 | b3<<24, w[1] = b4 | b5<<8
@@ -459,7 +544,7 @@ __device__ __forceinline__ void v_natural(const unsigned char* lut, const uint32
 // One 16-token tile: scores, online softmax, value accumulation.
 // `n_valid` (1..16) masks the tail of the last tile of a sequence.
 template <int BITS>
-__device__ __forceinline__ void process_tile(const unsigned char* lut, uint32_t lanebase, int g,
+__device__ __forceinline__ void process_tile(lut_t lut, uint32_t lanebase, int g,
                                              const uint32_t (&bq)[8][2], const TileData<BITS>& cur,
                                              int n_valid, float (&o)[8][4], SoftmaxState& st) {
   // ---- scores: S^T[16 tokens][8 q heads], two independent accumulation chains ----
@@ -602,6 +687,7 @@ tq_attn_mma_kernel(AttnArgs a) {
   if (h >= a.num_kv_heads) return;
   const int G = a.num_q_heads / a.num_kv_heads;
   const uint32_t lanebase = lane * 4;
+  const lut_t lut_s = (lut_t)__cvta_generic_to_shared(lut);
 
   // query fragments (B operand of the score product): thread (g,t) holds
   // q_rot[qh = g][32t .. 32t+31]; k-tile kk uses dims 32t+4kk .. 32t+4kk+3.
@@ -655,7 +741,7 @@ tq_attn_mma_kernel(AttnArgs a) {
       }
       {
         const int64_t rem = ctx - tile * 16;
-        process_tile<BITS>(lut, lanebase, g, bq, buf0, rem < 16 ? (int)rem : 16, o, st);
+        process_tile<BITS>(lut_s, lanebase, g, bq, buf0, rem < 16 ? (int)rem : 16, o, st);
       }
       if (i + 1 < cnt) {
         if (i + 2 < cnt) {
@@ -663,7 +749,7 @@ tq_attn_mma_kernel(AttnArgs a) {
           load_tile<BITS, VEC16>(a, off, pb, (int)((tile + 2 * wph) % tpb) * 16, lane, buf0);
         }
         const int64_t rem = ctx - (tile + wph) * 16;
-        process_tile<BITS>(lut, lanebase, g, bq, buf1, rem < 16 ? (int)rem : 16, o, st);
+        process_tile<BITS>(lut_s, lanebase, g, bq, buf1, rem < 16 ? (int)rem : 16, o, st);
       }
     }
   }
@@ -721,6 +807,7 @@ tq4_attn_pipe_kernel(AttnArgs a) {
   __shared__ float s_cent[16];
   unsigned char* lut = smem;
   unsigned char* ring = smem + LUT_BYTES;
+  const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
   const int split = blockIdx.x, hg = blockIdx.y, seq = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -781,6 +868,7 @@ tq4_attn_pipe_kernel(AttnArgs a) {
   const int h = hg * 8 + hl;
   const int G = a.num_q_heads / a.num_kv_heads;
   const uint32_t lanebase = lane * 4;
+  const lut_t lut_s = (lut_t)__cvta_generic_to_shared(lut);
   uint32_t bq[8][2];
   {
     const float* qp = a.qrot + ((int64_t)seq * a.num_q_heads + h * G + (g < G ? g : 0)) * 128 + 32 * t;
@@ -817,27 +905,27 @@ tq4_attn_pipe_kernel(AttnArgs a) {
     else asm volatile("cp.async.commit_group;\n" ::);
     const int bi = 2 * it + wj;
     if (bi < nb) {
-      const unsigned char* sb = ring + (it % PIPE_STAGES) * PIPE_STAGE_BYTES;
+      const uint32_t sb = ring_s + (it % PIPE_STAGES) * PIPE_STAGE_BYTES;
       TileData<4> cur;
-      const uint4 ka = *reinterpret_cast<const uint4*>(sb + kA_off);
-      const uint4 kb = *reinterpret_cast<const uint4*>(sb + kA_off + 4096);
+      const uint4 ka = lds128(sb + kA_off);
+      const uint4 kb = lds128(sb + kA_off + 4096);
       cur.kA[0] = ka.x; cur.kA[1] = ka.y; cur.kA[2] = ka.z; cur.kA[3] = ka.w;
       cur.kB[0] = kb.x; cur.kB[1] = kb.y; cur.kB[2] = kb.z; cur.kB[3] = kb.w;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const uint2 v = *reinterpret_cast<const uint2*>(sb + v_off[i]);
+        const uint2 v = lds64(sb + v_off[i]);
         cur.v[i][0] = v.x; cur.v[i][1] = v.y;
       }
 #if AKV_NORM_SHFL
-      cur.nrm = *reinterpret_cast<const float*>(sb + n_off);
+      cur.nrm = __uint_as_float(lds32(sb + n_off));
 #else
-      cur.nkA = *reinterpret_cast<const float*>(sb + 32768 + wj * 512 + (g * 8 + hl) * 4);
-      cur.nkB = *reinterpret_cast<const float*>(sb + 32768 + wj * 512 + ((g + 8) * 8 + hl) * 4);
-      cur.nvA = *reinterpret_cast<const float*>(sb + 33792 + wj * 512 + (g * 8 + hl) * 4);
-      cur.nvB = *reinterpret_cast<const float*>(sb + 33792 + wj * 512 + ((g + 8) * 8 + hl) * 4);
+      cur.nkA = __uint_as_float(lds32(sb + 32768 + wj * 512 + (g * 8 + hl) * 4));
+      cur.nkB = __uint_as_float(lds32(sb + 32768 + wj * 512 + ((g + 8) * 8 + hl) * 4));
+      cur.nvA = __uint_as_float(lds32(sb + 33792 + wj * 512 + (g * 8 + hl) * 4));
+      cur.nvB = __uint_as_float(lds32(sb + 33792 + wj * 512 + ((g + 8) * 8 + hl) * 4));
 #endif
       const int64_t rem = ctx - (blk_begin + bi) * 16;
-      process_tile<4>(lut, lanebase, g, bq, cur, rem < 16 ? (int)rem : 16, o, st);
+      process_tile<4>(lut_s, lanebase, g, bq, cur, rem < 16 ? (int)rem : 16, o, st);
     }
   }
   asm volatile("cp.async.wait_group 0;\n" ::: "memory");
@@ -892,16 +980,258 @@ tq4_attn_pipe_kernel(AttnArgs a) {
   }
 }
 
+// ---------------------------------------------------------------------------
+// Persistent ("stream-K") form of the pipelined kernel.  The two-block stages of all sequences
+// are laid end to end and cut into gridDim.x equal ranges (plan in a.sk); every CTA streams its
+// range through the copy ring without draining between sequences, so all CTAs finish together
+// and a sequence produces only as many partials as CTAs touch it.  Partial slot of (sequence, CTA
+// b, warp j): 2 * (b - first_cta[sequence]) + j.
+// ---------------------------------------------------------------------------
+constexpr int SK_MAX_SEQS = 1024;
+// Shared-memory map in ABSOLUTE shared-window addresses.  The lookup table sits at exactly 64 KB so
+// that its address bits 8..15 are free: the PRMT that inserts the code byte then yields the complete
+// address and a lookup is two instructions (PRMT, LDS).
+//   [dyn start, 64 KB)   plan arrays (8.2 KB) + ring stage 0
+//   [64 KB, 128 KB)      lookup table
+//   [128 KB, ...)        ring stages 1, 2
+constexpr int SK_STAGES = 3;
+constexpr uint32_t SK_LUT = 65536;
+constexpr uint32_t SK_END = 131072 + (SK_STAGES - 1) * PIPE_STAGE_BYTES;   // 200704
+constexpr uint32_t SK_LOW_BYTES = (SK_MAX_SEQS + 2) * 4 + SK_MAX_SEQS * 4 + PIPE_STAGE_BYTES;   // below 64 KB
+constexpr int SK_DYN_SMEM = SK_END;        // requested dynamic bytes: covers [start, SK_END) for any start >= 0
+
+__device__ __forceinline__ void cp_async16_s(uint32_t smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" :: "r"(smem_dst), "l"(gsrc));
+}
+
+__global__ void __launch_bounds__(512, 1)
+tq4_attn_streamk_kernel(AttnArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ float s_cent[16];
+  const uint32_t dyn0 = (uint32_t)__cvta_generic_to_shared(smem);
+  // generic pointers into the low region (all shared addresses below are absolute)
+  int* s_P = reinterpret_cast<int*>(smem + (SK_LUT - SK_LOW_BYTES - dyn0));   // stage prefix, total, chunk
+  int* s_nb = s_P + (SK_MAX_SEQS + 2);                                        // blocks per sequence
+  const uint32_t stage0_s = SK_LUT - PIPE_STAGE_BYTES;
+  auto stage_addr = [&](int slot) -> uint32_t { return slot == 0 ? stage0_s : 131072u + (uint32_t)(slot - 1) * PIPE_STAGE_BYTES; };
+  const int b = blockIdx.x, hg = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int S = a.num_seqs;
+  for (int i = tid; i < S + 2; i += 512) s_P[i] = a.sk[i];
+  for (int i = tid; i < S; i += 512) s_nb[i] = a.sk[3 * S + 2 + i];
+  if (tid < 16) s_cent[tid] = a.centroids[tid];
+  __syncthreads();
+  const int T = s_P[S], chunk = s_P[S + 1];
+  const int u_begin = b * chunk;
+  const int u_end = (u_begin + chunk < T) ? u_begin + chunk : T;
+  if (u_begin >= u_end) return;            // uniform for the CTA
+  const int n_it = u_end - u_begin;
+
+  // sequence that owns stage u: the one with P[s] <= u < P[s+1] (empty sequences are skipped)
+  auto locate = [&](int u, int hint) {
+    while (u >= s_P[hint + 1]) ++hint;
+    return hint;
+  };
+  int seq0;
+  {
+    int lo = 0, hi = S - 1;                // binary search for the first stage
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (s_P[mid] <= u_begin) lo = mid; else hi = mid - 1;
+    }
+    seq0 = locate(u_begin, lo);
+  }
+
+  // ---- producer ----
+  const int c_tok = tid >> 5, c_r = tid & 31;
+  const int k_dst = c_tok * 512 + (((c_r >> 2) ^ (c_tok & 1)) << 6) + (c_r & 3) * 16;
+  const int v_dst = c_tok * 512 + (((c_r >> 1) ^ ((c_tok >> 1) & 3)) << 5) + (c_r & 1) * 16;
+  const int64_t k_src = (int64_t)c_tok * a.kp_sp + hg * 512 + c_r * 16;
+  const int64_t v_src = (int64_t)c_tok * a.vp_sp + hg * 512 + c_r * 16;
+  // 32-bit strides (checked on the host) keep the address arithmetic to one wide multiply-add
+  const int kp_sb = (int)a.kp_sb, vp_sb = (int)a.vp_sb, kn_sb = (int)a.kn_sb, vn_sb = (int)a.vn_sb;
+  const bool bt64 = a.bt_dtype == AKV_I64;
+  int up = u_begin;                        // next stage to issue
+  int p_seq = seq0 - 1, p_base = 0, p_end = u_begin, p_nb = 0;   // its sequence: stages [p_base, p_end), p_nb blocks
+  const char* bt_row = nullptr;
+  int pb0 = 0, pb1 = 0;                    // physical blocks of stage `up` (raw table entries until issue())
+  bool has1 = false;
+  // Block ids of stage `up` (all threads read the same entries).  Only the loads are issued here;
+  // the values are first touched (clamped) by the next issue(), one iteration later, so no warp
+  // waits on them.
+  auto load_pb = [&]() {
+    if (up >= p_end) {                     // next sequence (rare)
+      p_seq = locate(up, p_seq < 0 ? 0 : p_seq);
+      p_base = s_P[p_seq]; p_end = s_P[p_seq + 1]; p_nb = s_nb[p_seq];
+      bt_row = reinterpret_cast<const char*>(a.block_tables) + (int64_t)p_seq * a.bt_stride * (bt64 ? 8 : 4);
+    }
+    const int bi = 2 * (up - p_base);
+    has1 = bi + 1 < p_nb;
+    const int bj = bi + (has1 ? 1 : 0);
+    if (bt64) {
+      pb0 = (int)reinterpret_cast<const int64_t*>(bt_row)[bi];
+      pb1 = (int)reinterpret_cast<const int64_t*>(bt_row)[bj];
+    } else {
+      pb0 = reinterpret_cast<const int*>(bt_row)[bi];
+      pb1 = reinterpret_cast<const int*>(bt_row)[bj];
+    }
+  };
+  const int nblocks = (int)a.num_blocks;
+  auto issue = [&](int slot) {
+    pb0 = min(max(pb0, 0), nblocks - 1);
+    pb1 = min(max(pb1, 0), nblocks - 1);
+    const uint32_t st = stage_addr(slot);
+    cp_async16_s(st + k_dst, a.k_packed + ((int64_t)pb0 * kp_sb + k_src));
+    cp_async16_s(st + 16384 + v_dst, a.v_packed + ((int64_t)pb0 * vp_sb + v_src));
+    if (has1) {
+      cp_async16_s(st + 8192 + k_dst, a.k_packed + ((int64_t)pb1 * kp_sb + k_src));
+      cp_async16_s(st + 16384 + 8192 + v_dst, a.v_packed + ((int64_t)pb1 * vp_sb + v_src));
+    }
+    if (tid < 128) {
+      const int which = tid >> 5, ch = tid & 31, b2 = which & 1;
+      if (b2 == 0 || has1) {
+        const int pb = b2 ? pb1 : pb0;
+        const int tok = ch >> 1, half = ch & 1;
+        const float* src = (which < 2)
+            ? a.k_norms + ((int64_t)pb * kn_sb + (int64_t)tok * a.kn_sp + hg * 8 + half * 4)
+            : a.v_norms + ((int64_t)pb * vn_sb + (int64_t)tok * a.vn_sp + hg * 8 + half * 4);
+        cp_async16_s(st + 32768 + which * 512 + ch * 16, src);
+      }
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
+    ++up;
+    if (up < u_end) load_pb();             // for the next issue, one iteration from now
+  };
+  load_pb();
+#pragma unroll
+  for (int ss = 0; ss < SK_STAGES - 1; ++ss) {
+    if (ss < n_it) issue(ss);
+    else asm volatile("cp.async.commit_group;\n" ::);
+  }
+  for (int i = tid; i < 256 * 32; i += 512) {
+    const int e = i >> 5, l = i & 31;
+    const uint32_t v = pack_half2(s_cent[e >> 4], s_cent[e & 15]);
+    asm volatile("st.shared.u32 [%0], %1;\n" :: "r"(SK_LUT + e * LUT_STRIDE + l * 4), "r"(v));
+  }
+
+  // ---- consumer ----
+  const int hl = warp & 7, wj = warp >> 3;
+  const int h = hg * 8 + hl;
+  const int G = a.num_q_heads / a.num_kv_heads;
+  const uint32_t lanebase = SK_LUT | (lane * 4);   // upper address bytes ride along in the PRMT
+  constexpr lut_t lut_s = 0;
+  const int kA_off = wj * 8192 + g * 512 + ((hl ^ (g & 1)) << 6) + 16 * t;
+  int v_off[4];
+  {
+    const int toks[4] = {2 * t, 2 * t + 1, 2 * t + 8, 2 * t + 9};
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      v_off[i] = 16384 + wj * 8192 + toks[i] * 512 + (((2 * hl + (g >> 2)) ^ ((toks[i] >> 1) & 3)) << 5) + (g & 3) * 8;
+  }
+  const int n_off = 32768 + (lane < 16 ? wj * 512 + (lane * 8 + hl) * 4 : 1024 + wj * 512 + ((lane - 16) * 8 + hl) * 4);
+
+  uint32_t bq[8][2];
+  float o[8][4];
+  SoftmaxState st{-CUDART_INF_F, -CUDART_INF_F, 0.f, 0.f};
+  int seq_c = -1, c_base = 0, c_end = 0, c_nb = 0, ctx_c = 0;
+  auto begin_seq = [&](int seq) {          // query fragments and fresh accumulators
+    seq_c = seq;
+    c_base = s_P[seq]; c_end = s_P[seq + 1]; c_nb = s_nb[seq];
+    ctx_c = (int)load_index(a.context_lens, a.cl_dtype, seq);
+    const float* qp = a.qrot + ((int64_t)seq * a.num_q_heads + h * G + (g < G ? g : 0)) * 128 + 32 * t;
+    float4 f[8];
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) f[kk] = *reinterpret_cast<const float4*>(qp + 4 * kk);
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      if (g >= G) f[kk] = make_float4(0.f, 0.f, 0.f, 0.f);
+      bq[kk][0] = pack_half2(f[kk].x, f[kk].y);
+      bq[kk][1] = pack_half2(f[kk].z, f[kk].w);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+    st = SoftmaxState{-CUDART_INF_F, -CUDART_INF_F, 0.f, 0.f};
+  };
+  auto end_seq = [&]() {                   // this CTA's partial of sequence seq_c
+    float l0 = st.l0, l1 = st.l1;
+#pragma unroll
+    for (int offs = 4; offs < 32; offs <<= 1) {
+      l0 += __shfl_xor_sync(0xffffffffu, l0, offs);
+      l1 += __shfl_xor_sync(0xffffffffu, l1, offs);
+    }
+    const int part = 2 * (b - a.sk[S + 2 + seq_c]) + wj;
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int qg = 2 * t + e;
+      if (qg >= G) continue;
+      const int64_t row = (int64_t)seq_c * a.num_q_heads + h * G + qg;
+      float* pa = a.part_acc + (row * a.num_parts + part) * 128;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<float2*>(pa + 16 * g + 2 * j) = make_float2(o[j][e], o[j][2 + e]);
+      if (g == 0) {
+        a.part_ml[(row * a.num_parts + part) * 2] = e ? st.m1 : st.m0;
+        a.part_ml[(row * a.num_parts + part) * 2 + 1] = e ? l1 : l0;
+      }
+    }
+  };
+  begin_seq(seq0);
+
+  for (int it = 0; it < n_it; ++it) {
+    asm volatile("cp.async.wait_group %0;\n" :: "n"(SK_STAGES - 2) : "memory");
+    __syncthreads();
+    if (it + SK_STAGES - 1 < n_it) issue((it + SK_STAGES - 1) % SK_STAGES);
+    else asm volatile("cp.async.commit_group;\n" ::);
+    const int u = u_begin + it;
+    if (u >= c_end) { end_seq(); begin_seq(locate(u, seq_c)); }     // next sequence (rare)
+    const int bi = 2 * (u - c_base) + wj;
+    if (bi < c_nb) {
+      const uint32_t sb = stage_addr(it % SK_STAGES);
+      TileData<4> cur;
+      const uint4 ka = lds128(sb + kA_off);
+      const uint4 kb = lds128(sb + kA_off + 4096);
+      cur.kA[0] = ka.x; cur.kA[1] = ka.y; cur.kA[2] = ka.z; cur.kA[3] = ka.w;
+      cur.kB[0] = kb.x; cur.kB[1] = kb.y; cur.kB[2] = kb.z; cur.kB[3] = kb.w;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint2 v = lds64(sb + v_off[i]);
+        cur.v[i][0] = v.x; cur.v[i][1] = v.y;
+      }
+#if AKV_NORM_SHFL
+      cur.nrm = __uint_as_float(lds32(sb + n_off));
+#else
+      cur.nkA = __uint_as_float(lds32(sb + 32768 + wj * 512 + (g * 8 + hl) * 4));
+      cur.nkB = __uint_as_float(lds32(sb + 32768 + wj * 512 + ((g + 8) * 8 + hl) * 4));
+      cur.nvA = __uint_as_float(lds32(sb + 33792 + wj * 512 + (g * 8 + hl) * 4));
+      cur.nvB = __uint_as_float(lds32(sb + 33792 + wj * 512 + ((g + 8) * 8 + hl) * 4));
+#endif
+      const int rem = ctx_c - bi * 16;
+      process_tile<4>(lut_s, lanebase, g, bq, cur, rem < 16 ? rem : 16, o, st);
+    }
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+  end_seq();
+}
+
 static inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 struct Plan {
   bool mma;
+  bool persist_shape;     // shapes allow the persistent stream-K kernel (strides are checked at run time)
+  int sk_grid;            // persistent CTAs per head group
   int blocks_per_split, num_splits, warps_per_head, num_parts;
-  size_t off_qrot, off_acc, off_ml, total;
+  size_t parts_alloc;     // partial slots per (sequence, q head) the buffers are sized for
+  size_t off_qrot, off_acc, off_ml, off_sk, total;
 };
 
+static bool persist_enabled() {
+  static const bool on = getenv("AKV_NO_PERSIST") == nullptr;
+  return on;
+}
+
 static Plan make_plan(int num_seqs, int num_q_heads, int num_kv_heads, int head_dim, int bits,
-                      int block_size, int max_blocks_per_seq, int blocks_per_split) {
+                      int block_size, int max_blocks_per_seq, int blocks_per_split, bool persist_ok = true) {
   Plan p;
   const int G = num_q_heads / num_kv_heads;
   p.mma = (head_dim == 128 && G >= 1 && G <= 8 && block_size % 16 == 0);
@@ -916,12 +1246,18 @@ static Plan make_plan(int num_seqs, int num_q_heads, int num_kv_heads, int head_
     p.warps_per_head = GEN_WARPS;
   }
   p.num_parts = p.num_splits * p.warps_per_head;
-  const size_t parts_alloc = (size_t)p.num_parts;
+  const int head_groups = (num_kv_heads + 7) / 8;
+  p.sk_grid = sm_count() / head_groups > 0 ? sm_count() / head_groups : 1;
+  p.persist_shape = persist_ok && persist_enabled() && p.mma && bits == 4 && block_size == 16 &&
+                    num_kv_heads % 8 == 0 && num_seqs <= SK_MAX_SEQS && max_blocks_per_seq > 0;
+  p.parts_alloc = (size_t)p.num_parts;
+  if (p.persist_shape && (size_t)2 * p.sk_grid > p.parts_alloc) p.parts_alloc = (size_t)2 * p.sk_grid;
   size_t rows = (size_t)num_seqs * num_q_heads;
   p.off_qrot = 0;
   p.off_acc = align256(rows * head_dim * sizeof(float));
-  p.off_ml = p.off_acc + align256(rows * parts_alloc * head_dim * sizeof(float));
-  p.total = p.off_ml + align256(rows * parts_alloc * 2 * sizeof(float));
+  p.off_ml = p.off_acc + align256(rows * p.parts_alloc * head_dim * sizeof(float));
+  p.off_sk = p.off_ml + align256(rows * p.parts_alloc * 2 * sizeof(float));
+  p.total = p.off_sk + align256(((size_t)4 * num_seqs + 4) * sizeof(int));
   return p;
 }
 
@@ -961,10 +1297,10 @@ AKV_EXPORT size_t akv_tq_paged_attn_workspace_bytes(int num_seqs, int num_q_head
 }
 
 namespace akv {
-int run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t workspace_bytes);
+int run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t workspace_bytes, bool allow_persist = true);
 }
 
-int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t workspace_bytes) {
+int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t workspace_bytes, bool allow_persist) {
   if (!p) return fail(AKV_ERR_ARG, "null params");
   if (p->bits != 2 && p->bits != 3 && p->bits != 4)
     return fail(AKV_ERR_ARG, "Supported bit-widths: 2, 3, 4. Got %d", p->bits);
@@ -981,7 +1317,7 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
   if (p->num_blocks <= 0) return fail(AKV_ERR_ARG, "paged attention: num_blocks must be > 0");
   cudaStream_t st = (cudaStream_t)p->stream;
   Plan plan = make_plan(p->num_seqs, p->num_q_heads, p->num_kv_heads, D, p->bits, p->block_size,
-                        p->max_blocks_per_seq, p->blocks_per_split);
+                        p->max_blocks_per_seq, p->blocks_per_split, allow_persist);
   if (workspace == nullptr || workspace_bytes < plan.total)
     return fail(AKV_ERR_WORKSPACE, "workspace too small: need %zu bytes, got %zu", plan.total, workspace_bytes);
   char* ws = reinterpret_cast<char*>(workspace);
@@ -990,9 +1326,34 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
   float* part_ml = reinterpret_cast<float*>(ws + plan.off_ml);
   const int rows = p->num_seqs * p->num_q_heads;
 
-  akv_qrot_kernel<<<rows, D < 128 ? D : 128, D * sizeof(float), st>>>(
+  // which split-K kernel serves this call
+  const bool aligned4 = (p->kp_stride_blk % 4 == 0) && (p->kp_stride_pos % 4 == 0) && (p->kp_stride_head % 4 == 0) &&
+                        (p->vp_stride_blk % 4 == 0) && (p->vp_stride_pos % 4 == 0) && (p->vp_stride_head % 4 == 0) &&
+                        (reinterpret_cast<uintptr_t>(p->k_packed) % 4 == 0) &&
+                        (reinterpret_cast<uintptr_t>(p->v_packed) % 4 == 0);
+  if (plan.mma && !aligned4) return fail(AKV_ERR_UNSUPPORTED, "packed cache rows must be 4-byte aligned");
+  const bool vec16 = (p->kp_stride_blk % 16 == 0) && (p->kp_stride_pos % 16 == 0) && (p->kp_stride_head % 16 == 0) &&
+                     (p->vp_stride_blk % 16 == 0) && (p->vp_stride_pos % 16 == 0) && (p->vp_stride_head % 16 == 0) &&
+                     (reinterpret_cast<uintptr_t>(p->k_packed) % 16 == 0) &&
+                     (reinterpret_cast<uintptr_t>(p->v_packed) % 16 == 0);
+  static const bool no_pipe = getenv("AKV_NO_PIPE") != nullptr;
+  const bool pipe = plan.mma && !no_pipe && vec16 && p->bits == 4 && p->block_size == 16 && p->num_kv_heads % 8 == 0 &&
+                    p->kp_stride_head == 64 && p->vp_stride_head == 64 && p->kn_stride_head == 1 &&
+                    p->vn_stride_head == 1 && p->kn_stride_pos % 4 == 0 && p->vn_stride_pos % 4 == 0 &&
+                    p->kn_stride_blk % 4 == 0 && p->vn_stride_blk % 4 == 0 &&
+                    reinterpret_cast<uintptr_t>(p->k_norms) % 16 == 0 &&
+                    reinterpret_cast<uintptr_t>(p->v_norms) % 16 == 0 && p->max_blocks_per_seq > 0;
+  const int64_t lim = (int64_t)1 << 31;
+  const bool persist = pipe && plan.persist_shape && p->kp_stride_blk < lim && p->vp_stride_blk < lim &&
+                       p->kn_stride_blk < lim && p->vn_stride_blk < lim && p->num_blocks < lim;
+  int* sk = reinterpret_cast<int*>(ws + plan.off_sk);
+
+  StreamKPlanArgs pl{};
+  pl.context_lens = p->context_lens; pl.cl_dtype = p->cl_dtype; pl.num_seqs = p->num_seqs;
+  pl.block_size = p->block_size; pl.grid = plan.sk_grid; pl.sk = persist ? sk : nullptr;
+  akv_qrot_kernel<<<rows + (persist ? 1 : 0), D < 128 ? D : 128, D * sizeof(float), st>>>(
       p->query, p->q_dtype, p->q_stride_seq, p->q_stride_head, p->num_q_heads, D, p->rotation_t,
-      p->scale * 1.4426950408889634f, qrot);
+      p->scale * 1.4426950408889634f, qrot, rows, pl);
   if (int rc = check_launch("akv_qrot_kernel")) return rc;
 
   AttnArgs a{};
@@ -1010,37 +1371,26 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
   a.blocks_per_split = plan.blocks_per_split; a.num_splits = plan.num_splits;
   a.warps_per_head = plan.warps_per_head; a.num_parts = plan.num_parts;
   a.qrot = qrot; a.centroids = p->centroids; a.part_acc = part_acc; a.part_ml = part_ml;
+  a.sk = sk;
+  int merge_parts = plan.num_parts;          // stride (and upper bound) of the partial slots the merge reads
 
   if (p->ev_kernel_start) cudaEventRecord((cudaEvent_t)p->ev_kernel_start, st);
   if (p->max_blocks_per_seq > 0) {
-    bool mma = plan.mma && (p->kp_stride_blk % 4 == 0) && (p->kp_stride_pos % 4 == 0) &&
-               (p->kp_stride_head % 4 == 0) && (p->vp_stride_blk % 4 == 0) &&
-               (p->vp_stride_pos % 4 == 0) && (p->vp_stride_head % 4 == 0) &&
-               (reinterpret_cast<uintptr_t>(p->k_packed) % 4 == 0) &&
-               (reinterpret_cast<uintptr_t>(p->v_packed) % 4 == 0);
-    if (plan.mma && !mma)
-      return fail(AKV_ERR_UNSUPPORTED, "packed cache rows must be 4-byte aligned");
-    if (mma) {
-      bool vec16 = (p->kp_stride_blk % 16 == 0) && (p->kp_stride_pos % 16 == 0) &&
-                   (p->kp_stride_head % 16 == 0) && (p->vp_stride_blk % 16 == 0) &&
-                   (p->vp_stride_pos % 16 == 0) && (p->vp_stride_head % 16 == 0) &&
-                   (reinterpret_cast<uintptr_t>(p->k_packed) % 16 == 0) &&
-                   (reinterpret_cast<uintptr_t>(p->v_packed) % 16 == 0);
-      static const bool no_pipe = getenv("AKV_NO_PIPE") != nullptr;
-      const bool pipe = !no_pipe && vec16 && p->bits == 4 && p->block_size == 16 && p->num_kv_heads % 8 == 0 &&
-                        p->kp_stride_head == 64 && p->vp_stride_head == 64 && p->kn_stride_head == 1 &&
-                        p->vn_stride_head == 1 && p->kn_stride_pos % 4 == 0 && p->vn_stride_pos % 4 == 0 &&
-                        p->kn_stride_blk % 4 == 0 && p->vn_stride_blk % 4 == 0 &&
-                        reinterpret_cast<uintptr_t>(p->k_norms) % 16 == 0 &&
-                        reinterpret_cast<uintptr_t>(p->v_norms) % 16 == 0 &&
-                        plan.blocks_per_split <= PIPE_MAX_BLOCKS;
-      if (pipe) {
-        cudaError_t e = cudaFuncSetAttribute(tq4_attn_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PIPE_SMEM);
-        if (e != cudaSuccess) return fail((int)e, "attention: smem attribute: %s", cudaGetErrorString(e));
-        dim3 grid(plan.num_splits, p->num_kv_heads / 8, p->num_seqs);
-        tq4_attn_pipe_kernel<<<grid, 512, PIPE_SMEM, st>>>(a);
-        if (int rc = check_launch("tq4_attn_pipe_kernel")) return rc;
-      } else {
+    if (persist) {
+      a.num_parts = 2 * plan.sk_grid;
+      merge_parts = a.num_parts;
+      cudaError_t e = cudaFuncSetAttribute(tq4_attn_streamk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_DYN_SMEM);
+      if (e != cudaSuccess) return fail((int)e, "attention: smem attribute: %s", cudaGetErrorString(e));
+      dim3 grid(plan.sk_grid, p->num_kv_heads / 8);
+      tq4_attn_streamk_kernel<<<grid, 512, SK_DYN_SMEM, st>>>(a);
+      if (int rc = check_launch("tq4_attn_streamk_kernel")) return rc;
+    } else if (pipe && plan.blocks_per_split <= PIPE_MAX_BLOCKS) {
+      cudaError_t e = cudaFuncSetAttribute(tq4_attn_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PIPE_SMEM);
+      if (e != cudaSuccess) return fail((int)e, "attention: smem attribute: %s", cudaGetErrorString(e));
+      dim3 grid(plan.num_splits, p->num_kv_heads / 8, p->num_seqs);
+      tq4_attn_pipe_kernel<<<grid, 512, PIPE_SMEM, st>>>(a);
+      if (int rc = check_launch("tq4_attn_pipe_kernel")) return rc;
+    } else if (plan.mma) {
       int nh = p->num_kv_heads < 8 ? p->num_kv_heads : 8;
       dim3 grid(plan.num_splits, (p->num_kv_heads + 7) / 8, p->num_seqs);
       dim3 block(32 * nh * plan.warps_per_head);
@@ -1053,20 +1403,19 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
       if (e != cudaSuccess) return fail((int)e, "attention: smem attribute: %s", cudaGetErrorString(e));
       kern<<<grid, block, lut_bytes, st>>>(a);
       if (int rc = check_launch("tq_attn_mma_kernel")) return rc;
-      }
     } else {
       dim3 grid(plan.num_splits, p->num_kv_heads, p->num_seqs);
       tq_attn_generic_kernel<<<grid, GEN_WARPS * 32, 0, st>>>(a);
       if (int rc = check_launch("tq_attn_generic_kernel")) return rc;
     }
   }
-
   if (p->ev_kernel_stop) cudaEventRecord((cudaEvent_t)p->ev_kernel_stop, st);
 
   MergeArgs mg{};
-  mg.acc = part_acc; mg.acc_row = (int64_t)plan.num_parts * D; mg.acc_part = D;
-  mg.ml = part_ml; mg.ml_row = (int64_t)plan.num_parts * 2; mg.ml_part = 2;
-  mg.np = p->max_blocks_per_seq > 0 ? plan.num_parts : 0;
+  mg.acc = part_acc; mg.acc_row = (int64_t)merge_parts * D; mg.acc_part = D;
+  mg.ml = part_ml; mg.ml_row = (int64_t)merge_parts * 2; mg.ml_part = 2;
+  mg.np = p->max_blocks_per_seq > 0 ? merge_parts : 0;
+  mg.part_counts = (persist && p->max_blocks_per_seq > 0) ? sk + 2 * p->num_seqs + 2 : nullptr;
   mg.context_lens = p->context_lens; mg.cl_dtype = p->cl_dtype; mg.num_q_heads = p->num_q_heads;
   mg.tokens_per_split = plan.blocks_per_split * p->block_size; mg.warps_per_head = plan.warps_per_head;
   mg.D = D;
@@ -1143,13 +1492,13 @@ AKV_EXPORT int akv_tq_paged_attn_static(const akv_tq_attn_params* p) {
   akv_tq_attn_params q = *p;
   int bps = p->blocks_per_split;
   Plan plan = make_plan(p->num_seqs, p->num_q_heads, p->num_kv_heads, p->head_dim, p->bits,
-                        p->block_size, p->max_blocks_per_seq, bps);
+                        p->block_size, p->max_blocks_per_seq, bps, false);
   if (bps <= 0) {
     bps = plan.blocks_per_split;
     while (plan.total > AKV_STATIC_SCRATCH_BYTES && plan.num_splits > 1) {
       bps *= 2;
       plan = make_plan(p->num_seqs, p->num_q_heads, p->num_kv_heads, p->head_dim, p->bits,
-                       p->block_size, p->max_blocks_per_seq, bps);
+                       p->block_size, p->max_blocks_per_seq, bps, false);
     }
     q.blocks_per_split = plan.blocks_per_split;
   }
@@ -1160,7 +1509,7 @@ AKV_EXPORT int akv_tq_paged_attn_static(const akv_tq_attn_params* p) {
                 plan.total, (unsigned)AKV_STATIC_SCRATCH_BYTES, p->num_seqs * p->num_q_heads, plan.num_parts);
   void* scratch = nullptr;
   if (int rc = static_scratch_ptr(&scratch)) return rc;
-  return run_tq_attn(&q, scratch, AKV_STATIC_SCRATCH_BYTES);
+  return run_tq_attn(&q, scratch, AKV_STATIC_SCRATCH_BYTES, false);
 }
 
 // Merge `num_parts` raw partials laid out [part][row][D+2] (m in log2 units, l,

@@ -90,11 +90,17 @@ class TQPagedAttention:
         p.blocks_per_split = self.SPLITK_BLOCKS
         return p
 
+    # Split-K scratch is shared by all instances on a device (one per layer would multiply it);
+    # calls are stream-ordered, so instances used on one stream can safely take turns.
+    _shared_workspace: dict = {}
+
     def _get_workspace(self, nbytes: int, device) -> torch.Tensor:
-        ws = self._workspace
-        if ws is None or ws.numel() < nbytes or ws.device != device:
+        ws = TQPagedAttention._shared_workspace.get(device)
+        if ws is None or ws.numel() < nbytes:
             ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
-            self._workspace = ws
+            TQPagedAttention._shared_workspace[device] = ws
+            self._params_key = None
+        self._workspace = ws
         return ws
 
     def forward(

@@ -65,9 +65,8 @@ def test_static_scratch_entry_point_matches_workspace_entry_point():
                    "akv_tq_paged_attn_static")
         torch.cuda.synchronize()
         assert torch.isfinite(got).all()
-        # same kernels, same split size here -> same bits; the tolerance is the suite's fp16 one
+        # the two entry points may pick different split-K kernels; the tolerance is the suite's fp16 one
         assert (got.float() - ref.float()).abs().max().item() <= 2e-3
-        assert torch.equal(got, ref)
 
 
 def test_static_scratch_rejects_oversized_problems():
