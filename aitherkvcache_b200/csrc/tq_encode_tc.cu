@@ -1,0 +1,409 @@
+// TurboQuant encode on the 5th-generation tensor cores (tcgen05 / TMEM), head_dim 128,
+// fp16 or bf16 input.
+//
+// Same operation as the scalar kernels in tq_codec.cu (reference: quantizer.py:122-168,
+// fused_kv_update.py:220-293): norm, rotate by the float32 matrix R, searchsorted against
+// the Lloyd-Max boundaries, MSB-first pack.  The rotation of a tile of 128 vectors is one
+// 128 x 128 x 128 GEMM, issued by a single thread as tcgen05.mma instructions that read both
+// operands from shared memory and accumulate in tensor memory:
+//
+//   * R is float32 and the input is 16-bit, so R is split into 16-bit terms whose sum carries
+//     it to 2^-22 or better: fp16 input -> two fp16 terms of 1024 R (the factor keeps the
+//     second term out of fp16's subnormal range; it is divided out with the norm); bf16
+//     input -> three bf16 terms.  All terms accumulate into the same 128 TMEM columns.
+//     Products are exact, accumulation is float32.
+//   * The vector is rotated before it is normalised, y = (R x) * (1 / (norm + 1e-10f)), so y
+//     differs from the scalar kernels' value by a few float32 ulps; a code can differ only for
+//     a coordinate within ~2e-7 of a boundary.  Norms are bit-equal (same eight-lane order).
+//
+// One persistent CTA of 16 warps per SM.  Per tile: 16-byte cp.async copies fill a 32 KB
+// operand buffer in the 128-byte-swizzled K-major layout the MMA descriptors name; the
+// MMAs of tile t run while the warps compute the norms of tile t, start the copies of tile
+// t+1 and quantise tile t-1 out of its own tensor-memory columns (tcgen05.ld, one thread
+// per vector, 32 consecutive coordinates per load, so packing needs no exchange).
+// Every wait on the MMA barrier is bounded; a wait that gives up sets g_tc_status and the
+// CTA leaves after releasing its tensor memory.
+#include "tq_rowmap.cuh"
+
+namespace akv {
+namespace {
+
+constexpr int TC_HALF_BYTES = 128 * 128;          // 128 rows x 64 16-bit elements (one swizzle atom wide)
+constexpr int TC_OPER_BYTES = 2 * TC_HALF_BYTES;  // a 128 x 128 16-bit operand
+constexpr int TC_CELLS = 128;
+constexpr int TC_LUT_BYTES = TC_CELLS * 32 * 8;   // every cell replicated once per lane
+constexpr int TC_TAIL_BYTES = TC_LUT_BYTES + 4 * 128 * 24 + 2 * 2 * 128 * 4 + 64 + 16 + 16;
+constexpr int TC_SPIN_LIMIT = 1 << 17;
+
+struct TcRow {
+  int64_t src_off;   // element offset of the vector; < 0: beyond the last row
+  uint8_t* dst;      // nullptr: skipped slot
+  float* dst_norm;
+};
+
+__device__ int g_tc_status;   // 1: a wait on the MMA barrier gave up
+
+template <bool BF16> constexpr size_t tc_smem_bytes() {
+  return (size_t)(BF16 ? 3 : 2) * TC_OPER_BYTES + 2 * TC_OPER_BYTES + TC_TAIL_BYTES + 1024;
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+// K-major operand, 128-byte swizzle: rows 128 B apart, 8-row groups 1024 B apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+      :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t mbar_s) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+               :: "r"(mbar_s) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_wait(uint32_t mbar_s, uint32_t parity) {
+  for (int it = 0; it < TC_SPIN_LIMIT; ++it) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(done) : "r"(mbar_s), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+template <bool BF16>
+__device__ __forceinline__ float bits16_to_float(uint32_t h) {
+  if (BF16) return __uint_as_float(h << 16);
+  return __half2float(__ushort_as_half((unsigned short)h));
+}
+
+__device__ __forceinline__ TcRow make_row(const RowMap& m, int64_t n, int64_t n_rows) {
+  TcRow r;
+  if (n >= n_rows) { r.src_off = -1; r.dst = nullptr; r.dst_norm = nullptr; return r; }
+  RowAddr a = map_row(m, n);
+  r.src_off = a.src_off; r.dst = a.dst; r.dst_norm = a.dst_norm;
+  return r;
+}
+
+__device__ __forceinline__ uint32_t bswap32(uint32_t v) { return __byte_perm(v, 0u, 0x0123); }
+
+template <int BITS, bool BF16>
+__global__ void __launch_bounds__(512, 1)
+tq_encode_tc_kernel(RowMap m, int64_t n_rows, const float* __restrict__ rot_t,
+                    const float* __restrict__ boundaries) {
+  constexpr int TERMS = BF16 ? 3 : 2;
+  constexpr int ACC_COLS = 128;                // tensor-memory columns of one tile's accumulator
+  constexpr float PRESCALE = BF16 ? 1.0f : 1024.0f;
+  constexpr int NB = (1 << BITS) - 1;
+  constexpr int CHUNK_BYTES = 32 * BITS / 8;   // packed bytes of 32 coordinates
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_s = smem_u32(smem_raw);
+  const uint32_t base_s = (raw_s + 1023u) & ~1023u;
+  uint8_t* base = smem_raw + (base_s - raw_s);
+  uint8_t* terms = base;
+  uint8_t* abuf = base + TERMS * TC_OPER_BYTES;
+  uint8_t* tail = abuf + 2 * TC_OPER_BYTES;
+  float2* lut = reinterpret_cast<float2*>(tail);                 // [cells][32 lanes]
+  TcRow* rows = reinterpret_cast<TcRow*>(tail + TC_LUT_BYTES);   // [4][128]
+  float* rinv_s = reinterpret_cast<float*>(tail + TC_LUT_BYTES + 4 * 128 * 24);  // [2][128]
+  float* nrm_s = rinv_s + 256;                                   // [2][128]
+  float* bnd = nrm_s + 256;                                      // [16]
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(bnd + 16);        // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mbar + 2);
+  int* simple_flag = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t terms_s = base_s;
+  const uint32_t abuf_s = base_s + TERMS * TC_OPER_BYTES;
+  const uint32_t mbar_s = smem_u32(mbar);
+
+  // ---------------- one-time setup ----------------
+  if (tid == 0) {
+    *simple_flag = 1;
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(mbar_s));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(mbar_s + 8));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (tid < 16) bnd[tid] = tid < NB ? boundaries[tid] : __int_as_float(0x7f800000);
+  __syncwarp();
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;"
+                 :: "r"(smem_u32(tmem_slot)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  // Matrix terms.  rot_t[j][i] = R[i][j] is read with i fastest (coalesced) into a float32
+  // staging copy (the operand buffers, not yet in use), then each operand row i is written
+  // with j fastest; the XOR on the staging column keeps both passes free of bank conflicts.
+  {
+    float* stg = reinterpret_cast<float*>(abuf);
+    for (int e = tid; e < 128 * 128; e += 512) {
+      int j = e >> 7, i = e & 127;
+      stg[j * 128 + (i ^ (j & 31))] = rot_t[e];
+    }
+    __syncthreads();
+    for (int e = tid; e < 128 * 128; e += 512) {
+      int i = e >> 7, j = e & 127;       // operand row i, K index j
+      float r = stg[j * 128 + (i ^ (j & 31))] * PRESCALE;
+      uint32_t off = (uint32_t)((j >> 6) * TC_HALF_BYTES + i * 128 + (((((j & 63) >> 3) ^ (i & 7)) << 4) | ((j & 7) << 1)));
+      if (BF16) {
+        __nv_bfloat16 t1 = __float2bfloat16_rn(r);
+        float e1 = r - __bfloat162float(t1);
+        __nv_bfloat16 t2 = __float2bfloat16_rn(e1);
+        float e2 = e1 - __bfloat162float(t2);
+        *reinterpret_cast<__nv_bfloat16*>(terms + off) = t1;
+        *reinterpret_cast<__nv_bfloat16*>(terms + TC_OPER_BYTES + off) = t2;
+        *reinterpret_cast<__nv_bfloat16*>(terms + 2 * TC_OPER_BYTES + off) = __float2bfloat16_rn(e2);
+      } else {
+        __half t1 = __float2half_rn(r);
+        *reinterpret_cast<__half*>(terms + off) = t1;
+        *reinterpret_cast<__half*>(terms + TC_OPER_BYTES + off) = __float2half_rn(r - __half2float(t1));
+      }
+    }
+  }
+  __syncthreads();
+  // Cell table over [b_first - 4w, b_last + 4w): the entry of cell c answers for any y whose
+  // cell index, computed in float32, comes out as c-1, c or c+1.
+  const float b_first = bnd[0], b_last = bnd[NB - 1];
+  const float cw = (b_last - b_first) / (float)(TC_CELLS - 8);
+  const float inv_cw = 1.0f / cw;
+  const float cell_off = 4.0f - b_first * inv_cw;
+  {
+    float2* cells = reinterpret_cast<float2*>(rinv_s);   // scratch until the main loop starts
+    if (tid < TC_CELLS) {
+      const int c = tid;
+      const float lo_edge = b_first + (float)(c - 5) * cw;
+      const float hi_edge = b_first + (float)(c - 2) * cw;
+      int below_n = 0, cnt = 0;
+      for (int k = 0; k < NB; ++k) {
+        bool below = (c > 0) && (bnd[k] < lo_edge);
+        bool above = (c < TC_CELLS - 1) && (bnd[k] >= hi_edge);
+        below_n += below ? 1 : 0;
+        cnt += (!below && !above) ? 1 : 0;
+      }
+      cells[c] = make_float2(cnt > 0 ? bnd[below_n] : __int_as_float(0x7f800000), __int_as_float(below_n));
+      if (cnt > 1 || !(cw > 0.f) || !(inv_cw < 3.0e38f)) *simple_flag = 0;
+    }
+    __syncthreads();
+    // one copy per lane, 8 bytes apart: a warp's 32 lookups never share a bank
+    for (int e = tid; e < TC_CELLS * 32; e += 512) lut[e] = cells[e >> 5];
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+  const bool simple = *simple_flag != 0;
+
+  // instruction descriptor: D = f32, A/B = f16 or bf16, both K-major, N = 128, M = 128
+  constexpr uint32_t FMT = BF16 ? 1u : 0u;
+  constexpr uint32_t IDESC = (1u << 4) | (FMT << 7) | (FMT << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+
+  const int64_t num_tiles = (n_rows + 127) >> 7;
+  const int n_my = (int)((num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
+
+  auto issue_loads = [&](int t) {
+    const TcRow* rs = rows + (t & 3) * 128;
+    const uint32_t dst0 = abuf_s + (uint32_t)(t & 1) * TC_OPER_BYTES;
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+      const int r = (tid >> 3) + 64 * pass, c = tid & 7;
+      const int64_t off = rs[r].src_off;
+      const uint32_t nbytes = off >= 0 ? 16u : 0u;
+      const uint16_t* src = reinterpret_cast<const uint16_t*>(m.x) + (off >= 0 ? off : 0) + c * 8;
+      const uint32_t dst = dst0 + (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4));
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                     :: "r"(dst + h * TC_HALF_BYTES), "l"(src + h * 64), "r"(nbytes) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  if (n_my > 0 && tid < 128) rows[tid] = make_row(m, (int64_t)blockIdx.x * 128 + tid, n_rows);
+  __syncthreads();
+  if (n_my > 0) issue_loads(0);
+
+  int gave_up = 0;
+  for (int t = 0; t <= n_my; ++t) {
+    const bool have = t < n_my;
+    if (have) {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      if (t + 1 < n_my && tid < 128)
+        rows[((t + 1) & 3) * 128 + tid] =
+            make_row(m, ((int64_t)blockIdx.x + (int64_t)(t + 1) * gridDim.x) * 128 + tid, n_rows);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    if (__syncthreads_or(gave_up)) { gave_up = 1; break; }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+    // ---- tile t: the whole rotation, issued by one thread ----
+    if (have && tid == 0) {
+      const uint32_t a_s = abuf_s + (uint32_t)(t & 1) * TC_OPER_BYTES;
+      const uint32_t d0 = tmem_base + (uint32_t)(t & 1) * ACC_COLS;
+#pragma unroll
+      for (int tm = 0; tm < TERMS; ++tm) {
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t koff = (uint32_t)((kk >> 2) * TC_HALF_BYTES + (kk & 3) * 32);
+          umma_f16(d0, umma_desc(a_s + koff),
+                   umma_desc(terms_s + (uint32_t)tm * TC_OPER_BYTES + koff), IDESC, (uint32_t)((tm | kk) != 0));
+        }
+      }
+      umma_commit(mbar_s + 8u * (uint32_t)(t & 1));
+    }
+    // ---- tile t: norms, four threads per vector, in the reference's summation order ----
+    if (have) {
+      const int row = tid >> 2, qs = tid & 3;
+      const uint8_t* rp = abuf + (t & 1) * TC_OPER_BYTES + row * 128 + qs * 4;
+      float s0 = 0.f, s1 = 0.f;          // partial sums of lanes 2 qs and 2 qs + 1
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        uint32_t w = *reinterpret_cast<const uint32_t*>(rp + (c >> 3) * TC_HALF_BYTES + (((c & 7) ^ (row & 7)) << 4));
+        float x0 = bits16_to_float<BF16>(w & 0xffffu), x1 = bits16_to_float<BF16>(w >> 16);
+        s0 = __fadd_rn(s0, __fmul_rn(x0, x0));
+        s1 = __fadd_rn(s1, __fmul_rn(x1, x1));
+      }
+      float acc = __fadd_rn(s0, s1);     // right for qs == 0; the others chain on below
+#pragma unroll
+      for (int step = 1; step < 4; ++step) {
+        float prev = __shfl_sync(0xffffffffu, acc, (lane & ~3) + step - 1);
+        if (qs == step) acc = __fadd_rn(__fadd_rn(prev, s0), s1);
+      }
+      if (qs == 3) {
+        float nrm = __fsqrt_rn(acc);
+        nrm_s[(t & 1) * 128 + row] = nrm;
+        rinv_s[(t & 1) * 128 + row] = __frcp_rn(__fadd_rn(nrm, 1e-10f)) * (1.0f / PRESCALE);
+      }
+    }
+    // ---- tile t-1: wait for its MMAs (frees its operand buffer, fills its accumulators) ----
+    if (t >= 1) {
+      if (!mbar_wait(mbar_s + 8u * (uint32_t)((t - 1) & 1), (uint32_t)(((t - 1) >> 1) & 1))) gave_up = 1;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    }
+    if (t + 1 < n_my && !gave_up) issue_loads(t + 1);
+    // ---- tile t-1: quantise and pack out of tensor memory ----
+    if (t >= 1 && !gave_up) {
+      const int p = (t - 1) & 1;
+      const int w4 = warp & 3, colq = warp >> 2;
+      const int row = w4 * 32 + lane;
+      const TcRow ri = rows[((t - 1) & 3) * 128 + row];
+      const float rinv = rinv_s[p * 128 + row];
+      const bool store = ri.src_off >= 0 && ri.dst != nullptr;
+      {
+        uint32_t v1[32];
+        tmem_ld32(tmem_base + ((uint32_t)(w4 * 32) << 16) + (uint32_t)(p * ACC_COLS + colq * 32), v1);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        float y[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) y[k] = __fmul_rn(__uint_as_float(v1[k]), rinv);
+        // 32 codes -> MSB-first bit stream, 8 codes per 4*BITS-bit group
+        uint32_t grp[4];
+#pragma unroll
+        for (int g8 = 0; g8 < 4; ++g8) {
+          uint32_t acc = 0;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const float yy = y[g8 * 8 + k];
+            int c;
+            if (simple) {
+              unsigned ci = __float2uint_rd(__fmaf_rn(yy, inv_cw, cell_off));
+              ci = min(ci, (unsigned)(TC_CELLS - 1));
+              const float2 e = lut[ci * 32 + lane];
+              c = __float_as_int(e.y) + ((e.x < yy) ? 1 : 0);
+            } else {
+              c = 0;
+              for (int b = 0; b < NB; ++b) c += (bnd[b] < yy) ? 1 : 0;
+            }
+            acc = (acc << BITS) | (uint32_t)c;
+          }
+          grp[g8] = acc;
+        }
+        uint32_t pw[CHUNK_BYTES / 4];
+        if (BITS == 4) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) pw[k] = bswap32(grp[k]);
+        } else if (BITS == 3) {   // four 24-bit groups -> 12 bytes
+          pw[0] = bswap32((grp[0] << 8) | (grp[1] >> 16));
+          pw[1] = bswap32((grp[1] << 16) | (grp[2] >> 8));
+          pw[2] = bswap32((grp[2] << 24) | grp[3]);
+        } else {                  // four 16-bit groups -> 8 bytes
+          pw[0] = bswap32((grp[0] << 16) | grp[1]);
+          pw[1] = bswap32((grp[2] << 16) | grp[3]);
+        }
+        if (store) {
+          uint8_t* dp = ri.dst + colq * CHUNK_BYTES;
+          const uintptr_t da = reinterpret_cast<uintptr_t>(dp);
+          if (BITS == 4 && (da & 15) == 0) {
+            *reinterpret_cast<uint4*>(dp) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+          } else if ((da & 3) == 0) {
+#pragma unroll
+            for (int k = 0; k < CHUNK_BYTES / 4; ++k) reinterpret_cast<uint32_t*>(dp)[k] = pw[k];
+          } else {
+#pragma unroll
+            for (int b = 0; b < CHUNK_BYTES; ++b) dp[b] = (uint8_t)(pw[b >> 2] >> (8 * (b & 3)));
+          }
+        }
+      }
+      if (store && colq == 0) *ri.dst_norm = nrm_s[p * 128 + row];
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" :: "r"(tmem_base) : "memory");
+  }
+  if (gave_up && tid == 0) g_tc_status = 1;
+}
+
+template <int BITS, bool BF16>
+int launch_tc(const RowMap& m, int64_t n_rows, const float* rot_t, const float* bnd, cudaStream_t st) {
+  auto kern = tq_encode_tc_kernel<BITS, BF16>;
+  constexpr size_t SMEM = tc_smem_bytes<BF16>();
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
+  if (e != cudaSuccess) return fail((int)e, "encode: smem attribute: %s", cudaGetErrorString(e));
+  int64_t tiles = (n_rows + 127) / 128;
+  int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+  kern<<<grid, 512, SMEM, st>>>(m, n_rows, rot_t, bnd);
+  return check_launch("tq_encode_tc_kernel");
+}
+
+}  // namespace
+
+int launch_encode_tc(const RowMap& m, int64_t n_rows, int bits, bool bf16, const float* rot_t,
+                     const float* boundaries, cudaStream_t st) {
+  if (bits == 4) return bf16 ? launch_tc<4, true>(m, n_rows, rot_t, boundaries, st)
+                             : launch_tc<4, false>(m, n_rows, rot_t, boundaries, st);
+  if (bits == 3) return bf16 ? launch_tc<3, true>(m, n_rows, rot_t, boundaries, st)
+                             : launch_tc<3, false>(m, n_rows, rot_t, boundaries, st);
+  if (bits == 2) return bf16 ? launch_tc<2, true>(m, n_rows, rot_t, boundaries, st)
+                             : launch_tc<2, false>(m, n_rows, rot_t, boundaries, st);
+  return fail(AKV_ERR_ARG, "launch_encode_tc: bits %d", bits);
+}
+
+}  // namespace akv

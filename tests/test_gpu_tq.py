@@ -119,6 +119,68 @@ def test_generic_head_dims_vs_oracle(d, bits):
     assert np.abs(dec - ref).max() <= 2e-3 * max(1.0, np.abs(ref).max())
 
 
+@pytest.mark.parametrize("d", (128, 64))
+@pytest.mark.parametrize("bits", BITS)
+@pytest.mark.parametrize("dt", (torch.float16, torch.bfloat16))
+def test_encode_large_batch_16bit_vs_oracle(d, bits, dt):
+    """Batches of 2048+ fp16/bf16 vectors take the tensor-core kernel: same contract
+    (norms bit-equal, codes equal away from boundaries), ragged tail, hand-made rows,
+    and agreement with the small-batch kernel on the same rows."""
+    g = load_golden(f"tq_d{d}_b{bits}.npz")
+    tq = _tq(d, bits, g)
+    gen = torch.Generator().manual_seed(1000 + d + bits)
+    n = 4096 + 37
+    x = torch.randn(n, d, generator=gen)
+    x[5] = 0.0                                   # zero vector
+    x[6] = 0.0; x[6, 3] = 1.0                    # one-hot
+    x[7] = 200.0                                 # large
+    x[8] = 1e-4                                  # tiny
+    x[9] *= 100.0
+    x[-1] = 0.0; x[-1, d - 1] = -2.0
+    x = x.to(dt)
+    packed, norms = tq.encode(x.cuda())
+    xf = x.float().numpy()
+    op, on, margin = otq.encode(xf, g["rotation"], g["boundaries"], bits, return_margin=True)
+    assert np.array_equal(norms.cpu().numpy().view(np.uint32), on.view(np.uint32))
+    diff = otq.unpack(packed.cpu().numpy(), d, bits) != otq.unpack(op, d, bits)
+    near = margin < 1e-6
+    assert not (diff & ~near).any(), f"{(diff & ~near).sum()} codes differ away from a boundary"
+    assert diff.mean() < 1e-5
+    for r in (5, 6, 7, 8, n - 1):
+        assert not diff[r].any()
+    ps, ns = tq.encode(x[:1000].cuda())          # small batch: scalar kernel
+    assert torch.equal(ns, norms[:1000])
+    assert (ps != packed[:1000]).float().mean().item() < 1e-4
+
+
+@pytest.mark.parametrize("bits", BITS)
+def test_paged_write_large_batch_vs_oracle(bits):
+    """A prefill-sized paged write (tokens x heads >= 2048) through the tensor-core kernel,
+    from a strided key view, with skipped and out-of-range slots."""
+    from aitherkvcache_b200 import fused_tq4_kv_update
+    t = load_golden(f"tq_d128_b{bits}.npz")
+    tq = _tq(128, bits, t)
+    pd = 128 * bits // 8
+    nblk, bs, H, T = 70, 16, 8, 1000
+    gen = torch.Generator().manual_seed(55 + bits)
+    qkv = torch.randn(T, 3, H, 128, generator=gen).half()
+    key = qkv[:, 1]                               # strided over tokens
+    slots = torch.randperm(nblk * bs, generator=gen)[:T].to(torch.int64)
+    slots[7] = -1
+    slots[11] = nblk * bs + 5                     # beyond max_blocks: skipped
+    kv = torch.zeros(nblk, 2, bs, H, pd, dtype=torch.uint8, device="cuda")
+    norms = torch.zeros(nblk, bs, H, device="cuda")
+    fused_tq4_kv_update(qkv.cuda()[:, 1], slots.cuda(), kv[:, 0], norms, tq.rotation,
+                        tq.boundaries_inner, bs, nblk)
+    refp = np.zeros((nblk, bs, H, pd), np.uint8)
+    refn = np.zeros((nblk, bs, H), np.float32)
+    otq.paged_kv_update(key.numpy(), slots.numpy(), refp, refn, t["rotation"], t["boundaries"], bits, bs, nblk)
+    assert np.array_equal(norms.cpu().numpy().view(np.uint32), refn.view(np.uint32))
+    got = kv[:, 0].cpu().numpy()
+    assert (got != refp).mean() < 1e-4
+    assert (kv[:, 1] == 0).all()
+
+
 def test_shapes_and_errors():
     tq = _tq(128, 4)
     x = torch.randn(2, 3, 5, 128, device="cuda", dtype=torch.float16)
