@@ -32,7 +32,8 @@ constexpr int TC_HALF_BYTES = 128 * 128;          // 128 rows x 64 16-bit elemen
 constexpr int TC_OPER_BYTES = 2 * TC_HALF_BYTES;  // a 128 x 128 16-bit operand
 constexpr int TC_CELLS = 128;
 constexpr int TC_LUT_BYTES = TC_CELLS * 32 * 8;   // every cell replicated once per lane
-constexpr int TC_TAIL_BYTES = TC_LUT_BYTES + 4 * 128 * 24 + 2 * 2 * 128 * 4 + 64 + 16 + 16;
+constexpr int TC_RING = 8;                          // tiles whose destination rows are remembered
+constexpr int TC_TAIL_BYTES = TC_LUT_BYTES + 2 * 128 * 8 + TC_RING * 128 * 16 + 2 * 2 * 128 * 4 + 64 + 16 + 16;
 constexpr int TC_SPIN_LIMIT = 1 << 17;
 
 struct TcRow {
@@ -43,8 +44,11 @@ struct TcRow {
 
 __device__ int g_tc_status;   // 1: a wait on the MMA barrier gave up
 
+// Operand buffers of vector tiles in flight: what fits beside the matrix terms.
+template <bool BF16> struct TcBuf { static constexpr int N = BF16 ? 2 : 3; };
+
 template <bool BF16> constexpr size_t tc_smem_bytes() {
-  return (size_t)(BF16 ? 3 : 2) * TC_OPER_BYTES + 2 * TC_OPER_BYTES + TC_TAIL_BYTES + 1024;
+  return (size_t)(BF16 ? 3 : 2) * TC_OPER_BYTES + TcBuf<BF16>::N * TC_OPER_BYTES + TC_TAIL_BYTES + 1024;
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -126,10 +130,14 @@ tq_encode_tc_kernel(RowMap m, int64_t n_rows, const float* __restrict__ rot_t,
   uint8_t* base = smem_raw + (base_s - raw_s);
   uint8_t* terms = base;
   uint8_t* abuf = base + TERMS * TC_OPER_BYTES;
-  uint8_t* tail = abuf + 2 * TC_OPER_BYTES;
+  constexpr int NBUF = TcBuf<BF16>::N;        // copies run NBUF - 1 tiles ahead of the MMAs
+  constexpr int AHEAD = NBUF - 1;
+  uint8_t* tail = abuf + NBUF * TC_OPER_BYTES;
   float2* lut = reinterpret_cast<float2*>(tail);                 // [cells][32 lanes]
-  TcRow* rows = reinterpret_cast<TcRow*>(tail + TC_LUT_BYTES);   // [4][128]
-  float* rinv_s = reinterpret_cast<float*>(tail + TC_LUT_BYTES + 4 * 128 * 24);  // [2][128]
+  int64_t* src_ring = reinterpret_cast<int64_t*>(tail + TC_LUT_BYTES);            // [2][128]
+  uint8_t** dst_ring = reinterpret_cast<uint8_t**>(src_ring + 2 * 128);           // [TC_RING][128]
+  float** dstn_ring = reinterpret_cast<float**>(dst_ring + TC_RING * 128);        // [TC_RING][128]
+  float* rinv_s = reinterpret_cast<float*>(dstn_ring + TC_RING * 128);            // [2][128]
   float* nrm_s = rinv_s + 256;                                   // [2][128]
   float* bnd = nrm_s + 256;                                      // [16]
   uint64_t* mbar = reinterpret_cast<uint64_t*>(bnd + 16);        // [2]
@@ -226,12 +234,12 @@ tq_encode_tc_kernel(RowMap m, int64_t n_rows, const float* __restrict__ rot_t,
   const int n_my = (int)((num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
 
   auto issue_loads = [&](int t) {
-    const TcRow* rs = rows + (t & 3) * 128;
-    const uint32_t dst0 = abuf_s + (uint32_t)(t & 1) * TC_OPER_BYTES;
+    const int64_t* rs = src_ring + (t & 1) * 128;
+    const uint32_t dst0 = abuf_s + (uint32_t)(t % NBUF) * TC_OPER_BYTES;
 #pragma unroll
     for (int pass = 0; pass < 2; ++pass) {
       const int r = (tid >> 3) + 64 * pass, c = tid & 7;
-      const int64_t off = rs[r].src_off;
+      const int64_t off = rs[r];
       const uint32_t nbytes = off >= 0 ? 16u : 0u;
       const uint16_t* src = reinterpret_cast<const uint16_t*>(m.x) + (off >= 0 ? off : 0) + c * 8;
       const uint32_t dst = dst0 + (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4));
@@ -240,22 +248,36 @@ tq_encode_tc_kernel(RowMap m, int64_t n_rows, const float* __restrict__ rot_t,
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
                      :: "r"(dst + h * TC_HALF_BYTES), "l"(src + h * 64), "r"(nbytes) : "memory");
     }
-    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  // Row addresses of tile t, worked out by the last four warps one iteration before the
+  // tile's copies start (a barrier lies between): source offsets live for one iteration
+  // (2 slots), destinations until the tile's epilogue AHEAD + 2 iterations later.
+  auto note_rows = [&](int t) {
+    if (tid >= 384) {
+      const int r = tid - 384;
+      TcRow row = make_row(m, ((int64_t)blockIdx.x + (int64_t)t * gridDim.x) * 128 + r, n_rows);
+      src_ring[(t & 1) * 128 + r] = row.src_off;
+      dst_ring[(t & (TC_RING - 1)) * 128 + r] = row.dst;
+      dstn_ring[(t & (TC_RING - 1)) * 128 + r] = row.dst_norm;
+    }
   };
 
-  if (n_my > 0 && tid < 128) rows[tid] = make_row(m, (int64_t)blockIdx.x * 128 + tid, n_rows);
-  __syncthreads();
-  if (n_my > 0) issue_loads(0);
+  // one commit group per tile slot, empty past the last tile, so that "all but the newest
+  // AHEAD - 1 groups" always means "up to tile t"
+  for (int t = 0; t < AHEAD; ++t) {
+    if (t < n_my) note_rows(t);
+    __syncthreads();
+    if (t < n_my) issue_loads(t);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  if (AHEAD < n_my) note_rows(AHEAD);
 
   int gave_up = 0;
   for (int t = 0; t <= n_my; ++t) {
     const bool have = t < n_my;
     if (have) {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      asm volatile("cp.async.wait_group %0;" :: "n"(AHEAD - 1) : "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      if (t + 1 < n_my && tid < 128)
-        rows[((t + 1) & 3) * 128 + tid] =
-            make_row(m, ((int64_t)blockIdx.x + (int64_t)(t + 1) * gridDim.x) * 128 + tid, n_rows);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     if (__syncthreads_or(gave_up)) { gave_up = 1; break; }
@@ -263,7 +285,7 @@ tq_encode_tc_kernel(RowMap m, int64_t n_rows, const float* __restrict__ rot_t,
 
     // ---- tile t: the whole rotation, issued by one thread ----
     if (have && tid == 0) {
-      const uint32_t a_s = abuf_s + (uint32_t)(t & 1) * TC_OPER_BYTES;
+      const uint32_t a_s = abuf_s + (uint32_t)(t % NBUF) * TC_OPER_BYTES;
       const uint32_t d0 = tmem_base + (uint32_t)(t & 1) * ACC_COLS;
 #pragma unroll
       for (int tm = 0; tm < TERMS; ++tm) {
@@ -276,17 +298,30 @@ tq_encode_tc_kernel(RowMap m, int64_t n_rows, const float* __restrict__ rot_t,
       }
       umma_commit(mbar_s + 8u * (uint32_t)(t & 1));
     }
+    // ---- tile t-1: wait for its MMAs (frees its operand buffer, fills its accumulators) ----
+    if (t >= 1) {
+      if (!mbar_wait(mbar_s + 8u * (uint32_t)((t - 1) & 1), (uint32_t)(((t - 1) >> 1) & 1))) gave_up = 1;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    }
+    if (t + AHEAD < n_my && !gave_up) issue_loads(t + AHEAD);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    if (t + AHEAD + 1 < n_my) note_rows(t + AHEAD + 1);
     // ---- tile t: norms, four threads per vector, in the reference's summation order ----
     if (have) {
       const int row = tid >> 2, qs = tid & 3;
-      const uint8_t* rp = abuf + (t & 1) * TC_OPER_BYTES + row * 128 + qs * 4;
+      const uint8_t* rp = abuf + (t % NBUF) * TC_OPER_BYTES + row * 128 + qs * 4;
       float s0 = 0.f, s1 = 0.f;          // partial sums of lanes 2 qs and 2 qs + 1
 #pragma unroll
       for (int c = 0; c < 16; ++c) {
         uint32_t w = *reinterpret_cast<const uint32_t*>(rp + (c >> 3) * TC_HALF_BYTES + (((c & 7) ^ (row & 7)) << 4));
         float x0 = bits16_to_float<BF16>(w & 0xffffu), x1 = bits16_to_float<BF16>(w >> 16);
-        s0 = __fadd_rn(s0, __fmul_rn(x0, x0));
-        s1 = __fadd_rn(s1, __fmul_rn(x1, x1));
+        if (BF16) {
+          s0 = __fadd_rn(s0, __fmul_rn(x0, x0));
+          s1 = __fadd_rn(s1, __fmul_rn(x1, x1));
+        } else {     // the square of an fp16 value is exact in float32: one rounding either way
+          s0 = __fmaf_rn(x0, x0, s0);
+          s1 = __fmaf_rn(x1, x1, s1);
+        }
       }
       float acc = __fadd_rn(s0, s1);     // right for qs == 0; the others chain on below
 #pragma unroll
@@ -300,20 +335,14 @@ tq_encode_tc_kernel(RowMap m, int64_t n_rows, const float* __restrict__ rot_t,
         rinv_s[(t & 1) * 128 + row] = __frcp_rn(__fadd_rn(nrm, 1e-10f)) * (1.0f / PRESCALE);
       }
     }
-    // ---- tile t-1: wait for its MMAs (frees its operand buffer, fills its accumulators) ----
-    if (t >= 1) {
-      if (!mbar_wait(mbar_s + 8u * (uint32_t)((t - 1) & 1), (uint32_t)(((t - 1) >> 1) & 1))) gave_up = 1;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    }
-    if (t + 1 < n_my && !gave_up) issue_loads(t + 1);
     // ---- tile t-1: quantise and pack out of tensor memory ----
     if (t >= 1 && !gave_up) {
       const int p = (t - 1) & 1;
       const int w4 = warp & 3, colq = warp >> 2;
       const int row = w4 * 32 + lane;
-      const TcRow ri = rows[((t - 1) & 3) * 128 + row];
+      uint8_t* const dst = dst_ring[((t - 1) & (TC_RING - 1)) * 128 + row];
       const float rinv = rinv_s[p * 128 + row];
-      const bool store = ri.src_off >= 0 && ri.dst != nullptr;
+      const bool store = dst != nullptr;
       {
         uint32_t v1[32];
         tmem_ld32(tmem_base + ((uint32_t)(w4 * 32) << 16) + (uint32_t)(p * ACC_COLS + colq * 32), v1);
@@ -323,25 +352,37 @@ tq_encode_tc_kernel(RowMap m, int64_t n_rows, const float* __restrict__ rot_t,
         for (int k = 0; k < 32; ++k) y[k] = __fmul_rn(__uint_as_float(v1[k]), rinv);
         // 32 codes -> MSB-first bit stream, 8 codes per 4*BITS-bit group
         uint32_t grp[4];
+        if (simple) {
+          const float2* my_lut = lut + lane;
 #pragma unroll
-        for (int g8 = 0; g8 < 4; ++g8) {
-          uint32_t acc = 0;
+          for (int g8 = 0; g8 < 4; ++g8) {
+            uint32_t acc = 0;
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const float yy = y[g8 * 8 + k];
-            int c;
-            if (simple) {
-              unsigned ci = __float2uint_rd(__fmaf_rn(yy, inv_cw, cell_off));
+            for (int k = 0; k < 8; ++k) {
+              const float yy = y[g8 * 8 + k];
+              unsigned ci = __float2uint_rd(__fmaf_rn(yy, inv_cw, cell_off));   // negative, NaN -> 0
               ci = min(ci, (unsigned)(TC_CELLS - 1));
-              const float2 e = lut[ci * 32 + lane];
-              c = __float_as_int(e.y) + ((e.x < yy) ? 1 : 0);
-            } else {
-              c = 0;
-              for (int b = 0; b < NB; ++b) c += (bnd[b] < yy) ? 1 : 0;
+              const float2 e = my_lut[ci * 32];
+              // acc = (acc << BITS) + cell's count + (its boundary < y)
+              asm("{\n\t.reg .pred p;\n\tsetp.lt.f32 p, %2, %3;\n\tmad.lo.u32 %0, %0, %4, %1;\n\t@p add.u32 %0, %0, 1;\n\t}"
+                  : "+r"(acc) : "r"(__float_as_int(e.y)), "f"(e.x), "f"(yy), "n"(1 << BITS));
             }
-            acc = (acc << BITS) | (uint32_t)c;
+            grp[g8] = acc;
           }
-          grp[g8] = acc;
+        } else {        // boundaries too close for the cell table: count them all
+#pragma unroll
+          for (int g8 = 0; g8 < 4; ++g8) {
+            uint32_t acc = 0;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const float yy = y[g8 * 8 + k];
+              uint32_t c = 0;
+#pragma unroll
+              for (int b = 0; b < NB; ++b) c += (bnd[b] < yy) ? 1u : 0u;
+              acc = (acc << BITS) | c;
+            }
+            grp[g8] = acc;
+          }
         }
         uint32_t pw[CHUNK_BYTES / 4];
         if (BITS == 4) {
@@ -356,7 +397,7 @@ tq_encode_tc_kernel(RowMap m, int64_t n_rows, const float* __restrict__ rot_t,
           pw[1] = bswap32((grp[2] << 16) | grp[3]);
         }
         if (store) {
-          uint8_t* dp = ri.dst + colq * CHUNK_BYTES;
+          uint8_t* dp = dst + colq * CHUNK_BYTES;
           const uintptr_t da = reinterpret_cast<uintptr_t>(dp);
           if (BITS == 4 && (da & 15) == 0) {
             *reinterpret_cast<uint4*>(dp) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
@@ -369,7 +410,7 @@ tq_encode_tc_kernel(RowMap m, int64_t n_rows, const float* __restrict__ rot_t,
           }
         }
       }
-      if (store && colq == 0) *ri.dst_norm = nrm_s[p * 128 + row];
+      if (store && colq == 0) *dstn_ring[((t - 1) & (TC_RING - 1)) * 128 + row] = nrm_s[p * 128 + row];
     }
   }
 

@@ -153,6 +153,25 @@ def test_encode_large_batch_16bit_vs_oracle(d, bits, dt):
     assert (ps != packed[:1000]).float().mean().item() < 1e-4
 
 
+@pytest.mark.parametrize("d", (128, 64))
+def test_encode_large_batch_clustered_boundaries(d):
+    """A caller-supplied codebook whose boundaries nearly coincide: the tensor-core kernels
+    must not rely on their uniform cell table for it."""
+    g = load_golden(f"tq_d{d}_b4.npz")
+    tq = _tq(d, 4, g)
+    bnd = g["boundaries"].copy()
+    bnd[5] = bnd[4] + 1e-6
+    bnd[9] = bnd[8] + 3e-7
+    bnd = np.sort(bnd).astype(np.float32)
+    tq.boundaries_inner = torch.from_numpy(bnd).cuda()
+    x = torch.randn(3000, d, generator=torch.Generator().manual_seed(77)).half()
+    packed, norms = tq.encode(x.cuda())
+    op, on, margin = otq.encode(x.numpy(), g["rotation"], bnd, 4, return_margin=True)
+    assert np.array_equal(norms.cpu().numpy().view(np.uint32), on.view(np.uint32))
+    diff = otq.unpack(packed.cpu().numpy(), d, 4) != otq.unpack(op, d, 4)
+    assert not (diff & ~(margin < 1e-6)).any()
+
+
 @pytest.mark.parametrize("bits", BITS)
 def test_paged_write_large_batch_vs_oracle(bits):
     """A prefill-sized paged write (tokens x heads >= 2048) through the tensor-core kernel,
