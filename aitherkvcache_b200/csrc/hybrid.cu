@@ -26,21 +26,26 @@ struct HybridTables {
   float qjl_scale0, qjl_scale1;
 };
 
-template <int N>
-__device__ __forceinline__ void fwht_pow2(float* w) {
+// Butterfly stages h = 1, 2, 4, ... as a compile-time recursion, so that every index is a
+// constant and the array stays in registers.
+template <int N, int H>
+__device__ __forceinline__ void fwht_stage(float* w) {
+  if constexpr (H < N) {
 #pragma unroll
-  for (int h = 1; h < N; h <<= 1) {
+    for (int i = 0; i < N; i += 2 * H) {
 #pragma unroll
-    for (int i = 0; i < N; i += 2 * h) {
-#pragma unroll
-      for (int j = i; j < i + h; ++j) {
-        float a = w[j], b = w[j + h];
-        w[j] = __fadd_rn(a, b);
-        w[j + h] = __fsub_rn(a, b);
+      for (int j = 0; j < H; ++j) {
+        const float a = w[i + j], b = w[i + j + H];
+        w[i + j] = __fadd_rn(a, b);
+        w[i + j + H] = __fsub_rn(a, b);
       }
     }
+    fwht_stage<N, 2 * H>(w);
   }
 }
+
+template <int N>
+__device__ __forceinline__ void fwht_pow2(float* w) { fwht_stage<N, 1>(w); }
 
 // Block-diagonal transform for sizes that are a sum of two powers of two (96 = 64 + 32).
 template <int G>
@@ -186,6 +191,186 @@ hybrid_encode_kernel(const void* __restrict__ x, int x_dtype, int64_t n_rows, in
 #pragma unroll
     for (int b = 0; b < BYTES0 + BYTES1; ++b) dst[b] = rec[b];
   }
+}
+
+// ---------------------------------------------------------------------------
+// Encode for 16-bit inputs: 128 vectors per CTA, one thread per vector, same
+// arithmetic as encode_group (byte-identical records) with
+//   * the rows staged once as raw 16-bit words (16-byte coalesced loads, word index
+//     XOR-swizzled by row so that a warp's gathers of one coordinate hit 32 banks),
+//   * the normalised vector parked in shared memory between the two uses (one live
+//     G-element register array instead of two),
+//   * codes and sign bits accumulated straight into big-endian 32-bit words,
+//   * division by sqrt(G) done as a multiplication when sqrt(G) is a power of two
+//     (exact either way), and dropped where only the sign of the quotient is used.
+// ---------------------------------------------------------------------------
+constexpr int HE_THREADS = 128;
+
+template <int G> struct SqrtG {
+  static constexpr bool POW2 = (G == 4 || G == 16 || G == 64 || G == 256);
+};
+
+template <int G>
+__device__ __forceinline__ float div_sqrt_g(float v, float sq) {
+  if constexpr (SqrtG<G>::POW2) return __fmul_rn(v, 1.0f / sq);
+  else return __fdiv_rn(v, sq);
+}
+
+template <int BITS>
+__device__ __forceinline__ void stream_put(uint32_t* W, int k, uint32_t c) {
+  const int pos = k * BITS, j = pos >> 5, off = pos & 31;
+  if (off + BITS <= 32) {
+    W[j] |= c << (32 - BITS - off);
+  } else {
+    W[j] |= c >> (off + BITS - 32);
+    W[j + 1] |= c << (64 - BITS - off);
+  }
+}
+
+template <int G, int BITS, bool BF16>
+__device__ __forceinline__ void encode_group16(const uint8_t* xrow, int swz, const int* gidx,
+                                               const float* had, const float* qjl, const float* cent,
+                                               const float* bnd, float* us, uint32_t* out_words) {
+  constexpr int MSE_W = G * BITS / 32, QJL_W = G / 32;
+  static_assert((G * BITS) % 32 == 0 && G % 32 == 0, "group streams must fill whole words");
+  const float sq = sqrtf((float)G);
+  float w[G];
+#pragma unroll
+  for (int k = 0; k < G; ++k) {
+    const int idx = gidx[k];
+    const uint16_t h = *reinterpret_cast<const uint16_t*>(xrow + ((((idx >> 1) ^ swz) << 2) | ((idx & 1) << 1)));
+    w[k] = BF16 ? __uint_as_float((uint32_t)h << 16) : __half2float(__ushort_as_half(h));
+  }
+  const float n = norm8<G>(w);
+  const float den = __fadd_rn(n, 1e-10f);
+#pragma unroll
+  for (int k = 0; k < G; ++k) {
+    const float u = __fdiv_rn(w[k], den);
+    us[k * HE_THREADS] = u;
+    w[k] = __fmul_rn(u, had[k]);
+  }
+  fwht<G>(w);
+  uint32_t W[MSE_W + QJL_W];
+#pragma unroll
+  for (int j = 0; j < MSE_W + QJL_W; ++j) W[j] = 0u;
+#pragma unroll
+  for (int k = 0; k < G; ++k) {
+    const float r = div_sqrt_g<G>(w[k], sq);
+    uint32_t c = 0;
+#pragma unroll
+    for (int b = 0; b < (1 << BITS) - 1; ++b) c += (bnd[b] < r) ? 1u : 0u;
+    stream_put<BITS>(W, k, c);
+    w[k] = cent[c];
+  }
+  fwht<G>(w);
+#pragma unroll
+  for (int k = 0; k < G; ++k)
+    w[k] = __fsub_rn(us[k * HE_THREADS], div_sqrt_g<G>(__fmul_rn(w[k], had[k]), sq));
+  const float rho = norm8<G>(w);
+#pragma unroll
+  for (int k = 0; k < G; ++k) w[k] = __fmul_rn(w[k], qjl[k]);
+  fwht<G>(w);
+#pragma unroll
+  for (int k = 0; k < G; ++k) {
+    // sign of w / sqrt(G): the quotient of a non-NaN w keeps w's sign (and its zero)
+    const uint32_t bit = SqrtG<G>::POW2 ? ((w[k] >= 0.f) ? 1u : 0u) : ((__fdiv_rn(w[k], sq) >= 0.f) ? 1u : 0u);
+    stream_put<1>(W + MSE_W, k, bit);
+  }
+#pragma unroll
+  for (int j = 0; j < MSE_W + QJL_W; ++j) out_words[j] = __byte_perm(W[j], 0u, 0x0123);
+  const uint32_t bn = __half_as_ushort(__float2half_rn(n)), br = __half_as_ushort(__float2half_rn(rho));
+  out_words[MSE_W + QJL_W] = bn | (br << 16);
+}
+
+template <int G0, int B0, int G1, int B1, bool BF16>
+#ifndef AKV_HE_MINB
+#define AKV_HE_MINB 2
+#endif
+__global__ void __launch_bounds__(HE_THREADS, AKV_HE_MINB)
+hybrid_encode16_kernel(const uint16_t* __restrict__ x, int64_t n_rows, int64_t x_row_stride,
+                       HybridTables t, uint8_t* __restrict__ out, int64_t out_row_stride) {
+  constexpr int D = G0 + G1;
+  static_assert(D == 128, "rows are staged as 16 chunks of 16 bytes");
+  constexpr int GMAX = G0 > G1 ? G0 : G1;
+  constexpr int W0 = G0 * B0 / 32 + G0 / 32 + 1, W1 = G1 * B1 / 32 + G1 / 32 + 1;
+  extern __shared__ __align__(16) uint8_t he_smem[];
+  uint32_t* xs = reinterpret_cast<uint32_t*>(he_smem);                 // [128 rows][64 words]
+  float* us = reinterpret_cast<float*>(he_smem + HE_THREADS * 256);     // [GMAX][128]
+  __shared__ float s_had[D], s_qjl[D], s_cent[16], s_bnd[16];
+  __shared__ int s_idx[D];
+  const int tid = threadIdx.x;
+  if (tid < D) { s_had[tid] = t.had_signs[tid]; s_qjl[tid] = t.qjl_signs[tid]; s_idx[tid] = t.group_index[tid]; }
+  if (tid < 16) { s_cent[tid] = t.centroids[tid]; s_bnd[tid] = t.boundaries[tid]; }
+  const int64_t row0 = (int64_t)blockIdx.x * HE_THREADS;
+  const bool vec = (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (x_row_stride & 7) == 0;
+#pragma unroll
+  for (int i0 = 0; i0 < 16; i0 += 8) {
+    uint4 v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int e = (i0 + i) * HE_THREADS + tid, r = e >> 4, c = e & 15;
+      const int64_t n = row0 + r;
+      v[i] = make_uint4(0u, 0u, 0u, 0u);
+      if (n < n_rows) {
+        const uint16_t* src = x + n * x_row_stride + c * 8;
+        if (vec) {
+          v[i] = *reinterpret_cast<const uint4*>(src);
+        } else {
+          v[i].x = src[0] | ((uint32_t)src[1] << 16); v[i].y = src[2] | ((uint32_t)src[3] << 16);
+          v[i].z = src[4] | ((uint32_t)src[5] << 16); v[i].w = src[6] | ((uint32_t)src[7] << 16);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int e = (i0 + i) * HE_THREADS + tid, r = e >> 4, c = e & 15;
+      uint32_t* dst = xs + r * 64;
+      const int sw = r & 31;
+      dst[(4 * c + 0) ^ sw] = v[i].x; dst[(4 * c + 1) ^ sw] = v[i].y;
+      dst[(4 * c + 2) ^ sw] = v[i].z; dst[(4 * c + 3) ^ sw] = v[i].w;
+    }
+  }
+  __syncthreads();
+  const int64_t n = row0 + tid;
+  if (n >= n_rows) return;
+  // The index map can differ per head: then every thread reads its own head's map from
+  // global memory, the shared copy otherwise.
+  const int* gidx = s_idx;
+  if (t.num_index_heads > 1) gidx = t.group_index + (int)(n % t.num_index_heads) * D;
+  uint32_t rec[W0 + W1];
+  const uint8_t* xrow = reinterpret_cast<const uint8_t*>(xs + tid * 64);
+  encode_group16<G0, B0, BF16>(xrow, tid & 31, gidx, s_had, s_qjl, s_cent, s_bnd, us + tid, rec);
+  encode_group16<G1, B1, BF16>(xrow, tid & 31, gidx + G0, s_had + G0, s_qjl + G0, s_cent + 8, s_bnd + 8,
+                               us + tid, rec + W0);
+  uint8_t* dst = out + n * out_row_stride;
+  if ((reinterpret_cast<uintptr_t>(dst) & 3) == 0) {
+#pragma unroll
+    for (int wd = 0; wd < W0 + W1; ++wd) reinterpret_cast<uint32_t*>(dst)[wd] = rec[wd];
+  } else {
+#pragma unroll
+    for (int b = 0; b < 4 * (W0 + W1); ++b) dst[b] = (uint8_t)(rec[b >> 2] >> (8 * (b & 3)));
+  }
+}
+
+template <int G0, int B0, int G1, int B1>
+static int launch_hybrid_encode16(const void* x, int x_dtype, int64_t n_rows, int64_t x_row_stride,
+                                  const HybridTables& t, uint8_t* out, int64_t out_row_stride, cudaStream_t st) {
+  constexpr int GMAX = G0 > G1 ? G0 : G1;
+  constexpr size_t SMEM = (size_t)HE_THREADS * 256 + (size_t)GMAX * HE_THREADS * 4;
+  const int grid = (int)((n_rows + HE_THREADS - 1) / HE_THREADS);
+  const uint16_t* xp = reinterpret_cast<const uint16_t*>(x);
+  cudaError_t e;
+  if (x_dtype == AKV_BF16) {
+    auto kern = hybrid_encode16_kernel<G0, B0, G1, B1, true>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
+    if (e == cudaSuccess) kern<<<grid, HE_THREADS, SMEM, st>>>(xp, n_rows, x_row_stride, t, out, out_row_stride);
+  } else {
+    auto kern = hybrid_encode16_kernel<G0, B0, G1, B1, false>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
+    if (e == cudaSuccess) kern<<<grid, HE_THREADS, SMEM, st>>>(xp, n_rows, x_row_stride, t, out, out_row_stride);
+  }
+  if (e != cudaSuccess) return fail((int)e, "hybrid encode: smem attribute: %s", cudaGetErrorString(e));
+  return check_launch("hybrid_encode16_kernel");
 }
 
 template <int G, int BITS>
@@ -512,8 +697,13 @@ AKV_EXPORT int akv_hybrid_encode(const void* x, int x_dtype, int64_t n_rows, int
   if (n_rows == 0) return AKV_OK;
   if (!x || !packed) return fail(AKV_ERR_ARG, "akv_hybrid_encode: null pointer");
   if (x_dtype < AKV_F16 || x_dtype > AKV_F32) return fail(AKV_ERR_ARG, "bad x_dtype %d", x_dtype);
-  const int grid = (int)((n_rows + HY_THREADS - 1) / HY_THREADS);
   cudaStream_t st = (cudaStream_t)stream;
+  if (x_dtype != AKV_F32) {
+    if (mode == 35)
+      return launch_hybrid_encode16<64, 3, 64, 2>(x, x_dtype, n_rows, x_row_stride, t, packed, packed_row_stride, st);
+    return launch_hybrid_encode16<32, 2, 96, 1>(x, x_dtype, n_rows, x_row_stride, t, packed, packed_row_stride, st);
+  }
+  const int grid = (int)((n_rows + HY_THREADS - 1) / HY_THREADS);
   if (mode == 35)
     hybrid_encode_kernel<64, 3, 64, 2><<<grid, HY_THREADS, 0, st>>>(x, x_dtype, n_rows, x_row_stride, t, packed, packed_row_stride);
   else
