@@ -13,6 +13,7 @@
 //   tq35 (d=128): 24+8+2+2 | 16+8+2+2 = 64 bytes;  tq25: 8+4+2+2 | 12+12+2+2 = 44 bytes.
 #include "common.cuh"
 #include <math_constants.h>
+#include <stdlib.h>
 
 namespace akv {
 
@@ -587,6 +588,387 @@ hybrid_attn_kernel(HybridAttnArgs a) {
   }
 }
 
+// ---------------------------------------------------------------------------
+// Tensor-core version of the same computation (same grid, same partials).
+//
+// A warp owns one part (one KV head, every HA_WARPS-th 16-token tile of the split) and all
+// query heads of the head's GQA group (up to 8).  Per tile it copies the 16 K records and the
+// 16 V records (2 KB) into its own double-buffered staging area with 16-byte cp.async (chunk
+// q of token r is stored at chunk q ^ ((r >> 1) & 3), which spreads the fragment reads over
+// the banks), then:
+//   scores  S^T[16 tokens][8 q heads] = sum over the four segments of w_seg(token) * (A_seg q'_seg),
+//           A_seg = 16 x 64 fp16 operand decoded from the record: centroid pairs through
+//           per-lane lookup tables (3-bit: 6-bit pair index, 2-bit: whole byte -> 4 values),
+//           sign nibbles through a 16-entry table of +-1 pairs; mma.sync m16n8k16, fp32 accumulate;
+//   values  O^T[256 virtual dims][8 q heads] += V_seg^T (P . w_seg)^T with the softmax weights
+//           scaled per segment and token, transposed by movmatrix.
+// Thread (g, t) of the warp (g = lane / 4, t = lane % 4) decodes, for the scores, coordinates
+// 16t..16t+15 of every segment of tokens g and g + 8; for the values, coordinates 8g..8g+7 of
+// every segment of tokens 2t, 2t+1, 2t+8, 2t+9.
+// ---------------------------------------------------------------------------
+constexpr int HM_LUT2 = 0;                       // 256 entries x 256 B: byte of four 2-bit codes -> 4 halves
+constexpr int HM_LUT3 = 65536;                   // 64 entries x 128 B: two 3-bit codes -> 2 halves
+constexpr int HM_LUTS = HM_LUT3 + 8192;          // 16 entries x 256 B: four sign bits -> 4 halves
+constexpr int HM_STAGE = HM_LUTS + 4096;         // per warp: 2 buffers x (1 KB K + 1 KB V)
+constexpr int HM_SMEM = HM_STAGE + HA_WARPS * 4096;
+
+__device__ __forceinline__ uint32_t hm_lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t hm_lds16(uint32_t addr) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];\n" : "=h"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t hm_lds8(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u8 %0, [%1];\n" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint2 hm_lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void hm_mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                       uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t hm_trans(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(y) : "r"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t hm_pack(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ float hm_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// Pair P of an MSB-first 3-bit stream whose first 32 bits are B (P <= 4) -> half2 of two centroids.
+template <int P>
+__device__ __forceinline__ uint32_t hm_pair3(uint32_t lut3, uint32_t B, uint32_t lane4) {
+  static_assert(6 * P <= 26, "pair must lie in the first word");
+  return hm_lds32(lut3 + ((((B >> (26 - 6 * P)) & 63u) << 7) | lane4));
+}
+// Sign nibble (already shifted to bits 8..11 of x) -> two half2 of +-1.
+__device__ __forceinline__ uint2 hm_signs(uint32_t luts, uint32_t x, uint32_t lane8) {
+  return hm_lds64(luts + ((x & 0xF00u) | lane8));
+}
+// Byte K of w (four 2-bit codes) -> two half2 of centroids.
+template <int K>
+__device__ __forceinline__ uint2 hm_quad2(uint32_t lut2, uint32_t w, uint32_t lane8) {
+  return hm_lds64(lut2 + __byte_perm(w, lane8, 0x7604 + (K << 4)));
+}
+
+__global__ void __launch_bounds__(HA_WARPS * 32, 2)
+hybrid_attn_mma_kernel(HybridAttnArgs a) {
+  extern __shared__ __align__(16) unsigned char hm_smem[];
+  const int split = blockIdx.x, h = blockIdx.y, seq = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int G = a.num_q_heads / a.num_kv_heads;
+  const int64_t ctx = load_index(a.context_lens, a.cl_dtype, seq);
+  const int tpb = a.block_size / 16;
+  const int64_t tiles_total = (ctx + 15) / 16;
+  const int64_t tile_begin = (int64_t)split * a.blocks_per_split * tpb;
+  if (tile_begin >= tiles_total) return;   // uniform for the CTA
+  int64_t tile_end = tile_begin + (int64_t)a.blocks_per_split * tpb;
+  if (tile_end > tiles_total) tile_end = tiles_total;
+
+  // ---- lookup tables, one copy per lane ----
+  const float* c0 = a.centroids;        // 8 centroids of group 0 (3-bit)
+  const float* c1 = a.centroids + 8;    // 4 centroids of group 1 (2-bit)
+  for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x) {
+    const int e = i >> 5, l = i & 31;
+    *reinterpret_cast<uint2*>(hm_smem + HM_LUT2 + e * 256 + l * 8) =
+        make_uint2(hm_pack(c1[e >> 6], c1[(e >> 4) & 3]), hm_pack(c1[(e >> 2) & 3], c1[e & 3]));
+  }
+  for (int i = threadIdx.x; i < 64 * 32; i += blockDim.x) {
+    const int e = i >> 5, l = i & 31;
+    *reinterpret_cast<uint32_t*>(hm_smem + HM_LUT3 + e * 128 + l * 4) = hm_pack(c0[e >> 3], c0[e & 7]);
+  }
+  for (int i = threadIdx.x; i < 16 * 32; i += blockDim.x) {
+    const int e = i >> 5, l = i & 31;
+    *reinterpret_cast<uint2*>(hm_smem + HM_LUTS + e * 256 + l * 8) =
+        make_uint2(hm_pack((e & 8) ? 1.f : -1.f, (e & 4) ? 1.f : -1.f),
+                   hm_pack((e & 2) ? 1.f : -1.f, (e & 1) ? 1.f : -1.f));
+  }
+  __syncthreads();
+
+  const uint32_t smem_s = (uint32_t)__cvta_generic_to_shared(hm_smem);
+  const uint32_t lut2 = smem_s + HM_LUT2, lut3 = smem_s + HM_LUT3, luts = smem_s + HM_LUTS;
+  const uint32_t stage_s = smem_s + HM_STAGE + warp * 4096;
+  const uint32_t lane4 = lane * 4, lane8 = lane * 8;
+
+  // ---- query fragments: thread (g, t) holds q'[q head g][segment][16t .. 16t+15] ----
+  uint32_t bq[4][4][2];
+  {
+    const float* qp = a.qprime + ((int64_t)seq * a.num_q_heads + h * G + (g < G ? g : 0)) * 256 + 16 * t;
+#pragma unroll
+    for (int sg = 0; sg < 4; ++sg)
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        float4 f = *reinterpret_cast<const float4*>(qp + 64 * sg + 4 * kk);
+        if (g >= G) f = make_float4(0.f, 0.f, 0.f, 0.f);
+        bq[sg][kk][0] = hm_pack(f.x, f.y);
+        bq[sg][kk][1] = hm_pack(f.z, f.w);
+      }
+  }
+
+  // ---- per-thread byte offsets inside a staged record ----
+  // logical byte b of token r lives at r*64 + (((b >> 4) ^ ((r >> 1) & 3)) << 4) + (b & 15)
+  const uint32_t sK = (g >> 1) & 3;     // tokens g, g + 8
+  const uint32_t sV = t;                // tokens 2t, 2t+1, 2t+8, 2t+9
+  auto swz = [](uint32_t b, uint32_t sw) { return (((b >> 4) ^ sw) << 4) | (b & 15u); };
+  const uint32_t kRow = g * 64;
+  const uint32_t kw0 = 4 * ((6 * t) >> 2);
+  const uint32_t oK0a = kRow + swz(kw0, sK), oK0b = kRow + swz(kw0 + 4, sK);
+  const uint32_t oKs0 = kRow + swz(24 + 2 * t, sK), oKn0 = kRow + swz(32, sK);
+  const uint32_t oKc1 = kRow + swz(36 + 4 * t, sK), oKs1 = kRow + swz(52 + 2 * t, sK), oKn1 = kRow + swz(60, sK);
+  // 48 stream bits start at byte 6t: at byte 0 (t even) or byte 2 (t odd) of the two words read
+  const uint32_t selK0 = (t & 1) ? 0x2345u : 0x0123u, selK1 = (t & 1) ? 0x6700u : 0x4500u;
+  const uint32_t vRow = 1024 + 2 * t * 64;
+  const uint32_t vw0 = 4 * ((3 * g) >> 2), vo = (3 * g) & 3;
+  const uint32_t oV0a = vRow + swz(vw0, sV), oV0b = vRow + swz(vw0 + 4, sV);
+  const uint32_t oVs0 = vRow + swz(24 + g, sV), oVc1 = vRow + swz(36 + 2 * g, sV), oVs1 = vRow + swz(52 + g, sV);
+  const uint32_t selV0 = (vo << 12) | ((vo + 1) << 8) | ((vo + 2) << 4) | (vo + 3);
+
+  float o[4][4][4];
+#pragma unroll
+  for (int sg = 0; sg < 4; ++sg)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { o[sg][j][0] = o[sg][j][1] = o[sg][j][2] = o[sg][j][3] = 0.f; }
+  float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
+
+  const int64_t first = tile_begin + warp;
+  const int n_tiles = first < tile_end ? (int)((tile_end - first + HA_WARPS - 1) / HA_WARPS) : 0;
+
+  auto issue = [&](int i) {     // copy tile i of this warp into buffer i & 1
+    const int64_t tile = first + (int64_t)i * HA_WARPS;
+    int64_t pb = load_index(a.block_tables, a.bt_dtype, (int64_t)seq * a.bt_stride + tile / tpb);
+    if (pb < 0) pb = 0;
+    if (pb >= a.num_blocks) pb = a.num_blocks - 1;
+    const int pos0 = (int)(tile % tpb) * 16;
+    const uint32_t dst0 = stage_s + (uint32_t)(i & 1) * 2048;
+#pragma unroll
+    for (int r2 = 0; r2 < 2; ++r2) {
+      const int c = lane + 32 * r2, tok = c >> 2, q = c & 3;
+      const uint32_t d = dst0 + tok * 64 + ((q ^ ((tok >> 1) & 3)) << 4);
+      const uint8_t* ks = a.k_cache + pb * a.k_sb + (int64_t)(pos0 + tok) * a.k_sp + h * a.k_sh + q * 16;
+      const uint8_t* vs = a.v_cache + pb * a.v_sb + (int64_t)(pos0 + tok) * a.v_sp + h * a.v_sh + q * 16;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" :: "r"(d), "l"(ks) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" :: "r"(d + 1024), "l"(vs) : "memory");
+    }
+  };
+
+  if (n_tiles > 0) issue(0);
+  asm volatile("cp.async.commit_group;\n" ::: "memory");
+#pragma unroll 1
+  for (int i = 0; i < n_tiles; ++i) {
+    if (i + 1 < n_tiles) issue(i + 1);
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+    asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+    __syncwarp();
+    const uint32_t buf = stage_s + (uint32_t)(i & 1) * 2048;
+    const int64_t tile = first + (int64_t)i * HA_WARPS;
+    const int64_t rem = ctx - tile * 16;
+    const int n_valid = rem < 16 ? (int)rem : 16;
+
+    // ================= scores =================
+    float sc[4][4];
+#pragma unroll
+    for (int sg = 0; sg < 4; ++sg) sc[sg][0] = sc[sg][1] = sc[sg][2] = sc[sg][3] = 0.f;
+    {   // segment 0: 3-bit codes
+      const uint32_t a0 = hm_lds32(buf + oK0a), a1 = hm_lds32(buf + oK0b);
+      const uint32_t b0 = hm_lds32(buf + oK0a + 512), b1 = hm_lds32(buf + oK0b + 512);
+      const uint32_t A0 = __byte_perm(a0, a1, selK0), A1 = __byte_perm(a0, a1, selK1);
+      const uint32_t B0 = __byte_perm(b0, b1, selK0), B1 = __byte_perm(b0, b1, selK1);
+      uint32_t na[8], nb[8];
+      na[0] = hm_pair3<0>(lut3, A0, lane4); na[1] = hm_pair3<1>(lut3, A0, lane4);
+      na[2] = hm_pair3<2>(lut3, A0, lane4); na[3] = hm_pair3<3>(lut3, A0, lane4);
+      na[4] = hm_pair3<4>(lut3, A0, lane4);
+      nb[0] = hm_pair3<0>(lut3, B0, lane4); nb[1] = hm_pair3<1>(lut3, B0, lane4);
+      nb[2] = hm_pair3<2>(lut3, B0, lane4); nb[3] = hm_pair3<3>(lut3, B0, lane4);
+      nb[4] = hm_pair3<4>(lut3, B0, lane4);
+      // pair 5 = stream bits 30..35 straddles the words; pairs 6, 7 sit in the second word
+      na[5] = hm_lds32(lut3 + (((__funnelshift_l(A1, A0, 4) & 63u) << 7) | lane4));
+      nb[5] = hm_lds32(lut3 + (((__funnelshift_l(B1, B0, 4) & 63u) << 7) | lane4));
+      na[6] = hm_lds32(lut3 + ((((A1 >> 22) & 63u) << 7) | lane4));
+      nb[6] = hm_lds32(lut3 + ((((B1 >> 22) & 63u) << 7) | lane4));
+      na[7] = hm_lds32(lut3 + ((((A1 >> 16) & 63u) << 7) | lane4));
+      nb[7] = hm_lds32(lut3 + ((((B1 >> 16) & 63u) << 7) | lane4));
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)
+        hm_mma(sc[0], na[2 * kk], nb[2 * kk], na[2 * kk + 1], nb[2 * kk + 1], bq[0][kk][0], bq[0][kk][1]);
+    }
+#pragma unroll
+    for (int sgn = 0; sgn < 2; ++sgn) {   // segments 1 and 3: sign bits
+      const uint32_t va = hm_lds16(buf + (sgn ? oKs1 : oKs0)), vb = hm_lds16(buf + (sgn ? oKs1 : oKs0) + 512);
+      const uint2 a0 = hm_signs(luts, va << 4, lane8), a1 = hm_signs(luts, va << 8, lane8);
+      const uint2 a2 = hm_signs(luts, va >> 4, lane8), a3 = hm_signs(luts, va, lane8);
+      const uint2 b0 = hm_signs(luts, vb << 4, lane8), b1 = hm_signs(luts, vb << 8, lane8);
+      const uint2 b2 = hm_signs(luts, vb >> 4, lane8), b3 = hm_signs(luts, vb, lane8);
+      const int sg = 1 + 2 * sgn;
+      hm_mma(sc[sg], a0.x, b0.x, a0.y, b0.y, bq[sg][0][0], bq[sg][0][1]);
+      hm_mma(sc[sg], a1.x, b1.x, a1.y, b1.y, bq[sg][1][0], bq[sg][1][1]);
+      hm_mma(sc[sg], a2.x, b2.x, a2.y, b2.y, bq[sg][2][0], bq[sg][2][1]);
+      hm_mma(sc[sg], a3.x, b3.x, a3.y, b3.y, bq[sg][3][0], bq[sg][3][1]);
+    }
+    {   // segment 2: 2-bit codes, one byte per k-tile
+      const uint32_t wa = hm_lds32(buf + oKc1), wb = hm_lds32(buf + oKc1 + 512);
+      const uint2 a0 = hm_quad2<0>(lut2, wa, lane8), a1 = hm_quad2<1>(lut2, wa, lane8);
+      const uint2 a2 = hm_quad2<2>(lut2, wa, lane8), a3 = hm_quad2<3>(lut2, wa, lane8);
+      const uint2 b0 = hm_quad2<0>(lut2, wb, lane8), b1 = hm_quad2<1>(lut2, wb, lane8);
+      const uint2 b2 = hm_quad2<2>(lut2, wb, lane8), b3 = hm_quad2<3>(lut2, wb, lane8);
+      hm_mma(sc[2], a0.x, b0.x, a0.y, b0.y, bq[2][0][0], bq[2][0][1]);
+      hm_mma(sc[2], a1.x, b1.x, a1.y, b1.y, bq[2][1][0], bq[2][1][1]);
+      hm_mma(sc[2], a2.x, b2.x, a2.y, b2.y, bq[2][2][0], bq[2][2][1]);
+      hm_mma(sc[2], a3.x, b3.x, a3.y, b3.y, bq[2][3][0], bq[2][3][1]);
+    }
+    float s0, s1, s2, s3;
+    {
+      const __half2 kA0 = *reinterpret_cast<const __half2*>(hm_smem + (buf - smem_s) + oKn0);
+      const __half2 kA1 = *reinterpret_cast<const __half2*>(hm_smem + (buf - smem_s) + oKn1);
+      const __half2 kB0 = *reinterpret_cast<const __half2*>(hm_smem + (buf - smem_s) + oKn0 + 512);
+      const __half2 kB1 = *reinterpret_cast<const __half2*>(hm_smem + (buf - smem_s) + oKn1 + 512);
+      const float nA0 = __low2float(kA0), rA0 = nA0 * __high2float(kA0);
+      const float nA1 = __low2float(kA1), rA1 = nA1 * __high2float(kA1);
+      const float nB0 = __low2float(kB0), rB0 = nB0 * __high2float(kB0);
+      const float nB1 = __low2float(kB1), rB1 = nB1 * __high2float(kB1);
+      s0 = nA0 * sc[0][0] + rA0 * sc[1][0] + nA1 * sc[2][0] + rA1 * sc[3][0];
+      s1 = nA0 * sc[0][1] + rA0 * sc[1][1] + nA1 * sc[2][1] + rA1 * sc[3][1];
+      s2 = nB0 * sc[0][2] + rB0 * sc[1][2] + nB1 * sc[2][2] + rB1 * sc[3][2];
+      s3 = nB0 * sc[0][3] + rB0 * sc[1][3] + nB1 * sc[2][3] + rB1 * sc[3][3];
+    }
+    // value-side segment weights of tokens g and g + 8 (same staged layout, V half)
+    float wA[4], wB[4];
+    {
+      const __half2 vA0 = *reinterpret_cast<const __half2*>(hm_smem + (buf - smem_s) + 1024 + oKn0);
+      const __half2 vA1 = *reinterpret_cast<const __half2*>(hm_smem + (buf - smem_s) + 1024 + oKn1);
+      const __half2 vB0 = *reinterpret_cast<const __half2*>(hm_smem + (buf - smem_s) + 1024 + oKn0 + 512);
+      const __half2 vB1 = *reinterpret_cast<const __half2*>(hm_smem + (buf - smem_s) + 1024 + oKn1 + 512);
+      wA[0] = __low2float(vA0); wA[1] = wA[0] * __high2float(vA0);
+      wA[2] = __low2float(vA1); wA[3] = wA[2] * __high2float(vA1);
+      wB[0] = __low2float(vB0); wB[1] = wB[0] * __high2float(vB0);
+      wB[2] = __low2float(vB1); wB[3] = wB[2] * __high2float(vB1);
+    }
+    if (n_valid < 16) {   // warp-uniform: only the last tile of a sequence
+      if (g >= n_valid) { s0 = -CUDART_INF_F; s1 = -CUDART_INF_F; wA[0] = wA[1] = wA[2] = wA[3] = 0.f; }
+      if (g + 8 >= n_valid) { s2 = -CUDART_INF_F; s3 = -CUDART_INF_F; wB[0] = wB[1] = wB[2] = wB[3] = 0.f; }
+    }
+
+    // ================= online softmax (log2 units) =================
+    float mx0 = fmaxf(s0, s2), mx1 = fmaxf(s1, s3);
+#pragma unroll
+    for (int off = 4; off < 32; off <<= 1) {
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+    }
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    if (__any_sync(0xffffffffu, (mn0 != m0) | (mn1 != m1))) {
+      const float al0 = hm_ex2(m0 - mn0), al1 = hm_ex2(m1 - mn1);
+      l0 *= al0; l1 *= al1;
+#pragma unroll
+      for (int sg = 0; sg < 4; ++sg)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { o[sg][j][0] *= al0; o[sg][j][1] *= al1; o[sg][j][2] *= al0; o[sg][j][3] *= al1; }
+      m0 = mn0; m1 = mn1;
+    }
+    const float p0 = hm_ex2(s0 - mn0), p1 = hm_ex2(s1 - mn1), p2 = hm_ex2(s2 - mn0), p3 = hm_ex2(s3 - mn1);
+    l0 += p0 + p2;
+    l1 += p1 + p3;
+    uint32_t pbA[4], pbB[4];
+#pragma unroll
+    for (int sg = 0; sg < 4; ++sg) {
+      pbA[sg] = hm_trans(hm_pack(p0 * wA[sg], p1 * wA[sg]));
+      pbB[sg] = hm_trans(hm_pack(p2 * wB[sg], p3 * wB[sg]));
+    }
+
+    // ================= values =================
+    // n[tok][j] = half2(coordinate 8g+2j, 8g+2j+1) of token tok; M-tile j pairs the same
+    // coordinate of two tokens: rows g / g+8 of the tile are coordinates 8g+2j / 8g+2j+1.
+    {   // segment 0
+      uint32_t n[4][4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t ro = (k & 1) * 64 + (k >> 1) * 512;
+        const uint32_t B = __byte_perm(hm_lds32(buf + oV0a + ro), hm_lds32(buf + oV0b + ro), selV0);
+        n[k][0] = hm_pair3<0>(lut3, B, lane4); n[k][1] = hm_pair3<1>(lut3, B, lane4);
+        n[k][2] = hm_pair3<2>(lut3, B, lane4); n[k][3] = hm_pair3<3>(lut3, B, lane4);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        hm_mma(o[0][j], __byte_perm(n[0][j], n[1][j], 0x5410), __byte_perm(n[0][j], n[1][j], 0x7632),
+               __byte_perm(n[2][j], n[3][j], 0x5410), __byte_perm(n[2][j], n[3][j], 0x7632), pbA[0], pbB[0]);
+    }
+#pragma unroll
+    for (int sgn = 0; sgn < 2; ++sgn) {   // segments 1 and 3
+      const int sg = 1 + 2 * sgn;
+      uint32_t n[4][4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t ro = (k & 1) * 64 + (k >> 1) * 512;
+        const uint32_t v = hm_lds8(buf + (sgn ? oVs1 : oVs0) + ro);
+        const uint2 hi = hm_signs(luts, v << 4, lane8), lo = hm_signs(luts, v << 8, lane8);
+        n[k][0] = hi.x; n[k][1] = hi.y; n[k][2] = lo.x; n[k][3] = lo.y;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        hm_mma(o[sg][j], __byte_perm(n[0][j], n[1][j], 0x5410), __byte_perm(n[0][j], n[1][j], 0x7632),
+               __byte_perm(n[2][j], n[3][j], 0x5410), __byte_perm(n[2][j], n[3][j], 0x7632), pbA[sg], pbB[sg]);
+    }
+    {   // segment 2
+      uint32_t n[4][4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t ro = (k & 1) * 64 + (k >> 1) * 512;
+        const uint32_t v = hm_lds16(buf + oVc1 + ro);
+        const uint2 q0 = hm_quad2<0>(lut2, v, lane8), q1 = hm_quad2<1>(lut2, v, lane8);
+        n[k][0] = q0.x; n[k][1] = q0.y; n[k][2] = q1.x; n[k][3] = q1.y;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        hm_mma(o[2][j], __byte_perm(n[0][j], n[1][j], 0x5410), __byte_perm(n[0][j], n[1][j], 0x7632),
+               __byte_perm(n[2][j], n[3][j], 0x5410), __byte_perm(n[2][j], n[3][j], 0x7632), pbA[2], pbB[2]);
+    }
+    __syncwarp();   // every lane is done with this buffer before the copy after next lands in it
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+
+  // ---- this warp's partial ----
+#pragma unroll
+  for (int offs = 4; offs < 32; offs <<= 1) {
+    l0 += __shfl_xor_sync(0xffffffffu, l0, offs);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, offs);
+  }
+  const int part = split * HA_WARPS + warp;
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const int qg = 2 * t + e;
+    if (qg >= G) continue;
+    const int64_t row = (int64_t)seq * a.num_q_heads + h * G + qg;
+    float* pa = a.part_acc + (row * a.num_parts + part) * 256;
+#pragma unroll
+    for (int sg = 0; sg < 4; ++sg)
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        *reinterpret_cast<float2*>(pa + 64 * sg + 8 * g + 2 * j) = make_float2(o[sg][j][e], o[sg][j][2 + e]);
+    if (g == 0) {
+      a.part_ml[(row * a.num_parts + part) * 2] = e ? m1 : m0;
+      a.part_ml[(row * a.num_parts + part) * 2 + 1] = e ? l1 : l0;
+    }
+  }
+}
+
 // q'[s][qh] = [FWHT(q_g0.s_had0)/8 | kappa0 FWHT(q_g0.s_qjl0)/8 | same for g1] * premul.
 // One warp per (seq, q head); 64-point transforms via shared memory.
 __device__ __forceinline__ void fwht64_smem(float* w, int lane) {
@@ -808,8 +1190,20 @@ AKV_EXPORT int akv_hybrid_paged_attn(const akv_hybrid_attn_params* p) {
     a.num_blocks = p->num_blocks; a.blocks_per_split = bps; a.num_parts = parts;
     a.qprime = qprime; a.centroids = t.centroids; a.part_acc = part_acc; a.part_ml = part_ml;
     dim3 grid(parts / HA_WARPS, p->num_kv_heads, p->num_seqs);
-    hybrid_attn_kernel<<<grid, HA_WARPS * 32, 0, st>>>(a);
-    if (int rc = check_launch("hybrid_attn_kernel")) return rc;
+    // tensor-core kernel: 16-token tiles, GQA groups of up to 8, records readable in 16-byte pieces
+    static const bool force_scalar = getenv("AKV_HYBRID_SCALAR") != nullptr;
+    const bool aligned16 = ((reinterpret_cast<uintptr_t>(p->k_cache) | reinterpret_cast<uintptr_t>(p->v_cache) |
+                             p->k_stride_blk | p->k_stride_pos | p->k_stride_head | p->v_stride_blk |
+                             p->v_stride_pos | p->v_stride_head) & 15) == 0;
+    if (!force_scalar && aligned16 && p->block_size % 16 == 0 && p->num_q_heads / p->num_kv_heads <= 8) {
+      cudaError_t e = cudaFuncSetAttribute(hybrid_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, HM_SMEM);
+      if (e != cudaSuccess) return fail((int)e, "hybrid attention: smem attribute: %s", cudaGetErrorString(e));
+      hybrid_attn_mma_kernel<<<grid, HA_WARPS * 32, HM_SMEM, st>>>(a);
+      if (int rc = check_launch("hybrid_attn_mma_kernel")) return rc;
+    } else {
+      hybrid_attn_kernel<<<grid, HA_WARPS * 32, 0, st>>>(a);
+      if (int rc = check_launch("hybrid_attn_kernel")) return rc;
+    }
   }
   hybrid_merge_kernel<<<rows, 32, 0, st>>>(part_acc, part_ml, p->max_blocks_per_seq > 0 ? parts : 0,
                                            p->context_lens, p->cl_dtype, bps * p->block_size, p->num_q_heads, t,
