@@ -1007,32 +1007,82 @@ hybrid_qprime_kernel(const void* __restrict__ q, int q_dtype, int64_t q_ss, int6
 }
 
 // LSE merge of the 256-coordinate partials and the inverse transforms of the epilogue.
-__global__ void __launch_bounds__(32)
+// One CTA of 256 threads per (sequence, query head): thread c owns coordinate c, so every
+// read of a partial is one coalesced 1 KB row; the weights 2^(m_p - M) are computed once
+// per part (256 parts at a time) and shared.
+__device__ __forceinline__ float block_reduce_256(float v, bool is_max, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float u = __shfl_xor_sync(0xffffffffu, v, o);
+    v = is_max ? fmaxf(v, u) : v + u;
+  }
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = scratch[0];
+#pragma unroll
+  for (int k = 1; k < 8; ++k) r = is_max ? fmaxf(r, scratch[k]) : r + scratch[k];
+  return r;
+}
+
+__global__ void __launch_bounds__(256)
 hybrid_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml, int num_parts,
                     const void* context_lens, int cl_dtype, int tokens_per_split, int num_q_heads,
                     HybridTables t, void* __restrict__ out, int out_dtype, int64_t out_ss, int64_t out_sh) {
   __shared__ float w[4][64];
-  const int row = blockIdx.x, seq = row / num_q_heads, qh = row % num_q_heads, lane = threadIdx.x;
+  __shared__ float wgt[256];
+  __shared__ float scratch[8];
+  const int row = blockIdx.x, seq = row / num_q_heads, qh = row % num_q_heads, tid = threadIdx.x;
   const int64_t ctx = load_index(context_lens, cl_dtype, seq);
   int64_t nv = (ctx + tokens_per_split - 1) / tokens_per_split * HA_WARPS;
   const int np = (int)(nv < num_parts ? nv : num_parts);
   const float* ml = part_ml + (int64_t)row * num_parts * 2;
-  float M = -CUDART_INF_F, L = 0.f;
-  for (int p = 0; p < np; ++p) if (ml[2 * p + 1] > 0.f) M = fmaxf(M, ml[2 * p]);
-  for (int p = 0; p < np; ++p) if (ml[2 * p + 1] > 0.f) L += ml[2 * p + 1] * exp2f(ml[2 * p] - M);
-  const float inv = L > 0.f ? 1.f / L : 0.f;
-  for (int c = lane; c < 256; c += 32) {
-    float o = 0.f;
-    for (int p = 0; p < np; ++p)
-      if (ml[2 * p + 1] > 0.f) o += part_acc[((int64_t)row * num_parts + p) * 256 + c] * exp2f(ml[2 * p] - M);
-    w[c >> 6][c & 63] = o * inv;
+  float mx = -CUDART_INF_F;
+  for (int p = tid; p < np; p += 256) if (ml[2 * p + 1] > 0.f) mx = fmaxf(mx, ml[2 * p]);
+  const float M = block_reduce_256(mx, true, scratch);
+  float ls = 0.f, acc = 0.f;
+  const float* pa = part_acc + (int64_t)row * num_parts * 256 + tid;
+  for (int p0 = 0; p0 < np; p0 += 256) {
+    __syncthreads();
+    {
+      const int p = p0 + tid;
+      float wv = 0.f;
+      if (p < np && ml[2 * p + 1] > 0.f) { wv = exp2f(ml[2 * p] - M); ls += ml[2 * p + 1] * wv; }
+      wgt[tid] = wv;
+    }
+    __syncthreads();
+    const int cnt = np - p0 < 256 ? np - p0 : 256;
+    int q = 0;
+    for (; q + 8 <= cnt; q += 8) {
+      float v[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] = pa[(int64_t)(p0 + q + k) * 256];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc = __fmaf_rn(v[k], wgt[q + k], acc);   // weight 0: part never written
+    }
+    for (; q < cnt; ++q) if (wgt[q] > 0.f) acc = __fmaf_rn(pa[(int64_t)(p0 + q) * 256], wgt[q], acc);
   }
-  for (int s = 0; s < 4; ++s) fwht64_smem(w[s], lane);
-  for (int k = lane; k < 64; k += 32) {
-    const float o0 = (w[0][k] * t.had_signs[k] + w[1][k] * t.qjl_scale0 * t.qjl_signs[k]) * 0.125f;
-    const float o1 = (w[2][k] * t.had_signs[64 + k] + w[3][k] * t.qjl_scale1 * t.qjl_signs[64 + k]) * 0.125f;
-    store_from_float(out, out_dtype, seq * out_ss + qh * out_sh + t.group_index[k], o0);
-    store_from_float(out, out_dtype, seq * out_ss + qh * out_sh + t.group_index[64 + k], o1);
+  const float L = block_reduce_256(ls, false, scratch);
+  const float inv = L > 0.f ? 1.f / L : 0.f;
+  w[tid >> 6][tid & 63] = acc * inv;
+  // four 64-point transforms: 128 butterflies per stage, one per thread of the first half
+  for (int h = 1; h < 64; h <<= 1) {
+    __syncthreads();
+    if (tid < 128) {
+      const int sg = tid >> 5, l = tid & 31;
+      const int j = ((l & ~(h - 1)) << 1) | (l & (h - 1));
+      const float a = w[sg][j], b = w[sg][j + h];
+      w[sg][j] = a + b;
+      w[sg][j + h] = a - b;
+    }
+  }
+  __syncthreads();
+  if (tid < 128) {
+    const int grp = tid >> 6, k = tid & 63;
+    const float o = (w[2 * grp][k] * t.had_signs[64 * grp + k] +
+                     w[2 * grp + 1][k] * (grp ? t.qjl_scale1 : t.qjl_scale0) * t.qjl_signs[64 * grp + k]) * 0.125f;
+    store_from_float(out, out_dtype, seq * out_ss + qh * out_sh + t.group_index[64 * grp + k], o);
   }
 }
 
@@ -1205,7 +1255,7 @@ AKV_EXPORT int akv_hybrid_paged_attn(const akv_hybrid_attn_params* p) {
       if (int rc = check_launch("hybrid_attn_kernel")) return rc;
     }
   }
-  hybrid_merge_kernel<<<rows, 32, 0, st>>>(part_acc, part_ml, p->max_blocks_per_seq > 0 ? parts : 0,
+  hybrid_merge_kernel<<<rows, 256, 0, st>>>(part_acc, part_ml, p->max_blocks_per_seq > 0 ? parts : 0,
                                            p->context_lens, p->cl_dtype, bps * p->block_size, p->num_q_heads, t,
                                            p->out, p->out_dtype, p->out_stride_seq, p->out_stride_head);
   return check_launch("hybrid_merge_kernel");
