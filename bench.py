@@ -565,10 +565,10 @@ def main():
                     "api": "torch.ops.tq.decode_step (encode new token + attention), host pinned buffers"},
             "gpu_launches": 3 * args.steps,
             # traffic: dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this
-            # workload, from the ncu capture summarised in profiles/tq4_attn_pipe_kernel_config1.md
+            # workload, from the ncu capture summarised in profiles/tq4_attn_streamk_kernel_config1.md
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES if world == 1 else None,
-                         "algorithmic_bytes": kv_bytes, "kernel": "tq4_attn_pipe_kernel",
+                         "algorithmic_bytes": kv_bytes, "kernel": "tq4_attn_streamk_kernel",
                          "kernel_ms": kernel_ms, "peak_source": peak_src,
                          "frac_of_8TBs_nominal": achieved / 8000.0},
             "clocks": clocks,
