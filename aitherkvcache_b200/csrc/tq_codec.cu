@@ -744,6 +744,10 @@ AKV_EXPORT int akv_tq_decode(const uint8_t* packed, int64_t packed_row_stride, c
   if (out_dtype < AKV_F16 || out_dtype > AKV_F32) return fail(AKV_ERR_ARG, "bad out_dtype %d", out_dtype);
   cudaStream_t st = (cudaStream_t)stream;
   const int D = head_dim;
+  static const bool no_tc = getenv("AKV_NO_TC_DECODE") != nullptr;
+  if (D == 128 && n_rows >= 2048 && !no_tc && (packed_row_stride & 3) == 0 &&
+      (reinterpret_cast<uintptr_t>(packed) & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0)
+    return launch_decode_tc(packed, packed_row_stride, norms, n_rows, bits, rotation, centroids, out, out_dtype, st);
 #define AKV_DEC(DD, BB)            \
   if (D == DD && bits == BB)       \
     return launch_decode_tiled<DD, BB>(packed, packed_row_stride, norms, n_rows, rotation, centroids, out, out_dtype, st);

@@ -1,0 +1,274 @@
+// TurboQuant decode on the 5th-generation tensor cores (tcgen05 / TMEM), head_dim 128.
+//
+// Same operation as tq_decode_tiled_kernel in tq_codec.cu (reference: quantizer.py:170-212):
+//   x_hat[j] = norm * sum_i centroid[code_i] * R[i][j],   rounded to the output type.
+// A tile of 128 vectors is one 128 x 128 x 128 GEMM.  Centroids and R are float32, so both are
+// split into two fp16 terms of 1024 x the value (c = c1 + c2, R = R1 + R2; the factor keeps
+// the second terms out of fp16's subnormal range) and the product is accumulated as
+// c1 R1 + c1 R2 + c2 R1 in one float32 TMEM accumulator (the dropped c2 R2 term is 2^-22 of the
+// result); the factor 2^-20 is folded into the norm.  Results agree with the float32 FMA kernel
+// to a few float32 ulps, i.e. the fp16 outputs differ only where a value sits on a rounding tie.
+//
+// One persistent CTA of 16 warps per SM.  Thread (row, q) owns the 32 codes 32q..32q+31 of a row:
+// it prefetches their 4*BITS bytes two tiles ahead into registers, turns them into the two fp16
+// operand rows (per-lane table: code -> (c1, c2)) in the 128-byte-swizzled K-major layout, and
+// the MMAs of tile t run while the warps unpack tile t+1 and write out tile t-1 from the other
+// half of tensor memory (tcgen05.ld: one thread per vector, 32 consecutive outputs = 64 bytes).
+// The wait on the MMA barrier is bounded; a wait that gives up sets g_tc_decode_status and the
+// CTA leaves after releasing its tensor memory.
+#include "tq_rowmap.cuh"
+#include "umma.cuh"
+
+namespace akv {
+namespace {
+
+__device__ int g_tc_decode_status;   // 1: a wait on the MMA barrier gave up
+
+constexpr int DT_TERMS_R = 0;                          // R1, R2: 2 operands
+constexpr int DT_ABUF = 2 * TC_OPER_BYTES;             // 2 stages x (c1, c2) operands
+constexpr int DT_LUT = DT_ABUF + 4 * TC_OPER_BYTES;    // 16 entries x 128 B
+constexpr int DT_MISC = DT_LUT + 2048;                 // mbarriers, TMEM slot
+constexpr int DT_SMEM = DT_MISC + 64 + 1024;           // + slack for the 1024-byte alignment
+
+// Code e (0..31) of a thread's MSB-first stream held as big-endian words B[]; returns the byte
+// address of the code's table entry for this lane (entry stride 128 B).
+template <int BITS, int E>
+__device__ __forceinline__ uint32_t entry_addr(const uint32_t* B, uint32_t lut_lane) {
+  constexpr int pos = E * BITS, w = pos >> 5, off = pos & 31, sh = 32 - BITS - off;
+  constexpr uint32_t mask = ((1u << BITS) - 1u) << 7;
+  uint32_t x;
+  if constexpr (sh >= 7) x = B[w] >> (sh - 7);
+  else if constexpr (sh >= 0) x = B[w] << (7 - sh);
+  else x = __funnelshift_l(B[w + 1], B[w], 7 + BITS + off - 32);   // field straddles two words
+  return lut_lane + (x & mask);
+}
+
+template <int BITS, int C>
+__device__ __forceinline__ void unpack_chunk(const uint32_t* B, uint32_t lut_lane, uint4& c1, uint4& c2) {
+  uint32_t r[8];
+  r[0] = lds_u32(entry_addr<BITS, 8 * C + 0>(B, lut_lane)); r[1] = lds_u32(entry_addr<BITS, 8 * C + 1>(B, lut_lane));
+  r[2] = lds_u32(entry_addr<BITS, 8 * C + 2>(B, lut_lane)); r[3] = lds_u32(entry_addr<BITS, 8 * C + 3>(B, lut_lane));
+  r[4] = lds_u32(entry_addr<BITS, 8 * C + 4>(B, lut_lane)); r[5] = lds_u32(entry_addr<BITS, 8 * C + 5>(B, lut_lane));
+  r[6] = lds_u32(entry_addr<BITS, 8 * C + 6>(B, lut_lane)); r[7] = lds_u32(entry_addr<BITS, 8 * C + 7>(B, lut_lane));
+  c1 = make_uint4(__byte_perm(r[0], r[1], 0x5410), __byte_perm(r[2], r[3], 0x5410),
+                  __byte_perm(r[4], r[5], 0x5410), __byte_perm(r[6], r[7], 0x5410));
+  c2 = make_uint4(__byte_perm(r[0], r[1], 0x7632), __byte_perm(r[2], r[3], 0x7632),
+                  __byte_perm(r[4], r[5], 0x7632), __byte_perm(r[6], r[7], 0x7632));
+}
+
+__device__ __forceinline__ void sts128(uint32_t addr, const uint4& v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" :: "r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+template <int BITS>
+__global__ void __launch_bounds__(512, 1)
+tq_decode_tc_kernel(const uint8_t* __restrict__ packed, int64_t p_stride_row, const float* __restrict__ norms,
+                    int64_t n_rows, const float* __restrict__ rot, const float* __restrict__ centroids,
+                    void* __restrict__ out, int out_dtype) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_s = smem_u32(smem_raw);
+  const uint32_t base_s = (raw_s + 1023u) & ~1023u;
+  uint8_t* base = smem_raw + (base_s - raw_s);
+  uint8_t* rterms = base + DT_TERMS_R;
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(base + DT_MISC);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mbar + 2);
+  const uint32_t abuf_s = base_s + DT_ABUF, lut_s = base_s + DT_LUT, mbar_s = base_s + DT_MISC;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  // ---------------- one-time setup ----------------
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(mbar_s));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(mbar_s + 8));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;"
+                 :: "r"(smem_u32(tmem_slot)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  // B operand: row n = output coordinate j, K index i, value 1024 R[i][j] in two fp16 terms.  rot is
+  // read with j fastest (coalesced) into a float32 staging copy (the A buffers, not yet in use); the
+  // XOR on the staging column keeps both passes free of bank conflicts.
+  {
+    float* stg = reinterpret_cast<float*>(base + DT_ABUF);
+    for (int e = tid; e < 128 * 128; e += 512) {
+      const int i = e >> 7, j = e & 127;
+      stg[i * 128 + (j ^ (i & 31))] = rot[e];
+    }
+    __syncthreads();
+    for (int e = tid; e < 128 * 128; e += 512) {
+      const int j = e >> 7, i = e & 127;
+      const float r = stg[i * 128 + (j ^ (i & 31))] * 1024.0f;
+      const uint32_t off = tc_operand_offset(j, i);
+      const __half t1 = __float2half_rn(r);
+      *reinterpret_cast<__half*>(rterms + off) = t1;
+      *reinterpret_cast<__half*>(rterms + TC_OPER_BYTES + off) = __float2half_rn(r - __half2float(t1));
+    }
+  }
+  // table: code -> half2(c1, c2), one copy per lane
+  for (int e = tid; e < (1 << BITS) * 32; e += 512) {
+    const float c = centroids[e >> 5] * 1024.0f;
+    const __half h1 = __float2half_rn(c), h2 = __float2half_rn(c - __half2float(h1));
+    *reinterpret_cast<uint32_t*>(base + DT_LUT + (e >> 5) * 128 + (e & 31) * 4) =
+        (uint32_t)__half_as_ushort(h1) | ((uint32_t)__half_as_ushort(h2) << 16);
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  // instruction descriptor: D = f32, A/B = f16, both K-major, N = 128, M = 128
+  constexpr uint32_t IDESC = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+
+  const int64_t num_tiles = (n_rows + 127) >> 7;
+  const int n_my = (int)((num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
+  auto tile_row0 = [&](int t) { return ((int64_t)blockIdx.x + (int64_t)t * gridDim.x) * 128; };
+
+  // unpack role: thread (row, q) owns codes 32q .. 32q+31 of a row = 4*BITS bytes
+  const int urow = tid >> 2, uq = tid & 3;
+  const uint32_t lut_lane = lut_s + lane * 4;
+  // the four 16-byte chunks of the operand row this thread writes: K = 32 uq + 8 c
+  const uint32_t u_off = (uint32_t)((uq >> 1) * TC_HALF_BYTES + urow * 128);
+  const uint32_t u_chunk0 = (uint32_t)((4 * uq) & 7), u_swz = (uint32_t)(urow & 7);
+  // epilogue role: thread = row, 32 consecutive outputs
+  const int w4 = warp & 3, colq = warp >> 2, erow = w4 * 32 + lane;
+
+  uint32_t cw[BITS];      // packed bytes of the tile to unpack next
+  auto prefetch = [&](int t) {
+    const int64_t n = tile_row0(t) + urow;
+#pragma unroll
+    for (int k = 0; k < BITS; ++k) cw[k] = 0u;
+    if (t < n_my && n < n_rows) {
+      const uint32_t* src = reinterpret_cast<const uint32_t*>(packed + n * p_stride_row + 4 * BITS * uq);
+#pragma unroll
+      for (int k = 0; k < BITS; ++k) cw[k] = __ldg(src + k);
+    }
+  };
+  auto unpack = [&](int t) {      // registers cw -> operand buffers of stage t & 1
+    uint32_t B[BITS];
+#pragma unroll
+    for (int k = 0; k < BITS; ++k) B[k] = bswap32(cw[k]);
+    const uint32_t a1 = abuf_s + (uint32_t)(t & 1) * 2 * TC_OPER_BYTES + u_off, a2 = a1 + TC_OPER_BYTES;
+    uint4 c1, c2;
+    unpack_chunk<BITS, 0>(B, lut_lane, c1, c2);
+    sts128(a1 + (((u_chunk0 + 0) ^ u_swz) << 4), c1); sts128(a2 + (((u_chunk0 + 0) ^ u_swz) << 4), c2);
+    unpack_chunk<BITS, 1>(B, lut_lane, c1, c2);
+    sts128(a1 + (((u_chunk0 + 1) ^ u_swz) << 4), c1); sts128(a2 + (((u_chunk0 + 1) ^ u_swz) << 4), c2);
+    unpack_chunk<BITS, 2>(B, lut_lane, c1, c2);
+    sts128(a1 + (((u_chunk0 + 2) ^ u_swz) << 4), c1); sts128(a2 + (((u_chunk0 + 2) ^ u_swz) << 4), c2);
+    unpack_chunk<BITS, 3>(B, lut_lane, c1, c2);
+    sts128(a1 + (((u_chunk0 + 3) ^ u_swz) << 4), c1); sts128(a2 + (((u_chunk0 + 3) ^ u_swz) << 4), c2);
+  };
+
+  prefetch(0);
+  if (n_my > 0) unpack(0);
+  prefetch(1);
+  float nrm_cur = 0.f;
+
+  int gave_up = 0;
+  for (int t = 0; t <= n_my; ++t) {
+    const bool have = t < n_my;
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // this thread's operand stores
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    if (__syncthreads_or(gave_up)) { gave_up = 1; break; }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+    // ---- tile t: c1 R1 + c1 R2 + c2 R1, issued by one thread ----
+    if (have && tid == 0) {
+      const uint32_t a_s = abuf_s + (uint32_t)(t & 1) * 2 * TC_OPER_BYTES;
+      const uint32_t d0 = tmem_base + (uint32_t)(t & 1) * 128;
+#pragma unroll
+      for (int pass = 0; pass < 3; ++pass) {
+        const uint32_t ao = pass == 2 ? TC_OPER_BYTES : 0u, bo = pass == 1 ? TC_OPER_BYTES : 0u;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t koff = (uint32_t)((kk >> 2) * TC_HALF_BYTES + (kk & 3) * 32);
+          umma_f16(d0, umma_desc(a_s + ao + koff), umma_desc(base_s + DT_TERMS_R + bo + koff), IDESC,
+                   (uint32_t)((pass | kk) != 0));
+        }
+      }
+      umma_commit(mbar_s + 8u * (uint32_t)(t & 1));
+    }
+    float nrm_next = 0.f;
+    if (have) {
+      const int64_t n = tile_row0(t) + erow;
+      if (n < n_rows) nrm_next = __ldg(norms + n);
+    }
+    // ---- tile t-1: wait for its MMAs (frees its operand stage, fills its accumulator) ----
+    if (t >= 1) {
+      if (!mbar_wait(mbar_s + 8u * (uint32_t)((t - 1) & 1), (uint32_t)(((t - 1) >> 1) & 1))) gave_up = 1;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    }
+    if (t + 1 < n_my && !gave_up) unpack(t + 1);
+    prefetch(t + 2);
+    // ---- tile t-1: scale by the norm, convert, store ----
+    if (t >= 1 && !gave_up) {
+      uint32_t v[32];
+      tmem_ld32(tmem_base + ((uint32_t)(w4 * 32) << 16) + (uint32_t)(((t - 1) & 1) * 128 + colq * 32), v);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      const int64_t n = tile_row0(t - 1) + erow;
+      if (n < n_rows) {
+        const float sc = nrm_cur * (1.0f / 1048576.0f);
+        if (out_dtype == AKV_F32) {
+          float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + n * 128 + colq * 32);
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            dst[k] = make_float4(__uint_as_float(v[4 * k]) * sc, __uint_as_float(v[4 * k + 1]) * sc,
+                                 __uint_as_float(v[4 * k + 2]) * sc, __uint_as_float(v[4 * k + 3]) * sc);
+        } else {
+          uint32_t h[16];
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {
+            const float lo = __uint_as_float(v[2 * k]) * sc, hi = __uint_as_float(v[2 * k + 1]) * sc;
+            if (out_dtype == AKV_F16) {
+              __half2 p = __floats2half2_rn(lo, hi);
+              h[k] = *reinterpret_cast<uint32_t*>(&p);
+            } else {
+              __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+              h[k] = *reinterpret_cast<uint32_t*>(&p);
+            }
+          }
+          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out) + n * 128 + colq * 32);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) dst[k] = make_uint4(h[4 * k], h[4 * k + 1], h[4 * k + 2], h[4 * k + 3]);
+        }
+      }
+    }
+    nrm_cur = nrm_next;
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" :: "r"(tmem_base) : "memory");
+  }
+  if (gave_up && tid == 0) g_tc_decode_status = 1;
+}
+
+template <int BITS>
+int launch_dtc(const uint8_t* packed, int64_t ps, const float* norms, int64_t n_rows, const float* rot,
+               const float* cent, void* out, int out_dtype, cudaStream_t st) {
+  auto kern = tq_decode_tc_kernel<BITS>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DT_SMEM);
+  if (e != cudaSuccess) return fail((int)e, "decode: smem attribute: %s", cudaGetErrorString(e));
+  int64_t tiles = (n_rows + 127) / 128;
+  int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+  kern<<<grid, 512, DT_SMEM, st>>>(packed, ps, norms, n_rows, rot, cent, out, out_dtype);
+  return check_launch("tq_decode_tc_kernel");
+}
+
+}  // namespace
+
+int launch_decode_tc(const uint8_t* packed, int64_t packed_row_stride, const float* norms, int64_t n_rows,
+                     int bits, const float* rot, const float* centroids, void* out, int out_dtype,
+                     cudaStream_t st) {
+  if (bits == 4) return launch_dtc<4>(packed, packed_row_stride, norms, n_rows, rot, centroids, out, out_dtype, st);
+  if (bits == 3) return launch_dtc<3>(packed, packed_row_stride, norms, n_rows, rot, centroids, out, out_dtype, st);
+  if (bits == 2) return launch_dtc<2>(packed, packed_row_stride, norms, n_rows, rot, centroids, out, out_dtype, st);
+  return fail(AKV_ERR_ARG, "launch_decode_tc: bits %d", bits);
+}
+
+}  // namespace akv

@@ -66,4 +66,9 @@ __device__ __forceinline__ RowAddr map_row(const RowMap& m, int64_t n) {
 int launch_encode_tc(const RowMap& m, int64_t n_rows, int bits, bool bf16, const float* rot_t,
                      const float* boundaries, cudaStream_t st);
 
+// Tensor-core decode for head_dim 128 (tq_decode_tc.cu).
+int launch_decode_tc(const uint8_t* packed, int64_t packed_row_stride, const float* norms, int64_t n_rows,
+                     int bits, const float* rot, const float* centroids, void* out, int out_dtype,
+                     cudaStream_t st);
+
 }  // namespace akv

@@ -101,6 +101,37 @@ def test_decode_golden(d, bits):
     assert (ulp != 0).mean() < 2e-3
 
 
+@pytest.mark.parametrize("bits", BITS)
+@pytest.mark.parametrize("out_dtype", (torch.float16, torch.bfloat16, torch.float32))
+def test_decode_large_batch_vs_oracle(bits, out_dtype):
+    """Batches of 2048+ vectors at head_dim 128 take the tensor-core decode kernel: same
+    tolerance as the small-batch kernel, ragged tail, and agreement with that kernel."""
+    g = load_golden(f"tq_d128_b{bits}.npz")
+    tq = _tq(128, bits, g, dtype=out_dtype)
+    n = 4096 + 77
+    x = torch.randn(n, 128, generator=torch.Generator().manual_seed(31 + bits)).half()
+    x[3] = 0.0
+    x[4] *= 50.0
+    packed, norms = otq.encode(x.numpy(), g["rotation"], g["boundaries"], bits)
+    dec = tq.decode(torch.from_numpy(packed).cuda(), torch.from_numpy(norms).cuda())
+    assert dec.dtype == out_dtype and dec.shape == (n, 128)
+    ref = otq.decode_f32(packed, norms, g["rotation"], g["centroids"], bits)
+    small = tq.decode(torch.from_numpy(packed[:1000]).cuda(), torch.from_numpy(norms[:1000]).cuda())
+    if out_dtype == torch.float32:
+        err = np.abs(dec.cpu().numpy() - ref)
+        assert (err <= 2e-6 * np.maximum(norms[:, None], 1e-30) + 1e-30).all()
+        assert np.abs(small.cpu().numpy() - dec[:1000].cpu().numpy()).max() <= 2e-6 * norms[:1000].max()
+    else:
+        want = torch.from_numpy(ref).to(out_dtype)
+        got = dec.cpu()
+        tol = 2.0 ** (-10 if out_dtype == torch.float16 else -7)       # one ulp of the output type
+        diff = (got.float() - want.float()).abs().numpy()
+        assert (diff <= tol * np.abs(ref) + 1e-6 * norms[:, None]).all()
+        assert (got != want).float().mean().item() < 2e-3
+        assert (small.cpu() != got[:1000]).float().mean().item() < 5e-3   # two roundings of near-ties
+    assert (dec[3] == 0).all()
+
+
 @pytest.mark.parametrize("d,bits", [(256, 4), (32, 3), (16, 2), (512, 4)])
 def test_generic_head_dims_vs_oracle(d, bits):
     tq = _tq(d, bits)
