@@ -72,6 +72,7 @@ __device__ __forceinline__ int64_t phys_block(const AttnArgs& a, int seq, int bl
 struct StreamKPlanArgs {
   const void* context_lens; int cl_dtype; int num_seqs; int block_size; int grid;
   int* sk;    // nullptr: no plan wanted
+  int parts_per_cta;   // partials a CTA writes per (sequence, q head): warps per KV head
 };
 
 __device__ void streamk_plan(const StreamKPlanArgs& p) {
@@ -102,7 +103,7 @@ __device__ void streamk_plan(const StreamKPlanArgs& p) {
     const int cnt = (p.sk[3 * S + 2 + s] + 1) / 2;
     p.sk[s] = run;
     p.sk[S + 2 + s] = cnt > 0 ? run / chunk : 0;
-    p.sk[2 * S + 2 + s] = cnt > 0 ? 2 * ((run + cnt - 1) / chunk - run / chunk + 1) : 0;
+    p.sk[2 * S + 2 + s] = cnt > 0 ? p.parts_per_cta * ((run + cnt - 1) / chunk - run / chunk + 1) : 0;
     run += cnt;
   }
   if (tid == 0) { p.sk[S] = T; p.sk[S + 1] = chunk; }
@@ -1004,8 +1005,12 @@ __device__ __forceinline__ void cp_async16_s(uint32_t smem_dst, const void* gsrc
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" :: "r"(smem_dst), "l"(gsrc));
 }
 
-__global__ void __launch_bounds__(512, 1)
+// WPH = warps per KV head: 2 -> 16 warps, warp (head, j) takes block j of every stage and writes its own
+// partial; 1 -> 8 warps with twice the registers, a warp takes both blocks of its head's stage.
+template <int WPH>
+__global__ void __launch_bounds__(256 * WPH, 1)
 tq4_attn_streamk_kernel(AttnArgs a) {
+  constexpr int NT = 256 * WPH;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ float s_cent[16];
   const uint32_t dyn0 = (uint32_t)__cvta_generic_to_shared(smem);
@@ -1018,8 +1023,8 @@ tq4_attn_streamk_kernel(AttnArgs a) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int S = a.num_seqs;
-  for (int i = tid; i < S + 2; i += 512) s_P[i] = a.sk[i];
-  for (int i = tid; i < S; i += 512) s_nb[i] = a.sk[3 * S + 2 + i];
+  for (int i = tid; i < S + 2; i += NT) s_P[i] = a.sk[i];
+  for (int i = tid; i < S; i += NT) s_nb[i] = a.sk[3 * S + 2 + i];
   if (tid < 16) s_cent[tid] = a.centroids[tid];
   __syncthreads();
   const int T = s_P[S], chunk = s_P[S + 1];
@@ -1044,11 +1049,15 @@ tq4_attn_streamk_kernel(AttnArgs a) {
   }
 
   // ---- producer ----
+  // thread -> (token, 16-byte piece) of a block; with 8 warps a thread copies tokens c_tok and c_tok + 8
+  // (same swizzle: token parity and (token >> 1) & 3 are unchanged by +8)
+  constexpr int TOK_PASSES = 2 / WPH;
   const int c_tok = tid >> 5, c_r = tid & 31;
   const int k_dst = c_tok * 512 + (((c_r >> 2) ^ (c_tok & 1)) << 6) + (c_r & 3) * 16;
   const int v_dst = c_tok * 512 + (((c_r >> 1) ^ ((c_tok >> 1) & 3)) << 5) + (c_r & 1) * 16;
   const int64_t k_src = (int64_t)c_tok * a.kp_sp + hg * 512 + c_r * 16;
   const int64_t v_src = (int64_t)c_tok * a.vp_sp + hg * 512 + c_r * 16;
+  const int64_t k_step = 8 * a.kp_sp, v_step = 8 * a.vp_sp;
   // 32-bit strides (checked on the host) keep the address arithmetic to one wide multiply-add
   const int kp_sb = (int)a.kp_sb, vp_sb = (int)a.vp_sb, kn_sb = (int)a.kn_sb, vn_sb = (int)a.vn_sb;
   const bool bt64 = a.bt_dtype == AKV_I64;
@@ -1082,11 +1091,14 @@ tq4_attn_streamk_kernel(AttnArgs a) {
     pb0 = min(max(pb0, 0), nblocks - 1);
     pb1 = min(max(pb1, 0), nblocks - 1);
     const uint32_t st = stage_addr(slot);
-    cp_async16_s(st + k_dst, a.k_packed + ((int64_t)pb0 * kp_sb + k_src));
-    cp_async16_s(st + 16384 + v_dst, a.v_packed + ((int64_t)pb0 * vp_sb + v_src));
-    if (has1) {
-      cp_async16_s(st + 8192 + k_dst, a.k_packed + ((int64_t)pb1 * kp_sb + k_src));
-      cp_async16_s(st + 16384 + 8192 + v_dst, a.v_packed + ((int64_t)pb1 * vp_sb + v_src));
+#pragma unroll
+    for (int tp = 0; tp < TOK_PASSES; ++tp) {
+      cp_async16_s(st + k_dst + tp * 4096, a.k_packed + ((int64_t)pb0 * kp_sb + k_src + tp * k_step));
+      cp_async16_s(st + 16384 + v_dst + tp * 4096, a.v_packed + ((int64_t)pb0 * vp_sb + v_src + tp * v_step));
+      if (has1) {
+        cp_async16_s(st + 8192 + k_dst + tp * 4096, a.k_packed + ((int64_t)pb1 * kp_sb + k_src + tp * k_step));
+        cp_async16_s(st + 16384 + 8192 + v_dst + tp * 4096, a.v_packed + ((int64_t)pb1 * vp_sb + v_src + tp * v_step));
+      }
     }
     if (tid < 128) {
       const int which = tid >> 5, ch = tid & 31, b2 = which & 1;
@@ -1109,27 +1121,26 @@ tq4_attn_streamk_kernel(AttnArgs a) {
     if (ss < n_it) issue(ss);
     else asm volatile("cp.async.commit_group;\n" ::);
   }
-  for (int i = tid; i < 256 * 32; i += 512) {
+  for (int i = tid; i < 256 * 32; i += NT) {
     const int e = i >> 5, l = i & 31;
     const uint32_t v = pack_half2(s_cent[e >> 4], s_cent[e & 15]);
     asm volatile("st.shared.u32 [%0], %1;\n" :: "r"(SK_LUT + e * LUT_STRIDE + l * 4), "r"(v));
   }
 
   // ---- consumer ----
-  const int hl = warp & 7, wj = warp >> 3;
+  const int hl = warp & 7, wj0 = (WPH == 2) ? (warp >> 3) : 0;
   const int h = hg * 8 + hl;
   const int G = a.num_q_heads / a.num_kv_heads;
   const uint32_t lanebase = SK_LUT | (lane * 4);   // upper address bytes ride along in the PRMT
   constexpr lut_t lut_s = 0;
-  const int kA_off = wj * 8192 + g * 512 + ((hl ^ (g & 1)) << 6) + 16 * t;
+  const int kA_off = wj0 * 8192 + g * 512 + ((hl ^ (g & 1)) << 6) + 16 * t;
   int v_off[4];
   {
     const int toks[4] = {2 * t, 2 * t + 1, 2 * t + 8, 2 * t + 9};
 #pragma unroll
     for (int i = 0; i < 4; ++i)
-      v_off[i] = 16384 + wj * 8192 + toks[i] * 512 + (((2 * hl + (g >> 2)) ^ ((toks[i] >> 1) & 3)) << 5) + (g & 3) * 8;
+      v_off[i] = 16384 + wj0 * 8192 + toks[i] * 512 + (((2 * hl + (g >> 2)) ^ ((toks[i] >> 1) & 3)) << 5) + (g & 3) * 8;
   }
-  const int n_off = 32768 + (lane < 16 ? wj * 512 + (lane * 8 + hl) * 4 : 1024 + wj * 512 + ((lane - 16) * 8 + hl) * 4);
 
   uint32_t bq[8][2];
   float o[8][4];
@@ -1160,7 +1171,7 @@ tq4_attn_streamk_kernel(AttnArgs a) {
       l0 += __shfl_xor_sync(0xffffffffu, l0, offs);
       l1 += __shfl_xor_sync(0xffffffffu, l1, offs);
     }
-    const int part = 2 * (b - a.sk[S + 2 + seq_c]) + wj;
+    const int part = WPH * (b - a.sk[S + 2 + seq_c]) + wj0;
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int qg = 2 * t + e;
@@ -1185,29 +1196,30 @@ tq4_attn_streamk_kernel(AttnArgs a) {
     else asm volatile("cp.async.commit_group;\n" ::);
     const int u = u_begin + it;
     if (u >= c_end) { end_seq(); begin_seq(locate(u, seq_c)); }     // next sequence (rare)
-    const int bi = 2 * (u - c_base) + wj;
-    if (bi < c_nb) {
-      const uint32_t sb = stage_addr(it % SK_STAGES);
-      TileData<4> cur;
-      const uint4 ka = lds128(sb + kA_off);
-      const uint4 kb = lds128(sb + kA_off + 4096);
-      cur.kA[0] = ka.x; cur.kA[1] = ka.y; cur.kA[2] = ka.z; cur.kA[3] = ka.w;
-      cur.kB[0] = kb.x; cur.kB[1] = kb.y; cur.kB[2] = kb.z; cur.kB[3] = kb.w;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint2 v = lds64(sb + v_off[i]);
-        cur.v[i][0] = v.x; cur.v[i][1] = v.y;
+    for (int jj = 0; jj < 2 / WPH; ++jj) {
+      const int wj = wj0 + jj;
+      const int bi = 2 * (u - c_base) + wj;
+      if (bi < c_nb) {
+        const uint32_t sb = stage_addr(it % SK_STAGES) + jj * 8192;
+        const uint32_t nb_ = stage_addr(it % SK_STAGES) + 32768 + wj * 512;
+        TileData<4> cur;
+        const uint4 ka = lds128(sb + kA_off);
+        const uint4 kb = lds128(sb + kA_off + 4096);
+        cur.kA[0] = ka.x; cur.kA[1] = ka.y; cur.kA[2] = ka.z; cur.kA[3] = ka.w;
+        cur.kB[0] = kb.x; cur.kB[1] = kb.y; cur.kB[2] = kb.z; cur.kB[3] = kb.w;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint2 v = lds64(sb + v_off[i]);
+          cur.v[i][0] = v.x; cur.v[i][1] = v.y;
+        }
+        cur.nkA = __uint_as_float(lds32(nb_ + (g * 8 + hl) * 4));
+        cur.nkB = __uint_as_float(lds32(nb_ + ((g + 8) * 8 + hl) * 4));
+        cur.nvA = __uint_as_float(lds32(nb_ + 1024 + (g * 8 + hl) * 4));
+        cur.nvB = __uint_as_float(lds32(nb_ + 1024 + ((g + 8) * 8 + hl) * 4));
+        const int rem = ctx_c - bi * 16;
+        process_tile<4>(lut_s, lanebase, g, bq, cur, rem < 16 ? rem : 16, o, st);
       }
-#if AKV_NORM_SHFL
-      cur.nrm = __uint_as_float(lds32(sb + n_off));
-#else
-      cur.nkA = __uint_as_float(lds32(sb + 32768 + wj * 512 + (g * 8 + hl) * 4));
-      cur.nkB = __uint_as_float(lds32(sb + 32768 + wj * 512 + ((g + 8) * 8 + hl) * 4));
-      cur.nvA = __uint_as_float(lds32(sb + 33792 + wj * 512 + (g * 8 + hl) * 4));
-      cur.nvB = __uint_as_float(lds32(sb + 33792 + wj * 512 + ((g + 8) * 8 + hl) * 4));
-#endif
-      const int rem = ctx_c - bi * 16;
-      process_tile<4>(lut_s, lanebase, g, bq, cur, rem < 16 ? rem : 16, o, st);
     }
   }
   asm volatile("cp.async.wait_group 0;\n" ::: "memory");
@@ -1351,6 +1363,8 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
   StreamKPlanArgs pl{};
   pl.context_lens = p->context_lens; pl.cl_dtype = p->cl_dtype; pl.num_seqs = p->num_seqs;
   pl.block_size = p->block_size; pl.grid = plan.sk_grid; pl.sk = persist ? sk : nullptr;
+  static const int sk_wph = (getenv("AKV_SK_WPH") && atoi(getenv("AKV_SK_WPH")) == 2) ? 2 : 1;
+  pl.parts_per_cta = sk_wph;
   akv_qrot_kernel<<<rows + (persist ? 1 : 0), D < 128 ? D : 128, D * sizeof(float), st>>>(
       p->query, p->q_dtype, p->q_stride_seq, p->q_stride_head, p->num_q_heads, D, p->rotation_t,
       p->scale * 1.4426950408889634f, qrot, rows, pl);
@@ -1377,12 +1391,13 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
   if (p->ev_kernel_start) cudaEventRecord((cudaEvent_t)p->ev_kernel_start, st);
   if (p->max_blocks_per_seq > 0) {
     if (persist) {
-      a.num_parts = 2 * plan.sk_grid;
+      a.num_parts = sk_wph * plan.sk_grid;
       merge_parts = a.num_parts;
-      cudaError_t e = cudaFuncSetAttribute(tq4_attn_streamk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_DYN_SMEM);
+      auto kern = sk_wph == 2 ? tq4_attn_streamk_kernel<2> : tq4_attn_streamk_kernel<1>;
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_DYN_SMEM);
       if (e != cudaSuccess) return fail((int)e, "attention: smem attribute: %s", cudaGetErrorString(e));
       dim3 grid(plan.sk_grid, p->num_kv_heads / 8);
-      tq4_attn_streamk_kernel<<<grid, 512, SK_DYN_SMEM, st>>>(a);
+      kern<<<grid, 256 * sk_wph, SK_DYN_SMEM, st>>>(a);
       if (int rc = check_launch("tq4_attn_streamk_kernel")) return rc;
     } else if (pipe && plan.blocks_per_split <= PIPE_MAX_BLOCKS) {
       cudaError_t e = cudaFuncSetAttribute(tq4_attn_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PIPE_SMEM);
