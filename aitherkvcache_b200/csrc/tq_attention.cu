@@ -644,6 +644,85 @@ __device__ __forceinline__ void process_tile(lut_t lut, uint32_t lanebase, int g
   }
 }
 
+// Two 16-token tiles of one KV head at once (4-bit codes): the score products of both tiles are
+// independent, one softmax update covers the 32 tokens, and both value products accumulate into the
+// same output fragments.  Twice the independent work per warp for the 8-warp persistent kernel.
+// n_valid_b may be 0 (no second tile): its scores are masked and its weights are zero.
+__device__ __forceinline__ void process_tile_pair4(uint32_t lanebase, int g, const uint32_t (&bq)[8][2],
+                                                   const TileData<4>& ta, const TileData<4>& tb,
+                                                   int n_valid_a, int n_valid_b, float (&o)[8][4],
+                                                   SoftmaxState& st) {
+  constexpr lut_t lut = 0;
+  float sa[4] = {0.f, 0.f, 0.f, 0.f}, sa2[4] = {0.f, 0.f, 0.f, 0.f};
+  float sb[4] = {0.f, 0.f, 0.f, 0.f}, sb2[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    mma16816(sa, lut4<0>(lut, ta.kA[w], lanebase), lut4<0>(lut, ta.kB[w], lanebase),
+             lut4<1>(lut, ta.kA[w], lanebase), lut4<1>(lut, ta.kB[w], lanebase), bq[2 * w][0], bq[2 * w][1]);
+    mma16816(sb, lut4<0>(lut, tb.kA[w], lanebase), lut4<0>(lut, tb.kB[w], lanebase),
+             lut4<1>(lut, tb.kA[w], lanebase), lut4<1>(lut, tb.kB[w], lanebase), bq[2 * w][0], bq[2 * w][1]);
+    mma16816(sa2, lut4<2>(lut, ta.kA[w], lanebase), lut4<2>(lut, ta.kB[w], lanebase),
+             lut4<3>(lut, ta.kA[w], lanebase), lut4<3>(lut, ta.kB[w], lanebase), bq[2 * w + 1][0], bq[2 * w + 1][1]);
+    mma16816(sb2, lut4<2>(lut, tb.kA[w], lanebase), lut4<2>(lut, tb.kB[w], lanebase),
+             lut4<3>(lut, tb.kA[w], lanebase), lut4<3>(lut, tb.kB[w], lanebase), bq[2 * w + 1][0], bq[2 * w + 1][1]);
+  }
+  float nvAa = ta.nvA, nvBa = ta.nvB, nvAb = tb.nvA, nvBb = tb.nvB;
+  sa[0] = (sa[0] + sa2[0]) * ta.nkA; sa[1] = (sa[1] + sa2[1]) * ta.nkA;
+  sa[2] = (sa[2] + sa2[2]) * ta.nkB; sa[3] = (sa[3] + sa2[3]) * ta.nkB;
+  sb[0] = (sb[0] + sb2[0]) * tb.nkA; sb[1] = (sb[1] + sb2[1]) * tb.nkA;
+  sb[2] = (sb[2] + sb2[2]) * tb.nkB; sb[3] = (sb[3] + sb2[3]) * tb.nkB;
+  if (n_valid_a < 16 || n_valid_b < 16) {   // warp-uniform: only at the end of a sequence
+    if (g >= n_valid_a) { sa[0] = -CUDART_INF_F; sa[1] = -CUDART_INF_F; nvAa = 0.f; }
+    if (g + 8 >= n_valid_a) { sa[2] = -CUDART_INF_F; sa[3] = -CUDART_INF_F; nvBa = 0.f; }
+    if (g >= n_valid_b) { sb[0] = -CUDART_INF_F; sb[1] = -CUDART_INF_F; nvAb = 0.f; }
+    if (g + 8 >= n_valid_b) { sb[2] = -CUDART_INF_F; sb[3] = -CUDART_INF_F; nvBb = 0.f; }
+  }
+  float mx0 = fmaxf(fmaxf(sa[0], sa[2]), fmaxf(sb[0], sb[2]));
+  float mx1 = fmaxf(fmaxf(sa[1], sa[3]), fmaxf(sb[1], sb[3]));
+#pragma unroll
+  for (int off = 4; off < 32; off <<= 1) {
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+  }
+  const float mn0 = fmaxf(st.m0, mx0), mn1 = fmaxf(st.m1, mx1);
+  if (__any_sync(0xffffffffu, (mn0 != st.m0) | (mn1 != st.m1))) {
+    const float al0 = ex2_approx(st.m0 - mn0), al1 = ex2_approx(st.m1 - mn1);
+    st.l0 *= al0; st.l1 *= al1;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { o[j][0] *= al0; o[j][1] *= al1; o[j][2] *= al0; o[j][3] *= al1; }
+    st.m0 = mn0; st.m1 = mn1;
+  }
+  const float pa0 = ex2_approx(sa[0] - mn0), pa1 = ex2_approx(sa[1] - mn1);
+  const float pa2 = ex2_approx(sa[2] - mn0), pa3 = ex2_approx(sa[3] - mn1);
+  const float pb0f = ex2_approx(sb[0] - mn0), pb1f = ex2_approx(sb[1] - mn1);
+  const float pb2f = ex2_approx(sb[2] - mn0), pb3f = ex2_approx(sb[3] - mn1);
+  st.l0 += (pa0 + pa2) + (pb0f + pb2f);
+  st.l1 += (pa1 + pa3) + (pb1f + pb3f);
+  const uint32_t qa0 = movmatrix_trans(pack_half2(pa0 * nvAa, pa1 * nvAa));
+  const uint32_t qa1 = movmatrix_trans(pack_half2(pa2 * nvBa, pa3 * nvBa));
+  const uint32_t qb0 = movmatrix_trans(pack_half2(pb0f * nvAb, pb1f * nvAb));
+  const uint32_t qb1 = movmatrix_trans(pack_half2(pb2f * nvBb, pb3f * nvBb));
+#pragma unroll
+  for (int w = 0; w < 2; ++w) {
+    uint32_t x01[2], y01[2], x23[2], y23[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const TileData<4>& tt = k ? tb : ta;
+      const uint32_t va = tt.v[0][w], vb = tt.v[1][w], vc = tt.v[2][w], vd = tt.v[3][w];
+      x01[k] = (va & 0xF0F0F0F0u) | ((vb >> 4) & 0x0F0F0F0Fu);
+      y01[k] = ((va << 4) & 0xF0F0F0F0u) | (vb & 0x0F0F0F0Fu);
+      x23[k] = (vc & 0xF0F0F0F0u) | ((vd >> 4) & 0x0F0F0F0Fu);
+      y23[k] = ((vc << 4) & 0xF0F0F0F0u) | (vd & 0x0F0F0F0Fu);
+    }
+#define AKV_PV(J, K)                                                                                        \
+    mma16816(o[4 * w + J], lut4<J>(lut, x01[K], lanebase), lut4<J>(lut, y01[K], lanebase),                  \
+             lut4<J>(lut, x23[K], lanebase), lut4<J>(lut, y23[K], lanebase), K ? qb0 : qa0, K ? qb1 : qa1);
+    AKV_PV(0, 0) AKV_PV(1, 0) AKV_PV(2, 0) AKV_PV(3, 0)
+    AKV_PV(0, 1) AKV_PV(1, 1) AKV_PV(2, 1) AKV_PV(3, 1)
+#undef AKV_PV
+  }
+}
+
 template <int BITS, bool VEC16>
 __global__ void __launch_bounds__(256, 2)
 tq_attn_mma_kernel(AttnArgs a) {
@@ -1196,27 +1275,38 @@ tq4_attn_streamk_kernel(AttnArgs a) {
     else asm volatile("cp.async.commit_group;\n" ::);
     const int u = u_begin + it;
     if (u >= c_end) { end_seq(); begin_seq(locate(u, seq_c)); }     // next sequence (rare)
+    auto load_tile_s = [&](int jj, TileData<4>& cur) {
+      const uint32_t sb = stage_addr(it % SK_STAGES) + jj * 8192;
+      const uint32_t nb_ = stage_addr(it % SK_STAGES) + 32768 + (wj0 + jj) * 512;
+      const uint4 ka = lds128(sb + kA_off);
+      const uint4 kb = lds128(sb + kA_off + 4096);
+      cur.kA[0] = ka.x; cur.kA[1] = ka.y; cur.kA[2] = ka.z; cur.kA[3] = ka.w;
+      cur.kB[0] = kb.x; cur.kB[1] = kb.y; cur.kB[2] = kb.z; cur.kB[3] = kb.w;
 #pragma unroll
-    for (int jj = 0; jj < 2 / WPH; ++jj) {
-      const int wj = wj0 + jj;
-      const int bi = 2 * (u - c_base) + wj;
+      for (int i = 0; i < 4; ++i) {
+        const uint2 v = lds64(sb + v_off[i]);
+        cur.v[i][0] = v.x; cur.v[i][1] = v.y;
+      }
+      cur.nkA = __uint_as_float(lds32(nb_ + (g * 8 + hl) * 4));
+      cur.nkB = __uint_as_float(lds32(nb_ + ((g + 8) * 8 + hl) * 4));
+      cur.nvA = __uint_as_float(lds32(nb_ + 1024 + (g * 8 + hl) * 4));
+      cur.nvB = __uint_as_float(lds32(nb_ + 1024 + ((g + 8) * 8 + hl) * 4));
+    };
+    if constexpr (WPH == 1) {
+      // both blocks of the stage at once; a missing second block (odd block count) is masked out:
+      // its shared-memory slot holds stale but decodable bytes
+      const int bi = 2 * (u - c_base);
+      TileData<4> ta, tb;
+      load_tile_s(0, ta);
+      load_tile_s(1, tb);
+      const int rem_a = ctx_c - bi * 16, rem_b = rem_a - 16;
+      process_tile_pair4(lanebase, g, bq, ta, tb, rem_a < 16 ? rem_a : 16,
+                         rem_b < 0 ? 0 : (rem_b < 16 ? rem_b : 16), o, st);
+    } else {
+      const int bi = 2 * (u - c_base) + wj0;
       if (bi < c_nb) {
-        const uint32_t sb = stage_addr(it % SK_STAGES) + jj * 8192;
-        const uint32_t nb_ = stage_addr(it % SK_STAGES) + 32768 + wj * 512;
         TileData<4> cur;
-        const uint4 ka = lds128(sb + kA_off);
-        const uint4 kb = lds128(sb + kA_off + 4096);
-        cur.kA[0] = ka.x; cur.kA[1] = ka.y; cur.kA[2] = ka.z; cur.kA[3] = ka.w;
-        cur.kB[0] = kb.x; cur.kB[1] = kb.y; cur.kB[2] = kb.z; cur.kB[3] = kb.w;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint2 v = lds64(sb + v_off[i]);
-          cur.v[i][0] = v.x; cur.v[i][1] = v.y;
-        }
-        cur.nkA = __uint_as_float(lds32(nb_ + (g * 8 + hl) * 4));
-        cur.nkB = __uint_as_float(lds32(nb_ + ((g + 8) * 8 + hl) * 4));
-        cur.nvA = __uint_as_float(lds32(nb_ + 1024 + (g * 8 + hl) * 4));
-        cur.nvB = __uint_as_float(lds32(nb_ + 1024 + ((g + 8) * 8 + hl) * 4));
+        load_tile_s(0, cur);
         const int rem = ctx_c - bi * 16;
         process_tile<4>(lut_s, lanebase, g, bq, cur, rem < 16 ? rem : 16, o, st);
       }
