@@ -1086,7 +1086,7 @@ __device__ __forceinline__ void cp_async16_s(uint32_t smem_dst, const void* gsrc
 
 // WPH = warps per KV head: 2 -> 16 warps, warp (head, j) takes block j of every stage and writes its own
 // partial; 1 -> 8 warps with twice the registers, a warp takes both blocks of its head's stage.
-template <int WPH>
+template <int WPH, bool PAIR>
 __global__ void __launch_bounds__(256 * WPH, 1)
 tq4_attn_streamk_kernel(AttnArgs a) {
   constexpr int NT = 256 * WPH;
@@ -1292,7 +1292,7 @@ tq4_attn_streamk_kernel(AttnArgs a) {
       cur.nvA = __uint_as_float(lds32(nb_ + 1024 + (g * 8 + hl) * 4));
       cur.nvB = __uint_as_float(lds32(nb_ + 1024 + ((g + 8) * 8 + hl) * 4));
     };
-    if constexpr (WPH == 1) {
+    if constexpr (WPH == 1 && PAIR) {
       // both blocks of the stage at once; a missing second block (odd block count) is masked out:
       // its shared-memory slot holds stale but decodable bytes
       const int bi = 2 * (u - c_base);
@@ -1303,12 +1303,15 @@ tq4_attn_streamk_kernel(AttnArgs a) {
       process_tile_pair4(lanebase, g, bq, ta, tb, rem_a < 16 ? rem_a : 16,
                          rem_b < 0 ? 0 : (rem_b < 16 ? rem_b : 16), o, st);
     } else {
-      const int bi = 2 * (u - c_base) + wj0;
-      if (bi < c_nb) {
-        TileData<4> cur;
-        load_tile_s(0, cur);
-        const int rem = ctx_c - bi * 16;
-        process_tile<4>(lut_s, lanebase, g, bq, cur, rem < 16 ? rem : 16, o, st);
+#pragma unroll
+      for (int jj = 0; jj < 2 / WPH; ++jj) {
+        const int bi = 2 * (u - c_base) + wj0 + jj;
+        if (bi < c_nb) {
+          TileData<4> cur;
+          load_tile_s(jj, cur);
+          const int rem = ctx_c - bi * 16;
+          process_tile<4>(lut_s, lanebase, g, bq, cur, rem < 16 ? rem : 16, o, st);
+        }
       }
     }
   }
@@ -1483,7 +1486,9 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
     if (persist) {
       a.num_parts = sk_wph * plan.sk_grid;
       merge_parts = a.num_parts;
-      auto kern = sk_wph == 2 ? tq4_attn_streamk_kernel<2> : tq4_attn_streamk_kernel<1>;
+      static const bool sk_pair = getenv("AKV_SK_PAIR") != nullptr;
+      auto kern = sk_wph == 2 ? tq4_attn_streamk_kernel<2, false>
+                              : (sk_pair ? tq4_attn_streamk_kernel<1, true> : tq4_attn_streamk_kernel<1, false>);
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_DYN_SMEM);
       if (e != cudaSuccess) return fail((int)e, "attention: smem attribute: %s", cudaGetErrorString(e));
       dim3 grid(plan.sk_grid, p->num_kv_heads / 8);
