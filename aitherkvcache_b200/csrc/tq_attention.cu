@@ -1486,7 +1486,7 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
     if (persist) {
       a.num_parts = sk_wph * plan.sk_grid;
       merge_parts = a.num_parts;
-      static const bool sk_pair = getenv("AKV_SK_PAIR") != nullptr;
+      static const bool sk_pair = getenv("AKV_SK_NO_PAIR") == nullptr;   // two tiles per warp at once
       auto kern = sk_wph == 2 ? tq4_attn_streamk_kernel<2, false>
                               : (sk_pair ? tq4_attn_streamk_kernel<1, true> : tq4_attn_streamk_kernel<1, false>);
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_DYN_SMEM);
