@@ -43,7 +43,7 @@ WORKLOAD = ("paged decode attention, tq-t4nc cache: 16 seqs, ctx U[4096,32768] s
             "head_dim 128, block_size 16, permuted block tables")
 
 
-NCU_TRAFFIC_BYTES = 281_302_000     # dram read + write per launch (ncu: 2.7557 TB/s x 102.08 us, rank-0 workload)
+NCU_TRAFFIC_BYTES = 281_170_000     # dram read + write per launch (ncu: 3.1392 TB/s x 89.568 us, rank-0 workload)
 
 
 def context_lengths(rank=0):
