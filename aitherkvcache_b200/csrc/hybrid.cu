@@ -374,6 +374,229 @@ static int launch_hybrid_encode16(const void* x, int x_dtype, int64_t n_rows, in
   return check_launch("hybrid_encode16_kernel");
 }
 
+// ---------------------------------------------------------------------------
+// tq35 encode for 16-bit inputs, four lanes per vector.
+//
+// Same arithmetic as encode_group (byte-identical records).  A 64-coordinate group is spread over
+// four lanes: lane q holds coordinates k = 8 m + 2 q + b (m = 0..7, b = 0, 1), i.e. the index bits
+// 1..2 select the lane.  With that split
+//   * the eight-lane norm sums (s_j over k = j mod 8, in the order m = 0..7) are complete chains
+//     inside one lane (j = 2q, 2q+1); only the final fold s_0 + s_1 + ... hops over the lanes;
+//   * the Walsh-Hadamard butterflies of stages h = 1, 8, 16, 32 pair registers of one lane, stages
+//     h = 2, 4 pair lanes q ^ 1, q ^ 2 (one shuffle per element);
+//   * every lane quantises and packs its own 16 coordinates into its bit positions of the stream
+//     words, and the words are OR-reduced over the four lanes.
+// Sixteen live values per lane instead of 64 per thread: small code (the thread-per-vector kernel
+// stalled on instruction fetch) and enough warps per SM to hide latencies.
+// ---------------------------------------------------------------------------
+constexpr int HC_THREADS = 128;                 // 32 vectors per CTA
+constexpr int HC_ROW_WORDS = 68;                // staged row pitch in 32-bit words (64 + 4: conflict-free gathers)
+
+// element slot i = 2 m + b of a lane <-> coordinate k = 8 m + 2 q + b
+__device__ __forceinline__ int hc_coord(int i, int q) { return 8 * (i >> 1) + 2 * q + (i & 1); }
+
+// In-lane butterfly over the slots whose index differs in bit `bit` (slot bit 0 = coordinate bit 0,
+// slot bits 1..3 = coordinate bits 3..5).
+template <int BIT>
+__device__ __forceinline__ void hc_stage_local(float (&w)[16]) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    if (!(i & (1 << BIT))) {
+      const float a = w[i], b = w[i | (1 << BIT)];
+      w[i] = __fadd_rn(a, b);
+      w[i | (1 << BIT)] = __fsub_rn(a, b);
+    }
+  }
+}
+
+// Butterfly between lanes q and q ^ MASK: the lane whose bit is clear holds the lower coordinate.
+template <int MASK>
+__device__ __forceinline__ void hc_stage_cross(float (&w)[16], uint32_t neg_mask) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float p = __shfl_xor_sync(0xffffffffu, w[i], MASK);
+    // lower lane: w + p; upper lane: p - w  (= (-w) + p, same rounding)
+    w[i] = __fadd_rn(__uint_as_float(__float_as_uint(w[i]) ^ neg_mask), p);
+  }
+}
+
+// 64-point transform in the reference's stage order h = 1, 2, 4, 8, 16, 32.
+__device__ __forceinline__ void hc_fwht64(float (&w)[16], int q) {
+  hc_stage_local<0>(w);                                          // h = 1
+  hc_stage_cross<1>(w, (q & 1) ? 0x80000000u : 0u);              // h = 2
+  hc_stage_cross<2>(w, (q & 2) ? 0x80000000u : 0u);              // h = 4
+  hc_stage_local<1>(w);                                          // h = 8
+  hc_stage_local<2>(w);                                          // h = 16
+  hc_stage_local<3>(w);                                          // h = 32
+}
+
+// sqrt of the eight-lane sum of squares of the group (every lane of the quad returns it).
+__device__ __forceinline__ float hc_norm(const float (&v)[16], int q, int lane) {
+  float s0 = 0.f, s1 = 0.f;        // lanes j = 2q and 2q + 1 of the reference's reduction
+#pragma unroll
+  for (int m = 0; m < 8; ++m) {
+    s0 = __fadd_rn(s0, __fmul_rn(v[2 * m], v[2 * m]));
+    s1 = __fadd_rn(s1, __fmul_rn(v[2 * m + 1], v[2 * m + 1]));
+  }
+  // fold ((((s_0 + s_1) + s_2) + s_3) + ...) + s_7 across the quad
+  float acc = __fadd_rn(s0, s1);
+#pragma unroll
+  for (int step = 1; step < 4; ++step) {
+    const float prev = __shfl_sync(0xffffffffu, acc, (lane & ~3) + step - 1);
+    if (q == step) acc = __fadd_rn(__fadd_rn(prev, s0), s1);
+  }
+  return __fsqrt_rn(__shfl_sync(0xffffffffu, acc, (lane & ~3) + 3));
+}
+
+// x / den for one den and many x: with r = RN(1 / den), q0 = RN(x r), rem = x - q0 den (exact, FMA),
+// q1 = RN(q0 + rem r) is the correctly rounded quotient unless den's significand is all ones
+// (Markstein); that case and non-finite / tiny operands take the IEEE division.
+struct HcDivisor { float den, rcp; bool fast; };
+
+__device__ __forceinline__ HcDivisor hc_divisor(float d) {
+  HcDivisor v;
+  v.den = d;
+  v.rcp = __frcp_rn(d);
+  const uint32_t bits = __float_as_uint(d);
+  const uint32_t ex = (bits >> 23) & 0xffu;
+  v.fast = (bits & 0x7fffffu) != 0x7fffffu && ex > 32u && ex < 222u;
+  return v;
+}
+
+__device__ __forceinline__ float hc_div(const HcDivisor& v, float x) {
+  if (v.fast && x != 0.f) {
+    const float q0 = __fmul_rn(x, v.rcp);
+    const float rem = __fmaf_rn(-q0, v.den, x);
+    const float q1 = __fmaf_rn(rem, v.rcp, q0);
+    // the shortcut needs a normal, finite quotient; anything unusual goes the long way
+    const uint32_t qe = (__float_as_uint(q1) >> 23) & 0xffu;
+    if (qe > 1u && qe < 254u) return q1;
+  }
+  return __fdiv_rn(x, v.den);
+}
+
+template <int BITS, bool BF16>
+__device__ __forceinline__ void hc_encode_group(const uint32_t* xrow, const int* gidx, const float* had,
+                                                const float* qjl, const float* cent, const float* bnd,
+                                                int q, int lane, uint32_t* out_words, bool store) {
+  constexpr int MSE_W = 64 * BITS / 32, QJL_W = 2, NB = (1 << BITS) - 1;
+  float u[16], w[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int idx = gidx[hc_coord(i, q)];
+    const uint32_t word = xrow[idx >> 1];
+    const uint32_t h = (idx & 1) ? (word >> 16) : (word & 0xffffu);
+    w[i] = BF16 ? __uint_as_float(h << 16) : __half2float(__ushort_as_half((unsigned short)h));
+  }
+  const float n = hc_norm(w, q, lane);
+  const HcDivisor dv = hc_divisor(__fadd_rn(n, 1e-10f));
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    u[i] = hc_div(dv, w[i]);
+    w[i] = __fmul_rn(u[i], had[hc_coord(i, q)]);
+  }
+  hc_fwht64(w, q);
+  uint32_t W[MSE_W + QJL_W];
+#pragma unroll
+  for (int j = 0; j < MSE_W + QJL_W; ++j) W[j] = 0u;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float r = __fmul_rn(w[i], 0.125f);          // / sqrt(64), exact
+    uint32_t c = 0;
+#pragma unroll
+    for (int b = 0; b < NB; ++b) c += (bnd[b] < r) ? 1u : 0u;
+    // code of coordinate k goes to stream bits [k BITS, (k+1) BITS), MSB first; k depends on q at run
+    // time only through the term 2 q BITS, a shift inside the 8-code (8 BITS-bit) group of slot pair m
+    const int m = i >> 1, b01 = i & 1;
+    // group m occupies stream bits [8 m BITS, 8 (m+1) BITS); inside it the code sits (2 q + b01) BITS from the top
+    const uint32_t in_group = c << (8 * BITS - BITS - b01 * BITS);     // still to be shifted right by 2 q BITS
+    const uint32_t placed = in_group >> (2 * BITS * q);                // 8 BITS-bit value
+    // append the group value to the stream words (compile-time positions)
+    const int pos = 8 * m * BITS, j = pos >> 5, off = pos & 31;       // group start bit
+    if (off + 8 * BITS <= 32) {
+      W[j] |= placed << (32 - 8 * BITS - off);
+    } else {
+      W[j] |= placed >> (off + 8 * BITS - 32);
+      W[j + 1] |= placed << (64 - 8 * BITS - off);
+    }
+    w[i] = cent[c];
+  }
+  hc_fwht64(w, q);
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+    w[i] = __fsub_rn(u[i], __fmul_rn(__fmul_rn(w[i], had[hc_coord(i, q)]), 0.125f));
+  const float rho = hc_norm(w, q, lane);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) w[i] = __fmul_rn(w[i], qjl[hc_coord(i, q)]);
+  hc_fwht64(w, q);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const uint32_t bit = (w[i] >= 0.f) ? 1u : 0u;      // sign of w / 8
+    const int m = i >> 1, b01 = i & 1;
+    // byte m of the sign stream holds coordinates 8 m .. 8 m + 7, MSB first
+    const uint32_t placed = (bit << (7 - b01)) >> (2 * q);
+    W[MSE_W + (m >> 2)] |= placed << (24 - 8 * (m & 3));
+  }
+  // OR the four lanes' contributions, convert to the byte order of the record, spread the stores
+#pragma unroll
+  for (int j = 0; j < MSE_W + QJL_W; ++j) {
+    W[j] |= __shfl_xor_sync(0xffffffffu, W[j], 1);
+    W[j] |= __shfl_xor_sync(0xffffffffu, W[j], 2);
+  }
+#pragma unroll
+  for (int j = 0; j < MSE_W + QJL_W; ++j)
+    if (store && (j & 3) == q) out_words[j] = __byte_perm(W[j], 0u, 0x0123);
+  if (store && q == 3) {
+    const uint32_t bn = __half_as_ushort(__float2half_rn(n)), br = __half_as_ushort(__float2half_rn(rho));
+    out_words[MSE_W + QJL_W] = bn | (br << 16);
+  }
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(HC_THREADS, 4)
+hybrid_encode35_coop_kernel(const uint16_t* __restrict__ x, int64_t n_rows, int64_t x_row_stride,
+                            HybridTables t, uint8_t* __restrict__ out, int64_t out_row_stride) {
+  __shared__ __align__(16) uint32_t xs[32 * HC_ROW_WORDS];
+  __shared__ float s_had[128], s_qjl[128], s_cent[16], s_bnd[16];
+  __shared__ int s_idx[128];
+  const int tid = threadIdx.x, lane = tid & 31;
+  if (tid < 128) { s_had[tid] = t.had_signs[tid]; s_qjl[tid] = t.qjl_signs[tid]; s_idx[tid] = t.group_index[tid]; }
+  if (tid < 16) { s_cent[tid] = t.centroids[tid]; s_bnd[tid] = t.boundaries[tid]; }
+  const int64_t row0 = (int64_t)blockIdx.x * 32;
+  // stage 32 rows: 512 pieces of 16 bytes, 4 per thread, coalesced
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int e = i * HC_THREADS + tid, r = e >> 4, c = e & 15;
+    const int64_t n = row0 + r;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (n < n_rows) v = *reinterpret_cast<const uint4*>(x + n * x_row_stride + c * 8);
+    *reinterpret_cast<uint4*>(xs + r * HC_ROW_WORDS + 4 * c) = v;
+  }
+  __syncthreads();
+  const int vec = tid >> 2, q = tid & 3;
+  const int64_t n = row0 + vec;
+  // whole quads leave together (n is the same for the four lanes); the shuffles below name all 32
+  // lanes, so a warp with some finished quads keeps them running on zeros instead
+  const bool live = n < n_rows;
+  const int* gidx = s_idx;
+  if (t.num_index_heads > 1 && live) gidx = t.group_index + (int)(n % t.num_index_heads) * 128;
+  uint32_t* dst = reinterpret_cast<uint32_t*>(out + (live ? n : 0) * out_row_stride);
+  hc_encode_group<3, BF16>(xs + vec * HC_ROW_WORDS, gidx, s_had, s_qjl, s_cent, s_bnd, q, lane, dst, live);
+  hc_encode_group<2, BF16>(xs + vec * HC_ROW_WORDS, gidx + 64, s_had + 64, s_qjl + 64, s_cent + 8, s_bnd + 8, q, lane,
+                           dst + 9, live);
+}
+
+static int launch_hybrid_encode35_coop(const void* x, int x_dtype, int64_t n_rows, int64_t x_row_stride,
+                                       const HybridTables& t, uint8_t* out, int64_t out_row_stride, cudaStream_t st) {
+  const int grid = (int)((n_rows + 31) / 32);
+  const uint16_t* xp = reinterpret_cast<const uint16_t*>(x);
+  if (x_dtype == AKV_BF16)
+    hybrid_encode35_coop_kernel<true><<<grid, HC_THREADS, 0, st>>>(xp, n_rows, x_row_stride, t, out, out_row_stride);
+  else
+    hybrid_encode35_coop_kernel<false><<<grid, HC_THREADS, 0, st>>>(xp, n_rows, x_row_stride, t, out, out_row_stride);
+  return check_launch("hybrid_encode35_coop_kernel");
+}
+
 template <int G, int BITS>
 __device__ __forceinline__ void decode_group(const uint8_t* rec, const int* gidx, const float* had,
                                              const float* qjl, const float* cent, float qjl_scale,
@@ -1131,6 +1354,11 @@ AKV_EXPORT int akv_hybrid_encode(const void* x, int x_dtype, int64_t n_rows, int
   if (x_dtype < AKV_F16 || x_dtype > AKV_F32) return fail(AKV_ERR_ARG, "bad x_dtype %d", x_dtype);
   cudaStream_t st = (cudaStream_t)stream;
   if (x_dtype != AKV_F32) {
+    static const bool no_coop = getenv("AKV_HYBRID_NO_COOP") != nullptr;
+    const bool rows16 = (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (x_row_stride & 7) == 0 &&
+                        (reinterpret_cast<uintptr_t>(packed) & 3) == 0 && (packed_row_stride & 3) == 0;
+    if (mode == 35 && rows16 && !no_coop)
+      return launch_hybrid_encode35_coop(x, x_dtype, n_rows, x_row_stride, t, packed, packed_row_stride, st);
     if (mode == 35)
       return launch_hybrid_encode16<64, 3, 64, 2>(x, x_dtype, n_rows, x_row_stride, t, packed, packed_row_stride, st);
     return launch_hybrid_encode16<32, 2, 96, 1>(x, x_dtype, n_rows, x_row_stride, t, packed, packed_row_stride, st);

@@ -73,6 +73,7 @@ struct StreamKPlanArgs {
   const void* context_lens; int cl_dtype; int num_seqs; int block_size; int grid;
   int* sk;    // nullptr: no plan wanted
   int parts_per_cta;   // partials a CTA writes per (sequence, q head): warps per KV head
+  int blocks_per_stage;   // 16-token blocks in a stage (2 or 4)
 };
 
 __device__ void streamk_plan(const StreamKPlanArgs& p) {
@@ -86,7 +87,7 @@ __device__ void streamk_plan(const StreamKPlanArgs& p) {
     const int64_t ctx = load_index(p.context_lens, p.cl_dtype, s);
     const int nb = (int)((ctx + p.block_size - 1) / p.block_size);
     p.sk[3 * S + 2 + s] = nb;
-    local += (nb + 1) / 2;
+    local += (nb + p.blocks_per_stage - 1) / p.blocks_per_stage;
   }
   s_part[tid] = local;
   __syncthreads();
@@ -100,7 +101,7 @@ __device__ void streamk_plan(const StreamKPlanArgs& p) {
   const int chunk = T > 0 ? (T + p.grid - 1) / p.grid : 1;
   int run = s_part[tid];
   for (int s = s0; s < s1; ++s) {
-    const int cnt = (p.sk[3 * S + 2 + s] + 1) / 2;
+    const int cnt = (p.sk[3 * S + 2 + s] + p.blocks_per_stage - 1) / p.blocks_per_stage;
     p.sk[s] = run;
     p.sk[S + 2 + s] = cnt > 0 ? run / chunk : 0;
     p.sk[2 * S + 2 + s] = cnt > 0 ? p.parts_per_cta * ((run + cnt - 1) / chunk - run / chunk + 1) : 0;
@@ -1319,6 +1320,306 @@ tq4_attn_streamk_kernel(AttnArgs a) {
   end_seq();
 }
 
+// ---------------------------------------------------------------------------
+// Four tiles at once: the persistent kernel with 4-block stages.
+//
+// Same schedule, copies, swizzles and lookups as tq4_attn_streamk_kernel; a stage is now four
+// 16-token blocks of a sequence (64 tokens) and a warp runs the four tiles of its head through one
+// code path: four independent score products, one softmax update per 64 tokens, four value
+// products into the same fragments.  Two ring slots of 68 KB; their pieces sit where the fixed
+// lookup-table address leaves room (absolute shared addresses):
+//   [1 KB, 9.5 KB) plan arrays   [9.5 KB, 41.5 KB) slot 0 K   [41.5 KB, 49.5 KB) norms of slots 0, 1
+//   [64 KB, 128 KB) lookup table [128 KB, 160 KB) slot 1 K    [160 KB, 192 KB) slot 1 V   [192 KB, 224 KB) slot 0 V
+// Blocks missing from the last stage of a sequence are not copied; their tiles are masked.
+// ---------------------------------------------------------------------------
+constexpr uint32_t SK4_PLAN = 1024;
+constexpr uint32_t SK4_K0 = 9728, SK4_N0 = SK4_K0 + 32768, SK4_N1 = SK4_N0 + 4096;
+constexpr uint32_t SK4_K1 = 131072, SK4_V1 = SK4_K1 + 32768, SK4_V0 = SK4_V1 + 32768;
+constexpr int SK4_DYN_SMEM = SK4_V0 + 32768;     // 229376: covers every address above for any start >= 0
+static_assert(SK4_PLAN + (SK_MAX_SEQS + 2) * 4 + SK_MAX_SEQS * 4 <= SK4_K0, "plan arrays overlap the ring");
+static_assert(SK4_N1 + 4096 <= SK_LUT, "low region overlaps the lookup table");
+
+// K data, norms and scores of NTILE tiles, one softmax update, then V data and the value products.
+template <int NTILE>
+__device__ __forceinline__ void process_tiles4(uint32_t lanebase, int g, const uint32_t (&bq)[8][2],
+                                               uint32_t k_addr, const uint32_t (&v_addr)[4], uint32_t n_addr,
+                                               int rem, float (&o)[8][4], SoftmaxState& st) {
+  constexpr lut_t lut = 0;
+  float s[NTILE][4], s2[NTILE][4];
+  float nk[NTILE][2], nv[NTILE][2];
+  {
+    uint4 ka[NTILE], kb[NTILE];
+#pragma unroll
+    for (int j = 0; j < NTILE; ++j) {
+      ka[j] = lds128(k_addr + j * 8192);
+      kb[j] = lds128(k_addr + j * 8192 + 4096);
+      nk[j][0] = __uint_as_float(lds32(n_addr + j * 512));
+      nk[j][1] = __uint_as_float(lds32(n_addr + j * 512 + 256));
+      nv[j][0] = __uint_as_float(lds32(n_addr + 2048 + j * 512));
+      nv[j][1] = __uint_as_float(lds32(n_addr + 2048 + j * 512 + 256));
+      s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+      s2[j][0] = s2[j][1] = s2[j][2] = s2[j][3] = 0.f;
+    }
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+#pragma unroll
+      for (int j = 0; j < NTILE; ++j) {
+        const uint32_t a = w == 0 ? ka[j].x : w == 1 ? ka[j].y : w == 2 ? ka[j].z : ka[j].w;
+        const uint32_t b = w == 0 ? kb[j].x : w == 1 ? kb[j].y : w == 2 ? kb[j].z : kb[j].w;
+        mma16816(s[j], lut4<0>(lut, a, lanebase), lut4<0>(lut, b, lanebase),
+                 lut4<1>(lut, a, lanebase), lut4<1>(lut, b, lanebase), bq[2 * w][0], bq[2 * w][1]);
+        mma16816(s2[j], lut4<2>(lut, a, lanebase), lut4<2>(lut, b, lanebase),
+                 lut4<3>(lut, a, lanebase), lut4<3>(lut, b, lanebase), bq[2 * w + 1][0], bq[2 * w + 1][1]);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < NTILE; ++j) {
+    s[j][0] = (s[j][0] + s2[j][0]) * nk[j][0]; s[j][1] = (s[j][1] + s2[j][1]) * nk[j][0];
+    s[j][2] = (s[j][2] + s2[j][2]) * nk[j][1]; s[j][3] = (s[j][3] + s2[j][3]) * nk[j][1];
+  }
+  if (rem < 16 * NTILE) {     // warp-uniform: only the last stage of a sequence
+#pragma unroll
+    for (int j = 0; j < NTILE; ++j) {
+      const int nvld = rem - 16 * j;
+      if (g >= nvld) { s[j][0] = -CUDART_INF_F; s[j][1] = -CUDART_INF_F; nv[j][0] = 0.f; }
+      if (g + 8 >= nvld) { s[j][2] = -CUDART_INF_F; s[j][3] = -CUDART_INF_F; nv[j][1] = 0.f; }
+    }
+  }
+  float mx0 = fmaxf(s[0][0], s[0][2]), mx1 = fmaxf(s[0][1], s[0][3]);
+#pragma unroll
+  for (int j = 1; j < NTILE; ++j) {
+    mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][2]));
+    mx1 = fmaxf(mx1, fmaxf(s[j][1], s[j][3]));
+  }
+#pragma unroll
+  for (int off = 4; off < 32; off <<= 1) {
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+  }
+  const float mn0 = fmaxf(st.m0, mx0), mn1 = fmaxf(st.m1, mx1);
+  if (__any_sync(0xffffffffu, (mn0 != st.m0) | (mn1 != st.m1))) {
+    const float al0 = ex2_approx(st.m0 - mn0), al1 = ex2_approx(st.m1 - mn1);
+    st.l0 *= al0; st.l1 *= al1;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { o[j][0] *= al0; o[j][1] *= al1; o[j][2] *= al0; o[j][3] *= al1; }
+    st.m0 = mn0; st.m1 = mn1;
+  }
+  uint32_t pq[NTILE][2];
+  float ls0 = 0.f, ls1 = 0.f;
+#pragma unroll
+  for (int j = 0; j < NTILE; ++j) {
+    const float p0 = ex2_approx(s[j][0] - mn0), p1 = ex2_approx(s[j][1] - mn1);
+    const float p2 = ex2_approx(s[j][2] - mn0), p3 = ex2_approx(s[j][3] - mn1);
+    ls0 += p0 + p2;
+    ls1 += p1 + p3;
+    pq[j][0] = movmatrix_trans(pack_half2(p0 * nv[j][0], p1 * nv[j][0]));
+    pq[j][1] = movmatrix_trans(pack_half2(p2 * nv[j][1], p3 * nv[j][1]));
+  }
+  st.l0 += ls0;
+  st.l1 += ls1;
+#pragma unroll
+  for (int j = 0; j < NTILE; ++j) {
+    uint2 vv[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) vv[i] = lds64(v_addr[i] + j * 8192);
+#pragma unroll
+    for (int w = 0; w < 2; ++w) {
+      const uint32_t va = w ? vv[0].y : vv[0].x, vb = w ? vv[1].y : vv[1].x;
+      const uint32_t vc = w ? vv[2].y : vv[2].x, vd = w ? vv[3].y : vv[3].x;
+      const uint32_t x01 = (va & 0xF0F0F0F0u) | ((vb >> 4) & 0x0F0F0F0Fu);
+      const uint32_t y01 = ((va << 4) & 0xF0F0F0F0u) | (vb & 0x0F0F0F0Fu);
+      const uint32_t x23 = (vc & 0xF0F0F0F0u) | ((vd >> 4) & 0x0F0F0F0Fu);
+      const uint32_t y23 = ((vc << 4) & 0xF0F0F0F0u) | (vd & 0x0F0F0F0Fu);
+      mma16816(o[4 * w + 0], lut4<0>(lut, x01, lanebase), lut4<0>(lut, y01, lanebase),
+               lut4<0>(lut, x23, lanebase), lut4<0>(lut, y23, lanebase), pq[j][0], pq[j][1]);
+      mma16816(o[4 * w + 1], lut4<1>(lut, x01, lanebase), lut4<1>(lut, y01, lanebase),
+               lut4<1>(lut, x23, lanebase), lut4<1>(lut, y23, lanebase), pq[j][0], pq[j][1]);
+      mma16816(o[4 * w + 2], lut4<2>(lut, x01, lanebase), lut4<2>(lut, y01, lanebase),
+               lut4<2>(lut, x23, lanebase), lut4<2>(lut, y23, lanebase), pq[j][0], pq[j][1]);
+      mma16816(o[4 * w + 3], lut4<3>(lut, x01, lanebase), lut4<3>(lut, y01, lanebase),
+               lut4<3>(lut, x23, lanebase), lut4<3>(lut, y23, lanebase), pq[j][0], pq[j][1]);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256, 1)
+tq4_attn_streamk4_kernel(AttnArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ float s_cent[16];
+  const uint32_t dyn0 = (uint32_t)__cvta_generic_to_shared(smem);
+  int* s_P = reinterpret_cast<int*>(smem + (SK4_PLAN - dyn0));   // stage prefix, total, chunk
+  int* s_nb = s_P + (SK_MAX_SEQS + 2);                           // blocks per sequence
+  const int b = blockIdx.x, hg = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int S = a.num_seqs;
+  for (int i = tid; i < S + 2; i += 256) s_P[i] = a.sk[i];
+  for (int i = tid; i < S; i += 256) s_nb[i] = a.sk[3 * S + 2 + i];
+  if (tid < 16) s_cent[tid] = a.centroids[tid];
+  __syncthreads();
+  const int T = s_P[S], chunk = s_P[S + 1];
+  const int u_begin = b * chunk;
+  const int u_end = (u_begin + chunk < T) ? u_begin + chunk : T;
+  if (u_begin >= u_end) return;            // uniform for the CTA
+  const int n_it = u_end - u_begin;
+
+  auto locate = [&](int u, int hint) {
+    while (u >= s_P[hint + 1]) ++hint;
+    return hint;
+  };
+  int seq0;
+  {
+    int lo = 0, hi = S - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (s_P[mid] <= u_begin) lo = mid; else hi = mid - 1;
+    }
+    seq0 = locate(u_begin, lo);
+  }
+
+  // ---- producer: thread -> (token c_tok and c_tok + 8, 16-byte piece c_r) of every block ----
+  const int c_tok = tid >> 5, c_r = tid & 31;
+  const int k_dst = c_tok * 512 + (((c_r >> 2) ^ (c_tok & 1)) << 6) + (c_r & 3) * 16;
+  const int v_dst = c_tok * 512 + (((c_r >> 1) ^ ((c_tok >> 1) & 3)) << 5) + (c_r & 1) * 16;
+  const int64_t k_src = (int64_t)c_tok * a.kp_sp + hg * 512 + c_r * 16;
+  const int64_t v_src = (int64_t)c_tok * a.vp_sp + hg * 512 + c_r * 16;
+  const int64_t k_step = 8 * a.kp_sp, v_step = 8 * a.vp_sp;
+  const int kp_sb = (int)a.kp_sb, vp_sb = (int)a.vp_sb, kn_sb = (int)a.kn_sb, vn_sb = (int)a.vn_sb;
+  const bool bt64 = a.bt_dtype == AKV_I64;
+  int up = u_begin;
+  int p_seq = seq0 - 1, p_base = 0, p_end = u_begin, p_nb = 0;
+  const char* bt_row = nullptr;
+  int pb[4] = {0, 0, 0, 0};                // physical blocks of stage `up` (raw table entries until issue())
+  int n_has = 0;                           // blocks present in stage `up` (1..4)
+  auto load_pb = [&]() {
+    if (up >= p_end) {
+      p_seq = locate(up, p_seq < 0 ? 0 : p_seq);
+      p_base = s_P[p_seq]; p_end = s_P[p_seq + 1]; p_nb = s_nb[p_seq];
+      bt_row = reinterpret_cast<const char*>(a.block_tables) + (int64_t)p_seq * a.bt_stride * (bt64 ? 8 : 4);
+    }
+    const int bi = 4 * (up - p_base);
+    n_has = p_nb - bi < 4 ? p_nb - bi : 4;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int bj = bi + (j < n_has ? j : 0);
+      pb[j] = bt64 ? (int)reinterpret_cast<const int64_t*>(bt_row)[bj] : reinterpret_cast<const int*>(bt_row)[bj];
+    }
+  };
+  const int nblocks = (int)a.num_blocks;
+  auto issue = [&](int slot) {
+    const uint32_t kb = slot ? SK4_K1 : SK4_K0, vb = slot ? SK4_V1 : SK4_V0, nb_ = slot ? SK4_N1 : SK4_N0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      pb[j] = min(max(pb[j], 0), nblocks - 1);
+      if (j < n_has) {
+#pragma unroll
+        for (int tp = 0; tp < 2; ++tp) {
+          cp_async16_s(kb + j * 8192 + k_dst + tp * 4096, a.k_packed + ((int64_t)pb[j] * kp_sb + k_src + tp * k_step));
+          cp_async16_s(vb + j * 8192 + v_dst + tp * 4096, a.v_packed + ((int64_t)pb[j] * vp_sb + v_src + tp * v_step));
+        }
+      }
+    }
+    {   // norms: 8 x 512 B, one 16-byte piece per thread
+      const int which = tid >> 5, ch = tid & 31, j = which & 3;
+      if (j < n_has) {
+        const int tok = ch >> 1, half = ch & 1;
+        const int pbj = j == 0 ? pb[0] : j == 1 ? pb[1] : j == 2 ? pb[2] : pb[3];
+        const float* src = (which < 4)
+            ? a.k_norms + ((int64_t)pbj * kn_sb + (int64_t)tok * a.kn_sp + hg * 8 + half * 4)
+            : a.v_norms + ((int64_t)pbj * vn_sb + (int64_t)tok * a.vn_sp + hg * 8 + half * 4);
+        cp_async16_s(nb_ + which * 512 + ch * 16, src);
+      }
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
+    ++up;
+    if (up < u_end) load_pb();             // for the next issue, one iteration from now
+  };
+  load_pb();
+  issue(0);
+  for (int i = tid; i < 256 * 32; i += 256) {
+    const int e = i >> 5, l = i & 31;
+    const uint32_t v = pack_half2(s_cent[e >> 4], s_cent[e & 15]);
+    asm volatile("st.shared.u32 [%0], %1;\n" :: "r"(SK_LUT + e * LUT_STRIDE + l * 4), "r"(v));
+  }
+
+  // ---- consumer: warp = KV head ----
+  const int hl = warp;
+  const int h = hg * 8 + hl;
+  const int G = a.num_q_heads / a.num_kv_heads;
+  const uint32_t lanebase = SK_LUT | (lane * 4);
+  const int kA_off = g * 512 + ((hl ^ (g & 1)) << 6) + 16 * t;
+  int v_off[4];
+  {
+    const int toks[4] = {2 * t, 2 * t + 1, 2 * t + 8, 2 * t + 9};
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      v_off[i] = toks[i] * 512 + (((2 * hl + (g >> 2)) ^ ((toks[i] >> 1) & 3)) << 5) + (g & 3) * 8;
+  }
+  const int n_off = (g * 8 + hl) * 4;      // norm of token g; token g + 8 is 256 bytes further
+
+  uint32_t bq[8][2];
+  float o[8][4];
+  SoftmaxState st{-CUDART_INF_F, -CUDART_INF_F, 0.f, 0.f};
+  int seq_c = -1, c_base = 0, c_end = 0, ctx_c = 0;
+  auto begin_seq = [&](int seq) {
+    seq_c = seq;
+    c_base = s_P[seq]; c_end = s_P[seq + 1];
+    ctx_c = (int)load_index(a.context_lens, a.cl_dtype, seq);
+    const float* qp = a.qrot + ((int64_t)seq * a.num_q_heads + h * G + (g < G ? g : 0)) * 128 + 32 * t;
+    float4 f[8];
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) f[kk] = *reinterpret_cast<const float4*>(qp + 4 * kk);
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      if (g >= G) f[kk] = make_float4(0.f, 0.f, 0.f, 0.f);
+      bq[kk][0] = pack_half2(f[kk].x, f[kk].y);
+      bq[kk][1] = pack_half2(f[kk].z, f[kk].w);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+    st = SoftmaxState{-CUDART_INF_F, -CUDART_INF_F, 0.f, 0.f};
+  };
+  auto end_seq = [&]() {
+    float l0 = st.l0, l1 = st.l1;
+#pragma unroll
+    for (int offs = 4; offs < 32; offs <<= 1) {
+      l0 += __shfl_xor_sync(0xffffffffu, l0, offs);
+      l1 += __shfl_xor_sync(0xffffffffu, l1, offs);
+    }
+    const int part = b - a.sk[S + 2 + seq_c];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int qg = 2 * t + e;
+      if (qg >= G) continue;
+      const int64_t row = (int64_t)seq_c * a.num_q_heads + h * G + qg;
+      float* pa = a.part_acc + (row * a.num_parts + part) * 128;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<float2*>(pa + 16 * g + 2 * j) = make_float2(o[j][e], o[j][2 + e]);
+      if (g == 0) {
+        a.part_ml[(row * a.num_parts + part) * 2] = e ? st.m1 : st.m0;
+        a.part_ml[(row * a.num_parts + part) * 2 + 1] = e ? l1 : l0;
+      }
+    }
+  };
+  begin_seq(seq0);
+
+  for (int it = 0; it < n_it; ++it) {
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();                       // stage `it` has landed; the other slot is free again
+    if (it + 1 < n_it) issue((it + 1) & 1);
+    const int u = u_begin + it;
+    if (u >= c_end) { end_seq(); begin_seq(locate(u, seq_c)); }     // next sequence (rare)
+    const int slot = it & 1;
+    const uint32_t kb = slot ? SK4_K1 : SK4_K0, vb = slot ? SK4_V1 : SK4_V0, nb_ = slot ? SK4_N1 : SK4_N0;
+    const uint32_t va[4] = {vb + v_off[0], vb + v_off[1], vb + v_off[2], vb + v_off[3]};
+    const int rem = ctx_c - 64 * (u - c_base);
+    process_tiles4<4>(lanebase, g, bq, kb + kA_off, va, nb_ + n_off, rem, o, st);
+  }
+  end_seq();
+}
+
 static inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 struct Plan {
@@ -1457,7 +1758,9 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
   pl.context_lens = p->context_lens; pl.cl_dtype = p->cl_dtype; pl.num_seqs = p->num_seqs;
   pl.block_size = p->block_size; pl.grid = plan.sk_grid; pl.sk = persist ? sk : nullptr;
   static const int sk_wph = (getenv("AKV_SK_WPH") && atoi(getenv("AKV_SK_WPH")) == 2) ? 2 : 1;
-  pl.parts_per_cta = sk_wph;
+  static const bool sk4 = getenv("AKV_SK4") != nullptr;       // 4-block stages, four tiles per warp at once
+  pl.parts_per_cta = sk4 ? 1 : sk_wph;
+  pl.blocks_per_stage = sk4 ? 4 : 2;
   akv_qrot_kernel<<<rows + (persist ? 1 : 0), D < 128 ? D : 128, D * sizeof(float), st>>>(
       p->query, p->q_dtype, p->q_stride_seq, p->q_stride_head, p->num_q_heads, D, p->rotation_t,
       p->scale * 1.4426950408889634f, qrot, rows, pl);
@@ -1483,7 +1786,15 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
 
   if (p->ev_kernel_start) cudaEventRecord((cudaEvent_t)p->ev_kernel_start, st);
   if (p->max_blocks_per_seq > 0) {
-    if (persist) {
+    if (persist && sk4) {
+      a.num_parts = plan.sk_grid;
+      merge_parts = a.num_parts;
+      cudaError_t e = cudaFuncSetAttribute(tq4_attn_streamk4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SK4_DYN_SMEM);
+      if (e != cudaSuccess) return fail((int)e, "attention: smem attribute: %s", cudaGetErrorString(e));
+      dim3 grid(plan.sk_grid, p->num_kv_heads / 8);
+      tq4_attn_streamk4_kernel<<<grid, 256, SK4_DYN_SMEM, st>>>(a);
+      if (int rc = check_launch("tq4_attn_streamk4_kernel")) return rc;
+    } else if (persist) {
       a.num_parts = sk_wph * plan.sk_grid;
       merge_parts = a.num_parts;
       static const bool sk_pair = getenv("AKV_SK_NO_PAIR") == nullptr;   // two tiles per warp at once
