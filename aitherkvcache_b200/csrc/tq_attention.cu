@@ -1328,12 +1328,12 @@ tq4_attn_streamk_kernel(AttnArgs a) {
 // code path: four independent score products, one softmax update per 64 tokens, four value
 // products into the same fragments.  Two ring slots of 68 KB; their pieces sit where the fixed
 // lookup-table address leaves room (absolute shared addresses):
-//   [1 KB, 9.5 KB) plan arrays   [9.5 KB, 41.5 KB) slot 0 K   [41.5 KB, 49.5 KB) norms of slots 0, 1
+//   [4 KB, 12.5 KB) plan arrays  [12.5 KB, 44.5 KB) slot 0 K  [44.5 KB, 52.5 KB) norms of slots 0, 1
 //   [64 KB, 128 KB) lookup table [128 KB, 160 KB) slot 1 K    [160 KB, 192 KB) slot 1 V   [192 KB, 224 KB) slot 0 V
 // Blocks missing from the last stage of a sequence are not copied; their tiles are masked.
 // ---------------------------------------------------------------------------
-constexpr uint32_t SK4_PLAN = 1024;
-constexpr uint32_t SK4_K0 = 9728, SK4_N0 = SK4_K0 + 32768, SK4_N1 = SK4_N0 + 4096;
+constexpr uint32_t SK4_PLAN = 4096;        // dynamic shared memory starts at about 1.1 KB (system-reserved 1 KB + statics)
+constexpr uint32_t SK4_K0 = 12800, SK4_N0 = SK4_K0 + 32768, SK4_N1 = SK4_N0 + 4096;
 constexpr uint32_t SK4_K1 = 131072, SK4_V1 = SK4_K1 + 32768, SK4_V0 = SK4_V1 + 32768;
 constexpr int SK4_DYN_SMEM = SK4_V0 + 32768;     // 229376: covers every address above for any start >= 0
 static_assert(SK4_PLAN + (SK_MAX_SEQS + 2) * 4 + SK_MAX_SEQS * 4 <= SK4_K0, "plan arrays overlap the ring");
@@ -1454,6 +1454,10 @@ tq4_attn_streamk4_kernel(AttnArgs a) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int S = a.num_seqs;
+  if (dyn0 > SK4_PLAN) {       // the window below the plan arrays is taken (static + system-reserved bytes)
+    if (tid == 0 && b == 0) printf("tq4_attn_streamk4_kernel: dynamic shared memory starts at %u, above %u\n", dyn0, SK4_PLAN);
+    return;
+  }
   for (int i = tid; i < S + 2; i += 256) s_P[i] = a.sk[i];
   for (int i = tid; i < S; i += 256) s_nb[i] = a.sk[3 * S + 2 + i];
   if (tid < 16) s_cent[tid] = a.centroids[tid];
@@ -1465,7 +1469,7 @@ tq4_attn_streamk4_kernel(AttnArgs a) {
   const int n_it = u_end - u_begin;
 
   auto locate = [&](int u, int hint) {
-    while (u >= s_P[hint + 1]) ++hint;
+    while (hint < S - 1 && u >= s_P[hint + 1]) ++hint;
     return hint;
   };
   int seq0;
@@ -1758,7 +1762,7 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
   pl.context_lens = p->context_lens; pl.cl_dtype = p->cl_dtype; pl.num_seqs = p->num_seqs;
   pl.block_size = p->block_size; pl.grid = plan.sk_grid; pl.sk = persist ? sk : nullptr;
   static const int sk_wph = (getenv("AKV_SK_WPH") && atoi(getenv("AKV_SK_WPH")) == 2) ? 2 : 1;
-  static const bool sk4 = getenv("AKV_SK4") != nullptr;       // 4-block stages, four tiles per warp at once
+  static const bool sk4 = getenv("AKV_NO_SK4") == nullptr;    // 4-block stages, four tiles per warp at once
   pl.parts_per_cta = sk4 ? 1 : sk_wph;
   pl.blocks_per_stage = sk4 ? 4 : 2;
   akv_qrot_kernel<<<rows + (persist ? 1 : 0), D < 128 ? D : 128, D * sizeof(float), st>>>(
