@@ -1407,7 +1407,7 @@ struct akv_hybrid_attn_params {
 
 static void hybrid_plan(int num_seqs, int num_q_heads, int block_size, int max_blocks, int bps_in, int* bps,
                         int* parts, size_t* off_acc, size_t* off_ml, size_t* total) {
-  int b = bps_in > 0 ? bps_in : (1024 + block_size - 1) / block_size;
+  int b = bps_in > 0 ? bps_in : (2048 + block_size - 1) / block_size;   // ~2048 tokens per split
   if (b > max_blocks) b = max_blocks > 0 ? max_blocks : 1;
   const int splits = max_blocks > 0 ? (max_blocks + b - 1) / b : 1;
   *bps = b;

@@ -334,7 +334,11 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
   d[0] = e0; d[1] = e1; d[2] = e2; d[3] = e3;
   return;
 #endif
+#if AKV_LUT_VOLATILE
   asm volatile(
+#else
+  asm(
+#endif
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
       "{%0,%1,%2,%3};\n"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -378,9 +382,21 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   return v;
 }
 
+// Table reads are not volatile: the table is constant once filled (a barrier before the first
+// lookup), and every address depends on tile data read after the barriers, so the compiler may
+// schedule them - and the MMAs they feed - freely.
+__device__ __forceinline__ uint32_t lds32_table(uint32_t addr) {
+  uint32_t v;
+#if AKV_LUT_VOLATILE
+  asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+#else
+  asm("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+#endif
+  return v;
+}
 template <int K>
 __device__ __forceinline__ uint32_t lut4(lut_t lut, uint32_t w, uint32_t lanebase) {
-  return lds32(lut + __byte_perm(w, lanebase, 0x7604 + (K << 4)));
+  return lds32_table(lut + __byte_perm(w, lanebase, 0x7604 + (K << 4)));
 }
 
 template <bool VEC16>

@@ -43,7 +43,7 @@ WORKLOAD = ("paged decode attention, tq-t4nc cache: 16 seqs, ctx U[4096,32768] s
             "head_dim 128, block_size 16, permuted block tables")
 
 
-NCU_TRAFFIC_BYTES = 281_170_000     # dram read + write per launch (ncu: 3.1392 TB/s x 89.568 us, rank-0 workload)
+NCU_TRAFFIC_BYTES = 281_614_000     # dram read + write per launch (ncu: 3.3731 TB/s x 83.488 us, rank-0 workload)
 
 
 def context_lengths(rank=0):
@@ -568,7 +568,7 @@ def main():
             # workload, from the ncu capture summarised in profiles/tq4_attn_streamk_kernel_config1.md
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES if world == 1 else None,
-                         "algorithmic_bytes": kv_bytes, "kernel": "tq4_attn_streamk_kernel",
+                         "algorithmic_bytes": kv_bytes, "kernel": "tq4_attn_streamk4_kernel",
                          "kernel_ms": kernel_ms, "peak_source": peak_src,
                          "frac_of_8TBs_nominal": achieved / 8000.0},
             "clocks": clocks,
