@@ -124,12 +124,12 @@ __global__ void akv_qrot_kernel(const void* __restrict__ q, int q_dtype, int64_t
   __syncthreads();
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int j = 0; j < D; j += 16) {      // 16 loads in flight per round (the matrix sits in L2)
-      float r[16];
+    for (int j = 0; j < D; j += 32) {      // 32 loads in flight per round (the matrix sits in L2)
+      float r[32];
 #pragma unroll
-      for (int k = 0; k < 16; ++k) r[k] = rot_t[(int64_t)(j + k) * D + i];
+      for (int k = 0; k < 32; ++k) r[k] = rot_t[(int64_t)(j + k) * D + i];
 #pragma unroll
-      for (int k = 0; k < 16; ++k) acc[k & 3] = __fmaf_rn(r[k], qs[j + k], acc[k & 3]);
+      for (int k = 0; k < 32; ++k) acc[k & 3] = __fmaf_rn(r[k], qs[j + k], acc[k & 3]);
     }
     qrot[(int64_t)blockIdx.x * D + i] = ((acc[0] + acc[1]) + (acc[2] + acc[3])) * premul;
   }
@@ -217,12 +217,12 @@ __global__ void akv_merge_kernel(MergeArgs a) {
   __syncthreads();
   for (int j = threadIdx.x; j < a.D; j += blockDim.x) {
     float x4[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int i = 0; i < a.D; i += 16) {
-      float r[16];
+    for (int i = 0; i < a.D; i += 32) {
+      float r[32];
 #pragma unroll
-      for (int k = 0; k < 16; ++k) r[k] = a.rot[(int64_t)(i + k) * a.D + j];
+      for (int k = 0; k < 32; ++k) r[k] = a.rot[(int64_t)(i + k) * a.D + j];
 #pragma unroll
-      for (int k = 0; k < 16; ++k) x4[k & 3] = __fmaf_rn(sm[i + k], r[k], x4[k & 3]);
+      for (int k = 0; k < 32; ++k) x4[k & 3] = __fmaf_rn(sm[i + k], r[k], x4[k & 3]);
     }
     store_from_float(a.out, a.out_dtype, seq * a.out_ss + qh * a.out_sh + j, (x4[0] + x4[1]) + (x4[2] + x4[3]));
   }
