@@ -47,6 +47,19 @@ class TQAttnParams(C.Structure):
     ]
 
 
+class TQDecodeStepParams(C.Structure):
+    """Mirror of ``akv_tq_decode_step_params``."""
+    _fields_ = [
+        ("key", c_vp), ("value", c_vp), ("kv_dtype", c_int),
+        ("num_tokens", c_i64),
+        ("k_stride_tok", c_i64), ("k_stride_head", c_i64), ("v_stride_tok", c_i64), ("v_stride_head", c_i64),
+        ("slot_mapping", c_vp),
+        ("boundaries", c_vp),
+        ("max_blocks", c_i64),
+        ("attn", TQAttnParams),
+    ]
+
+
 class HybridTables(C.Structure):
     """Mirror of ``akv_hybrid_tables``."""
     _fields_ = [
@@ -108,6 +121,7 @@ _SIGNATURES = {
                                  c_i64, c_vp, c_i64, c_i64, c_i64, c_int, c_vp, c_vp, c_int, c_i64, c_vp]),
     "akv_tq_paged_attn_workspace_bytes": (C.c_size_t, [c_int] * 8),
     "akv_tq_paged_attn": (c_int, [C.POINTER(TQAttnParams)]),
+    "akv_tq_decode_step": (c_int, [C.POINTER(TQDecodeStepParams)]),
     "akv_tq_paged_attn_static_scratch_bytes": (C.c_size_t, []),
     "akv_tq_paged_attn_static": (c_int, [C.POINTER(TQAttnParams)]),
     "akv_hybrid_encode": (c_int, [c_vp, c_int, c_i64, c_i64, C.POINTER(HybridTables), c_vp, c_i64, c_vp]),

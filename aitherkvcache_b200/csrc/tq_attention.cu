@@ -1872,6 +1872,47 @@ AKV_EXPORT int akv_tq_paged_attn(const akv_tq_attn_params* p) {
   return run_tq_attn(p, p->workspace, p->workspace_bytes);
 }
 
+// Mirror of akv_tq_decode_step_params in include/akv_b200.h.
+struct akv_tq_decode_step_params {
+  const void* key; const void* value; int kv_dtype;
+  int64_t num_tokens;
+  int64_t k_stride_tok, k_stride_head, v_stride_tok, v_stride_head;
+  const int64_t* slot_mapping;
+  const float* boundaries;
+  int64_t max_blocks;
+  akv_tq_attn_params attn;
+};
+
+extern "C" int akv_tq_kv_update(const void* x, int x_dtype, int64_t num_tokens, int num_kv_heads, int head_dim,
+                                int64_t x_stride_tok, int64_t x_stride_head, const int64_t* slot_mapping,
+                                uint8_t* out_packed, int64_t p_stride_blk, int64_t p_stride_pos,
+                                int64_t p_stride_head, float* out_norms, int64_t n_stride_blk,
+                                int64_t n_stride_pos, int64_t n_stride_head, int bits, const float* rotation_t,
+                                const float* boundaries, int block_size, int64_t max_blocks, void* stream);
+
+// One serving step in one call: write the new tokens' K and V into the packed cache, then attend.
+AKV_EXPORT int akv_tq_decode_step(const akv_tq_decode_step_params* p) {
+  if (!p) return fail(AKV_ERR_ARG, "null params");
+  const akv_tq_attn_params& a = p->attn;
+  if (p->num_tokens > 0) {
+    if (!p->key || !p->value || !p->slot_mapping || !p->boundaries)
+      return fail(AKV_ERR_ARG, "akv_tq_decode_step: null pointer");
+    int rc = akv_tq_kv_update(p->key, p->kv_dtype, p->num_tokens, a.num_kv_heads, a.head_dim, p->k_stride_tok,
+                              p->k_stride_head, p->slot_mapping, const_cast<uint8_t*>(a.k_packed), a.kp_stride_blk,
+                              a.kp_stride_pos, a.kp_stride_head, const_cast<float*>(a.k_norms), a.kn_stride_blk,
+                              a.kn_stride_pos, a.kn_stride_head, a.bits, a.rotation_t, p->boundaries, a.block_size,
+                              p->max_blocks, a.stream);
+    if (rc) return rc;
+    rc = akv_tq_kv_update(p->value, p->kv_dtype, p->num_tokens, a.num_kv_heads, a.head_dim, p->v_stride_tok,
+                          p->v_stride_head, p->slot_mapping, const_cast<uint8_t*>(a.v_packed), a.vp_stride_blk,
+                          a.vp_stride_pos, a.vp_stride_head, const_cast<float*>(a.v_norms), a.vn_stride_blk,
+                          a.vn_stride_pos, a.vn_stride_head, a.bits, a.rotation_t, p->boundaries, a.block_size,
+                          p->max_blocks, a.stream);
+    if (rc) return rc;
+  }
+  return run_tq_attn(&p->attn, a.workspace, a.workspace_bytes);
+}
+
 // ---------------------------------------------------------------------------
 // Allocation-free variant of akv_tq_paged_attn.
 //

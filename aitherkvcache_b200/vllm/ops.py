@@ -17,9 +17,12 @@ uses 1/sqrt(head_size)).
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Dict, Tuple
 
 import torch
+
+from .. import _lib
 
 from ..fused_attention import TQPagedAttention
 from ..fused_kv_update import fused_tq4_kv_update
@@ -28,6 +31,7 @@ from ..quantizer import TurboQuant
 _quantizers: Dict[int, TurboQuant] = {}        # head_size -> quantiser
 _attn: Dict[Tuple[int, int, int], TQPagedAttention] = {}   # (head_size, layer, num_heads) -> attention
 _registered = False
+_step_state: Dict[tuple, object] = {}            # cached argument blocks of decode_step
 
 
 def init_quantizer(head_size: int, bits: int = 4, device: str = "cuda", **kw) -> TurboQuant:
@@ -36,6 +40,7 @@ def init_quantizer(head_size: int, bits: int = 4, device: str = "cuda", **kw) ->
     _quantizers[head_size] = tq
     for key in [k for k in _attn if k[0] == head_size]:
         del _attn[key]
+    _step_state.clear()
     return tq
 
 
@@ -46,9 +51,8 @@ def _get_tq(head_size: int) -> Tuple[TurboQuant, int]:
     return tq, tq._packed_dim
 
 
-def decode_step(query, key, value, kv_cache, output, k_norms, v_norms, slot_mapping, block_table,
-                seq_lens, layer_idx: int, num_heads: int, num_kv_heads: int, head_size: int,
-                scale: float, num_actual: int) -> torch.Tensor:
+def _decode_step_slow(query, key, value, kv_cache, output, k_norms, v_norms, slot_mapping, block_table,
+                      seq_lens, layer_idx, num_heads, num_kv_heads, head_size, scale, num_actual):
     tq, pd = _get_tq(head_size)
     key_cache, value_cache = kv_cache[:, 0], kv_cache[:, 1]
     block_size = key_cache.shape[1]
@@ -63,6 +67,91 @@ def decode_step(query, key, value, kv_cache, output, k_norms, v_norms, slot_mapp
         _attn[(head_size, layer_idx, num_heads)] = attn
     attn.forward(query[:num_actual], kc, kn, vc, vn, block_table, seq_lens, block_size=block_size,
                  num_kv_heads=num_kv_heads, out=output[:num_actual], scale=scale)
+    return output.clone()
+
+
+def decode_step(query, key, value, kv_cache, output, k_norms, v_norms, slot_mapping, block_table,
+                seq_lens, layer_idx: int, num_heads: int, num_kv_heads: int, head_size: int,
+                scale: float, num_actual: int) -> torch.Tensor:
+    """Body of ``tq::decode_step``: one call into ``akv_tq_decode_step`` (both cache writes and the
+    attention) with an argument block that is reused while the caller keeps its cache, norm and
+    output buffers; anything unusual (strided last dimensions, other index dtypes) takes the
+    step-by-step path above."""
+    fast = (key.dtype == value.dtype and key.dtype in _lib._FLOAT_CODES and query.dtype in _lib._FLOAT_CODES
+            and key.stride(-1) == 1 and value.stride(-1) == 1 and query.stride(-1) == 1
+            and slot_mapping.dtype == torch.int64 and slot_mapping.is_contiguous()
+            and block_table.dim() == 2 and block_table.stride(-1) == 1 and seq_lens.is_contiguous()
+            and block_table.dtype in _lib._INDEX_CODES and seq_lens.dtype in _lib._INDEX_CODES
+            and output.dtype in _lib._FLOAT_CODES and output.stride(-1) == 1
+            and query.is_cuda and kv_cache.is_cuda and key.shape[0] > 0 and num_actual > 0)
+    if not fast:
+        return _decode_step_slow(query, key, value, kv_cache, output, k_norms, v_norms, slot_mapping,
+                                 block_table, seq_lens, layer_idx, num_heads, num_kv_heads, head_size,
+                                 scale, num_actual)
+    tq, pd = _get_tq(head_size)
+    dev = query.device
+    state_key = (kv_cache.data_ptr(), tuple(kv_cache.shape), tuple(kv_cache.stride()), k_norms.data_ptr(),
+                 v_norms.data_ptr(), tuple(k_norms.shape), layer_idx, num_heads, num_kv_heads, head_size,
+                 num_actual, block_table.shape[1], tq.rotation.data_ptr(), tq.rotation_T.data_ptr(),
+                 tq.centroids.data_ptr(), tq.boundaries_inner.data_ptr())
+    st = _step_state.get(state_key)
+    if st is None:
+        if kv_cache.dtype != torch.uint8 or kv_cache.stride(-1) != 1:
+            raise ValueError("kv_cache must be uint8 with a contiguous last dimension")
+        if k_norms.dtype != torch.float32 or v_norms.dtype != torch.float32:
+            raise TypeError("norm tensors must be float32")
+        attn = _attn.get((head_size, layer_idx, num_heads))
+        if attn is None:
+            attn = TQPagedAttention(tq, num_heads)
+            _attn[(head_size, layer_idx, num_heads)] = attn
+        kc, vc = kv_cache[:, 0, :, :, :pd], kv_cache[:, 1, :, :, :pd]
+        kn, vn = k_norms[layer_idx], v_norms[layer_idx]
+        block_size = kv_cache.shape[2]
+        L = _lib.lib()
+        nbytes = L.akv_tq_paged_attn_workspace_bytes(num_actual, num_heads, num_kv_heads, head_size, tq.bits,
+                                                     block_size, block_table.shape[1], attn.SPLITK_BLOCKS)
+        ws = attn._get_workspace(nbytes, dev)
+        p = _lib.TQDecodeStepParams()
+        p.boundaries = tq.boundaries_inner.data_ptr()
+        p.max_blocks = kv_cache.shape[0]
+        a = p.attn
+        a.k_packed, a.v_packed = kc.data_ptr(), vc.data_ptr()
+        a.kp_stride_blk, a.kp_stride_pos, a.kp_stride_head = kc.stride(0), kc.stride(1), kc.stride(2)
+        a.vp_stride_blk, a.vp_stride_pos, a.vp_stride_head = vc.stride(0), vc.stride(1), vc.stride(2)
+        a.k_norms, a.v_norms = kn.data_ptr(), vn.data_ptr()
+        a.kn_stride_blk, a.kn_stride_pos, a.kn_stride_head = kn.stride(0), kn.stride(1), kn.stride(2)
+        a.vn_stride_blk, a.vn_stride_pos, a.vn_stride_head = vn.stride(0), vn.stride(1), vn.stride(2)
+        a.num_seqs, a.num_q_heads, a.num_kv_heads, a.head_dim = num_actual, num_heads, num_kv_heads, head_size
+        a.block_size, a.max_blocks_per_seq, a.num_blocks = block_size, block_table.shape[1], kv_cache.shape[0]
+        a.bits = tq.bits
+        a.rotation, a.rotation_t, a.centroids = (tq.rotation.data_ptr(), tq.rotation_T.data_ptr(),
+                                                 tq.centroids.data_ptr())
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        a.blocks_per_split = attn.SPLITK_BLOCKS
+        st = (p, ws, (kc, vc, kn, vn))
+        _step_state[state_key] = st
+    p = st[0]
+    a = p.attn
+    p.key, p.value, p.kv_dtype = key.data_ptr(), value.data_ptr(), _lib._FLOAT_CODES[key.dtype]
+    p.num_tokens = key.shape[0]
+    p.k_stride_tok, p.k_stride_head = key.stride(0), key.stride(1)
+    p.v_stride_tok, p.v_stride_head = value.stride(0), value.stride(1)
+    p.slot_mapping = slot_mapping.data_ptr()
+    a.query, a.q_dtype = query.data_ptr(), _lib._FLOAT_CODES[query.dtype]
+    a.q_stride_seq, a.q_stride_head = query.stride(0), query.stride(1)
+    a.block_tables, a.bt_dtype, a.bt_stride_seq = (block_table.data_ptr(), _lib._INDEX_CODES[block_table.dtype],
+                                                   block_table.stride(0))
+    a.context_lens, a.cl_dtype = seq_lens.data_ptr(), _lib._INDEX_CODES[seq_lens.dtype]
+    a.scale = float(scale)
+    a.out, a.out_dtype = output.data_ptr(), _lib._FLOAT_CODES[output.dtype]
+    a.out_stride_seq, a.out_stride_head = output.stride(0), output.stride(1)
+    a.stream = torch.cuda.current_stream(dev).cuda_stream
+    if torch.cuda.current_device() == dev.index:
+        rc = _lib.lib().akv_tq_decode_step(ctypes.byref(p))
+    else:
+        with torch.cuda.device(dev):
+            rc = _lib.lib().akv_tq_decode_step(ctypes.byref(p))
+    _lib.check(rc, "akv_tq_decode_step")
     return output.clone()
 
 

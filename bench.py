@@ -515,11 +515,26 @@ def main():
     }
     out_host = torch.empty(NUM_SEQS, H_Q, D, dtype=torch.float16).pin_memory()
     out_dev = torch.empty(NUM_SEQS, H_Q, D, dtype=torch.float16, device=dev)
-    h2d = sum(t.numel() * t.element_size() for t in host.values())
     d2h = out_host.numel() * out_host.element_size()
 
+    # the step's inputs travel as one pinned staging buffer and one host-to-device copy; the typed
+    # device views over it are made once
+    offs, total = {}, 0
+    for k_, v_ in host.items():
+        offs[k_] = total
+        total += (v_.numel() * v_.element_size() + 255) // 256 * 256
+    host_buf = torch.empty(total, dtype=torch.uint8).pin_memory()
+    dev_buf = torch.empty(total, dtype=torch.uint8, device=dev)
+    d = {}
+    for k_, v_ in host.items():
+        n = v_.numel() * v_.element_size()
+        host_buf[offs[k_]:offs[k_] + n].view(v_.dtype).view(v_.shape).copy_(v_)
+        d[k_] = dev_buf[offs[k_]:offs[k_] + n].view(v_.dtype).view(v_.shape)
+
+    h2d = total    # bytes of the staging buffer copied every step (payload padded to 256-byte pieces)
+
     def e2e_step():
-        d = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
+        dev_buf.copy_(host_buf, non_blocking=True)
         res = torch.ops.tq.decode_step(d["query"], d["key"], d["value"], kv_cache, out_dev, k_norms, v_norms,
                                        d["slot_mapping"], d["block_table"], d["seq_lens"], 0, H_Q, H_KV, D,
                                        1.0 / math.sqrt(D), NUM_SEQS)

@@ -118,6 +118,26 @@ size_t akv_tq_paged_attn_workspace_bytes(int num_seqs, int num_q_heads, int num_
                                          int max_blocks_per_seq, int blocks_per_split);
 int akv_tq_paged_attn(const akv_tq_attn_params* params);
 
+/* One decode step of the serving path in a single call: encode the new tokens'
+ * key and value ([num_tokens, num_kv_heads, head_dim], one dtype) into the packed
+ * cache named by attn.k_packed / k_norms / v_packed / v_norms (akv_tq_kv_update
+ * twice, with attn.bits, attn.rotation_t, attn.block_size), then run
+ * akv_tq_paged_attn(&attn) over the updated cache.  Replaces the body of the
+ * reference's tq::decode_step op (aither_kvcache/vllm/hooks.py:150-195:
+ * encode + index-put of K and V, then TQPagedAttention.forward).  max_blocks
+ * bounds the slots that are written (0 is not allowed: pass the number of cache
+ * blocks).  Nothing is allocated and nothing synchronises. */
+typedef struct akv_tq_decode_step_params {
+  const void* key; const void* value; int kv_dtype;
+  int64_t num_tokens;
+  int64_t k_stride_tok, k_stride_head, v_stride_tok, v_stride_head;
+  const int64_t* slot_mapping;
+  const float* boundaries;
+  int64_t max_blocks;
+  akv_tq_attn_params attn;
+} akv_tq_decode_step_params;
+int akv_tq_decode_step(const akv_tq_decode_step_params* params);
+
 /* akv_tq_paged_attn without a caller-supplied workspace and without any device
  * allocation.  It has no counterpart in the reference.  It is for callers that
  * cannot allocate around the call - an engine whose memory is fully committed to

@@ -65,6 +65,39 @@ def test_decode_step_op(bits):
     assert np.abs(out[:S].float().cpu().numpy() - ref).max() < 2e-3
 
 
+def test_decode_step_single_call_matches_stepwise_path():
+    """The one-call entry point and the step-by-step path (taken here through an int32 slot mapping)
+    write the same cache bytes and return the same output; the cached argument block survives a
+    second step with different inputs."""
+    from aitherkvcache_b200.vllm import ops
+    H, QH, ctx = 8, 32, [300, 17, 64]
+    outs, caches = [], []
+    for slot_dtype in (torch.int64, torch.int32):
+        t, d, kv, kn, vn, q, key, val, slots = _setup_decode(4, H, QH, ctx, 77)
+        tq = ops.init_quantizer(128, bits=4)
+        tq.rotation = torch.from_numpy(t["rotation"]).cuda()
+        assert ops.register_custom_ops()
+        S = len(ctx)
+        out = torch.zeros(S + 2, QH, 128, dtype=torch.float16, device="cuda")
+        bt = torch.from_numpy(d["block_tables"]).cuda()
+        sl = torch.tensor(ctx, dtype=torch.int32, device="cuda")
+        res = []
+        for step in range(2):
+            g = torch.Generator().manual_seed(500 + step)
+            qq = torch.randn(S + 2, QH, 128, generator=g).half().cuda()
+            kk = torch.randn(S, H, 128, generator=g).half().cuda()
+            vv = torch.randn(S, H, 128, generator=g).half().cuda()
+            res.append(torch.ops.tq.decode_step(qq, kk, vv, kv, out, kn, vn, slots.to(slot_dtype).cuda(), bt, sl,
+                                                0, QH, H, 128, 1.0 / math.sqrt(128), S).clone())
+        outs.append(res)
+        caches.append((kv.clone(), kn.clone(), vn.clone()))
+    for a, b in zip(outs[0], outs[1]):
+        assert torch.equal(a, b)
+    for a, b in zip(caches[0], caches[1]):
+        assert torch.equal(a, b)
+    assert not torch.equal(outs[0][0], outs[0][1])
+
+
 def test_hybrid_decode_step_op():
     from aitherkvcache_b200.vllm import ops
     g = load_golden("hybrid_tq35.npz")
