@@ -1640,6 +1640,333 @@ tq4_attn_streamk4_kernel(AttnArgs a) {
   end_seq();
 }
 
+// ---------------------------------------------------------------------------
+// The persistent 4-block-stage kernel for 3-bit and 2-bit codes.
+//
+// Same schedule, ring slots and plan as tq4_attn_streamk4_kernel.  Token rows of a block are
+// 8 heads x PD bytes (PD = 48 or 32); they are copied in 16-byte pieces into rows of a padded pitch
+// (400 / 288 bytes) instead of an XOR swizzle: with those pitches the 12-byte (3-bit) and 8-byte
+// (2-bit) K fragment reads of the 8 tokens x 4 dim-quarters of a warp fall on distinct banks.
+// Tables at absolute shared address 64 KB: 3-bit - 64 entries x 128 B, a 6-bit code pair -> half2;
+// 2-bit - 256 entries x 256 B, a byte of four codes -> four halves.  A warp runs the four tiles of
+// its head with one softmax update per 64 tokens; scores are built tile by tile (each tile's 32
+// natural-order fragments are transient), the value products likewise.
+// ---------------------------------------------------------------------------
+template <int BITS> struct LowBit {
+  static constexpr int PD = 16 * BITS;                   // packed bytes per (token, head)
+  static constexpr int ROW = 8 * PD;                     // bytes of a token row (8 heads)
+  static constexpr int PITCH = BITS == 3 ? 400 : 288;    // padded row pitch in shared memory
+  static constexpr int BLK = 16 * PITCH;                 // one block's K (or V) in shared memory
+  static constexpr int PPT = ROW / 16;                   // 16-byte pieces per token row
+};
+
+// k-tile fragments of one token in natural order from its 4*BITS packed bytes at `addr`
+// (n[p] = half2(dim 32t+2p, 32t+2p+1)); lb4 / lb8 = table base | lane*4 / lane*8.
+template <int BITS>
+__device__ __forceinline__ void lowbit_k_fragments(uint32_t addr, uint32_t lb4, uint32_t lb8, uint32_t (&n)[16]) {
+  if constexpr (BITS == 3) {
+    const uint32_t B[3] = {bswap32(lds32(addr)), bswap32(lds32(addr + 4)), bswap32(lds32(addr + 8))};
+    n[0] = lut3<0>(0, B, lb4);   n[1] = lut3<1>(0, B, lb4);   n[2] = lut3<2>(0, B, lb4);   n[3] = lut3<3>(0, B, lb4);
+    n[4] = lut3<4>(0, B, lb4);   n[5] = lut3<5>(0, B, lb4);   n[6] = lut3<6>(0, B, lb4);   n[7] = lut3<7>(0, B, lb4);
+    n[8] = lut3<8>(0, B, lb4);   n[9] = lut3<9>(0, B, lb4);   n[10] = lut3<10>(0, B, lb4); n[11] = lut3<11>(0, B, lb4);
+    n[12] = lut3<12>(0, B, lb4); n[13] = lut3<13>(0, B, lb4); n[14] = lut3<14>(0, B, lb4); n[15] = lut3<15>(0, B, lb4);
+  } else {
+    const uint2 w = lds64(addr);
+    uint2 r;
+    r = lut2<0>(0, w.x, lb8); n[0] = r.x;  n[1] = r.y;
+    r = lut2<1>(0, w.x, lb8); n[2] = r.x;  n[3] = r.y;
+    r = lut2<2>(0, w.x, lb8); n[4] = r.x;  n[5] = r.y;
+    r = lut2<3>(0, w.x, lb8); n[6] = r.x;  n[7] = r.y;
+    r = lut2<0>(0, w.y, lb8); n[8] = r.x;  n[9] = r.y;
+    r = lut2<1>(0, w.y, lb8); n[10] = r.x; n[11] = r.y;
+    r = lut2<2>(0, w.y, lb8); n[12] = r.x; n[13] = r.y;
+    r = lut2<3>(0, w.y, lb8); n[14] = r.x; n[15] = r.y;
+  }
+}
+
+// value fragments of one token: n[j] = half2(dim 16g+2j, 16g+2j+1), from its 2*BITS bytes at addr
+// (3-bit: the 6 bytes start 0 or 2 bytes into the aligned word at addr; sh = 8 * that offset)
+template <int BITS>
+__device__ __forceinline__ void lowbit_v_fragments(uint32_t addr, uint32_t sh, uint32_t lb4, uint32_t lb8,
+                                                   uint32_t (&n)[8]) {
+  if constexpr (BITS == 3) {
+    const uint32_t wa = lds32(addr), wb = lds32(addr + 4);
+    const uint32_t w0 = __funnelshift_r(wa, wb, sh), w1 = wb >> sh;
+    const uint32_t B[2] = {bswap32(w0), __byte_perm(w1, 0, 0x0144)};
+    n[0] = lut3<0>(0, B, lb4); n[1] = lut3<1>(0, B, lb4); n[2] = lut3<2>(0, B, lb4); n[3] = lut3<3>(0, B, lb4);
+    n[4] = lut3<4>(0, B, lb4); n[5] = lut3<5>(0, B, lb4); n[6] = lut3<6>(0, B, lb4); n[7] = lut3<7>(0, B, lb4);
+  } else {
+    const uint32_t w = lds32(addr);
+    uint2 r;
+    r = lut2<0>(0, w, lb8); n[0] = r.x; n[1] = r.y;
+    r = lut2<1>(0, w, lb8); n[2] = r.x; n[3] = r.y;
+    r = lut2<2>(0, w, lb8); n[4] = r.x; n[5] = r.y;
+    r = lut2<3>(0, w, lb8); n[6] = r.x; n[7] = r.y;
+  }
+}
+
+template <int BITS>
+__global__ void __launch_bounds__(256, 1)
+tq_attn_streamk4_lowbit_kernel(AttnArgs a) {
+  using LB = LowBit<BITS>;
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ float s_cent[16];
+  const uint32_t dyn0 = (uint32_t)__cvta_generic_to_shared(smem);
+  int* s_P = reinterpret_cast<int*>(smem + (SK4_PLAN - dyn0));
+  int* s_nb = s_P + (SK_MAX_SEQS + 2);
+  const int b = blockIdx.x, hg = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int S = a.num_seqs;
+  if (dyn0 > SK4_PLAN) {
+    if (tid == 0 && b == 0) printf("tq_attn_streamk4_lowbit_kernel: dynamic shared memory starts at %u, above %u\n", dyn0, SK4_PLAN);
+    return;
+  }
+  for (int i = tid; i < S + 2; i += 256) s_P[i] = a.sk[i];
+  for (int i = tid; i < S; i += 256) s_nb[i] = a.sk[3 * S + 2 + i];
+  if (tid < 16) s_cent[tid] = tid < (1 << BITS) ? a.centroids[tid] : 0.f;
+  __syncthreads();
+  const int T = s_P[S], chunk = s_P[S + 1];
+  const int u_begin = b * chunk;
+  const int u_end = (u_begin + chunk < T) ? u_begin + chunk : T;
+  if (u_begin >= u_end) return;            // uniform for the CTA
+  const int n_it = u_end - u_begin;
+
+  auto locate = [&](int u, int hint) {
+    while (hint < S - 1 && u >= s_P[hint + 1]) ++hint;
+    return hint;
+  };
+  int seq0;
+  {
+    int lo = 0, hi = S - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (s_P[mid] <= u_begin) lo = mid; else hi = mid - 1;
+    }
+    seq0 = locate(u_begin, lo);
+  }
+
+  // ---- producer: 16 x PPT pieces of 16 bytes per block and side, spread over the 256 threads ----
+  const int kp_sb = (int)a.kp_sb, vp_sb = (int)a.vp_sb, kn_sb = (int)a.kn_sb, vn_sb = (int)a.vn_sb;
+  const bool bt64 = a.bt_dtype == AKV_I64;
+  int up = u_begin;
+  int p_seq = seq0 - 1, p_base = 0, p_end = u_begin, p_nb = 0;
+  const char* bt_row = nullptr;
+  int pb[4] = {0, 0, 0, 0};
+  int n_has = 0;
+  auto load_pb = [&]() {
+    if (up >= p_end) {
+      p_seq = locate(up, p_seq < 0 ? 0 : p_seq);
+      p_base = s_P[p_seq]; p_end = s_P[p_seq + 1]; p_nb = s_nb[p_seq];
+      bt_row = reinterpret_cast<const char*>(a.block_tables) + (int64_t)p_seq * a.bt_stride * (bt64 ? 8 : 4);
+    }
+    const int bi = 4 * (up - p_base);
+    n_has = p_nb - bi < 4 ? p_nb - bi : 4;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int bj = bi + (j < n_has ? j : 0);
+      pb[j] = bt64 ? (int)reinterpret_cast<const int64_t*>(bt_row)[bj] : reinterpret_cast<const int*>(bt_row)[bj];
+    }
+  };
+  const int nblocks = (int)a.num_blocks;
+  constexpr int PIECES = 16 * LB::PPT;      // per block and side
+  auto issue = [&](int slot) {
+    const uint32_t kb = slot ? SK4_K1 : SK4_K0, vb = slot ? SK4_V1 : SK4_V0, nb_ = slot ? SK4_N1 : SK4_N0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      pb[j] = min(max(pb[j], 0), nblocks - 1);
+      if (j < n_has) {
+        for (int e = tid; e < PIECES; e += 256) {
+          const int tok = e / LB::PPT, pc = e - tok * LB::PPT;
+          const uint32_t d = (uint32_t)(j * LB::BLK + tok * LB::PITCH + pc * 16);
+          cp_async16_s(kb + d, a.k_packed + ((int64_t)pb[j] * kp_sb + (int64_t)tok * a.kp_sp + hg * LB::ROW + pc * 16));
+          cp_async16_s(vb + d, a.v_packed + ((int64_t)pb[j] * vp_sb + (int64_t)tok * a.vp_sp + hg * LB::ROW + pc * 16));
+        }
+      }
+    }
+    {
+      const int which = tid >> 5, ch = tid & 31, j = which & 3;
+      if (j < n_has) {
+        const int tok = ch >> 1, half = ch & 1;
+        const int pbj = j == 0 ? pb[0] : j == 1 ? pb[1] : j == 2 ? pb[2] : pb[3];
+        const float* src = (which < 4)
+            ? a.k_norms + ((int64_t)pbj * kn_sb + (int64_t)tok * a.kn_sp + hg * 8 + half * 4)
+            : a.v_norms + ((int64_t)pbj * vn_sb + (int64_t)tok * a.vn_sp + hg * 8 + half * 4);
+        cp_async16_s(nb_ + which * 512 + ch * 16, src);
+      }
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
+    ++up;
+    if (up < u_end) load_pb();
+  };
+  load_pb();
+  issue(0);
+  if constexpr (BITS == 3) {          // 6 bits -> half2(c[hi 3 bits], c[lo 3 bits])
+    for (int i = tid; i < 64 * 32; i += 256) {
+      const int e = i >> 5, l = i & 31;
+      const uint32_t v = pack_half2(s_cent[e >> 3], s_cent[e & 7]);
+      asm volatile("st.shared.u32 [%0], %1;\n" :: "r"(SK_LUT + e * LUT3_STRIDE + l * 4), "r"(v));
+    }
+  } else {                            // byte -> four halves
+    for (int i = tid; i < 256 * 32; i += 256) {
+      const int e = i >> 5, l = i & 31;
+      const uint32_t v0 = pack_half2(s_cent[e >> 6], s_cent[(e >> 4) & 3]);
+      const uint32_t v1 = pack_half2(s_cent[(e >> 2) & 3], s_cent[e & 3]);
+      asm volatile("st.shared.v2.u32 [%0], {%1,%2};\n" :: "r"(SK_LUT + e * LUT_STRIDE + l * 8), "r"(v0), "r"(v1));
+    }
+  }
+
+  // ---- consumer: warp = KV head ----
+  const int hl = warp;
+  const int h = hg * 8 + hl;
+  const int G = a.num_q_heads / a.num_kv_heads;
+  const uint32_t lb4 = SK_LUT | (lane * 4), lb8 = SK_LUT | (lane * 8);
+  const uint32_t kA_off = (uint32_t)(g * LB::PITCH + hl * LB::PD + 4 * BITS * t);
+  uint32_t v_off[4];
+  const uint32_t v_byte = (uint32_t)(hl * LB::PD + 2 * BITS * g);
+  const uint32_t v_sh = BITS == 3 ? 8u * (v_byte & 3u) : 0u;
+  {
+    const int toks[4] = {2 * t, 2 * t + 1, 2 * t + 8, 2 * t + 9};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v_off[i] = (uint32_t)(toks[i] * LB::PITCH) + (BITS == 3 ? (v_byte & ~3u) : v_byte);
+  }
+  const int n_off = (g * 8 + hl) * 4;
+
+  uint32_t bq[8][2];
+  float o[8][4];
+  SoftmaxState st{-CUDART_INF_F, -CUDART_INF_F, 0.f, 0.f};
+  int seq_c = -1, c_base = 0, c_end = 0, ctx_c = 0;
+  auto begin_seq = [&](int seq) {
+    seq_c = seq;
+    c_base = s_P[seq]; c_end = s_P[seq + 1];
+    ctx_c = (int)load_index(a.context_lens, a.cl_dtype, seq);
+    const float* qp = a.qrot + ((int64_t)seq * a.num_q_heads + h * G + (g < G ? g : 0)) * 128 + 32 * t;
+    float4 f[8];
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) f[kk] = *reinterpret_cast<const float4*>(qp + 4 * kk);
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      if (g >= G) f[kk] = make_float4(0.f, 0.f, 0.f, 0.f);
+      bq[kk][0] = pack_half2(f[kk].x, f[kk].y);
+      bq[kk][1] = pack_half2(f[kk].z, f[kk].w);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+    st = SoftmaxState{-CUDART_INF_F, -CUDART_INF_F, 0.f, 0.f};
+  };
+  auto end_seq = [&]() {
+    float l0 = st.l0, l1 = st.l1;
+#pragma unroll
+    for (int offs = 4; offs < 32; offs <<= 1) {
+      l0 += __shfl_xor_sync(0xffffffffu, l0, offs);
+      l1 += __shfl_xor_sync(0xffffffffu, l1, offs);
+    }
+    const int part = b - a.sk[S + 2 + seq_c];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int qg = 2 * t + e;
+      if (qg >= G) continue;
+      const int64_t row = (int64_t)seq_c * a.num_q_heads + h * G + qg;
+      float* pa = a.part_acc + (row * a.num_parts + part) * 128;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<float2*>(pa + 16 * g + 2 * j) = make_float2(o[j][e], o[j][2 + e]);
+      if (g == 0) {
+        a.part_ml[(row * a.num_parts + part) * 2] = e ? st.m1 : st.m0;
+        a.part_ml[(row * a.num_parts + part) * 2 + 1] = e ? l1 : l0;
+      }
+    }
+  };
+  begin_seq(seq0);
+
+  for (int it = 0; it < n_it; ++it) {
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();
+    if (it + 1 < n_it) issue((it + 1) & 1);
+    const int u = u_begin + it;
+    if (u >= c_end) { end_seq(); begin_seq(locate(u, seq_c)); }
+    const int slot = it & 1;
+    const uint32_t kb = slot ? SK4_K1 : SK4_K0, vb = slot ? SK4_V1 : SK4_V0, nb_ = (slot ? SK4_N1 : SK4_N0) + n_off;
+    const int rem = ctx_c - 64 * (u - c_base);
+
+    // ---- scores of the four tiles ----
+    float s[4][4];
+    float nv[4][2];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t na[16], nb2[16];
+      lowbit_k_fragments<BITS>(kb + j * LB::BLK + kA_off, lb4, lb8, na);
+      lowbit_k_fragments<BITS>(kb + j * LB::BLK + kA_off + 8 * LB::PITCH, lb4, lb8, nb2);
+      float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int kk = 0; kk < 8; kk += 2) {
+        mma16816(sa, na[2 * kk], nb2[2 * kk], na[2 * kk + 1], nb2[2 * kk + 1], bq[kk][0], bq[kk][1]);
+        mma16816(sb, na[2 * kk + 2], nb2[2 * kk + 2], na[2 * kk + 3], nb2[2 * kk + 3], bq[kk + 1][0], bq[kk + 1][1]);
+      }
+      const float nkA = __uint_as_float(lds32(nb_ + j * 512)), nkB = __uint_as_float(lds32(nb_ + j * 512 + 256));
+      nv[j][0] = __uint_as_float(lds32(nb_ + 2048 + j * 512));
+      nv[j][1] = __uint_as_float(lds32(nb_ + 2048 + j * 512 + 256));
+      s[j][0] = (sa[0] + sb[0]) * nkA; s[j][1] = (sa[1] + sb[1]) * nkA;
+      s[j][2] = (sa[2] + sb[2]) * nkB; s[j][3] = (sa[3] + sb[3]) * nkB;
+    }
+    if (rem < 64) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int nvld = rem - 16 * j;
+        if (g >= nvld) { s[j][0] = -CUDART_INF_F; s[j][1] = -CUDART_INF_F; nv[j][0] = 0.f; }
+        if (g + 8 >= nvld) { s[j][2] = -CUDART_INF_F; s[j][3] = -CUDART_INF_F; nv[j][1] = 0.f; }
+      }
+    }
+    // ---- one softmax update for the 64 tokens ----
+    float mx0 = fmaxf(s[0][0], s[0][2]), mx1 = fmaxf(s[0][1], s[0][3]);
+#pragma unroll
+    for (int j = 1; j < 4; ++j) {
+      mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][2]));
+      mx1 = fmaxf(mx1, fmaxf(s[j][1], s[j][3]));
+    }
+#pragma unroll
+    for (int off = 4; off < 32; off <<= 1) {
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+    }
+    const float mn0 = fmaxf(st.m0, mx0), mn1 = fmaxf(st.m1, mx1);
+    if (__any_sync(0xffffffffu, (mn0 != st.m0) | (mn1 != st.m1))) {
+      const float al0 = ex2_approx(st.m0 - mn0), al1 = ex2_approx(st.m1 - mn1);
+      st.l0 *= al0; st.l1 *= al1;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { o[j][0] *= al0; o[j][1] *= al1; o[j][2] *= al0; o[j][3] *= al1; }
+      st.m0 = mn0; st.m1 = mn1;
+    }
+    uint32_t pq[4][2];
+    float ls0 = 0.f, ls1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float p0 = ex2_approx(s[j][0] - mn0), p1 = ex2_approx(s[j][1] - mn1);
+      const float p2 = ex2_approx(s[j][2] - mn0), p3 = ex2_approx(s[j][3] - mn1);
+      ls0 += p0 + p2;
+      ls1 += p1 + p3;
+      pq[j][0] = movmatrix_trans(pack_half2(p0 * nv[j][0], p1 * nv[j][0]));
+      pq[j][1] = movmatrix_trans(pack_half2(p2 * nv[j][1], p3 * nv[j][1]));
+    }
+    st.l0 += ls0;
+    st.l1 += ls1;
+    // ---- values ----
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t n0[8], n1[8], n2[8], n3[8];
+      lowbit_v_fragments<BITS>(vb + j * LB::BLK + v_off[0], v_sh, lb4, lb8, n0);
+      lowbit_v_fragments<BITS>(vb + j * LB::BLK + v_off[1], v_sh, lb4, lb8, n1);
+      lowbit_v_fragments<BITS>(vb + j * LB::BLK + v_off[2], v_sh, lb4, lb8, n2);
+      lowbit_v_fragments<BITS>(vb + j * LB::BLK + v_off[3], v_sh, lb4, lb8, n3);
+#pragma unroll
+      for (int m = 0; m < 8; ++m)
+        mma16816(o[m], __byte_perm(n0[m], n1[m], 0x5410), __byte_perm(n0[m], n1[m], 0x7632),
+                 __byte_perm(n2[m], n3[m], 0x5410), __byte_perm(n2[m], n3[m], 0x7632), pq[j][0], pq[j][1]);
+    }
+  }
+  end_seq();
+}
+
 static inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 struct Plan {
@@ -1674,7 +2001,7 @@ static Plan make_plan(int num_seqs, int num_q_heads, int num_kv_heads, int head_
   p.num_parts = p.num_splits * p.warps_per_head;
   const int head_groups = (num_kv_heads + 7) / 8;
   p.sk_grid = sm_count() / head_groups > 0 ? sm_count() / head_groups : 1;
-  p.persist_shape = persist_ok && persist_enabled() && p.mma && bits == 4 && block_size == 16 &&
+  p.persist_shape = persist_ok && persist_enabled() && p.mma && block_size == 16 &&
                     num_kv_heads % 8 == 0 && num_seqs <= SK_MAX_SEQS && max_blocks_per_seq > 0;
   p.parts_alloc = (size_t)p.num_parts;
   if (p.persist_shape && (size_t)2 * p.sk_grid > p.parts_alloc) p.parts_alloc = (size_t)2 * p.sk_grid;
@@ -1770,7 +2097,18 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
                     reinterpret_cast<uintptr_t>(p->k_norms) % 16 == 0 &&
                     reinterpret_cast<uintptr_t>(p->v_norms) % 16 == 0 && p->max_blocks_per_seq > 0;
   const int64_t lim = (int64_t)1 << 31;
-  const bool persist = pipe && plan.persist_shape && p->kp_stride_blk < lim && p->vp_stride_blk < lim &&
+  // the same layout test for any bit width: heads contiguous in a token row, rows readable in 16-byte pieces
+  const int pd_bytes = 16 * p->bits;
+  const bool ring_layout = plan.mma && vec16 && p->block_size == 16 && p->num_kv_heads % 8 == 0 &&
+                           p->kp_stride_head == pd_bytes && p->vp_stride_head == pd_bytes && p->kn_stride_head == 1 &&
+                           p->vn_stride_head == 1 && p->kn_stride_pos % 4 == 0 && p->vn_stride_pos % 4 == 0 &&
+                           p->kn_stride_blk % 4 == 0 && p->vn_stride_blk % 4 == 0 &&
+                           reinterpret_cast<uintptr_t>(p->k_norms) % 16 == 0 &&
+                           reinterpret_cast<uintptr_t>(p->v_norms) % 16 == 0 && p->max_blocks_per_seq > 0;
+  static const bool sk4 = getenv("AKV_NO_SK4") == nullptr;    // 4-block stages, four tiles per warp at once
+  static const bool no_lowbit_ring = getenv("AKV_NO_LOWBIT_RING") != nullptr;
+  const bool ring = p->bits == 4 ? pipe : (ring_layout && sk4 && !no_pipe && !no_lowbit_ring);
+  const bool persist = ring && plan.persist_shape && p->kp_stride_blk < lim && p->vp_stride_blk < lim &&
                        p->kn_stride_blk < lim && p->vn_stride_blk < lim && p->num_blocks < lim;
   int* sk = reinterpret_cast<int*>(ws + plan.off_sk);
 
@@ -1778,7 +2116,6 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
   pl.context_lens = p->context_lens; pl.cl_dtype = p->cl_dtype; pl.num_seqs = p->num_seqs;
   pl.block_size = p->block_size; pl.grid = plan.sk_grid; pl.sk = persist ? sk : nullptr;
   static const int sk_wph = (getenv("AKV_SK_WPH") && atoi(getenv("AKV_SK_WPH")) == 2) ? 2 : 1;
-  static const bool sk4 = getenv("AKV_NO_SK4") == nullptr;    // 4-block stages, four tiles per warp at once
   pl.parts_per_cta = sk4 ? 1 : sk_wph;
   pl.blocks_per_stage = sk4 ? 4 : 2;
   akv_qrot_kernel<<<rows + (persist ? 1 : 0), D < 128 ? D : 128, D * sizeof(float), st>>>(
@@ -1809,11 +2146,13 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
     if (persist && sk4) {
       a.num_parts = plan.sk_grid;
       merge_parts = a.num_parts;
-      cudaError_t e = cudaFuncSetAttribute(tq4_attn_streamk4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SK4_DYN_SMEM);
+      auto kern = p->bits == 4 ? tq4_attn_streamk4_kernel
+                               : (p->bits == 3 ? tq_attn_streamk4_lowbit_kernel<3> : tq_attn_streamk4_lowbit_kernel<2>);
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SK4_DYN_SMEM);
       if (e != cudaSuccess) return fail((int)e, "attention: smem attribute: %s", cudaGetErrorString(e));
       dim3 grid(plan.sk_grid, p->num_kv_heads / 8);
-      tq4_attn_streamk4_kernel<<<grid, 256, SK4_DYN_SMEM, st>>>(a);
-      if (int rc = check_launch("tq4_attn_streamk4_kernel")) return rc;
+      kern<<<grid, 256, SK4_DYN_SMEM, st>>>(a);
+      if (int rc = check_launch(p->bits == 4 ? "tq4_attn_streamk4_kernel" : "tq_attn_streamk4_lowbit_kernel")) return rc;
     } else if (persist) {
       a.num_parts = sk_wph * plan.sk_grid;
       merge_parts = a.num_parts;
