@@ -277,7 +277,15 @@ tq_encode_generic_kernel(RowMap m, int64_t n_rows, int D, int bits, const float*
     __syncthreads();
     for (int o = tid; o < D; o += 128) {
       float y = 0.f;      // one chain in the order j = 0..D-1 (bit-identical to the tiled kernel)
-      for (int j0 = 0; j0 < D; j0 += 8) {    // 8 loads in flight per round (D is a multiple of 8)
+      int j0 = 0;
+      for (; j0 + 32 <= D; j0 += 32) {       // 32 loads in flight per round: the matrix comes from L2
+        float r[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) r[k] = rot_t[(int64_t)(j0 + k) * D + o];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) y = __fmaf_rn(u[j0 + k], r[k], y);
+      }
+      for (; j0 < D; j0 += 8) {              // D is a multiple of 8
         float r[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k) r[k] = rot_t[(int64_t)(j0 + k) * D + o];
