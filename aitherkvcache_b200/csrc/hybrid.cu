@@ -586,6 +586,101 @@ hybrid_encode35_coop_kernel(const uint16_t* __restrict__ x, int64_t n_rows, int6
                            dst + 9, live);
 }
 
+// ---------------------------------------------------------------------------
+// tq35 decode, four lanes per vector (same lane <-> coordinate split as the encoder above):
+// records staged in shared memory, codes and sign bits picked out of the big-endian stream
+// words, two 64-point transforms per group (centroids, signs), the reference's float32
+// arithmetic step for step (bit-identical output), results staged and written as whole rows.
+// ---------------------------------------------------------------------------
+template <int BITS>
+__device__ __forceinline__ void hc_decode_group(const uint32_t* rec /* this group's words, staged */,
+                                                const int* gidx, const float* had, const float* qjl,
+                                                const float* cent, float qjl_scale, int q, float* orow) {
+  constexpr int MSE_W = 64 * BITS / 32;
+  uint32_t W[MSE_W + 2];
+#pragma unroll
+  for (int j = 0; j < MSE_W + 2; ++j) W[j] = __byte_perm(rec[j], 0u, 0x0123);    // big-endian stream words
+  const uint32_t sc = rec[MSE_W + 2];
+  const float n = __half2float(__ushort_as_half((unsigned short)(sc & 0xffffu)));
+  const float rho = __half2float(__ushort_as_half((unsigned short)(sc >> 16)));
+  float a[16], b[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int m = i >> 1, b01 = i & 1;
+    // 8-code group m: stream bits [8 m BITS, 8 (m+1) BITS)
+    const int pos = 8 * m * BITS, j = pos >> 5, off = pos & 31;
+    uint32_t grp;
+    if (off + 8 * BITS <= 32) grp = W[j] >> (32 - 8 * BITS - off);
+    else grp = __funnelshift_l(W[j + 1], W[j], off + 8 * BITS - 32);
+    const uint32_t code = (grp >> (BITS * (7 - b01) - 2 * BITS * q)) & ((1u << BITS) - 1u);
+    a[i] = cent[code];
+    const uint32_t byte = (W[MSE_W + (m >> 2)] >> (24 - 8 * (m & 3))) & 0xffu;
+    const uint32_t bit = (byte >> (7 - b01 - 2 * q)) & 1u;
+    b[i] = __fmul_rn(bit ? 1.f : -1.f, qjl_scale);
+  }
+  hc_fwht64(a, q);
+  hc_fwht64(b, q);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int k = hc_coord(i, q);
+    const float mse_hat = __fmul_rn(__fmul_rn(a[i], had[k]), 0.125f);     // / sqrt(64), exact
+    const float qjl_hat = __fmul_rn(__fmul_rn(b[i], qjl[k]), 0.125f);
+    orow[gidx[k]] = __fmul_rn(__fadd_rn(mse_hat, __fmul_rn(qjl_hat, rho)), n);
+  }
+}
+
+constexpr int HD_ROW = 132;       // staged output row pitch in floats (128 + 4: quads of a warp hit distinct banks)
+
+__global__ void __launch_bounds__(HC_THREADS, 4)
+hybrid_decode35_coop_kernel(const uint8_t* __restrict__ packed, int64_t p_row_stride, int64_t n_rows,
+                            HybridTables t, void* __restrict__ out, int out_dtype) {
+  __shared__ uint32_t recs[32 * 17];                // 16 words per record, pitch 17
+  __shared__ __align__(16) float outs[32 * HD_ROW];
+  __shared__ float s_had[128], s_qjl[128], s_cent[16];
+  __shared__ int s_idx[128];
+  const int tid = threadIdx.x;
+  if (tid < 128) { s_had[tid] = t.had_signs[tid]; s_qjl[tid] = t.qjl_signs[tid]; s_idx[tid] = t.group_index[tid]; }
+  if (tid < 16) s_cent[tid] = t.centroids[tid];
+  const int64_t row0 = (int64_t)blockIdx.x * 32;
+  {   // 32 records x 16 words, one 16-byte piece per thread
+    const int r = tid >> 2, c = tid & 3;
+    const int64_t n = row0 + r;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (n < n_rows) v = *reinterpret_cast<const uint4*>(packed + n * p_row_stride + c * 16);
+    uint32_t* d = recs + r * 17 + 4 * c;
+    d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
+  }
+  __syncthreads();
+  const int vec = tid >> 2, q = tid & 3;
+  const int64_t n = row0 + vec;
+  const int* gidx = s_idx;
+  if (t.num_index_heads > 1 && n < n_rows) gidx = t.group_index + (int)(n % t.num_index_heads) * 128;
+  hc_decode_group<3>(recs + vec * 17, gidx, s_had, s_qjl, s_cent, t.qjl_scale0, q, outs + vec * HD_ROW);
+  hc_decode_group<2>(recs + vec * 17 + 9, gidx + 64, s_had + 64, s_qjl + 64, s_cent + 8, t.qjl_scale1, q,
+                     outs + vec * HD_ROW);
+  __syncthreads();
+  // 32 rows x 128 values, coalesced
+  for (int e = tid; e < 32 * 32; e += HC_THREADS) {
+    const int r = e >> 5, c4 = (e & 31) * 4;
+    const int64_t nn = row0 + r;
+    if (nn >= n_rows) continue;
+    const float4 v = *reinterpret_cast<const float4*>(outs + r * HD_ROW + c4);
+    if (out_dtype == AKV_F32) {
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + nn * 128 + c4) = v;
+    } else {
+      uint2 h;
+      if (out_dtype == AKV_F16) {
+        __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+        h = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+      } else {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        h = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+      }
+      *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(out) + nn * 128 + c4) = h;
+    }
+  }
+}
+
 static int launch_hybrid_encode35_coop(const void* x, int x_dtype, int64_t n_rows, int64_t x_row_stride,
                                        const HybridTables& t, uint8_t* out, int64_t out_row_stride, cudaStream_t st) {
   const int grid = (int)((n_rows + 31) / 32);
@@ -1379,8 +1474,15 @@ AKV_EXPORT int akv_hybrid_decode(const uint8_t* packed, int64_t packed_row_strid
   if (n_rows == 0) return AKV_OK;
   if (!packed || !out) return fail(AKV_ERR_ARG, "akv_hybrid_decode: null pointer");
   if (out_dtype < AKV_F16 || out_dtype > AKV_F32) return fail(AKV_ERR_ARG, "bad out_dtype %d", out_dtype);
-  const int grid = (int)((n_rows + HY_THREADS - 1) / HY_THREADS);
   cudaStream_t st = (cudaStream_t)stream;
+  static const bool no_coop = getenv("AKV_HYBRID_NO_COOP") != nullptr;
+  if (mode == 35 && !no_coop && (reinterpret_cast<uintptr_t>(packed) & 15) == 0 && (packed_row_stride & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    hybrid_decode35_coop_kernel<<<(int)((n_rows + 31) / 32), HC_THREADS, 0, st>>>(packed, packed_row_stride, n_rows, t,
+                                                                                   out, out_dtype);
+    return check_launch("hybrid_decode35_coop_kernel");
+  }
+  const int grid = (int)((n_rows + HY_THREADS - 1) / HY_THREADS);
   if (mode == 35)
     hybrid_decode_kernel<64, 3, 64, 2><<<grid, HY_THREADS, 0, st>>>(packed, packed_row_stride, n_rows, t, out, out_dtype);
   else
