@@ -2,7 +2,7 @@
 """Benchmark of the headline path: paged decode attention over a tq-t4nc (4-bit
 TurboQuant) KV cache.
 
-Workload (BASELINE.json configs[1]): 16 sequences, context lengths uniform in
+Workload (the benchmark specification's paged decode configuration): 16 sequences, context lengths uniform in
 [4096, 32768] (torch CPU generator, seed 1), 32 query / 8 KV heads, head_dim 128,
 block_size 16, block tables a random permutation of the physical blocks, K and V
 N(0,1) fp16 encoded to 4-bit codes + float32 norms, one fp16 query token per sequence.
@@ -299,7 +299,7 @@ def run_micro(args):
 
 
 def run_tri128k(args, rank, world, local):
-    """BASELINE.json configs[4]: TriAttention decode_step, batch 8, 128K context, F=12 int4, split-K over
+    """The long-context configuration of the benchmark specification: TriAttention decode_step, batch 8, 128K context, F=12 int4, split-K over
     the ranks by contiguous key ranges; partials merged after one NCCL all-gather (strong scaling)."""
     import torch.distributed as dist
     from aitherkvcache_b200.parallel import all_gather_partials, merge_partials, shard_range

@@ -15,7 +15,9 @@ import sys
 import numpy as np
 import torch
 
-REF = os.environ.get("AKV_REFERENCE", "/root/reference")
+REF = os.environ.get("AKV_REFERENCE")
+if not REF:
+    sys.exit("set AKV_REFERENCE to a checkout of the reference (Aitherium/aitherkvcache)")
 sys.path.insert(0, REF)
 HERE = os.path.dirname(os.path.abspath(__file__))
 
