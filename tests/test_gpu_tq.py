@@ -357,6 +357,30 @@ def test_paged_attention_vs_oracle(bits, H, QH, ctx):
     assert np.abs(out - sdpa.astype(np.float32)).max() < 2e-3
 
 
+@pytest.mark.parametrize("bits", BITS)
+def test_paged_attention_many_sequences_two_head_groups(bits):
+    """The persistent kernels: 16 KV heads (two head groups per CTA column), GQA 2, forty sequences
+    of very different lengths - empty, one token, exact multiples of a 64-token stage, and long ones -
+    so that CTAs switch sequences mid-range and stages end ragged."""
+    t = load_golden(f"tq_d128_b{bits}.npz")
+    tq = _tq(128, bits, t)
+    H, QH = 16, 32
+    gen = np.random.default_rng(1234 + bits)
+    ctx = [0, 1, 64, 128, 63, 65, 4097, 16, 15, 17] + [int(v) for v in gen.integers(1, 700, 30)]
+    d = make_paged_cache(900 + bits, ctx, H, 128, bits, t["rotation"], t["boundaries"])
+    q = torch.randn(len(ctx), QH, 128, generator=torch.Generator().manual_seed(19)).half()
+    c = to_cuda(d, ["k_packed", "k_norms", "v_packed", "v_norms", "block_tables", "context_lens"])
+    out = _attn(tq, QH).forward(q.cuda(), c["k_packed"], c["k_norms"], c["v_packed"], c["v_norms"],
+                                c["block_tables"], c["context_lens"]).float().cpu().numpy()
+    ref = otq.paged_attention_rotated(q.numpy(), d["k_packed"], d["k_norms"], d["v_packed"], d["v_norms"],
+                                      d["block_tables"], d["context_lens"], t["rotation"], t["centroids"],
+                                      bits, 1.0 / math.sqrt(128))
+    assert (out[0] == 0).all()
+    # one-token contexts return a single decoded value vector of magnitude 2..4, where one fp16 ulp is
+    # already 2e-3: the tolerance scales with the magnitude there
+    assert (np.abs(out - ref) <= 2e-3 * np.maximum(1.0, np.abs(ref))).all()
+
+
 def test_paged_attention_strided_cache_and_query_dtypes():
     """kv_cache[:, 0/1, ..., :pd] views (row pitch pd+4) and bf16 / fp32 queries."""
     bits, H, QH, ctx = 4, 8, 32, [200, 95]
