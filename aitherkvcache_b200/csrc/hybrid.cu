@@ -924,11 +924,15 @@ hybrid_attn_kernel(HybridAttnArgs a) {
 // 16t..16t+15 of every segment of tokens g and g + 8; for the values, coordinates 8g..8g+7 of
 // every segment of tokens 2t, 2t+1, 2t+8, 2t+9.
 // ---------------------------------------------------------------------------
-constexpr int HM_LUT2 = 0;                       // 256 entries x 256 B: byte of four 2-bit codes -> 4 halves
-constexpr int HM_LUT3 = 65536;                   // 64 entries x 128 B: two 3-bit codes -> 2 halves
-constexpr int HM_LUTS = HM_LUT3 + 8192;          // 16 entries x 256 B: four sign bits -> 4 halves
-constexpr int HM_STAGE = HM_LUTS + 4096;         // per warp: 2 buffers x (1 KB K + 1 KB V)
-constexpr int HM_SMEM = HM_STAGE + HA_WARPS * 4096;
+// Absolute shared-window addresses (a CTA's dynamic shared memory starts a little above 1 KB; the
+// kernel checks).  Fixed addresses let every table lookup do without an address add: the 3-bit and
+// the sign table are aligned to their size, so their base is OR-ed into the lane offset once, and
+// the 2-bit table's base rides in the load instruction as an immediate.
+constexpr uint32_t HM_LUT2 = 4096;               // 256 entries x 256 B: byte of four 2-bit codes -> 4 halves
+constexpr uint32_t HM_LUT3 = 73728;              // 64 entries x 128 B (8 KB aligned): two 3-bit codes -> 2 halves
+constexpr uint32_t HM_LUTS = 81920;              // 16 entries x 256 B (4 KB aligned): four sign bits -> 4 halves
+constexpr uint32_t HM_STAGE = 86016;             // per warp: 2 buffers x (1 KB K + 1 KB V)
+constexpr int HM_SMEM = HM_STAGE + HA_WARPS * 4096;   // 102400: covers every address above for any start >= 0
 
 __device__ __forceinline__ uint32_t hm_lds32(uint32_t addr) {
   uint32_t v;
@@ -949,6 +953,34 @@ __device__ __forceinline__ uint2 hm_lds64(uint32_t addr) {
   uint2 v;
   asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr));
   return v;
+}
+template <uint32_t C>
+__device__ __forceinline__ uint32_t hm_lds32c(uint32_t r) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1+%2];\n" : "=r"(v) : "r"(r), "n"(C));
+  return v;
+}
+template <uint32_t C>
+__device__ __forceinline__ uint32_t hm_lds16c(uint32_t r) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1+%2];\n" : "=h"(v) : "r"(r), "n"(C));
+  return v;
+}
+template <uint32_t C>
+__device__ __forceinline__ uint32_t hm_lds8c(uint32_t r) {
+  uint32_t v;
+  asm volatile("ld.shared.u8 %0, [%1+%2];\n" : "=r"(v) : "r"(r), "n"(C));
+  return v;
+}
+template <uint32_t C>
+__device__ __forceinline__ uint2 hm_lds64c(uint32_t r) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];\n" : "=r"(v.x), "=r"(v.y) : "r"(r), "n"(C));
+  return v;
+}
+__device__ __forceinline__ float2 hm_half2_bits(uint32_t u) {
+  const __half2 h = *reinterpret_cast<const __half2*>(&u);
+  return make_float2(__low2float(h), __high2float(h));
 }
 __device__ __forceinline__ void hm_mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                        uint32_t b0, uint32_t b1) {
@@ -983,8 +1015,8 @@ __device__ __forceinline__ uint2 hm_signs(uint32_t luts, uint32_t x, uint32_t la
 }
 // Byte K of w (four 2-bit codes) -> two half2 of centroids.
 template <int K>
-__device__ __forceinline__ uint2 hm_quad2(uint32_t lut2, uint32_t w, uint32_t lane8) {
-  return hm_lds64(lut2 + __byte_perm(w, lane8, 0x7604 + (K << 4)));
+__device__ __forceinline__ uint2 hm_quad2(uint32_t w, uint32_t lane8) {
+  return hm_lds64c<HM_LUT2>(__byte_perm(w, lane8, 0x7604 + (K << 4)));
 }
 
 __global__ void __launch_bounds__(HA_WARPS * 32, 2)
@@ -1002,30 +1034,38 @@ hybrid_attn_mma_kernel(HybridAttnArgs a) {
   int64_t tile_end = tile_begin + (int64_t)a.blocks_per_split * tpb;
   if (tile_end > tiles_total) tile_end = tiles_total;
 
+  const uint32_t dyn0 = (uint32_t)__cvta_generic_to_shared(hm_smem);
+  if (dyn0 > HM_LUT2) {        // the window below the tables is taken (static + system-reserved bytes)
+    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
+      printf("hybrid_attn_mma_kernel: dynamic shared memory starts at %u, above %u\n", dyn0, HM_LUT2);
+    return;
+  }
+  unsigned char* const abs0 = hm_smem - dyn0;     // generic pointer to shared-window address 0
   // ---- lookup tables, one copy per lane ----
   const float* c0 = a.centroids;        // 8 centroids of group 0 (3-bit)
   const float* c1 = a.centroids + 8;    // 4 centroids of group 1 (2-bit)
   for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x) {
     const int e = i >> 5, l = i & 31;
-    *reinterpret_cast<uint2*>(hm_smem + HM_LUT2 + e * 256 + l * 8) =
+    *reinterpret_cast<uint2*>(abs0 + HM_LUT2 + e * 256 + l * 8) =
         make_uint2(hm_pack(c1[e >> 6], c1[(e >> 4) & 3]), hm_pack(c1[(e >> 2) & 3], c1[e & 3]));
   }
   for (int i = threadIdx.x; i < 64 * 32; i += blockDim.x) {
     const int e = i >> 5, l = i & 31;
-    *reinterpret_cast<uint32_t*>(hm_smem + HM_LUT3 + e * 128 + l * 4) = hm_pack(c0[e >> 3], c0[e & 7]);
+    *reinterpret_cast<uint32_t*>(abs0 + HM_LUT3 + e * 128 + l * 4) = hm_pack(c0[e >> 3], c0[e & 7]);
   }
   for (int i = threadIdx.x; i < 16 * 32; i += blockDim.x) {
     const int e = i >> 5, l = i & 31;
-    *reinterpret_cast<uint2*>(hm_smem + HM_LUTS + e * 256 + l * 8) =
+    *reinterpret_cast<uint2*>(abs0 + HM_LUTS + e * 256 + l * 8) =
         make_uint2(hm_pack((e & 8) ? 1.f : -1.f, (e & 4) ? 1.f : -1.f),
                    hm_pack((e & 2) ? 1.f : -1.f, (e & 1) ? 1.f : -1.f));
   }
   __syncthreads();
 
-  const uint32_t smem_s = (uint32_t)__cvta_generic_to_shared(hm_smem);
-  const uint32_t lut2 = smem_s + HM_LUT2, lut3 = smem_s + HM_LUT3, luts = smem_s + HM_LUTS;
-  const uint32_t stage_s = smem_s + HM_STAGE + warp * 4096;
-  const uint32_t lane4 = lane * 4, lane8 = lane * 8;
+  constexpr uint32_t lut3 = 0, luts = 0;           // bases are folded into the lane offsets below
+  const uint32_t stage_s = HM_STAGE + warp * 4096;
+  const uint32_t lane4 = HM_LUT3 | (lane * 4);     // 3-bit table lookups: (pair << 7) | lane4
+  const uint32_t lane8s = HM_LUTS | (lane * 8);    // sign table lookups: (nibble << 8) | lane8s
+  const uint32_t lane8 = lane * 8;                 // 2-bit table lookups: base as load immediate
 
   // ---- query fragments: thread (g, t) holds q'[q head g][segment][16t .. 16t+15] ----
   uint32_t bq[4][4][2];
@@ -1097,6 +1137,10 @@ hybrid_attn_mma_kernel(HybridAttnArgs a) {
     asm volatile("cp.async.wait_group 1;\n" ::: "memory");
     __syncwarp();
     const uint32_t buf = stage_s + (uint32_t)(i & 1) * 2048;
+    // this tile's load bases; every further displacement is an immediate of the load
+    const uint32_t pK0a = buf + oK0a, pK0b = buf + oK0b, pKs0 = buf + oKs0, pKs1 = buf + oKs1;
+    const uint32_t pKn0 = buf + oKn0, pKn1 = buf + oKn1, pKc1 = buf + oKc1;
+    const uint32_t pV0a = buf + oV0a, pV0b = buf + oV0b, pVs0 = buf + oVs0, pVs1 = buf + oVs1, pVc1 = buf + oVc1;
     const int64_t tile = first + (int64_t)i * HA_WARPS;
     const int64_t rem = ctx - tile * 16;
     const int n_valid = rem < 16 ? (int)rem : 16;
@@ -1106,8 +1150,8 @@ hybrid_attn_mma_kernel(HybridAttnArgs a) {
 #pragma unroll
     for (int sg = 0; sg < 4; ++sg) sc[sg][0] = sc[sg][1] = sc[sg][2] = sc[sg][3] = 0.f;
     {   // segment 0: 3-bit codes
-      const uint32_t a0 = hm_lds32(buf + oK0a), a1 = hm_lds32(buf + oK0b);
-      const uint32_t b0 = hm_lds32(buf + oK0a + 512), b1 = hm_lds32(buf + oK0b + 512);
+      const uint32_t a0 = hm_lds32c<0>(pK0a), a1 = hm_lds32c<0>(pK0b);
+      const uint32_t b0 = hm_lds32c<512>(pK0a), b1 = hm_lds32c<512>(pK0b);
       const uint32_t A0 = __byte_perm(a0, a1, selK0), A1 = __byte_perm(a0, a1, selK1);
       const uint32_t B0 = __byte_perm(b0, b1, selK0), B1 = __byte_perm(b0, b1, selK1);
       uint32_t na[8], nb[8];
@@ -1130,11 +1174,11 @@ hybrid_attn_mma_kernel(HybridAttnArgs a) {
     }
 #pragma unroll
     for (int sgn = 0; sgn < 2; ++sgn) {   // segments 1 and 3: sign bits
-      const uint32_t va = hm_lds16(buf + (sgn ? oKs1 : oKs0)), vb = hm_lds16(buf + (sgn ? oKs1 : oKs0) + 512);
-      const uint2 a0 = hm_signs(luts, va << 4, lane8), a1 = hm_signs(luts, va << 8, lane8);
-      const uint2 a2 = hm_signs(luts, va >> 4, lane8), a3 = hm_signs(luts, va, lane8);
-      const uint2 b0 = hm_signs(luts, vb << 4, lane8), b1 = hm_signs(luts, vb << 8, lane8);
-      const uint2 b2 = hm_signs(luts, vb >> 4, lane8), b3 = hm_signs(luts, vb, lane8);
+      const uint32_t va = hm_lds16c<0>(sgn ? pKs1 : pKs0), vb = hm_lds16c<512>(sgn ? pKs1 : pKs0);
+      const uint2 a0 = hm_signs(luts, va << 4, lane8s), a1 = hm_signs(luts, va << 8, lane8s);
+      const uint2 a2 = hm_signs(luts, va >> 4, lane8s), a3 = hm_signs(luts, va, lane8s);
+      const uint2 b0 = hm_signs(luts, vb << 4, lane8s), b1 = hm_signs(luts, vb << 8, lane8s);
+      const uint2 b2 = hm_signs(luts, vb >> 4, lane8s), b3 = hm_signs(luts, vb, lane8s);
       const int sg = 1 + 2 * sgn;
       hm_mma(sc[sg], a0.x, b0.x, a0.y, b0.y, bq[sg][0][0], bq[sg][0][1]);
       hm_mma(sc[sg], a1.x, b1.x, a1.y, b1.y, bq[sg][1][0], bq[sg][1][1]);
@@ -1142,11 +1186,11 @@ hybrid_attn_mma_kernel(HybridAttnArgs a) {
       hm_mma(sc[sg], a3.x, b3.x, a3.y, b3.y, bq[sg][3][0], bq[sg][3][1]);
     }
     {   // segment 2: 2-bit codes, one byte per k-tile
-      const uint32_t wa = hm_lds32(buf + oKc1), wb = hm_lds32(buf + oKc1 + 512);
-      const uint2 a0 = hm_quad2<0>(lut2, wa, lane8), a1 = hm_quad2<1>(lut2, wa, lane8);
-      const uint2 a2 = hm_quad2<2>(lut2, wa, lane8), a3 = hm_quad2<3>(lut2, wa, lane8);
-      const uint2 b0 = hm_quad2<0>(lut2, wb, lane8), b1 = hm_quad2<1>(lut2, wb, lane8);
-      const uint2 b2 = hm_quad2<2>(lut2, wb, lane8), b3 = hm_quad2<3>(lut2, wb, lane8);
+      const uint32_t wa = hm_lds32c<0>(pKc1), wb = hm_lds32c<512>(pKc1);
+      const uint2 a0 = hm_quad2<0>(wa, lane8), a1 = hm_quad2<1>(wa, lane8);
+      const uint2 a2 = hm_quad2<2>(wa, lane8), a3 = hm_quad2<3>(wa, lane8);
+      const uint2 b0 = hm_quad2<0>(wb, lane8), b1 = hm_quad2<1>(wb, lane8);
+      const uint2 b2 = hm_quad2<2>(wb, lane8), b3 = hm_quad2<3>(wb, lane8);
       hm_mma(sc[2], a0.x, b0.x, a0.y, b0.y, bq[2][0][0], bq[2][0][1]);
       hm_mma(sc[2], a1.x, b1.x, a1.y, b1.y, bq[2][1][0], bq[2][1][1]);
       hm_mma(sc[2], a2.x, b2.x, a2.y, b2.y, bq[2][2][0], bq[2][2][1]);
@@ -1154,14 +1198,12 @@ hybrid_attn_mma_kernel(HybridAttnArgs a) {
     }
     float s0, s1, s2, s3;
     {
-      const __half2 kA0 = *reinterpret_cast<const __half2*>(hm_smem + (buf - smem_s) + oKn0);
-      const __half2 kA1 = *reinterpret_cast<const __half2*>(hm_smem + (buf - smem_s) + oKn1);
-      const __half2 kB0 = *reinterpret_cast<const __half2*>(hm_smem + (buf - smem_s) + oKn0 + 512);
-      const __half2 kB1 = *reinterpret_cast<const __half2*>(hm_smem + (buf - smem_s) + oKn1 + 512);
-      const float nA0 = __low2float(kA0), rA0 = nA0 * __high2float(kA0);
-      const float nA1 = __low2float(kA1), rA1 = nA1 * __high2float(kA1);
-      const float nB0 = __low2float(kB0), rB0 = nB0 * __high2float(kB0);
-      const float nB1 = __low2float(kB1), rB1 = nB1 * __high2float(kB1);
+      const float2 kA0 = hm_half2_bits(hm_lds32c<0>(pKn0)), kA1 = hm_half2_bits(hm_lds32c<0>(pKn1));
+      const float2 kB0 = hm_half2_bits(hm_lds32c<512>(pKn0)), kB1 = hm_half2_bits(hm_lds32c<512>(pKn1));
+      const float nA0 = kA0.x, rA0 = nA0 * kA0.y;
+      const float nA1 = kA1.x, rA1 = nA1 * kA1.y;
+      const float nB0 = kB0.x, rB0 = nB0 * kB0.y;
+      const float nB1 = kB1.x, rB1 = nB1 * kB1.y;
       s0 = nA0 * sc[0][0] + rA0 * sc[1][0] + nA1 * sc[2][0] + rA1 * sc[3][0];
       s1 = nA0 * sc[0][1] + rA0 * sc[1][1] + nA1 * sc[2][1] + rA1 * sc[3][1];
       s2 = nB0 * sc[0][2] + rB0 * sc[1][2] + nB1 * sc[2][2] + rB1 * sc[3][2];
@@ -1170,14 +1212,12 @@ hybrid_attn_mma_kernel(HybridAttnArgs a) {
     // value-side segment weights of tokens g and g + 8 (same staged layout, V half)
     float wA[4], wB[4];
     {
-      const __half2 vA0 = *reinterpret_cast<const __half2*>(hm_smem + (buf - smem_s) + 1024 + oKn0);
-      const __half2 vA1 = *reinterpret_cast<const __half2*>(hm_smem + (buf - smem_s) + 1024 + oKn1);
-      const __half2 vB0 = *reinterpret_cast<const __half2*>(hm_smem + (buf - smem_s) + 1024 + oKn0 + 512);
-      const __half2 vB1 = *reinterpret_cast<const __half2*>(hm_smem + (buf - smem_s) + 1024 + oKn1 + 512);
-      wA[0] = __low2float(vA0); wA[1] = wA[0] * __high2float(vA0);
-      wA[2] = __low2float(vA1); wA[3] = wA[2] * __high2float(vA1);
-      wB[0] = __low2float(vB0); wB[1] = wB[0] * __high2float(vB0);
-      wB[2] = __low2float(vB1); wB[3] = wB[2] * __high2float(vB1);
+      const float2 vA0 = hm_half2_bits(hm_lds32c<1024>(pKn0)), vA1 = hm_half2_bits(hm_lds32c<1024>(pKn1));
+      const float2 vB0 = hm_half2_bits(hm_lds32c<1536>(pKn0)), vB1 = hm_half2_bits(hm_lds32c<1536>(pKn1));
+      wA[0] = vA0.x; wA[1] = wA[0] * vA0.y;
+      wA[2] = vA1.x; wA[3] = wA[2] * vA1.y;
+      wB[0] = vB0.x; wB[1] = wB[0] * vB0.y;
+      wB[2] = vB1.x; wB[3] = wB[2] * vB1.y;
     }
     if (n_valid < 16) {   // warp-uniform: only the last tile of a sequence
       if (g >= n_valid) { s0 = -CUDART_INF_F; s1 = -CUDART_INF_F; wA[0] = wA[1] = wA[2] = wA[3] = 0.f; }
@@ -1214,15 +1254,18 @@ hybrid_attn_mma_kernel(HybridAttnArgs a) {
     // ================= values =================
     // n[tok][j] = half2(coordinate 8g+2j, 8g+2j+1) of token tok; M-tile j pairs the same
     // coordinate of two tokens: rows g / g+8 of the tile are coordinates 8g+2j / 8g+2j+1.
+    // token k of the thread's four (2t, 2t+1, 2t+8, 2t+9) sits RO bytes after the first one
+#define HM_FOUR_TOKENS(F) F(0, 0) F(1, 64) F(2, 512) F(3, 576)
     {   // segment 0
       uint32_t n[4][4];
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const uint32_t ro = (k & 1) * 64 + (k >> 1) * 512;
-        const uint32_t B = __byte_perm(hm_lds32(buf + oV0a + ro), hm_lds32(buf + oV0b + ro), selV0);
-        n[k][0] = hm_pair3<0>(lut3, B, lane4); n[k][1] = hm_pair3<1>(lut3, B, lane4);
-        n[k][2] = hm_pair3<2>(lut3, B, lane4); n[k][3] = hm_pair3<3>(lut3, B, lane4);
+#define HM_V0(K, RO)                                                                                  \
+      {                                                                                               \
+        const uint32_t B = __byte_perm(hm_lds32c<RO>(pV0a), hm_lds32c<RO>(pV0b), selV0);              \
+        n[K][0] = hm_pair3<0>(lut3, B, lane4); n[K][1] = hm_pair3<1>(lut3, B, lane4);                 \
+        n[K][2] = hm_pair3<2>(lut3, B, lane4); n[K][3] = hm_pair3<3>(lut3, B, lane4);                 \
       }
+      HM_FOUR_TOKENS(HM_V0)
+#undef HM_V0
 #pragma unroll
       for (int j = 0; j < 4; ++j)
         hm_mma(o[0][j], __byte_perm(n[0][j], n[1][j], 0x5410), __byte_perm(n[0][j], n[1][j], 0x7632),
@@ -1231,14 +1274,16 @@ hybrid_attn_mma_kernel(HybridAttnArgs a) {
 #pragma unroll
     for (int sgn = 0; sgn < 2; ++sgn) {   // segments 1 and 3
       const int sg = 1 + 2 * sgn;
+      const uint32_t pVs = sgn ? pVs1 : pVs0;
       uint32_t n[4][4];
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const uint32_t ro = (k & 1) * 64 + (k >> 1) * 512;
-        const uint32_t v = hm_lds8(buf + (sgn ? oVs1 : oVs0) + ro);
-        const uint2 hi = hm_signs(luts, v << 4, lane8), lo = hm_signs(luts, v << 8, lane8);
-        n[k][0] = hi.x; n[k][1] = hi.y; n[k][2] = lo.x; n[k][3] = lo.y;
+#define HM_VS(K, RO)                                                                                  \
+      {                                                                                               \
+        const uint32_t v = hm_lds8c<RO>(pVs);                                                         \
+        const uint2 hi = hm_signs(luts, v << 4, lane8s), lo = hm_signs(luts, v << 8, lane8s);         \
+        n[K][0] = hi.x; n[K][1] = hi.y; n[K][2] = lo.x; n[K][3] = lo.y;                               \
       }
+      HM_FOUR_TOKENS(HM_VS)
+#undef HM_VS
 #pragma unroll
       for (int j = 0; j < 4; ++j)
         hm_mma(o[sg][j], __byte_perm(n[0][j], n[1][j], 0x5410), __byte_perm(n[0][j], n[1][j], 0x7632),
@@ -1246,13 +1291,15 @@ hybrid_attn_mma_kernel(HybridAttnArgs a) {
     }
     {   // segment 2
       uint32_t n[4][4];
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const uint32_t ro = (k & 1) * 64 + (k >> 1) * 512;
-        const uint32_t v = hm_lds16(buf + oVc1 + ro);
-        const uint2 q0 = hm_quad2<0>(lut2, v, lane8), q1 = hm_quad2<1>(lut2, v, lane8);
-        n[k][0] = q0.x; n[k][1] = q0.y; n[k][2] = q1.x; n[k][3] = q1.y;
+#define HM_V2(K, RO)                                                                                  \
+      {                                                                                               \
+        const uint32_t v = hm_lds16c<RO>(pVc1);                                                       \
+        const uint2 q0 = hm_quad2<0>(v, lane8), q1 = hm_quad2<1>(v, lane8);                           \
+        n[K][0] = q0.x; n[K][1] = q0.y; n[K][2] = q1.x; n[K][3] = q1.y;                               \
       }
+      HM_FOUR_TOKENS(HM_V2)
+#undef HM_V2
+#undef HM_FOUR_TOKENS
 #pragma unroll
       for (int j = 0; j < 4; ++j)
         hm_mma(o[2][j], __byte_perm(n[0][j], n[1][j], 0x5410), __byte_perm(n[0][j], n[1][j], 0x7632),
