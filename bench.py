@@ -398,6 +398,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--replicas", type=int, default=2, help="cache copies cycled through (L2 defeat)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--e2e-eager", action="store_true", help="end-to-end loop without CUDA-graph capture")
     ap.add_argument("--workload", default="decode_tq4", choices=["decode_tq4", "tri128k", "micro"],
                     help="decode_tq4 is the headline configuration; the others are secondary measurements")
     args = ap.parse_args()
@@ -543,14 +544,47 @@ def main():
 
     for _ in range(args.warmup):
         e2e_step()
+    eager_out = out_host.clone()                      # what the eager path returned, to check the replay against
+    # A serving loop replays its decode step as a CUDA graph: the copy of the staging buffer, the op
+    # and the copy of the result back are captured once; every replay moves the bytes again.
+    e2e_mode, e2e_graph = "eager", None
+    if not args.e2e_eager:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                g_ = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g_, stream=side):
+                    dev_buf.copy_(host_buf, non_blocking=True)
+                    res_ = torch.ops.tq.decode_step(d["query"], d["key"], d["value"], kv_cache, out_dev, k_norms,
+                                                    v_norms, d["slot_mapping"], d["block_table"], d["seq_lens"], 0,
+                                                    H_Q, H_KV, D, 1.0 / math.sqrt(D), NUM_SEQS)
+                    out_host.copy_(res_, non_blocking=True)
+            torch.cuda.current_stream().wait_stream(side)
+            e2e_graph, e2e_mode = g_, "cuda graph replay (H2D copy + tq::decode_step + D2H copy)"
+        except Exception as exc:                      # noqa: BLE001 - capture is an optimisation
+            e2e_mode = f"eager (graph capture failed: {type(exc).__name__})"
+            torch.cuda.synchronize()
+
+    def e2e_timed():
+        if e2e_graph is None:
+            e2e_step()
+        else:
+            e2e_graph.replay()
+            torch.cuda.current_stream().synchronize()  # the caller reads the result every step
+
+    for _ in range(args.warmup):
+        e2e_timed()
     barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record()
     for _ in range(args.steps):
-        e2e_step()
+        e2e_timed()
     f1.record()
     barrier()
     e2e_ms = f0.elapsed_time(f1)
+    if not torch.equal(out_host, eager_out):
+        raise RuntimeError("end-to-end replay returned a different result than the eager call")
 
     times = torch.tensor([ms_total, e2e_ms, float(total_ctx)], dtype=torch.float64, device=dev)
     if world > 1:
@@ -577,6 +611,7 @@ def main():
                        "parallelism": f"dp{world} (sequences sharded, no collective)"},
             "e2e": {"value": job_ctx * args.steps / (e2e_ms * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps,
+                    "launch": e2e_mode,
                     "api": "torch.ops.tq.decode_step (encode new token + attention), host pinned buffers"},
             "gpu_launches": 3 * args.steps,
             # traffic: dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this
