@@ -18,6 +18,7 @@
 //   * tq_attn_generic_kernel - any power-of-two head_dim in [32, 256], 2/3/4 bits,
 //     any GQA ratio.  Scalar; lanes own dims.
 #include "common.cuh"
+#include "tq_rowmap.cuh"
 #include <math_constants.h>
 #include <stdlib.h>
 
@@ -2236,6 +2237,29 @@ AKV_EXPORT int akv_tq_decode_step(const akv_tq_decode_step_params* p) {
   if (p->num_tokens > 0) {
     if (!p->key || !p->value || !p->slot_mapping || !p->boundaries)
       return fail(AKV_ERR_ARG, "akv_tq_decode_step: null pointer");
+    // a decode step writes few vectors: K and V go out as one launch when the arguments are plainly valid
+    // (anything else takes the two calls below, which report what is wrong)
+    const int64_t rows = p->num_tokens * (int64_t)a.num_kv_heads;
+    const int D = a.head_dim;
+    if (rows > 0 && rows < 2048 && p->max_blocks > 0 && a.block_size > 0 && a.bits >= 2 && a.bits <= 4 &&
+        D >= 8 && D <= 1024 && (D & (D - 1)) == 0 && p->kv_dtype >= AKV_F16 && p->kv_dtype <= AKV_F32 &&
+        a.rotation_t && a.k_packed && a.v_packed && a.k_norms && a.v_norms) {
+      RowMap mk{}, mv{};
+      mk.x = p->key; mk.x_dtype = p->kv_dtype; mk.x_stride_tok = p->k_stride_tok; mk.x_stride_head = p->k_stride_head;
+      mk.packed = const_cast<uint8_t*>(a.k_packed); mk.norms = const_cast<float*>(a.k_norms);
+      mk.slot_mapping = p->slot_mapping; mk.num_heads = a.num_kv_heads; mk.block_size = a.block_size;
+      mk.max_blocks = p->max_blocks;
+      mk.p_stride_blk = a.kp_stride_blk; mk.p_stride_pos = a.kp_stride_pos; mk.p_stride_head = a.kp_stride_head;
+      mk.n_stride_blk = a.kn_stride_blk; mk.n_stride_pos = a.kn_stride_pos; mk.n_stride_head = a.kn_stride_head;
+      mv = mk;
+      mv.x = p->value; mv.x_stride_tok = p->v_stride_tok; mv.x_stride_head = p->v_stride_head;
+      mv.packed = const_cast<uint8_t*>(a.v_packed); mv.norms = const_cast<float*>(a.v_norms);
+      mv.p_stride_blk = a.vp_stride_blk; mv.p_stride_pos = a.vp_stride_pos; mv.p_stride_head = a.vp_stride_head;
+      mv.n_stride_blk = a.vn_stride_blk; mv.n_stride_pos = a.vn_stride_pos; mv.n_stride_head = a.vn_stride_head;
+      if (int rc = launch_encode_generic_pair(mk, mv, rows, D, a.bits, a.rotation_t, p->boundaries, (cudaStream_t)a.stream))
+        return rc;
+      return run_tq_attn(&p->attn, a.workspace, a.workspace_bytes);
+    }
     int rc = akv_tq_kv_update(p->key, p->kv_dtype, p->num_tokens, a.num_kv_heads, a.head_dim, p->k_stride_tok,
                               p->k_stride_head, p->slot_mapping, const_cast<uint8_t*>(a.k_packed), a.kp_stride_blk,
                               a.kp_stride_pos, a.kp_stride_head, const_cast<float*>(a.k_norms), a.kn_stride_blk,

@@ -251,9 +251,9 @@ tq_decode_tiled_kernel(const uint8_t* __restrict__ packed, int64_t p_stride_row,
 // Any power-of-two head_dim up to 1024: one warp per vector, the matrix is read
 // through L2.  Slow path for shapes outside {64, 128}.
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(128)
-tq_encode_generic_kernel(RowMap m, int64_t n_rows, int D, int bits, const float* __restrict__ rot_t,
-                         const float* __restrict__ boundaries) {
+__device__ __forceinline__ void encode_generic_rows(const RowMap& m, int64_t n_rows, int D, int bits,
+                                                    const float* __restrict__ rot_t,
+                                                    const float* __restrict__ boundaries) {
   // one CTA per vector: thread o produces outputs o, o+128, ...
   extern __shared__ __align__(16) float smem_f[];
   float* u = smem_f;                                        // [D]
@@ -311,6 +311,19 @@ tq_encode_generic_kernel(RowMap m, int64_t n_rows, int D, int bits, const float*
     }
     __syncthreads();
   }
+}
+
+__global__ void __launch_bounds__(128)
+tq_encode_generic_kernel(RowMap m, int64_t n_rows, int D, int bits, const float* __restrict__ rot_t,
+                         const float* __restrict__ boundaries) {
+  encode_generic_rows(m, n_rows, D, bits, rot_t, boundaries);
+}
+
+// The K and the V vectors of a decode step in one launch: blockIdx.y picks the tensor.
+__global__ void __launch_bounds__(128)
+tq_encode_generic_pair_kernel(RowMap mk, RowMap mv, int64_t n_rows, int D, int bits,
+                              const float* __restrict__ rot_t, const float* __restrict__ boundaries) {
+  encode_generic_rows(blockIdx.y ? mv : mk, n_rows, D, bits, rot_t, boundaries);
 }
 
 __global__ void __launch_bounds__(128)
@@ -711,6 +724,16 @@ static int encode_dispatch(const RowMap& m, int64_t n_rows, int D, int bits, con
   int grid = (int)(n_rows < 16 * sm_count() ? n_rows : 16 * sm_count());
   tq_encode_generic_kernel<<<grid, 128, smem, st>>>(m, n_rows, D, bits, rot_t, bnd);
   return check_launch("tq_encode_generic_kernel");
+}
+
+// Two small paged writes (the new token's K and V) as one launch of the generic kernel.
+int launch_encode_generic_pair(const RowMap& mk, const RowMap& mv, int64_t n_rows, int D, int bits,
+                               const float* rot_t, const float* bnd, cudaStream_t st) {
+  if (n_rows == 0) return AKV_OK;
+  size_t smem = (size_t)(D + D / 4 + 16) * sizeof(float);
+  dim3 grid((unsigned)(n_rows < 8 * sm_count() ? n_rows : 8 * sm_count()), 2);
+  tq_encode_generic_pair_kernel<<<grid, 128, smem, st>>>(mk, mv, n_rows, D, bits, rot_t, bnd);
+  return check_launch("tq_encode_generic_pair_kernel");
 }
 
 static int check_codec_args(int head_dim, int bits) {

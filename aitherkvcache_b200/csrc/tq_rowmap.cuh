@@ -66,6 +66,10 @@ __device__ __forceinline__ RowAddr map_row(const RowMap& m, int64_t n) {
 int launch_encode_tc(const RowMap& m, int64_t n_rows, int bits, bool bf16, const float* rot_t,
                      const float* boundaries, cudaStream_t st);
 
+// The K and V paged writes of a decode step (few rows) as one launch of the generic kernel (tq_codec.cu).
+int launch_encode_generic_pair(const RowMap& mk, const RowMap& mv, int64_t n_rows, int D, int bits,
+                               const float* rot_t, const float* boundaries, cudaStream_t st);
+
 // Tensor-core decode for head_dim 128 (tq_decode_tc.cu).
 int launch_decode_tc(const uint8_t* packed, int64_t packed_row_stride, const float* norms, int64_t n_rows,
                      int bits, const float* rot, const float* centroids, void* out, int out_dtype,
