@@ -989,7 +989,6 @@ tq4_attn_pipe_kernel(AttnArgs a) {
     for (int i = 0; i < 4; ++i)
       v_off[i] = 16384 + wj * 8192 + toks[i] * 512 + (((2 * hl + (g >> 2)) ^ ((toks[i] >> 1) & 3)) << 5) + (g & 3) * 8;
   }
-  const int n_off = 32768 + (lane < 16 ? wj * 512 + (lane * 8 + hl) * 4 : 1024 + wj * 512 + ((lane - 16) * 8 + hl) * 4);
 
   float o[8][4];
 #pragma unroll
