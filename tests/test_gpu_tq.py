@@ -458,3 +458,60 @@ def test_split_context_raw_partials_merge():
                                   torch.cuda.current_stream().cuda_stream)
     _lib.check(rc, "akv_lse_merge")
     assert (out.float() - full.float()).abs().max().item() < 1e-3
+
+
+@pytest.mark.parametrize("bits", BITS)
+def test_paged_attention_full_size_properties(bits):
+    """The headline workload at full size (16 sequences of 4096..32768 tokens, 32 query / 8 KV heads,
+    permuted block tables), checked through properties that do not need the oracle on 254 K tokens:
+      * every value vector of a (sequence, KV head) is the same vector, so whatever the scores are the
+        output must be that vector's decoded value (the softmax weights of all partials sum to one);
+      * the two shortest sequences are also compared with the oracle, element by element."""
+    from aitherkvcache_b200 import fused_tq4_kv_update
+    t = load_golden(f"tq_d128_b{bits}.npz")
+    tq = _tq(128, bits, t)
+    H, QH, D, BS, S = 8, 32, 128, 16, 16
+    gen = torch.Generator().manual_seed(1)
+    ctx = torch.randint(4096, 32769, (S,), generator=gen)
+    nblk = [(int(c) + BS - 1) // BS for c in ctx]
+    total = sum(nblk)
+    perm = torch.randperm(total, generator=gen)
+    bt = torch.zeros(S, max(nblk), dtype=torch.int32)
+    p = 0
+    for s, n in enumerate(nblk):
+        bt[s, :n] = perm[p:p + n].to(torch.int32)
+        p += n
+    pd = D * bits // 8
+    kp = torch.zeros(total, BS, H, pd, dtype=torch.uint8, device="cuda")
+    vp = torch.zeros_like(kp)
+    kn = torch.zeros(total, BS, H, device="cuda")
+    vn = torch.zeros_like(kn)
+    gg = torch.Generator(device="cuda").manual_seed(2)
+    v_const = torch.randn(S, H, D, generator=gg, device="cuda").half()
+    for s, n in enumerate(nblk):
+        c = int(ctx[s])
+        blocks = bt[s, :n].cuda().long()
+        slots = (blocks[:, None] * BS + torch.arange(BS, device="cuda")[None, :]).reshape(-1)[:c]
+        k = torch.randn(c, H, D, generator=gg, device="cuda").half()
+        fused_tq4_kv_update(k, slots, kp, kn, tq.rotation, tq.boundaries_inner, BS)
+        fused_tq4_kv_update(v_const[s][None].expand(c, H, D).contiguous(), slots, vp, vn, tq.rotation,
+                            tq.boundaries_inner, BS)
+    q = torch.randn(S, QH, D, generator=torch.Generator().manual_seed(5)).half().cuda()
+    out = _attn(tq, QH).forward(q, kp, kn, vp, vn, bt.cuda(), ctx.to(torch.int32).cuda()).float().cpu().numpy()
+
+    # property: out[s, qh] == the decoded value record of (s, qh // G), read back from the cache's first token
+    first = bt[:, 0].cuda().long()
+    assert all(torch.equal(vp[bt[s, (int(ctx[s]) - 1) // BS].item(), (int(ctx[s]) - 1) % BS], vp[first[s], 0])
+               for s in range(S))                                  # the records are indeed all the same
+    v_hat = tq.decode(vp[first, 0].reshape(-1, pd), vn[first, 0].reshape(-1)).float().reshape(S, H, D).cpu().numpy()
+    G = QH // H
+    want = np.repeat(v_hat, G, axis=1)
+    assert np.abs(out - want).max() <= 2e-3 * max(1.0, float(np.abs(want).max()))
+
+    # spot check against the oracle: the two shortest sequences
+    pick = np.argsort(ctx.numpy())[:2]
+    kp_h, kn_h, vp_h, vn_h = (x.cpu().numpy() for x in (kp, kn, vp, vn))
+    ref = otq.paged_attention_rotated(q.cpu().numpy()[pick], kp_h, kn_h, vp_h, vn_h, bt.numpy()[pick],
+                                      ctx.numpy()[pick].astype(np.int64), t["rotation"], t["centroids"], bits,
+                                      1.0 / math.sqrt(D))
+    assert (np.abs(out[pick] - ref) <= 2e-3 * np.maximum(1.0, np.abs(ref))).all()
