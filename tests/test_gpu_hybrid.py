@@ -132,3 +132,40 @@ def test_paged_attention_vs_oracle(H, QH, ctx):
     for s, c in enumerate(ctx):
         if c == 0:
             assert (out[s] == 0).all()
+
+
+def test_paged_attention_full_size_properties():
+    """tq35 attention at the headline shapes (16 sequences of 4096..32768 tokens, 32 query / 8 KV heads,
+    permuted block tables): with one value record per (sequence, KV head) repeated over all tokens the
+    output must be that record's decoded vector whatever the scores are; the shortest sequence is also
+    compared with the oracle."""
+    from aitherkvcache_b200.hybrid_quantizer import HybridPagedAttention
+    g = load_golden("hybrid_tq35.npz")
+    h = _htq("tq35", g, heads=1)
+    t = _oracle_tables(g, "tq35")
+    H, QH, D, BS, S = 8, 32, 128, 16, 16
+    gen = torch.Generator().manual_seed(1)
+    ctx = torch.randint(4096, 32769, (S,), generator=gen)
+    nblk = [(int(c) + BS - 1) // BS for c in ctx]
+    total = sum(nblk)
+    perm = torch.randperm(total, generator=gen)
+    bt = torch.zeros(S, max(nblk), dtype=torch.int32)
+    p = 0
+    for s, n in enumerate(nblk):
+        bt[s, :n] = perm[p:p + n].to(torch.int32)
+        p += n
+    gg = torch.Generator(device="cuda").manual_seed(2)
+    kc = h.encode(torch.randn(total, BS, H, D, generator=gg, device="cuda").half())
+    v_rec = h.encode(torch.randn(S, H, D, generator=gg, device="cuda").half())        # [S, H, packed_dim]
+    vc = torch.empty_like(kc)
+    for s, n in enumerate(nblk):
+        vc[bt[s, :n].cuda().long()] = v_rec[s][None, None].expand(n, BS, H, v_rec.shape[-1])
+    q = torch.randn(S, QH, D, generator=torch.Generator().manual_seed(5)).half().cuda()
+    out = HybridPagedAttention(h, QH).forward(q, kc, vc, bt.cuda(), ctx.to(torch.int32).cuda()).float().cpu().numpy()
+    want = np.repeat(h.decode(v_rec).float().cpu().numpy(), QH // H, axis=1)
+    assert np.abs(out - want).max() <= 2e-3 * max(1.0, float(np.abs(want).max()))
+
+    pick = np.argsort(ctx.numpy())[:1]
+    ref = ohy.paged_attention_decode_sdpa(q.cpu().numpy()[pick], kc.cpu().numpy(), vc.cpu().numpy(), bt.numpy()[pick],
+                                          ctx.numpy()[pick], t, 1.0 / math.sqrt(D), BS, kv_dtype=np.float32)
+    assert (np.abs(out[pick] - ref) <= 2e-3 * np.maximum(1.0, np.abs(ref))).all()
