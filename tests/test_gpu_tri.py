@@ -109,3 +109,36 @@ def test_split_ranges_merge_like_devices():
                                   out.stride(0), out.stride(1), torch.cuda.current_stream().cuda_stream)
     _lib.check(rc, "akv_lse_merge")
     assert (out - full).abs().max().item() < 1e-4
+
+
+def test_decode_step_full_size_properties():
+    """The 128K-token workload (1 x 131072 keys, 32 query / 8 KV heads): with the same value vector at
+    every position of a KV head the output must be that vector's spectral reconstruction whatever the
+    scores are, and splitting the key range in uneven parts and merging the raw partials must give
+    the same result as the single call."""
+    from aitherkvcache_b200 import _lib
+    from aitherkvcache_b200.triattention import SpectralEncoding
+    B, S, H, QH = 1, 131072, 8, 32
+    tri = _tri(H, QH)
+    keys, _, g = _synthetic(B, S, H, seed=9)
+    v_one = torch.randn(B, 1, H, 128, generator=g).half()
+    q = torch.randn(B, QH, 128, generator=g).half().cuda()
+    k_enc, v_enc = tri.encode_kv(keys.cuda(), v_one.expand(B, S, H, 128).contiguous().cuda())
+    out = tri.decode_step(q, k_enc, v_enc)
+    first = SpectralEncoding(v_enc.indices[:, :1], v_enc.packed[:, :1], v_enc.scales[:, :1])
+    want = tri.encoder.decode(first)[:, 0].repeat_interleave(QH // H, dim=1)          # [B, QH, 128]
+    assert (out.float() - want).abs().max().item() <= 2e-3 * max(1.0, want.abs().max().item())
+
+    bounds = [0, 1, 40000, 40000, 131071, 131072]
+    parts = []
+    for r in range(len(bounds) - 1):
+        lo, hi = bounds[r], bounds[r + 1]
+        sl = lambda e: SpectralEncoding(e.indices[:, lo:hi].contiguous(), e.packed[:, lo:hi].contiguous(),   # noqa: E731
+                                        e.scales[:, lo:hi].contiguous())
+        parts.append(tri.decode_step_partial(q, sl(k_enc), sl(v_enc), key_pos_start=lo, query_pos_default=S))
+    stacked = torch.stack(parts).contiguous()
+    merged = torch.empty(B, QH, 128, dtype=torch.float32, device="cuda")
+    rc = _lib.lib().akv_lse_merge(stacked.data_ptr(), len(parts), B, QH, 128, None, merged.data_ptr(), _lib.AKV_F32,
+                                  merged.stride(0), merged.stride(1), torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "akv_lse_merge")
+    assert (merged - out.float()).abs().max().item() < 1e-3
