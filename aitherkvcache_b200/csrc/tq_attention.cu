@@ -19,6 +19,7 @@
 //     any GQA ratio.  Scalar; lanes own dims.
 #include "common.cuh"
 #include "tq_rowmap.cuh"
+#include "tq_encode_generic.cuh"
 #include <math_constants.h>
 #include <stdlib.h>
 
@@ -111,10 +112,27 @@ __device__ void streamk_plan(const StreamKPlanArgs& p) {
   if (tid == 0) { p.sk[S] = T; p.sk[S + 1] = chunk; }
 }
 
+// The new token's K and V vectors of a decode step, written into the paged cache by extra blocks of
+// the query-rotation launch (n_rows vectors each; n_rows == 0: nothing to write).
+struct NewTokenWrite {
+  RowMap k, v;
+  int64_t n_rows;
+  int bits;
+  const float* boundaries;
+};
+
 __global__ void akv_qrot_kernel(const void* __restrict__ q, int q_dtype, int64_t q_ss, int64_t q_sh,
                                 int num_q_heads, int D, const float* __restrict__ rot_t,
-                                float premul, float* __restrict__ qrot, int rows, StreamKPlanArgs plan) {
-  extern __shared__ float qs[];
+                                float premul, float* __restrict__ qrot, int rows, int plan_blocks,
+                                StreamKPlanArgs plan, NewTokenWrite nt) {
+  extern __shared__ __align__(16) float qs[];
+  if ((int)blockIdx.x >= rows + plan_blocks) {   // blocks past the plan block: one K or V vector each (128 threads)
+    const int64_t e = (int64_t)blockIdx.x - rows - plan_blocks;
+    const bool is_v = e >= nt.n_rows;
+    encode_generic_rows(is_v ? nt.v : nt.k, is_v ? e - nt.n_rows : e, nt.n_rows, nt.n_rows, D, nt.bits, rot_t,
+                        nt.boundaries);
+    return;
+  }
   if ((int)blockIdx.x == rows) {   // the extra block computes the stream-K plan
     streamk_plan(plan);
     return;
@@ -2050,10 +2068,14 @@ AKV_EXPORT size_t akv_tq_paged_attn_workspace_bytes(int num_seqs, int num_q_head
 }
 
 namespace akv {
-int run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t workspace_bytes, bool allow_persist = true);
+// new_token (optional): K and V vectors to write into the cache by the first launch; once the arguments
+// have passed validation that launch always happens.
+int run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t workspace_bytes, bool allow_persist = true,
+                const NewTokenWrite* new_token = nullptr);
 }
 
-int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t workspace_bytes, bool allow_persist) {
+int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t workspace_bytes, bool allow_persist,
+                     const NewTokenWrite* new_token) {
   if (!p) return fail(AKV_ERR_ARG, "null params");
   if (p->bits != 2 && p->bits != 3 && p->bits != 4)
     return fail(AKV_ERR_ARG, "Supported bit-widths: 2, 3, 4. Got %d", p->bits);
@@ -2118,9 +2140,16 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
   static const int sk_wph = (getenv("AKV_SK_WPH") && atoi(getenv("AKV_SK_WPH")) == 2) ? 2 : 1;
   pl.parts_per_cta = sk4 ? 1 : sk_wph;
   pl.blocks_per_stage = sk4 ? 4 : 2;
-  akv_qrot_kernel<<<rows + (persist ? 1 : 0), D < 128 ? D : 128, D * sizeof(float), st>>>(
+  NewTokenWrite nt{};
+  size_t qrot_smem = D * sizeof(float);
+  if (new_token != nullptr && new_token->n_rows > 0) {       // D >= 128 here (the caller checked): 128-thread blocks
+    nt = *new_token;
+    qrot_smem = (size_t)(D + D / 4 + 16) * sizeof(float);
+  }
+  const int plan_blocks = persist ? 1 : 0;
+  akv_qrot_kernel<<<rows + plan_blocks + (unsigned)(2 * nt.n_rows), D < 128 ? D : 128, qrot_smem, st>>>(
       p->query, p->q_dtype, p->q_stride_seq, p->q_stride_head, p->num_q_heads, D, p->rotation_t,
-      p->scale * 1.4426950408889634f, qrot, rows, pl);
+      p->scale * 1.4426950408889634f, qrot, rows, plan_blocks, pl, nt);
   if (int rc = check_launch("akv_qrot_kernel")) return rc;
 
   AttnArgs a{};
@@ -2255,6 +2284,13 @@ AKV_EXPORT int akv_tq_decode_step(const akv_tq_decode_step_params* p) {
       mv.packed = const_cast<uint8_t*>(a.v_packed); mv.norms = const_cast<float*>(a.v_norms);
       mv.p_stride_blk = a.vp_stride_blk; mv.p_stride_pos = a.vp_stride_pos; mv.p_stride_head = a.vp_stride_head;
       mv.n_stride_blk = a.vn_stride_blk; mv.n_stride_pos = a.vn_stride_pos; mv.n_stride_head = a.vn_stride_head;
+      // head_dim 128 or 256 and at least one sequence: the vectors ride in the attention's first launch (if the
+      // attention arguments are rejected nothing is written and the error is returned)
+      if (D >= 128 && D <= 256 && a.num_seqs > 0) {
+        NewTokenWrite nt{};
+        nt.k = mk; nt.v = mv; nt.n_rows = rows; nt.bits = a.bits; nt.boundaries = p->boundaries;
+        return run_tq_attn(&p->attn, a.workspace, a.workspace_bytes, true, &nt);
+      }
       if (int rc = launch_encode_generic_pair(mk, mv, rows, D, a.bits, a.rotation_t, p->boundaries, (cudaStream_t)a.stream))
         return rc;
       return run_tq_attn(&p->attn, a.workspace, a.workspace_bytes);

@@ -14,21 +14,10 @@
 //   * code = number of boundaries strictly below y (searchsorted "left").
 #include "common.cuh"
 #include "tq_rowmap.cuh"
+#include "tq_encode_generic.cuh"
 #include <stdlib.h>
 
 namespace akv {
-
-// Sum of squares of `d` floats spaced `stride` apart, in the reference's order.
-// Called by 8 consecutive lanes (j = lane & 7); every one of them returns the total.
-__device__ __forceinline__ float sumsq_8lane(const float* row, int d, int j, unsigned mask) {
-  float s = 0.f;
-  for (int i = j; i < d; i += 8) s = __fadd_rn(s, __fmul_rn(row[i], row[i]));
-  int base = (threadIdx.x & 31) & ~7;
-  float tot = __shfl_sync(mask, s, base);
-#pragma unroll
-  for (int k = 1; k < 8; ++k) tot = __fadd_rn(tot, __shfl_sync(mask, s, base + k));
-  return tot;
-}
 
 __device__ __forceinline__ int quantize(float y, const float* bnd, int nb) {
   int c = 0;
@@ -251,79 +240,17 @@ tq_decode_tiled_kernel(const uint8_t* __restrict__ packed, int64_t p_stride_row,
 // Any power-of-two head_dim up to 1024: one warp per vector, the matrix is read
 // through L2.  Slow path for shapes outside {64, 128}.
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ void encode_generic_rows(const RowMap& m, int64_t n_rows, int D, int bits,
-                                                    const float* __restrict__ rot_t,
-                                                    const float* __restrict__ boundaries) {
-  // one CTA per vector: thread o produces outputs o, o+128, ...
-  extern __shared__ __align__(16) float smem_f[];
-  float* u = smem_f;                                        // [D]
-  uint8_t* codes = reinterpret_cast<uint8_t*>(u + D);       // [D]
-  __shared__ float s_nrm;
-  const int tid = threadIdx.x;
-  const int nb = (1 << bits) - 1;
-  const int pd = D * bits / 8;
-  for (int64_t n = blockIdx.x; n < n_rows; n += gridDim.x) {
-    RowAddr a = map_row(m, n);
-    for (int i = tid; i < D; i += 128) u[i] = load_as_float(a.src_base, m.x_dtype, a.src_off + i);
-    __syncthreads();
-    if (tid < 32) {
-      float tot = sumsq_8lane(u, D, tid & 7, 0xffffffffu);
-      if (tid == 0) s_nrm = __fsqrt_rn(tot);
-    }
-    __syncthreads();
-    const float nrm = s_nrm;
-    const float den = __fadd_rn(nrm, 1e-10f);
-    for (int i = tid; i < D; i += 128) u[i] = __fdiv_rn(u[i], den);
-    __syncthreads();
-    for (int o = tid; o < D; o += 128) {
-      float y = 0.f;      // one chain in the order j = 0..D-1 (bit-identical to the tiled kernel)
-      int j0 = 0;
-      for (; j0 + 32 <= D; j0 += 32) {       // 32 loads in flight per round: the matrix comes from L2
-        float r[32];
-#pragma unroll
-        for (int k = 0; k < 32; ++k) r[k] = rot_t[(int64_t)(j0 + k) * D + o];
-#pragma unroll
-        for (int k = 0; k < 32; ++k) y = __fmaf_rn(u[j0 + k], r[k], y);
-      }
-      for (; j0 < D; j0 += 8) {              // D is a multiple of 8
-        float r[8];
-#pragma unroll
-        for (int k = 0; k < 8; ++k) r[k] = rot_t[(int64_t)(j0 + k) * D + o];
-#pragma unroll
-        for (int k = 0; k < 8; ++k) y = __fmaf_rn(u[j0 + k], r[k], y);
-      }
-      int c = 0;
-      for (int k = 0; k < nb; ++k) c += (boundaries[k] < y) ? 1 : 0;
-      codes[o] = (uint8_t)c;
-    }
-    __syncthreads();
-    if (a.dst != nullptr) {
-      for (int bi = tid; bi < pd; bi += 128) {
-        int val = 0;
-        for (int bit = 0; bit < 8; ++bit) {
-          int pos = bi * 8 + bit;
-          int k = pos / bits, off = pos - k * bits;
-          val = (val << 1) | ((codes[k] >> (bits - 1 - off)) & 1);
-        }
-        a.dst[bi] = (uint8_t)val;
-      }
-      if (tid == 0) *a.dst_norm = nrm;
-    }
-    __syncthreads();
-  }
-}
-
 __global__ void __launch_bounds__(128)
 tq_encode_generic_kernel(RowMap m, int64_t n_rows, int D, int bits, const float* __restrict__ rot_t,
                          const float* __restrict__ boundaries) {
-  encode_generic_rows(m, n_rows, D, bits, rot_t, boundaries);
+  encode_generic_rows(m, blockIdx.x, gridDim.x, n_rows, D, bits, rot_t, boundaries);
 }
 
 // The K and the V vectors of a decode step in one launch: blockIdx.y picks the tensor.
 __global__ void __launch_bounds__(128)
 tq_encode_generic_pair_kernel(RowMap mk, RowMap mv, int64_t n_rows, int D, int bits,
                               const float* __restrict__ rot_t, const float* __restrict__ boundaries) {
-  encode_generic_rows(blockIdx.y ? mv : mk, n_rows, D, bits, rot_t, boundaries);
+  encode_generic_rows(blockIdx.y ? mv : mk, blockIdx.x, gridDim.x, n_rows, D, bits, rot_t, boundaries);
 }
 
 __global__ void __launch_bounds__(128)
