@@ -61,15 +61,50 @@ def peak_hbm():
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    """SM clock and throttle reasons sampled while the timed region runs: NVML polled from a thread,
+    else nvidia-smi every 200 ms."""
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
+    _NVML_REASONS = ((0x8, "hw_slowdown"), (0x40, "hw_thermal_slowdown"), (0x20, "sw_thermal_slowdown"),
+                     (0x4, "sw_power_cap"))
+
     def __init__(self, gpu_index):
         self.gpu, self.proc, self.path = gpu_index, None, None
+        self.thread, self.samples, self.halt, self.max_mhz = None, [], False, None
+
+    def _start_nvml(self):
+        """Poll NVML from a thread (a timed region of a few milliseconds is over before nvidia-smi's
+        first 200 ms tick).  Read-only queries."""
+        import threading
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            uuid = str(torch.cuda.get_device_properties(self.gpu).uuid)
+            h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+        except Exception:
+            h = pynvml.nvmlDeviceGetHandleByIndex(self.gpu)
+        self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+
+        def poll():
+            while not self.halt:
+                try:
+                    self.samples.append((float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)),
+                                         int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h))))
+                except Exception:
+                    break
+                time.sleep(0.0005)
+
+        self.thread = threading.Thread(target=poll, daemon=True)
+        self.thread.start()
 
     def start(self):
+        try:
+            self._start_nvml()
+            return
+        except Exception:
+            self.thread = None
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
@@ -81,6 +116,17 @@ class ClockSampler:
 
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.thread is not None:
+            self.halt = True
+            self.thread.join(timeout=2)
+            if self.samples:
+                mask = 0
+                for _, m in self.samples:
+                    mask |= m
+                return {"sm_mhz": float(np.median([c for c, _ in self.samples])), "sm_max_mhz": self.max_mhz,
+                        "reasons": sorted(n for bit, n in self._NVML_REASONS if mask & bit),
+                        "samples": len(self.samples), "source": "nvml, polled during the timed region"}
+            return out
         if self.proc is None:
             return out
         time.sleep(0.25)
@@ -393,8 +439,10 @@ def run_tri128k(args, rank, world, local):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=None,
+                    help="timed steps (default 1000: a timed region of 0.1 s, long enough for the clock sampler; "
+                         "30 for --impl reference, whose steps take seconds)")
+    ap.add_argument("--warmup", type=int, default=None, help="untimed steps first (default 20; 5 for --impl reference)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--replicas", type=int, default=2, help="cache copies cycled through (L2 defeat)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -402,6 +450,11 @@ def main():
     ap.add_argument("--workload", default="decode_tq4", choices=["decode_tq4", "tri128k", "micro"],
                     help="decode_tq4 is the headline configuration; the others are secondary measurements")
     args = ap.parse_args()
+    slow = args.impl == "reference" or args.workload != "decode_tq4"
+    if args.steps is None:
+        args.steps = 30 if slow else 1000
+    if args.warmup is None:
+        args.warmup = 5 if slow else 20
     args.warmup = max(args.warmup, 3)
 
     rank = int(os.environ.get("RANK", 0))
