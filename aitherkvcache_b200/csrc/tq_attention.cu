@@ -81,9 +81,10 @@ struct StreamKPlanArgs {
 __device__ void streamk_plan(const StreamKPlanArgs& p) {
   __shared__ int s_part[128];
   __shared__ int s_total;
-  const int S = p.num_seqs, tid = threadIdx.x, nthr = blockDim.x;
+  const int S = p.num_seqs, tid = threadIdx.x, nthr = blockDim.x < 128 ? blockDim.x : 128;
   const int per = (S + nthr - 1) / nthr;
-  const int s0 = tid * per, s1 = (s0 + per < S) ? s0 + per : S;
+  const bool act = tid < nthr;             // threads past the first 128 only keep the barriers company
+  const int s0 = act ? tid * per : S, s1 = (s0 + per < S) ? s0 + per : S;
   int local = 0;
   for (int s = s0; s < s1; ++s) {
     const int64_t ctx = load_index(p.context_lens, p.cl_dtype, s);
@@ -91,7 +92,7 @@ __device__ void streamk_plan(const StreamKPlanArgs& p) {
     p.sk[3 * S + 2 + s] = nb;
     local += (nb + p.blocks_per_stage - 1) / p.blocks_per_stage;
   }
-  s_part[tid] = local;
+  if (act) s_part[tid] = local;
   __syncthreads();
   if (tid == 0) {
     int run = 0;
@@ -101,7 +102,7 @@ __device__ void streamk_plan(const StreamKPlanArgs& p) {
   __syncthreads();
   const int T = s_total;
   const int chunk = T > 0 ? (T + p.grid - 1) / p.grid : 1;
-  int run = s_part[tid];
+  int run = act ? s_part[tid] : 0;
   for (int s = s0; s < s1; ++s) {
     const int cnt = (p.sk[3 * S + 2 + s] + p.blocks_per_stage - 1) / p.blocks_per_stage;
     p.sk[s] = run;
@@ -181,8 +182,10 @@ __global__ void akv_merge_kernel(MergeArgs a) {
   // weights w_p = 2^(m_p - M) for parts with l_p > 0 (first warp), L = sum l_p w_p
   if (threadIdx.x < 32) {
     float M = -CUDART_INF_F;
-    for (int p = threadIdx.x; p < np; p += 32)
-      if (ml[(int64_t)p * a.ml_part + 1] > 0.f) M = fmaxf(M, ml[(int64_t)p * a.ml_part]);
+    for (int p = threadIdx.x; p < np; p += 32) {
+      const float m = ml[(int64_t)p * a.ml_part], l = ml[(int64_t)p * a.ml_part + 1];   // both loads in flight together
+      if (l > 0.f) M = fmaxf(M, m);
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
     float L = 0.f;
@@ -212,9 +215,15 @@ __global__ void akv_merge_kernel(MergeArgs a) {
         o4[k & 3] = (w != 0.f) ? __fmaf_rn(v[k], w, o4[k & 3]) : o4[k & 3];
       }
     }
-    for (; p < np; ++p) {
-      const float w = wts[p];
-      if (w != 0.f) o4[0] = __fmaf_rn(acc[(int64_t)p * a.acc_part + d], w, o4[0]);
+    if (p < np) {                          // the last np % 8 parts: one masked round, loads in flight together
+      float v[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] = (p + k < np) ? acc[(int64_t)(p + k) * a.acc_part + d] : 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float w = (p + k < np) ? wts[p + k] : 0.f;
+        o4[k & 3] = (w != 0.f) ? __fmaf_rn(v[k], w, o4[k & 3]) : o4[k & 3];
+      }
     }
     const float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
     if (a.mode == MERGE_RAW) {
@@ -247,8 +256,192 @@ __global__ void akv_merge_kernel(MergeArgs a) {
   }
 }
 
+
+// ---------------------------------------------------------------------------
+// head_dim 128: the same two kernels with the 64 KB rotation matrix staged in shared memory.
+// 512 threads; each group of 128 threads owns one (sequence, q head) row at a time, a CTA walks over
+// row quads.  The matrix is copied once per CTA with cp.async while the rows' own data arrives, so a
+// row costs one trip to L2 for its inputs and none for the matrix.  Summation orders are those of
+// akv_qrot_kernel / akv_merge_kernel: results are bit-identical.
+// ---------------------------------------------------------------------------
+constexpr int ROT128_THREADS = 512;
+constexpr int ROT128_MAT_BYTES = 128 * 128 * 4;
+
+__device__ __forceinline__ void stage_matrix128(float* dst, const float* __restrict__ src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  for (int i = threadIdx.x; i < 128 * 128 / 4; i += ROT128_THREADS)
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" :: "r"(d + i * 16), "l"(src + i * 4));
+  asm volatile("cp.async.commit_group;\n" ::);
+}
+__device__ __forceinline__ void group_sync(int g) {      // the 128 threads of row group g
+  asm volatile("bar.sync %0, 128;\n" :: "r"(g + 1) : "memory");
+}
+
+__global__ void __launch_bounds__(ROT128_THREADS)
+akv_qrot128_kernel(const void* __restrict__ q, int q_dtype, int64_t q_ss, int64_t q_sh, int num_q_heads,
+                   const float* __restrict__ rot_t, float premul, float* __restrict__ qrot, int rows,
+                   int rot_blocks, int plan_blocks, StreamKPlanArgs plan, NewTokenWrite nt) {
+  extern __shared__ __align__(16) float qs[];
+  constexpr int D = 128;
+  // block order: the new token's vectors first (the longest-running blocks, so they start at once), then
+  // the plan block, then the rotation blocks
+  const int enc_blocks = (int)(2 * nt.n_rows);
+  if ((int)blockIdx.x < enc_blocks) {       // one K or V vector of the new token
+    const int64_t e = blockIdx.x;
+    const bool is_v = e >= nt.n_rows;
+    encode_generic_rows(is_v ? nt.v : nt.k, is_v ? e - nt.n_rows : e, nt.n_rows, nt.n_rows, D, nt.bits, rot_t,
+                        nt.boundaries);
+    return;
+  }
+  if ((int)blockIdx.x < enc_blocks + plan_blocks) {
+    streamk_plan(plan);
+    return;
+  }
+  const int rb = (int)blockIdx.x - enc_blocks - plan_blocks;      // rotation block index
+  float* mat = qs;                          // [128][128]: mat[j * 128 + i] = rot_t[j * 128 + i]
+  float* qv = qs + D * D;                   // [4][128]
+  stage_matrix128(mat, rot_t);
+  const int g = threadIdx.x >> 7, i = threadIdx.x & 127;
+  bool first = true;
+  for (int r0 = rb * 4; r0 < rows; r0 += rot_blocks * 4) {
+    const int row = r0 + g;
+    const bool live = row < rows;
+    if (live) {
+      const int s = row / num_q_heads, qh = row % num_q_heads;
+      qv[g * D + i] = load_as_float(q, q_dtype, s * q_ss + qh * q_sh + i);
+    }
+    if (first) {
+      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+      __syncthreads();                      // matrix and the first quad of queries
+      first = false;
+    } else {
+      group_sync(g);
+    }
+    if (live) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 8
+      for (int j = 0; j < D; j += 4) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) acc[k] = __fmaf_rn(mat[(j + k) * D + i], qv[g * D + j + k], acc[k]);
+      }
+      qrot[(int64_t)row * D + i] = ((acc[0] + acc[1]) + (acc[2] + acc[3])) * premul;
+    }
+    group_sync(g);                          // qv[g] is free again
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+}
+
+__global__ void __launch_bounds__(ROT128_THREADS)
+akv_merge128_kernel(MergeArgs a, int rows, int np_alloc) {
+  extern __shared__ __align__(16) float sm[];
+  constexpr int D = 128;
+  float* mat = sm;                          // [128][128]: rot[i * 128 + j]
+  float* vec = sm + D * D;                  // [4][128] merged vectors
+  float* wall = vec + 4 * D;                // [4][np_alloc] weights
+  float* red = wall + 4 * np_alloc;         // [4][2]  M, L
+  stage_matrix128(mat, a.rot);
+  const int g = threadIdx.x >> 7, d = threadIdx.x & 127;
+  float* wts = wall + g * np_alloc;
+  bool first = true;
+  for (int r0 = blockIdx.x * 4; r0 < rows; r0 += gridDim.x * 4) {
+    const int row = r0 + g;
+    const bool live = row < rows;
+    const int seq = live ? row / a.num_q_heads : 0, qh = live ? row % a.num_q_heads : 0;
+    int np = 0;
+    if (live) {
+      np = a.np;
+      if (a.part_counts != nullptr) {
+        np = a.part_counts[seq] < np ? a.part_counts[seq] : np;
+      } else if (a.context_lens != nullptr) {
+        int64_t ctx = load_index(a.context_lens, a.cl_dtype, seq);
+        int64_t splits = (ctx + a.tokens_per_split - 1) / a.tokens_per_split;
+        int64_t v = splits * a.warps_per_head;
+        np = (int)(v < np ? v : np);
+      }
+      if (d < 32) {                         // first warp of the group: weights, as in akv_merge_kernel
+        const float* ml = a.ml + (int64_t)row * a.ml_row;
+        float M = -CUDART_INF_F;
+        for (int p = d; p < np; p += 32) {
+          const float m = ml[(int64_t)p * a.ml_part], l = ml[(int64_t)p * a.ml_part + 1];
+          if (l > 0.f) M = fmaxf(M, m);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        float L = 0.f;
+        for (int p = d; p < np; p += 32) {
+          const float l = ml[(int64_t)p * a.ml_part + 1];
+          const float w = (l > 0.f) ? exp2f(ml[(int64_t)p * a.ml_part] - M) : 0.f;
+          wts[p] = w;
+          L += l * w;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+        if (d == 0) { red[2 * g] = M; red[2 * g + 1] = L; }
+      }
+    }
+    group_sync(g);
+    if (live) {
+      const float L = red[2 * g + 1];
+      const float* acc = a.acc + (int64_t)row * a.acc_row;
+      float o4[4] = {0.f, 0.f, 0.f, 0.f};
+      int p = 0;
+      for (; p + 8 <= np; p += 8) {
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = acc[(int64_t)(p + k) * a.acc_part + d];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float w = wts[p + k];
+          o4[k & 3] = (w != 0.f) ? __fmaf_rn(v[k], w, o4[k & 3]) : o4[k & 3];
+        }
+      }
+      if (p < np) {                        // the last np % 8 parts: one masked round
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = (p + k < np) ? acc[(int64_t)(p + k) * a.acc_part + d] : 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float w = (p + k < np) ? wts[p + k] : 0.f;
+          o4[k & 3] = (w != 0.f) ? __fmaf_rn(v[k], w, o4[k & 3]) : o4[k & 3];
+        }
+      }
+      const float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
+      vec[g * D + d] = (L > 0.f) ? o / L : 0.f;
+    }
+    if (first) {
+      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+      __syncthreads();                      // matrix and the first quad of merged vectors
+      first = false;
+    } else {
+      group_sync(g);
+    }
+    if (live) {
+      float x4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 8
+      for (int i = 0; i < D; i += 4) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) x4[k] = __fmaf_rn(vec[g * D + i + k], mat[(i + k) * D + d], x4[k]);
+      }
+      store_from_float(a.out, a.out_dtype, seq * a.out_ss + qh * a.out_sh + d, (x4[0] + x4[1]) + (x4[2] + x4[3]));
+    }
+    group_sync(g);                          // vec[g], wts and red[g] are free again
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+}
+
 int launch_merge(const MergeArgs& a, int rows, cudaStream_t st) {
-  akv_merge_kernel<<<rows, a.D < 128 ? (a.D < 32 ? 32 : a.D) : 128, (a.D + (a.np > 0 ? a.np : 1)) * sizeof(float), st>>>(a);
+  const int np_alloc = a.np > 0 ? a.np : 1;
+  static const bool no_rot128 = getenv("AKV_NO_ROT128") != nullptr;
+  const size_t smem128 = (size_t)ROT128_MAT_BYTES + (size_t)(4 * 128 + 4 * np_alloc + 8) * sizeof(float);
+  if (a.D == 128 && a.mode == MERGE_ROTATE && !no_rot128 && rows > 0 && smem128 <= 200 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(akv_merge128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem128);
+    if (e != cudaSuccess) return fail((int)e, "merge: smem attribute: %s", cudaGetErrorString(e));
+    const int quads = (rows + 3) / 4;
+    const int grid = quads < 2 * sm_count() ? quads : 2 * sm_count();
+    akv_merge128_kernel<<<grid, ROT128_THREADS, smem128, st>>>(a, rows, np_alloc);
+    return check_launch("akv_merge128_kernel");
+  }
+  akv_merge_kernel<<<rows, a.D < 128 ? (a.D < 32 ? 32 : a.D) : 128, (a.D + np_alloc) * sizeof(float), st>>>(a);
   return check_launch("akv_merge_kernel");
 }
 
@@ -2147,10 +2340,24 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
     qrot_smem = (size_t)(D + D / 4 + 16) * sizeof(float);
   }
   const int plan_blocks = persist ? 1 : 0;
-  akv_qrot_kernel<<<rows + plan_blocks + (unsigned)(2 * nt.n_rows), D < 128 ? D : 128, qrot_smem, st>>>(
-      p->query, p->q_dtype, p->q_stride_seq, p->q_stride_head, p->num_q_heads, D, p->rotation_t,
-      p->scale * 1.4426950408889634f, qrot, rows, plan_blocks, pl, nt);
-  if (int rc = check_launch("akv_qrot_kernel")) return rc;
+  static const bool no_rot128 = getenv("AKV_NO_ROT128") != nullptr;
+  if (D == 128 && !no_rot128) {            // rotation matrix staged in shared memory, four rows per CTA pass
+    const size_t smem128 = (size_t)ROT128_MAT_BYTES + 4 * 128 * sizeof(float);
+    cudaError_t e = cudaFuncSetAttribute(akv_qrot128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem128);
+    if (e != cudaSuccess) return fail((int)e, "attention: smem attribute: %s", cudaGetErrorString(e));
+    const int quads = (rows + 3) / 4;
+    const int rot_blocks = quads < 2 * sm_count() ? quads : 2 * sm_count();
+    akv_qrot128_kernel<<<rot_blocks + plan_blocks + (unsigned)(2 * nt.n_rows), ROT128_THREADS, smem128, st>>>(
+        p->query, p->q_dtype, p->q_stride_seq, p->q_stride_head, p->num_q_heads, p->rotation_t,
+        p->scale * 1.4426950408889634f, qrot, rows, rot_blocks, plan_blocks, pl, nt);
+    if (int rc = check_launch("akv_qrot128_kernel")) return rc;
+  } else {
+    const int qrot_threads = D < 128 ? D : 128;
+    akv_qrot_kernel<<<rows + plan_blocks + (unsigned)(2 * nt.n_rows), qrot_threads, qrot_smem, st>>>(
+        p->query, p->q_dtype, p->q_stride_seq, p->q_stride_head, p->num_q_heads, D, p->rotation_t,
+        p->scale * 1.4426950408889634f, qrot, rows, plan_blocks, pl, nt);
+    if (int rc = check_launch("akv_qrot_kernel")) return rc;
+  }
 
   AttnArgs a{};
   a.k_packed = p->k_packed; a.v_packed = p->v_packed;

@@ -1,6 +1,6 @@
 // The one-vector-per-CTA TurboQuant encoder (any power-of-two head_dim up to 1024), as a device
 // function so that a small batch - the new token of a decode step - can ride in another kernel's launch.
-// 128 threads; dynamic shared memory (D + D/4 + 16) floats.  Same arithmetic, in the same order, as the
+// Any block size that is a multiple of 32; dynamic shared memory (D + D/4 + 16) floats.  Same arithmetic, in the same order, as the
 // tiled encoders (reference semantics: aither_kvcache/quantizer.py:90-125).
 #pragma once
 
@@ -29,12 +29,12 @@ __device__ __forceinline__ void encode_generic_rows(const RowMap& m, int64_t fir
   float* u = smem_f;                                        // [D]
   uint8_t* codes = reinterpret_cast<uint8_t*>(u + D);       // [D]
   __shared__ float s_nrm;
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, nthr = blockDim.x;
   const int nb = (1 << bits) - 1;
   const int pd = D * bits / 8;
   for (int64_t n = first; n < n_rows; n += step) {
     RowAddr a = map_row(m, n);
-    for (int i = tid; i < D; i += 128) u[i] = load_as_float(a.src_base, m.x_dtype, a.src_off + i);
+    for (int i = tid; i < D; i += nthr) u[i] = load_as_float(a.src_base, m.x_dtype, a.src_off + i);
     __syncthreads();
     if (tid < 32) {
       float tot = sumsq_8lane(u, D, tid & 7, 0xffffffffu);
@@ -43,9 +43,9 @@ __device__ __forceinline__ void encode_generic_rows(const RowMap& m, int64_t fir
     __syncthreads();
     const float nrm = s_nrm;
     const float den = __fadd_rn(nrm, 1e-10f);
-    for (int i = tid; i < D; i += 128) u[i] = __fdiv_rn(u[i], den);
+    for (int i = tid; i < D; i += nthr) u[i] = __fdiv_rn(u[i], den);
     __syncthreads();
-    for (int o = tid; o < D; o += 128) {
+    for (int o = tid; o < D; o += nthr) {
       float y = 0.f;      // one chain in the order j = 0..D-1 (bit-identical to the tiled kernel)
       int j0 = 0;
       for (; j0 + 32 <= D; j0 += 32) {       // 32 loads in flight per round: the matrix comes from L2
@@ -68,7 +68,7 @@ __device__ __forceinline__ void encode_generic_rows(const RowMap& m, int64_t fir
     }
     __syncthreads();
     if (a.dst != nullptr) {
-      for (int bi = tid; bi < pd; bi += 128) {
+      for (int bi = tid; bi < pd; bi += nthr) {
         int val = 0;
         for (int bit = 0; bit < 8; ++bit) {
           int pos = bi * 8 + bit;
