@@ -348,6 +348,8 @@ akv_merge128_kernel(MergeArgs a, int rows, int np_alloc) {
     const bool live = row < rows;
     const int seq = live ? row / a.num_q_heads : 0, qh = live ? row % a.num_q_heads : 0;
     int np = 0;
+    constexpr int MP = 24;
+    float v[MP];
     if (live) {
       np = a.np;
       if (a.part_counts != nullptr) {
@@ -357,6 +359,13 @@ akv_merge128_kernel(MergeArgs a, int rows, int np_alloc) {
         int64_t splits = (ctx + a.tokens_per_split - 1) / a.tokens_per_split;
         int64_t v = splits * a.warps_per_head;
         np = (int)(v < np ? v : np);
+      }
+      // the partial sums do not depend on the weights: up to MP parts are requested now and arrive while
+      // the group's first warp works the weights out
+      if (np <= MP) {
+        const float* accp = a.acc + (int64_t)row * a.acc_row + d;
+#pragma unroll
+        for (int k = 0; k < MP; ++k) v[k] = (k < np) ? accp[(int64_t)k * a.acc_part] : 0.f;
       }
       if (d < 32) {                         // first warp of the group: weights, as in akv_merge_kernel
         const float* ml = a.ml + (int64_t)row * a.ml_row;
@@ -385,6 +394,14 @@ akv_merge128_kernel(MergeArgs a, int rows, int np_alloc) {
       const float* acc = a.acc + (int64_t)row * a.acc_row;
       float o4[4] = {0.f, 0.f, 0.f, 0.f};
       int p = 0;
+      if (np <= MP) {                       // same order of additions as the rounds of eight below
+#pragma unroll
+        for (int k = 0; k < MP; ++k) {
+          const float w = (k < np) ? wts[k] : 0.f;
+          o4[k & 3] = (w != 0.f) ? __fmaf_rn(v[k], w, o4[k & 3]) : o4[k & 3];
+        }
+        p = np;
+      }
       for (; p + 8 <= np; p += 8) {
         float v[8];
 #pragma unroll
