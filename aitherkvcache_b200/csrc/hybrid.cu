@@ -1418,15 +1418,16 @@ hybrid_merge_kernel(const float* __restrict__ part_acc, const float* __restrict_
     }
     __syncthreads();
     const int cnt = np - p0 < 256 ? np - p0 : 256;
-    int q = 0;
-    for (; q + 8 <= cnt; q += 8) {
-      float v[8];
+    for (int q = 0; q < cnt; q += 16) {     // 16 loads in flight per round, the last round masked
+      float v[16];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) v[k] = pa[(int64_t)(p0 + q + k) * 256];
+      for (int k = 0; k < 16; ++k) v[k] = (q + k < cnt) ? pa[(int64_t)(p0 + q + k) * 256] : 0.f;
 #pragma unroll
-      for (int k = 0; k < 8; ++k) acc = __fmaf_rn(v[k], wgt[q + k], acc);   // weight 0: part never written
+      for (int k = 0; k < 16; ++k) {
+        const float wv = (q + k < cnt) ? wgt[q + k] : 0.f;
+        acc = (wv > 0.f) ? __fmaf_rn(v[k], wv, acc) : acc;                   // weight 0: part never written
+      }
     }
-    for (; q < cnt; ++q) if (wgt[q] > 0.f) acc = __fmaf_rn(pa[(int64_t)(p0 + q) * 256], wgt[q], acc);
   }
   const float L = block_reduce_256(ls, false, scratch);
   const float inv = L > 0.f ? 1.f / L : 0.f;
