@@ -126,7 +126,10 @@ int akv_tq_paged_attn(const akv_tq_attn_params* params);
  * reference's tq::decode_step op (aither_kvcache/vllm/hooks.py:150-195:
  * encode + index-put of K and V, then TQPagedAttention.forward).  max_blocks
  * bounds the slots that are written (0 is not allowed: pass the number of cache
- * blocks).  Nothing is allocated and nothing synchronises. */
+ * blocks).  Nothing is allocated and nothing synchronises.  With fewer than 2048
+ * vectors to write and head_dim 128 or 256 the vectors are encoded by extra
+ * blocks of the attention's first launch; in that case a call whose attention
+ * arguments are rejected returns the error without having written the cache. */
 typedef struct akv_tq_decode_step_params {
   const void* key; const void* value; int kv_dtype;
   int64_t num_tokens;
