@@ -338,6 +338,7 @@ def test_paged_attention_golden(bits, idx_dtype):
     (4, 4, 4, [100, 48, 1]),                  # the reference tests' layout (no GQA)
     (3, 8, 32, [600, 31]),
     (2, 8, 32, [600, 129]),
+    (4, 1, 3, [50, 7, 300]),                  # 9 (sequence, q head) rows: a ragged last row quad in rotation and merge
 ])
 def test_paged_attention_vs_oracle(bits, H, QH, ctx):
     t = load_golden(f"tq_d128_b{bits}.npz")
