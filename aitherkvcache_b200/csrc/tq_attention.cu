@@ -96,7 +96,8 @@ __device__ void streamk_plan(const StreamKPlanArgs& p) {
   __syncthreads();
   if (tid == 0) {
     int run = 0;
-    for (int i = 0; i < nthr; ++i) { const int v = s_part[i]; s_part[i] = run; run += v; }
+    const int used = per > 0 ? (S + per - 1) / per : 0;     // only these threads own sequences and read their prefix
+    for (int i = 0; i < used; ++i) { const int v = s_part[i]; s_part[i] = run; run += v; }
     s_total = run;
   }
   __syncthreads();
