@@ -292,11 +292,10 @@ hybrid_encode16_kernel(const uint16_t* __restrict__ x, int64_t n_rows, int64_t x
                        HybridTables t, uint8_t* __restrict__ out, int64_t out_row_stride) {
   constexpr int D = G0 + G1;
   static_assert(D == 128, "rows are staged as 16 chunks of 16 bytes");
-  constexpr int GMAX = G0 > G1 ? G0 : G1;
   constexpr int W0 = G0 * B0 / 32 + G0 / 32 + 1, W1 = G1 * B1 / 32 + G1 / 32 + 1;
   extern __shared__ __align__(16) uint8_t he_smem[];
   uint32_t* xs = reinterpret_cast<uint32_t*>(he_smem);                 // [128 rows][64 words]
-  float* us = reinterpret_cast<float*>(he_smem + HE_THREADS * 256);     // [GMAX][128]
+  float* us = reinterpret_cast<float*>(he_smem + HE_THREADS * 256);     // [max(G0, G1)][128]
   __shared__ float s_had[D], s_qjl[D], s_cent[16], s_bnd[16];
   __shared__ int s_idx[D];
   const int tid = threadIdx.x;
