@@ -1852,21 +1852,27 @@ tq4_attn_streamk4_kernel(AttnArgs a) {
       }
     }
   };
-  begin_seq(seq0);
-
-  for (int it = 0; it < n_it; ++it) {
-    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-    __syncthreads();                       // stage `it` has landed; the other slot is free again
-    if (it + 1 < n_it) issue((it + 1) & 1);
-    const int u = u_begin + it;
-    if (u >= c_end) { end_seq(); begin_seq(locate(u, seq_c)); }     // next sequence (rare)
-    const int slot = it & 1;
-    const uint32_t kb = slot ? SK4_K1 : SK4_K0, vb = slot ? SK4_V1 : SK4_V0, nb_ = slot ? SK4_N1 : SK4_N0;
-    const uint32_t va[4] = {vb + v_off[0], vb + v_off[1], vb + v_off[2], vb + v_off[3]};
-    const int rem = ctx_c - 64 * (u - c_base);
-    process_tiles4<4>(lanebase, g, bq, kb + kA_off, va, nb_ + n_off, rem, o, st);
+  // outer loop: the sequences this CTA's range touches; inner loop: their stages, with nothing but
+  // copy, barrier and tile code in it
+  int it = 0;
+  int seq_next = seq0;
+  while (it < n_it) {
+    begin_seq(seq_next);
+    const int it_end = (c_end - u_begin < n_it) ? c_end - u_begin : n_it;   // stages of this sequence in the range
+    for (; it < it_end; ++it) {
+      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+      __syncthreads();                     // stage `it` has landed; the other slot is free again
+      if (it + 1 < n_it) issue((it + 1) & 1);
+      const int u = u_begin + it;
+      const int slot = it & 1;
+      const uint32_t kb = slot ? SK4_K1 : SK4_K0, vb = slot ? SK4_V1 : SK4_V0, nb_ = slot ? SK4_N1 : SK4_N0;
+      const uint32_t va[4] = {vb + v_off[0], vb + v_off[1], vb + v_off[2], vb + v_off[3]};
+      const int rem = ctx_c - 64 * (u - c_base);
+      process_tiles4<4>(lanebase, g, bq, kb + kA_off, va, nb_ + n_off, rem, o, st);
+    }
+    end_seq();
+    if (it < n_it) seq_next = locate(u_begin + it, seq_c);
   }
-  end_seq();
 }
 
 // ---------------------------------------------------------------------------
@@ -2106,14 +2112,17 @@ tq_attn_streamk4_lowbit_kernel(AttnArgs a) {
       }
     }
   };
-  begin_seq(seq0);
-
-  for (int it = 0; it < n_it; ++it) {
+  // outer loop: the sequences of this CTA's range; inner loop: their stages
+  int it = 0;
+  int seq_next = seq0;
+  while (it < n_it) {
+  begin_seq(seq_next);
+  const int it_end = (c_end - u_begin < n_it) ? c_end - u_begin : n_it;
+  for (; it < it_end; ++it) {
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     __syncthreads();
     if (it + 1 < n_it) issue((it + 1) & 1);
     const int u = u_begin + it;
-    if (u >= c_end) { end_seq(); begin_seq(locate(u, seq_c)); }
     const int slot = it & 1;
     const uint32_t kb = slot ? SK4_K1 : SK4_K0, vb = slot ? SK4_V1 : SK4_V0, nb_ = (slot ? SK4_N1 : SK4_N0) + n_off;
     const int rem = ctx_c - 64 * (u - c_base);
@@ -2194,6 +2203,8 @@ tq_attn_streamk4_lowbit_kernel(AttnArgs a) {
     }
   }
   end_seq();
+  if (it < n_it) seq_next = locate(u_begin + it, seq_c);
+  }
 }
 
 static inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
