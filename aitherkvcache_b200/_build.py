@@ -19,8 +19,9 @@ LIB = os.path.join(HERE, "libakv_b200.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
+    "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
 ]
+OBJ_DIR = os.path.join(HERE, "build")
 
 
 def _nvcc() -> str:
@@ -42,15 +43,35 @@ def is_stale() -> bool:
     return any(os.path.getmtime(p) > t for p in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    if not force and not is_stale():
-        return LIB
-    cmd = [_nvcc(), *NVCC_FLAGS, "-o", LIB, *sources()]
+def _compile_one(args):
+    nvcc, src, obj, verbose = args
+    cmd = [nvcc, *NVCC_FLAGS, "-c", "-o", obj, src]
     if verbose:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
+        cmd[1:1] = ["-Xptxas", "-v"]
         print(" ".join(cmd), file=sys.stderr)
     subprocess.run(cmd, check=True, cwd=CSRC)
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile each source to an object (in parallel, only those older than their inputs unless
+    `force`), then link the shared library."""
+    if not force and not is_stale():
+        return LIB
+    from concurrent.futures import ThreadPoolExecutor
+
+    nvcc = _nvcc()
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    headers = glob.glob(os.path.join(CSRC, "*.cuh"))
+    newest_header = max((os.path.getmtime(h) for h in headers), default=0.0)
+    jobs, objs = [], []
+    for src in sources():
+        obj = os.path.join(OBJ_DIR, os.path.splitext(os.path.basename(src))[0] + ".o")
+        objs.append(obj)
+        if force or not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(src), newest_header):
+            jobs.append((nvcc, src, obj, verbose))
+    with ThreadPoolExecutor(max_workers=max(1, min(len(jobs), os.cpu_count() or 1))) as pool:
+        list(pool.map(_compile_one, jobs))
+    subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", LIB, *objs], check=True, cwd=CSRC)
     return LIB
 
 

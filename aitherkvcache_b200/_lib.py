@@ -115,6 +115,8 @@ _SIGNATURES = {
     "akv_version": (c_int, []),
     "akv_last_error": (C.c_char_p, []),
     "akv_device_arch": (c_int, []),
+    "akv_device_status": (c_int, [C.POINTER(c_int), c_int]),
+    "akv_debug_tc_withhold": (c_int, [c_int, c_int]),
     "akv_tq_encode": (c_int, [c_vp, c_int, c_i64, c_i64, c_int, c_int, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp]),
     "akv_tq_decode": (c_int, [c_vp, c_i64, c_vp, c_i64, c_int, c_int, c_vp, c_vp, c_vp, c_int, c_vp]),
     "akv_tq_kv_update": (c_int, [c_vp, c_int, c_i64, c_int, c_int, c_i64, c_i64, c_vp, c_vp, c_i64, c_i64,
@@ -167,6 +169,14 @@ def check(rc: int, what: str) -> None:
         if rc == -1:
             raise ValueError(f"{what}: {msg}")
         raise AkvError(f"{what} failed (code {rc}): {msg}")
+
+
+def device_status(reset: bool = False) -> dict:
+    """Device-side status words of the current device (synchronises): all zero unless a bounded
+    wait gave up or a fixed-address kernel found its shared-memory window taken."""
+    out = (c_int * 4)()
+    check(lib().akv_device_status(out, 1 if reset else 0), "akv_device_status")
+    return {"tc_encode": out[0], "tc_decode": out[1], "attn_window": out[2], "hybrid_window": out[3]}
 
 
 def float_code(t: torch.Tensor) -> int:

@@ -22,3 +22,30 @@ AKV_EXPORT int akv_device_arch(void) {
   cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev);
   return major * 10 + minor;
 }
+
+// Device-side status words of the current device, copied to out[0..3] after everything queued on the
+// device so far has finished (this call synchronises; it is a diagnostic, not part of a serving step):
+//   out[0] tensor-core encoder, out[1] tensor-core decoder: 0 = fine, 1 = a bounded wait on an MMA barrier
+//          gave up and the CTA left its tile unwritten, 2 = it also kept its tensor-memory columns
+//   out[2] packed-cache attention, out[3] hybrid attention: 1 = a fixed-address kernel found its shared
+//          window taken and returned without writing partials
+// reset != 0 clears the words after reading them.
+AKV_EXPORT int akv_device_status(int* out, int reset) {
+  if (!out) return akv::fail(AKV_ERR_ARG, "akv_device_status: null pointer");
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return akv::fail((int)e, "akv_device_status: %s", cudaGetErrorString(e));
+  if (int rc = akv::tc_encode_status(out + 0, reset)) return rc;
+  if (int rc = akv::tc_decode_status(out + 1, reset)) return rc;
+  if (int rc = akv::attn_window_status(out + 2, reset)) return rc;
+  return akv::hybrid_window_status(out + 3, reset);
+}
+
+// Test hook for the bounded waits of the tensor-core codec kernels: CTA 0 of the next launches of the
+// encoder (which = 0) or decoder (which = 1) issues neither the MMAs nor the commit of its tile number
+// `tile`, so the wait on that tile's barrier runs out with no tensor work in flight, the CTA leaves
+// through its give-up path and akv_device_status reports 1.  tile < 0 switches the hook off (the default).
+AKV_EXPORT int akv_debug_tc_withhold(int which, int tile) {
+  if (which == 0) return akv::tc_encode_withhold(tile);
+  if (which == 1) return akv::tc_decode_withhold(tile);
+  return akv::fail(AKV_ERR_ARG, "akv_debug_tc_withhold: which must be 0 (encode) or 1 (decode)");
+}

@@ -58,6 +58,35 @@ inline int sm_count() {
   return n;
 }
 
+// Shared-window address at which `kernel`'s dynamic shared memory will start on the current
+// device: the bytes the system reserves per CTA plus the kernel's static shared memory, rounded
+// up to the 128-byte alignment the kernels declare for their dynamic array.  Kernels that place
+// tables at fixed shared addresses are only launched when this is at or below their first
+// fixed address.  0xffffffff if the attributes cannot be read.
+inline uint32_t dyn_smem_window_start(const void* kernel) {
+  cudaFuncAttributes fa{};
+  int dev = 0, reserved = 0;
+  if (cudaFuncGetAttributes(&fa, kernel) != cudaSuccess || cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&reserved, cudaDevAttrReservedSharedMemoryPerBlock, dev) != cudaSuccess) {
+    cudaGetLastError();
+    return 0xffffffffu;
+  }
+  return (uint32_t)(((size_t)reserved + fa.sharedSizeBytes + 127) / 128 * 128);
+}
+
+// Device-side status words, one per group of kernels (0 = nothing happened):
+//   tc_encode / tc_decode : 1 = a bounded wait on the MMA barrier gave up (rows of the tile were not
+//                           written), 2 = and the CTA could not confirm its MMAs had drained, so it kept
+//                           its tensor-memory columns
+//   attn_window / hybrid_window : 1 = a kernel found its dynamic shared memory starting above its first
+//                           fixed table address and returned without writing partials
+int tc_encode_status(int* host_out, int reset);
+int tc_decode_status(int* host_out, int reset);
+int attn_window_status(int* host_out, int reset);
+int hybrid_window_status(int* host_out, int reset);
+int tc_encode_withhold(int tile);
+int tc_decode_withhold(int tile);
+
 __device__ __forceinline__ float load_as_float(const void* p, int dtype, int64_t i) {
   if (dtype == AKV_F16) return __half2float(reinterpret_cast<const __half*>(p)[i]);
   if (dtype == AKV_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
@@ -73,6 +102,14 @@ __device__ __forceinline__ void store_from_float(void* p, int dtype, int64_t i, 
 __device__ __forceinline__ int64_t load_index(const void* p, int itype, int64_t i) {
   return itype == AKV_I64 ? reinterpret_cast<const int64_t*>(p)[i]
                           : (int64_t)reinterpret_cast<const int32_t*>(p)[i];
+}
+
+// Context length of one sequence, clamped to [0, limit]: `limit` is what the sequence's
+// block-table row can address (max_blocks_per_seq * block_size), so a stale, padded or
+// negative entry can never index past the row.
+__device__ __forceinline__ int64_t load_ctx(const void* p, int itype, int64_t seq, int64_t limit) {
+  const int64_t c = load_index(p, itype, seq);
+  return c < 0 ? 0 : (c > limit ? limit : c);
 }
 
 // Code k (0-based) of an MSB-first packed row with `bits` bits per code

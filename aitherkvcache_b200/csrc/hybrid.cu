@@ -779,12 +779,14 @@ hybrid_decode_kernel(const uint8_t* __restrict__ packed, int64_t p_row_stride, i
 // calls dense SDPA); this is a scalar first version: warp per (seq, kv head, part), lane
 // l owns dims 2l, 2l+1 of each of the four segments.
 // ---------------------------------------------------------------------------
+__device__ int g_hybrid_window_status;   // 1: hybrid_attn_mma_kernel found its shared window taken and returned
+
 struct HybridAttnArgs {
   const uint8_t* k_cache; const uint8_t* v_cache;
   int64_t k_sb, k_sp, k_sh, v_sb, v_sp, v_sh;   // bytes
   const void* block_tables; int bt_dtype; int64_t bt_stride;
   const void* context_lens; int cl_dtype;
-  int num_q_heads, num_kv_heads, block_size;
+  int num_q_heads, num_kv_heads, block_size, max_blocks_per_seq;
   int64_t num_blocks;
   int blocks_per_split, num_parts;
   const float* qprime;     // [S][QH][256], scale*log2e and kappa folded in
@@ -834,7 +836,7 @@ hybrid_attn_kernel(HybridAttnArgs a) {
   const int split = blockIdx.x, h = blockIdx.y, seq = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = a.num_q_heads / a.num_kv_heads;
-  const int64_t ctx = load_index(a.context_lens, a.cl_dtype, seq);
+  const int64_t ctx = load_ctx(a.context_lens, a.cl_dtype, seq, (int64_t)a.max_blocks_per_seq * a.block_size);
   const int bs = a.block_size;
   const int64_t nblk = (ctx + bs - 1) / bs;
   const int64_t blk_begin = (int64_t)split * a.blocks_per_split;
@@ -1025,7 +1027,7 @@ hybrid_attn_mma_kernel(HybridAttnArgs a) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int G = a.num_q_heads / a.num_kv_heads;
-  const int64_t ctx = load_index(a.context_lens, a.cl_dtype, seq);
+  const int64_t ctx = load_ctx(a.context_lens, a.cl_dtype, seq, (int64_t)a.max_blocks_per_seq * a.block_size);
   const int tpb = a.block_size / 16;
   const int64_t tiles_total = (ctx + 15) / 16;
   const int64_t tile_begin = (int64_t)split * a.blocks_per_split * tpb;
@@ -1035,8 +1037,7 @@ hybrid_attn_mma_kernel(HybridAttnArgs a) {
 
   const uint32_t dyn0 = (uint32_t)__cvta_generic_to_shared(hm_smem);
   if (dyn0 > HM_LUT2) {        // the window below the tables is taken (static + system-reserved bytes)
-    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
-      printf("hybrid_attn_mma_kernel: dynamic shared memory starts at %u, above %u\n", dyn0, HM_LUT2);
+    if (threadIdx.x == 0) g_hybrid_window_status = 1;   // the host checks the window before launching
     return;
   }
   unsigned char* const abs0 = hm_smem - dyn0;     // generic pointer to shared-window address 0
@@ -1568,6 +1569,14 @@ static void hybrid_plan(int num_seqs, int num_q_heads, int block_size, int max_b
   *total = *off_ml + al(rows * (size_t)*parts * 2 * sizeof(float));
 }
 
+namespace akv {
+int hybrid_window_status(int* host_out, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(host_out, g_hybrid_window_status, sizeof(int));
+  if (e == cudaSuccess && reset) { const int z = 0; e = cudaMemcpyToSymbol(g_hybrid_window_status, &z, sizeof(int)); }
+  return e == cudaSuccess ? AKV_OK : fail((int)e, "hybrid status: %s", cudaGetErrorString(e));
+}
+}  // namespace akv
+
 AKV_EXPORT size_t akv_hybrid_paged_attn_workspace_bytes(int num_seqs, int num_q_heads, int block_size,
                                                         int max_blocks_per_seq, int blocks_per_split) {
   if (num_seqs <= 0 || num_q_heads <= 0 || block_size <= 0) return 0;
@@ -1614,6 +1623,7 @@ AKV_EXPORT int akv_hybrid_paged_attn(const akv_hybrid_attn_params* p) {
     a.block_tables = p->block_tables; a.bt_dtype = p->bt_dtype; a.bt_stride = p->bt_stride_seq;
     a.context_lens = p->context_lens; a.cl_dtype = p->cl_dtype;
     a.num_q_heads = p->num_q_heads; a.num_kv_heads = p->num_kv_heads; a.block_size = p->block_size;
+    a.max_blocks_per_seq = p->max_blocks_per_seq;
     a.num_blocks = p->num_blocks; a.blocks_per_split = bps; a.num_parts = parts;
     a.qprime = qprime; a.centroids = t.centroids; a.part_acc = part_acc; a.part_ml = part_ml;
     dim3 grid(parts / HA_WARPS, p->num_kv_heads, p->num_seqs);
@@ -1622,7 +1632,9 @@ AKV_EXPORT int akv_hybrid_paged_attn(const akv_hybrid_attn_params* p) {
     const bool aligned16 = ((reinterpret_cast<uintptr_t>(p->k_cache) | reinterpret_cast<uintptr_t>(p->v_cache) |
                              p->k_stride_blk | p->k_stride_pos | p->k_stride_head | p->v_stride_blk |
                              p->v_stride_pos | p->v_stride_head) & 15) == 0;
-    if (!force_scalar && aligned16 && p->block_size % 16 == 0 && p->num_q_heads / p->num_kv_heads <= 8) {
+    // the tensor-core kernel keeps its tables at fixed shared addresses: its dynamic window must start below them
+    static const bool window_ok = dyn_smem_window_start(reinterpret_cast<const void*>(hybrid_attn_mma_kernel)) <= HM_LUT2;
+    if (!force_scalar && window_ok && aligned16 && p->block_size % 16 == 0 && p->num_q_heads / p->num_kv_heads <= 8) {
       cudaError_t e = cudaFuncSetAttribute(hybrid_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, HM_SMEM);
       if (e != cudaSuccess) return fail((int)e, "hybrid attention: smem attribute: %s", cudaGetErrorString(e));
       hybrid_attn_mma_kernel<<<grid, HA_WARPS * 32, HM_SMEM, st>>>(a);

@@ -37,6 +37,8 @@
 
 namespace akv {
 
+__device__ int g_attn_window_status;   // 1: a fixed-address kernel found its shared window taken and returned
+
 struct AttnArgs {
   const uint8_t* k_packed; const uint8_t* v_packed;
   int64_t kp_sb, kp_sp, kp_sh;   // bytes: block, position, head
@@ -73,6 +75,7 @@ __device__ __forceinline__ int64_t phys_block(const AttnArgs& a, int seq, int bl
 // sequences, laid end to end, are cut into `grid` equal ranges, one per persistent CTA.
 struct StreamKPlanArgs {
   const void* context_lens; int cl_dtype; int num_seqs; int block_size; int grid;
+  int64_t max_ctx;   // max_blocks_per_seq * block_size: context lengths are clamped to [0, max_ctx]
   int* sk;    // nullptr: no plan wanted
   int parts_per_cta;   // partials a CTA writes per (sequence, q head): warps per KV head
   int blocks_per_stage;   // 16-token blocks in a stage (2 or 4)
@@ -87,7 +90,7 @@ __device__ void streamk_plan(const StreamKPlanArgs& p) {
   const int s0 = act ? tid * per : S, s1 = (s0 + per < S) ? s0 + per : S;
   int local = 0;
   for (int s = s0; s < s1; ++s) {
-    const int64_t ctx = load_index(p.context_lens, p.cl_dtype, s);
+    const int64_t ctx = load_ctx(p.context_lens, p.cl_dtype, s, p.max_ctx);
     const int nb = (int)((ctx + p.block_size - 1) / p.block_size);
     p.sk[3 * S + 2 + s] = nb;
     local += (nb + p.blocks_per_stage - 1) / p.blocks_per_stage;
@@ -477,7 +480,7 @@ tq_attn_generic_kernel(AttnArgs a) {
   const int D = a.head_dim, bits = a.bits, pd = D * bits / 8;
   const int dpl = D / 32;
   const int G = a.num_q_heads / a.num_kv_heads;
-  const int64_t ctx = load_index(a.context_lens, a.cl_dtype, seq);
+  const int64_t ctx = load_ctx(a.context_lens, a.cl_dtype, seq, (int64_t)a.max_blocks_per_seq * a.block_size);
   const int bs = a.block_size;
   const int64_t nblk = (ctx + bs - 1) / bs;
   const int64_t blk_begin = (int64_t)split * a.blocks_per_split;
@@ -977,7 +980,7 @@ tq_attn_mma_kernel(AttnArgs a) {
   const int split = blockIdx.x, hg = blockIdx.y, seq = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int64_t ctx = load_index(a.context_lens, a.cl_dtype, seq);
+  const int64_t ctx = load_ctx(a.context_lens, a.cl_dtype, seq, (int64_t)a.max_blocks_per_seq * a.block_size);
   const int tpb = a.block_size / 16;
   const int64_t tiles_total = (ctx + 15) / 16;
   const int64_t tile_begin = (int64_t)split * a.blocks_per_split * tpb;
@@ -1138,7 +1141,7 @@ tq4_attn_pipe_kernel(AttnArgs a) {
   const int split = blockIdx.x, hg = blockIdx.y, seq = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int64_t ctx = load_index(a.context_lens, a.cl_dtype, seq);
+  const int64_t ctx = load_ctx(a.context_lens, a.cl_dtype, seq, (int64_t)a.max_blocks_per_seq * a.block_size);
   const int64_t nblk = (ctx + 15) / 16;
   const int64_t blk_begin = (int64_t)split * a.blocks_per_split;
   if (blk_begin >= nblk) return;   // uniform for the CTA
@@ -1474,7 +1477,7 @@ tq4_attn_streamk_kernel(AttnArgs a) {
   auto begin_seq = [&](int seq) {          // query fragments and fresh accumulators
     seq_c = seq;
     c_base = s_P[seq]; c_end = s_P[seq + 1]; c_nb = s_nb[seq];
-    ctx_c = (int)load_index(a.context_lens, a.cl_dtype, seq);
+    ctx_c = (int)load_ctx(a.context_lens, a.cl_dtype, seq, (int64_t)a.max_blocks_per_seq * a.block_size);
     const float* qp = a.qrot + ((int64_t)seq * a.num_q_heads + h * G + (g < G ? g : 0)) * 128 + 32 * t;
     float4 f[8];
 #pragma unroll
@@ -1700,7 +1703,7 @@ tq4_attn_streamk4_kernel(AttnArgs a) {
   const int g = lane >> 2, t = lane & 3;
   const int S = a.num_seqs;
   if (dyn0 > SK4_PLAN) {       // the window below the plan arrays is taken (static + system-reserved bytes)
-    if (tid == 0 && b == 0) printf("tq4_attn_streamk4_kernel: dynamic shared memory starts at %u, above %u\n", dyn0, SK4_PLAN);
+    if (tid == 0) g_attn_window_status = 1;      // the host checks the window before launching; see run_tq_attn
     return;
   }
   for (int i = tid; i < S + 2; i += 256) s_P[i] = a.sk[i];
@@ -1814,7 +1817,7 @@ tq4_attn_streamk4_kernel(AttnArgs a) {
   auto begin_seq = [&](int seq) {
     seq_c = seq;
     c_base = s_P[seq]; c_end = s_P[seq + 1];
-    ctx_c = (int)load_index(a.context_lens, a.cl_dtype, seq);
+    ctx_c = (int)load_ctx(a.context_lens, a.cl_dtype, seq, (int64_t)a.max_blocks_per_seq * a.block_size);
     const float* qp = a.qrot + ((int64_t)seq * a.num_q_heads + h * G + (g < G ? g : 0)) * 128 + 32 * t;
     float4 f[8];
 #pragma unroll
@@ -1954,7 +1957,7 @@ tq_attn_streamk4_lowbit_kernel(AttnArgs a) {
   const int g = lane >> 2, t = lane & 3;
   const int S = a.num_seqs;
   if (dyn0 > SK4_PLAN) {
-    if (tid == 0 && b == 0) printf("tq_attn_streamk4_lowbit_kernel: dynamic shared memory starts at %u, above %u\n", dyn0, SK4_PLAN);
+    if (tid == 0) g_attn_window_status = 1;
     return;
   }
   for (int i = tid; i < S + 2; i += 256) s_P[i] = a.sk[i];
@@ -2074,7 +2077,7 @@ tq_attn_streamk4_lowbit_kernel(AttnArgs a) {
   auto begin_seq = [&](int seq) {
     seq_c = seq;
     c_base = s_P[seq]; c_end = s_P[seq + 1];
-    ctx_c = (int)load_index(a.context_lens, a.cl_dtype, seq);
+    ctx_c = (int)load_ctx(a.context_lens, a.cl_dtype, seq, (int64_t)a.max_blocks_per_seq * a.block_size);
     const float* qp = a.qrot + ((int64_t)seq * a.num_q_heads + h * G + (g < G ? g : 0)) * 128 + 32 * t;
     float4 f[8];
 #pragma unroll
@@ -2205,6 +2208,12 @@ tq_attn_streamk4_lowbit_kernel(AttnArgs a) {
   end_seq();
   if (it < n_it) seq_next = locate(u_begin + it, seq_c);
   }
+}
+
+int attn_window_status(int* host_out, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(host_out, g_attn_window_status, sizeof(int));
+  if (e == cudaSuccess && reset) { const int z = 0; e = cudaMemcpyToSymbol(g_attn_window_status, &z, sizeof(int)); }
+  return e == cudaSuccess ? AKV_OK : fail((int)e, "attention status: %s", cudaGetErrorString(e));
 }
 
 static inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
@@ -2352,13 +2361,20 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
   static const bool sk4 = getenv("AKV_NO_SK4") == nullptr;    // 4-block stages, four tiles per warp at once
   static const bool no_lowbit_ring = getenv("AKV_NO_LOWBIT_RING") != nullptr;
   const bool ring = p->bits == 4 ? pipe : (ring_layout && sk4 && !no_pipe && !no_lowbit_ring);
-  const bool persist = ring && plan.persist_shape && p->kp_stride_blk < lim && p->vp_stride_blk < lim &&
+  // the 4-block-stage kernels address their plan arrays and tables at fixed shared addresses; they are
+  // used only where the dynamic window starts at or below the first of them (else: the per-split kernels)
+  static const bool sk4_window_ok =
+      dyn_smem_window_start(reinterpret_cast<const void*>(tq4_attn_streamk4_kernel)) <= SK4_PLAN &&
+      dyn_smem_window_start(reinterpret_cast<const void*>(tq_attn_streamk4_lowbit_kernel<3>)) <= SK4_PLAN &&
+      dyn_smem_window_start(reinterpret_cast<const void*>(tq_attn_streamk4_lowbit_kernel<2>)) <= SK4_PLAN;
+  const bool persist = ring && (!sk4 || sk4_window_ok) && plan.persist_shape && p->kp_stride_blk < lim && p->vp_stride_blk < lim &&
                        p->kn_stride_blk < lim && p->vn_stride_blk < lim && p->num_blocks < lim;
   int* sk = reinterpret_cast<int*>(ws + plan.off_sk);
 
   StreamKPlanArgs pl{};
   pl.context_lens = p->context_lens; pl.cl_dtype = p->cl_dtype; pl.num_seqs = p->num_seqs;
   pl.block_size = p->block_size; pl.grid = plan.sk_grid; pl.sk = persist ? sk : nullptr;
+  pl.max_ctx = (int64_t)p->max_blocks_per_seq * p->block_size;
   static const int sk_wph = (getenv("AKV_SK_WPH") && atoi(getenv("AKV_SK_WPH")) == 2) ? 2 : 1;
   pl.parts_per_cta = sk4 ? 1 : sk_wph;
   pl.blocks_per_stage = sk4 ? 4 : 2;

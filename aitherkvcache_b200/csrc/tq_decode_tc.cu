@@ -22,7 +22,8 @@
 namespace akv {
 namespace {
 
-__device__ int g_tc_decode_status;   // 1: a wait on the MMA barrier gave up
+__device__ int g_tc_decode_status;          // 1: a wait on the MMA barrier gave up
+__device__ int g_tc_decode_withhold = -1;   // test hook: CTA 0 issues neither the MMAs nor the commit of this tile
 
 constexpr int DT_TERMS_R = 0;                          // R1, R2: 2 operands
 constexpr int DT_ABUF = 2 * TC_OPER_BYTES;             // 2 stages x (c1, c2) operands
@@ -71,7 +72,7 @@ tq_decode_tc_kernel(const uint8_t* __restrict__ packed, int64_t p_stride_row, co
   uint8_t* base = smem_raw + (base_s - raw_s);
   uint8_t* rterms = base + DT_TERMS_R;
   uint64_t* mbar = reinterpret_cast<uint64_t*>(base + DT_MISC);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mbar + 2);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mbar + 3);   // mbar[2]: drain barrier
   const uint32_t abuf_s = base_s + DT_ABUF, lut_s = base_s + DT_LUT, mbar_s = base_s + DT_MISC;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -80,8 +81,10 @@ tq_decode_tc_kernel(const uint8_t* __restrict__ packed, int64_t p_stride_row, co
   if (tid == 0) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(mbar_s));
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(mbar_s + 8));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(mbar_s + 16));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  const int withhold = blockIdx.x == 0 ? g_tc_decode_withhold : -1;
   __syncwarp();
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;"
@@ -177,7 +180,7 @@ tq_decode_tc_kernel(const uint8_t* __restrict__ packed, int64_t p_stride_row, co
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
     // ---- tile t: c1 R1 + c1 R2 + c2 R1, issued by one thread ----
-    if (have && tid == 0) {
+    if (have && tid == 0 && t != withhold) {
       const uint32_t a_s = abuf_s + (uint32_t)(t & 1) * 2 * TC_OPER_BYTES;
       const uint32_t d0 = tmem_base + (uint32_t)(t & 1) * 128;
 #pragma unroll
@@ -240,12 +243,18 @@ tq_decode_tc_kernel(const uint8_t* __restrict__ packed, int64_t p_stride_row, co
     nrm_cur = nrm_next;
   }
 
+  // as in the encoder: drain whatever this thread did issue before the columns are released
+  int leak = 0;
+  if (gave_up && tid == 0) {
+    umma_commit(mbar_s + 16);
+    leak = mbar_wait(mbar_s + 16, 0u) ? 0 : 1;
+    g_tc_decode_status = 1 + leak;
+  }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  if (warp == 0) {
+  leak = __syncthreads_or(leak);
+  if (warp == 0 && !leak) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" :: "r"(tmem_base) : "memory");
   }
-  if (gave_up && tid == 0) g_tc_decode_status = 1;
 }
 
 template <int BITS>
@@ -261,6 +270,17 @@ int launch_dtc(const uint8_t* packed, int64_t ps, const float* norms, int64_t n_
 }
 
 }  // namespace
+
+int tc_decode_status(int* host_out, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(host_out, g_tc_decode_status, sizeof(int));
+  if (e == cudaSuccess && reset) { const int z = 0; e = cudaMemcpyToSymbol(g_tc_decode_status, &z, sizeof(int)); }
+  return e == cudaSuccess ? AKV_OK : fail((int)e, "decode status: %s", cudaGetErrorString(e));
+}
+
+int tc_decode_withhold(int tile) {
+  cudaError_t e = cudaMemcpyToSymbol(g_tc_decode_withhold, &tile, sizeof(int));
+  return e == cudaSuccess ? AKV_OK : fail((int)e, "decode test hook: %s", cudaGetErrorString(e));
+}
 
 int launch_decode_tc(const uint8_t* packed, int64_t packed_row_stride, const float* norms, int64_t n_rows,
                      int bits, const float* rot, const float* centroids, void* out, int out_dtype,

@@ -40,7 +40,8 @@ struct TcRow {
   float* dst_norm;
 };
 
-__device__ int g_tc_status;   // 1: a wait on the MMA barrier gave up
+__device__ int g_tc_status;          // 1: a wait on the MMA barrier gave up
+__device__ int g_tc_withhold = -1;   // test hook: CTA 0 issues neither the MMAs nor the commit of this tile
 
 // Operand buffers of vector tiles in flight: what fits beside the matrix terms.
 template <bool BF16> struct TcBuf { static constexpr int N = BF16 ? 2 : 3; };
@@ -88,8 +89,8 @@ tq_encode_tc_kernel(RowMap m, int64_t n_rows, const float* __restrict__ rot_t,
   float* rinv_s = reinterpret_cast<float*>(dstn_ring + TC_RING * 128);            // [2][128]
   float* nrm_s = rinv_s + 256;                                   // [2][128]
   float* bnd = nrm_s + 256;                                      // [16]
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(bnd + 16);        // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mbar + 2);
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(bnd + 16);        // [2] tile barriers, [1] drain barrier
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mbar + 3);
   int* simple_flag = reinterpret_cast<int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -102,8 +103,10 @@ tq_encode_tc_kernel(RowMap m, int64_t n_rows, const float* __restrict__ rot_t,
     *simple_flag = 1;
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(mbar_s));
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(mbar_s + 8));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(mbar_s + 16));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  const int withhold = blockIdx.x == 0 ? g_tc_withhold : -1;
   if (tid < 16) bnd[tid] = tid < NB ? boundaries[tid] : __int_as_float(0x7f800000);
   __syncwarp();
   if (warp == 0) {
@@ -232,7 +235,7 @@ tq_encode_tc_kernel(RowMap m, int64_t n_rows, const float* __restrict__ rot_t,
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
     // ---- tile t: the whole rotation, issued by one thread ----
-    if (have && tid == 0) {
+    if (have && tid == 0 && t != withhold) {
       const uint32_t a_s = abuf_s + (uint32_t)(t % NBUF) * TC_OPER_BYTES;
       const uint32_t d0 = tmem_base + (uint32_t)(t & 1) * ACC_COLS;
 #pragma unroll
@@ -362,12 +365,21 @@ tq_encode_tc_kernel(RowMap m, int64_t n_rows, const float* __restrict__ rot_t,
     }
   }
 
+  // A CTA that gave up may still have MMAs of a later tile in flight: before its columns go back,
+  // one more commit on the drain barrier (it completes when every MMA this thread issued has) and
+  // one more bounded wait.  Only if that wait gives up too are the columns kept (status 2): they
+  // are lost to this SM until the context ends, which is better than freeing them under an MMA.
+  int leak = 0;
+  if (gave_up && tid == 0) {
+    umma_commit(mbar_s + 16);
+    leak = mbar_wait(mbar_s + 16, 0u) ? 0 : 1;
+    g_tc_status = 1 + leak;
+  }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  if (warp == 0) {
+  leak = __syncthreads_or(leak);
+  if (warp == 0 && !leak) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" :: "r"(tmem_base) : "memory");
   }
-  if (gave_up && tid == 0) g_tc_status = 1;
 }
 
 template <int BITS, bool BF16>
@@ -383,6 +395,17 @@ int launch_tc(const RowMap& m, int64_t n_rows, const float* rot_t, const float* 
 }
 
 }  // namespace
+
+int tc_encode_status(int* host_out, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(host_out, g_tc_status, sizeof(int));
+  if (e == cudaSuccess && reset) { const int z = 0; e = cudaMemcpyToSymbol(g_tc_status, &z, sizeof(int)); }
+  return e == cudaSuccess ? AKV_OK : fail((int)e, "encode status: %s", cudaGetErrorString(e));
+}
+
+int tc_encode_withhold(int tile) {
+  cudaError_t e = cudaMemcpyToSymbol(g_tc_withhold, &tile, sizeof(int));
+  return e == cudaSuccess ? AKV_OK : fail((int)e, "encode test hook: %s", cudaGetErrorString(e));
+}
 
 int launch_encode_tc(const RowMap& m, int64_t n_rows, int bits, bool bf16, const float* rot_t,
                      const float* boundaries, cudaStream_t st) {

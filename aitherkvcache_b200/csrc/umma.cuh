@@ -14,7 +14,8 @@ namespace akv {
 
 constexpr int TC_HALF_BYTES = 128 * 128;          // 128 rows x 64 16-bit elements (one swizzle atom wide)
 constexpr int TC_OPER_BYTES = 2 * TC_HALF_BYTES;  // a 128 x 128 16-bit operand
-constexpr int TC_SPIN_LIMIT = 1 << 17;            // tries of one mbarrier wait before giving up
+constexpr int TC_SPIN_LIMIT = 1 << 17;            // tries of one mbarrier wait before giving up ...
+constexpr long long TC_WAIT_CYCLES = 1ll << 27;   // ... or this many SM cycles (tens of milliseconds), whichever comes first
 
 // Byte offset of element (row, k) inside an operand.
 __device__ __forceinline__ uint32_t tc_operand_offset(int row, int k) {
@@ -57,6 +58,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
 }
 
 __device__ __forceinline__ bool mbar_wait(uint32_t mbar_s, uint32_t parity) {
+  const long long t0 = clock64();
   for (int it = 0; it < TC_SPIN_LIMIT; ++it) {
     uint32_t done;
     asm volatile(
@@ -65,6 +67,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t mbar_s, uint32_t parity) {
         "selp.u32 %0, 1, 0, p;\n\t}\n"
         : "=r"(done) : "r"(mbar_s), "r"(parity) : "memory");
     if (done) return true;
+    if ((it & 15) == 15 && clock64() - t0 > TC_WAIT_CYCLES) break;
   }
   return false;
 }

@@ -132,6 +132,15 @@ class TQPagedAttention:
         num_seqs, num_q_heads, head_dim = query.shape
         assert head_dim == self.head_dim and num_q_heads == self.num_query_heads
         assert k_packed.shape[1] == block_size, "block_size does not match the cache"
+        if block_tables.dim() != 2 or block_tables.shape[0] < num_seqs or context_lens.numel() < num_seqs:
+            raise ValueError(f"block_tables {tuple(block_tables.shape)} / context_lens {tuple(context_lens.shape)} "
+                             f"do not cover {num_seqs} sequences")
+        if (k_packed.shape[-1] < self.packed_dim or v_packed.shape[-1] < self.packed_dim
+                or k_packed.shape[2] != num_kv_heads or tuple(k_norms.shape) != tuple(k_packed.shape[:3])
+                or tuple(v_norms.shape) != tuple(v_packed.shape[:3]) or v_packed.shape[:3] != k_packed.shape[:3]):
+            raise ValueError(f"packed cache {tuple(k_packed.shape)} / {tuple(v_packed.shape)} and norms "
+                             f"{tuple(k_norms.shape)} / {tuple(v_norms.shape)} do not match "
+                             f"[blocks, {block_size}, {num_kv_heads}, >= {self.packed_dim}]")
         if query.dtype not in _lib._FLOAT_CODES:
             query = query.float()
         if query.stride(-1) != 1:

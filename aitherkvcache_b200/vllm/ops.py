@@ -90,8 +90,24 @@ def decode_step(query, key, value, kv_cache, output, k_norms, v_norms, slot_mapp
                                  scale, num_actual)
     tq, pd = _get_tq(head_size)
     dev = query.device
+    # the reference's indexing raises on mismatched sizes; raw pointers would read or write out of bounds
+    if slot_mapping.numel() < key.shape[0] or value.shape[0] != key.shape[0]:
+        raise ValueError(f"decode_step: {key.shape[0]} key tokens, {value.shape[0]} value tokens, "
+                         f"{slot_mapping.numel()} slots")
+    if min(query.shape[0], output.shape[0], block_table.shape[0], seq_lens.numel()) < num_actual:
+        raise ValueError(f"decode_step: num_actual={num_actual} exceeds query/output/block_table/seq_lens rows "
+                         f"({query.shape[0]}, {output.shape[0]}, {block_table.shape[0]}, {seq_lens.numel()})")
+    if kv_cache.dim() != 5 or kv_cache.shape[1] != 2 or kv_cache.shape[3] != num_kv_heads or kv_cache.shape[4] < pd:
+        raise ValueError(f"decode_step: kv_cache {tuple(kv_cache.shape)} does not hold [blocks, 2, block_size, "
+                         f"{num_kv_heads}, >= {pd}]")
+    want_norms = (kv_cache.shape[0], kv_cache.shape[2], num_kv_heads)
+    if (k_norms.dim() != 4 or v_norms.dim() != 4 or not 0 <= layer_idx < k_norms.shape[0]
+            or tuple(k_norms.shape[1:]) != want_norms or tuple(v_norms.shape) != tuple(k_norms.shape)):
+        raise ValueError(f"decode_step: norms {tuple(k_norms.shape)} / {tuple(v_norms.shape)} do not match "
+                         f"[layers > {layer_idx}, {want_norms[0]}, {want_norms[1]}, {want_norms[2]}]")
     state_key = (kv_cache.data_ptr(), tuple(kv_cache.shape), tuple(kv_cache.stride()), k_norms.data_ptr(),
-                 v_norms.data_ptr(), tuple(k_norms.shape), layer_idx, num_heads, num_kv_heads, head_size,
+                 v_norms.data_ptr(), tuple(k_norms.shape), tuple(k_norms.stride()), tuple(v_norms.stride()),
+                 dev.index, tq.bits, layer_idx, num_heads, num_kv_heads, head_size,
                  num_actual, block_table.shape[1], tq.rotation.data_ptr(), tq.rotation_T.data_ptr(),
                  tq.centroids.data_ptr(), tq.boundaries_inner.data_ptr())
     st = _step_state.get(state_key)

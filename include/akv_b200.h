@@ -41,6 +41,25 @@ const char* akv_last_error(void);
 /* major*10+minor of the current device (100 on B200), negative if none */
 int akv_device_arch(void);
 
+/* Device-side status words of the current device (no counterpart in the reference: its Triton
+ * kernels have no bounded waits).  Synchronises the device, then copies four words to the HOST
+ * array out[0..3]; reset != 0 clears them.  0 = nothing happened.
+ *   out[0] tensor-core encoder (akv_tq_encode / akv_tq_kv_update), out[1] tensor-core decoder
+ *          (akv_tq_decode): 1 = a bounded wait on an MMA-completion barrier gave up and that CTA left
+ *          its remaining tiles unwritten; 2 = it also could not confirm that its MMAs had drained and
+ *          kept its tensor-memory columns.
+ *   out[2] akv_tq_paged_attn / akv_tq_decode_step, out[3] akv_hybrid_paged_attn: 1 = a kernel that keeps
+ *          tables at fixed shared-memory addresses found its window taken and returned without writing
+ *          partials (the host checks the window before choosing such a kernel, so this stays 0).
+ * A diagnostic call for health checks and tests, not part of a serving step. */
+int akv_device_status(int* out, int reset);
+
+/* Test hook for those bounded waits: CTA 0 of later encoder (which = 0) or decoder (which = 1)
+ * launches issues neither the MMAs nor the commit of its tile number `tile`, so the wait on that tile
+ * runs out with no tensor work in flight and the CTA leaves through its give-up path.  tile < 0
+ * (the default) switches the hook off. */
+int akv_debug_tc_withhold(int which, int tile);
+
 /* ------------------------------------------------------------------------
  * Uniform TurboQuant codec
  * ---------------------------------------------------------------------- */

@@ -516,3 +516,122 @@ def test_paged_attention_full_size_properties(bits):
                                       ctx.numpy()[pick].astype(np.int64), t["rotation"], t["centroids"], bits,
                                       1.0 / math.sqrt(D))
     assert (np.abs(out[pick] - ref) <= 2e-3 * np.maximum(1.0, np.abs(ref))).all()
+
+
+def _config1_cache(bits, tq, constant_v=None, seed=1):
+    """The headline workload's cache at full size, built with the fused paged write on the GPU:
+    16 sequences of 4096..32768 tokens (seed 1), 8 KV heads, block 16, permuted block tables."""
+    from aitherkvcache_b200 import fused_tq4_kv_update
+    H, D, BS, S = 8, 128, 16, 16
+    gen = torch.Generator().manual_seed(seed)
+    ctx = torch.randint(4096, 32769, (S,), generator=gen)
+    nblk = [(int(c) + BS - 1) // BS for c in ctx]
+    total = sum(nblk)
+    perm = torch.randperm(total, generator=gen)
+    bt = torch.zeros(S, max(nblk), dtype=torch.int32)
+    p = 0
+    for s, n in enumerate(nblk):
+        bt[s, :n] = perm[p:p + n].to(torch.int32)
+        p += n
+    pd = D * bits // 8
+    kp = torch.zeros(total, BS, H, pd, dtype=torch.uint8, device="cuda")
+    vp = torch.zeros_like(kp)
+    kn = torch.zeros(total, BS, H, device="cuda")
+    vn = torch.zeros_like(kn)
+    gg = torch.Generator(device="cuda").manual_seed(2)
+    for s, n in enumerate(nblk):
+        c = int(ctx[s])
+        blocks = bt[s, :n].cuda().long()
+        slots = (blocks[:, None] * BS + torch.arange(BS, device="cuda")[None, :]).reshape(-1)[:c]
+        k = torch.randn(c, H, D, generator=gg, device="cuda").half()
+        v = torch.randn(c, H, D, generator=gg, device="cuda").half()
+        fused_tq4_kv_update(k, slots, kp, kn, tq.rotation, tq.boundaries_inner, BS)
+        fused_tq4_kv_update(v, slots, vp, vn, tq.rotation, tq.boundaries_inner, BS)
+    return ctx, bt, kp, kn, vp, vn
+
+
+@pytest.mark.parametrize("bits", BITS)
+def test_paged_attention_full_size_random_values_vs_oracle(bits):
+    """The headline workload at full size with random K AND random V: the shortest and the longest
+    (about 31 K tokens) sequence are compared element by element with the oracle's
+    decode -> fp16 -> dense attention, the comparison the benchmark configuration names."""
+    t = load_golden(f"tq_d128_b{bits}.npz")
+    tq = _tq(128, bits, t)
+    QH, D = 32, 128
+    ctx, bt, kp, kn, vp, vn = _config1_cache(bits, tq)
+    q = torch.randn(16, QH, D, generator=torch.Generator().manual_seed(5)).half()
+    out = _attn(tq, QH).forward(q.cuda(), kp, kn, vp, vn, bt.cuda(), ctx.to(torch.int32).cuda()).float().cpu().numpy()
+    order = np.argsort(ctx.numpy())
+    pick = np.array([order[0], order[-1]])
+    assert int(ctx[pick[1]]) > 30000
+    kp_h, kn_h, vp_h, vn_h = (x.cpu().numpy() for x in (kp, kn, vp, vn))
+    ref = otq.paged_attention_decode_sdpa(q.numpy()[pick], kp_h, kn_h, vp_h, vn_h, bt.numpy()[pick],
+                                          ctx.numpy()[pick].astype(np.int64), t["rotation"], t["centroids"], bits,
+                                          1.0 / math.sqrt(D))
+    err = np.abs(out[pick] - ref.astype(np.float32)).max()
+    assert err < 2e-3, err
+    rot = otq.paged_attention_rotated(q.numpy()[pick], kp_h, kn_h, vp_h, vn_h, bt.numpy()[pick],
+                                      ctx.numpy()[pick].astype(np.int64), t["rotation"], t["centroids"], bits,
+                                      1.0 / math.sqrt(D))
+    assert np.abs(out[pick] - rot).max() < 2e-3
+
+
+@pytest.mark.parametrize("bits,H", [(4, 8), (3, 8), (2, 8), (4, 4)])
+def test_context_lens_beyond_the_block_table_are_clamped(bits, H):
+    """A context length larger than the block-table row can address (a stale or padded entry), or a
+    negative one, is clamped on the device: the result equals the call with the clamped lengths and no
+    table entry beyond the row is read (the rows beyond it hold out-of-range block numbers, which
+    would otherwise select other blocks' data)."""
+    t = load_golden(f"tq_d128_b{bits}.npz")
+    tq = _tq(128, bits, t)
+    QH = 4 * H
+    ctx = [300, 80, 33]
+    d = make_paged_cache(300 + bits, ctx, H, 128, bits, t["rotation"], t["boundaries"])
+    c = to_cuda(d, ["k_packed", "k_norms", "v_packed", "v_norms", "block_tables", "context_lens"])
+    q = torch.randn(len(ctx), QH, 128, generator=torch.Generator().manual_seed(8)).half().cuda()
+    width = c["block_tables"].shape[1]                 # 19 blocks = 304 tokens
+    # a wider allocation whose extra columns are poison, of which the kernel is shown only the first `width`
+    wide = torch.full((len(ctx), width + 64), 7, dtype=torch.int32, device="cuda")
+    wide[:, :width] = c["block_tables"]
+    bt = wide[:, :width]
+    attn = _attn(tq, QH)
+    bad = torch.tensor([10_000_000, -5, 33], dtype=torch.int64, device="cuda")
+    clamped = torch.tensor([width * 16, 0, 33], dtype=torch.int64, device="cuda")
+    # sequence 0 at the clamped length reads the whole row: fill its unused tail entries with valid blocks
+    bt[0, (300 + 15) // 16:] = c["block_tables"][0, 0]
+    got = attn.forward(q, c["k_packed"], c["k_norms"], c["v_packed"], c["v_norms"], bt, bad)
+    want = attn.forward(q, c["k_packed"], c["k_norms"], c["v_packed"], c["v_norms"], bt, clamped)
+    torch.cuda.synchronize()
+    assert torch.isfinite(got).all()
+    assert torch.equal(got, want)
+    assert (got[1] == 0).all()                          # negative length: an empty context
+
+
+def test_device_status_is_clean_and_reports_a_wait_that_gave_up():
+    """akv_device_status: zero after normal work; with the test hook withholding the MMAs of one tile
+    of CTA 0, the bounded wait on that tile's barrier runs out (nothing is in flight), the CTA leaves
+    through its give-up path and the status word reads 1.  The kernels stay usable afterwards."""
+    from aitherkvcache_b200 import _lib
+    L = _lib.lib()
+    t = load_golden("tq_d128_b4.npz")
+    tq = _tq(128, 4, t)
+    x = torch.randn(148 * 128 * 3, 128, generator=torch.Generator().manual_seed(3)).half().cuda()
+    packed, norms = tq.encode(x)
+    y = tq.decode(packed, norms)
+    assert _lib.device_status(reset=True) == {"tc_encode": 0, "tc_decode": 0, "attn_window": 0, "hybrid_window": 0}
+    try:
+        _lib.check(L.akv_debug_tc_withhold(0, 1), "withhold")
+        p2, n2 = tq.encode(x)
+        st = _lib.device_status(reset=True)
+        assert st["tc_encode"] == 1 and st["tc_decode"] == 0
+        _lib.check(L.akv_debug_tc_withhold(1, 1), "withhold")
+        tq.decode(packed, norms)
+        st = _lib.device_status(reset=True)
+        assert st["tc_decode"] == 1
+    finally:
+        L.akv_debug_tc_withhold(0, -1)
+        L.akv_debug_tc_withhold(1, -1)
+    p3, n3 = tq.encode(x)
+    y3 = tq.decode(packed, norms)
+    assert torch.equal(p3, packed) and torch.equal(n3, norms) and torch.equal(y3, y)
+    assert _lib.device_status() == {"tc_encode": 0, "tc_decode": 0, "attn_window": 0, "hybrid_window": 0}

@@ -4,7 +4,8 @@ A serving engine that has committed all device memory to its KV-cache pool, or a
 must not call into the host program's allocator, cannot provide (or let the library allocate)
 the split-K workspace.  This entry point keeps that scratch in a fixed array inside the
 library.  The test drives it through the C ABI and compares it with akv_tq_paged_attn on the
-same inputs, twice in a row because the array keeps the previous call's contents.
+same inputs and with the oracle, twice in a row because the array keeps the previous call's
+contents.
 
 Collected last on purpose (file name): a run that stops at the first failure has then already
 executed every other test.
@@ -18,6 +19,7 @@ import torch
 
 from conftest import load_golden
 from helpers import make_paged_cache, to_cuda
+from oracle import tq as otq
 
 pytestmark = pytest.mark.gpu
 
@@ -67,6 +69,10 @@ def test_static_scratch_entry_point_matches_workspace_entry_point():
         assert torch.isfinite(got).all()
         # the two entry points may pick different split-K kernels; the tolerance is the suite's fp16 one
         assert (got.float() - ref.float()).abs().max().item() <= 2e-3
+        want = otq.paged_attention_decode_sdpa(q.cpu().numpy(), d["k_packed"], d["k_norms"], d["v_packed"],
+                                               d["v_norms"], d["block_tables"], d["context_lens"], t["rotation"],
+                                               t["centroids"], bits, 1.0 / math.sqrt(128))
+        assert np.abs(got.float().cpu().numpy() - want.astype(np.float32)).max() <= 2e-3
 
 
 def test_static_scratch_rejects_oversized_problems():
