@@ -115,6 +115,8 @@ _SIGNATURES = {
     "akv_version": (c_int, []),
     "akv_last_error": (C.c_char_p, []),
     "akv_device_arch": (c_int, []),
+    "akv_launch_count": (C.c_longlong, []),
+    "akv_last_split_kernel": (C.c_char_p, []),
     "akv_device_status": (c_int, [C.POINTER(c_int), c_int]),
     "akv_debug_tc_withhold": (c_int, [c_int, c_int]),
     "akv_tq_encode": (c_int, [c_vp, c_int, c_i64, c_i64, c_int, c_int, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp]),

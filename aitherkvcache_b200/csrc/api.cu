@@ -6,9 +6,28 @@ char* error_buffer() {
   static thread_local char buf[512] = {0};
   return buf;
 }
+
+static long long g_launches = 0;                 // kernels launched by this process through the library
+static thread_local const char* t_split_kernel = "";   // last split-K attention kernel of this thread
+
+void note_launch(const char* what) {
+  __atomic_add_fetch(&g_launches, 1, __ATOMIC_RELAXED);
+  // the split-K kernels are the ones whose names contain "attn" or "tri_decode"; rotation, merge and
+  // codec launches do not overwrite the record
+  for (const char* c = what; *c; ++c)
+    if ((c[0] == 'a' && c[1] == 't' && c[2] == 't' && c[3] == 'n') ||
+        (c[0] == 't' && c[1] == 'r' && c[2] == 'i' && c[3] == '_' && c[4] == 'd')) { t_split_kernel = what; break; }
+}
 }  // namespace akv
 
-AKV_EXPORT int akv_version(void) { return 100; }
+AKV_EXPORT int akv_version(void) { return 101; }
+
+// Number of kernels the library has launched in this process so far (launches recorded while a stream
+// is being captured count once, at capture time).
+AKV_EXPORT long long akv_launch_count(void) { return __atomic_load_n(&akv::g_launches, __ATOMIC_RELAXED); }
+
+// Name of the split-K attention kernel most recently launched from the calling thread ("" if none).
+AKV_EXPORT const char* akv_last_split_kernel(void) { return akv::t_split_kernel; }
 
 AKV_EXPORT const char* akv_last_error(void) { return akv::error_buffer(); }
 

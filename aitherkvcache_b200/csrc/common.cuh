@@ -35,7 +35,12 @@ inline int fail(int code, const char* fmt, ...) {
   return code;
 }
 
+// Launch bookkeeping (api.cu): every kernel launch of the library passes through check_launch, which
+// counts it and remembers the kernel's name (per host thread).
+void note_launch(const char* what);
+
 inline int check_launch(const char* what) {
+  note_launch(what);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     return fail((int)e, "%s: %s", what, cudaGetErrorString(e));

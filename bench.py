@@ -8,14 +8,22 @@ block_size 16, block tables a random permutation of the physical blocks, K and V
 N(0,1) fp16 encoded to 4-bit codes + float32 norms, one fp16 query token per sequence.
 
 A step is one decode-attention pass over the whole batch.
-  value : KV-tokens/s with everything resident in HBM (CUDA events around the K timed steps)
-  e2e   : the same through the serving op tq::decode_step with HOST inputs - every step copies
-          query, new K/V token, slot mapping, block table and sequence lengths from pinned host
-          memory, encodes the new token into the cache, attends, and copies the output back.
+  value    : KV-tokens/s with everything resident in HBM (CUDA events around the K timed steps); `timing`
+             repeats that region and gives median / min / max
+  e2e      : the same through the serving op tq::decode_step with HOST inputs - every step copies
+             query, new K/V token, slot mapping, block table and sequence lengths from pinned host
+             memory, encodes the new token into the cache, attends, and copies the output back
   roofline : algorithmic packed-KV bytes / duration of the split-K kernel alone (events recorded
-          around that launch inside the library).
-With --gpus N (torchrun) every rank runs its own batch of 16 sequences (batched decode shards by
-sequence, no collective): weak scaling.
+             around that launch inside the library)
+  parity   : measured in the same run, outside the timed regions: attention output against the CPU
+             oracle, packed codes against the oracle's encoder with the fraction of coordinates
+             within 1e-6 of a codebook boundary
+  splitk   : the long-context configurations, one batch sharded by key range over the N ranks:
+             local split-K kernel -> one NCCL all-gather of the (m, l, acc) partials -> LSE merge,
+             replayed as a CUDA graph, with the per-phase times of an eager pass beside it
+  secondary: (N = 1) the other configured kernels on their shapes
+With --gpus N (torchrun) every rank runs its own batch of 16 sequences for the headline value (batched
+decode shards by sequence, no collective: weak scaling); the `splitk` entries are strong scaling.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 """
@@ -42,8 +50,12 @@ UNIT = "KV-tokens/s"
 WORKLOAD = ("paged decode attention, tq-t4nc cache: 16 seqs, ctx U[4096,32768] seed 1, 32Q/8KV heads, "
             "head_dim 128, block_size 16, permuted block tables")
 
-
-NCU_TRAFFIC_BYTES = 281_614_000     # dram read + write per launch (ncu: 3.3731 TB/s x 83.488 us, rank-0 workload)
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the named kernel on the rank-0 headline
+# workload, from the ncu capture summarised under profiles/ (the file is named after the kernel).  A kernel
+# that is not listed here has no capture and its roofline.traffic is null.
+NCU_TRAFFIC_BYTES = {
+    "tq4_attn_streamk4_kernel": 281_600_000,
+}
 
 
 def context_lengths(rank=0):
@@ -58,6 +70,13 @@ def peak_hbm():
             return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
     except Exception:
         return 6650.0, "fallback (6.65 TB/s)"
+
+
+def host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
 
 
 class ClockSampler:
@@ -158,21 +177,26 @@ class ClockSampler:
         return out
 
 
-def build_cache(tq, ctx, device, seed, replicas):
-    """Encode N(0,1) fp16 K/V into `replicas` paged caches with permuted block tables (on the GPU)."""
-    from aitherkvcache_b200 import fused_tq4_kv_update
+def block_tables_for(ctx, seed):
     nblk = [(int(c) + BS - 1) // BS for c in ctx]
     total = sum(nblk)
-    g = torch.Generator().manual_seed(seed)
-    perm = torch.randperm(total, generator=g)
-    bt = torch.zeros(NUM_SEQS, max(nblk), dtype=torch.int32)
+    perm = torch.randperm(total, generator=torch.Generator().manual_seed(seed))
+    bt = torch.zeros(len(ctx), max(nblk), dtype=torch.int32)
     p = 0
     for s, n in enumerate(nblk):
         bt[s, :n] = perm[p:p + n].to(torch.int32)
         p += n
-    caches = []
+    return bt, nblk, total
+
+
+def build_cache(tq, ctx, device, seed, replicas, keep_sample=0):
+    """Encode N(0,1) fp16 K/V into `replicas` paged caches with permuted block tables (on the GPU).
+    keep_sample > 0: also return the first `keep_sample` K vectors of sequence 0 (fp16) and their slots."""
+    from aitherkvcache_b200 import fused_tq4_kv_update
+    bt, nblk, total = block_tables_for(ctx, seed)
+    caches, sample = [], None
     gg = torch.Generator(device=device).manual_seed(seed)
-    for _ in range(replicas):
+    for r in range(replicas):
         kp = torch.zeros(total, BS, H_KV, PD, dtype=torch.uint8, device=device)
         vp = torch.zeros_like(kp)
         kn = torch.zeros(total, BS, H_KV, device=device)
@@ -184,78 +208,110 @@ def build_cache(tq, ctx, device, seed, replicas):
                 x = torch.randn(int(ctx[s]), H_KV, D, generator=gg, device=device, dtype=torch.float32).half()
                 fused_tq4_kv_update(x, slots, packed, norms, tq.rotation, tq.boundaries_inner, BS,
                                     rotation_t=tq.rotation_T)
+                if keep_sample and sample is None:
+                    sample = (x[:keep_sample].cpu(), slots[:keep_sample].cpu())
         caches.append((kp, kn, vp, vn))
-    return caches, bt.to(device), total
+    return caches, bt.to(device), total, sample
 
 
-def cpu_baseline(tq, cache, bt, ctx, q, budget_s=10.0):
-    """Oracle (numpy port of the reference torch path: decode -> fp16 -> dense attention) timed on
-    the host, one sequence after another until the time budget is spent."""
+def parity_report(tq, cache, bt, ctx, q, out, sample):
+    """Parity figures of this very run (outside every timed region): the attention output of the
+    shortest and the longest sequence against the CPU oracle (decode -> fp16 -> dense attention), and
+    a sample of the K vectors the cache was built from against the oracle's encoder."""
     from oracle import tq as otq
-    try:
-        from threadpoolctl import threadpool_info
-        threads = max([p.get("num_threads", 1) for p in threadpool_info()] or [1])
-    except Exception:
-        threads = os.cpu_count() or 1
-    kp, kn, vp, vn = cache
-    R = tq.rotation.cpu().numpy()
-    cent = tq.centroids.cpu().numpy()
-    btc = bt.cpu().numpy()
-    order = np.argsort(ctx.numpy())           # shortest first, so several sequences fit the budget
-    done_tokens, elapsed, used = 0, 0.0, []
-    for s in order:
-        c = int(ctx[s])
-        nb = (c + BS - 1) // BS
-        blocks = torch.from_numpy(btc[s, :nb].astype(np.int64)).to(kp.device)
-        # gather this sequence's blocks on the device and hand the oracle a compact copy
-        sub = [t[blocks].cpu().numpy() for t in (kp, kn, vp, vn)]
-        local_bt = np.arange(nb, dtype=np.int32)[None, :]
-        t0 = time.perf_counter()
-        otq.paged_attention_decode_sdpa(q[s:s + 1].cpu().numpy(), sub[0], sub[1], sub[2], sub[3], local_bt,
-                                        np.asarray([c]), R, cent, BITS, 1.0 / math.sqrt(D), BS)
-        elapsed += time.perf_counter() - t0
-        done_tokens += c
-        used.append(int(s))
-        if elapsed >= budget_s:
-            break
-    return {"value": done_tokens / elapsed, "unit": UNIT, "cores": int(threads), "kind": "port",
-            "sample": f"{len(used)} of {NUM_SEQS} sequences ({done_tokens} KV-tokens, shortest first), "
-                      f"{elapsed:.1f} s of numpy decode->fp16->attention"}, done_tokens, elapsed
+    kp, kn, vp, vn = (t.cpu().numpy() for t in cache)
+    R, cent = tq.rotation.cpu().numpy(), tq.centroids.cpu().numpy()
+    bnd = tq.boundaries_inner.cpu().numpy()
+    order = np.argsort(ctx.numpy())
+    pick = np.array([order[0], order[-1]])
+    ref = otq.paged_attention_decode_sdpa(q.cpu().numpy()[pick], kp, kn, vp, vn, bt.cpu().numpy()[pick],
+                                          ctx.numpy()[pick].astype(np.int64), R, cent, BITS, 1.0 / math.sqrt(D), BS)
+    err = float(np.abs(out.float().cpu().numpy()[pick] - ref.astype(np.float32)).max())
+    x, slots = sample
+    ref_p, ref_n, margin = otq.encode(x.numpy(), R, bnd, BITS, return_margin=True)
+    got_p = cache[0].reshape(-1, H_KV, PD)[slots.to(cache[0].device)].cpu().numpy()
+    got_n = cache[1].reshape(-1, H_KV)[slots.to(cache[1].device)].cpu().numpy()
+    a, b = otq.unpack(got_p, D, BITS), otq.unpack(ref_p, D, BITS)
+    diff = a != b
+    near = margin.reshape(diff.shape) < 1e-6
+    return {"max_abs_err": err, "tolerance": 2e-3,
+            "attention_checked": f"sequences {int(pick[0])} ({int(ctx[pick[0]])} tokens) and {int(pick[1])} "
+                                 f"({int(ctx[pick[1]])} tokens), 32 query heads, vs oracle decode->fp16->attention",
+            "boundary_window_frac": float(near.mean()), "code_mismatch_frac": float(diff.mean()),
+            "code_mismatch_outside_window": int((diff & ~near).sum()),
+            "norms_bit_equal": bool(np.array_equal(got_n.view(np.uint32), ref_n.view(np.uint32))),
+            "codes_checked": int(diff.size)}
+
+
+def cpu_baseline(tq, cache, bt, ctx, q, repeats=2):
+    """The reference's CPU route (torch float32: gather -> TurboQuant.decode -> fp16 -> SDPA, all host
+    threads; restated in oracle/tq_torch.py) timed on all 16 sequences of the workload."""
+    from oracle import tq_torch as ott
+    torch.set_num_threads(host_threads())
+    kp, kn, vp, vn = (t.cpu() for t in cache)
+    R, cent = tq.rotation.cpu(), tq.centroids.cpu()
+    btc, qc = bt.cpu(), q.cpu()
+    ott.paged_decode_attention(qc, kp, kn, vp, vn, btc, ctx, R, cent, block_size=BS, sequences=[0])   # warm-up
+    t0 = time.perf_counter()
+    for _ in range(repeats):
+        ott.paged_decode_attention(qc, kp, kn, vp, vn, btc, ctx, R, cent, block_size=BS)
+    el = (time.perf_counter() - t0) / repeats
+    tokens = int(ctx.sum())
+    return {"value": tokens / el, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"all {NUM_SEQS} sequences ({tokens} KV-tokens) x {repeats} passes, {el:.2f} s per pass of torch "
+                      "float32 gather -> decode -> fp16 -> SDPA (per-sequence gathers included)"}
 
 
 def run_reference(args, rank, world):
-    """--impl reference: the oracle port of the reference's CPU torch path on the host cores."""
+    """--impl reference: the reference's CPU torch route for the same workload, on the host cores.  The
+    reference is Python and does not travel to the GPU box; its route is restated in oracle/tq_torch.py
+    (same torch calls, float32 sgemm, all host threads).  The packed cache is built on the host too, so
+    nothing of the product library is loaded."""
     if rank != 0:
         return
-    # the CPU arm needs the packed cache; build it with the product encoder if a GPU is present,
-    # otherwise with the oracle encoder on a reduced batch.
-    from oracle import tq as otq
+    from oracle import tq_torch as ott
+    threads = host_threads()
+    torch.set_num_threads(threads)
     ctx = context_lengths(0)
-    info = None
-    steps_done, tok, el = 0, 0, 0.0
-    if torch.cuda.is_available():
-        from aitherkvcache_b200 import TurboQuant
-        dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
-        torch.cuda.set_device(dev)
-        tq = TurboQuant(head_dim=D, bits=BITS, device=str(dev))
-        caches, bt, _ = build_cache(tq, ctx, dev, seed=1, replicas=1)
-        q = torch.randn(NUM_SEQS, H_Q, D, generator=torch.Generator().manual_seed(2)).half()
-        budget = max(2.0, min(10.0, 120.0 / max(1, args.steps + args.warmup)))
-        for i in range(args.warmup + args.steps):
-            info, t, e = cpu_baseline(tq, caches[0], bt, ctx, q, budget_s=budget)
-            if i >= args.warmup:
-                tok += t; el += e; steps_done += 1
-    else:
-        raise SystemExit("bench.py --impl reference needs the packed cache built on a GPU")
-    value = tok / el
+    bt, nblk, total = block_tables_for(ctx, 1)
+    # the reference's own tables (seed-42 rotation, 16-level Lloyd-Max codebook), stored with the fixtures
+    with np.load(os.path.join(ROOT, "tests", "golden", "tq_d128_b4.npz")) as z:
+        R, cent, bnd = (torch.from_numpy(z[k].astype(np.float32)) for k in ("rotation", "centroids", "boundaries"))
+    g = torch.Generator().manual_seed(1)
+    kp = torch.zeros(total, BS, H_KV, PD, dtype=torch.uint8)
+    vp = torch.zeros_like(kp)
+    kn = torch.zeros(total, BS, H_KV)
+    vn = torch.zeros_like(kn)
+    for s, n in enumerate(nblk):
+        c = int(ctx[s])
+        slots = (bt[s, :n].long()[:, None] * BS + torch.arange(BS)[None, :]).reshape(-1)[:c]
+        for packed, norms in ((kp, kn), (vp, vn)):
+            p_, n_ = ott.encode4(torch.randn(c, H_KV, D, generator=g).half(), R, bnd)
+            packed.reshape(-1, H_KV, PD)[slots] = p_
+            norms.reshape(-1, H_KV)[slots] = n_
+    q = torch.randn(NUM_SEQS, H_Q, D, generator=torch.Generator().manual_seed(2)).half()
+    tokens = int(ctx.sum())
+    times = []
+    for i in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        ott.paged_decode_attention(q, kp, kn, vp, vn, bt, ctx, R, cent, block_size=BS)
+        if i >= args.warmup:
+            times.append(time.perf_counter() - t0)
+    el = float(np.sum(times))
+    value = tokens * len(times) / el
+    sample = (f"all {NUM_SEQS} sequences ({tokens} KV-tokens) every step; torch float32 gather -> decode -> fp16 -> "
+              f"SDPA on {threads} host threads")
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * el / steps_done,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * el / len(times),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic", "config": {"workload": WORKLOAD, "sample": info["sample"]},
-            "cpu_baseline": dict(info, value=value),
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "kv_tokens_per_gpu": tokens,
+                       "packed_kv_bytes_per_step": tokens * H_KV * 2 * (PD + 4)},
+            "timing": {"ms_per_step_median": 1e3 * float(np.median(times)), "ms_per_step_min": 1e3 * float(np.min(times)),
+                       "ms_per_step_max": 1e3 * float(np.max(times))},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
-
 
 
 def _event_time(fn, steps, warmup):
@@ -271,26 +327,29 @@ def _event_time(fn, steps, warmup):
     return e0.elapsed_time(e1) / steps
 
 
-def run_micro(args):
-    """Secondary kernels on their configured shapes (informative; one JSON object, not the bench line)."""
+def secondary_kernels(steps, warmup, dev):
+    """The other configured kernels on their shapes (configs 0, 2, 3 of the benchmark specification), device-resident,
+    CUDA events, inputs larger than L2: encode / decode / fused paged prefill write at 4, 3, 2 bits on
+    524 288 vectors, decode attention at 3 and 2 bits and with the hybrid tq35 layout on the headline shapes."""
     from aitherkvcache_b200 import TQPagedAttention, TurboQuant, fused_tq4_kv_update
     from aitherkvcache_b200.hybrid_quantizer import HybridPagedAttention, HybridTurboQuant
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(dev)
     peak, _ = peak_hbm()
     res = {}
     g = torch.Generator(device=dev).manual_seed(0)
     x = torch.randn(4 * 1024 * 8 * 16, D, generator=g, device=dev).half()       # 524 288 vectors (prefill-write size)
+    n = x.shape[0]
+
+    def rate(ms, units, bytes_per_unit):
+        gbs = units * bytes_per_unit / ms / 1e6
+        return {"Mvec/s": units / ms / 1e3, "GB/s": gbs, "frac_of_measured_peak": gbs / peak, "ms": ms}
+
     for bits in (4, 3, 2):
         tq = TurboQuant(head_dim=D, bits=bits, device=str(dev))
         packed, norms = tq.encode(x)
-        ms = _event_time(lambda: tq.encode(x), args.steps, args.warmup)
-        n = x.shape[0]
-        res[f"tq{bits}_encode"] = {"Mvec/s": n / ms / 1e3, "GB/s": n * (256 + D * bits // 8 + 4) / ms / 1e6}
-        ms = _event_time(lambda: tq.decode(packed, norms), args.steps, args.warmup)
-        res[f"tq{bits}_decode"] = {"Mvec/s": n / ms / 1e3, "GB/s": n * (256 + D * bits // 8 + 4) / ms / 1e6}
-        # fused prefill write: 16 seqs x 2048 tokens x 8 heads into random paged blocks
-        T = 16 * 2048
+        by = 256 + D * bits // 8 + 4
+        res[f"tq{bits}_encode"] = rate(_event_time(lambda: tq.encode(x), steps, warmup), n, by)
+        res[f"tq{bits}_decode"] = rate(_event_time(lambda: tq.decode(packed, norms), steps, warmup), n, by)
+        T = 16 * 2048            # fused prefill write: 16 seqs x 2048 tokens x 8 heads into random paged blocks
         xk = x[:T * H_KV].reshape(T, H_KV, D)
         nblk = T // BS
         perm = torch.randperm(nblk, generator=torch.Generator().manual_seed(1)).to(dev)
@@ -298,20 +357,11 @@ def run_micro(args):
         outp = torch.zeros(nblk, BS, H_KV, D * bits // 8, dtype=torch.uint8, device=dev)
         outn = torch.zeros(nblk, BS, H_KV, device=dev)
         ms = _event_time(lambda: fused_tq4_kv_update(xk, slots, outp, outn, tq.rotation, tq.boundaries_inner, BS,
-                                                     rotation_t=tq.rotation_T), args.steps, args.warmup)
-        res[f"tq{bits}_paged_write"] = {"Mvec/s": T * H_KV / ms / 1e3,
-                                        "GB/s": T * H_KV * (256 + D * bits // 8 + 4) / ms / 1e6}
-    # decode attention at 3 and 2 bits and hybrid tq35 on the config-1 shapes
+                                                     rotation_t=tq.rotation_T), steps, warmup)
+        res[f"tq{bits}_paged_write"] = rate(ms, T * H_KV, by)
     ctx = context_lengths(0)
     total_ctx = int(ctx.sum())
-    nblk = [(int(c) + BS - 1) // BS for c in ctx]
-    total = sum(nblk)
-    perm = torch.randperm(total, generator=torch.Generator().manual_seed(1))
-    bt = torch.zeros(NUM_SEQS, max(nblk), dtype=torch.int32)
-    p = 0
-    for s_, n_ in enumerate(nblk):
-        bt[s_, :n_] = perm[p:p + n_].to(torch.int32)
-        p += n_
+    bt, nblk, total = block_tables_for(ctx, 1)
     bt = bt.to(dev)
     ctx_dev = ctx.to(torch.int32).to(dev)
     q = torch.randn(NUM_SEQS, H_Q, D, generator=g, device=dev).half()
@@ -323,7 +373,7 @@ def run_micro(args):
         kn = torch.rand(total, BS, H_KV, device=dev) + 10.8
         vn = torch.rand(total, BS, H_KV, device=dev) + 10.8
         attn = TQPagedAttention(tq, H_Q)
-        ms = _event_time(lambda: attn.forward(q, kp, kn, vp, vn, bt, ctx_dev), args.steps, args.warmup)
+        ms = _event_time(lambda: attn.forward(q, kp, kn, vp, vn, bt, ctx_dev), steps, warmup)
         by = total_ctx * H_KV * 2 * (pd + 4)
         res[f"tq{bits}_decode_attn"] = {"KV-tokens/s": total_ctx / ms * 1e3, "GB/s": by / ms / 1e6,
                                         "frac_of_measured_peak": by / ms / 1e6 / peak, "ms": ms}
@@ -331,29 +381,125 @@ def run_micro(args):
     htq.calibrate_uniform()
     xh = torch.randn(8 * 4096 * 8, D, generator=g, device=dev).half()
     ph = htq.encode(xh)
-    ms = _event_time(lambda: htq.encode(xh), args.steps, args.warmup)
-    res["tq35_encode"] = {"Mvec/s": xh.shape[0] / ms / 1e3, "GB/s": xh.shape[0] * 320 / ms / 1e6}
-    ms = _event_time(lambda: htq.decode(ph), args.steps, args.warmup)
-    res["tq35_decode"] = {"Mvec/s": xh.shape[0] / ms / 1e3, "GB/s": xh.shape[0] * 576 / ms / 1e6}
+    nh = xh.shape[0]
+    res["tq35_encode"] = rate(_event_time(lambda: htq.encode(xh), steps, warmup), nh, 320)
+    res["tq35_decode"] = rate(_event_time(lambda: htq.decode(ph), steps, warmup), nh, 576)
     kc = torch.randint(0, 256, (total, BS, H_KV, 64), dtype=torch.uint8, device=dev)
     kc[..., 32:36] = htq.encode(torch.randn(1, D, device=dev))[0, 32:36]       # sane fp16 norm fields
     kc[..., 60:64] = kc[..., 32:36]
     hattn = HybridPagedAttention(htq, H_Q)
-    ms = _event_time(lambda: hattn.forward(q, kc, kc, bt, ctx_dev), max(3, args.steps // 4), 2)
-    res["tq35_decode_attn"] = {"KV-tokens/s": total_ctx / ms * 1e3, "GB/s": total_ctx * H_KV * 128 / ms / 1e6, "ms": ms}
-    print(json.dumps({"workload": "micro", "results": res}))
+    ms = _event_time(lambda: hattn.forward(q, kc, kc, bt, ctx_dev), max(3, steps // 4), 3)
+    by = total_ctx * H_KV * 128
+    res["tq35_decode_attn"] = {"KV-tokens/s": total_ctx / ms * 1e3, "GB/s": by / ms / 1e6,
+                               "frac_of_measured_peak": by / ms / 1e6 / peak, "ms": ms}
+    return res
 
 
-def run_tri128k(args, rank, world, local):
-    """The long-context configuration of the benchmark specification: TriAttention decode_step, batch 8, 128K context, F=12 int4, split-K over
-    the ranks by contiguous key ranges; partials merged after one NCCL all-gather (strong scaling)."""
-    import torch.distributed as dist
-    from aitherkvcache_b200.parallel import all_gather_partials, merge_partials, shard_range
+class SplitK:
+    """One long-context batch whose key range is split over the ranks.  Every step: the local split-K
+    call writes this rank's un-normalised (m, l, acc) partials, one NCCL all-gather moves them, a local
+    kernel merges them by log-sum-exp.  With one rank the library's own call (kernel + in-library merge)
+    is the step.  Replicas of the local shard are cycled so that a step never finds its inputs in L2."""
+
+    def __init__(self, name, world, rank, dev, rows, local_calls, direct_calls, merge, shard_bytes, kv_tokens,
+                 workload):
+        self.name, self.world, self.rank, self.dev = name, world, rank, dev
+        self.local_calls, self.direct_calls, self.merge = local_calls, direct_calls, merge
+        self.shard_bytes, self.kv_tokens, self.workload = shard_bytes, kv_tokens, workload
+        self.raw = torch.empty(rows, D + 2, dtype=torch.float32, device=dev)
+        self.parts = torch.empty(world, rows, D + 2, dtype=torch.float32, device=dev)
+        self.nrep = len(local_calls)
+
+    def step(self, r, ev=None, marks=None):
+        import torch.distributed as dist
+        if self.world == 1:
+            self.direct_calls[r % self.nrep](ev)
+            return
+        self.local_calls[r % self.nrep](self.raw, ev)
+        if marks:
+            marks[0].record()
+        dist.all_gather_into_tensor(self.parts, self.raw)
+        if marks:
+            marks[1].record()
+        self.merge(self.parts)
+
+    def measure(self, steps, warmup, barrier, allreduce_max):
+        from aitherkvcache_b200 import _lib
+        L = _lib.lib()
+        for i in range(warmup):
+            self.step(i)
+        # eager pass: per-phase times (events between the phases) and the split-K kernel alone
+        ev = lambda: torch.cuda.Event(enable_timing=True)      # noqa: E731
+        rec = [(ev(), ev(), ev(), ev(), ev(), ev()) for _ in range(steps)]
+        barrier()
+        for i, (a, k0, k1, m0, m1, b) in enumerate(rec):
+            a.record()
+            self.step(i, (k0, k1), (m0, m1) if self.world > 1 else None)
+            b.record()
+        barrier()
+        kernel_ms = float(np.mean([k0.elapsed_time(k1) for _, k0, k1, _, _, _ in rec]))
+        eager_ms = float(np.mean([a.elapsed_time(b) for a, _, _, _, _, b in rec]))
+        if self.world > 1:
+            local_ms = float(np.mean([a.elapsed_time(m0) for a, _, _, m0, _, _ in rec]))
+            gather_ms = float(np.mean([m0.elapsed_time(m1) for _, _, _, m0, m1, _ in rec]))
+            merge_ms = float(np.mean([m1.elapsed_time(b) for _, _, _, _, m1, b in rec]))
+        else:
+            local_ms, gather_ms, merge_ms = eager_ms, 0.0, 0.0
+        kernel_name = L.akv_last_split_kernel().decode()
+        # the step as a CUDA graph (NCCL's all-gather is captured with it), one graph per replica
+        mode, graphs = "cuda graph replay", []
+        n0 = L.akv_launch_count()
+        try:
+            side = torch.cuda.Stream(device=self.dev)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for r in range(self.nrep):
+                    self.step(r)
+            torch.cuda.current_stream().wait_stream(side)
+            n0 = L.akv_launch_count()
+            for r in range(self.nrep):
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr):
+                    self.step(r)
+                graphs.append(gr)
+        except Exception as exc:      # noqa: BLE001 - keep measuring, but say how
+            graphs, mode = [], f"eager (graph capture failed: {type(exc).__name__}: {exc})"[:200]
+            torch.cuda.synchronize()
+        launches = (L.akv_launch_count() - n0) // max(1, len(graphs)) if graphs else None
+        run = (lambda i: graphs[i % len(graphs)].replay()) if graphs else self.step
+        for i in range(warmup):
+            run(i)
+        regions = []
+        for _ in range(5):
+            barrier()
+            e0, e1 = ev(), ev()
+            e0.record()
+            for i in range(steps):
+                run(i)
+            e1.record()
+            barrier()
+            regions.append(e0.elapsed_time(e1) / steps)
+        t = allreduce_max([kernel_ms, local_ms, gather_ms, merge_ms, eager_ms] + regions)
+        kernel_ms, local_ms, gather_ms, merge_ms, eager_ms = t[:5]
+        regions = t[5:]
+        ms = float(np.median(regions))
+        peak, _ = peak_hbm()
+        achieved = self.shard_bytes / (kernel_ms * 1e-3) / 1e9
+        return {"workload": self.workload, "n_gpus": self.world, "scaling": "strong", "launch": mode,
+                "ms_per_step": ms, "ms_per_step_min": float(min(regions)), "ms_per_step_max": float(max(regions)),
+                "value": self.kv_tokens / (ms * 1e-3), "unit": UNIT, "kv_tokens_per_step": self.kv_tokens,
+                "eager": {"ms_per_step": eager_ms, "local_call_ms": local_ms, "all_gather_ms": gather_ms,
+                          "merge_ms": merge_ms, "note": "max over ranks of per-rank means; CUDA events between the phases"},
+                "kernel": kernel_name, "kernel_ms": kernel_ms, "library_launches_per_step": launches,
+                "replicas_cycled": self.nrep, "shard_bytes_per_rank": self.shard_bytes,
+                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                             "per": "rank (max over ranks of the kernel time)"}}
+
+
+def splitk_tri(world, rank, dev):
+    """TriAttention decode_step, batch 8, 131072 keys, F=12 int4 coefficients (26 B per token, head and side)."""
+    from aitherkvcache_b200.parallel import merge_partials, shard_range
     from aitherkvcache_b200.triattention import SpectralEncoding, TriAttention, TriAttentionConfig
-    dev = torch.device("cuda", local)
-    torch.cuda.set_device(dev)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
     B, S, F = 8, 131072, 12
     cfg = TriAttentionConfig(head_dim=D, num_freqs=F, coeff_bits=4, num_kv_heads=H_KV, num_query_heads=H_Q,
                              rope_base=1_000_000.0)
@@ -372,68 +518,60 @@ def run_tri128k(args, rank, world, local):
                 x = x * pair_scale[None, :, :, None]
             parts.append(tri.encoder.encode(x.reshape(1, hi - lo, H_KV, D).half()))
         encs.append(SpectralEncoding(*[torch.cat([p_[i] for p_ in parts]) for i in range(3)]))
-    k_enc, v_enc = encs
+    shard_bytes = B * (hi - lo) * H_KV * 2 * (2 * F + 2)
+    nrep = max(2, -(-300_000_000 // max(1, shard_bytes)))
+    reps = [encs] + [[SpectralEncoding(*[t.clone() for t in e]) for e in encs] for _ in range(nrep - 1)]
     q = torch.randn(B, H_Q, D, generator=torch.Generator().manual_seed(3)).half().to(dev)
     out = torch.empty(B, H_Q, D, dtype=torch.float32, device=dev)
-    kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    local = [(lambda raw, ev, k=k, v=v: tri._run(q, k, v, None, None, raw_out=raw, key_pos_start=lo,
+                                                 query_pos_default=S, kernel_events=ev)) for k, v in reps]
+    direct = [(lambda ev, k=k, v=v: tri._run(q, k, v, None, None, out=out, kernel_events=ev)) for k, v in reps]
+    return SplitK("tri128k", world, rank, dev, B * H_Q, local, direct,
+                  lambda parts: merge_partials(parts, B, H_Q, D, out=out), shard_bytes, B * S,
+                  "TriAttention decode_step: batch 8, 131072 keys (positions 0..131071, query at 131072), F=12 int4 "
+                  "coefficients, 32Q/8KV heads, head_dim 128, rope_base 1e6, pre-RoPE keys with shuffled exp(-i/16) "
+                  "pair scales; key range split over the ranks"), out
 
-    def step(events=None):
-        if world == 1:
-            tri._run(q, k_enc, v_enc, None, None, out=out, kernel_events=events)
-        else:
-            raw = torch.empty(B * H_Q, D + 2, dtype=torch.float32, device=dev)
-            tri._run(q, k_enc, v_enc, None, None, raw_out=raw, key_pos_start=lo, query_pos_default=S,
-                     kernel_events=events)
-            merge_partials(all_gather_partials(raw), B, H_Q, D, out=out)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(args.warmup):
-        step()
-    sampler = ClockSampler(local)
-    barrier()
-    sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        step(kev[i])
-    e1.record()
-    barrier()
-    clocks = sampler.stop()
-    ms_total = e0.elapsed_time(e1)
-    kernel_ms = float(np.mean([a.elapsed_time(b) for a, b in kev]))
-    tm = torch.tensor([ms_total, kernel_ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
-    ms_total, kernel_ms = float(tm[0]), float(tm[1])
-    if rank == 0:
-        peak, peak_src = peak_hbm()
-        by = B * (hi - lo) * H_KV * 52
-        achieved = by / (kernel_ms * 1e-3) / 1e9
-        line = {"metric": "TriAttention decode_step KV-tokens/s (batch x context / time)",
-                "value": B * S * args.steps / (ms_total * 1e-3), "unit": UNIT, "n_gpus": world,
-                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_total / args.steps,
-                "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-                "dtype": "f32 trig series, f16 mma / f32 accumulate over u8 int4 coefficients",
-                "data": "synthetic",
-                "config": {"workload": "TriAttention decode_step: batch 8, 131072 keys, F=12 int4 (26 B/token/side), "
-                                       "32Q/8KV heads, head_dim 128, rope_base 1e6, keys pre-RoPE with shuffled "
-                                       "exp(-i/16) pair scales",
-                           "l2_policy": f"inputs larger than L2: {by / 1e6:.0f} MB of coefficients per rank per step",
-                           "launch": "eager", "parallelism": f"split-K over {world} ranks, one NCCL all-gather of "
-                                                            f"{B * H_Q * (D + 2) * 4} B per rank + local LSE merge"},
-                "gpu_launches": (2 if world == 1 else 3) * args.steps,
-                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                             "frac": achieved / peak, "traffic": None, "kernel": "tri_decode_kernel",
-                             "kernel_ms": kernel_ms, "peak_source": peak_src,
-                             "frac_of_8TBs_nominal": achieved / 8000.0},
-                "clocks": clocks}
-        print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+def splitk_tq4(world, rank, dev):
+    """tq-t4nc paged decode attention over one long batch: 8 sequences of 131072 tokens, every rank holding a
+    contiguous block range of every sequence in its own paged cache."""
+    from aitherkvcache_b200 import TQPagedAttention, TurboQuant, fused_tq4_kv_update
+    from aitherkvcache_b200.parallel import merge_partials, shard_range
+    B, S = 8, 131072
+    tq = TurboQuant(head_dim=D, bits=BITS, device=str(dev))
+    lo, hi = shard_range(S, rank, world, BS)
+    n_loc = hi - lo
+    nb = n_loc // BS
+    total = B * nb
+    perm = torch.randperm(total, generator=torch.Generator().manual_seed(7 + rank))
+    bt = perm.reshape(B, nb).to(torch.int32).to(dev)
+    kp = torch.zeros(total, BS, H_KV, PD, dtype=torch.uint8, device=dev)
+    vp = torch.zeros_like(kp)
+    kn = torch.zeros(total, BS, H_KV, device=dev)
+    vn = torch.zeros_like(kn)
+    gg = torch.Generator(device=dev).manual_seed(11 + rank)
+    for s in range(B):
+        slots = (bt[s].long()[:, None] * BS + torch.arange(BS, device=dev)[None, :]).reshape(-1)
+        for packed, norms in ((kp, kn), (vp, vn)):
+            x = torch.randn(n_loc, H_KV, D, generator=gg, device=dev).half()
+            fused_tq4_kv_update(x, slots, packed, norms, tq.rotation, tq.boundaries_inner, BS, rotation_t=tq.rotation_T)
+            del x
+    shard_bytes = B * n_loc * H_KV * 2 * (PD + 4)
+    nrep = max(2, -(-300_000_000 // max(1, shard_bytes)))
+    reps = [(kp, kn, vp, vn)] + [tuple(t.clone() for t in (kp, kn, vp, vn)) for _ in range(nrep - 1)]
+    ctx_loc = torch.full((B,), n_loc, dtype=torch.int32, device=dev)
+    q = torch.randn(B, H_Q, D, generator=torch.Generator().manual_seed(5)).half().to(dev)
+    out = torch.empty(B, H_Q, D, dtype=torch.float16, device=dev)
+    attn = TQPagedAttention(tq, H_Q)
+    local = [(lambda raw, ev, c=c: attn.forward(q, c[0], c[1], c[2], c[3], bt, ctx_loc, raw_out=raw, kernel_events=ev))
+             for c in reps]
+    direct = [(lambda ev, c=c: attn.forward(q, c[0], c[1], c[2], c[3], bt, ctx_loc, out=out, kernel_events=ev))
+              for c in reps]
+    return SplitK("tq4_128k", world, rank, dev, B * H_Q, local, direct,
+                  lambda parts: merge_partials(parts, B, H_Q, D, rotation=tq.rotation, out=out), shard_bytes, B * S,
+                  "tq-t4nc paged decode attention: 8 sequences x 131072 tokens, 32Q/8KV heads, head_dim 128, "
+                  "block_size 16, permuted block tables; each sequence's block range split over the ranks"), out
 
 
 def main():
@@ -441,20 +579,21 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None,
                     help="timed steps (default 1000: a timed region of 0.1 s, long enough for the clock sampler; "
-                         "30 for --impl reference, whose steps take seconds)")
-    ap.add_argument("--warmup", type=int, default=None, help="untimed steps first (default 20; 5 for --impl reference)")
+                         "10 for --impl reference, whose steps take seconds)")
+    ap.add_argument("--warmup", type=int, default=None, help="untimed steps first (default 20; 3 for --impl reference)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--replicas", type=int, default=2, help="cache copies cycled through (L2 defeat)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-splitk", action="store_true", help="skip the long-context split-K configurations")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the secondary kernels (N = 1 only)")
+    ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--e2e-eager", action="store_true", help="end-to-end loop without CUDA-graph capture")
-    ap.add_argument("--workload", default="decode_tq4", choices=["decode_tq4", "tri128k", "micro"],
-                    help="decode_tq4 is the headline configuration; the others are secondary measurements")
     args = ap.parse_args()
-    slow = args.impl == "reference" or args.workload != "decode_tq4"
+    slow = args.impl == "reference"
     if args.steps is None:
-        args.steps = 30 if slow else 1000
+        args.steps = 10 if slow else 1000
     if args.warmup is None:
-        args.warmup = 5 if slow else 20
+        args.warmup = 3 if slow else 20
     args.warmup = max(args.warmup, 3)
 
     rank = int(os.environ.get("RANK", 0))
@@ -463,27 +602,33 @@ def main():
     if args.impl == "reference":
         run_reference(args, rank, world)
         return
-    if args.workload == "micro":
-        if rank == 0:
-            run_micro(args)
-        return
-    if args.workload == "tri128k":
-        run_tri128k(args, rank, world, local)
-        return
 
     import torch.distributed as dist
-    from aitherkvcache_b200 import TQPagedAttention, TurboQuant
+    from aitherkvcache_b200 import TQPagedAttention, TurboQuant, _lib
     from aitherkvcache_b200.vllm import ops
 
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    L = _lib.lib()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def allreduce_max(values):
+        t = torch.tensor(values, dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(v) for v in t]
 
     tq = TurboQuant(head_dim=D, bits=BITS, device=str(dev))
     ctx = context_lengths(rank)
     total_ctx = int(ctx.sum())
-    caches, bt, total_blocks = build_cache(tq, ctx, dev, seed=1 + rank, replicas=args.replicas)
+    caches, bt, total_blocks, sample = build_cache(tq, ctx, dev, seed=1 + rank, replicas=args.replicas,
+                                                   keep_sample=4096)
     ctx_dev = ctx.to(torch.int32).to(dev)
     q_host = torch.randn(NUM_SEQS, H_Q, D, generator=torch.Generator().manual_seed(2 + rank)).half()
     q = q_host.to(dev)
@@ -495,11 +640,6 @@ def main():
         kp, kn, vp, vn = caches[i % len(caches)]
         attn.forward(q, kp, kn, vp, vn, bt, ctx_dev, out=out, kernel_events=events)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
     # ---- per-kernel timing: eager launches with events around the split-K kernel -------
     for i in range(args.warmup):
         step(i)
@@ -509,10 +649,17 @@ def main():
         step(i, kev[i])
     barrier()
     kernel_ms = float(np.mean([a.elapsed_time(b) for a, b in kev]))
+    kernel_name = L.akv_last_split_kernel().decode()
+    parity = None
+    if not args.no_parity and rank == 0:
+        step(0)
+        torch.cuda.synchronize()
+        parity = parity_report(tq, caches[0], bt, ctx, q, out, sample)
 
     # ---- device-resident timing: one CUDA graph per cache replica, replayed -------------
     launch_mode = "cuda graph replay"
     graphs = []
+    launches_per_step = 3
     try:
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream())
@@ -520,11 +667,13 @@ def main():
             for r in range(len(caches)):
                 step(r)
         torch.cuda.current_stream().wait_stream(side)
+        n0 = L.akv_launch_count()
         for r in range(len(caches)):
             gr = torch.cuda.CUDAGraph()
             with torch.cuda.graph(gr):
                 step(r)
             graphs.append(gr)
+        launches_per_step = int((L.akv_launch_count() - n0) // len(caches))
     except Exception as exc:          # keep measuring, but say how
         graphs, launch_mode = [], f"eager (graph capture failed: {type(exc).__name__})"
 
@@ -545,8 +694,19 @@ def main():
         timed_step(i)
     e1.record()
     barrier()
-    clocks = sampler.stop()
     ms_total = e0.elapsed_time(e1)
+    # the same region ten more times: the spread of the number above
+    regions = [ms_total / args.steps]
+    for _ in range(10):
+        barrier()
+        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        r0.record()
+        for i in range(args.steps):
+            timed_step(i)
+        r1.record()
+        barrier()
+        regions.append(r0.elapsed_time(r1) / args.steps)
+    clocks = sampler.stop()
 
     # ---- end to end through tq::decode_step with host buffers ---------------------
     ops.register_custom_ops()
@@ -638,16 +798,46 @@ def main():
     e2e_ms = f0.elapsed_time(f1)
     if not torch.equal(out_host, eager_out):
         raise RuntimeError("end-to-end replay returned a different result than the eager call")
+    e2e_oracle_err = None
+    if parity is not None:
+        # the op's output (new token written over the last position) against the oracle on the shortest sequence
+        from oracle import tq as otq
+        s0 = int(np.argmin(ctx.numpy()))
+        kc_, vc_ = kv_cache[:, 0].cpu().numpy(), kv_cache[:, 1].cpu().numpy()
+        ref = otq.paged_attention_decode_sdpa(q_host.numpy()[s0:s0 + 1], kc_, k_norms[0].cpu().numpy(), vc_,
+                                              v_norms[0].cpu().numpy(), bt.cpu().numpy()[s0:s0 + 1],
+                                              ctx.numpy()[s0:s0 + 1].astype(np.int64), tq.rotation.cpu().numpy(),
+                                              tq.centroids.cpu().numpy(), BITS, 1.0 / math.sqrt(D), BS)
+        e2e_oracle_err = float(np.abs(out_host[s0].float().numpy() - ref[0].astype(np.float32)).max())
+        parity["e2e_max_abs_err"] = e2e_oracle_err
+    status = _lib.device_status()
 
-    times = torch.tensor([ms_total, e2e_ms, float(total_ctx)], dtype=torch.float64, device=dev)
+    # free the headline's buffers before the long-context configurations
+    del graphs, e2e_graph, kv_cache, k_norms, v_norms
+    cache0 = caches[0]
+    caches = [cache0]
+    torch.cuda.empty_cache()
+
+    splitk = {}
+    if not args.no_splitk:
+        for make in (splitk_tri, splitk_tq4):
+            job, job_out = make(world, rank, dev)
+            res = job.measure(min(args.steps, 200), min(args.warmup, 10), barrier, allreduce_max)
+            res["output_finite"] = bool(torch.isfinite(job_out.float()).all())
+            splitk[job.name] = res
+            del job, job_out
+            torch.cuda.empty_cache()
+
+    secondary = None
+    if world == 1 and not args.no_secondary:
+        secondary = secondary_kernels(min(args.steps, 50), 3, dev)
+
+    t = allreduce_max([ms_total, e2e_ms] + regions)
+    ms_total, e2e_ms, regions = t[0], t[1], t[2:]
+    job = torch.tensor([float(total_ctx)], dtype=torch.float64, device=dev)
     if world > 1:
-        mx = times.clone()
-        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-        sm = times.clone()
-        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
-        ms_total, e2e_ms, job_ctx = float(mx[0]), float(mx[1]), float(sm[2])
-    else:
-        job_ctx = float(total_ctx)
+        dist.all_reduce(job, op=dist.ReduceOp.SUM)
+    job_ctx = float(job[0])
 
     if rank == 0:
         peak, peak_src = peak_hbm()
@@ -662,25 +852,36 @@ def main():
                                     "cycled between steps",
                        "launch": launch_mode,
                        "parallelism": f"dp{world} (sequences sharded, no collective)"},
+            "timing": {"regions": len(regions), "steps_per_region": args.steps,
+                       "ms_per_step_median": float(np.median(regions)), "ms_per_step_min": float(min(regions)),
+                       "ms_per_step_max": float(max(regions)),
+                       "note": "the first region is the one `value` is computed from; max over ranks per region"},
             "e2e": {"value": job_ctx * args.steps / (e2e_ms * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps,
                     "launch": e2e_mode,
                     "api": "torch.ops.tq.decode_step (encode new token + attention), host pinned buffers"},
-            "gpu_launches": 3 * args.steps,
-            # traffic: dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this
-            # workload, from the ncu capture summarised in profiles/tq4_attn_streamk_kernel_config1.md
+            "gpu_launches": launches_per_step * args.steps,
+            "gpu_launches_per_step": launches_per_step,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES if world == 1 else None,
-                         "algorithmic_bytes": kv_bytes, "kernel": "tq4_attn_streamk4_kernel",
+                         "frac": achieved / peak,
+                         "traffic": NCU_TRAFFIC_BYTES.get(kernel_name) if world == 1 else None,
+                         "algorithmic_bytes": kv_bytes, "kernel": kernel_name,
                          "kernel_ms": kernel_ms, "peak_source": peak_src,
                          "frac_of_8TBs_nominal": achieved / 8000.0},
             "clocks": clocks,
+            "device_status": status,
         }
+        if parity is not None:
+            line["parity"] = parity
+        if splitk:
+            line["splitk"] = splitk
+        if secondary is not None:
+            line["secondary"] = secondary
         if not args.no_cpu_baseline and world == 1:
-            info, _, _ = cpu_baseline(tq, caches[0], bt, ctx, q)
-            line["cpu_baseline"] = info
+            line["cpu_baseline"] = cpu_baseline(tq, cache0, bt, ctx, q)
         print(json.dumps(line))
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 

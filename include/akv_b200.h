@@ -41,6 +41,12 @@ const char* akv_last_error(void);
 /* major*10+minor of the current device (100 on B200), negative if none */
 int akv_device_arch(void);
 
+/* Bookkeeping for benchmarks and tests (no counterpart in the reference): the number of kernels the
+ * library has launched in this process (a launch recorded during stream capture counts once), and the
+ * name of the split-K attention kernel the calling thread launched last ("" if none). */
+long long akv_launch_count(void);
+const char* akv_last_split_kernel(void);
+
 /* Device-side status words of the current device (no counterpart in the reference: its Triton
  * kernels have no bounded waits).  Synchronises the device, then copies four words to the HOST
  * array out[0..3]; reset != 0 clears them.  0 = nothing happened.

@@ -164,3 +164,33 @@ def test_tri_decode_step_matches():
     assert np.abs(sc - g["scores_far"]).max() < 1e-4
     out = otri.decode_step(g["query"], k_enc, v_enc, g["theta"], g["query_pos"], g["key_positions"])
     assert np.abs(out - g["out_far"]).max() < 1e-4
+
+
+def test_torch_cpu_baseline_matches_the_oracle():
+    """oracle/tq_torch.py (the timed CPU baseline: float32 torch ops like the reference) against the
+    float64 numpy oracle: codes equal outside the boundary window, decode within one fp16 ulp, attention
+    within the benchmark tolerance."""
+    import math
+    import torch
+    from helpers import make_paged_cache
+    from oracle import tq_torch as ott
+    t = load_golden("tq_d128_b4.npz")
+    R, cent, bnd = t["rotation"], t["centroids"], t["boundaries"]
+    T = lambda a: torch.from_numpy(np.ascontiguousarray(a))     # noqa: E731
+    x = torch.randn(300, 8, 128, generator=torch.Generator().manual_seed(0)).half()
+    p_np, n_np, margin = otq.encode(x.numpy(), R, bnd, 4, return_margin=True)
+    p_t, n_t = ott.encode4(x, T(R), T(bnd))
+    diff = otq.unpack(p_t.numpy(), 128, 4) != otq.unpack(p_np, 128, 4)
+    assert not (diff & ~(margin.reshape(diff.shape) < 1e-6)).any()
+    assert np.abs(n_t.numpy() - n_np).max() <= 1e-6 * np.abs(n_np).max()
+    d_np = otq.decode(p_np, n_np, R, cent, 4).astype(np.float32)
+    d_t = ott.decode4(T(p_np), T(n_np), T(R), T(cent)).float().numpy()
+    assert (np.abs(d_t - d_np) <= np.maximum(np.abs(d_np) * 2.0 ** -10, 1e-5)).all()
+    ctx = [700, 33, 0, 90]
+    d = make_paged_cache(3, ctx, 8, 128, 4, R, bnd)
+    q = torch.randn(len(ctx), 32, 128, generator=torch.Generator().manual_seed(1)).half()
+    ref = otq.paged_attention_decode_sdpa(q.numpy(), d["k_packed"], d["k_norms"], d["v_packed"], d["v_norms"],
+                                          d["block_tables"], d["context_lens"], R, cent, 4, 1 / math.sqrt(128))
+    out = ott.paged_decode_attention(q, T(d["k_packed"]), T(d["k_norms"]), T(d["v_packed"]), T(d["v_norms"]),
+                                     T(d["block_tables"]), T(d["context_lens"]), T(R), T(cent))
+    assert np.abs(out.float().numpy() - ref.astype(np.float32)).max() < 2e-3
