@@ -90,6 +90,18 @@ class HybridAttnParams(C.Structure):
     ]
 
 
+class HybridDecodeStepParams(C.Structure):
+    """Mirror of ``akv_hybrid_decode_step_params``."""
+    _fields_ = [
+        ("key", c_vp), ("value", c_vp), ("kv_dtype", c_int),
+        ("num_tokens", c_i64),
+        ("k_stride_tok", c_i64), ("k_stride_head", c_i64), ("v_stride_tok", c_i64), ("v_stride_head", c_i64),
+        ("slot_mapping", c_vp),
+        ("max_blocks", c_i64),
+        ("attn", HybridAttnParams),
+    ]
+
+
 class TriDecodeParams(C.Structure):
     """Mirror of ``akv_tri_decode_params``."""
     _fields_ = [
@@ -128,10 +140,20 @@ _SIGNATURES = {
     "akv_tq_decode_step": (c_int, [C.POINTER(TQDecodeStepParams)]),
     "akv_tq_paged_attn_static_scratch_bytes": (C.c_size_t, []),
     "akv_tq_paged_attn_static": (c_int, [C.POINTER(TQAttnParams)]),
+    "akv_block_select_update": (c_int, [c_vp, c_i64, c_vp, c_i64, c_i64, c_vp, c_i64, c_i64, c_vp, c_int, c_int, c_int,
+                                        c_i64, c_vp, c_vp, c_vp, c_vp]),
+    "akv_block_select_clear": (c_int, [c_vp, c_i64, c_int, c_i64, c_vp, c_vp, c_vp, c_vp]),
+    "akv_block_select_workspace_bytes": (C.c_size_t, [c_int] * 3),
+    "akv_block_select": (c_int, [c_vp, c_int, c_i64, c_i64, c_int, c_int, c_int, c_int, c_vp, c_vp, c_i64, c_vp, c_int,
+                                 c_i64, c_vp, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp,
+                                 C.c_size_t, c_vp]),
     "akv_hybrid_encode": (c_int, [c_vp, c_int, c_i64, c_i64, C.POINTER(HybridTables), c_vp, c_i64, c_vp]),
     "akv_hybrid_decode": (c_int, [c_vp, c_i64, c_i64, C.POINTER(HybridTables), c_vp, c_int, c_vp]),
     "akv_hybrid_paged_attn_workspace_bytes": (C.c_size_t, [c_int] * 5),
     "akv_hybrid_paged_attn": (c_int, [C.POINTER(HybridAttnParams)]),
+    "akv_hybrid_kv_update": (c_int, [c_vp, c_int, c_i64, c_int, c_i64, c_i64, c_vp, C.POINTER(HybridTables), c_vp,
+                                     c_i64, c_i64, c_i64, c_int, c_i64, c_vp]),
+    "akv_hybrid_decode_step": (c_int, [C.POINTER(HybridDecodeStepParams)]),
     "akv_tri_encode": (c_int, [c_vp, c_int, c_i64, c_i64, c_int, c_int, c_vp, c_vp, c_vp, c_vp]),
     "akv_tri_decode_workspace_bytes": (C.c_size_t, [c_int] * 4),
     "akv_tri_decode_step": (c_int, [C.POINTER(TriDecodeParams)]),

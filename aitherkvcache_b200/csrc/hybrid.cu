@@ -27,6 +27,44 @@ struct HybridTables {
   float qjl_scale0, qjl_scale1;
 };
 
+// Where row n of an encode call comes from and where its record goes.  Contiguous mode
+// (slot_mapping == nullptr): rows x_stride_row elements apart, records out_stride_row bytes apart.
+// Paged mode: row n is (token n / num_heads, head n % num_heads); the record goes to the cache slot
+// slot_mapping[token] (block = slot / block_size, position = slot % block_size); tokens with a
+// negative slot or a block >= max_blocks are skipped (vllm/hooks.py:259-296 in the reference
+// writes them by index-put; a negative slot there wraps to the last block).
+struct HyRowMap {
+  int64_t x_stride_row, out_stride_row;
+  const int64_t* slot_mapping;
+  int num_heads, block_size;
+  int64_t max_blocks;
+  int64_t x_stride_tok, x_stride_head;
+  int64_t p_stride_blk, p_stride_pos, p_stride_head;
+};
+
+__device__ __forceinline__ int64_t hy_src_off(const HyRowMap& m, int64_t n) {
+  if (m.slot_mapping == nullptr) return n * m.x_stride_row;
+  const int64_t tok = n / m.num_heads;
+  return tok * m.x_stride_tok + (n - tok * m.num_heads) * m.x_stride_head;
+}
+
+__device__ __forceinline__ uint8_t* hy_dst(const HyRowMap& m, uint8_t* out, int64_t n) {
+  if (m.slot_mapping == nullptr) return out + n * m.out_stride_row;
+  const int64_t tok = n / m.num_heads;
+  const int64_t slot = m.slot_mapping[tok];
+  if (slot < 0) return nullptr;
+  const int64_t blk = slot / m.block_size;
+  if (blk >= m.max_blocks) return nullptr;
+  return out + blk * m.p_stride_blk + (slot - blk * m.block_size) * m.p_stride_pos + (n - tok * m.num_heads) * m.p_stride_head;
+}
+
+static inline HyRowMap hy_contiguous(int64_t x_row_stride, int64_t out_row_stride) {
+  HyRowMap m{};
+  m.x_stride_row = x_row_stride; m.out_stride_row = out_row_stride;
+  return m;
+}
+
+
 // Butterfly stages h = 1, 2, 4, ... as a compile-time recursion, so that every index is a
 // constant and the array stays in registers.
 template <int N, int H>
@@ -147,8 +185,8 @@ constexpr int HY_LD = 129;       // row pitch of the float staging tile: bank = 
 
 template <int G0, int B0, int G1, int B1>
 __global__ void __launch_bounds__(HY_THREADS)
-hybrid_encode_kernel(const void* __restrict__ x, int x_dtype, int64_t n_rows, int64_t x_row_stride,
-                     HybridTables t, uint8_t* __restrict__ out, int64_t out_row_stride) {
+hybrid_encode_kernel(const void* __restrict__ x, int x_dtype, int64_t n_rows, HyRowMap map,
+                     HybridTables t, uint8_t* __restrict__ out) {
   constexpr int D = G0 + G1;
   constexpr int BYTES0 = (G0 * B0 + 7) / 8 + (G0 + 7) / 8 + 4;
   constexpr int BYTES1 = (G1 * B1 + 7) / 8 + (G1 + 7) / 8 + 4;
@@ -163,7 +201,7 @@ hybrid_encode_kernel(const void* __restrict__ x, int x_dtype, int64_t n_rows, in
   for (int e = tid; e < HY_THREADS * D; e += HY_THREADS) {
     const int r = e / D, c = e % D;
     const int64_t n = row0 + r;
-    xs[r * HY_LD + c] = (n < n_rows) ? load_as_float(x, x_dtype, n * x_row_stride + c) : 0.f;
+    xs[r * HY_LD + c] = (n < n_rows) ? load_as_float(x, x_dtype, hy_src_off(map, n) + c) : 0.f;
   }
   const int64_t n = row0 + tid;
   const int head = (t.num_index_heads > 1) ? (int)(n % t.num_index_heads) : 0;
@@ -177,11 +215,12 @@ hybrid_encode_kernel(const void* __restrict__ x, int x_dtype, int64_t n_rows, in
     gidx = s_idx;
   }
   if (n >= n_rows) return;
+  uint8_t* dst = hy_dst(map, out, n);
+  if (dst == nullptr) return;
   uint8_t rec[BYTES0 + BYTES1];
   encode_group<G0, B0>(xs + tid * HY_LD, gidx, s_had, s_qjl, s_cent, s_bnd, rec);
   encode_group<G1, B1>(xs + tid * HY_LD, gidx + G0, s_had + G0, s_qjl + G0, s_cent + 8, s_bnd + 8,
                        rec + BYTES0);
-  uint8_t* dst = out + n * out_row_stride;
   static_assert((BYTES0 + BYTES1) % 4 == 0, "record size must be a multiple of 4");
   if ((reinterpret_cast<uintptr_t>(dst) & 3) == 0) {
 #pragma unroll
@@ -288,8 +327,8 @@ template <int G0, int B0, int G1, int B1, bool BF16>
 #define AKV_HE_MINB 2
 #endif
 __global__ void __launch_bounds__(HE_THREADS, AKV_HE_MINB)
-hybrid_encode16_kernel(const uint16_t* __restrict__ x, int64_t n_rows, int64_t x_row_stride,
-                       HybridTables t, uint8_t* __restrict__ out, int64_t out_row_stride) {
+hybrid_encode16_kernel(const uint16_t* __restrict__ x, int64_t n_rows, HyRowMap map,
+                       HybridTables t, uint8_t* __restrict__ out) {
   constexpr int D = G0 + G1;
   static_assert(D == 128, "rows are staged as 16 chunks of 16 bytes");
   constexpr int W0 = G0 * B0 / 32 + G0 / 32 + 1, W1 = G1 * B1 / 32 + G1 / 32 + 1;
@@ -302,7 +341,8 @@ hybrid_encode16_kernel(const uint16_t* __restrict__ x, int64_t n_rows, int64_t x
   if (tid < D) { s_had[tid] = t.had_signs[tid]; s_qjl[tid] = t.qjl_signs[tid]; s_idx[tid] = t.group_index[tid]; }
   if (tid < 16) { s_cent[tid] = t.centroids[tid]; s_bnd[tid] = t.boundaries[tid]; }
   const int64_t row0 = (int64_t)blockIdx.x * HE_THREADS;
-  const bool vec = (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (x_row_stride & 7) == 0;
+  const bool vec = (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                   ((map.x_stride_row | map.x_stride_tok | map.x_stride_head) & 7) == 0;
 #pragma unroll
   for (int i0 = 0; i0 < 16; i0 += 8) {
     uint4 v[8];
@@ -312,7 +352,7 @@ hybrid_encode16_kernel(const uint16_t* __restrict__ x, int64_t n_rows, int64_t x
       const int64_t n = row0 + r;
       v[i] = make_uint4(0u, 0u, 0u, 0u);
       if (n < n_rows) {
-        const uint16_t* src = x + n * x_row_stride + c * 8;
+        const uint16_t* src = x + hy_src_off(map, n) + c * 8;
         if (vec) {
           v[i] = *reinterpret_cast<const uint4*>(src);
         } else {
@@ -342,7 +382,8 @@ hybrid_encode16_kernel(const uint16_t* __restrict__ x, int64_t n_rows, int64_t x
   encode_group16<G0, B0, BF16>(xrow, tid & 31, gidx, s_had, s_qjl, s_cent, s_bnd, us + tid, rec);
   encode_group16<G1, B1, BF16>(xrow, tid & 31, gidx + G0, s_had + G0, s_qjl + G0, s_cent + 8, s_bnd + 8,
                                us + tid, rec + W0);
-  uint8_t* dst = out + n * out_row_stride;
+  uint8_t* dst = hy_dst(map, out, n);
+  if (dst == nullptr) return;
   if ((reinterpret_cast<uintptr_t>(dst) & 3) == 0) {
 #pragma unroll
     for (int wd = 0; wd < W0 + W1; ++wd) reinterpret_cast<uint32_t*>(dst)[wd] = rec[wd];
@@ -353,8 +394,8 @@ hybrid_encode16_kernel(const uint16_t* __restrict__ x, int64_t n_rows, int64_t x
 }
 
 template <int G0, int B0, int G1, int B1>
-static int launch_hybrid_encode16(const void* x, int x_dtype, int64_t n_rows, int64_t x_row_stride,
-                                  const HybridTables& t, uint8_t* out, int64_t out_row_stride, cudaStream_t st) {
+static int launch_hybrid_encode16(const void* x, int x_dtype, int64_t n_rows, const HyRowMap& map,
+                                  const HybridTables& t, uint8_t* out, cudaStream_t st) {
   constexpr int GMAX = G0 > G1 ? G0 : G1;
   constexpr size_t SMEM = (size_t)HE_THREADS * 256 + (size_t)GMAX * HE_THREADS * 4;
   const int grid = (int)((n_rows + HE_THREADS - 1) / HE_THREADS);
@@ -363,11 +404,11 @@ static int launch_hybrid_encode16(const void* x, int x_dtype, int64_t n_rows, in
   if (x_dtype == AKV_BF16) {
     auto kern = hybrid_encode16_kernel<G0, B0, G1, B1, true>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
-    if (e == cudaSuccess) kern<<<grid, HE_THREADS, SMEM, st>>>(xp, n_rows, x_row_stride, t, out, out_row_stride);
+    if (e == cudaSuccess) kern<<<grid, HE_THREADS, SMEM, st>>>(xp, n_rows, map, t, out);
   } else {
     auto kern = hybrid_encode16_kernel<G0, B0, G1, B1, false>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
-    if (e == cudaSuccess) kern<<<grid, HE_THREADS, SMEM, st>>>(xp, n_rows, x_row_stride, t, out, out_row_stride);
+    if (e == cudaSuccess) kern<<<grid, HE_THREADS, SMEM, st>>>(xp, n_rows, map, t, out);
   }
   if (e != cudaSuccess) return fail((int)e, "hybrid encode: smem attribute: %s", cudaGetErrorString(e));
   return check_launch("hybrid_encode16_kernel");
@@ -551,24 +592,22 @@ __device__ __forceinline__ void hc_encode_group(const uint32_t* xrow, const int*
   }
 }
 
+// Body of the tq35 four-lanes-per-vector encoder for the 32 rows starting at row0 (a CTA of HC_THREADS).
 template <bool BF16>
-__global__ void __launch_bounds__(HC_THREADS, 4)
-hybrid_encode35_coop_kernel(const uint16_t* __restrict__ x, int64_t n_rows, int64_t x_row_stride,
-                            HybridTables t, uint8_t* __restrict__ out, int64_t out_row_stride) {
-  __shared__ __align__(16) uint32_t xs[32 * HC_ROW_WORDS];
-  __shared__ float s_had[128], s_qjl[128], s_cent[16], s_bnd[16];
-  __shared__ int s_idx[128];
+__device__ __forceinline__ void hc_encode35_rows(const uint16_t* __restrict__ x, int64_t n_rows, int64_t row0,
+                                                 const HyRowMap& map, const HybridTables& t,
+                                                 uint8_t* __restrict__ out, uint32_t* xs, float* s_had, float* s_qjl,
+                                                 float* s_cent, float* s_bnd, int* s_idx) {
   const int tid = threadIdx.x, lane = tid & 31;
   if (tid < 128) { s_had[tid] = t.had_signs[tid]; s_qjl[tid] = t.qjl_signs[tid]; s_idx[tid] = t.group_index[tid]; }
   if (tid < 16) { s_cent[tid] = t.centroids[tid]; s_bnd[tid] = t.boundaries[tid]; }
-  const int64_t row0 = (int64_t)blockIdx.x * 32;
   // stage 32 rows: 512 pieces of 16 bytes, 4 per thread, coalesced
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int e = i * HC_THREADS + tid, r = e >> 4, c = e & 15;
     const int64_t n = row0 + r;
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (n < n_rows) v = *reinterpret_cast<const uint4*>(x + n * x_row_stride + c * 8);
+    if (n < n_rows) v = *reinterpret_cast<const uint4*>(x + hy_src_off(map, n) + c * 8);
     *reinterpret_cast<uint4*>(xs + r * HC_ROW_WORDS + 4 * c) = v;
   }
   __syncthreads();
@@ -576,13 +615,24 @@ hybrid_encode35_coop_kernel(const uint16_t* __restrict__ x, int64_t n_rows, int6
   const int64_t n = row0 + vec;
   // whole quads leave together (n is the same for the four lanes); the shuffles below name all 32
   // lanes, so a warp with some finished quads keeps them running on zeros instead
-  const bool live = n < n_rows;
+  uint8_t* rec = n < n_rows ? hy_dst(map, out, n) : nullptr;     // nullptr: past the end, or a skipped slot
+  const bool live = rec != nullptr;
   const int* gidx = s_idx;
-  if (t.num_index_heads > 1 && live) gidx = t.group_index + (int)(n % t.num_index_heads) * 128;
-  uint32_t* dst = reinterpret_cast<uint32_t*>(out + (live ? n : 0) * out_row_stride);
+  if (t.num_index_heads > 1 && n < n_rows) gidx = t.group_index + (int)(n % t.num_index_heads) * 128;
+  uint32_t* dst = reinterpret_cast<uint32_t*>(live ? rec : out);
   hc_encode_group<3, BF16>(xs + vec * HC_ROW_WORDS, gidx, s_had, s_qjl, s_cent, s_bnd, q, lane, dst, live);
   hc_encode_group<2, BF16>(xs + vec * HC_ROW_WORDS, gidx + 64, s_had + 64, s_qjl + 64, s_cent + 8, s_bnd + 8, q, lane,
                            dst + 9, live);
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(HC_THREADS, 4)
+hybrid_encode35_coop_kernel(const uint16_t* __restrict__ x, int64_t n_rows, HyRowMap map,
+                            HybridTables t, uint8_t* __restrict__ out) {
+  __shared__ __align__(16) uint32_t xs[32 * HC_ROW_WORDS];
+  __shared__ float s_had[128], s_qjl[128], s_cent[16], s_bnd[16];
+  __shared__ int s_idx[128];
+  hc_encode35_rows<BF16>(x, n_rows, (int64_t)blockIdx.x * 32, map, t, out, xs, s_had, s_qjl, s_cent, s_bnd, s_idx);
 }
 
 // ---------------------------------------------------------------------------
@@ -680,14 +730,14 @@ hybrid_decode35_coop_kernel(const uint8_t* __restrict__ packed, int64_t p_row_st
   }
 }
 
-static int launch_hybrid_encode35_coop(const void* x, int x_dtype, int64_t n_rows, int64_t x_row_stride,
-                                       const HybridTables& t, uint8_t* out, int64_t out_row_stride, cudaStream_t st) {
+static int launch_hybrid_encode35_coop(const void* x, int x_dtype, int64_t n_rows, const HyRowMap& map,
+                                       const HybridTables& t, uint8_t* out, cudaStream_t st) {
   const int grid = (int)((n_rows + 31) / 32);
   const uint16_t* xp = reinterpret_cast<const uint16_t*>(x);
   if (x_dtype == AKV_BF16)
-    hybrid_encode35_coop_kernel<true><<<grid, HC_THREADS, 0, st>>>(xp, n_rows, x_row_stride, t, out, out_row_stride);
+    hybrid_encode35_coop_kernel<true><<<grid, HC_THREADS, 0, st>>>(xp, n_rows, map, t, out);
   else
-    hybrid_encode35_coop_kernel<false><<<grid, HC_THREADS, 0, st>>>(xp, n_rows, x_row_stride, t, out, out_row_stride);
+    hybrid_encode35_coop_kernel<false><<<grid, HC_THREADS, 0, st>>>(xp, n_rows, map, t, out);
   return check_launch("hybrid_encode35_coop_kernel");
 }
 
@@ -1348,11 +1398,10 @@ __device__ __forceinline__ void fwht64_smem(float* w, int lane) {
   __syncwarp();
 }
 
-__global__ void __launch_bounds__(32)
-hybrid_qprime_kernel(const void* __restrict__ q, int q_dtype, int64_t q_ss, int64_t q_sh, int num_q_heads,
-                     HybridTables t, float premul, float* __restrict__ qprime) {
-  __shared__ float w[4][64];
-  const int row = blockIdx.x, seq = row / num_q_heads, qh = row % num_q_heads, lane = threadIdx.x;
+__device__ __forceinline__ void hybrid_qprime_row(const void* __restrict__ q, int q_dtype, int64_t q_ss, int64_t q_sh,
+                                                  int num_q_heads, const HybridTables& t, float premul,
+                                                  float* __restrict__ qprime, int row, int lane, float (*w)[64]) {
+  const int seq = row / num_q_heads, qh = row % num_q_heads;
   for (int k = lane; k < 64; k += 32) {
     const float a = load_as_float(q, q_dtype, seq * q_ss + qh * q_sh + t.group_index[k]);
     const float b = load_as_float(q, q_dtype, seq * q_ss + qh * q_sh + t.group_index[64 + k]);
@@ -1369,6 +1418,45 @@ hybrid_qprime_kernel(const void* __restrict__ q, int q_dtype, int64_t q_ss, int6
     o[128 + k] = w[2][k] * 0.125f * premul;
     o[192 + k] = w[3][k] * 0.125f * premul * t.qjl_scale1;
   }
+}
+
+__global__ void __launch_bounds__(32)
+hybrid_qprime_kernel(const void* __restrict__ q, int q_dtype, int64_t q_ss, int64_t q_sh, int num_q_heads,
+                     HybridTables t, float premul, float* __restrict__ qprime) {
+  __shared__ float w[4][64];
+  hybrid_qprime_row(q, q_dtype, q_ss, q_sh, num_q_heads, t, premul, qprime, blockIdx.x, threadIdx.x, w);
+}
+
+// The new token's K and V vectors of a serving step (16-bit, rows readable in 16-byte pieces), written
+// into the paged record cache by extra blocks of the query-transform launch.
+struct HyStepWrite {
+  const uint16_t* xk; const uint16_t* xv;
+  HyRowMap mk, mv;
+  uint8_t* ck; uint8_t* cv;
+  int64_t n_rows;          // vectors per side (tokens x KV heads); 0: nothing to write
+};
+
+// First launch of a serving step: blocks [0, q_blocks) transform four query rows each (one warp per
+// row), the blocks after them encode 32 K vectors each, then 32 V vectors each.
+template <bool BF16>
+__global__ void __launch_bounds__(HC_THREADS, 4)
+hybrid_step_prologue_kernel(const void* __restrict__ q, int q_dtype, int64_t q_ss, int64_t q_sh, int num_q_heads,
+                            HybridTables t, float premul, float* __restrict__ qprime, int rows, int q_blocks,
+                            HyStepWrite wr) {
+  __shared__ __align__(16) uint32_t xs[32 * HC_ROW_WORDS];
+  __shared__ float s_had[128], s_qjl[128], s_cent[16], s_bnd[16];
+  __shared__ int s_idx[128];
+  if ((int)blockIdx.x >= q_blocks) {
+    const int e = (int)blockIdx.x - q_blocks, nb = (int)((wr.n_rows + 31) / 32);
+    const bool is_v = e >= nb;
+    hc_encode35_rows<BF16>(is_v ? wr.xv : wr.xk, wr.n_rows, (int64_t)(is_v ? e - nb : e) * 32, is_v ? wr.mv : wr.mk, t,
+                           is_v ? wr.cv : wr.ck, xs, s_had, s_qjl, s_cent, s_bnd, s_idx);
+    return;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = (int)blockIdx.x * 4 + warp;
+  float (*w)[64] = reinterpret_cast<float (*)[64]>(reinterpret_cast<float*>(xs) + warp * 256);   // 4 x 64 floats per warp
+  if (row < rows) hybrid_qprime_row(q, q_dtype, q_ss, q_sh, num_q_heads, t, premul, qprime, row, lane, w);
 }
 
 // LSE merge of the 256-coordinate partials and the inverse transforms of the epilogue.
@@ -1486,6 +1574,29 @@ static int tables_from(const akv_hybrid_tables* t, HybridTables* o, int* mode) {
   return AKV_OK;
 }
 
+// Encode n_rows vectors through `map` (contiguous rows or the paged scatter) with the kernel that fits
+// the input type and alignment.
+static int hybrid_encode_rows(const void* x, int x_dtype, int64_t n_rows, const HyRowMap& map, const HybridTables& t,
+                              int mode, uint8_t* out, cudaStream_t st) {
+  const bool paged = map.slot_mapping != nullptr;
+  if (x_dtype != AKV_F32) {
+    static const bool no_coop = getenv("AKV_HYBRID_NO_COOP") != nullptr;
+    const int64_t xs = paged ? (map.x_stride_tok | map.x_stride_head) : map.x_stride_row;
+    const int64_t os = paged ? (map.p_stride_blk | map.p_stride_pos | map.p_stride_head) : map.out_stride_row;
+    const bool rows16 = (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (xs & 7) == 0 &&
+                        (reinterpret_cast<uintptr_t>(out) & 3) == 0 && (os & 3) == 0;
+    if (mode == 35 && rows16 && !no_coop) return launch_hybrid_encode35_coop(x, x_dtype, n_rows, map, t, out, st);
+    if (mode == 35) return launch_hybrid_encode16<64, 3, 64, 2>(x, x_dtype, n_rows, map, t, out, st);
+    return launch_hybrid_encode16<32, 2, 96, 1>(x, x_dtype, n_rows, map, t, out, st);
+  }
+  const int grid = (int)((n_rows + HY_THREADS - 1) / HY_THREADS);
+  if (mode == 35)
+    hybrid_encode_kernel<64, 3, 64, 2><<<grid, HY_THREADS, 0, st>>>(x, x_dtype, n_rows, map, t, out);
+  else
+    hybrid_encode_kernel<32, 2, 96, 1><<<grid, HY_THREADS, 0, st>>>(x, x_dtype, n_rows, map, t, out);
+  return check_launch("hybrid_encode_kernel");
+}
+
 AKV_EXPORT int akv_hybrid_encode(const void* x, int x_dtype, int64_t n_rows, int64_t x_row_stride,
                                  const akv_hybrid_tables* tables, uint8_t* packed,
                                  int64_t packed_row_stride, void* stream) {
@@ -1495,23 +1606,39 @@ AKV_EXPORT int akv_hybrid_encode(const void* x, int x_dtype, int64_t n_rows, int
   if (n_rows == 0) return AKV_OK;
   if (!x || !packed) return fail(AKV_ERR_ARG, "akv_hybrid_encode: null pointer");
   if (x_dtype < AKV_F16 || x_dtype > AKV_F32) return fail(AKV_ERR_ARG, "bad x_dtype %d", x_dtype);
-  cudaStream_t st = (cudaStream_t)stream;
-  if (x_dtype != AKV_F32) {
-    static const bool no_coop = getenv("AKV_HYBRID_NO_COOP") != nullptr;
-    const bool rows16 = (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (x_row_stride & 7) == 0 &&
-                        (reinterpret_cast<uintptr_t>(packed) & 3) == 0 && (packed_row_stride & 3) == 0;
-    if (mode == 35 && rows16 && !no_coop)
-      return launch_hybrid_encode35_coop(x, x_dtype, n_rows, x_row_stride, t, packed, packed_row_stride, st);
-    if (mode == 35)
-      return launch_hybrid_encode16<64, 3, 64, 2>(x, x_dtype, n_rows, x_row_stride, t, packed, packed_row_stride, st);
-    return launch_hybrid_encode16<32, 2, 96, 1>(x, x_dtype, n_rows, x_row_stride, t, packed, packed_row_stride, st);
-  }
-  const int grid = (int)((n_rows + HY_THREADS - 1) / HY_THREADS);
-  if (mode == 35)
-    hybrid_encode_kernel<64, 3, 64, 2><<<grid, HY_THREADS, 0, st>>>(x, x_dtype, n_rows, x_row_stride, t, packed, packed_row_stride);
-  else
-    hybrid_encode_kernel<32, 2, 96, 1><<<grid, HY_THREADS, 0, st>>>(x, x_dtype, n_rows, x_row_stride, t, packed, packed_row_stride);
-  return check_launch("hybrid_encode_kernel");
+  return hybrid_encode_rows(x, x_dtype, n_rows, hy_contiguous(x_row_stride, packed_row_stride), t, mode, packed,
+                            (cudaStream_t)stream);
+}
+
+static int hybrid_paged_map(HyRowMap* m, int64_t num_tokens, int num_kv_heads, int64_t x_stride_tok,
+                            int64_t x_stride_head, const int64_t* slot_mapping, int64_t c_stride_blk,
+                            int64_t c_stride_pos, int64_t c_stride_head, int block_size, int64_t max_blocks) {
+  if (num_tokens < 0 || num_kv_heads <= 0 || block_size <= 0 || max_blocks <= 0)
+    return fail(AKV_ERR_ARG, "hybrid paged write: bad sizes");
+  *m = HyRowMap{};
+  m->slot_mapping = slot_mapping; m->num_heads = num_kv_heads; m->block_size = block_size; m->max_blocks = max_blocks;
+  m->x_stride_tok = x_stride_tok; m->x_stride_head = x_stride_head;
+  m->p_stride_blk = c_stride_blk; m->p_stride_pos = c_stride_pos; m->p_stride_head = c_stride_head;
+  return AKV_OK;
+}
+
+// Paged write of hybrid records: x [num_tokens, num_kv_heads, 128] is encoded and record (token, head) is
+// stored at cache[slot / block_size][slot % block_size][head]; tokens whose slot is negative or whose block is
+// >= max_blocks are skipped.
+AKV_EXPORT int akv_hybrid_kv_update(const void* x, int x_dtype, int64_t num_tokens, int num_kv_heads,
+                                    int64_t x_stride_tok, int64_t x_stride_head, const int64_t* slot_mapping,
+                                    const akv_hybrid_tables* tables, uint8_t* cache, int64_t c_stride_blk,
+                                    int64_t c_stride_pos, int64_t c_stride_head, int block_size,
+                                    int64_t max_blocks, void* stream) {
+  HybridTables t; int mode;
+  if (int rc = tables_from(tables, &t, &mode)) return rc;
+  HyRowMap m;
+  if (int rc = hybrid_paged_map(&m, num_tokens, num_kv_heads, x_stride_tok, x_stride_head, slot_mapping, c_stride_blk,
+                                c_stride_pos, c_stride_head, block_size, max_blocks)) return rc;
+  if (num_tokens == 0) return AKV_OK;
+  if (!x || !cache || !slot_mapping) return fail(AKV_ERR_ARG, "akv_hybrid_kv_update: null pointer");
+  if (x_dtype < AKV_F16 || x_dtype > AKV_F32) return fail(AKV_ERR_ARG, "bad x_dtype %d", x_dtype);
+  return hybrid_encode_rows(x, x_dtype, num_tokens * num_kv_heads, m, t, mode, cache, (cudaStream_t)stream);
 }
 
 AKV_EXPORT int akv_hybrid_decode(const uint8_t* packed, int64_t packed_row_stride, int64_t n_rows,
@@ -1585,7 +1712,7 @@ AKV_EXPORT size_t akv_hybrid_paged_attn_workspace_bytes(int num_seqs, int num_q_
   return total;
 }
 
-AKV_EXPORT int akv_hybrid_paged_attn(const akv_hybrid_attn_params* p) {
+static int run_hybrid_attn(const akv_hybrid_attn_params* p, const HyStepWrite* wr, bool wr_bf16) {
   if (!p) return fail(AKV_ERR_ARG, "null params");
   HybridTables t; int mode;
   if (int rc = tables_from(p->tables, &t, &mode)) return rc;
@@ -1612,9 +1739,21 @@ AKV_EXPORT int akv_hybrid_paged_attn(const akv_hybrid_attn_params* p) {
   float* part_ml = reinterpret_cast<float*>(ws + off_ml);
   cudaStream_t st = (cudaStream_t)p->stream;
   const int rows = p->num_seqs * p->num_q_heads;
-  hybrid_qprime_kernel<<<rows, 32, 0, st>>>(p->query, p->q_dtype, p->q_stride_seq, p->q_stride_head,
-                                            p->num_q_heads, t, p->scale * 1.4426950408889634f, qprime);
-  if (int rc = check_launch("hybrid_qprime_kernel")) return rc;
+  if (wr != nullptr && wr->n_rows > 0) {
+    const int q_blocks = (rows + 3) / 4;
+    const unsigned grid0 = (unsigned)(q_blocks + 2 * ((wr->n_rows + 31) / 32));
+    if (wr_bf16)
+      hybrid_step_prologue_kernel<true><<<grid0, HC_THREADS, 0, st>>>(p->query, p->q_dtype, p->q_stride_seq,
+          p->q_stride_head, p->num_q_heads, t, p->scale * 1.4426950408889634f, qprime, rows, q_blocks, *wr);
+    else
+      hybrid_step_prologue_kernel<false><<<grid0, HC_THREADS, 0, st>>>(p->query, p->q_dtype, p->q_stride_seq,
+          p->q_stride_head, p->num_q_heads, t, p->scale * 1.4426950408889634f, qprime, rows, q_blocks, *wr);
+    if (int rc = check_launch("hybrid_step_prologue_kernel")) return rc;
+  } else {
+    hybrid_qprime_kernel<<<rows, 32, 0, st>>>(p->query, p->q_dtype, p->q_stride_seq, p->q_stride_head,
+                                              p->num_q_heads, t, p->scale * 1.4426950408889634f, qprime);
+    if (int rc = check_launch("hybrid_qprime_kernel")) return rc;
+  }
   if (p->max_blocks_per_seq > 0) {
     HybridAttnArgs a{};
     a.k_cache = p->k_cache; a.v_cache = p->v_cache;
@@ -1648,4 +1787,53 @@ AKV_EXPORT int akv_hybrid_paged_attn(const akv_hybrid_attn_params* p) {
                                            p->context_lens, p->cl_dtype, bps * p->block_size, p->num_q_heads, t,
                                            p->out, p->out_dtype, p->out_stride_seq, p->out_stride_head);
   return check_launch("hybrid_merge_kernel");
+}
+
+AKV_EXPORT int akv_hybrid_paged_attn(const akv_hybrid_attn_params* p) { return run_hybrid_attn(p, nullptr, false); }
+
+// Mirror of akv_hybrid_decode_step_params in include/akv_b200.h.
+struct akv_hybrid_decode_step_params {
+  const void* key; const void* value; int kv_dtype;
+  int64_t num_tokens;
+  int64_t k_stride_tok, k_stride_head, v_stride_tok, v_stride_head;
+  const int64_t* slot_mapping;
+  int64_t max_blocks;
+  akv_hybrid_attn_params attn;
+};
+
+// One serving step in one call: encode the new tokens' K and V records into the paged cache, then attend.
+// With 16-bit K/V rows readable in 16-byte pieces (the serving case) the records are written by extra
+// blocks of the query-transform launch: three launches in all (transform + write, attention, merge).
+AKV_EXPORT int akv_hybrid_decode_step(const akv_hybrid_decode_step_params* p) {
+  if (!p) return fail(AKV_ERR_ARG, "null params");
+  const akv_hybrid_attn_params& a = p->attn;
+  if (p->num_tokens <= 0) return run_hybrid_attn(&p->attn, nullptr, false);
+  if (!p->key || !p->value || !p->slot_mapping || !a.k_cache || !a.v_cache)
+    return fail(AKV_ERR_ARG, "akv_hybrid_decode_step: null pointer");
+  HybridTables t; int mode;
+  if (int rc = tables_from(a.tables, &t, &mode)) return rc;
+  HyRowMap mk, mv;
+  if (int rc = hybrid_paged_map(&mk, p->num_tokens, a.num_kv_heads, p->k_stride_tok, p->k_stride_head, p->slot_mapping,
+                                a.k_stride_blk, a.k_stride_pos, a.k_stride_head, a.block_size, p->max_blocks)) return rc;
+  if (int rc = hybrid_paged_map(&mv, p->num_tokens, a.num_kv_heads, p->v_stride_tok, p->v_stride_head, p->slot_mapping,
+                                a.v_stride_blk, a.v_stride_pos, a.v_stride_head, a.block_size, p->max_blocks)) return rc;
+  const int64_t rows = p->num_tokens * (int64_t)a.num_kv_heads;
+  uint8_t* ck = const_cast<uint8_t*>(a.k_cache);
+  uint8_t* cv = const_cast<uint8_t*>(a.v_cache);
+  const bool x16 = p->kv_dtype == AKV_F16 || p->kv_dtype == AKV_BF16;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(p->key) | reinterpret_cast<uintptr_t>(p->value)) & 15) == 0 &&
+                       ((p->k_stride_tok | p->k_stride_head | p->v_stride_tok | p->v_stride_head) & 7) == 0 &&
+                       ((reinterpret_cast<uintptr_t>(ck) | reinterpret_cast<uintptr_t>(cv) | a.k_stride_blk | a.k_stride_pos |
+                         a.k_stride_head | a.v_stride_blk | a.v_stride_pos | a.v_stride_head) & 3) == 0;
+  if (mode == 35 && x16 && aligned && a.num_seqs > 0 && rows < (1 << 20)) {
+    HyStepWrite wr{};
+    wr.xk = reinterpret_cast<const uint16_t*>(p->key); wr.xv = reinterpret_cast<const uint16_t*>(p->value);
+    wr.mk = mk; wr.mv = mv; wr.ck = ck; wr.cv = cv; wr.n_rows = rows;
+    return run_hybrid_attn(&p->attn, &wr, p->kv_dtype == AKV_BF16);
+  }
+  if (p->kv_dtype < AKV_F16 || p->kv_dtype > AKV_F32) return fail(AKV_ERR_ARG, "bad kv_dtype %d", p->kv_dtype);
+  cudaStream_t st = (cudaStream_t)a.stream;
+  if (int rc = hybrid_encode_rows(p->key, p->kv_dtype, rows, mk, t, mode, ck, st)) return rc;
+  if (int rc = hybrid_encode_rows(p->value, p->kv_dtype, rows, mv, t, mode, cv, st)) return rc;
+  return run_hybrid_attn(&p->attn, nullptr, false);
 }

@@ -2210,6 +2210,10 @@ tq_attn_streamk4_lowbit_kernel(AttnArgs a) {
   }
 }
 
+}  // namespace akv
+#include "tq_attention_tma.cuh"
+namespace akv {
+
 int attn_window_status(int* host_out, int reset) {
   cudaError_t e = cudaMemcpyFromSymbol(host_out, g_attn_window_status, sizeof(int));
   if (e == cudaSuccess && reset) { const int z = 0; e = cudaMemcpyToSymbol(g_attn_window_status, &z, sizeof(int)); }
@@ -2422,9 +2426,26 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
   a.sk = sk;
   int merge_parts = plan.num_parts;          // stride (and upper bound) of the partial slots the merge reads
 
+  // 4-bit codes, at most four query heads per KV head, cache strides a tensor map can describe: the kernel
+  // with the TMA-fed ring (tensor maps cover the caller's cache on this GPU only)
+  static const bool no_tma = getenv("AKV_NO_TMA") != nullptr;
+  static const bool tma_window_ok = dyn_smem_window_start(reinterpret_cast<const void*>(tq4_attn_tma_kernel)) <= T4_BAR;
+  T4Maps maps;
+  const bool tma = persist && sk4 && !no_tma && tma_window_ok && p->bits == 4 && p->max_blocks_per_seq > 0 &&
+                   p->num_q_heads / p->num_kv_heads <= 4 && p->kp_stride_pos % 16 == 0 && p->vp_stride_pos % 16 == 0 &&
+                   p->kp_stride_blk % 16 == 0 && p->vp_stride_blk % 16 == 0 && t4_make_maps(a, &maps);
+
   if (p->ev_kernel_start) cudaEventRecord((cudaEvent_t)p->ev_kernel_start, st);
   if (p->max_blocks_per_seq > 0) {
-    if (persist && sk4) {
+    if (tma) {
+      a.num_parts = plan.sk_grid;
+      merge_parts = a.num_parts;
+      cudaError_t e = cudaFuncSetAttribute(tq4_attn_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T4_DYN_SMEM);
+      if (e != cudaSuccess) return fail((int)e, "attention: smem attribute: %s", cudaGetErrorString(e));
+      dim3 grid(plan.sk_grid, p->num_kv_heads / 8);
+      tq4_attn_tma_kernel<<<grid, T4_THREADS, T4_DYN_SMEM, st>>>(a, maps);
+      if (int rc = check_launch("tq4_attn_tma_kernel")) return rc;
+    } else if (persist && sk4) {
       a.num_parts = plan.sk_grid;
       merge_parts = a.num_parts;
       auto kern = p->bits == 4 ? tq4_attn_streamk4_kernel

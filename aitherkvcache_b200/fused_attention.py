@@ -29,8 +29,9 @@ class TQPagedAttention:
     SPLITK_BLOCKS = int(os.environ.get("AITHER_TQ_SPLITK_BLOCKS", "0"))
 
     def __init__(self, tq, num_query_heads: int, block_selector=None):
-        if block_selector is not None:
-            raise NotImplementedError("sparse block selection is not part of this build")
+        # optional BlockSelector (block_selector.py): filters block_tables / context_lens per query on the
+        # device before the attention kernels run (hook of the reference: fused_attention.py:664-668)
+        self._block_selector = block_selector
         self.rotation = tq.rotation
         self.rotation_T = getattr(tq, "rotation_T", None)
         if self.rotation_T is None:
@@ -148,6 +149,9 @@ class TQPagedAttention:
         if block_tables.stride(-1) != 1:
             block_tables = block_tables.contiguous()
         context_lens = context_lens.contiguous()
+        if self._block_selector is not None:
+            block_tables, context_lens = self._block_selector.select_for_query(
+                query, block_tables, context_lens, block_size, rotation_T=self.rotation_T)
         if out is None and raw_out is None:
             out = torch.empty(num_seqs, num_q_heads, head_dim, dtype=query.dtype, device=dev)
         target = raw_out if raw_out is not None else out

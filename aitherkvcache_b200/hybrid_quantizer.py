@@ -301,7 +301,10 @@ class HybridPagedAttention:
 
     def forward(self, query, k_cache, v_cache, block_tables, context_lens, block_size: int = 16,
                 num_kv_heads: Optional[int] = None, out: Optional[torch.Tensor] = None,
-                scale: Optional[float] = None) -> torch.Tensor:
+                scale: Optional[float] = None, new_kv=None) -> torch.Tensor:
+        """``new_kv = (key, value, slot_mapping)`` (``[tokens, kv_heads, 128]`` each, int64 slots): the
+        records of these tokens are written into the caches first, in the same call
+        (``akv_hybrid_decode_step``); tokens with a negative slot are skipped."""
         if num_kv_heads is None:
             num_kv_heads = k_cache.shape[2]
         dev = _lib.require_cuda(query, k_cache, v_cache, block_tables, context_lens)
@@ -325,7 +328,8 @@ class HybridPagedAttention:
         if self._workspace is None or self._workspace.numel() < nbytes or self._workspace.device != dev:
             self._workspace = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=dev)
         tables = self.htq._kernel_tables(1)      # one dim split shared by all heads
-        p = _lib.HybridAttnParams()
+        step = _lib.HybridDecodeStepParams() if new_kv is not None else None
+        p = step.attn if step is not None else _lib.HybridAttnParams()
         p.query, p.q_dtype, p.q_stride_seq, p.q_stride_head = query.data_ptr(), _lib.float_code(query), query.stride(0), query.stride(1)
         p.k_cache, p.k_stride_blk, p.k_stride_pos, p.k_stride_head = k_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1), k_cache.stride(2)
         p.v_cache, p.v_stride_blk, p.v_stride_pos, p.v_stride_head = v_cache.data_ptr(), v_cache.stride(0), v_cache.stride(1), v_cache.stride(2)
@@ -339,7 +343,61 @@ class HybridPagedAttention:
         p.workspace, p.workspace_bytes = self._workspace.data_ptr(), self._workspace.numel()
         p.blocks_per_split = 0
         p.stream = _lib.stream_ptr(dev)
+        if step is not None:
+            key, value, slots = new_kv
+            _lib.require_cuda(key, value, slots)
+            if key.shape != value.shape or key.dim() != 3 or key.shape[1] != num_kv_heads or key.shape[2] != 128:
+                raise ValueError(f"new K/V must be [tokens, {num_kv_heads}, 128], got {tuple(key.shape)} / {tuple(value.shape)}")
+            if key.dtype != value.dtype or key.dtype not in _lib._FLOAT_CODES:
+                raise TypeError("new K/V must share one of float16 / bfloat16 / float32")
+            if key.stride(-1) != 1:
+                key = key.contiguous()
+            if value.stride(-1) != 1:
+                value = value.contiguous()
+            if slots.dtype != torch.int64 or slots.numel() < key.shape[0]:
+                raise ValueError("slot_mapping must be int64 with one entry per token")
+            slots = slots.contiguous()
+            step.key, step.value, step.kv_dtype = key.data_ptr(), value.data_ptr(), _lib.float_code(key)
+            step.num_tokens = key.shape[0]
+            step.k_stride_tok, step.k_stride_head = key.stride(0), key.stride(1)
+            step.v_stride_tok, step.v_stride_head = value.stride(0), value.stride(1)
+            step.slot_mapping, step.max_blocks = slots.data_ptr(), k_cache.shape[0]
+            with torch.cuda.device(dev):
+                rc = L.akv_hybrid_decode_step(ctypes.byref(step))
+            _lib.check(rc, "akv_hybrid_decode_step")
+            return out
         with torch.cuda.device(dev):
             rc = L.akv_hybrid_paged_attn(ctypes.byref(p))
         _lib.check(rc, "akv_hybrid_paged_attn")
         return out
+
+
+def hybrid_kv_update(htq: HybridTurboQuant, x: torch.Tensor, slot_mapping: torch.Tensor, cache: torch.Tensor,
+                     block_size: Optional[int] = None, max_blocks: int = 0) -> None:
+    """Encode ``x`` ``[tokens, kv_heads, 128]`` and store the records at ``cache[slot // block_size,
+    slot % block_size, head, :packed_dim]`` (``cache``: uint8 ``[blocks, block_size, kv_heads, >= packed_dim]``,
+    views allowed).  The encode + index-put of the reference's ``tq::hybrid_decode_step``
+    (``vllm/hooks.py:259-296``) as one kernel; tokens with a negative slot are skipped."""
+    htq._ensure_calibrated()
+    dev = _lib.require_cuda(x, slot_mapping, cache)
+    if x.dim() != 3 or x.shape[2] != htq.head_dim or cache.dim() != 4 or cache.shape[2] != x.shape[1]:
+        raise ValueError(f"x {tuple(x.shape)} / cache {tuple(cache.shape)} do not match [tokens, heads, {htq.head_dim}] "
+                         "and [blocks, block_size, heads, bytes]")
+    if cache.dtype != torch.uint8 or cache.stride(-1) != 1 or cache.shape[-1] < htq.packed_dim:
+        raise ValueError(f"cache must be uint8 [..., >= {htq.packed_dim}] with a contiguous last dimension")
+    if x.dtype not in _lib._FLOAT_CODES:
+        x = x.float()
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    if slot_mapping.dtype != torch.int64 or slot_mapping.numel() < x.shape[0]:
+        raise ValueError("slot_mapping must be int64 with one entry per token")
+    slot_mapping = slot_mapping.contiguous()
+    bs = cache.shape[1] if block_size is None else block_size
+    assert bs == cache.shape[1], "block_size does not match the cache"
+    tables = htq._kernel_tables(x.shape[0] * x.shape[1])
+    with torch.cuda.device(dev):
+        rc = _lib.lib().akv_hybrid_kv_update(x.data_ptr(), _lib.float_code(x), x.shape[0], x.shape[1], x.stride(0),
+                                             x.stride(1), slot_mapping.data_ptr(), ctypes.byref(tables),
+                                             cache.data_ptr(), cache.stride(0), cache.stride(1), cache.stride(2), bs,
+                                             max_blocks or cache.shape[0], _lib.stream_ptr(dev))
+    _lib.check(rc, "akv_hybrid_kv_update")

@@ -2,32 +2,52 @@
 
 Surface of the reference's ``aither_kvcache/vllm/backend.py`` (``TurboQuantBackend`` :261-311,
 ``TurboQuantImpl`` :324-1273, ``register_turboquant_backend`` :1280-1295) restricted to what the
-hot path needs: the cache is uint8 ``[num_blocks, 2, block_size, kv_heads, packed_dim + 4]``
-(``get_kv_cache_shape`` keeps the reference's 5-D form), ``do_kv_cache_update`` encodes new
-K/V straight into it (norms in per-layer float32 tensors, as the reference's PRIMARY mode),
-and decode steps call the paged attention kernel on strided views of it.  Prefill chunks
-(more than one query token per sequence) decode the needed blocks and use dense attention;
-the reference's shadow mode, cold tier and block selection are not part of this build.
+hot path needs: the cache is uint8 ``[num_blocks, 2, block_size, kv_heads, head_size]``
+(``get_kv_cache_shape`` keeps the reference's 5-D form; the first ``packed_dim`` bytes of a row
+hold the codes), ``do_kv_cache_update`` encodes new K/V straight into it (norms in per-layer
+float32 tensors for the uniform codec, as the reference's PRIMARY mode; inside the record for the
+hybrid codec), and every forward - single-token decode, chunked prefill, or a batch that mixes
+the two - attends over the packed cache with the paged kernels: each query token becomes one row
+with its own causal context length and its sequence's block-table row, built on the device
+without a host synchronisation.  Nothing is decompressed to fp16.  The reference's shadow mode,
+cold tier and block selection are not part of this build.
 
-The codec is picked like the reference does (``AITHER_TQ_BITS``, default 4) or from a
-``tq-t4nc`` / ``tq-t3nc`` / ``tq-t2nc`` cache-dtype string.  The classes are created on first
-attribute access so that importing this module does not import vLLM.
+The codec is picked like the reference does (``vllm/backend.py:618-626``): ``AITHER_TQ_MODE=tq35``
+selects the hybrid codec, otherwise ``AITHER_TQ_BITS`` (default 4) the uniform one; a
+``tq-t4nc`` / ``tq-t3nc`` / ``tq-t2nc`` / ``tq-t35nc`` cache-dtype string overrides both.  The
+classes are created on first attribute access so that importing this module does not import vLLM.
 """
 from __future__ import annotations
 
-import math
+import inspect
 import os
-from typing import Dict, Optional
+from typing import Dict, Optional, Tuple
 
 import torch
 
 KV_DTYPE_BITS = {"tq-t4nc": 4, "tq-t3nc": 3, "tq-t2nc": 2}
+KV_DTYPE_HYBRID = {"tq-t35nc": "tq35"}
 
 
 def bits_from_env_or_dtype(cache_dtype_str: Optional[str] = None) -> int:
     if cache_dtype_str in KV_DTYPE_BITS:
         return KV_DTYPE_BITS[cache_dtype_str]
     return int(os.environ.get("AITHER_TQ_BITS", "4"))
+
+
+def codec_from_env_or_dtype(cache_dtype_str: Optional[str] = None) -> Tuple[str, object]:
+    """``("uniform", bits)`` or ``("hybrid", "tq35")``."""
+    if cache_dtype_str in KV_DTYPE_HYBRID:
+        return "hybrid", KV_DTYPE_HYBRID[cache_dtype_str]
+    if cache_dtype_str in KV_DTYPE_BITS:
+        return "uniform", KV_DTYPE_BITS[cache_dtype_str]
+    mode = os.environ.get("AITHER_TQ_MODE", "")
+    if mode == "tq35":
+        return "hybrid", mode
+    if mode == "tq25":
+        raise NotImplementedError("AITHER_TQ_MODE=tq25: the tq25 codec exists (HybridTurboQuant), its paged "
+                                  "attention kernel does not; use tq35")
+    return "uniform", bits_from_env_or_dtype(cache_dtype_str)
 
 
 class _LayerState:
@@ -48,15 +68,48 @@ def _quantizer(head_size: int, bits: int, device):
     return tq
 
 
+def _hybrid_quantizer(head_size: int, mode: str, device):
+    from ..hybrid_quantizer import HybridTurboQuant
+    key = (head_size, mode, str(device))
+    htq = _LayerState.quantizers.get(key)
+    if htq is None:
+        htq = HybridTurboQuant(head_dim=head_size, mode=mode, device=str(device))
+        htq.calibrate_uniform()
+        _LayerState.quantizers[key] = htq
+    return htq
+
+
+def token_rows(query_start_loc: torch.Tensor, seq_lens: torch.Tensor, block_table: torch.Tensor,
+               num_tokens: int):
+    """One attention row per query token of a (chunked-prefill or mixed) batch, computed on the device:
+    token t of sequence s, the i-th of its n_s query tokens, attends causally over the first
+    ``seq_lens[s] - (n_s - 1 - i)`` cached tokens through sequence s's block-table row.
+    Returns (block_tables [num_tokens, max_blocks], context_lens int32 [num_tokens])."""
+    dev = block_table.device
+    tok = torch.arange(num_tokens, device=dev, dtype=query_start_loc.dtype)
+    ends = query_start_loc[1:]
+    seq = torch.bucketize(tok, ends, right=True).clamp_(max=ends.numel() - 1)
+    ctx = seq_lens.index_select(0, seq) - (ends.index_select(0, seq) - 1 - tok).to(seq_lens.dtype)
+    return block_table.index_select(0, seq), ctx.clamp_(min=0).to(torch.int32)
+
+
 class TurboQuantImplBase:
     """Backend-independent part of the impl (usable and testable without vLLM)."""
+
+    PREFILL_ROWS = 64        # query tokens per attention call of a prefill chunk
 
     def _tq_setup(self, num_heads: int, head_size: int, scale: float, num_kv_heads: int,
                   kv_cache_dtype: str = "auto") -> None:
         self.num_heads, self.head_size, self.scale = num_heads, head_size, float(scale)
         self.num_kv_heads = num_kv_heads
-        self.tq_bits = bits_from_env_or_dtype(kv_cache_dtype)
-        self.packed_dim = head_size * self.tq_bits // 8
+        self.tq_codec, what = codec_from_env_or_dtype(kv_cache_dtype)
+        if self.tq_codec == "hybrid":
+            from ..hybrid_quantizer import HybridTurboQuant
+            self.tq_mode, self.tq_bits = what, 0
+            self.packed_dim = HybridTurboQuant.packed_dim_for_mode(head_size, what)
+        else:
+            self.tq_mode, self.tq_bits = "", int(what)
+            self.packed_dim = head_size * self.tq_bits // 8
 
     def _norms(self, layer_name: str, kv_cache: torch.Tensor):
         kn = _LayerState.k_norms.get(layer_name)
@@ -69,13 +122,41 @@ class TurboQuantImplBase:
 
     def do_kv_cache_update(self, layer, key, value, kv_cache, slot_mapping) -> None:
         """Encode ``key`` / ``value`` [tokens, kv_heads, head_size] into the packed cache in place."""
+        pd, bs = self.packed_dim, kv_cache.shape[2]
+        if self.tq_codec == "hybrid":
+            from ..hybrid_quantizer import hybrid_kv_update
+            htq = _hybrid_quantizer(self.head_size, self.tq_mode, kv_cache.device)
+            for x, side in ((key, 0), (value, 1)):
+                hybrid_kv_update(htq, x, slot_mapping, kv_cache[:, side, :, :, :pd], bs, kv_cache.shape[0])
+            return
         from ..fused_kv_update import fused_tq4_kv_update
         tq = _quantizer(self.head_size, self.tq_bits, kv_cache.device)
         kn, vn = self._norms(getattr(layer, "layer_name", "layer"), kv_cache)
-        pd, bs = self.packed_dim, kv_cache.shape[2]
         for x, side, norms in ((key, 0, kn), (value, 1, vn)):
             fused_tq4_kv_update(x, slot_mapping, kv_cache[:, side, :, :, :pd], norms, tq.rotation,
                                 tq.boundaries_inner, bs, kv_cache.shape[0], rotation_t=tq.rotation_T)
+
+    def _attend(self, layer, q, out, kv_cache, block_table, context_lens) -> None:
+        pd, bs = self.packed_dim, kv_cache.shape[2]
+        kc, vc = kv_cache[:, 0, :, :, :pd], kv_cache[:, 1, :, :, :pd]
+        key_ = (self.head_size, self.tq_codec, self.tq_mode or self.tq_bits, self.num_heads, str(kv_cache.device))
+        attn = _LayerState.attention.get(key_)
+        if self.tq_codec == "hybrid":
+            if attn is None:
+                from ..hybrid_quantizer import HybridPagedAttention
+                attn = HybridPagedAttention(_hybrid_quantizer(self.head_size, self.tq_mode, kv_cache.device),
+                                            self.num_heads)
+                _LayerState.attention[key_] = attn
+            attn.forward(q, kc, vc, block_table, context_lens, block_size=bs, num_kv_heads=self.num_kv_heads,
+                         out=out, scale=self.scale)
+            return
+        if attn is None:
+            from ..fused_attention import TQPagedAttention
+            attn = TQPagedAttention(_quantizer(self.head_size, self.tq_bits, kv_cache.device), self.num_heads)
+            _LayerState.attention[key_] = attn
+        kn, vn = self._norms(getattr(layer, "layer_name", "layer"), kv_cache)
+        attn.forward(q, kc, kn, vc, vn, block_table, context_lens, block_size=bs, num_kv_heads=self.num_kv_heads,
+                     out=out, scale=self.scale)
 
     def forward(self, layer, query, key, value, kv_cache, attn_metadata, output=None, output_scale=None,
                 output_block_scale=None):
@@ -86,46 +167,15 @@ class TurboQuantImplBase:
         n = attn_metadata.num_actual_tokens
         q = query[:n].view(n, self.num_heads, self.head_size)
         out = output[:n].view(n, self.num_heads, self.head_size)
-        tq = _quantizer(self.head_size, self.tq_bits, kv_cache.device)
-        kn, vn = self._norms(getattr(layer, "layer_name", "layer"), kv_cache)
-        pd, bs = self.packed_dim, kv_cache.shape[2]
-        kc, vc = kv_cache[:, 0, :, :, :pd], kv_cache[:, 1, :, :, :pd]
-        if attn_metadata.max_query_len == 1:
-            from ..fused_attention import TQPagedAttention
-            key_ = (self.head_size, self.tq_bits, self.num_heads, str(kv_cache.device))
-            attn = _LayerState.attention.get(key_)
-            if attn is None:
-                attn = TQPagedAttention(tq, self.num_heads)
-                _LayerState.attention[key_] = attn
-            attn.forward(q, kc, kn, vc, vn, attn_metadata.block_table, attn_metadata.seq_lens, block_size=bs,
-                         num_kv_heads=self.num_kv_heads, out=out, scale=self.scale)
+        if attn_metadata.max_query_len == 1:      # one token per sequence: rows are the sequences
+            self._attend(layer, q, out, kv_cache, attn_metadata.block_table, attn_metadata.seq_lens)
             return output
-        self._prefill(q, out, tq, kc, kn, vc, vn, attn_metadata, bs)
+        bt, ctx = token_rows(attn_metadata.query_start_loc, attn_metadata.seq_lens, attn_metadata.block_table, n)
+        # the split-K workspace grows with the number of rows of a call: a chunk goes through in slices
+        for lo in range(0, n, self.PREFILL_ROWS):
+            hi = min(n, lo + self.PREFILL_ROWS)
+            self._attend(layer, q[lo:hi], out[lo:hi], kv_cache, bt[lo:hi], ctx[lo:hi])
         return output
-
-    def _prefill(self, q, out, tq, kc, kn, vc, vn, md, bs) -> None:
-        """Chunked prefill: decode each sequence's context to fp16 and run causal dense attention."""
-        starts = md.query_start_loc.tolist()
-        lens = md.seq_lens.tolist()
-        gqa = self.num_heads // self.num_kv_heads
-        for s in range(len(lens)):
-            q0, q1 = starts[s], starts[s + 1]
-            if q1 <= q0:
-                continue
-            ctx = lens[s]
-            blocks = md.block_table[s, :(ctx + bs - 1) // bs].long()
-            k = tq.decode(kc[blocks].reshape(-1, self.num_kv_heads, kc.shape[-1])[:ctx],
-                          kn[blocks].reshape(-1, self.num_kv_heads)[:ctx])
-            v = tq.decode(vc[blocks].reshape(-1, self.num_kv_heads, vc.shape[-1])[:ctx],
-                          vn[blocks].reshape(-1, self.num_kv_heads)[:ctx])
-            kh = k.permute(1, 0, 2).repeat_interleave(gqa, dim=0).to(q.dtype)
-            vh = v.permute(1, 0, 2).repeat_interleave(gqa, dim=0).to(q.dtype)
-            nq = q1 - q0
-            pos_q = torch.arange(ctx - nq, ctx, device=q.device)[:, None]
-            mask = torch.arange(ctx, device=q.device)[None, :] <= pos_q
-            o = torch.nn.functional.scaled_dot_product_attention(q[q0:q1].transpose(0, 1), kh, vh, attn_mask=mask,
-                                                                 scale=self.scale)
-            out[q0:q1] = o.transpose(0, 1)
 
 
 _backend_cls = None
@@ -135,11 +185,20 @@ _impl_cls = None
 def _make_impl_class():
     from vllm.v1.attention.backends.triton_attn import TritonAttentionImpl
 
+    base_params = list(inspect.signature(TritonAttentionImpl.__init__).parameters)[1:]
+
     class TurboQuantImpl(TurboQuantImplBase, TritonAttentionImpl):
-        def __init__(self, num_heads, head_size, scale, num_kv_heads=None, *args, kv_cache_dtype="auto", **kwargs):
-            TritonAttentionImpl.__init__(self, num_heads, head_size, scale, num_kv_heads, *args,
-                                         kv_cache_dtype="auto", **kwargs)
-            self._tq_setup(num_heads, head_size, scale, num_kv_heads or num_heads, kv_cache_dtype)
+        def __init__(self, *args, **kwargs):
+            # vLLM passes kv_cache_dtype by position or by name depending on its version: find it by the
+            # base class's own signature, keep it for the codec choice and give the base class "auto"
+            # (it would reject the tq-* names)
+            bound = dict(zip(base_params, args))
+            bound.update(kwargs)
+            kv_cache_dtype = bound.get("kv_cache_dtype", "auto")
+            bound["kv_cache_dtype"] = "auto"
+            TritonAttentionImpl.__init__(self, **bound)
+            self._tq_setup(bound["num_heads"], bound["head_size"], bound["scale"],
+                           bound.get("num_kv_heads") or bound["num_heads"], kv_cache_dtype)
 
     return TurboQuantImpl
 
@@ -148,7 +207,8 @@ def _make_backend_class():
     from vllm.v1.attention.backend import AttentionBackend
 
     class TurboQuantBackend(AttentionBackend):
-        supported_kv_cache_dtypes = ["auto", "bfloat16", "fp8", "fp8_e4m3", "fp8_e5m2", *KV_DTYPE_BITS]
+        supported_kv_cache_dtypes = ["auto", "bfloat16", "fp8", "fp8_e4m3", "fp8_e5m2", *KV_DTYPE_BITS,
+                                     *KV_DTYPE_HYBRID]
         accept_output_buffer = True
         forward_includes_kv_cache_update = False
 
@@ -169,7 +229,11 @@ def _make_backend_class():
             from vllm.v1.attention.backends.triton_attn import TritonAttentionMetadataBuilder
 
             class TQMetadataBuilder(TritonAttentionMetadataBuilder):
-                _cudagraph_support = AttentionCGSupport.NEVER
+                # The single-token decode step is a fixed sequence of kernel launches on raw device
+                # pointers (no host synchronisation, no allocation once the shared workspace exists), so
+                # it can be captured; prefill and mixed batches build per-token rows whose shapes
+                # follow the batch and stay eager.  (The reference declares NEVER.)
+                _cudagraph_support = AttentionCGSupport.UNIFORM_SINGLE_TOKEN_DECODE
 
             return TQMetadataBuilder
 

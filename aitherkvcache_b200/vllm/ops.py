@@ -192,27 +192,28 @@ def hybrid_decode_step(query, key, value, kv_cache, output, slot_mapping, block_
     """Same schema as the reference's ``tq::hybrid_decode_step`` (``vllm/hooks.py:240-355``):
     encode the new K/V records into ``kv_cache`` (uint8 ``[blocks, 2, block_size, kv_heads, >= packed_dim]``,
     norms embedded), then attend.  Where the reference decompresses every referenced block and runs
-    dense SDPA, this attends over the records directly.  Tokens with a negative slot are skipped."""
+    dense SDPA, this attends over the records directly (``akv_hybrid_decode_step``: cache write and
+    attention in three kernel launches).  Tokens with a negative slot are skipped."""
     from ..hybrid_quantizer import HybridPagedAttention
     htq = _hybrid.get(head_size)
     if htq is None:
         raise RuntimeError(f"no hybrid quantiser for head_size {head_size}: call init_hybrid_quantizer() first")
     pd = htq.packed_dim
+    if kv_cache.dim() != 5 or kv_cache.shape[1] != 2 or kv_cache.shape[3] != num_kv_heads or kv_cache.shape[4] < pd:
+        raise ValueError(f"hybrid_decode_step: kv_cache {tuple(kv_cache.shape)} does not hold [blocks, 2, block_size, "
+                         f"{num_kv_heads}, >= {pd}]")
+    if min(query.shape[0], output.shape[0], block_table.shape[0], seq_lens.numel()) < num_actual:
+        raise ValueError(f"hybrid_decode_step: num_actual={num_actual} exceeds query/output/block_table/seq_lens rows")
     key_cache, value_cache = kv_cache[:, 0], kv_cache[:, 1]
     block_size = key_cache.shape[1]
-    n, h, d = key.shape
-    valid = (slot_mapping >= 0).view(-1, 1, 1)
-    slot = slot_mapping.clamp(min=0)
-    bi, oi = slot // block_size, slot % block_size
-    for x, cache in ((key, key_cache), (value, value_cache)):
-        rec = htq.encode(x.reshape(n * h, d)).reshape(n, h, pd)
-        cache[bi, oi, :, :pd] = torch.where(valid, rec, cache[bi, oi, :, :pd])
     attn = _hybrid_attn.get((head_size, num_heads))
     if attn is None:
         attn = HybridPagedAttention(htq, num_heads)
         _hybrid_attn[(head_size, num_heads)] = attn
+    # one call: the records of the new tokens are written by the attention's first launch
     attn.forward(query[:num_actual], key_cache[..., :pd], value_cache[..., :pd], block_table, seq_lens,
-                 block_size=block_size, num_kv_heads=num_kv_heads, out=output[:num_actual], scale=scale)
+                 block_size=block_size, num_kv_heads=num_kv_heads, out=output[:num_actual], scale=scale,
+                 new_kv=(key, value, slot_mapping))
     return output.clone()
 
 

@@ -189,6 +189,41 @@ int akv_lse_merge(const float* parts, int num_parts, int num_seqs, int num_q_hea
                   int64_t out_stride_head, void* stream);
 
 /* ------------------------------------------------------------------------
+ * Block selection for sparse decode attention (head_dim 128)
+ * ---------------------------------------------------------------------- */
+
+/* Replaces BlockRepresentativeCache.update + finalize (aither_kvcache/block_selector.py:65-113): for
+ * every newly written token t and head h, centroid[code] * norm is added to acc[block_idx[t]][h][:] and
+ * counts[block][h] is incremented, then rep = acc / count for the touched blocks.  acc / rep
+ * [max_blocks][num_kv_heads][128] float32 and counts [max_blocks][num_kv_heads] int32 are the caller's
+ * (zero-initialised) tensors.  Strides in elements. */
+int akv_block_select_update(const int64_t* block_idx, int64_t num_tokens, const uint8_t* k_packed,
+                            int64_t kp_stride_tok, int64_t kp_stride_head, const float* k_norms,
+                            int64_t kn_stride_tok, int64_t kn_stride_head, const float* centroids, int bits,
+                            int num_kv_heads, int head_dim, int64_t max_blocks, float* acc, int* counts,
+                            float* rep, void* stream);
+
+/* Replaces BlockRepresentativeCache.clear_blocks (block_selector.py:115-121). */
+int akv_block_select_clear(const int64_t* block_idx, int64_t num_blocks_to_clear, int num_kv_heads,
+                           int64_t max_blocks, float* acc, int* counts, float* rep, void* stream);
+
+/* Replaces score_blocks + select_blocks (block_selector.py:128-228): scores every block of every sequence
+ * against the rotated, GQA-averaged query, keeps the first num_sink_blocks and last num_recent_blocks
+ * valid blocks, takes the max_selected best (ties: lower logical index) and writes their physical ids in
+ * logical order to out_block_tables int32 [num_seqs][max_selected] (rows padded with 0) and the adjusted
+ * context lengths to out_context_lens int32 [num_seqs].  exact_tail != 0 counts only the real tokens of a
+ * kept partial last block (the reference counts it as full).  scores_out (optional) float32
+ * [num_seqs][max_blocks_per_seq] receives the raw scores (-inf past the context). */
+size_t akv_block_select_workspace_bytes(int num_seqs, int num_kv_heads, int max_blocks_per_seq);
+int akv_block_select(const void* query, int q_dtype, int64_t q_stride_seq, int64_t q_stride_head,
+                     int num_seqs, int num_q_heads, int num_kv_heads, int head_dim, const float* rotation_t,
+                     const float* rep, int64_t max_blocks, const void* block_tables, int bt_dtype,
+                     int64_t bt_stride_seq, const void* context_lens, int cl_dtype, int block_size,
+                     int max_blocks_per_seq, int max_selected, int num_sink_blocks, int num_recent_blocks,
+                     int exact_tail, int* out_block_tables, int* out_context_lens, float* scores_out,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------
  * Hybrid split-group codec (tq35 / tq25, head_dim 128)
  * ---------------------------------------------------------------------- */
 
@@ -239,6 +274,32 @@ typedef struct akv_hybrid_attn_params {
 size_t akv_hybrid_paged_attn_workspace_bytes(int num_seqs, int num_q_heads, int block_size,
                                              int max_blocks_per_seq, int blocks_per_split);
 int akv_hybrid_paged_attn(const akv_hybrid_attn_params* params);
+
+/* Paged write of hybrid records.  Replaces the encode + index-put of tq::hybrid_decode_step
+ * (vllm/hooks.py:259-296): x [num_tokens, num_kv_heads, 128] (strides in elements) is encoded and the
+ * record of (token, head) is stored at cache[slot / block_size][slot % block_size][head] (strides in
+ * bytes), slot = slot_mapping[token].  Tokens with a negative slot, or whose block is >= max_blocks, are
+ * skipped (the reference's index-put would wrap a negative slot to the last block). */
+int akv_hybrid_kv_update(const void* x, int x_dtype, int64_t num_tokens, int num_kv_heads,
+                         int64_t x_stride_tok, int64_t x_stride_head, const int64_t* slot_mapping,
+                         const akv_hybrid_tables* tables, uint8_t* cache, int64_t c_stride_blk,
+                         int64_t c_stride_pos, int64_t c_stride_head, int block_size, int64_t max_blocks,
+                         void* stream);
+
+/* One serving step in one call: body of tq::hybrid_decode_step (vllm/hooks.py:240-355).  The new
+ * tokens' K and V records go into attn.k_cache / attn.v_cache at slot_mapping (as akv_hybrid_kv_update),
+ * then the attention of akv_hybrid_paged_attn runs over the updated cache.  With fp16 / bf16 K and V
+ * whose rows start on 16-byte boundaries the records are written by extra blocks of the attention's
+ * first launch (three kernel launches per step); other inputs take two write launches first. */
+typedef struct akv_hybrid_decode_step_params {
+  const void* key; const void* value; int kv_dtype;   /* [num_tokens, num_kv_heads, 128] */
+  int64_t num_tokens;
+  int64_t k_stride_tok, k_stride_head, v_stride_tok, v_stride_head;
+  const int64_t* slot_mapping;                        /* [num_tokens] */
+  int64_t max_blocks;
+  akv_hybrid_attn_params attn;
+} akv_hybrid_decode_step_params;
+int akv_hybrid_decode_step(const akv_hybrid_decode_step_params* params);
 
 /* ------------------------------------------------------------------------
  * TriAttention spectral codec (head_dim 128, int4 coefficients, pre-RoPE keys)

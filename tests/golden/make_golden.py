@@ -160,7 +160,52 @@ def tri():
          out_far=out_far, scores_far=sc_far)
 
 
+def block_select():
+    """The reference's BlockSelector on a seeded paged cache: representatives from the packed keys,
+    scores, filtered tables (ties are improbable with random data)."""
+    from aither_kvcache.block_selector import BlockSelector
+    H, QH, D, bs = 2, 8, 128, 16
+    tq = TurboQuant(head_dim=D, bits=4, device="cpu")
+    g = torch.Generator().manual_seed(5)
+    ctx = [1500, 1043, 70, 2000]
+    nblk = [(c + bs - 1) // bs for c in ctx]
+    total = sum(nblk) + 3
+    perm = torch.randperm(total, generator=g)
+    bt = torch.zeros(len(ctx), max(nblk), dtype=torch.int64)
+    p = 0
+    tok_blocks = []
+    for s, n in enumerate(nblk):
+        bt[s, :n] = perm[p:p + n]
+        p += n
+        tok_blocks.append(bt[s, :n].repeat_interleave(bs)[:ctx[s]])
+    tok_blocks = torch.cat(tok_blocks)
+    N = tok_blocks.numel()
+    # keys with a per-block drift so that block means differ
+    drift = torch.randn(total, H, D, generator=g)
+    k = (torch.randn(N, H, D, generator=g) + 1.5 * drift[tok_blocks]).half()
+    kp, kn = tq.encode(k)
+    sel = BlockSelector(total, H, D // 2, torch.device("cpu"), tq.centroids, select_ratio=0.25,
+                        num_sink_blocks=2, num_recent_blocks=2, min_blocks_for_selection=8)
+    sel.update_reps(tok_blocks, torch.zeros(N, dtype=torch.int64), kp, kn)
+    q = torch.randn(len(ctx), QH, D, generator=g).half()
+    q_rot = torch.matmul(q.float(), tq.rotation.T)
+    from aither_kvcache.block_selector import score_blocks
+    cl = torch.tensor(ctx, dtype=torch.int64)
+    scores = score_blocks(q_rot[..., 0::2].contiguous(), q_rot[..., 1::2].contiguous(), sel._rep_cache.rep_even,
+                          sel._rep_cache.rep_odd, bt, cl, QH // H, bs)
+    fbt, fcl = sel.select(q_rot[..., 0::2].contiguous(), q_rot[..., 1::2].contiguous(), bt, cl, QH // H, bs)
+    rep = torch.stack((sel._rep_cache.rep_even, sel._rep_cache.rep_odd), dim=-1).reshape(total, H, D)
+    save("block_select.npz", k_packed=kp, k_norms=kn, token_blocks=tok_blocks, block_tables=bt, context_lens=cl,
+         query=q, rotation=tq.rotation, centroids=tq.centroids, rep=rep, scores=scores, filtered_bt=fbt,
+         filtered_cl=fcl, max_selected=np.array(sel.max_selected), num_blocks=np.array(total))
+
+
 if __name__ == "__main__":
+    if len(sys.argv) > 1:          # regenerate only the named fixtures, e.g. `make_golden.py block_select`
+        for name in sys.argv[1:]:
+            globals()[name]()
+        sys.exit(0)
+    block_select()
     uniform_codec()
     paged_write()
     paged_attention()

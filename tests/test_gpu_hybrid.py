@@ -169,3 +169,34 @@ def test_paged_attention_full_size_properties():
     ref = ohy.paged_attention_decode_sdpa(q.cpu().numpy()[pick], kc.cpu().numpy(), vc.cpu().numpy(), bt.numpy()[pick],
                                           ctx.numpy()[pick], t, 1.0 / math.sqrt(D), BS, kv_dtype=np.float32)
     assert (np.abs(out[pick] - ref) <= 2e-3 * np.maximum(1.0, np.abs(ref))).all()
+
+
+def test_paged_attention_full_size_random_values_vs_oracle():
+    """tq35 attention at the headline shapes with random K and random V: the shortest and the longest
+    (about 31 K tokens) sequence against the oracle's decode -> dense attention, element by element."""
+    from aitherkvcache_b200.hybrid_quantizer import HybridPagedAttention
+    g = load_golden("hybrid_tq35.npz")
+    h = _htq("tq35", g, heads=1)
+    t = _oracle_tables(g, "tq35")
+    H, QH, D, BS, S = 8, 32, 128, 16, 16
+    gen = torch.Generator().manual_seed(1)
+    ctx = torch.randint(4096, 32769, (S,), generator=gen)
+    nblk = [(int(c) + BS - 1) // BS for c in ctx]
+    total = sum(nblk)
+    perm = torch.randperm(total, generator=gen)
+    bt = torch.zeros(S, max(nblk), dtype=torch.int32)
+    p = 0
+    for s, n in enumerate(nblk):
+        bt[s, :n] = perm[p:p + n].to(torch.int32)
+        p += n
+    gg = torch.Generator(device="cuda").manual_seed(2)
+    kc = h.encode(torch.randn(total, BS, H, D, generator=gg, device="cuda").half())
+    vc = h.encode(torch.randn(total, BS, H, D, generator=gg, device="cuda").half())
+    q = torch.randn(S, QH, D, generator=torch.Generator().manual_seed(5)).half().cuda()
+    out = HybridPagedAttention(h, QH).forward(q, kc, vc, bt.cuda(), ctx.to(torch.int32).cuda()).float().cpu().numpy()
+    order = np.argsort(ctx.numpy())
+    pick = np.array([order[0], order[-1]])
+    assert int(ctx[pick[1]]) > 30000
+    ref = ohy.paged_attention_decode_sdpa(q.cpu().numpy()[pick], kc.cpu().numpy(), vc.cpu().numpy(), bt.numpy()[pick],
+                                          ctx.numpy()[pick], t, 1.0 / math.sqrt(D), BS, kv_dtype=np.float32)
+    assert np.abs(out[pick] - ref).max() < 2e-3

@@ -176,3 +176,224 @@ def test_backend_impl_cache_update_decode_and_prefill():
     op, on = otq.encode(key.cpu().numpy(), tq.rotation.cpu().numpy(), tq.boundaries_inner.cpu().numpy(), bits)
     got_n = kn.reshape(-1, H)[slots.cuda()].cpu().numpy()
     assert np.array_equal(got_n.view(np.uint32), on.view(np.uint32))
+
+
+def test_hybrid_decode_step_is_three_launches_and_skips_negative_slots():
+    """tq::hybrid_decode_step writes the new records and attends in three kernel launches; a token with a
+    negative slot is skipped even when another token of the batch writes block 0, offset 0."""
+    from aitherkvcache_b200 import _lib
+    from aitherkvcache_b200.vllm import ops
+    g = load_golden("hybrid_tq35.npz")
+    htq = ops.init_hybrid_quantizer(128, "tq35")
+    t = ohy.Tables(128, "tq35", g["had0"], g["had1"], g["qjl0"], g["qjl1"],
+                   codebooks=[(g["cent0"], g["bnd0"]), (g["cent1"], g["bnd1"])])
+    H, QH, bs, total = 8, 32, 16, 6
+    gen = torch.Generator().manual_seed(18)
+    kv = torch.zeros(total, 2, bs, H, 64, dtype=torch.uint8, device="cuda")
+    kv[:, 0] = htq.encode(torch.randn(total, bs, H, 128, generator=gen).half().cuda())
+    kv[:, 1] = htq.encode(torch.randn(total, bs, H, 128, generator=gen).half().cuda())
+    before = kv.clone()
+    bt = torch.tensor([[0, 3], [2, 5], [4, 1]], dtype=torch.int32, device="cuda")
+    ctx = torch.tensor([1, 20, 7], dtype=torch.int32, device="cuda")
+    q = torch.randn(3, QH, 128, generator=gen).half().cuda()
+    key = torch.randn(3, H, 128, generator=gen).bfloat16()
+    val = torch.randn(3, H, 128, generator=gen).bfloat16()
+    slots = torch.tensor([0, -1, 4 * bs + 6], dtype=torch.int64)     # seq 0 -> block 0 offset 0; seq 1 skipped
+    ops.register_custom_ops()
+    out = torch.zeros(3, QH, 128, dtype=torch.float16, device="cuda")
+    L = _lib.lib()
+    args = (q, key.cuda(), val.cuda(), kv, out, slots.cuda(), bt, ctx, 0, QH, H, 128, 1.0 / math.sqrt(128), 3)
+    torch.ops.tq.hybrid_decode_step(*args)          # first call sets function attributes
+    kv.copy_(before)
+    n0 = L.akv_launch_count()
+    torch.ops.tq.hybrid_decode_step(*args)
+    assert L.akv_launch_count() - n0 == 3
+    kc, vc = before[:, 0].cpu().numpy().copy(), before[:, 1].cpu().numpy().copy()
+    kc[0, 0] = ohy.encode(key[0].float().numpy(), t)
+    vc[0, 0] = ohy.encode(val[0].float().numpy(), t)
+    kc[4, 6] = ohy.encode(key[2].float().numpy(), t)
+    vc[4, 6] = ohy.encode(val[2].float().numpy(), t)
+    assert np.array_equal(kv[:, 0].cpu().numpy(), kc) and np.array_equal(kv[:, 1].cpu().numpy(), vc)
+    ref = ohy.paged_attention_decode_sdpa(q.cpu().numpy(), kc, vc, bt.cpu().numpy(), ctx.cpu().numpy(), t,
+                                          1.0 / math.sqrt(128), bs)
+    assert np.abs(out.float().cpu().numpy() - ref).max() < 2e-3
+
+
+@pytest.mark.parametrize("dtype", (torch.float16, torch.bfloat16, torch.float32))
+def test_hybrid_kv_update_paged_write(dtype):
+    """akv_hybrid_kv_update: records land at their slots byte for byte (oracle encoder), skipped and
+    out-of-range slots leave the cache alone, a strided cache view (the K half of a [blocks, 2, ...] tensor)
+    is addressed through its strides."""
+    from aitherkvcache_b200.hybrid_quantizer import HybridTurboQuant, hybrid_kv_update
+    g = load_golden("hybrid_tq35.npz")
+    htq = HybridTurboQuant(128, "tq35", device="cuda")
+    htq.calibrate_uniform()
+    t = ohy.Tables(128, "tq35", g["had0"], g["had1"], g["qjl0"], g["qjl1"],
+                   codebooks=[(g["cent0"], g["bnd0"]), (g["cent1"], g["bnd1"])])
+    H, bs, blocks, T = 8, 16, 9, 70
+    gen = torch.Generator().manual_seed(4)
+    x = torch.randn(T, H, 128, generator=gen).to(dtype)
+    slots = torch.randperm(blocks * bs, generator=gen)[:T].to(torch.int64)
+    slots[5] = -1
+    slots[9] = blocks * bs + 3            # beyond the cache
+    kv = torch.full((blocks, 2, bs, H, 64), 0xAB, dtype=torch.uint8, device="cuda")
+    hybrid_kv_update(htq, x.cuda(), slots.cuda(), kv[:, 0])
+    want = np.full((blocks, bs, H, 64), 0xAB, np.uint8)
+    rec = ohy.encode(x.float().numpy(), t)
+    for i, s in enumerate(slots.tolist()):
+        if 0 <= s < blocks * bs:
+            want[s // bs, s % bs] = rec[i]
+    assert np.array_equal(kv[:, 0].cpu().numpy(), want)
+    assert (kv[:, 1] == 0xAB).all()
+
+
+def _causal_oracle(q, kp, kn, vp, vn, bt, lens, qlens, R, cent, bits):
+    """Oracle for a chunked-prefill batch: query token i of a sequence's n query tokens sees the first
+    len - (n - 1 - i) cached tokens (decode -> fp16 -> dense attention per token)."""
+    outs = []
+    p = 0
+    for s, (ln, n) in enumerate(zip(lens, qlens)):
+        for i in range(n):
+            c = ln - (n - 1 - i)
+            outs.append(otq.paged_attention_decode_sdpa(q[p:p + 1], kp, kn, vp, vn, bt[s:s + 1], np.asarray([c]), R, cent,
+                                                        bits, 1.0 / math.sqrt(128))[0])
+            p += 1
+    return np.stack(outs).astype(np.float32)
+
+
+def test_backend_mixed_batch_attends_over_the_packed_cache():
+    """A batch that mixes a prefill chunk in the middle of a sequence, a decode token and a full prefill:
+    every query token is a row of the paged kernel with its causal context; compared token by token with
+    the oracle.  More rows than one slice holds, so the slicing is exercised too."""
+    from aitherkvcache_b200.vllm.backend import TurboQuantImplBase, _LayerState
+    H, QH, bs, bits = 8, 32, 16, 4
+    impl = TurboQuantImplBase()
+    impl._tq_setup(QH, 128, 1.0 / math.sqrt(128), H, "tq-t4nc")
+    impl.PREFILL_ROWS = 32
+    layer = types.SimpleNamespace(layer_name="mixed.layers.0.attn")
+    lens, qlens = [150, 77, 60], [50, 1, 60]          # cached tokens incl. this step's, query tokens of this step
+    nb = sum((n + bs - 1) // bs for n in lens) + 1
+    gen = torch.Generator().manual_seed(14)
+    perm = torch.randperm(nb, generator=gen)
+    bt = torch.zeros(3, 10, dtype=torch.int32)
+    p = 0
+    for s, n in enumerate(lens):
+        k = (n + bs - 1) // bs
+        bt[s, :k] = perm[p:p + k].to(torch.int32)
+        p += k
+    kv = torch.zeros(nb, 2, bs, H, 128, dtype=torch.uint8, device="cuda")
+    # the whole context of every sequence goes through the cache update (earlier steps + this one)
+    T = sum(lens)
+    key = torch.randn(T, H, 128, generator=gen).half().cuda()
+    val = torch.randn(T, H, 128, generator=gen).half().cuda()
+    slots = torch.cat([(bt[s, :(n + bs - 1) // bs].long()[:, None] * bs + torch.arange(bs)[None]).reshape(-1)[:n]
+                       for s, n in enumerate(lens)])
+    impl.do_kv_cache_update(layer, key, val, kv, slots.cuda())
+    nq = sum(qlens)
+    qry = torch.randn(nq, QH * 128, generator=gen).half()
+    qsl = torch.tensor([0, 50, 51, 111], dtype=torch.int32, device="cuda")
+    md = types.SimpleNamespace(num_actual_tokens=nq, max_query_len=max(qlens), block_table=bt.cuda(),
+                               seq_lens=torch.tensor(lens, dtype=torch.int32, device="cuda"), query_start_loc=qsl)
+    out = torch.zeros(nq, QH * 128, dtype=torch.float16, device="cuda")
+    impl.forward(layer, qry.cuda(), None, None, kv, md, output=out)
+    tq = _LayerState.quantizers[(128, 4, "cuda:0")]
+    kn, vn = _LayerState.k_norms[layer.layer_name], _LayerState.v_norms[layer.layer_name]
+    ref = _causal_oracle(qry.reshape(nq, QH, 128).numpy(), kv[:, 0, ..., :64].cpu().numpy(), kn.cpu().numpy(),
+                         kv[:, 1, ..., :64].cpu().numpy(), vn.cpu().numpy(), bt.numpy(), lens, qlens,
+                         tq.rotation.cpu().numpy(), tq.centroids.cpu().numpy(), bits)
+    got = out.float().cpu().numpy().reshape(nq, QH, 128)
+    assert (np.abs(got - ref) <= 2e-3 * np.maximum(1.0, np.abs(ref))).all()
+
+
+def test_backend_hybrid_mode_from_environment(monkeypatch):
+    """AITHER_TQ_MODE=tq35 selects the hybrid codec in the backend impl: records (norms inside) written by
+    do_kv_cache_update equal the oracle's, decode and prefill rows match the oracle's decode -> attention."""
+    from aitherkvcache_b200.vllm.backend import TurboQuantImplBase
+    monkeypatch.setenv("AITHER_TQ_MODE", "tq35")
+    g = load_golden("hybrid_tq35.npz")
+    t = ohy.Tables(128, "tq35", g["had0"], g["had1"], g["qjl0"], g["qjl1"],
+                   codebooks=[(g["cent0"], g["bnd0"]), (g["cent1"], g["bnd1"])])
+    H, QH, bs = 8, 32, 16
+    impl = TurboQuantImplBase()
+    impl._tq_setup(QH, 128, 1.0 / math.sqrt(128), H, "auto")
+    assert impl.tq_codec == "hybrid" and impl.packed_dim == 64
+    layer = types.SimpleNamespace(layer_name="hy.layers.0.attn")
+    lens = [45, 130]
+    bt = torch.tensor([[3, 7, 1, 0, 0, 0, 0, 0, 0], [2, 4, 5, 6, 8, 9, 10, 11, 12]], dtype=torch.int32)
+    kv = torch.zeros(14, 2, bs, H, 128, dtype=torch.uint8, device="cuda")
+    gen = torch.Generator().manual_seed(24)
+    T = sum(lens)
+    key = torch.randn(T, H, 128, generator=gen).half()
+    val = torch.randn(T, H, 128, generator=gen).half()
+    slots = torch.cat([(bt[s, :(n + bs - 1) // bs].long()[:, None] * bs + torch.arange(bs)[None]).reshape(-1)[:n]
+                       for s, n in enumerate(lens)])
+    impl.do_kv_cache_update(layer, key.cuda(), val.cuda(), kv, slots.cuda())
+    kc = kv[:, 0, ..., :64].cpu().numpy()
+    vc = kv[:, 1, ..., :64].cpu().numpy()
+    assert np.array_equal(kc.reshape(-1, H, 64)[slots.numpy()], ohy.encode(key.numpy(), t))
+    q = torch.randn(2, QH * 128, generator=gen).half()
+    md1 = types.SimpleNamespace(num_actual_tokens=2, max_query_len=1, block_table=bt.cuda(),
+                                seq_lens=torch.tensor(lens, dtype=torch.int32, device="cuda"))
+    out1 = torch.zeros(2, QH * 128, dtype=torch.float16, device="cuda")
+    impl.forward(layer, q.cuda(), None, None, kv, md1, output=out1)
+    ref = ohy.paged_attention_decode_sdpa(q.reshape(2, QH, 128).numpy(), kc, vc, bt.numpy(), np.asarray(lens), t,
+                                          1.0 / math.sqrt(128), bs)
+    assert np.abs(out1.float().cpu().numpy().reshape(2, QH, 128) - ref).max() < 2e-3
+    # the last three tokens of sequence 1 as a prefill chunk: the last row equals the decode row
+    q3 = torch.cat([torch.randn(2, QH * 128, generator=gen).half(), q[1:2]])
+    md3 = types.SimpleNamespace(num_actual_tokens=3, max_query_len=3, block_table=bt[1:2].cuda(),
+                                seq_lens=torch.tensor(lens[1:], dtype=torch.int32, device="cuda"),
+                                query_start_loc=torch.tensor([0, 3], dtype=torch.int32, device="cuda"))
+    out3 = torch.zeros(3, QH * 128, dtype=torch.float16, device="cuda")
+    impl.forward(layer, q3.cuda(), None, None, kv, md3, output=out3)
+    assert (out3[2].float() - out1[1].float()).abs().max().item() < 1e-3
+    ref0 = ohy.paged_attention_decode_sdpa(q3[:1].reshape(1, QH, 128).numpy(), kc, vc, bt.numpy()[1:2],
+                                           np.asarray([lens[1] - 2]), t, 1.0 / math.sqrt(128), bs)
+    assert np.abs(out3[0].float().cpu().numpy().reshape(QH, 128) - ref0[0]).max() < 2e-3
+
+
+def test_backend_decode_step_replays_from_a_cuda_graph():
+    """The single-token decode forward of the backend impl (what the metadata builder declares
+    graph-capturable): captured once, replayed with new query / sequence-length contents in the same
+    buffers, equal to the eager result."""
+    from aitherkvcache_b200.vllm.backend import TurboQuantImplBase
+    H, QH, bs = 8, 32, 16
+    impl = TurboQuantImplBase()
+    impl._tq_setup(QH, 128, 1.0 / math.sqrt(128), H, "tq-t4nc")
+    layer = types.SimpleNamespace(layer_name="graph.layers.0.attn")
+    lens = [300, 41, 1000, 7]
+    nblk = [(n + bs - 1) // bs for n in lens]
+    gen = torch.Generator().manual_seed(31)
+    perm = torch.randperm(sum(nblk), generator=gen)
+    bt = torch.zeros(4, max(nblk), dtype=torch.int32)
+    p = 0
+    for s, k in enumerate(nblk):
+        bt[s, :k] = perm[p:p + k].to(torch.int32)
+        p += k
+    kv = torch.zeros(sum(nblk), 2, bs, H, 128, dtype=torch.uint8, device="cuda")
+    T = sum(lens)
+    slots = torch.cat([(bt[s, :nblk[s]].long()[:, None] * bs + torch.arange(bs)[None]).reshape(-1)[:n]
+                       for s, n in enumerate(lens)])
+    impl.do_kv_cache_update(layer, torch.randn(T, H, 128, generator=gen).half().cuda(),
+                            torch.randn(T, H, 128, generator=gen).half().cuda(), kv, slots.cuda())
+    q = torch.randn(4, QH * 128, generator=gen).half().cuda()
+    seq_lens = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    md = types.SimpleNamespace(num_actual_tokens=4, max_query_len=1, block_table=bt.cuda(), seq_lens=seq_lens)
+    out = torch.zeros(4, QH * 128, dtype=torch.float16, device="cuda")
+    impl.forward(layer, q, None, None, kv, md, output=out)            # warm-up: workspace, argument block
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        impl.forward(layer, q, None, None, kv, md, output=out)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        impl.forward(layer, q, None, None, kv, md, output=out)
+    for trial in range(2):
+        q.copy_(torch.randn(4, QH * 128, generator=gen).half())
+        seq_lens.copy_(torch.tensor([n - trial * 5 for n in lens], dtype=torch.int32).clamp(min=1))
+        graph.replay()
+        got = out.clone()
+        impl.forward(layer, q, None, None, kv, md, output=out)
+        torch.cuda.synchronize()
+        assert torch.equal(got, out)

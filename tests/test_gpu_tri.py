@@ -142,3 +142,19 @@ def test_decode_step_full_size_properties():
                                   merged.stride(0), merged.stride(1), torch.cuda.current_stream().cuda_stream)
     _lib.check(rc, "akv_lse_merge")
     assert (merged - out.float()).abs().max().item() < 1e-3
+
+
+def test_decode_step_full_context_random_values_vs_oracle():
+    """One batch element of the 128K-token workload (131072 keys at positions 0..131071, query at 131072,
+    32 query / 8 KV heads) with random keys AND random values, element by element against the oracle:
+    covers relative positions from -1 down to -131072."""
+    B, S, H, QH = 1, 131072, 8, 32
+    tri = _tri(H, QH)
+    keys, values, g = _synthetic(B, S, H, seed=11)
+    q = torch.randn(B, QH, 128, generator=g).half()
+    k_enc, v_enc = tri.encode_kv(keys.cuda(), values.cuda())
+    out = tri.decode_step(q.cuda(), k_enc, v_enc).cpu().numpy()
+    k_np = tuple(t.cpu().numpy() for t in k_enc)
+    v_np = tuple(t.cpu().numpy() for t in v_enc)
+    ref = otri.decode_step(q.numpy(), k_np, v_np, tri._theta.cpu().numpy())
+    assert np.abs(out - ref).max() < 2e-3

@@ -91,3 +91,56 @@ def test_kv_cache_dtype_table():
     import aitherkvcache_b200 as a
     assert a.KV_CACHE_DTYPES["tq-t4nc"] == {"kind": "uniform", "bits": 4}
     assert a.KV_CACHE_DTYPES["tq-t35nc"]["mode"] == "tq35"
+
+
+def test_plugin_entry_point_and_backend_construction_under_vllm(monkeypatch):
+    """The packaging of the serving boundary: pyproject.toml declares a vllm.general_plugins entry
+    point; it resolves to a callable that registers the CUSTOM backend with the installed vLLM, and
+    the real TurboQuantImpl (a subclass of vLLM's own impl) constructs with vLLM's argument order."""
+    import importlib
+    import tomllib
+    pytest.importorskip("vllm")
+    with open(os.path.join(ROOT, "pyproject.toml"), "rb") as f:
+        proj = tomllib.load(f)
+    eps = proj["project"]["entry-points"]["vllm.general_plugins"]
+    assert eps == {"aitherkvcache_b200": "aitherkvcache_b200.vllm.plugin:register"}
+    mod, attr = eps["aitherkvcache_b200"].split(":")
+    register = getattr(importlib.import_module(mod), attr)
+    register()
+    from vllm.v1.attention.backends.registry import AttentionBackendEnum
+    cls = AttentionBackendEnum.CUSTOM.get_class()
+    assert cls.get_name() == "CUSTOM" and cls.__module__ == "aitherkvcache_b200.vllm.backend"
+    assert cls.get_kv_cache_shape(10, 16, 8, 128) == (10, 2, 16, 8, 128)
+    from vllm.v1.attention.backend import AttentionCGSupport
+    assert cls.get_builder_cls()._cudagraph_support == AttentionCGSupport.UNIFORM_SINGLE_TOKEN_DECODE
+    impl_cls = cls.get_impl_cls()
+    monkeypatch.delenv("AITHER_TQ_MODE", raising=False)
+    monkeypatch.delenv("AITHER_TQ_BITS", raising=False)
+    impl = impl_cls(32, 128, 0.0884, 8, None, None, "tq-t3nc")            # positional, as vLLM's layers call it
+    assert (impl.tq_codec, impl.tq_bits, impl.packed_dim, impl.num_kv_heads) == ("uniform", 3, 48, 8)
+    monkeypatch.setenv("AITHER_TQ_MODE", "tq35")
+    impl = impl_cls(num_heads=32, head_size=128, scale=0.0884, num_kv_heads=8, alibi_slopes=None,
+                    sliding_window=None, kv_cache_dtype="auto")
+    assert (impl.tq_codec, impl.tq_mode, impl.packed_dim) == ("hybrid", "tq35", 64)
+    monkeypatch.setenv("AITHER_TQ_MODE", "")
+    monkeypatch.setenv("AITHER_TQ_BITS", "2")
+    assert impl_cls(32, 128, 0.0884, 8, None, None, "auto").packed_dim == 32
+
+
+def test_token_rows_of_a_mixed_batch():
+    """Per-token attention rows of a chunked-prefill / decode mix: causal context lengths and the
+    sequences' block-table rows, against a plain loop."""
+    import torch
+    from aitherkvcache_b200.vllm.backend import token_rows
+    qsl = torch.tensor([0, 5, 6, 6, 14], dtype=torch.int32)        # 5 prefill tokens, 1 decode, an empty one, 8 prefill
+    seq_lens = torch.tensor([5, 900, 3, 40], dtype=torch.int32)
+    bt = torch.arange(4 * 7, dtype=torch.int32).reshape(4, 7)
+    rows_bt, ctx = token_rows(qsl, seq_lens, bt, 14)
+    want_ctx, want_seq = [], []
+    for s in range(4):
+        n = int(qsl[s + 1] - qsl[s])
+        for i in range(n):
+            want_ctx.append(int(seq_lens[s]) - (n - 1 - i))
+            want_seq.append(s)
+    assert ctx.tolist() == want_ctx and ctx.dtype == torch.int32
+    assert torch.equal(rows_bt, bt[torch.tensor(want_seq)])

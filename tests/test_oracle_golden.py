@@ -194,3 +194,24 @@ def test_torch_cpu_baseline_matches_the_oracle():
     out = ott.paged_decode_attention(q, T(d["k_packed"]), T(d["k_norms"]), T(d["v_packed"]), T(d["v_norms"]),
                                      T(d["block_tables"]), T(d["context_lens"]), T(R), T(cent))
     assert np.abs(out.float().numpy() - ref.astype(np.float32)).max() < 2e-3
+
+
+def test_block_select_oracle_matches_the_reference():
+    """oracle/block_select.py against the reference's own representatives, scores and filtered tables."""
+    from oracle import block_select as obs
+    g = load_golden("block_select.npz")
+    codes = otq.unpack(g["k_packed"], 128, 4)
+    rep = obs.representatives(g["token_blocks"], codes, g["k_norms"], g["centroids"], int(g["num_blocks"]))
+    assert np.abs(rep - g["rep"]).max() < 1e-4
+    q_rot = g["query"].astype(np.float32) @ g["rotation"].T
+    sc = obs.score_blocks(q_rot, rep, g["block_tables"], g["context_lens"], 4, 16)
+    fin = np.isfinite(g["scores"])
+    assert np.array_equal(np.isfinite(sc), fin)
+    assert np.abs(sc[fin] - g["scores"][fin]).max() < 1e-2 * max(1.0, np.abs(g["scores"][fin]).max())
+    fbt, fcl = obs.select_blocks(g["scores"], g["block_tables"], g["context_lens"], 16, int(g["max_selected"]))
+    assert np.array_equal(fcl, g["filtered_cl"])
+    # rows are compared as far as the filtered context reaches (beyond it torch.topk's choice among
+    # equal -inf entries is unspecified)
+    for s in range(fbt.shape[0]):
+        n = (int(fcl[s]) + 15) // 16
+        assert np.array_equal(fbt[s, :n], g["filtered_bt"][s, :n])
