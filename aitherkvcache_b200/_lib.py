@@ -102,6 +102,20 @@ class HybridDecodeStepParams(C.Structure):
     ]
 
 
+class P2PMergeParams(C.Structure):
+    """Mirror of ``akv_p2p_merge_params``."""
+    _fields_ = [
+        ("local_raw", c_vp),
+        ("num_seqs", c_int), ("num_q_heads", c_int), ("head_dim", c_int),
+        ("world", c_int), ("rank", c_int),
+        ("peer_buffers", C.POINTER(c_vp)), ("peer_flags", C.POINTER(c_vp)),
+        ("state", c_vp),
+        ("rotation", c_vp),
+        ("out", c_vp), ("out_dtype", c_int), ("out_stride_seq", c_i64), ("out_stride_head", c_i64),
+        ("stream", c_vp),
+    ]
+
+
 class TriDecodeParams(C.Structure):
     """Mirror of ``akv_tri_decode_params``."""
     _fields_ = [
@@ -157,6 +171,8 @@ _SIGNATURES = {
     "akv_tri_encode": (c_int, [c_vp, c_int, c_i64, c_i64, c_int, c_int, c_vp, c_vp, c_vp, c_vp]),
     "akv_tri_decode_workspace_bytes": (C.c_size_t, [c_int] * 4),
     "akv_tri_decode_step": (c_int, [C.POINTER(TriDecodeParams)]),
+    "akv_p2p_exchange_bytes": (C.c_size_t, [c_int] * 4),
+    "akv_p2p_lse_merge": (c_int, [C.POINTER(P2PMergeParams)]),
     "akv_lse_merge": (c_int, [c_vp, c_int, c_int, c_int, c_int, c_vp, c_vp, c_int, c_i64, c_i64, c_vp]),
 }
 
@@ -198,9 +214,9 @@ def check(rc: int, what: str) -> None:
 def device_status(reset: bool = False) -> dict:
     """Device-side status words of the current device (synchronises): all zero unless a bounded
     wait gave up or a fixed-address kernel found its shared-memory window taken."""
-    out = (c_int * 4)()
+    out = (c_int * 5)()
     check(lib().akv_device_status(out, 1 if reset else 0), "akv_device_status")
-    return {"tc_encode": out[0], "tc_decode": out[1], "attn_window": out[2], "hybrid_window": out[3]}
+    return {"tc_encode": out[0], "tc_decode": out[1], "attn_window": out[2], "hybrid_window": out[3], "p2p": out[4]}
 
 
 def float_code(t: torch.Tensor) -> int:

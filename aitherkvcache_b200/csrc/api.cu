@@ -42,12 +42,13 @@ AKV_EXPORT int akv_device_arch(void) {
   return major * 10 + minor;
 }
 
-// Device-side status words of the current device, copied to out[0..3] after everything queued on the
+// Device-side status words of the current device, copied to out[0..4] after everything queued on the
 // device so far has finished (this call synchronises; it is a diagnostic, not part of a serving step):
 //   out[0] tensor-core encoder, out[1] tensor-core decoder: 0 = fine, 1 = a bounded wait on an MMA barrier
 //          gave up and the CTA left its tile unwritten, 2 = it also kept its tensor-memory columns
 //   out[2] packed-cache attention, out[3] hybrid attention: 1 = a fixed-address kernel found its shared
 //          window taken and returned without writing partials
+//   out[4] akv_p2p_lse_merge: 1 = the bounded wait for the peers' partials ran out (a peer is late or gone)
 // reset != 0 clears the words after reading them.
 AKV_EXPORT int akv_device_status(int* out, int reset) {
   if (!out) return akv::fail(AKV_ERR_ARG, "akv_device_status: null pointer");
@@ -56,7 +57,8 @@ AKV_EXPORT int akv_device_status(int* out, int reset) {
   if (int rc = akv::tc_encode_status(out + 0, reset)) return rc;
   if (int rc = akv::tc_decode_status(out + 1, reset)) return rc;
   if (int rc = akv::attn_window_status(out + 2, reset)) return rc;
-  return akv::hybrid_window_status(out + 3, reset);
+  if (int rc = akv::hybrid_window_status(out + 3, reset)) return rc;
+  return akv::p2p_status(out + 4, reset);
 }
 
 // Test hook for the bounded waits of the tensor-core codec kernels: CTA 0 of the next launches of the

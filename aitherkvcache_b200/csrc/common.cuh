@@ -143,7 +143,17 @@ struct MergeArgs {
   void* out; int out_dtype; int64_t out_ss, out_sh;
   float* raw_out;
   const int* part_counts;       // optional [num_seqs]: number of valid parts of each sequence
+  // optional: the partials live in one of two halves of a double buffer; *half_select (a device word
+  // written earlier in the stream) says which, half_stride floats apart
+  const unsigned int* half_select;
+  int64_t half_stride;
 };
+
+__device__ __forceinline__ int64_t merge_half_offset(const MergeArgs& a) {
+  return a.half_select != nullptr ? (int64_t)(*a.half_select) * a.half_stride : 0;
+}
+
+int p2p_status(int* host_out, int reset);
 
 int launch_merge(const MergeArgs& a, int rows, cudaStream_t st);
 

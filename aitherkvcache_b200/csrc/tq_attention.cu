@@ -182,7 +182,7 @@ __global__ void akv_merge_kernel(MergeArgs a) {
     int64_t v = splits * a.warps_per_head;
     np = (int)(v < np ? v : np);
   }
-  const float* ml = a.ml + (int64_t)row * a.ml_row;
+  const float* ml = a.ml + merge_half_offset(a) + (int64_t)row * a.ml_row;
   // weights w_p = 2^(m_p - M) for parts with l_p > 0 (first warp), L = sum l_p w_p
   if (threadIdx.x < 32) {
     float M = -CUDART_INF_F;
@@ -205,7 +205,7 @@ __global__ void akv_merge_kernel(MergeArgs a) {
   }
   __syncthreads();
   const float M = s_red[0], L = s_red[1];
-  const float* acc = a.acc + (int64_t)row * a.acc_row;
+  const float* acc = a.acc + merge_half_offset(a) + (int64_t)row * a.acc_row;
   for (int d = threadIdx.x; d < a.D; d += blockDim.x) {
     float o4[4] = {0.f, 0.f, 0.f, 0.f};    // independent chains so the loads overlap
     int p = 0;
@@ -367,12 +367,12 @@ akv_merge128_kernel(MergeArgs a, int rows, int np_alloc) {
       // the partial sums do not depend on the weights: up to MP parts are requested now and arrive while
       // the group's first warp works the weights out
       if (np <= MP) {
-        const float* accp = a.acc + (int64_t)row * a.acc_row + d;
+        const float* accp = a.acc + merge_half_offset(a) + (int64_t)row * a.acc_row + d;
 #pragma unroll
         for (int k = 0; k < MP; ++k) v[k] = (k < np) ? accp[(int64_t)k * a.acc_part] : 0.f;
       }
       if (d < 32) {                         // first warp of the group: weights, as in akv_merge_kernel
-        const float* ml = a.ml + (int64_t)row * a.ml_row;
+        const float* ml = a.ml + merge_half_offset(a) + (int64_t)row * a.ml_row;
         float M = -CUDART_INF_F;
         for (int p = d; p < np; p += 32) {
           const float m = ml[(int64_t)p * a.ml_part], l = ml[(int64_t)p * a.ml_part + 1];
@@ -395,7 +395,7 @@ akv_merge128_kernel(MergeArgs a, int rows, int np_alloc) {
     group_sync(g);
     if (live) {
       const float L = red[2 * g + 1];
-      const float* acc = a.acc + (int64_t)row * a.acc_row;
+      const float* acc = a.acc + merge_half_offset(a) + (int64_t)row * a.acc_row;
       float o4[4] = {0.f, 0.f, 0.f, 0.f};
       int p = 0;
       if (np <= MP) {                       // same order of additions as the rounds of eight below

@@ -42,8 +42,11 @@ __device__ __forceinline__ void t4_arrive(uint32_t bar) {
 __device__ __forceinline__ void t4_arrive_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
 }
-// Bounded wait: about a second of SM cycles at most.
+// Bounded wait: about a second of SM cycles at most.  After the first wait of a CTA that runs out, the
+// shared word T4_FAILED makes every later wait of the CTA return at once, so a broken run ends quickly.
+constexpr uint32_t T4_FAILED = T4_BAR + 64;
 __device__ __forceinline__ bool t4_wait(uint32_t bar, uint32_t parity) {
+  if (lds32(T4_FAILED) != 0u) return false;
   const long long t0 = clock64();
   for (int it = 0; it < (1 << 24); ++it) {
     uint32_t done;
@@ -56,6 +59,7 @@ __device__ __forceinline__ bool t4_wait(uint32_t bar, uint32_t parity) {
     if ((it & 63) == 63 && clock64() - t0 > (1ll << 31)) break;
   }
   g_attn_window_status = 2;
+  asm volatile("st.shared.u32 [%0], %1;" :: "r"(T4_FAILED), "r"(1u) : "memory");
   return false;
 }
 __device__ __forceinline__ void t4_tma4(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
@@ -126,6 +130,7 @@ tq4_attn_tma_kernel(AttnArgs a, const __grid_constant__ T4Maps maps) {
   }
   if (tid < 16) s_cent[tid] = a.centroids[tid];
   if (tid == 0) {
+    asm volatile("st.shared.u32 [%0], %1;" :: "r"(T4_FAILED), "r"(0u) : "memory");
 #pragma unroll
     for (int i = 0; i < 4; ++i) t4_bar_init(T4_BAR + 8 * i, 4);          // fullK[0..1], fullV[0..1]: four issuing lanes
 #pragma unroll

@@ -144,18 +144,9 @@ __device__ __forceinline__ float ex2a(float x) {
   return y;
 }
 
-// sin and cos of a float32 phase of magnitude up to ~2e5 rad: subtract n * 2*pi with 2*pi split
-// into three float32 terms (FMA keeps each product exact), then the hardware approximations
-// on the reduced argument in [-pi, pi] (absolute error ~5e-7).
-__device__ __forceinline__ void sincos_reduced(float phi, float& s, float& c) {
-  const float n = rintf(phi * 0.15915494309189535f);
-  float r = __fmaf_rn(-n, 6.2831854820251465f, phi);
-  r = __fmaf_rn(-n, -1.7484555314695172e-07f, r);
-  r = __fmaf_rn(-n, -6.8604980400235275e-15f, r);
-  s = __sinf(r);
-  c = __cosf(r);
-}
-
+// The phase phi = float32(delta) * theta of magnitude up to ~2e5 rad is reduced by n * 2*pi with 2*pi split
+// into two float32 terms (each FMA product is exact; the third term of the split would contribute below
+// 2e-10 rad at these magnitudes), then sin.approx / cos.approx on [-pi, pi] (absolute error ~5e-7).
 __device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" :: "r"(d), "l"(gsrc));
@@ -173,7 +164,8 @@ struct TriSmem {
                                                             // copies of one token row hit distinct banks
   static constexpr int ARR = 8 * HEAD;                      // words per staged array (8 heads)
   static constexpr int STAGE_WORDS = 4 * ARR + 2 * 128;     // + scales: 2 x 32 x 8 halves = 2 x 128 words
-  static constexpr size_t bytes(int nh) { return (size_t)nh * TD_TILE_HALVES * 2 + 2 * STAGE_WORDS * 4; }
+  static constexpr int THETA_BYTES = 64 * 32 * 4;           // phase table, one copy per lane
+  static constexpr size_t bytes(int nh) { return (size_t)nh * TD_TILE_HALVES * 2 + 2 * STAGE_WORDS * 4 + THETA_BYTES; }
 };
 
 template <int F>
@@ -221,15 +213,16 @@ __global__ void __launch_bounds__(256, 2)
 tri_decode_kernel(TriArgs a) {
   using SM = TriSmem<F>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __shared__ float s_theta[64];
   const int hg = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
   const int hg0 = hg * 8;
   const int nh = (a.KVH - hg0 < 8) ? a.KVH - hg0 : 8;        // heads (= warps) of this CTA
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  if (threadIdx.x < 64) s_theta[threadIdx.x] = a.theta[threadIdx.x];
   __half* tile = reinterpret_cast<__half*>(smem_raw) + (size_t)warp * TD_TILE_HALVES;
   uint32_t* stage0 = reinterpret_cast<uint32_t*>(smem_raw + (size_t)nh * TD_TILE_HALVES * 2);
+  float* theta_rep = reinterpret_cast<float*>(stage0 + 2 * SM::STAGE_WORDS);      // [64][32 lanes]: conflict-free lookups
+  for (int i = threadIdx.x; i < 64 * 32; i += blockDim.x) theta_rep[i] = a.theta[i >> 5];
+  const float* const my_theta = theta_rep + lane;
   const int kvh = hg0 + warp;
   const int G = a.QH / a.KVH;
 
@@ -297,17 +290,24 @@ tri_decode_kernel(TriArgs a) {
       delta = __fsub_rn(kpos, qpos);
     }
     __half2* row = reinterpret_cast<__half2*>(tile + lane * TD_LD);
-    // ---- rotated keys into the dense tile ----
+    // ---- rotated keys into the dense tile: integer coefficients 2n - 15 (the factor scale / 15 goes
+    //      onto the scores), exponent trick instead of int-to-float conversions ----
     if (valid) {
-      const float ka = ks * 0.13333334f;       // (n / 7.5 - 1) * scale = n * (scale / 7.5) - scale
 #pragma unroll
-      for (int f = 0; f < F; ++f) {
-        const int sh = 8 * (f & 3);
-        const int id = (kiw[f >> 2] >> sh) & 63, pk = (kpw[f >> 2] >> sh) & 255;
-        const float k0 = __fmaf_rn((float)(pk >> 4), ka, -ks), k1 = __fmaf_rn((float)(pk & 15), ka, -ks);
-        float sn, cs;
-        sincos_reduced(__fmul_rn(delta, s_theta[id]), sn, cs);
-        row[id] = __floats2half2_rn(k0 * cs - k1 * sn, k1 * cs + k0 * sn);
+      for (int w = 0; w < SM::WORDS; ++w) {
+        const uint32_t hi2 = (kpw[w] >> 3) & 0x1E1E1E1Eu, lo2 = (kpw[w] << 1) & 0x1E1E1E1Eu;     // 2n per byte
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const uint32_t id = __byte_perm(kiw[w], 0u, 0x4440 + c) & 63u;
+          const float phi = __fmul_rn(delta, my_theta[id * 32]);
+          const float n = rintf(phi * 0.15915494309189535f);
+          float r = __fmaf_rn(-n, 6.2831854820251465f, phi);
+          r = __fmaf_rn(-n, -1.7484555314695172e-07f, r);
+          const float sn = __sinf(r), cs = __cosf(r);
+          const float k0 = __uint_as_float(__byte_perm(hi2, 0x4B000000u, 0x7440 + c)) - 8388623.0f;   // 8388608 + 2n - 8388623
+          const float k1 = __uint_as_float(__byte_perm(lo2, 0x4B000000u, 0x7440 + c)) - 8388623.0f;
+          row[id] = __floats2half2_rn(__fmaf_rn(k0, cs, -k1 * sn), __fmaf_rn(k1, cs, k0 * sn));
+        }
       }
     }
     __syncwarp();
@@ -324,17 +324,30 @@ tri_decode_kernel(TriArgs a) {
         mma16816_tri(sc[mt], af, bq[kk][0], bq[kk][1]);
       }
     }
+    {   // rows of the score tiles are tokens g, g+8 (+16): their key scales come from the lanes that hold them
+      const float ksc = ks * (1.0f / 15.0f);
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        const float ka = __shfl_sync(0xffffffffu, ksc, mt * 16 + g), kb = __shfl_sync(0xffffffffu, ksc, mt * 16 + g + 8);
+        sc[mt][0] *= ka; sc[mt][1] *= ka; sc[mt][2] *= kb; sc[mt][3] *= kb;
+      }
+    }
     __syncwarp();
-    // ---- take the keys out again, put the values in ----
+    // ---- take the keys out again, put the integer values in (the factor scale / 15 goes onto P) ----
     if (valid) {
 #pragma unroll
-      for (int f = 0; f < F; ++f) row[(kiw[f >> 2] >> (8 * (f & 3))) & 63] = __floats2half2_rn(0.f, 0.f);
-      const float va = vs * 0.13333334f;
+      for (int f = 0; f < F; ++f) row[__byte_perm(kiw[f >> 2], 0u, 0x4440 + (f & 3)) & 63u] = __floats2half2_rn(0.f, 0.f);
 #pragma unroll
-      for (int f = 0; f < F; ++f) {
-        const int sh = 8 * (f & 3);
-        const int idv = (viw[f >> 2] >> sh) & 63, pv = (vpw[f >> 2] >> sh) & 255;
-        row[idv] = __floats2half2_rn(__fmaf_rn((float)(pv >> 4), va, -vs), __fmaf_rn((float)(pv & 15), va, -vs));
+      for (int w = 0; w < SM::WORDS; ++w) {
+        const uint32_t hi2 = (vpw[w] >> 3) & 0x1E1E1E1Eu, lo2 = (vpw[w] << 1) & 0x1E1E1E1Eu;
+        const uint32_t t01 = __byte_perm(hi2, lo2, 0x5140), t23 = __byte_perm(hi2, lo2, 0x7362);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const uint32_t idv = __byte_perm(viw[w], 0u, 0x4440 + c) & 63u;
+          // halves 0x6400 | 2n = 1024 + 2n, minus 1039: 2n - 15, exactly
+          const uint32_t hb = __byte_perm(c < 2 ? t01 : t23, 0x64646464u, (c & 1) ? 0x4342 : 0x4140);
+          row[idv] = __hsub2(*reinterpret_cast<const __half2*>(&hb), __floats2half2_rn(1039.f, 1039.f));
+        }
       }
     }
     const int rem = s_end - s0;    // tokens of this tile that exist
@@ -375,8 +388,10 @@ tri_decode_kernel(TriArgs a) {
       const float p2 = ex2a(sc[mt][2] - mn0), p3 = ex2a(sc[mt][3] - mn1);
       l0 += p0 + p2;
       l1 += p1 + p3;
-      pb[mt][0] = movmatrix_trans_tri(pack_h2(p0, p1));
-      pb[mt][1] = movmatrix_trans_tri(pack_h2(p2, p3));
+      const float vsc = vs * (1.0f / 15.0f);        // 0 for lanes past the end
+      const float va = __shfl_sync(0xffffffffu, vsc, mt * 16 + g), vb = __shfl_sync(0xffffffffu, vsc, mt * 16 + g + 8);
+      pb[mt][0] = movmatrix_trans_tri(pack_h2(p0 * va, p1 * va));
+      pb[mt][1] = movmatrix_trans_tri(pack_h2(p2 * vb, p3 * vb));
     }
     __syncwarp();
     // ---- values: O^T[dims][q heads] += V^T P^T ----
@@ -392,263 +407,8 @@ tri_decode_kernel(TriArgs a) {
     __syncwarp();
     if (valid) {
 #pragma unroll
-      for (int f = 0; f < F; ++f) row[(viw[f >> 2] >> (8 * (f & 3))) & 63] = __floats2half2_rn(0.f, 0.f);
+      for (int f = 0; f < F; ++f) row[__byte_perm(viw[f >> 2], 0u, 0x4440 + (f & 3)) & 63u] = __floats2half2_rn(0.f, 0.f);
     }
-  }
-
-#pragma unroll
-  for (int off = 4; off < 32; off <<= 1) {
-    l0 += __shfl_xor_sync(0xffffffffu, l0, off);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, off);
-  }
-  const int part = split;
-#pragma unroll
-  for (int e = 0; e < 2; ++e) {
-    const int qg = 2 * t + e;
-    if (qg >= G) continue;
-    const int64_t rowi = (int64_t)b * a.QH + kvh * G + qg;
-    float* pa = a.part_acc + (rowi * a.num_parts + part) * 128;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {   // M-tile j: rows g, g+8 -> dims 16j+g, 16j+g+8
-      pa[16 * j + g] = o[j][e];
-      pa[16 * j + g + 8] = o[j][2 + e];
-    }
-    if (g == 0) {
-      a.part_ml[(rowi * a.num_parts + part) * 2] = e ? m1 : m0;
-      a.part_ml[(rowi * a.num_parts + part) * 2 + 1] = e ? l1 : l0;
-    }
-  }
-}
-
-// ---------------------------------------------------------------------------
-// decode step, second kernel: eight KV heads per CTA, no staging copies.
-//
-// A 32-token tile is handled in two kinds of phases separated by CTA barriers:
-//   * record phases - thread (warp w, lane l) owns (token 4w + l/8, head l%8): the eight heads of four
-//     tokens are 96 contiguous bytes per array, so a warp's record loads are plain coalesced global
-//     loads (prefetched one tile ahead into registers, no shared-memory staging).  The thread turns its
-//     record into integer coefficients 2n-15 (exact in fp16; the factors scale/15 are applied to the
-//     scores and to P instead), rotates the key pairs by the float32 phase of the reference, and scatters
-//     half2 values into the dense [32 tokens][128] fp16 tile of its head; afterwards it clears exactly the
-//     entries it wrote.
-//   * matrix phases - warp h owns head h: ldmatrix + mma.sync m16n8k16 over the dense tile, online softmax,
-//     as in tri_decode_kernel.
-// Integer conversions use exponent tricks (0x4B000000 | n, 0x6400 | n) instead of I2F, the phase table is
-// replicated per lane, the phase is reduced with a two-term 2*pi.
-// ---------------------------------------------------------------------------
-template <int F>
-struct Tri2Smem {
-  static constexpr int TILES = 8 * TD_TILE_HALVES * 2;       // bytes
-  static constexpr int THETA = 64 * 32 * 4;
-  static constexpr int SCALES = 2 * 32 * 8 * 4;
-  static constexpr int BYTES = TILES + THETA + SCALES;
-};
-
-template <int F>
-__global__ void __launch_bounds__(256, 2)
-tri_decode2_kernel(TriArgs a) {
-  constexpr int WORDS = F / 4;
-  using SM = Tri2Smem<F>;
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  __half* tiles = reinterpret_cast<__half*>(smem_raw);
-  float* theta_rep = reinterpret_cast<float*>(smem_raw + SM::TILES);                 // [64][32 lanes]
-  float* ksc_s = reinterpret_cast<float*>(smem_raw + SM::TILES + SM::THETA);         // [32 tokens][8 heads]: k scale / 15
-  float* vsc_s = ksc_s + 256;
-  const int hg = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
-  const int hg0 = hg * 8;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int g = lane >> 2, t = lane & 3;
-  const int G = a.QH / a.KVH;
-  for (int i = threadIdx.x; i < 64 * 32; i += 256) theta_rep[i] = a.theta[i >> 5];
-  {   // all tiles start (and are left after every use) all zero
-    uint4* z = reinterpret_cast<uint4*>(smem_raw);
-    for (int i = threadIdx.x; i < SM::TILES / 16; i += 256) z[i] = make_uint4(0, 0, 0, 0);
-  }
-
-  // ---- record role ----
-  const int r_tok = 4 * warp + (lane >> 3), r_head = lane & 7;
-  __half2* const r_row = reinterpret_cast<__half2*>(tiles + (size_t)r_head * TD_TILE_HALVES + r_tok * TD_LD);
-  const float* const my_theta = theta_rep + lane;
-  const float qpos = (float)(a.query_pos ? a.query_pos[b] : a.query_pos_default);
-
-  // ---- matrix role: warp = head ----
-  __half* tile = tiles + (size_t)warp * TD_TILE_HALVES;
-  const int kvh = hg0 + warp;
-  uint32_t bq[8][2];
-  {
-    const int qh = kvh * G + (g < G ? g : 0);
-    const int64_t base = (int64_t)b * a.q_sb + (int64_t)qh * a.q_sh;
-#pragma unroll
-    for (int kk = 0; kk < 8; ++kk) {
-      float f0 = load_as_float(a.query, a.q_dtype, base + 16 * kk + 2 * t) * a.premul;
-      float f1 = load_as_float(a.query, a.q_dtype, base + 16 * kk + 2 * t + 1) * a.premul;
-      float f2 = load_as_float(a.query, a.q_dtype, base + 16 * kk + 2 * t + 8) * a.premul;
-      float f3 = load_as_float(a.query, a.q_dtype, base + 16 * kk + 2 * t + 9) * a.premul;
-      if (g >= G) { f0 = f1 = f2 = f3 = 0.f; }
-      bq[kk][0] = pack_h2(f0, f1);
-      bq[kk][1] = pack_h2(f2, f3);
-    }
-  }
-  float o[8][4];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
-  float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
-
-  const int s_begin = split * a.tokens_per_split;
-  int s_end = s_begin + a.tokens_per_split;
-  if (s_end > a.S) s_end = a.S;
-  const int n_iter = (s_end - s_begin + 31) / 32;
-
-  // records of the tile being prefetched
-  uint32_t n_ki[WORDS], n_kp[WORDS], n_vi[WORDS], n_vp[WORDS];
-  float n_ks = 0.f, n_vs = 0.f, n_delta = 0.f;
-  bool n_valid = false;
-  auto prefetch = [&](int s0) {
-    const int s = s0 + r_tok;
-    n_valid = s < s_end;
-    if (n_valid) {
-      const int64_t rec = ((int64_t)b * a.S + s) * a.KVH + hg0 + r_head;
-      const uint32_t* pki = reinterpret_cast<const uint32_t*>(a.k_idx + rec * F);
-      const uint32_t* pkp = reinterpret_cast<const uint32_t*>(a.k_packed + rec * F);
-      const uint32_t* pvi = reinterpret_cast<const uint32_t*>(a.v_idx + rec * F);
-      const uint32_t* pvp = reinterpret_cast<const uint32_t*>(a.v_packed + rec * F);
-#pragma unroll
-      for (int w = 0; w < WORDS; ++w) { n_ki[w] = __ldg(pki + w); n_kp[w] = __ldg(pkp + w); n_vi[w] = __ldg(pvi + w); n_vp[w] = __ldg(pvp + w); }
-      n_ks = __half2float(a.k_scales[rec]);
-      n_vs = __half2float(a.v_scales[rec]);
-      const float kpos = (float)(a.key_positions ? a.key_positions[(int64_t)b * a.S + s] : a.key_pos_start + s);
-      n_delta = __fsub_rn(kpos, qpos);
-    }
-  };
-  prefetch(s_begin);
-  __syncthreads();          // tables and zeroed tiles are in place
-
-  uint32_t kiw[WORDS], kpw[WORDS], viw[WORDS], vpw[WORDS];
-  bool valid = false;
-  for (int it = 0; it < n_iter; ++it) {
-    const int s0 = s_begin + it * 32;
-    // ---- record phase 1: take the previous tile's values out, put this tile's rotated keys in ----
-    if (valid) {
-#pragma unroll
-      for (int f = 0; f < F; ++f) r_row[__byte_perm(viw[f >> 2], 0u, 0x4440 + (f & 3)) & 63u] = __floats2half2_rn(0.f, 0.f);
-    }
-    valid = n_valid;
-    const float ks = n_ks, vs = n_vs, delta = n_delta;
-#pragma unroll
-    for (int w = 0; w < WORDS; ++w) { kiw[w] = n_ki[w]; kpw[w] = n_kp[w]; viw[w] = n_vi[w]; vpw[w] = n_vp[w]; }
-    if (it + 1 < n_iter) prefetch(s0 + 32);
-    ksc_s[r_tok * 8 + r_head] = valid ? ks * (1.0f / 15.0f) : 0.f;
-    vsc_s[r_tok * 8 + r_head] = valid ? vs * (1.0f / 15.0f) : 0.f;
-    if (valid) {
-#pragma unroll
-      for (int w = 0; w < WORDS; ++w) {
-        const uint32_t hi2 = (kpw[w] >> 3) & 0x1E1E1E1Eu, lo2 = (kpw[w] << 1) & 0x1E1E1E1Eu;     // 2n per byte
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const uint32_t id = __byte_perm(kiw[w], 0u, 0x4440 + c) & 63u;
-          const float phi = __fmul_rn(delta, my_theta[id * 32]);
-          const float n = rintf(phi * 0.15915494309189535f);
-          float r = __fmaf_rn(-n, 6.2831854820251465f, phi);
-          r = __fmaf_rn(-n, -1.7484555314695172e-07f, r);
-          const float sn = __sinf(r), cs = __cosf(r);
-          // 8388608 + 2n as a float, minus 8388623: 2n - 15, exactly
-          const float k0 = __uint_as_float(__byte_perm(hi2, 0x4B000000u, 0x7440 + c)) - 8388623.0f;
-          const float k1 = __uint_as_float(__byte_perm(lo2, 0x4B000000u, 0x7440 + c)) - 8388623.0f;
-          r_row[id] = __floats2half2_rn(__fmaf_rn(k0, cs, -k1 * sn), __fmaf_rn(k1, cs, k0 * sn));
-        }
-      }
-    }
-    __syncthreads();
-
-    // ---- matrix phase 1: scores for the two 16-token halves, online softmax ----
-    float sc[2][4];
-#pragma unroll
-    for (int mt = 0; mt < 2; ++mt) {
-      sc[mt][0] = sc[mt][1] = sc[mt][2] = sc[mt][3] = 0.f;
-#pragma unroll
-      for (int kk = 0; kk < 8; ++kk) {
-        uint32_t af[4];
-        ldmatrix_x4(af, tile + (mt * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * TD_LD + kk * 16 + 8 * (lane >> 4));
-        mma16816_tri(sc[mt], af, bq[kk][0], bq[kk][1]);
-      }
-      const float ka = ksc_s[(mt * 16 + g) * 8 + warp], kb = ksc_s[(mt * 16 + g + 8) * 8 + warp];
-      sc[mt][0] *= ka; sc[mt][1] *= ka; sc[mt][2] *= kb; sc[mt][3] *= kb;
-    }
-    const int rem = s_end - s0;    // tokens of this tile that exist
-    if (a.scores_out != nullptr) {
-#pragma unroll
-      for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int tok = mt * 16 + g + 8 * (e >> 1), qg = 2 * t + (e & 1);
-          if (tok < rem && qg < G)
-            a.scores_out[((int64_t)b * a.QH + kvh * G + qg) * a.S + s0 + tok] = sc[mt][e] * 0.6931471805599453f;
-        }
-    }
-#pragma unroll
-    for (int mt = 0; mt < 2; ++mt) {
-      if (mt * 16 + g >= rem) { sc[mt][0] = -CUDART_INF_F; sc[mt][1] = -CUDART_INF_F; }
-      if (mt * 16 + g + 8 >= rem) { sc[mt][2] = -CUDART_INF_F; sc[mt][3] = -CUDART_INF_F; }
-    }
-    float mx0 = fmaxf(fmaxf(sc[0][0], sc[0][2]), fmaxf(sc[1][0], sc[1][2]));
-    float mx1 = fmaxf(fmaxf(sc[0][1], sc[0][3]), fmaxf(sc[1][1], sc[1][3]));
-#pragma unroll
-    for (int off = 4; off < 32; off <<= 1) {
-      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
-      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
-    }
-    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-    if (__any_sync(0xffffffffu, (mn0 != m0) | (mn1 != m1))) {
-      const float al0 = ex2a(m0 - mn0), al1 = ex2a(m1 - mn1);
-      l0 *= al0; l1 *= al1;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) { o[j][0] *= al0; o[j][1] *= al1; o[j][2] *= al0; o[j][3] *= al1; }
-      m0 = mn0; m1 = mn1;
-    }
-    uint32_t pb[2][2];
-#pragma unroll
-    for (int mt = 0; mt < 2; ++mt) {
-      const float p0 = ex2a(sc[mt][0] - mn0), p1 = ex2a(sc[mt][1] - mn1);
-      const float p2 = ex2a(sc[mt][2] - mn0), p3 = ex2a(sc[mt][3] - mn1);
-      l0 += p0 + p2;
-      l1 += p1 + p3;
-      const float va = vsc_s[(mt * 16 + g) * 8 + warp], vb = vsc_s[(mt * 16 + g + 8) * 8 + warp];   // 0 beyond the end
-      pb[mt][0] = movmatrix_trans_tri(pack_h2(p0 * va, p1 * va));
-      pb[mt][1] = movmatrix_trans_tri(pack_h2(p2 * vb, p3 * vb));
-    }
-    __syncthreads();
-
-    // ---- record phase 2: keys out, integer values in ----
-    if (valid) {
-#pragma unroll
-      for (int f = 0; f < F; ++f) r_row[__byte_perm(kiw[f >> 2], 0u, 0x4440 + (f & 3)) & 63u] = __floats2half2_rn(0.f, 0.f);
-#pragma unroll
-      for (int w = 0; w < WORDS; ++w) {
-        const uint32_t hi2 = (vpw[w] >> 3) & 0x1E1E1E1Eu, lo2 = (vpw[w] << 1) & 0x1E1E1E1Eu;
-        const uint32_t t01 = __byte_perm(hi2, lo2, 0x5140), t23 = __byte_perm(hi2, lo2, 0x7362);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const uint32_t id = __byte_perm(viw[w], 0u, 0x4440 + c) & 63u;
-          // halves 0x6400 | 2n = 1024 + 2n, minus 1039: 2n - 15, exactly
-          const uint32_t hb = __byte_perm(c < 2 ? t01 : t23, 0x64646464u, (c & 1) ? 0x4342 : 0x4140);
-          const __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&hb), __floats2half2_rn(1039.f, 1039.f));
-          r_row[id] = v;
-        }
-      }
-    }
-    __syncthreads();
-
-    // ---- matrix phase 2: O^T[dims][q heads] += V^T P^T ----
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-#pragma unroll
-      for (int mt = 0; mt < 2; ++mt) {
-        uint32_t af[4];
-        ldmatrix_x4_trans(af, tile + (mt * 16 + (lane & 7) + 8 * (lane >> 4)) * TD_LD + j * 16 + 8 * ((lane >> 3) & 1));
-        mma16816_tri(o[j], af, pb[mt][0], pb[mt][1]);
-      }
-    }
-    __syncthreads();
   }
 
 #pragma unroll
@@ -677,6 +437,13 @@ tri_decode2_kernel(TriArgs a) {
 
 static void tri_plan(int B, int QH, int S, int tps_in, int* tps, int* parts, size_t* off_ml, size_t* total) {
   int tp = tps_in > 0 ? tps_in : 1024;
+  if (tps_in <= 0) {     // short key ranges (a rank's share of a split context): smaller splits, so that the grid
+                         // still holds about four CTAs per SM; never below 128 tokens
+    long long want = ((long long)B * S + 591) / 592;
+    want = (want + 31) / 32 * 32;
+    if (want < 128) want = 128;
+    if (want < tp) tp = (int)want;
+  }
   if (tp > S) tp = S > 0 ? S : 1;
   tp = (tp + 31) / 32 * 32;
   const int splits = S > 0 ? (S + tp - 1) / tp : 1;
@@ -773,20 +540,6 @@ AKV_EXPORT int akv_tri_decode_step(const akv_tri_decode_params* p) {
     const int nh = p->num_kv_heads < 8 ? p->num_kv_heads : 8;
     dim3 grid((p->num_kv_heads + 7) / 8, parts, p->batch);
     cudaError_t e = cudaSuccess;
-    // eight KV heads per CTA and word-aligned records: the kernel without staging copies
-    static const bool no_v2 = getenv("AKV_TRI_V1") != nullptr;
-    const bool v2 = !no_v2 && p->num_kv_heads % 8 == 0 &&
-                    ((reinterpret_cast<uintptr_t>(p->k_indices) | reinterpret_cast<uintptr_t>(p->k_packed) |
-                      reinterpret_cast<uintptr_t>(p->v_indices) | reinterpret_cast<uintptr_t>(p->v_packed)) & 3) == 0;
-#define AKV_TRI2(FF)                                                                                 \
-    e = cudaFuncSetAttribute(tri_decode2_kernel<FF>, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
-                             Tri2Smem<FF>::BYTES);                                                        \
-    if (e == cudaSuccess) tri_decode2_kernel<FF><<<grid, 256, Tri2Smem<FF>::BYTES, st>>>(a);
-    if (v2) {
-      if (p->num_freqs == 8) { AKV_TRI2(8) } else if (p->num_freqs == 12) { AKV_TRI2(12) } else { AKV_TRI2(16) }
-      if (e != cudaSuccess) return fail((int)e, "tri decode: smem attribute: %s", cudaGetErrorString(e));
-      if (int rc = check_launch("tri_decode2_kernel")) return rc;
-    } else {
 #define AKV_TRI(FF)                                                                                  \
     e = cudaFuncSetAttribute(tri_decode_kernel<FF>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
                              (int)TriSmem<FF>::bytes(8));                                                \
@@ -795,8 +548,6 @@ AKV_EXPORT int akv_tri_decode_step(const akv_tri_decode_params* p) {
 #undef AKV_TRI
     if (e != cudaSuccess) return fail((int)e, "tri decode: smem attribute: %s", cudaGetErrorString(e));
     if (int rc = check_launch("tri_decode_kernel")) return rc;
-    }
-#undef AKV_TRI2
   }
   if (p->ev_kernel_stop) cudaEventRecord((cudaEvent_t)p->ev_kernel_stop, st);
   const int rows = p->batch * p->num_q_heads;

@@ -56,7 +56,9 @@ const char* akv_last_split_kernel(void);
  *          kept its tensor-memory columns.
  *   out[2] akv_tq_paged_attn / akv_tq_decode_step, out[3] akv_hybrid_paged_attn: 1 = a kernel that keeps
  *          tables at fixed shared-memory addresses found its window taken and returned without writing
- *          partials (the host checks the window before choosing such a kernel, so this stays 0).
+ *          partials (the host checks the window before choosing such a kernel, so this stays 0); for the
+ *          TMA-fed attention kernel 2 = a bounded wait on a copy barrier ran out.
+ *   out[4] akv_p2p_lse_merge: 1 = the bounded wait for the peers' partials ran out (a peer is late or gone).
  * A diagnostic call for health checks and tests, not part of a serving step. */
 int akv_device_status(int* out, int reset);
 
@@ -343,6 +345,39 @@ typedef struct akv_tri_decode_params {
 
 size_t akv_tri_decode_workspace_bytes(int batch, int num_q_heads, int seq_len, int tokens_per_split);
 int akv_tri_decode_step(const akv_tri_decode_params* params);
+
+/* ------------------------------------------------------------------------
+ * Cross-GPU merge of split-K partials over NVLink peer memory (no counterpart in the reference, which
+ * has no multi-device path; the merge arithmetic is that of fused_attention.py:513-527)
+ * ---------------------------------------------------------------------- */
+
+/* Every rank calls this with its partial local_raw [num_seqs*num_q_heads][head_dim+2] (m in log2 units, l,
+ * acc - the raw_out of akv_tq_paged_attn / akv_tri_decode_step).  The call copies the partial into slot
+ * `rank` of every rank's exchange buffer with peer stores, raises a flag word on every rank, waits
+ * (bounded, about a second) until all ranks' partials of this step have arrived locally, and merges them:
+ * out = R^T (acc / l) with `rotation`, acc / l without.  Three kernel launches, no collective library, no
+ * multimem; capturable in a CUDA graph (step counter and buffer half live in `state`).
+ *   peer_buffers  HOST array [world]: device pointer of each rank's exchange buffer of
+ *                 akv_p2p_exchange_bytes() bytes, 16-byte aligned, mapped on this device (entry `rank`
+ *                 is this rank's own buffer) - e.g. torch symmetric memory
+ *   peer_flags    HOST array [world]: device pointer of each rank's flag array, `world` uint32 words,
+ *                 zero before the first step
+ *   state         two local uint32 device words, zero before the first step
+ * All ranks must make the same sequence of calls.  A wait that runs out sets status word 4 of
+ * akv_device_status and the merge proceeds on whatever has arrived. */
+typedef struct akv_p2p_merge_params {
+  const float* local_raw;
+  int num_seqs, num_q_heads, head_dim;
+  int world, rank;
+  void* const* peer_buffers;
+  void* const* peer_flags;
+  unsigned int* state;
+  const float* rotation;             /* optional R, row-major */
+  void* out; int out_dtype; int64_t out_stride_seq, out_stride_head;
+  void* stream;
+} akv_p2p_merge_params;
+size_t akv_p2p_exchange_bytes(int world, int num_seqs, int num_q_heads, int head_dim);
+int akv_p2p_lse_merge(const akv_p2p_merge_params* params);
 
 #ifdef __cplusplus
 }

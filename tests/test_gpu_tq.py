@@ -618,7 +618,7 @@ def test_device_status_is_clean_and_reports_a_wait_that_gave_up():
     x = torch.randn(148 * 128 * 3, 128, generator=torch.Generator().manual_seed(3)).half().cuda()
     packed, norms = tq.encode(x)
     y = tq.decode(packed, norms)
-    assert _lib.device_status(reset=True) == {"tc_encode": 0, "tc_decode": 0, "attn_window": 0, "hybrid_window": 0}
+    assert not any(_lib.device_status(reset=True).values())
     try:
         _lib.check(L.akv_debug_tc_withhold(0, 1), "withhold")
         p2, n2 = tq.encode(x)
@@ -634,4 +634,4 @@ def test_device_status_is_clean_and_reports_a_wait_that_gave_up():
     p3, n3 = tq.encode(x)
     y3 = tq.decode(packed, norms)
     assert torch.equal(p3, packed) and torch.equal(n3, norms) and torch.equal(y3, y)
-    assert _lib.device_status() == {"tc_encode": 0, "tc_decode": 0, "attn_window": 0, "hybrid_window": 0}
+    assert not any(_lib.device_status().values())
