@@ -1943,7 +1943,10 @@ __device__ __forceinline__ void lowbit_v_fragments(uint32_t addr, uint32_t sh, u
   }
 }
 
-template <int BITS>
+// PAR (at most four query heads per KV head): the eight MMA columns of the value products are (query head,
+// dim parity) as in tq4_attn_tma_kernel, so the natural-order pair fragments of a token are complete A
+// registers (no transposes between tokens) and the accumulators are 16 registers instead of 32.
+template <int BITS, bool PAR>
 __global__ void __launch_bounds__(256, 1)
 tq_attn_streamk4_lowbit_kernel(AttnArgs a) {
   using LB = LowBit<BITS>;
@@ -2070,26 +2073,29 @@ tq_attn_streamk4_lowbit_kernel(AttnArgs a) {
   }
   const int n_off = (g * 8 + hl) * 4;
 
+  constexpr int NO = PAR ? 4 : 8;
+  const uint32_t selA = (g >> 2) ? 0x1044u : 0x4410u, selB = (g >> 2) ? 0x3244u : 0x4432u;   // PAR: P with a zero parity
   uint32_t bq[8][2];
-  float o[8][4];
+  float o[NO][4];
   SoftmaxState st{-CUDART_INF_F, -CUDART_INF_F, 0.f, 0.f};
   int seq_c = -1, c_base = 0, c_end = 0, ctx_c = 0;
   auto begin_seq = [&](int seq) {
     seq_c = seq;
     c_base = s_P[seq]; c_end = s_P[seq + 1];
     ctx_c = (int)load_ctx(a.context_lens, a.cl_dtype, seq, (int64_t)a.max_blocks_per_seq * a.block_size);
-    const float* qp = a.qrot + ((int64_t)seq * a.num_q_heads + h * G + (g < G ? g : 0)) * 128 + 32 * t;
+    const int qg = PAR ? (g & 3) : g;        // PAR: columns 4..7 repeat the query heads 0..3
+    const float* qp = a.qrot + ((int64_t)seq * a.num_q_heads + h * G + (qg < G ? qg : 0)) * 128 + 32 * t;
     float4 f[8];
 #pragma unroll
     for (int kk = 0; kk < 8; ++kk) f[kk] = *reinterpret_cast<const float4*>(qp + 4 * kk);
 #pragma unroll
     for (int kk = 0; kk < 8; ++kk) {
-      if (g >= G) f[kk] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (qg >= G) f[kk] = make_float4(0.f, 0.f, 0.f, 0.f);
       bq[kk][0] = pack_half2(f[kk].x, f[kk].y);
       bq[kk][1] = pack_half2(f[kk].z, f[kk].w);
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+    for (int j = 0; j < NO; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
     st = SoftmaxState{-CUDART_INF_F, -CUDART_INF_F, 0.f, 0.f};
   };
   auto end_seq = [&]() {
@@ -2102,14 +2108,22 @@ tq_attn_streamk4_lowbit_kernel(AttnArgs a) {
     const int part = b - a.sk[S + 2 + seq_c];
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
-      const int qg = 2 * t + e;
+      const int n = 2 * t + e, qg = PAR ? (n & 3) : n, ep = PAR ? (n >> 2) : 0;      // column -> (query head, dim parity)
       if (qg >= G) continue;
       const int64_t row = (int64_t)seq_c * a.num_q_heads + h * G + qg;
       float* pa = a.part_acc + (row * a.num_parts + part) * 128;
+      if constexpr (PAR) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        *reinterpret_cast<float2*>(pa + 16 * g + 2 * j) = make_float2(o[j][e], o[j][2 + e]);
-      if (g == 0) {
+        for (int mt = 0; mt < 4; ++mt) {                     // rows g, g + 8 of tile mt: pair slots 2mt, 2mt + 1 of dims 16g..
+          pa[16 * g + 4 * mt + ep] = o[mt][e];
+          pa[16 * g + 4 * mt + 2 + ep] = o[mt][2 + e];
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<float2*>(pa + 16 * g + 2 * j) = make_float2(o[j][e], o[j][2 + e]);
+      }
+      if (g == 0 && ep == 0) {
         a.part_ml[(row * a.num_parts + part) * 2] = e ? st.m1 : st.m0;
         a.part_ml[(row * a.num_parts + part) * 2 + 1] = e ? l1 : l0;
       }
@@ -2175,7 +2189,7 @@ tq_attn_streamk4_lowbit_kernel(AttnArgs a) {
       const float al0 = ex2_approx(st.m0 - mn0), al1 = ex2_approx(st.m1 - mn1);
       st.l0 *= al0; st.l1 *= al1;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { o[j][0] *= al0; o[j][1] *= al1; o[j][2] *= al0; o[j][3] *= al1; }
+      for (int j = 0; j < NO; ++j) { o[j][0] *= al0; o[j][1] *= al1; o[j][2] *= al0; o[j][3] *= al1; }
       st.m0 = mn0; st.m1 = mn1;
     }
     uint32_t pq[4][2];
@@ -2199,10 +2213,20 @@ tq_attn_streamk4_lowbit_kernel(AttnArgs a) {
       lowbit_v_fragments<BITS>(vb + j * LB::BLK + v_off[1], v_sh, lb4, lb8, n1);
       lowbit_v_fragments<BITS>(vb + j * LB::BLK + v_off[2], v_sh, lb4, lb8, n2);
       lowbit_v_fragments<BITS>(vb + j * LB::BLK + v_off[3], v_sh, lb4, lb8, n3);
+      if constexpr (PAR) {
+        const uint32_t b00 = __byte_perm(pq[j][0], 0u, selA), b01 = __byte_perm(pq[j][0], 0u, selB);   // tokens 2t, 2t+1
+        const uint32_t b10 = __byte_perm(pq[j][1], 0u, selA), b11 = __byte_perm(pq[j][1], 0u, selB);   // tokens 2t+8, 2t+9
 #pragma unroll
-      for (int m = 0; m < 8; ++m)
-        mma16816(o[m], __byte_perm(n0[m], n1[m], 0x5410), __byte_perm(n0[m], n1[m], 0x7632),
-                 __byte_perm(n2[m], n3[m], 0x5410), __byte_perm(n2[m], n3[m], 0x7632), pq[j][0], pq[j][1]);
+        for (int mt = 0; mt < 4; ++mt) {
+          mma16816(o[mt], n0[2 * mt], n0[2 * mt + 1], n1[2 * mt], n1[2 * mt + 1], b00, b01);
+          mma16816(o[mt], n2[2 * mt], n2[2 * mt + 1], n3[2 * mt], n3[2 * mt + 1], b10, b11);
+        }
+      } else {
+#pragma unroll
+        for (int m = 0; m < 8; ++m)
+          mma16816(o[m], __byte_perm(n0[m], n1[m], 0x5410), __byte_perm(n0[m], n1[m], 0x7632),
+                   __byte_perm(n2[m], n3[m], 0x5410), __byte_perm(n2[m], n3[m], 0x7632), pq[j][0], pq[j][1]);
+      }
     }
   }
   end_seq();
@@ -2369,8 +2393,10 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
   // used only where the dynamic window starts at or below the first of them (else: the per-split kernels)
   static const bool sk4_window_ok =
       dyn_smem_window_start(reinterpret_cast<const void*>(tq4_attn_streamk4_kernel)) <= SK4_PLAN &&
-      dyn_smem_window_start(reinterpret_cast<const void*>(tq_attn_streamk4_lowbit_kernel<3>)) <= SK4_PLAN &&
-      dyn_smem_window_start(reinterpret_cast<const void*>(tq_attn_streamk4_lowbit_kernel<2>)) <= SK4_PLAN;
+      dyn_smem_window_start(reinterpret_cast<const void*>(tq_attn_streamk4_lowbit_kernel<3, true>)) <= SK4_PLAN &&
+      dyn_smem_window_start(reinterpret_cast<const void*>(tq_attn_streamk4_lowbit_kernel<2, true>)) <= SK4_PLAN &&
+      dyn_smem_window_start(reinterpret_cast<const void*>(tq_attn_streamk4_lowbit_kernel<3, false>)) <= SK4_PLAN &&
+      dyn_smem_window_start(reinterpret_cast<const void*>(tq_attn_streamk4_lowbit_kernel<2, false>)) <= SK4_PLAN;
   const bool persist = ring && (!sk4 || sk4_window_ok) && plan.persist_shape && p->kp_stride_blk < lim && p->vp_stride_blk < lim &&
                        p->kn_stride_blk < lim && p->vn_stride_blk < lim && p->num_blocks < lim;
   int* sk = reinterpret_cast<int*>(ws + plan.off_sk);
@@ -2448,8 +2474,10 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
     } else if (persist && sk4) {
       a.num_parts = plan.sk_grid;
       merge_parts = a.num_parts;
+      const bool par = p->num_q_heads / p->num_kv_heads <= 4;
       auto kern = p->bits == 4 ? tq4_attn_streamk4_kernel
-                               : (p->bits == 3 ? tq_attn_streamk4_lowbit_kernel<3> : tq_attn_streamk4_lowbit_kernel<2>);
+                  : p->bits == 3 ? (par ? tq_attn_streamk4_lowbit_kernel<3, true> : tq_attn_streamk4_lowbit_kernel<3, false>)
+                                 : (par ? tq_attn_streamk4_lowbit_kernel<2, true> : tq_attn_streamk4_lowbit_kernel<2, false>);
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SK4_DYN_SMEM);
       if (e != cudaSuccess) return fail((int)e, "attention: smem attribute: %s", cudaGetErrorString(e));
       dim3 grid(plan.sk_grid, p->num_kv_heads / 8);

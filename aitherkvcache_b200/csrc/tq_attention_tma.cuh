@@ -138,14 +138,10 @@ tq4_attn_tma_kernel(AttnArgs a, const __grid_constant__ T4Maps maps) {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  for (int i = tid; i < 256 * 32; i += T4_THREADS) {
-    const int e = i >> 5, l = i & 31;
-    const uint32_t v = pack_half2(s_cent[e >> 4], s_cent[e & 15]);
-    asm volatile("st.shared.u32 [%0], %1;\n" :: "r"(SK_LUT + e * LUT_STRIDE + l * 4), "r"(v));
-  }
-  __syncthreads();
 
-  // this CTA's range of stages (plan written by the query-rotation launch)
+  // this CTA's range of stages (plan written by the query-rotation launch).  The first sequence of the
+  // range is the last one whose stage prefix is <= u_begin: found with one round of parallel loads and a
+  // ballot for up to 64 sequences, by bisection beyond that.
   const int* __restrict__ P = a.sk;                 // [0..S] stage prefix, [S] total, [S+1] stages per CTA
   const int T = P[S], chunk = P[S + 1];
   const int u_begin = b * chunk;
@@ -153,14 +149,26 @@ tq4_attn_tma_kernel(AttnArgs a, const __grid_constant__ T4Maps maps) {
   if (u_begin >= u_end) return;                      // uniform for the CTA
   const int n_it = u_end - u_begin;
   int seq0;
-  {
+  if (S <= 64) {
+    const int c0 = (lane < S && P[lane] <= u_begin) ? 1 : 0, c1 = (lane + 32 < S && P[lane + 32] <= u_begin) ? 1 : 0;
+    seq0 = __popc(__ballot_sync(0xffffffffu, c0)) + __popc(__ballot_sync(0xffffffffu, c1)) - 1;
+  } else {
     int lo = 0, hi = S - 1;
     while (lo < hi) {
       const int mid = (lo + hi + 1) >> 1;
       if (P[mid] <= u_begin) lo = mid; else hi = mid - 1;
     }
     seq0 = lo;
-    while (seq0 < S - 1 && u_begin >= P[seq0 + 1]) ++seq0;      // skip sequences without stages
+  }
+  while (seq0 < S - 1 && u_begin >= P[seq0 + 1]) ++seq0;      // skip sequences without stages
+
+  if (warp < 8) {        // the consumers fill the lookup table while the producer already issues copies
+    for (int i = tid; i < 256 * 32; i += 256) {
+      const int e = i >> 5, l = i & 31;
+      const uint32_t v = pack_half2(s_cent[e >> 4], s_cent[e & 15]);
+      asm volatile("st.shared.u32 [%0], %1;\n" :: "r"(SK_LUT + e * LUT_STRIDE + l * 4), "r"(v));
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");
   }
 
   if (warp == 8) {

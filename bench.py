@@ -54,6 +54,7 @@ WORKLOAD = ("paged decode attention, tq-t4nc cache: 16 seqs, ctx U[4096,32768] s
 # workload, from the ncu capture summarised under profiles/ (the file is named after the kernel).  A kernel
 # that is not listed here has no capture and its roofline.traffic is null.
 NCU_TRAFFIC_BYTES = {
+    "tq4_attn_tma_kernel": 281_556_000,         # 4.362 TB/s x 64.544 us
     "tq4_attn_streamk4_kernel": 281_600_000,
 }
 
@@ -397,20 +398,31 @@ def secondary_kernels(steps, warmup, dev):
 
 class SplitK:
     """One long-context batch whose key range is split over the ranks.  Every step: the local split-K
-    call writes this rank's un-normalised (m, l, acc) partials, one NCCL all-gather moves them, a local
-    kernel merges them by log-sum-exp.  With one rank the library's own call (kernel + in-library merge)
-    is the step.  Replicas of the local shard are cycled so that a step never finds its inputs in L2."""
+    call writes this rank's un-normalised (m, l, acc) partials, the partials are exchanged, a local
+    kernel merges them by log-sum-exp.  Two exchanges are measured: "p2p" - the library's own kernels
+    over NVLink peer memory (peer stores + flag words, akv_p2p_lse_merge) - and "nccl" - one
+    all_gather_into_tensor followed by akv_lse_merge.  With one rank the library's own call (kernel +
+    in-library merge) is the step.  Replicas of the local shard are cycled so that a step never finds its
+    inputs in L2."""
 
     def __init__(self, name, world, rank, dev, rows, local_calls, direct_calls, merge, shard_bytes, kv_tokens,
-                 workload):
+                 workload, rotation=None, out=None, batch=0):
         self.name, self.world, self.rank, self.dev = name, world, rank, dev
         self.local_calls, self.direct_calls, self.merge = local_calls, direct_calls, merge
         self.shard_bytes, self.kv_tokens, self.workload = shard_bytes, kv_tokens, workload
         self.raw = torch.empty(rows, D + 2, dtype=torch.float32, device=dev)
         self.parts = torch.empty(world, rows, D + 2, dtype=torch.float32, device=dev)
         self.nrep = len(local_calls)
+        self.rotation, self.out, self.batch = rotation, out, batch
+        self.exchange, self.exchange_error = None, None
+        if world > 1:
+            try:
+                from aitherkvcache_b200.parallel import PeerExchange
+                self.exchange = PeerExchange(batch, H_Q, D, dev)
+            except Exception as exc:      # noqa: BLE001 - symmetric memory is optional; NCCL remains
+                self.exchange_error = f"{type(exc).__name__}: {exc}"[:200]
 
-    def step(self, r, ev=None, marks=None):
+    def step(self, r, ev=None, marks=None, mode="nccl"):
         import torch.distributed as dist
         if self.world == 1:
             self.direct_calls[r % self.nrep](ev)
@@ -418,23 +430,46 @@ class SplitK:
         self.local_calls[r % self.nrep](self.raw, ev)
         if marks:
             marks[0].record()
+        if mode == "p2p":
+            from aitherkvcache_b200.parallel import p2p_merge_partials
+            p2p_merge_partials(self.exchange, self.raw, rotation=self.rotation, out=self.out)
+            if marks:
+                marks[1].record()
+            return
         dist.all_gather_into_tensor(self.parts, self.raw)
         if marks:
             marks[1].record()
         self.merge(self.parts)
 
     def measure(self, steps, warmup, barrier, allreduce_max):
+        if self.world == 1:
+            return self._measure_mode("single", steps, warmup, barrier, allreduce_max)
+        res = {"nccl": self._measure_mode("nccl", steps, warmup, barrier, allreduce_max)}
+        ref_out = self.out.clone()
+        if self.exchange is not None:
+            res["p2p"] = self._measure_mode("p2p", steps, warmup, barrier, allreduce_max)
+            res["p2p"]["max_abs_diff_vs_nccl"] = float((self.out.float() - ref_out.float()).abs().max())
+        best = min(res, key=lambda k: res[k]["ms_per_step"])
+        top = dict(res[best])
+        top["exchange"] = best
+        top["variants"] = {k: {kk: v[kk] for kk in ("ms_per_step", "value", "eager", "launch", "library_launches_per_step")
+                               if kk in v} for k, v in res.items()}
+        if self.exchange_error:
+            top["p2p_unavailable"] = self.exchange_error
+        return top
+
+    def _measure_mode(self, mode, steps, warmup, barrier, allreduce_max):
         from aitherkvcache_b200 import _lib
         L = _lib.lib()
         for i in range(warmup):
-            self.step(i)
+            self.step(i, mode=mode)
         # eager pass: per-phase times (events between the phases) and the split-K kernel alone
         ev = lambda: torch.cuda.Event(enable_timing=True)      # noqa: E731
         rec = [(ev(), ev(), ev(), ev(), ev(), ev()) for _ in range(steps)]
         barrier()
         for i, (a, k0, k1, m0, m1, b) in enumerate(rec):
             a.record()
-            self.step(i, (k0, k1), (m0, m1) if self.world > 1 else None)
+            self.step(i, (k0, k1), (m0, m1) if self.world > 1 else None, mode=mode)
             b.record()
         barrier()
         kernel_ms = float(np.mean([k0.elapsed_time(k1) for _, k0, k1, _, _, _ in rec]))
@@ -446,27 +481,27 @@ class SplitK:
         else:
             local_ms, gather_ms, merge_ms = eager_ms, 0.0, 0.0
         kernel_name = L.akv_last_split_kernel().decode()
-        # the step as a CUDA graph (NCCL's all-gather is captured with it), one graph per replica
-        mode, graphs = "cuda graph replay", []
+        # the step as a CUDA graph (the exchange is captured with it), one graph per replica
+        launch, graphs = "cuda graph replay", []
         n0 = L.akv_launch_count()
         try:
             side = torch.cuda.Stream(device=self.dev)
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
                 for r in range(self.nrep):
-                    self.step(r)
+                    self.step(r, mode=mode)
             torch.cuda.current_stream().wait_stream(side)
             n0 = L.akv_launch_count()
             for r in range(self.nrep):
                 gr = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(gr):
-                    self.step(r)
+                    self.step(r, mode=mode)
                 graphs.append(gr)
         except Exception as exc:      # noqa: BLE001 - keep measuring, but say how
-            graphs, mode = [], f"eager (graph capture failed: {type(exc).__name__}: {exc})"[:200]
+            graphs, launch = [], f"eager (graph capture failed: {type(exc).__name__}: {exc})"[:200]
             torch.cuda.synchronize()
         launches = (L.akv_launch_count() - n0) // max(1, len(graphs)) if graphs else None
-        run = (lambda i: graphs[i % len(graphs)].replay()) if graphs else self.step
+        run = (lambda i: graphs[i % len(graphs)].replay()) if graphs else (lambda i: self.step(i, mode=mode))
         for i in range(warmup):
             run(i)
         regions = []
@@ -485,11 +520,13 @@ class SplitK:
         ms = float(np.median(regions))
         peak, _ = peak_hbm()
         achieved = self.shard_bytes / (kernel_ms * 1e-3) / 1e9
-        return {"workload": self.workload, "n_gpus": self.world, "scaling": "strong", "launch": mode,
+        phases = ({"local_call_ms": local_ms, "exchange_and_merge_ms": gather_ms} if mode == "p2p" else
+                  {"local_call_ms": local_ms, "all_gather_ms": gather_ms, "merge_ms": merge_ms})
+        return {"workload": self.workload, "n_gpus": self.world, "scaling": "strong", "launch": launch,
                 "ms_per_step": ms, "ms_per_step_min": float(min(regions)), "ms_per_step_max": float(max(regions)),
                 "value": self.kv_tokens / (ms * 1e-3), "unit": UNIT, "kv_tokens_per_step": self.kv_tokens,
-                "eager": {"ms_per_step": eager_ms, "local_call_ms": local_ms, "all_gather_ms": gather_ms,
-                          "merge_ms": merge_ms, "note": "max over ranks of per-rank means; CUDA events between the phases"},
+                "eager": dict(phases, ms_per_step=eager_ms,
+                              note="max over ranks of per-rank means; CUDA events between the phases"),
                 "kernel": kernel_name, "kernel_ms": kernel_ms, "library_launches_per_step": launches,
                 "replicas_cycled": self.nrep, "shard_bytes_per_rank": self.shard_bytes,
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -527,7 +564,8 @@ def splitk_tri(world, rank, dev):
                                                  query_pos_default=S, kernel_events=ev)) for k, v in reps]
     direct = [(lambda ev, k=k, v=v: tri._run(q, k, v, None, None, out=out, kernel_events=ev)) for k, v in reps]
     return SplitK("tri128k", world, rank, dev, B * H_Q, local, direct,
-                  lambda parts: merge_partials(parts, B, H_Q, D, out=out), shard_bytes, B * S,
+                  lambda parts: merge_partials(parts, B, H_Q, D, out=out), shard_bytes, B * S, rotation=None, out=out,
+                  batch=B, workload=
                   "TriAttention decode_step: batch 8, 131072 keys (positions 0..131071, query at 131072), F=12 int4 "
                   "coefficients, 32Q/8KV heads, head_dim 128, rope_base 1e6, pre-RoPE keys with shuffled exp(-i/16) "
                   "pair scales; key range split over the ranks"), out
@@ -570,6 +608,7 @@ def splitk_tq4(world, rank, dev):
               for c in reps]
     return SplitK("tq4_128k", world, rank, dev, B * H_Q, local, direct,
                   lambda parts: merge_partials(parts, B, H_Q, D, rotation=tq.rotation, out=out), shard_bytes, B * S,
+                  rotation=tq.rotation, out=out, batch=B, workload=
                   "tq-t4nc paged decode attention: 8 sequences x 131072 tokens, 32Q/8KV heads, head_dim 128, "
                   "block_size 16, permuted block tables; each sequence's block range split over the ranks"), out
 

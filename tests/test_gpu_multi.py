@@ -64,7 +64,38 @@ def _worker(rank, world, port, results):
             cl_l.append(b - a)
         out2 = tq_paged_attention_sharded(attn, q2, kp, kn, vp, vn, bt_l.to(dev),
                                           torch.tensor(cl_l, dtype=torch.int32, device=dev))
-        results[rank] = (err_tri, float((out2.float() - full2.float()).abs().max()))
+        # --- the same merges over peer memory instead of NCCL: three steps (both buffer halves), then the
+        #     step captured in a CUDA graph and replayed; equal to the NCCL route bit for bit ---
+        from aitherkvcache_b200 import _lib
+        from aitherkvcache_b200.parallel import PeerExchange, p2p_merge_partials
+        ex = PeerExchange(2, QH, 128, dev)
+        raw = torch.empty(2 * QH, 130, dtype=torch.float32, device=dev)
+        p2p_out = torch.empty_like(full2)
+        err_p2p = 0.0
+        for step in range(3):
+            attn.forward(q2 * (1.0 + 0.25 * step), kp, kn, vp, vn, bt_l.to(dev),
+                         torch.tensor(cl_l, dtype=torch.int32, device=dev), raw_out=raw)
+            p2p_merge_partials(ex, raw, rotation=attn.rotation, out=p2p_out)
+            want = tq_paged_attention_sharded(attn, q2 * (1.0 + 0.25 * step), kp, kn, vp, vn, bt_l.to(dev),
+                                              torch.tensor(cl_l, dtype=torch.int32, device=dev))
+            err_p2p = max(err_p2p, float((p2p_out.float() - want.float()).abs().max()))
+        bt_dev, cl_dev = bt_l.to(dev), torch.tensor(cl_l, dtype=torch.int32, device=dev)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            attn.forward(q2, kp, kn, vp, vn, bt_dev, cl_dev, raw_out=raw)
+            p2p_merge_partials(ex, raw, rotation=attn.rotation, out=p2p_out)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            attn.forward(q2, kp, kn, vp, vn, bt_dev, cl_dev, raw_out=raw)
+            p2p_merge_partials(ex, raw, rotation=attn.rotation, out=p2p_out)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        err_p2p = max(err_p2p, float((p2p_out.float() - out2.float()).abs().max()))
+        status = _lib.device_status()
+        results[rank] = (err_tri, float((out2.float() - full2.float()).abs().max()), err_p2p, status["p2p"])
     finally:
         dist.destroy_process_group()
 
@@ -75,5 +106,6 @@ def test_two_gpu_split_k_matches_single_gpu():
     results = mp.Manager().dict()
     mp.spawn(_worker, args=(2, _free_port(), results), nprocs=2, join=True)
     assert len(results) == 2
-    for err_tri, err_tq in results.values():
+    for err_tri, err_tq, err_p2p, p2p_status in results.values():
         assert err_tri < 1e-4 and err_tq < 2e-3
+        assert err_p2p == 0.0 and p2p_status == 0
