@@ -2455,9 +2455,13 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
   // 4-bit codes, at most four query heads per KV head, cache strides a tensor map can describe: the kernel
   // with the TMA-fed ring (tensor maps cover the caller's cache on this GPU only)
   static const bool no_tma = getenv("AKV_NO_TMA") != nullptr;
-  static const bool tma_window_ok = dyn_smem_window_start(reinterpret_cast<const void*>(tq4_attn_tma_kernel)) <= T4_BAR;
+  static const bool tma_window_ok =
+      dyn_smem_window_start(reinterpret_cast<const void*>(tq_attn_tma_kernel<4>)) <= T4_BAR &&
+      dyn_smem_window_start(reinterpret_cast<const void*>(tq_attn_tma_kernel<3>)) <= T4_BAR &&
+      dyn_smem_window_start(reinterpret_cast<const void*>(tq_attn_tma_kernel<2>)) <= T4_BAR;
+  static const bool no_tma_lowbit = getenv("AKV_NO_TMA_LOWBIT") != nullptr;
   T4Maps maps;
-  const bool tma = persist && sk4 && !no_tma && tma_window_ok && p->bits == 4 && p->max_blocks_per_seq > 0 &&
+  const bool tma = persist && sk4 && !no_tma && tma_window_ok && (p->bits == 4 || !no_tma_lowbit) && p->max_blocks_per_seq > 0 &&
                    p->num_q_heads / p->num_kv_heads <= 4 && p->kp_stride_pos % 16 == 0 && p->vp_stride_pos % 16 == 0 &&
                    p->kp_stride_blk % 16 == 0 && p->vp_stride_blk % 16 == 0 && t4_make_maps(a, &maps);
 
@@ -2466,11 +2470,12 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
     if (tma) {
       a.num_parts = plan.sk_grid;
       merge_parts = a.num_parts;
-      cudaError_t e = cudaFuncSetAttribute(tq4_attn_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T4_DYN_SMEM);
+      auto kern = p->bits == 4 ? tq_attn_tma_kernel<4> : (p->bits == 3 ? tq_attn_tma_kernel<3> : tq_attn_tma_kernel<2>);
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T4_DYN_SMEM);
       if (e != cudaSuccess) return fail((int)e, "attention: smem attribute: %s", cudaGetErrorString(e));
       dim3 grid(plan.sk_grid, p->num_kv_heads / 8);
-      tq4_attn_tma_kernel<<<grid, T4_THREADS, T4_DYN_SMEM, st>>>(a, maps);
-      if (int rc = check_launch("tq4_attn_tma_kernel")) return rc;
+      kern<<<grid, T4_THREADS, T4_DYN_SMEM, st>>>(a, maps);
+      if (int rc = check_launch(p->bits == 4 ? "tq4_attn_tma_kernel" : "tq_lowbit_attn_tma_kernel")) return rc;
     } else if (persist && sk4) {
       a.num_parts = plan.sk_grid;
       merge_parts = a.num_parts;

@@ -116,8 +116,14 @@ __device__ __forceinline__ void t4_scores(uint32_t lanebase, const uint32_t (&bq
   }
 }
 
+// BITS = 4: the layouts above.  BITS = 3, 2 (48 / 32 packed bytes per token and head): K and V codes both as
+// [head][token][PD] boxes without swizzle, the lookup tables and the natural-order fragment helpers of the
+// low-bit kernels (lowbit_k_fragments, lowbit_v_fragments); block slots keep their 8 KB spacing.
+template <int BITS>
 __global__ void __launch_bounds__(T4_THREADS, 1)
-tq4_attn_tma_kernel(AttnArgs a, const __grid_constant__ T4Maps maps) {
+tq_attn_tma_kernel(AttnArgs a, const __grid_constant__ T4Maps maps) {
+  constexpr int PD = 16 * BITS;                       // packed bytes per (token, head)
+  constexpr uint32_t BLOCK_TX = 8 * 16 * PD + 512;    // bytes of one block's codes and norms (one side)
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ float s_cent[16];
   const uint32_t dyn0 = (uint32_t)__cvta_generic_to_shared(smem);
@@ -128,7 +134,7 @@ tq4_attn_tma_kernel(AttnArgs a, const __grid_constant__ T4Maps maps) {
     if (tid == 0) g_attn_window_status = 1;
     return;
   }
-  if (tid < 16) s_cent[tid] = a.centroids[tid];
+  if (tid < 16) s_cent[tid] = tid < (1 << BITS) ? a.centroids[tid] : 0.f;
   if (tid == 0) {
     asm volatile("st.shared.u32 [%0], %1;" :: "r"(T4_FAILED), "r"(0u) : "memory");
 #pragma unroll
@@ -163,10 +169,25 @@ tq4_attn_tma_kernel(AttnArgs a, const __grid_constant__ T4Maps maps) {
   while (seq0 < S - 1 && u_begin >= P[seq0 + 1]) ++seq0;      // skip sequences without stages
 
   if (warp < 8) {        // the consumers fill the lookup table while the producer already issues copies
-    for (int i = tid; i < 256 * 32; i += 256) {
-      const int e = i >> 5, l = i & 31;
-      const uint32_t v = pack_half2(s_cent[e >> 4], s_cent[e & 15]);
-      asm volatile("st.shared.u32 [%0], %1;\n" :: "r"(SK_LUT + e * LUT_STRIDE + l * 4), "r"(v));
+    if constexpr (BITS == 4) {          // byte -> half2(c[hi nibble], c[lo nibble])
+      for (int i = tid; i < 256 * 32; i += 256) {
+        const int e = i >> 5, l = i & 31;
+        const uint32_t v = pack_half2(s_cent[e >> 4], s_cent[e & 15]);
+        asm volatile("st.shared.u32 [%0], %1;\n" :: "r"(SK_LUT + e * LUT_STRIDE + l * 4), "r"(v));
+      }
+    } else if constexpr (BITS == 3) {   // 6 bits -> half2(c[hi 3 bits], c[lo 3 bits])
+      for (int i = tid; i < 64 * 32; i += 256) {
+        const int e = i >> 5, l = i & 31;
+        const uint32_t v = pack_half2(s_cent[e >> 3], s_cent[e & 7]);
+        asm volatile("st.shared.u32 [%0], %1;\n" :: "r"(SK_LUT + e * LUT3_STRIDE + l * 4), "r"(v));
+      }
+    } else {                            // byte -> four halves
+      for (int i = tid; i < 256 * 32; i += 256) {
+        const int e = i >> 5, l = i & 31;
+        const uint32_t v0 = pack_half2(s_cent[e >> 6], s_cent[(e >> 4) & 3]);
+        const uint32_t v1 = pack_half2(s_cent[(e >> 2) & 3], s_cent[e & 3]);
+        asm volatile("st.shared.v2.u32 [%0], {%1,%2};\n" :: "r"(SK_LUT + e * LUT_STRIDE + l * 8), "r"(v0), "r"(v1));
+      }
     }
     asm volatile("bar.sync 1, 256;" ::: "memory");
   }
@@ -199,7 +220,7 @@ tq4_attn_tma_kernel(AttnArgs a, const __grid_constant__ T4Maps maps) {
       if (it >= 2) t4_wait(T4_BAR + 32 + 8 * slot, par);             // K slot handed back
       if (lane < 4) {
         if (lane < n_has) {
-          t4_arrive_tx(fullK, 8192 + 512);
+          t4_arrive_tx(fullK, BLOCK_TX);
           t4_tma4(k_dst, &maps.k, 0, 0, hg * 8, pb, fullK);
           t4_tma3(kn_dst, &maps.kn, hg * 8, 0, pb, fullK);
         } else {
@@ -209,8 +230,8 @@ tq4_attn_tma_kernel(AttnArgs a, const __grid_constant__ T4Maps maps) {
       if (it >= 2) t4_wait(T4_BAR + 48 + 8 * slot, par);             // V slot handed back
       if (lane < 4) {
         if (lane < n_has) {
-          t4_arrive_tx(fullV, 8192 + 512);
-          t4_tma4(v_dst, &maps.v, 0, 0, hg * 4, pb, fullV);
+          t4_arrive_tx(fullV, BLOCK_TX);
+          t4_tma4(v_dst, &maps.v, 0, 0, BITS == 4 ? hg * 4 : hg * 8, pb, fullV);
           t4_tma3(vn_dst, &maps.vn, hg * 8, 0, pb, fullV);
         } else {
           t4_arrive(fullV);
@@ -224,14 +245,20 @@ tq4_attn_tma_kernel(AttnArgs a, const __grid_constant__ T4Maps maps) {
   const int g = lane >> 2, t = lane & 3;
   const int hl = warp, h = hg * 8 + hl;
   const int G = a.num_q_heads / a.num_kv_heads;       // <= 4 here
-  const uint32_t lanebase = SK_LUT | (lane * 4);
-  const uint32_t k_off = hl * 1024 + g * 64 + 16 * t;
+  const uint32_t lanebase = SK_LUT | (lane * 4), lb8 = SK_LUT | (lane * 8);
+  const uint32_t k_off = hl * (16 * PD) + g * PD + 4 * BITS * t;
   uint32_t v_off[4];
+  const uint32_t v_byte = 2 * BITS * g;               // low-bit: the thread's 2*BITS value bytes inside a token's PD
+  const uint32_t v_sh = BITS == 3 ? 8u * (v_byte & 3u) : 0u;
   {
     const int toks[4] = {2 * t, 2 * t + 1, 2 * t + 8, 2 * t + 9};
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-      v_off[i] = (hl >> 1) * 2048 + toks[i] * 128 + ((((hl & 1) * 4 + (g >> 1)) ^ (toks[i] & 7)) << 4) + (g & 1) * 8;
+    for (int i = 0; i < 4; ++i) {
+      if constexpr (BITS == 4)
+        v_off[i] = (hl >> 1) * 2048 + toks[i] * 128 + ((((hl & 1) * 4 + (g >> 1)) ^ (toks[i] & 7)) << 4) + (g & 1) * 8;
+      else
+        v_off[i] = hl * (16 * PD) + toks[i] * PD + (BITS == 3 ? (v_byte & ~3u) : v_byte);
+    }
   }
   const uint32_t n_off = (g * 8 + hl) * 4;            // norm of token g; token g + 8 is 256 bytes further
   // B operand of the value products: column g = (query head g & 3, dim parity g >> 2)
@@ -298,7 +325,22 @@ tq4_attn_tma_kernel(AttnArgs a, const __grid_constant__ T4Maps maps) {
       const int rem = ctx_c - 64 * (u_begin + it - c_base);
       float s[4][4];
       t4_wait(T4_BAR + 8 * slot, par);                       // K codes and norms of the stage have landed
-      t4_scores(lanebase, bq, kb + k_off, nb_ + n_off, s);
+      if constexpr (BITS == 4) {
+        t4_scores(lanebase, bq, kb + k_off, nb_ + n_off, s);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t na[16], nb2[16];
+          lowbit_k_fragments<BITS>(kb + j * 8192 + k_off, lanebase, lb8, na);
+          lowbit_k_fragments<BITS>(kb + j * 8192 + k_off + 8 * PD, lanebase, lb8, nb2);
+          mma16816_zero(s[j], na[0], nb2[0], na[1], nb2[1], bq[0][0], bq[0][1]);
+#pragma unroll
+          for (int kk = 1; kk < 8; ++kk)
+            mma16816(s[j], na[2 * kk], nb2[2 * kk], na[2 * kk + 1], nb2[2 * kk + 1], bq[kk][0], bq[kk][1]);
+          const float nkA = __uint_as_float(lds32(nb_ + n_off + j * 512)), nkB = __uint_as_float(lds32(nb_ + n_off + j * 512 + 256));
+          s[j][0] *= nkA; s[j][1] *= nkA; s[j][2] *= nkB; s[j][3] *= nkB;
+        }
+      }
       __syncwarp();
       if (lane == 0) t4_arrive(T4_BAR + 32 + 8 * slot);      // K slot back to the producer
       t4_wait(T4_BAR + 16 + 8 * slot, par);                  // V codes and norms
@@ -351,6 +393,21 @@ tq4_attn_tma_kernel(AttnArgs a, const __grid_constant__ T4Maps maps) {
       st.l0 += ls0;
       st.l1 += ls1;
       constexpr lut_t lut = 0;
+      if constexpr (BITS != 4) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t n0[8], n1[8], n2[8], n3[8];
+          lowbit_v_fragments<BITS>(vb + j * 8192 + v_off[0], v_sh, lanebase, lb8, n0);
+          lowbit_v_fragments<BITS>(vb + j * 8192 + v_off[1], v_sh, lanebase, lb8, n1);
+          lowbit_v_fragments<BITS>(vb + j * 8192 + v_off[2], v_sh, lanebase, lb8, n2);
+          lowbit_v_fragments<BITS>(vb + j * 8192 + v_off[3], v_sh, lanebase, lb8, n3);
+#pragma unroll
+          for (int mt = 0; mt < 4; ++mt) {
+            mma16816(o[mt], n0[2 * mt], n0[2 * mt + 1], n1[2 * mt], n1[2 * mt + 1], pb[j][0][0], pb[j][0][1]);
+            mma16816(o[mt], n2[2 * mt], n2[2 * mt + 1], n3[2 * mt], n3[2 * mt + 1], pb[j][1][0], pb[j][1][1]);
+          }
+        }
+      } else {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         uint2 vv[4];
@@ -369,6 +426,7 @@ tq4_attn_tma_kernel(AttnArgs a, const __grid_constant__ T4Maps maps) {
           mma16816(o[2 * hf + 1], lut4<2>(lut, w2, lanebase), lut4<3>(lut, w2, lanebase), lut4<2>(lut, w3, lanebase),
                    lut4<3>(lut, w3, lanebase), pb[j][1][0], pb[j][1][1]);
         }
+      }
       }
       __syncwarp();
       if (lane == 0) t4_arrive(T4_BAR + 48 + 8 * slot);      // V slot back to the producer
@@ -405,27 +463,35 @@ static akv_encode_tiled_fn t4_encoder() {
 // Maps for one (cache, strides) combination; the last one built is kept, a serving loop asks for the
 // same one at every step.  False: the layout cannot be described (the caller takes another kernel).
 static bool t4_make_maps(const AttnArgs& p, T4Maps* out) {
-  struct Key { int64_t v[18]; };      // pointers, strides, sizes: eight-byte fields only, so memcmp sees no padding
+  const int pd = 16 * p.bits;
+  struct Key { int64_t v[19]; };      // pointers, strides, sizes: eight-byte fields only, so memcmp sees no padding
   static thread_local Key last{};
   static thread_local T4Maps last_maps;
   static thread_local bool have = false;
   const Key key{{(int64_t)(uintptr_t)p.k_packed, (int64_t)(uintptr_t)p.v_packed, (int64_t)(uintptr_t)p.k_norms,
                  (int64_t)(uintptr_t)p.v_norms, p.kp_sb, p.kp_sp, p.kp_sh, p.vp_sb, p.vp_sp, p.vp_sh, p.kn_sb, p.kn_sp,
-                 p.kn_sh, p.vn_sb, p.vn_sp, p.vn_sh, p.num_blocks, (int64_t)p.num_kv_heads}};
+                 p.kn_sh, p.vn_sb, p.vn_sp, p.vn_sh, p.num_blocks, (int64_t)p.num_kv_heads, (int64_t)p.bits}};
   if (have && memcmp(&key, &last, sizeof(Key)) == 0) { *out = last_maps; return true; }
   akv_encode_tiled_fn enc = t4_encoder();
   if (enc == nullptr) return false;
   const cuuint32_t ones[4] = {1, 1, 1, 1};
   T4Maps m;
-  {   // K codes: (64 bytes, 16 tokens, heads, blocks); a box holds eight heads of one block as [head][token][64]
-    const cuuint64_t dims[4] = {64, 16, (cuuint64_t)p.num_kv_heads, (cuuint64_t)p.num_blocks};
+  {   // K codes: (pd bytes, 16 tokens, heads, blocks); a box holds eight heads of one block as [head][token][pd]
+    const cuuint64_t dims[4] = {(cuuint64_t)pd, 16, (cuuint64_t)p.num_kv_heads, (cuuint64_t)p.num_blocks};
     const cuuint64_t strides[3] = {(cuuint64_t)p.kp_sp, (cuuint64_t)p.kp_sh, (cuuint64_t)p.kp_sb};
-    const cuuint32_t box[4] = {64, 16, 8, 1};
+    const cuuint32_t box[4] = {(cuuint32_t)pd, 16, 8, 1};
     if (enc(&m.k, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<uint8_t*>(p.k_packed), dims, strides, box, ones,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return false;
   }
-  {   // V codes: (128 bytes = a head pair, 16 tokens, head pairs, blocks), 128-byte swizzle
+  if (p.bits != 4) {   // low-bit V codes: the K layout
+    const cuuint64_t dims[4] = {(cuuint64_t)pd, 16, (cuuint64_t)p.num_kv_heads, (cuuint64_t)p.num_blocks};
+    const cuuint64_t strides[3] = {(cuuint64_t)p.vp_sp, (cuuint64_t)p.vp_sh, (cuuint64_t)p.vp_sb};
+    const cuuint32_t box[4] = {(cuuint32_t)pd, 16, 8, 1};
+    if (enc(&m.v, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<uint8_t*>(p.v_packed), dims, strides, box, ones,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return false;
+  } else {   // V codes: (128 bytes = a head pair, 16 tokens, head pairs, blocks), 128-byte swizzle
     const cuuint64_t dims[4] = {128, 16, (cuuint64_t)(p.num_kv_heads / 2), (cuuint64_t)p.num_blocks};
     const cuuint64_t strides[3] = {(cuuint64_t)p.vp_sp, (cuuint64_t)(2 * p.vp_sh), (cuuint64_t)p.vp_sb};
     const cuuint32_t box[4] = {128, 16, 4, 1};
