@@ -134,6 +134,9 @@ class TriDecodeParams(C.Structure):
         ("stream", c_vp),
         ("ev_kernel_start", c_vp), ("ev_kernel_stop", c_vp),
         ("scores_out", c_vp),
+        ("block_tables", c_vp), ("bt_dtype", c_int), ("bt_stride_batch", c_i64),
+        ("block_size", c_int), ("num_blocks", c_i64),
+        ("context_lens", c_vp), ("cl_dtype", c_int),
     ]
 
 

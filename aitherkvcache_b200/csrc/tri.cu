@@ -103,7 +103,21 @@ struct TriArgs {
   float* part_acc;                // [B*QH][NP][128]
   float* part_ml;                 // [B*QH][NP][2]
   float* scores_out;              // optional [B][QH][S] pre-softmax logits (natural units)
+  // paged mode (block_tables != nullptr): the arrays are [num_blocks][block_size][KVH]...; token s of batch b
+  // lives in physical block block_tables[b][s / block_size], slot s % block_size; S = table width * block_size
+  const void* block_tables; int bt_dtype; int64_t bt_stride;
+  int block_size; int64_t num_blocks;
+  const void* context_lens; int cl_dtype;      // optional [B]: tokens of each batch element (clamped to S)
 };
+
+// Row of (batch b, token s) in the record arrays, before the head index.
+__device__ __forceinline__ int64_t tri_token_row(const TriArgs& a, int b, int s) {
+  if (a.block_tables == nullptr) return (int64_t)b * a.S + s;
+  const int blk = s / a.block_size;
+  int64_t phys = load_index(a.block_tables, a.bt_dtype, (int64_t)b * a.bt_stride + blk);
+  phys = phys < 0 ? 0 : (phys >= a.num_blocks ? a.num_blocks - 1 : phys);
+  return phys * a.block_size + (s - blk * a.block_size);
+}
 
 constexpr int TD_LD = 136;                       // halves per row of the dense tiles (272 B: conflict-free ldmatrix)
 constexpr int TD_TILE_HALVES = 32 * TD_LD;
@@ -179,7 +193,7 @@ __device__ __forceinline__ void tri_stage_load(const TriArgs& a, uint32_t* stage
     const int tok = i / row_words, j = i - tok * row_words;
     if (s0 + tok >= s_end) continue;
     const int head = j / SM::WORDS, wj = j - head * SM::WORDS;
-    const int64_t g_off = (((int64_t)b * a.S + s0 + tok) * a.KVH + hg0) * F + 4 * j;
+    const int64_t g_off = (tri_token_row(a, b, s0 + tok) * a.KVH + hg0) * F + 4 * j;
     const int s_off = head * SM::HEAD + tok * SM::WORDS + wj;
 #pragma unroll
     for (int arr = 0; arr < 4; ++arr) cp_async4(stage + arr * SM::ARR + s_off, srcs[arr] + g_off);
@@ -193,7 +207,7 @@ __device__ __forceinline__ void tri_stage_load(const TriArgs& a, uint32_t* stage
     for (int i = threadIdx.x; i < 32 * hp; i += blockDim.x) {
       const int tok = i / hp, pr = i - tok * hp;
       if (s0 + tok >= s_end) continue;
-      const int64_t rec = ((int64_t)b * a.S + s0 + tok) * a.KVH + hg0 + 2 * pr;
+      const int64_t rec = tri_token_row(a, b, s0 + tok) * a.KVH + hg0 + 2 * pr;
       cp_async4(sk + tok * 8 + 2 * pr, a.k_scales + rec);
       cp_async4(sv + tok * 8 + 2 * pr, a.v_scales + rec);
     }
@@ -201,7 +215,7 @@ __device__ __forceinline__ void tri_stage_load(const TriArgs& a, uint32_t* stage
     for (int i = threadIdx.x; i < 32 * nh; i += blockDim.x) {
       const int tok = i / nh, head = i - tok * nh;
       if (s0 + tok >= s_end) continue;
-      const int64_t rec = ((int64_t)b * a.S + s0 + tok) * a.KVH + hg0 + head;
+      const int64_t rec = tri_token_row(a, b, s0 + tok) * a.KVH + hg0 + head;
       sk[tok * 8 + head] = a.k_scales[rec];
       sv[tok * 8 + head] = a.v_scales[rec];
     }
@@ -257,10 +271,11 @@ tri_decode_kernel(TriArgs a) {
 
   const int s_begin = split * a.tokens_per_split;
   int s_end = s_begin + a.tokens_per_split;
-  if (s_end > a.S) s_end = a.S;
-  const int n_iter = (s_end - s_begin + 31) / 32;
+  const int s_lim = a.context_lens ? (int)load_ctx(a.context_lens, a.cl_dtype, b, a.S) : a.S;
+  if (s_end > s_lim) s_end = s_lim;
+  const int n_iter = s_end > s_begin ? (s_end - s_begin + 31) / 32 : 0;
 
-  tri_stage_load<F>(a, stage0, b, hg0, nh, s_begin, s_end);
+  if (n_iter > 0) tri_stage_load<F>(a, stage0, b, hg0, nh, s_begin, s_end);
   cp_async_commit();
   for (int it = 0; it < n_iter; ++it) {
     const int s0 = s_begin + it * 32;
@@ -495,6 +510,9 @@ struct akv_tri_decode_params {
   void* stream;
   void* ev_kernel_start; void* ev_kernel_stop;
   float* scores_out;
+  const void* block_tables; int bt_dtype; int64_t bt_stride_batch;
+  int block_size; int64_t num_blocks;
+  const void* context_lens; int cl_dtype;
 };
 
 AKV_EXPORT size_t akv_tri_decode_workspace_bytes(int batch, int num_q_heads, int seq_len, int tokens_per_split) {
@@ -535,6 +553,14 @@ AKV_EXPORT int akv_tri_decode_step(const akv_tri_decode_params* p) {
   a.tokens_per_split = tps; a.num_parts = parts;
   a.part_acc = reinterpret_cast<float*>(ws); a.part_ml = reinterpret_cast<float*>(ws + off_ml);
   a.scores_out = p->scores_out;
+  if (p->block_tables != nullptr) {
+    if (p->block_size <= 0 || p->num_blocks <= 0 || p->seq_len % p->block_size != 0)
+      return fail(AKV_ERR_ARG, "tri decode (paged): seq_len must be block-table width x block_size, num_blocks > 0");
+    if (p->key_positions != nullptr) return fail(AKV_ERR_UNSUPPORTED, "tri decode (paged): explicit key positions are not supported");
+    a.block_tables = p->block_tables; a.bt_dtype = p->bt_dtype; a.bt_stride = p->bt_stride_batch;
+    a.block_size = p->block_size; a.num_blocks = p->num_blocks;
+  }
+  a.context_lens = p->context_lens; a.cl_dtype = p->cl_dtype;
   if (p->ev_kernel_start) cudaEventRecord((cudaEvent_t)p->ev_kernel_start, st);
   if (p->seq_len > 0) {
     const int nh = p->num_kv_heads < 8 ? p->num_kv_heads : 8;

@@ -40,13 +40,25 @@ class TriAttention:
         return self.encoder.encode(keys), self.encoder.encode(values)
 
     def _run(self, query, k_enc, v_enc, query_pos, key_positions, out=None, raw_out=None, scores_out=None,
-             key_pos_start: int = 0, query_pos_default: Optional[int] = None, kernel_events=None):
+             key_pos_start: int = 0, query_pos_default: Optional[int] = None, kernel_events=None,
+             block_tables: Optional[torch.Tensor] = None, context_lens: Optional[torch.Tensor] = None):
         if not self.config.pre_rope or self.config.coeff_bits != 4:
             raise NotImplementedError("the kernel implements pre-RoPE scoring with 4-bit coefficients")
         dev = _lib.require_cuda(query, k_enc.indices, k_enc.packed, k_enc.scales, v_enc.indices, v_enc.packed,
-                                v_enc.scales, query_pos, key_positions, self._theta)
+                                v_enc.scales, query_pos, key_positions, self._theta, block_tables, context_lens)
         B, QH, D = query.shape
         S, KVH, F = k_enc.indices.shape[1:]
+        paged = block_tables is not None
+        if paged:                                  # records are [num_blocks, block_size, KVH, ...]
+            num_blocks, block_size = k_enc.indices.shape[:2]
+            assert key_positions is None, "paged records take positions from the slot order"
+            assert block_tables.dim() == 2 and block_tables.shape[0] == B and block_tables.dtype in _lib._INDEX_CODES
+            if block_tables.stride(1) != 1:
+                block_tables = block_tables.contiguous()
+            S = block_tables.shape[1] * block_size
+        if context_lens is not None:
+            assert context_lens.dtype in _lib._INDEX_CODES and context_lens.numel() == B
+            context_lens = context_lens.reshape(-1).contiguous()
         assert D == self.head_dim and QH == self.num_query_heads and KVH == self.num_kv_heads
         if query.dtype not in _lib._FLOAT_CODES:
             query = query.float()
@@ -74,6 +86,11 @@ class TriAttention:
         p.out, p.raw_out, p.scores_out = _lib.ptr(out), _lib.ptr(raw_out), _lib.ptr(scores_out)
         p.workspace, p.workspace_bytes = self._workspace.data_ptr(), self._workspace.numel()
         p.tokens_per_split = self.tokens_per_split
+        if paged:
+            p.block_tables, p.bt_dtype, p.bt_stride_batch = block_tables.data_ptr(), _lib.index_code(block_tables), block_tables.stride(0)
+            p.block_size, p.num_blocks = block_size, num_blocks
+        if context_lens is not None:
+            p.context_lens, p.cl_dtype = context_lens.data_ptr(), _lib.index_code(context_lens)
         p.stream = _lib.stream_ptr(dev)
         if kernel_events is not None:
             for ev in kernel_events:
@@ -91,6 +108,20 @@ class TriAttention:
         B, QH, D = query.shape
         out = torch.empty(B, QH, D, dtype=torch.float32, device=query.device)
         self._run(query, k_enc, v_enc, query_pos, key_positions, out=out, **kw)
+        return out
+
+    def paged_decode_step(self, query: torch.Tensor, cache, block_tables: torch.Tensor, context_lens: torch.Tensor,
+                          query_pos: Optional[torch.Tensor] = None, **kw) -> torch.Tensor:
+        """One decode step straight off a ``SpectralKVCache``: query [B, QH, D], block_tables [B, max_blocks_per_seq],
+        context_lens [B].  Equal to ``decode_step`` on ``cache.fetch_sequence(block_tables[b], context_lens[b])`` for every
+        b (the reference's route, triattention/cache.py:157-198 then attention.py:186-215), without the gather.  Keys
+        sit at positions 0..len-1; the query position defaults to each sequence's length."""
+        B, QH, D = query.shape
+        out = torch.empty(B, QH, D, dtype=torch.float32, device=query.device)
+        if query_pos is None:
+            query_pos = context_lens
+        self._run(query, cache.k_encoding, cache.v_encoding, query_pos, None, out=out, block_tables=block_tables,
+                  context_lens=context_lens, **kw)
         return out
 
     def decode_step_partial(self, query, k_enc, v_enc, query_pos=None, key_positions=None,

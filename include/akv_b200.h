@@ -341,6 +341,14 @@ typedef struct akv_tri_decode_params {
   void* ev_kernel_start; void* ev_kernel_stop;   /* optional cudaEvent_t pair around the main kernel */
   float* scores_out;      /* optional [batch, num_q_heads, seq_len] float32: the pre-softmax scores
                              (what TrigSeriesScorer.score returns); NULL = not written */
+  /* Paged records (SpectralKVCache, triattention/cache.py:48-110): with block_tables the six arrays are
+   * [num_blocks, block_size, num_kv_heads, ...] and token s of batch element b is slot s % block_size of
+   * block block_tables[b][s / block_size]; seq_len = table width x block_size; key_positions must be NULL.
+   * context_lens (optional, also without block_tables) [batch]: tokens of each batch element, clamped to
+   * [0, seq_len]; an element of length 0 gives zeros.  Index arrays are int32 (dtype 0) or int64 (1). */
+  const void* block_tables; int bt_dtype; int64_t bt_stride_batch;
+  int block_size; int64_t num_blocks;
+  const void* context_lens; int cl_dtype;
 } akv_tri_decode_params;
 
 size_t akv_tri_decode_workspace_bytes(int batch, int num_q_heads, int seq_len, int tokens_per_split);

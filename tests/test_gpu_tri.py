@@ -158,3 +158,73 @@ def test_decode_step_full_context_random_values_vs_oracle():
     v_np = tuple(t.cpu().numpy() for t in v_enc)
     ref = otri.decode_step(q.numpy(), k_np, v_np, tri._theta.cpu().numpy())
     assert np.abs(out - ref).max() < 2e-3
+
+
+def _paged_case(ctx, H=8, QH=32, seed=11, bt_dtype=torch.int32):
+    """Sequences of the given lengths encoded and stored into a SpectralKVCache through shuffled block tables."""
+    from aitherkvcache_b200.triattention import SpectralEncoding, SpectralKVCache
+    tri = _tri(H, QH)
+    B, S_max = len(ctx), max(max(ctx), 1)
+    keys, values, g = _synthetic(B, S_max, H, seed=seed)
+    q = torch.randn(B, QH, 128, generator=g).half().cuda()
+    k_enc, v_enc = tri.encode_kv(keys.cuda(), values.cuda())
+    nblk = [(c + 15) // 16 for c in ctx]
+    cache = SpectralKVCache(tri.config, max_blocks=sum(nblk) + 3, device="cuda")
+    # every block starts as junk that an over-read would pick up
+    cache.k_indices.random_(0, 64), cache.v_indices.random_(0, 64)
+    cache.k_packed.random_(0, 256), cache.v_packed.random_(0, 256)
+    cache.k_scales.fill_(3.0), cache.v_scales.fill_(3.0)
+    perm = torch.randperm(sum(nblk) + 3, generator=g)
+    bt = torch.zeros(B, max(max(nblk), 1) + 2, dtype=bt_dtype)
+    used = 0
+    for b, c in enumerate(ctx):
+        bt[b, :nblk[b]] = perm[used:used + nblk[b]].to(bt_dtype)
+        used += nblk[b]
+        if c:
+            cache.store_sequence(bt[b], SpectralEncoding(*[t[b, :c] for t in k_enc]), SpectralEncoding(*[t[b, :c] for t in v_enc]))
+    return tri, cache, q, bt.cuda(), torch.tensor(ctx, dtype=bt_dtype).cuda(), k_enc, v_enc
+
+
+@pytest.mark.parametrize("ctx,bt_dtype", (((700, 33, 16, 1), torch.int32), ((2100, 0, 517), torch.int64)))
+def test_paged_decode_equals_gather_then_decode(ctx, bt_dtype):
+    """Block-table addressing inside the kernel = the reference's fetch_sequence + decode_step per sequence
+    (ragged lengths, a partial last block, an empty sequence), and both agree with the oracle."""
+    tri, cache, q, bt, cl, k_enc, v_enc = _paged_case(ctx, bt_dtype=bt_dtype)
+    out = tri.paged_decode_step(q, cache, bt, cl)
+    assert out.shape == (len(ctx), 32, 128) and out.dtype == torch.float32
+    for b, c in enumerate(ctx):
+        if c == 0:
+            assert out[b].abs().max().item() == 0.0
+            continue
+        kf, vf = cache.fetch_sequence(bt[b], c)
+        for got, want in zip(kf + vf, [t[b, :c] for t in k_enc] + [t[b, :c] for t in v_enc]):
+            assert torch.equal(got, want)
+        dense = tri.decode_step(q[b:b + 1], type(kf)(*[t[None] for t in kf]), type(vf)(*[t[None] for t in vf]))
+        assert (out[b] - dense[0]).abs().max().item() < 1e-5
+        ref = otri.decode_step(q[b:b + 1].cpu().numpy(), tuple(t[None].cpu().numpy() for t in kf),
+                               tuple(t[None].cpu().numpy() for t in vf), tri._theta.cpu().numpy())
+        assert np.abs(out[b].cpu().numpy() - ref[0]).max() < 2e-3
+
+
+def test_paged_decode_query_positions_and_block_ops():
+    """Explicit query positions; copy_block / clear_block act on what the kernel reads."""
+    ctx = (300, 64)
+    tri, cache, q, bt, cl, k_enc, v_enc = _paged_case(ctx, seed=12)
+    qpos = torch.tensor([5000, 64], dtype=torch.int64).cuda()
+    out = tri.paged_decode_step(q, cache, bt, cl, query_pos=qpos)
+    for b, c in enumerate(ctx):
+        kf, vf = cache.fetch_sequence(bt[b], c)
+        dense = tri.decode_step(q[b:b + 1], type(kf)(*[t[None] for t in kf]), type(vf)(*[t[None] for t in vf]), qpos[b:b + 1])
+        assert (out[b] - dense[0]).abs().max().item() < 1e-5
+    # fork sequence 1's first block into a spare block and point the table at the copy: same result
+    spare = int(set(range(cache.max_blocks)).difference(bt.cpu().flatten().tolist()).pop())
+    cache.copy_block(int(bt[1, 0]), spare)
+    bt2 = bt.clone()
+    bt2[1, 0] = spare
+    assert torch.equal(tri.paged_decode_step(q, cache, bt2, cl, query_pos=qpos), out)
+    # a cleared block holds zero scales: its 16 tokens score 0 and add nothing to the values
+    cache.clear_block(spare)
+    out3 = tri.paged_decode_step(q, cache, bt2, cl, query_pos=qpos)
+    assert torch.equal(out3[0], out[0]) and not torch.equal(out3[1], out[1])
+    stats = cache.memory_stats()
+    assert stats["total_tokens"] == 364 and stats["used_blocks"] == 19 + 4

@@ -144,3 +144,36 @@ def test_token_rows_of_a_mixed_batch():
             want_seq.append(s)
     assert ctx.tolist() == want_ctx and ctx.dtype == torch.int32
     assert torch.equal(rows_bt, bt[torch.tensor(want_seq)])
+
+
+def test_spectral_kv_cache_host_semantics():
+    """SpectralKVCache on CPU tensors: store / fetch / copy / clear and the statistics of the reference's class."""
+    from aitherkvcache_b200.triattention import SpectralEncoding, SpectralKVCache, TriAttentionConfig
+    cfg = TriAttentionConfig(head_dim=128, num_freqs=12, coeff_bits=4, num_kv_heads=2, num_query_heads=8)
+    cache = SpectralKVCache(cfg, max_blocks=6, device="cpu")
+    assert cache.bytes_allocated == 6 * 16 * 2 * (12 + 12 + 2) * 2 and cache.bytes_per_token == 2 * cfg.bytes_per_kv_token
+    g = torch.Generator().manual_seed(0)
+
+    def enc(n):
+        return SpectralEncoding(torch.randint(0, 64, (n, 2, 12), generator=g, dtype=torch.uint8),
+                                torch.randint(0, 256, (n, 2, 12), generator=g, dtype=torch.uint8),
+                                torch.rand(n, 2, generator=g).half())
+    k, v = enc(37), enc(37)
+    table = torch.tensor([4, 1, 5, 0], dtype=torch.int32)
+    cache.store_sequence(table, k, v)
+    kf, vf = cache.fetch_sequence(table, 37)
+    assert all(torch.equal(a, b) for a, b in zip(kf + vf, k + v))
+    assert cache.memory_stats()["total_tokens"] == 37 and cache.memory_stats()["used_blocks"] == 3
+    # the reference's per-block and per-token stores land in the same places
+    other = SpectralKVCache(cfg, max_blocks=6, device="cpu")
+    other.store_block(4, SpectralEncoding(*[t[:16] for t in k]), SpectralEncoding(*[t[:16] for t in v]))
+    other.store_block(1, SpectralEncoding(*[t[16:32] for t in k]), SpectralEncoding(*[t[16:32] for t in v]))
+    for s in range(5):
+        other.store_token(5, s, SpectralEncoding(*[t[32 + s] for t in k]), SpectralEncoding(*[t[32 + s] for t in v]))
+    for a, b in zip(other._sides(), cache._sides()):
+        assert all(torch.equal(x, y) for x, y in zip(a, b))
+    assert torch.equal(other._block_fill, cache._block_fill)
+    cache.copy_block(5, 2)
+    assert torch.equal(cache.k_packed[2], cache.k_packed[5]) and int(cache._block_fill[2]) == 5
+    cache.clear_block(5)
+    assert cache.k_scales[5].abs().sum() == 0 and cache.memory_stats()["total_tokens"] == 37
