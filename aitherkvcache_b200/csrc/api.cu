@@ -47,7 +47,8 @@ AKV_EXPORT int akv_device_arch(void) {
 //   out[0] tensor-core encoder, out[1] tensor-core decoder: 0 = fine, 1 = a bounded wait on an MMA barrier
 //          gave up and the CTA left its tile unwritten, 2 = it also kept its tensor-memory columns
 //   out[2] packed-cache attention, out[3] hybrid attention: 1 = a fixed-address kernel found its shared
-//          window taken and returned without writing partials
+//          window taken and returned without writing partials; out[2] = 2: a bounded wait for a bulk copy
+//          ran out in a packed-cache attention kernel or in the TriAttention decode kernel
 //   out[4] akv_p2p_lse_merge: 1 = the bounded wait for the peers' partials ran out (a peer is late or gone)
 // reset != 0 clears the words after reading them.
 AKV_EXPORT int akv_device_status(int* out, int reset) {
@@ -57,6 +58,9 @@ AKV_EXPORT int akv_device_status(int* out, int reset) {
   if (int rc = akv::tc_encode_status(out + 0, reset)) return rc;
   if (int rc = akv::tc_decode_status(out + 1, reset)) return rc;
   if (int rc = akv::attn_window_status(out + 2, reset)) return rc;
+  int tri = 0;
+  if (int rc = akv::tri_status(&tri, reset)) return rc;
+  if (tri > out[2]) out[2] = tri;
   if (int rc = akv::hybrid_window_status(out + 3, reset)) return rc;
   return akv::p2p_status(out + 4, reset);
 }

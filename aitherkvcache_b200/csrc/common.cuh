@@ -88,6 +88,7 @@ inline uint32_t dyn_smem_window_start(const void* kernel) {
 int tc_encode_status(int* host_out, int reset);
 int tc_decode_status(int* host_out, int reset);
 int attn_window_status(int* host_out, int reset);
+int tri_status(int* host_out, int reset);
 int hybrid_window_status(int* host_out, int reset);
 int tc_encode_withhold(int tile);
 int tc_decode_withhold(int tile);

@@ -450,6 +450,344 @@ tri_decode_kernel(TriArgs a) {
   }
 }
 
+// ---------------------------------------------------------------------------
+// decode step, record-lane kernel (8 KV heads, up to 4 query heads per KV head)
+//
+// The 32-token x 8-head tile of a step is 256 records, one per thread, in memory order (thread r holds
+// token r / 8, head r % 8), so the staged arrays are read as they lie in global memory: six bulk copies
+// per 16 tokens bring them in, completing on an mbarrier, three tiles deep.
+//   Scores run on the CUDA cores: per retained pair one 16-byte load fetches the pair's (even, odd) query
+//   values of the group's four heads from a table laid out [pair][KV head] (the eight lanes of a quarter
+//   warp are eight different heads, so the load never conflicts), the coefficient pair is rotated by the
+//   phase and the four dot products advance.  Nothing dense is built for the keys.
+//   Values go through the tensor cores: every lane drops its record's coefficient pairs (2n - 15, exact
+//   in e4m3) as 16-bit entries into the head's [pair][token] tile, and warp h multiplies head h's tile with
+//   the softmax weights: A = tile (M = pairs, K = (token, parity)), B = weights with N = (query head,
+//   parity) and zero where the parities differ, so 16 accumulators per thread cover 4 heads x 128 dims.
+//   The reader clears each 16 bytes of the tile as it takes them.
+// Scores and value scales cross from the record lanes to the head warps through a small float array.
+// ---------------------------------------------------------------------------
+template <int F>
+struct TriLanes {
+  static constexpr int W = F / 4;                 // words per record
+  static constexpr int ROW = 8 * F;               // bytes of one token's records of an array (8 heads)
+  static constexpr int ARR = 32 * ROW;            // one staged array of a tile
+  static constexpr int SC = 32 * 16;              // one side's scales of a tile
+  static constexpr int STAGE = 4 * ARR + 2 * SC;  // K ids, K coefficients, V ids, V coefficients, K scales, V scales
+  static constexpr int NSTAGE = 3;
+  static constexpr int OFF_BAR = 0;               // NSTAGE "stage full" mbarriers, "tile free" mbarrier at +32, the CTA's
+                                                  // "a wait ran out" word at +64
+  static constexpr int OFF_TAB = 256;             // [64 pairs] x 256 B: theta, one copy per lane (128 B), then the pair's
+                                                  // query values [8 heads] x 4 half2 (128 B)
+  static constexpr int OFF_SC = OFF_TAB + 16384;  // [8 heads][4 scores + value scale][32 tokens] float
+  static constexpr int OFF_TILE = OFF_SC + 8 * 160 * 4;   // [8 heads][64 pairs][32 tokens] e4m3x2
+  static constexpr int OFF_STAGE = OFF_TILE + 8 * 4096;
+  static constexpr int BYTES = OFF_STAGE + NSTAGE * STAGE;
+};
+
+__device__ int g_tri_status;    // 2: a bounded wait for a bulk copy ran out; the step's output is not valid
+
+__device__ __forceinline__ uint32_t tri_s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ bool tri_wait_raw(uint32_t bar, uint32_t parity) {
+  const long long t0 = clock64();
+  for (int it = 0; it < (1 << 24); ++it) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) return true;
+    if ((it & 63) == 63 && clock64() - t0 > (1ll << 31)) break;     // about a second
+  }
+  return false;
+}
+
+// Bounded wait; once one wait of the CTA has run out, the others return at once.
+__device__ __forceinline__ bool tri_wait(uint32_t bar, uint32_t parity, uint32_t failed_addr) {
+  uint32_t f;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(f) : "r"(failed_addr) : "memory");
+  if (f != 0u) return false;
+  if (tri_wait_raw(bar, parity)) return true;
+  g_tri_status = 2;
+  asm volatile("st.shared.u32 [%0], %1;" :: "r"(failed_addr), "r"(1u) : "memory");
+  return false;
+}
+
+__device__ __forceinline__ void tri_bulk(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               :: "r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// One thread: the copies of the tile that starts at token s0 (two units of 16 tokens; a unit lies in one
+// cache block), rows past s_end left out.
+template <int F>
+__device__ __forceinline__ void tri_lanes_issue(const TriArgs& a, uint32_t stage, uint32_t bar, int b, int s0, int s_end) {
+  using L = TriLanes<F>;
+  int n[2];
+  n[0] = s_end - s0;      n[0] = n[0] < 0 ? 0 : (n[0] > 16 ? 16 : n[0]);
+  n[1] = s_end - s0 - 16; n[1] = n[1] < 0 ? 0 : (n[1] > 16 ? 16 : n[1]);
+  const uint32_t total = (uint32_t)(n[0] + n[1]) * (4 * L::ROW + 2 * 16);
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(total) : "memory");
+  const uint8_t* const srcs[4] = {a.k_idx, a.k_packed, a.v_idx, a.v_packed};
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    if (n[u] == 0) continue;
+    const int64_t row = tri_token_row(a, b, s0 + 16 * u);
+#pragma unroll
+    for (int arr = 0; arr < 4; ++arr)
+      tri_bulk(stage + arr * L::ARR + u * 16 * L::ROW, srcs[arr] + row * L::ROW, (uint32_t)n[u] * L::ROW, bar);
+    tri_bulk(stage + 4 * L::ARR + u * 256, reinterpret_cast<const char*>(a.k_scales) + row * 16, (uint32_t)n[u] * 16, bar);
+    tri_bulk(stage + 4 * L::ARR + L::SC + u * 256, reinterpret_cast<const char*>(a.v_scales) + row * 16, (uint32_t)n[u] * 16, bar);
+  }
+}
+
+__device__ __forceinline__ uint32_t e4m3x2_to_h2(uint32_t e16) {
+  uint32_t h;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h) : "h"((unsigned short)e16));
+  return h;
+}
+
+template <int F>
+__global__ void __launch_bounds__(256, 2)
+tri_decode_lanes_kernel(TriArgs a) {
+  using L = TriLanes<F>;
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int split = blockIdx.y, b = blockIdx.z;
+  const int G = a.QH / a.KVH;
+  const uint32_t sb = tri_s32(smem);
+  const uint32_t failed_addr = sb + L::OFF_BAR + 64;
+
+  const int s_begin = split * a.tokens_per_split;
+  int s_end = s_begin + a.tokens_per_split;
+  const int s_lim = a.context_lens ? (int)load_ctx(a.context_lens, a.cl_dtype, b, a.S) : a.S;
+  if (s_end > s_lim) s_end = s_lim;
+  const int n_iter = s_end > s_begin ? (s_end - s_begin + 31) / 32 : 0;
+
+  if (tid == 0) {
+#pragma unroll
+    for (int i = 0; i < L::NSTAGE; ++i)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(sb + L::OFF_BAR + 8 * i), "r"(1u) : "memory");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(sb + L::OFF_BAR + 32), "r"(8u) : "memory");
+    asm volatile("st.shared.u32 [%0], %1;" :: "r"(failed_addr), "r"(0u) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (n_iter > 0) {
+    // query table: entry (pair, KV head) = four half2 (even, odd) of the group's query heads, scaled
+    uint32_t* tab = reinterpret_cast<uint32_t*>(smem + L::OFF_TAB);
+    for (int i = tid; i < 64 * 8 * 4; i += 256) {
+      const int pair = i >> 5, head = (i >> 2) & 7, h = i & 3;
+      uint32_t v = 0u;
+      if (h < G) {
+        const int64_t base = (int64_t)b * a.q_sb + (int64_t)(head * G + h) * a.q_sh + 2 * pair;
+        v = pack_h2(load_as_float(a.query, a.q_dtype, base) * a.premul, load_as_float(a.query, a.q_dtype, base + 1) * a.premul);
+      }
+      tab[pair * 64 + 32 + (i & 31)] = v;
+    }
+    for (int i = tid; i < 64 * 32; i += 256) tab[(i >> 5) * 64 + (i & 31)] = __float_as_uint(a.theta[i >> 5]);
+    uint4* tz = reinterpret_cast<uint4*>(smem + L::OFF_TILE);
+    for (int i = tid; i < 8 * 4096 / 16; i += 256) tz[i] = make_uint4(0, 0, 0, 0);
+  }
+  __syncthreads();
+  if (tid == 0)
+    for (int i = 0; i < L::NSTAGE && i < n_iter; ++i)
+      tri_lanes_issue<F>(a, sb + L::OFF_STAGE + i * L::STAGE, sb + L::OFF_BAR + 8 * i, b, s_begin + 32 * i, s_end);
+
+  // record-lane role: token jA of the tile, KV head headA; the head's tile and score rows are rotated by
+  // 4 * head tokens so that the 32 lanes of a warp store to distinct banks
+  const int headA = lane & 7, jA = 4 * warp + (lane >> 3);
+  const int tokp = (jA + 4 * headA) & 31;
+  const unsigned char* const tab = smem + L::OFF_TAB;
+  const uint32_t theta_part = lane * 4, q_part = 128 + headA * 16;     // this lane's bytes inside a pair's table row
+  const uint32_t free_bar = sb + L::OFF_BAR + 32;
+  float* const my_sc = reinterpret_cast<float*>(smem + L::OFF_SC) + headA * 160 + tokp;
+  const uint32_t my_tile = sb + L::OFF_TILE + headA * 4096 + tokp * 2;
+  const float qpos = (float)(a.query_pos ? a.query_pos[b] : a.query_pos_default);
+  // head-warp role: KV head `warp`; thread (g, t) weighs query head g / 2 into parity g % 2 and keeps the
+  // accumulators of query head t
+  const int g = lane >> 2, t = lane & 3, hq = g >> 1, par = g & 1;
+  float o[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  float m_run = -CUDART_INF_F, l_run = 0.f;
+
+  int it = 0;
+  bool broken = false;
+  for (; it < n_iter; ++it) {
+    const int s0 = s_begin + it * 32;
+    const int stg = it % L::NSTAGE;
+    const uint32_t bar = sb + L::OFF_BAR + 8 * stg;
+    const bool ok = tri_wait(bar, (uint32_t)((it / L::NSTAGE) & 1), failed_addr);
+    const uint32_t* stw = reinterpret_cast<const uint32_t*>(smem + L::OFF_STAGE + stg * L::STAGE);
+    const int s = s0 + jA;
+    const bool valid = ok && s < s_end;
+    // ---- scores of this lane's record ----
+    float sc4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+    float vsc = 0.f;
+    if (valid) {
+      uint32_t kiw[L::W], kpw[L::W];
+#pragma unroll
+      for (int w = 0; w < L::W; ++w) {
+        kiw[w] = stw[tid * L::W + w] & 0x3F3F3F3Fu;
+        kpw[w] = stw[L::ARR / 4 + tid * L::W + w];
+      }
+      const __half* sch = reinterpret_cast<const __half*>(stw + L::ARR);      // byte offset 4 * ARR
+      const float ks = __half2float(sch[tid]);
+      vsc = __half2float(sch[L::SC / 2 + tid]) * (1.0f / 15.0f);
+      const float kpos = (float)(a.key_positions ? a.key_positions[(int64_t)b * a.S + s] : a.key_pos_start + s);
+      const float delta = __fsub_rn(kpos, qpos);
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int w = 0; w < L::W; ++w) {
+        const uint32_t hi2 = (kpw[w] >> 3) & 0x1E1E1E1Eu, lo2 = (kpw[w] << 1) & 0x1E1E1E1Eu;     // 2n per byte
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          // byte c of the id word lands in byte 1 (id * 256 = the pair's table row), the lane's part in byte 0
+          const uint32_t th_off = __byte_perm(kiw[w], theta_part, 0x6504 + 16 * c);
+          const uint32_t q_off = __byte_perm(kiw[w], q_part, 0x6504 + 16 * c);
+          const float phi = __fmul_rn(delta, *reinterpret_cast<const float*>(tab + th_off));
+          const float n = __fadd_rn(__fmaf_rn(phi, 0.15915494309189535f, 12582912.0f), -12582912.0f);   // nearest integer
+          float r = __fmaf_rn(-n, 6.2831854820251465f, phi);
+          r = __fmaf_rn(-n, -1.7484555314695172e-07f, r);
+          const float sn = __sinf(r), cs = __cosf(r);
+          const float k0 = __uint_as_float(__byte_perm(hi2, 0x4B000000u, 0x7440 + c)) - 8388623.0f;   // 2n - 15
+          const float k1 = __uint_as_float(__byte_perm(lo2, 0x4B000000u, 0x7440 + c)) - 8388623.0f;
+          const float k0r = __fmaf_rn(k0, cs, -k1 * sn), k1r = __fmaf_rn(k1, cs, k0 * sn);
+          const uint4 q = *reinterpret_cast<const uint4*>(tab + q_off);
+          // the rotated pair goes to fp16 like the query values; products and sums are float32
+          const unsigned short h0 = __half_as_ushort(__float2half_rn(k0r)), h1 = __half_as_ushort(__float2half_rn(k1r));
+          const uint32_t qq[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            asm("fma.rn.f32.f16 %0, %1, %2, %0;" : "+f"(acc[h]) : "h"((unsigned short)(qq[h] & 0xffffu)), "h"(h0));
+            asm("fma.rn.f32.f16 %0, %1, %2, %0;" : "+f"(acc[h]) : "h"((unsigned short)(qq[h] >> 16)), "h"(h1));
+          }
+        }
+      }
+      const float ksc = ks * (1.0f / 15.0f);
+#pragma unroll
+      for (int h = 0; h < 4; ++h) sc4[h] = acc[h] * ksc;
+      if (a.scores_out != nullptr) {
+        for (int h = 0; h < G; ++h)
+          a.scores_out[((int64_t)b * a.QH + headA * G + h) * a.S + s] = sc4[h] * 0.6931471805599453f;
+      }
+    }
+    // the head warps have taken the previous tile's scores and emptied its value tiles
+    if (it > 0) tri_wait(free_bar, (uint32_t)((it - 1) & 1), failed_addr);
+    my_sc[0] = sc4[0]; my_sc[32] = sc4[1]; my_sc[64] = sc4[2]; my_sc[96] = sc4[3]; my_sc[128] = vsc;
+    if (valid) {
+      // ---- this record's value coefficients into the head's tile ----
+#pragma unroll
+      for (int w = 0; w < L::W; ++w) {
+        const uint32_t viw = stw[2 * (L::ARR / 4) + tid * L::W + w] & 0x3F3F3F3Fu, vpw = stw[3 * (L::ARR / 4) + tid * L::W + w];
+        const uint32_t hi2 = (vpw >> 3) & 0x1E1E1E1Eu, lo2 = (vpw << 1) & 0x1E1E1E1Eu;
+        const uint32_t t01 = __byte_perm(hi2, lo2, 0x5140), t23 = __byte_perm(hi2, lo2, 0x7362);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const uint32_t idv = __byte_perm(viw, 0u, 0x4440 + c);
+          // halves 0x6400 | 2n = 1024 + 2n, minus 1039: 2n - 15, exactly; odd integers up to 15 are exact in e4m3
+          const uint32_t hb = __byte_perm(c < 2 ? t01 : t23, 0x64646464u, (c & 1) ? 0x4342 : 0x4140);
+          const __half2 d = __hsub2(*reinterpret_cast<const __half2*>(&hb), __floats2half2_rn(1039.f, 1039.f));
+          unsigned short e;
+          asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(e) : "r"(*reinterpret_cast<const uint32_t*>(&d)));
+          asm volatile("st.shared.u16 [%0], %1;" :: "r"(my_tile + idv * 64), "h"(e) : "memory");
+        }
+      }
+    }
+    __syncthreads();        // the tile's scores and value entries are in place; the stage has been read
+    {
+      uint32_t f;
+      asm volatile("ld.shared.u32 %0, [%1];" : "=r"(f) : "r"(failed_addr) : "memory");
+      if (f != 0u) { broken = true; break; }
+    }
+    if (tid == 0 && it + L::NSTAGE < n_iter)
+      tri_lanes_issue<F>(a, sb + L::OFF_STAGE + stg * L::STAGE, bar, b, s0 + 32 * L::NSTAGE, s_end);
+
+    // ---- head warp: online softmax of its head's 32 tokens, then values ----
+    const float* scr = reinterpret_cast<const float*>(smem + L::OFF_SC) + warp * 160;
+    const float4 sa = *reinterpret_cast<const float4*>(scr + hq * 32 + 8 * t);
+    const float4 sb4 = *reinterpret_cast<const float4*>(scr + hq * 32 + 8 * t + 4);
+    const float4 va = *reinterpret_cast<const float4*>(scr + 128 + 8 * t);
+    const float4 vb = *reinterpret_cast<const float4*>(scr + 128 + 8 * t + 4);
+    const float sv[8] = {sa.x, sa.y, sa.z, sa.w, sb4.x, sb4.y, sb4.z, sb4.w};
+    const float vv[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+    float mx = fmaxf(fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3])), fmaxf(fmaxf(sv[4], sv[5]), fmaxf(sv[6], sv[7])));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float mn = fmaxf(m_run, mx);
+    const float mref = (mn == -CUDART_INF_F) ? 0.f : mn;
+    const float alpha = ex2a(m_run - mref);
+    m_run = mn;
+    const float alpha_o = __shfl_sync(0xffffffffu, alpha, 8 * t);      // lane 8t weighs query head t
+    if (__any_sync(0xffffffffu, alpha_o != 1.0f)) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { o[i][0] *= alpha_o; o[i][1] *= alpha_o; o[i][2] *= alpha_o; o[i][3] *= alpha_o; }
+    }
+    float psum = 0.f;
+    uint32_t b0[4], b1[4];
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+      const float p0 = ex2a(sv[2 * ks] - mref), p1 = ex2a(sv[2 * ks + 1] - mref);
+      psum += p0 + p1;
+      const float w0 = p0 * vv[2 * ks], w1 = p1 * vv[2 * ks + 1];
+      b0[ks] = par ? pack_h2(0.f, w0) : pack_h2(w0, 0.f);
+      b1[ks] = par ? pack_h2(0.f, w1) : pack_h2(w1, 0.f);
+    }
+    l_run = __fmaf_rn(l_run, alpha, psum);
+    const uint32_t trow = sb + L::OFF_TILE + warp * 4096 + g * 64 + t * 16;
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt) {
+      uint32_t r0[4], r1[4];
+      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r0[0]), "=r"(r0[1]), "=r"(r0[2]), "=r"(r0[3]) : "r"(trow + mt * 1024) : "memory");
+      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r1[0]), "=r"(r1[1]), "=r"(r1[2]), "=r"(r1[3]) : "r"(trow + mt * 1024 + 512) : "memory");
+      asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" :: "r"(trow + mt * 1024), "r"(0u) : "memory");
+      asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" :: "r"(trow + mt * 1024 + 512), "r"(0u) : "memory");
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        uint32_t af[4];
+        af[0] = e4m3x2_to_h2(r0[ks] & 0xffffu);
+        af[1] = e4m3x2_to_h2(r1[ks] & 0xffffu);
+        af[2] = e4m3x2_to_h2(r0[ks] >> 16);
+        af[3] = e4m3x2_to_h2(r1[ks] >> 16);
+        mma16816_tri(o[mt], af, b0[ks], b1[ks]);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(free_bar) : "memory");
+  }
+  if (broken && tid == 0) {
+    // copies of later tiles may still be landing in this CTA's shared memory: wait for them (bounded) before leaving
+    for (int j = it + 1; j < n_iter && j < it + L::NSTAGE; ++j)
+      tri_wait_raw(sb + L::OFF_BAR + 8 * (j % L::NSTAGE), (uint32_t)((j / L::NSTAGE) & 1));
+  }
+
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  const int part = split;
+  if (t == 0 && par == 0 && hq < G) {
+    const int64_t rowi = (int64_t)b * a.QH + warp * G + hq;
+    a.part_ml[(rowi * a.num_parts + part) * 2] = m_run;
+    a.part_ml[(rowi * a.num_parts + part) * 2 + 1] = l_run;
+  }
+  if (t < G) {
+    const int64_t rowi = (int64_t)b * a.QH + warp * G + t;
+    float* pa = a.part_acc + (rowi * a.num_parts + part) * 128;
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt) {
+      *reinterpret_cast<float2*>(pa + 2 * (16 * mt + g)) = make_float2(o[mt][0], o[mt][1]);
+      *reinterpret_cast<float2*>(pa + 2 * (16 * mt + g + 8)) = make_float2(o[mt][2], o[mt][3]);
+    }
+  }
+}
+
+int tri_status(int* host_out, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(host_out, g_tri_status, sizeof(int));
+  if (e == cudaSuccess && reset) { const int z = 0; e = cudaMemcpyToSymbol(g_tri_status, &z, sizeof(int)); }
+  return e == cudaSuccess ? AKV_OK : fail((int)e, "tri status: %s", cudaGetErrorString(e));
+}
+
 static void tri_plan(int B, int QH, int S, int tps_in, int* tps, int* parts, size_t* off_ml, size_t* total) {
   int tp = tps_in > 0 ? tps_in : 1024;
   if (tps_in <= 0) {     // short key ranges (a rank's share of a split context): smaller splits, so that the grid
@@ -566,6 +904,21 @@ AKV_EXPORT int akv_tri_decode_step(const akv_tri_decode_params* p) {
     const int nh = p->num_kv_heads < 8 ? p->num_kv_heads : 8;
     dim3 grid((p->num_kv_heads + 7) / 8, parts, p->batch);
     cudaError_t e = cudaSuccess;
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    static const bool dense_tiles_only = getenv("AKV_TRI_DENSE_TILES") != nullptr;
+    const bool lanes = !dense_tiles_only && p->num_kv_heads == 8 && G <= 4 && al16(p->k_indices) && al16(p->k_packed) &&
+                       al16(p->k_scales) && al16(p->v_indices) && al16(p->v_packed) && al16(p->v_scales) &&
+                       (p->block_tables == nullptr || p->block_size % 16 == 0);
+    if (lanes) {
+#define AKV_TRI_L(FF)                                                                                    \
+      e = cudaFuncSetAttribute(tri_decode_lanes_kernel<FF>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+                               TriLanes<FF>::BYTES);                                                      \
+      if (e == cudaSuccess) tri_decode_lanes_kernel<FF><<<grid, 256, TriLanes<FF>::BYTES, st>>>(a);
+      if (p->num_freqs == 8) { AKV_TRI_L(8) } else if (p->num_freqs == 12) { AKV_TRI_L(12) } else { AKV_TRI_L(16) }
+#undef AKV_TRI_L
+      if (e != cudaSuccess) return fail((int)e, "tri decode: smem attribute: %s", cudaGetErrorString(e));
+      if (int rc = check_launch("tri_decode_lanes_kernel")) return rc;
+    } else {
 #define AKV_TRI(FF)                                                                                  \
     e = cudaFuncSetAttribute(tri_decode_kernel<FF>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
                              (int)TriSmem<FF>::bytes(8));                                                \
@@ -574,6 +927,7 @@ AKV_EXPORT int akv_tri_decode_step(const akv_tri_decode_params* p) {
 #undef AKV_TRI
     if (e != cudaSuccess) return fail((int)e, "tri decode: smem attribute: %s", cudaGetErrorString(e));
     if (int rc = check_launch("tri_decode_kernel")) return rc;
+    }
   }
   if (p->ev_kernel_stop) cudaEventRecord((cudaEvent_t)p->ev_kernel_stop, st);
   const int rows = p->batch * p->num_q_heads;
