@@ -613,6 +613,9 @@ tri_decode_lanes_kernel(TriArgs a) {
   for (int i = 0; i < 4; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
   float m_run = -CUDART_INF_F, l_run = 0.f;
 
+  const int64_t* const key_positions = a.key_positions;
+  const int64_t key_pos_start = a.key_pos_start;
+  float* const scores_out = a.scores_out;
   int it = 0;
   bool broken = false;
   for (; it < n_iter; ++it) {
@@ -636,7 +639,7 @@ tri_decode_lanes_kernel(TriArgs a) {
       const __half* sch = reinterpret_cast<const __half*>(stw + L::ARR);      // byte offset 4 * ARR
       const float ks = __half2float(sch[tid]);
       vsc = __half2float(sch[L::SC / 2 + tid]) * (1.0f / 15.0f);
-      const float kpos = (float)(a.key_positions ? a.key_positions[(int64_t)b * a.S + s] : a.key_pos_start + s);
+      const float kpos = (float)(key_positions ? key_positions[(int64_t)b * a.S + s] : key_pos_start + s);
       const float delta = __fsub_rn(kpos, qpos);
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -657,7 +660,8 @@ tri_decode_lanes_kernel(TriArgs a) {
           const float k0r = __fmaf_rn(k0, cs, -k1 * sn), k1r = __fmaf_rn(k1, cs, k0 * sn);
           const uint4 q = *reinterpret_cast<const uint4*>(tab + q_off);
           // the rotated pair goes to fp16 like the query values; products and sums are float32
-          const unsigned short h0 = __half_as_ushort(__float2half_rn(k0r)), h1 = __half_as_ushort(__float2half_rn(k1r));
+          const uint32_t kr = pack_h2(k0r, k1r);
+          const unsigned short h0 = (unsigned short)(kr & 0xffffu), h1 = (unsigned short)(kr >> 16);
           const uint32_t qq[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
           for (int h = 0; h < 4; ++h) {
@@ -669,9 +673,10 @@ tri_decode_lanes_kernel(TriArgs a) {
       const float ksc = ks * (1.0f / 15.0f);
 #pragma unroll
       for (int h = 0; h < 4; ++h) sc4[h] = acc[h] * ksc;
-      if (a.scores_out != nullptr) {
-        for (int h = 0; h < G; ++h)
-          a.scores_out[((int64_t)b * a.QH + headA * G + h) * a.S + s] = sc4[h] * 0.6931471805599453f;
+      if (scores_out != nullptr) {
+#pragma unroll
+        for (int h = 0; h < 4; ++h)
+          if (h < G) scores_out[((int64_t)b * a.QH + headA * G + h) * a.S + s] = sc4[h] * 0.6931471805599453f;
       }
     }
     // the head warps have taken the previous tile's scores and emptied its value tiles
@@ -789,10 +794,14 @@ int tri_status(int* host_out, int reset) {
 }
 
 static void tri_plan(int B, int QH, int S, int tps_in, int* tps, int* parts, size_t* off_ml, size_t* total) {
-  int tp = tps_in > 0 ? tps_in : 1024;
-  if (tps_in <= 0) {     // short key ranges (a rank's share of a split context): smaller splits, so that the grid
-                         // still holds about four CTAs per SM; never below 128 tokens
-    long long want = ((long long)B * S + 591) / 592;
+  int tp = tps_in > 0 ? tps_in : 2048;
+  if (tps_in <= 0) {     // the grid should be whole waves of 296 CTAs (two per SM): the fewest waves whose CTAs take at
+                         // most 2048 tokens each, split evenly over the batch; never below 128 tokens per CTA
+    const long long tokens = (long long)B * S;
+    const long long waves = (tokens + 296ll * 2048 - 1) / (296ll * 2048);
+    long long per_batch = (296 * waves) / (B > 0 ? B : 1);
+    if (per_batch < 1) per_batch = 1;
+    long long want = (S + per_batch - 1) / per_batch;
     want = (want + 31) / 32 * 32;
     if (want < 128) want = 128;
     if (want < tp) tp = (int)want;
