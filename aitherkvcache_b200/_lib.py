@@ -137,6 +137,7 @@ class TriDecodeParams(C.Structure):
         ("block_tables", c_vp), ("bt_dtype", c_int), ("bt_stride_batch", c_i64),
         ("block_size", c_int), ("num_blocks", c_i64),
         ("context_lens", c_vp), ("cl_dtype", c_int),
+        ("coeff_bits", c_int), ("post_rope", c_int),
     ]
 
 
@@ -172,6 +173,7 @@ _SIGNATURES = {
                                      c_i64, c_i64, c_i64, c_int, c_i64, c_vp]),
     "akv_hybrid_decode_step": (c_int, [C.POINTER(HybridDecodeStepParams)]),
     "akv_tri_encode": (c_int, [c_vp, c_int, c_i64, c_i64, c_int, c_int, c_vp, c_vp, c_vp, c_vp]),
+    "akv_tri_encode_bits": (c_int, [c_vp, c_int, c_i64, c_i64, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp]),
     "akv_tri_decode_workspace_bytes": (C.c_size_t, [c_int] * 4),
     "akv_tri_decode_step": (c_int, [C.POINTER(TriDecodeParams)]),
     "akv_p2p_exchange_bytes": (C.c_size_t, [c_int] * 4),

@@ -29,7 +29,7 @@ constexpr int TE_LD = 129;
 
 template <int F>
 __global__ void __launch_bounds__(TE_THREADS)
-tri_encode_kernel(const void* __restrict__ x, int x_dtype, int64_t n_rows, int64_t x_row_stride,
+tri_encode_kernel(const void* __restrict__ x, int x_dtype, int64_t n_rows, int64_t x_row_stride, int coeff_bits,
                   uint8_t* __restrict__ indices, uint8_t* __restrict__ packed, __half* __restrict__ scales) {
   constexpr int D = 128, P = 64;
   __shared__ float xs[TE_THREADS * TE_LD];
@@ -63,24 +63,35 @@ tri_encode_kernel(const void* __restrict__ x, int x_dtype, int64_t n_rows, int64
   int c = 0;
   for (int i = 0; i < P && c < F; ++i)
     if ((mask >> i) & 1ull) ids[c++] = i;
+  if (coeff_bits == 16) {       // the pair values as fp16, no scale (encoder.py:104-112)
+    __half* ph = reinterpret_cast<__half*>(packed) + n * (2 * F);
+    for (int f = 0; f < F; ++f) {
+      indices[n * F + f] = (uint8_t)ids[f];
+      ph[2 * f] = __float2half_rn(v[2 * ids[f]]);
+      ph[2 * f + 1] = __float2half_rn(v[2 * ids[f] + 1]);
+    }
+    scales[n] = __float2half_rn(1.0f);
+    return;
+  }
   float amax = 0.f;
   for (int f = 0; f < F; ++f) {
     amax = fmaxf(amax, fabsf(v[2 * ids[f]]));
     amax = fmaxf(amax, fabsf(v[2 * ids[f] + 1]));
   }
   const float scale = fmaxf(amax, 1e-8f);
-  uint8_t oi[F], op[F];
+  const float half_code = coeff_bits == 8 ? 127.5f : 7.5f, max_code = coeff_bits == 8 ? 255.f : 15.f;
   for (int f = 0; f < F; ++f) {
-    float q0 = rintf(__fmul_rn(__fadd_rn(__fdiv_rn(v[2 * ids[f]], scale), 1.0f), 7.5f));
-    float q1 = rintf(__fmul_rn(__fadd_rn(__fdiv_rn(v[2 * ids[f] + 1], scale), 1.0f), 7.5f));
-    q0 = fminf(fmaxf(q0, 0.f), 15.f);
-    q1 = fminf(fmaxf(q1, 0.f), 15.f);
-    oi[f] = (uint8_t)ids[f];
-    op[f] = (uint8_t)(((int)q0 << 4) | (int)q1);
-  }
-  for (int f = 0; f < F; ++f) {
-    indices[n * F + f] = oi[f];
-    packed[n * F + f] = op[f];
+    float q0 = rintf(__fmul_rn(__fadd_rn(__fdiv_rn(v[2 * ids[f]], scale), 1.0f), half_code));
+    float q1 = rintf(__fmul_rn(__fadd_rn(__fdiv_rn(v[2 * ids[f] + 1], scale), 1.0f), half_code));
+    q0 = fminf(fmaxf(q0, 0.f), max_code);
+    q1 = fminf(fmaxf(q1, 0.f), max_code);
+    indices[n * F + f] = (uint8_t)ids[f];
+    if (coeff_bits == 8) {        // both components as bytes, pair by pair (encoder.py:136-145)
+      packed[n * (2 * F) + 2 * f] = (uint8_t)(int)q0;
+      packed[n * (2 * F) + 2 * f + 1] = (uint8_t)(int)q1;
+    } else {
+      packed[n * F + f] = (uint8_t)(((int)q0 << 4) | (int)q1);
+    }
   }
   scales[n] = __float2half_rn(scale);
 }
@@ -108,6 +119,7 @@ struct TriArgs {
   const void* block_tables; int bt_dtype; int64_t bt_stride;
   int block_size; int64_t num_blocks;
   const void* context_lens; int cl_dtype;      // optional [B]: tokens of each batch element (clamped to S)
+  int post_rope;                               // keys were rotated before encoding: all phases are zero (scorer.py:201-203)
 };
 
 // Row of (batch b, token s) in the record arrays, before the head index.
@@ -171,36 +183,53 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 // Shared-memory plan of one CTA (nh <= 8 KV heads, one warp each):
 //   dense tile per warp  [32 tokens][TD_LD halves]   (rotated keys, then values; all-zero between uses)
 //   two staging buffers  4 arrays x [nh][32 tokens][F bytes] + 2 x [32 tokens][nh] fp16 scales
-template <int F>
+// CB = bits of one coefficient: 4 (two per byte), 8 (bytes k0, k1 per pair) or 16 (fp16 k0, k1 per pair, no scale).
+template <int F, int CB>
 struct TriSmem {
-  static constexpr int WORDS = F / 4;                       // words per record
+  static constexpr int WORDS = F / 4;                       // words of ids per record
+  static constexpr int PWORDS = F * CB / 16;                // words of coefficients per record
   static constexpr int HEAD = 32 * WORDS + WORDS;            // words per head, padded so that the async
                                                             // copies of one token row hit distinct banks
-  static constexpr int ARR = 8 * HEAD;                      // words per staged array (8 heads)
-  static constexpr int STAGE_WORDS = 4 * ARR + 2 * 128;     // + scales: 2 x 32 x 8 halves = 2 x 128 words
+  static constexpr int PHEAD = 32 * PWORDS + PWORDS;
+  static constexpr int ARR = 8 * HEAD;                      // words per staged id array (8 heads)
+  static constexpr int PARR = 8 * PHEAD;                    // words per staged coefficient array
+  static constexpr int OFF_KP = ARR, OFF_VI = ARR + PARR, OFF_VP = 2 * ARR + PARR, OFF_SC = 2 * (ARR + PARR);
+  static constexpr int STAGE_WORDS = OFF_SC + 2 * 128;      // + scales: 2 x 32 x 8 halves = 2 x 128 words
   static constexpr int THETA_BYTES = 64 * 32 * 4;           // phase table, one copy per lane
   static constexpr size_t bytes(int nh) { return (size_t)nh * TD_TILE_HALVES * 2 + 2 * STAGE_WORDS * 4 + THETA_BYTES; }
 };
 
-template <int F>
+template <int F, int CB>
 __device__ __forceinline__ void tri_stage_load(const TriArgs& a, uint32_t* stage, int b, int hg0, int nh,
                                                int s0, int s_end) {
-  using SM = TriSmem<F>;
-  const int row_words = nh * SM::WORDS;                     // words per token of this head group
-  const int total = 32 * row_words;
-  const uint8_t* const srcs[4] = {a.k_idx, a.k_packed, a.v_idx, a.v_packed};
-  for (int i = threadIdx.x; i < total; i += blockDim.x) {
-    const int tok = i / row_words, j = i - tok * row_words;
-    if (s0 + tok >= s_end) continue;
-    const int head = j / SM::WORDS, wj = j - head * SM::WORDS;
-    const int64_t g_off = (tri_token_row(a, b, s0 + tok) * a.KVH + hg0) * F + 4 * j;
-    const int s_off = head * SM::HEAD + tok * SM::WORDS + wj;
-#pragma unroll
-    for (int arr = 0; arr < 4; ++arr) cp_async4(stage + arr * SM::ARR + s_off, srcs[arr] + g_off);
+  using SM = TriSmem<F, CB>;
+  {   // ids
+    const int row_words = nh * SM::WORDS;                     // words per token of this head group
+    for (int i = threadIdx.x; i < 32 * row_words; i += blockDim.x) {
+      const int tok = i / row_words, j = i - tok * row_words;
+      if (s0 + tok >= s_end) continue;
+      const int head = j / SM::WORDS, wj = j - head * SM::WORDS;
+      const int64_t g_off = (tri_token_row(a, b, s0 + tok) * a.KVH + hg0) * F + 4 * j;
+      const int s_off = head * SM::HEAD + tok * SM::WORDS + wj;
+      cp_async4(stage + s_off, a.k_idx + g_off);
+      cp_async4(stage + SM::OFF_VI + s_off, a.v_idx + g_off);
+    }
+  }
+  {   // coefficients
+    const int row_words = nh * SM::PWORDS;
+    for (int i = threadIdx.x; i < 32 * row_words; i += blockDim.x) {
+      const int tok = i / row_words, j = i - tok * row_words;
+      if (s0 + tok >= s_end) continue;
+      const int head = j / SM::PWORDS, wj = j - head * SM::PWORDS;
+      const int64_t g_off = (tri_token_row(a, b, s0 + tok) * a.KVH + hg0) * (4 * SM::PWORDS) + 4 * j;
+      const int s_off = head * SM::PHEAD + tok * SM::PWORDS + wj;
+      cp_async4(stage + SM::OFF_KP + s_off, a.k_packed + g_off);
+      cp_async4(stage + SM::OFF_VP + s_off, a.v_packed + g_off);
+    }
   }
   // scales, staged as [tok][8] halves: pairs of heads by 4-byte async copies when the layout
   // allows it, single halves through registers otherwise
-  __half* sk = reinterpret_cast<__half*>(stage + 4 * SM::ARR);
+  __half* sk = reinterpret_cast<__half*>(stage + SM::OFF_SC);
   __half* sv = sk + 256;
   if (((nh | a.KVH) & 1) == 0) {
     const int hp = nh / 2;
@@ -222,10 +251,29 @@ __device__ __forceinline__ void tri_stage_load(const TriArgs& a, uint32_t* stage
   }
 }
 
-template <int F>
+// Coefficient pair f of a record as the integers (or, for fp16 coefficients, the values) the tiles hold;
+// the common factor scale / 15 (4-bit), scale / 255 (8-bit) or 1 (fp16) goes onto the scores and onto P.
+template <int CB>
+__device__ __forceinline__ void tri_coeff_pair(const uint32_t* pw, int f, float& c0, float& c1) {
+  if (CB == 4) {
+    const uint32_t byte = (pw[f >> 2] >> (8 * (f & 3))) & 0xffu;
+    c0 = (float)(2 * (int)(byte >> 4) - 15);
+    c1 = (float)(2 * (int)(byte & 15u) - 15);
+  } else if (CB == 8) {
+    const uint32_t two = (pw[f >> 1] >> (16 * (f & 1))) & 0xffffu;
+    c0 = (float)(2 * (int)(two & 0xffu) - 255);
+    c1 = (float)(2 * (int)(two >> 8) - 255);
+  } else {
+    const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&pw[f]));
+    c0 = v.x;
+    c1 = v.y;
+  }
+}
+
+template <int F, int CB>
 __global__ void __launch_bounds__(256, 2)
 tri_decode_kernel(TriArgs a) {
-  using SM = TriSmem<F>;
+  using SM = TriSmem<F, CB>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int hg = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
   const int hg0 = hg * 8;
@@ -275,52 +323,71 @@ tri_decode_kernel(TriArgs a) {
   if (s_end > s_lim) s_end = s_lim;
   const int n_iter = s_end > s_begin ? (s_end - s_begin + 31) / 32 : 0;
 
-  if (n_iter > 0) tri_stage_load<F>(a, stage0, b, hg0, nh, s_begin, s_end);
+  constexpr float COEFF_DIV = CB == 4 ? 1.0f / 15.0f : (CB == 8 ? 1.0f / 255.0f : 1.0f);
+  if (n_iter > 0) tri_stage_load<F, CB>(a, stage0, b, hg0, nh, s_begin, s_end);
   cp_async_commit();
   for (int it = 0; it < n_iter; ++it) {
     const int s0 = s_begin + it * 32;
     uint32_t* st = stage0 + (it & 1) * SM::STAGE_WORDS;
     cp_async_wait_all();
     __syncthreads();            // stage `it` is complete; everyone is done with stage it-1
-    if (it + 1 < n_iter) tri_stage_load<F>(a, stage0 + ((it + 1) & 1) * SM::STAGE_WORDS, b, hg0, nh, s0 + 32, s_end);
+    if (it + 1 < n_iter) tri_stage_load<F, CB>(a, stage0 + ((it + 1) & 1) * SM::STAGE_WORDS, b, hg0, nh, s0 + 32, s_end);
     cp_async_commit();
 
     const int s = s0 + lane;
     const bool valid = s < s_end;
-    uint32_t kiw[SM::WORDS], kpw[SM::WORDS], viw[SM::WORDS], vpw[SM::WORDS];
+    uint32_t kiw[SM::WORDS], kpw[SM::PWORDS], viw[SM::WORDS], vpw[SM::PWORDS];
     float ks = 0.f, vs = 0.f, delta = 0.f;
     if (valid) {
-      const int r = warp * SM::HEAD + lane * SM::WORDS;
+      const int r = warp * SM::HEAD + lane * SM::WORDS, rp = warp * SM::PHEAD + lane * SM::PWORDS;
 #pragma unroll
       for (int w = 0; w < SM::WORDS; ++w) {
         kiw[w] = st[r + w];
-        kpw[w] = st[SM::ARR + r + w];
-        viw[w] = st[2 * SM::ARR + r + w];
-        vpw[w] = st[3 * SM::ARR + r + w];
+        viw[w] = st[SM::OFF_VI + r + w];
       }
-      const __half* sk = reinterpret_cast<const __half*>(st + 4 * SM::ARR);
-      ks = __half2float(sk[lane * 8 + warp]);
-      vs = __half2float(sk[256 + lane * 8 + warp]);
+#pragma unroll
+      for (int w = 0; w < SM::PWORDS; ++w) {
+        kpw[w] = st[SM::OFF_KP + rp + w];
+        vpw[w] = st[SM::OFF_VP + rp + w];
+      }
+      const __half* sk = reinterpret_cast<const __half*>(st + SM::OFF_SC);
+      ks = CB == 16 ? 1.0f : __half2float(sk[lane * 8 + warp]);       // fp16 coefficients carry no scale
+      vs = CB == 16 ? 1.0f : __half2float(sk[256 + lane * 8 + warp]);
       const float kpos = (float)(a.key_positions ? a.key_positions[(int64_t)b * a.S + s] : a.key_pos_start + s);
-      delta = __fsub_rn(kpos, qpos);
+      delta = a.post_rope ? 0.f : __fsub_rn(kpos, qpos);
     }
     __half2* row = reinterpret_cast<__half2*>(tile + lane * TD_LD);
     // ---- rotated keys into the dense tile: integer coefficients 2n - 15 (the factor scale / 15 goes
     //      onto the scores), exponent trick instead of int-to-float conversions ----
     if (valid) {
+      if (CB == 4) {
 #pragma unroll
-      for (int w = 0; w < SM::WORDS; ++w) {
-        const uint32_t hi2 = (kpw[w] >> 3) & 0x1E1E1E1Eu, lo2 = (kpw[w] << 1) & 0x1E1E1E1Eu;     // 2n per byte
+        for (int w = 0; w < SM::WORDS; ++w) {
+          const uint32_t hi2 = (kpw[w] >> 3) & 0x1E1E1E1Eu, lo2 = (kpw[w] << 1) & 0x1E1E1E1Eu;     // 2n per byte
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const uint32_t id = __byte_perm(kiw[w], 0u, 0x4440 + c) & 63u;
+          for (int c = 0; c < 4; ++c) {
+            const uint32_t id = __byte_perm(kiw[w], 0u, 0x4440 + c) & 63u;
+            const float phi = __fmul_rn(delta, my_theta[id * 32]);
+            const float n = rintf(phi * 0.15915494309189535f);
+            float r = __fmaf_rn(-n, 6.2831854820251465f, phi);
+            r = __fmaf_rn(-n, -1.7484555314695172e-07f, r);
+            const float sn = __sinf(r), cs = __cosf(r);
+            const float k0 = __uint_as_float(__byte_perm(hi2, 0x4B000000u, 0x7440 + c)) - 8388623.0f;   // 8388608 + 2n - 8388623
+            const float k1 = __uint_as_float(__byte_perm(lo2, 0x4B000000u, 0x7440 + c)) - 8388623.0f;
+            row[id] = __floats2half2_rn(__fmaf_rn(k0, cs, -k1 * sn), __fmaf_rn(k1, cs, k0 * sn));
+          }
+        }
+      } else {
+#pragma unroll
+        for (int f = 0; f < F; ++f) {
+          const uint32_t id = __byte_perm(kiw[f >> 2], 0u, 0x4440 + (f & 3)) & 63u;
           const float phi = __fmul_rn(delta, my_theta[id * 32]);
           const float n = rintf(phi * 0.15915494309189535f);
           float r = __fmaf_rn(-n, 6.2831854820251465f, phi);
           r = __fmaf_rn(-n, -1.7484555314695172e-07f, r);
           const float sn = __sinf(r), cs = __cosf(r);
-          const float k0 = __uint_as_float(__byte_perm(hi2, 0x4B000000u, 0x7440 + c)) - 8388623.0f;   // 8388608 + 2n - 8388623
-          const float k1 = __uint_as_float(__byte_perm(lo2, 0x4B000000u, 0x7440 + c)) - 8388623.0f;
+          float k0, k1;
+          tri_coeff_pair<CB>(kpw, f, k0, k1);
           row[id] = __floats2half2_rn(__fmaf_rn(k0, cs, -k1 * sn), __fmaf_rn(k1, cs, k0 * sn));
         }
       }
@@ -340,7 +407,7 @@ tri_decode_kernel(TriArgs a) {
       }
     }
     {   // rows of the score tiles are tokens g, g+8 (+16): their key scales come from the lanes that hold them
-      const float ksc = ks * (1.0f / 15.0f);
+      const float ksc = ks * COEFF_DIV;
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
         const float ka = __shfl_sync(0xffffffffu, ksc, mt * 16 + g), kb = __shfl_sync(0xffffffffu, ksc, mt * 16 + g + 8);
@@ -352,16 +419,26 @@ tri_decode_kernel(TriArgs a) {
     if (valid) {
 #pragma unroll
       for (int f = 0; f < F; ++f) row[__byte_perm(kiw[f >> 2], 0u, 0x4440 + (f & 3)) & 63u] = __floats2half2_rn(0.f, 0.f);
+      if (CB == 4) {
 #pragma unroll
-      for (int w = 0; w < SM::WORDS; ++w) {
-        const uint32_t hi2 = (vpw[w] >> 3) & 0x1E1E1E1Eu, lo2 = (vpw[w] << 1) & 0x1E1E1E1Eu;
-        const uint32_t t01 = __byte_perm(hi2, lo2, 0x5140), t23 = __byte_perm(hi2, lo2, 0x7362);
+        for (int w = 0; w < SM::WORDS; ++w) {
+          const uint32_t hi2 = (vpw[w] >> 3) & 0x1E1E1E1Eu, lo2 = (vpw[w] << 1) & 0x1E1E1E1Eu;
+          const uint32_t t01 = __byte_perm(hi2, lo2, 0x5140), t23 = __byte_perm(hi2, lo2, 0x7362);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const uint32_t idv = __byte_perm(viw[w], 0u, 0x4440 + c) & 63u;
-          // halves 0x6400 | 2n = 1024 + 2n, minus 1039: 2n - 15, exactly
-          const uint32_t hb = __byte_perm(c < 2 ? t01 : t23, 0x64646464u, (c & 1) ? 0x4342 : 0x4140);
-          row[idv] = __hsub2(*reinterpret_cast<const __half2*>(&hb), __floats2half2_rn(1039.f, 1039.f));
+          for (int c = 0; c < 4; ++c) {
+            const uint32_t idv = __byte_perm(viw[w], 0u, 0x4440 + c) & 63u;
+            // halves 0x6400 | 2n = 1024 + 2n, minus 1039: 2n - 15, exactly
+            const uint32_t hb = __byte_perm(c < 2 ? t01 : t23, 0x64646464u, (c & 1) ? 0x4342 : 0x4140);
+            row[idv] = __hsub2(*reinterpret_cast<const __half2*>(&hb), __floats2half2_rn(1039.f, 1039.f));
+          }
+        }
+      } else {
+#pragma unroll
+        for (int f = 0; f < F; ++f) {
+          const uint32_t idv = __byte_perm(viw[f >> 2], 0u, 0x4440 + (f & 3)) & 63u;
+          float v0, v1;
+          tri_coeff_pair<CB>(vpw, f, v0, v1);      // integers up to 255, or the fp16 values: exact in fp16
+          row[idv] = __floats2half2_rn(v0, v1);
         }
       }
     }
@@ -403,7 +480,7 @@ tri_decode_kernel(TriArgs a) {
       const float p2 = ex2a(sc[mt][2] - mn0), p3 = ex2a(sc[mt][3] - mn1);
       l0 += p0 + p2;
       l1 += p1 + p3;
-      const float vsc = vs * (1.0f / 15.0f);        // 0 for lanes past the end
+      const float vsc = vs * COEFF_DIV;        // 0 for lanes past the end
       const float va = __shfl_sync(0xffffffffu, vsc, mt * 16 + g), vb = __shfl_sync(0xffffffffu, vsc, mt * 16 + g + 8);
       pb[mt][0] = movmatrix_trans_tri(pack_h2(p0 * va, p1 * va));
       pb[mt][1] = movmatrix_trans_tri(pack_h2(p2 * vb, p3 * vb));
@@ -616,6 +693,7 @@ tri_decode_lanes_kernel(TriArgs a) {
   const int64_t* const key_positions = a.key_positions;
   const int64_t key_pos_start = a.key_pos_start;
   float* const scores_out = a.scores_out;
+  const bool post_rope = a.post_rope != 0;
   int it = 0;
   bool broken = false;
   for (; it < n_iter; ++it) {
@@ -640,7 +718,7 @@ tri_decode_lanes_kernel(TriArgs a) {
       const float ks = __half2float(sch[tid]);
       vsc = __half2float(sch[L::SC / 2 + tid]) * (1.0f / 15.0f);
       const float kpos = (float)(key_positions ? key_positions[(int64_t)b * a.S + s] : key_pos_start + s);
-      const float delta = __fsub_rn(kpos, qpos);
+      const float delta = post_rope ? 0.f : __fsub_rn(kpos, qpos);
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int w = 0; w < L::W; ++w) {
@@ -821,9 +899,12 @@ static void tri_plan(int B, int QH, int S, int tps_in, int* tps, int* parts, siz
 
 using namespace akv;
 
-AKV_EXPORT int akv_tri_encode(const void* x, int x_dtype, int64_t n_rows, int64_t x_row_stride, int head_dim,
-                              int num_freqs, uint8_t* indices, uint8_t* packed, void* scales_f16, void* stream) {
+AKV_EXPORT int akv_tri_encode_bits(const void* x, int x_dtype, int64_t n_rows, int64_t x_row_stride, int head_dim,
+                                   int num_freqs, int coeff_bits, uint8_t* indices, void* packed, void* scales_f16,
+                                   void* stream) {
   if (head_dim != 128) return fail(AKV_ERR_UNSUPPORTED, "tri encode is built for head_dim 128, got %d", head_dim);
+  if (coeff_bits != 4 && coeff_bits != 8 && coeff_bits != 16)
+    return fail(AKV_ERR_UNSUPPORTED, "tri encode: coeff_bits must be 4, 8 or 16, got %d", coeff_bits);
   if (n_rows < 0) return fail(AKV_ERR_ARG, "n_rows < 0");
   if (n_rows == 0) return AKV_OK;
   if (!x || !indices || !packed || !scales_f16) return fail(AKV_ERR_ARG, "akv_tri_encode: null pointer");
@@ -831,13 +912,19 @@ AKV_EXPORT int akv_tri_encode(const void* x, int x_dtype, int64_t n_rows, int64_
   const int grid = (int)((n_rows + TE_THREADS - 1) / TE_THREADS);
   cudaStream_t st = (cudaStream_t)stream;
   __half* sc = reinterpret_cast<__half*>(scales_f16);
+  uint8_t* pk = reinterpret_cast<uint8_t*>(packed);
   switch (num_freqs) {
-    case 8: tri_encode_kernel<8><<<grid, TE_THREADS, 0, st>>>(x, x_dtype, n_rows, x_row_stride, indices, packed, sc); break;
-    case 12: tri_encode_kernel<12><<<grid, TE_THREADS, 0, st>>>(x, x_dtype, n_rows, x_row_stride, indices, packed, sc); break;
-    case 16: tri_encode_kernel<16><<<grid, TE_THREADS, 0, st>>>(x, x_dtype, n_rows, x_row_stride, indices, packed, sc); break;
+    case 8: tri_encode_kernel<8><<<grid, TE_THREADS, 0, st>>>(x, x_dtype, n_rows, x_row_stride, coeff_bits, indices, pk, sc); break;
+    case 12: tri_encode_kernel<12><<<grid, TE_THREADS, 0, st>>>(x, x_dtype, n_rows, x_row_stride, coeff_bits, indices, pk, sc); break;
+    case 16: tri_encode_kernel<16><<<grid, TE_THREADS, 0, st>>>(x, x_dtype, n_rows, x_row_stride, coeff_bits, indices, pk, sc); break;
     default: return fail(AKV_ERR_UNSUPPORTED, "tri encode: num_freqs must be 8, 12 or 16, got %d", num_freqs);
   }
   return check_launch("tri_encode_kernel");
+}
+
+AKV_EXPORT int akv_tri_encode(const void* x, int x_dtype, int64_t n_rows, int64_t x_row_stride, int head_dim,
+                              int num_freqs, uint8_t* indices, uint8_t* packed, void* scales_f16, void* stream) {
+  return akv_tri_encode_bits(x, x_dtype, n_rows, x_row_stride, head_dim, num_freqs, 4, indices, packed, scales_f16, stream);
 }
 
 // Mirror of akv_tri_decode_params in include/akv_b200.h.
@@ -860,6 +947,7 @@ struct akv_tri_decode_params {
   const void* block_tables; int bt_dtype; int64_t bt_stride_batch;
   int block_size; int64_t num_blocks;
   const void* context_lens; int cl_dtype;
+  int coeff_bits, post_rope;
 };
 
 AKV_EXPORT size_t akv_tri_decode_workspace_bytes(int batch, int num_q_heads, int seq_len, int tokens_per_split) {
@@ -879,6 +967,8 @@ AKV_EXPORT int akv_tri_decode_step(const akv_tri_decode_params* p) {
     return fail(AKV_ERR_ARG, "tri decode: bad sizes");
   const int G = p->num_q_heads / p->num_kv_heads;
   if (G > 8) return fail(AKV_ERR_UNSUPPORTED, "tri decode: at most 8 query heads per KV head");
+  const int cb = p->coeff_bits == 0 ? 4 : p->coeff_bits;
+  if (cb != 4 && cb != 8 && cb != 16) return fail(AKV_ERR_UNSUPPORTED, "tri decode: coeff_bits must be 4, 8 or 16, got %d", cb);
   if (p->batch == 0) return AKV_OK;
   if (!p->query || !p->theta || (!p->out && !p->raw_out) ||
       (p->seq_len > 0 && (!p->k_indices || !p->k_packed || !p->k_scales || !p->v_indices || !p->v_packed || !p->v_scales)))
@@ -908,6 +998,7 @@ AKV_EXPORT int akv_tri_decode_step(const akv_tri_decode_params* p) {
     a.block_size = p->block_size; a.num_blocks = p->num_blocks;
   }
   a.context_lens = p->context_lens; a.cl_dtype = p->cl_dtype;
+  a.post_rope = p->post_rope;
   if (p->ev_kernel_start) cudaEventRecord((cudaEvent_t)p->ev_kernel_start, st);
   if (p->seq_len > 0) {
     const int nh = p->num_kv_heads < 8 ? p->num_kv_heads : 8;
@@ -915,7 +1006,7 @@ AKV_EXPORT int akv_tri_decode_step(const akv_tri_decode_params* p) {
     cudaError_t e = cudaSuccess;
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
     static const bool dense_tiles_only = getenv("AKV_TRI_DENSE_TILES") != nullptr;
-    const bool lanes = !dense_tiles_only && p->num_kv_heads == 8 && G <= 4 && al16(p->k_indices) && al16(p->k_packed) &&
+    const bool lanes = !dense_tiles_only && cb == 4 && p->num_kv_heads == 8 && G <= 4 && al16(p->k_indices) && al16(p->k_packed) &&
                        al16(p->k_scales) && al16(p->v_indices) && al16(p->v_packed) && al16(p->v_scales) &&
                        (p->block_tables == nullptr || p->block_size % 16 == 0);
     if (lanes) {
@@ -928,11 +1019,14 @@ AKV_EXPORT int akv_tri_decode_step(const akv_tri_decode_params* p) {
       if (e != cudaSuccess) return fail((int)e, "tri decode: smem attribute: %s", cudaGetErrorString(e));
       if (int rc = check_launch("tri_decode_lanes_kernel")) return rc;
     } else {
-#define AKV_TRI(FF)                                                                                  \
-    e = cudaFuncSetAttribute(tri_decode_kernel<FF>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
-                             (int)TriSmem<FF>::bytes(8));                                                \
-    if (e == cudaSuccess) tri_decode_kernel<FF><<<grid, 32 * nh, TriSmem<FF>::bytes(nh), st>>>(a);
-    if (p->num_freqs == 8) { AKV_TRI(8) } else if (p->num_freqs == 12) { AKV_TRI(12) } else { AKV_TRI(16) }
+#define AKV_TRI(FF, CC)                                                                              \
+    e = cudaFuncSetAttribute(tri_decode_kernel<FF, CC>, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
+                             (int)TriSmem<FF, CC>::bytes(8));                                            \
+    if (e == cudaSuccess) tri_decode_kernel<FF, CC><<<grid, 32 * nh, TriSmem<FF, CC>::bytes(nh), st>>>(a);
+#define AKV_TRI_F(CC)                                                                                \
+    if (p->num_freqs == 8) { AKV_TRI(8, CC) } else if (p->num_freqs == 12) { AKV_TRI(12, CC) } else { AKV_TRI(16, CC) }
+    if (cb == 4) { AKV_TRI_F(4) } else if (cb == 8) { AKV_TRI_F(8) } else { AKV_TRI_F(16) }
+#undef AKV_TRI_F
 #undef AKV_TRI
     if (e != cudaSuccess) return fail((int)e, "tri decode: smem attribute: %s", cudaGetErrorString(e));
     if (int rc = check_launch("tri_decode_kernel")) return rc;

@@ -42,8 +42,9 @@ class TriAttention:
     def _run(self, query, k_enc, v_enc, query_pos, key_positions, out=None, raw_out=None, scores_out=None,
              key_pos_start: int = 0, query_pos_default: Optional[int] = None, kernel_events=None,
              block_tables: Optional[torch.Tensor] = None, context_lens: Optional[torch.Tensor] = None):
-        if not self.config.pre_rope or self.config.coeff_bits != 4:
-            raise NotImplementedError("the kernel implements pre-RoPE scoring with 4-bit coefficients")
+        cb = self.config.coeff_bits
+        want = torch.float16 if cb == 16 else torch.uint8
+        assert k_enc.packed.dtype == want and v_enc.packed.dtype == want, f"coeff_bits={cb} takes {want} coefficients"
         dev = _lib.require_cuda(query, k_enc.indices, k_enc.packed, k_enc.scales, v_enc.indices, v_enc.packed,
                                 v_enc.scales, query_pos, key_positions, self._theta, block_tables, context_lens)
         B, QH, D = query.shape
@@ -86,6 +87,7 @@ class TriAttention:
         p.out, p.raw_out, p.scores_out = _lib.ptr(out), _lib.ptr(raw_out), _lib.ptr(scores_out)
         p.workspace, p.workspace_bytes = self._workspace.data_ptr(), self._workspace.numel()
         p.tokens_per_split = self.tokens_per_split
+        p.coeff_bits, p.post_rope = cb, 0 if self.config.pre_rope else 1
         if paged:
             p.block_tables, p.bt_dtype, p.bt_stride_batch = block_tables.data_ptr(), _lib.index_code(block_tables), block_tables.stride(0)
             p.block_size, p.num_blocks = block_size, num_blocks

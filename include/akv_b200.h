@@ -314,6 +314,11 @@ int akv_hybrid_decode_step(const akv_hybrid_decode_step_params* params);
  *   indices, packed [n_rows, num_freqs] uint8; scales [n_rows] fp16. */
 int akv_tri_encode(const void* x, int x_dtype, int64_t n_rows, int64_t x_row_stride, int head_dim,
                    int num_freqs, uint8_t* indices, uint8_t* packed, void* scales_f16, void* stream);
+/* The same with the encoder's other coefficient formats (encoder.py:104-147): coeff_bits 8 stores the
+ * two components of a pair as bytes, packed [n_rows, 2 * num_freqs] uint8 (q = round((v / scale + 1) * 127.5));
+ * coeff_bits 16 stores them as fp16, packed [n_rows, num_freqs, 2], scales all 1; coeff_bits 4 as above. */
+int akv_tri_encode_bits(const void* x, int x_dtype, int64_t n_rows, int64_t x_row_stride, int head_dim,
+                        int num_freqs, int coeff_bits, uint8_t* indices, void* packed, void* scales_f16, void* stream);
 
 /* Replaces TriAttention.decode_step (attention.py:186-280) = TrigSeriesScorer.score
  * (scorer.py:115-208) + softmax + _accumulate_values.
@@ -349,6 +354,11 @@ typedef struct akv_tri_decode_params {
   const void* block_tables; int bt_dtype; int64_t bt_stride_batch;
   int block_size; int64_t num_blocks;
   const void* context_lens; int cl_dtype;
+  /* Coefficient format of the packed arrays (SpectralKVEncoder, encoder.py:97-147; scorer.py:94-113):
+   * 0 or 4: one byte per pair, [.., F]; 8: two bytes per pair (even, odd), [.., 2F]; 16: two fp16 per pair,
+   * [.., F, 2], scales ignored.  post_rope != 0: keys were encoded after RoPE, scores are the plain sparse
+   * dot product (scorer.py:201-203) and positions are not used. */
+  int coeff_bits, post_rope;
 } akv_tri_decode_params;
 
 size_t akv_tri_decode_workspace_bytes(int batch, int num_q_heads, int seq_len, int tokens_per_split);

@@ -4,10 +4,9 @@ TEST INFRASTRUCTURE ONLY (see oracle/__init__.py).
 
 Reference:
   aither_kvcache/triattention/spectral.py:34-51    RoPE frequencies
-  aither_kvcache/triattention/encoder.py:73-149    top-F pair selection, int4 coefficients
-  aither_kvcache/triattention/scorer.py:84-208     trig-series scores
+  aither_kvcache/triattention/encoder.py:73-149    top-F pair selection, 4-bit / 8-bit / fp16 coefficients
+  aither_kvcache/triattention/scorer.py:84-208     trig-series scores (pre-RoPE) or sparse dot product (post-RoPE)
   aither_kvcache/triattention/attention.py:186-280 softmax + scattered value sum
-Only the int4 / pre-RoPE configuration is restated.
 """
 from __future__ import annotations
 
@@ -24,10 +23,11 @@ def rope_frequencies(head_dim, base=1_000_000.0):
     return np.power(np.float32(base), e).astype(np.float32)
 
 
-def encode(x, num_freqs=12):
-    """encoder.py:73-149 for coeff_bits == 4.
+def encode(x, num_freqs=12, coeff_bits=4):
+    """encoder.py:73-149.
 
-    Returns (indices u8[...,F] ascending, packed u8[...,F], scales f16[...]).
+    Returns (indices u8[...,F] ascending, packed, scales f16[...]); packed is u8[...,F] for
+    coeff_bits 4, u8[...,2F] for 8 and f16[...,F,2] (scales all 1) for 16.
     Ties between equal pair energies at rank F are broken towards the lower
     pair id here; torch.topk does not promise an order, so callers compare
     index sets only where the F-th and (F+1)-th energies differ.
@@ -41,13 +41,16 @@ def encode(x, num_freqs=12):
     order = np.argsort(-energy, axis=-1, kind="stable")[:, :num_freqs]
     top = np.sort(order, axis=-1)
     tp = np.take_along_axis(pairs, top[..., None], axis=1)          # [N,F,2]
+    idx = top.astype(np.uint8).reshape(*lead, num_freqs)
+    if coeff_bits == 16:
+        return idx, tp.astype(np.float16).reshape(*lead, num_freqs, 2), np.ones(lead, np.float16)
     scales = np.maximum(np.abs(tp).reshape(len(tp), -1).max(-1), np.float32(1e-8))
     normed = tp / scales[:, None, None]
-    q = np.clip(np.rint((normed + np.float32(1.0)) * np.float32(7.5)), 0, 15).astype(np.uint8)
-    packed = (q[..., 0] << 4) | q[..., 1]
-    return (top.astype(np.uint8).reshape(*lead, num_freqs),
-            packed.reshape(*lead, num_freqs),
-            scales.astype(np.float16).reshape(lead))
+    half, top_code = (np.float32(7.5), 15) if coeff_bits == 4 else (np.float32(127.5), 255)
+    q = np.clip(np.rint((normed + np.float32(1.0)) * half), 0, top_code).astype(np.uint8)
+    packed = ((q[..., 0] << 4) | q[..., 1]).reshape(*lead, num_freqs) if coeff_bits == 4 \
+        else q.reshape(*lead, 2 * num_freqs)
+    return idx, packed, scales.astype(np.float16).reshape(lead)
 
 
 def rank_gap(x, num_freqs=12):
@@ -60,17 +63,24 @@ def rank_gap(x, num_freqs=12):
     return (e[:, num_freqs - 1] - e[:, num_freqs]).reshape(x.shape[:-1])
 
 
-def unpack_coeffs(packed, scales):
-    """scorer.py:99-104."""
-    s = np.asarray(scales).astype(np.float32)[..., None]
+def unpack_coeffs(packed, scales, coeff_bits=4):
+    """scorer.py:84-113."""
     p = np.asarray(packed)
+    if coeff_bits == 16:
+        return p[..., 0].astype(np.float32), p[..., 1].astype(np.float32)
+    s = np.asarray(scales).astype(np.float32)[..., None]
+    if coeff_bits == 8:
+        raw = p.astype(np.float32).reshape(*p.shape[:-1], p.shape[-1] // 2, 2)
+        return ((raw[..., 0] / np.float32(127.5) - np.float32(1.0)) * s,
+                (raw[..., 1] / np.float32(127.5) - np.float32(1.0)) * s)
     k0 = ((p >> 4).astype(np.float32) / np.float32(7.5) - np.float32(1.0)) * s
     k1 = ((p & 15).astype(np.float32) / np.float32(7.5) - np.float32(1.0)) * s
     return k0, k1
 
 
-def scores(query, k_idx, k_packed, k_scales, theta, query_pos=None, key_positions=None):
-    """scorer.py:115-208 (pre-RoPE).  query [B,QH,D]; k_* [B,S,KVH,F] / [B,S,KVH].
+def scores(query, k_idx, k_packed, k_scales, theta, query_pos=None, key_positions=None, coeff_bits=4, pre_rope=True):
+    """scorer.py:115-208.  query [B,QH,D]; k_* [B,S,KVH,F] / [B,S,KVH].  Post-RoPE is the
+    same sum with every phase zero (scorer.py:201-203).
 
     The phase is the float32 product float32(pos_k - pos_q) * theta, exactly as
     the reference forms it; everything after that is float64 here.
@@ -84,9 +94,11 @@ def scores(query, k_idx, k_packed, k_scales, theta, query_pos=None, key_position
         key_positions = np.broadcast_to(np.arange(S), (B, S))
     if query_pos is None:
         query_pos = np.full((B,), S)
-    k0, k1 = unpack_coeffs(k_packed, k_scales)
+    k0, k1 = unpack_coeffs(k_packed, k_scales, coeff_bits)
     delta = (np.asarray(key_positions).astype(np.float32)
              - np.asarray(query_pos).astype(np.float32)[:, None])            # [B,S]
+    if not pre_rope:
+        delta = np.zeros_like(delta)
     idx = np.asarray(k_idx).astype(np.int64)
     phase = (delta[:, :, None, None] * theta.astype(np.float32)[idx]).astype(np.float32)
     cos, sin = np.cos(phase.astype(np.float64)), np.sin(phase.astype(np.float64))
@@ -103,9 +115,9 @@ def scores(query, k_idx, k_packed, k_scales, theta, query_pos=None, key_position
     return out * (1.0 / math.sqrt(D))
 
 
-def decode_step(query, k_enc, v_enc, theta, query_pos=None, key_positions=None):
+def decode_step(query, k_enc, v_enc, theta, query_pos=None, key_positions=None, coeff_bits=4, pre_rope=True):
     """attention.py:186-280 -> float32 [B,QH,D]."""
-    sc = scores(query, *k_enc, theta, query_pos, key_positions)
+    sc = scores(query, *k_enc, theta, query_pos, key_positions, coeff_bits, pre_rope)
     B, QH, S = sc.shape
     v_idx, v_packed, v_scales = v_enc
     KVH, F = v_idx.shape[2:]
@@ -113,7 +125,7 @@ def decode_step(query, k_enc, v_enc, theta, query_pos=None, key_positions=None):
     D = np.asarray(query).shape[-1]
     w = np.exp(sc - sc.max(-1, keepdims=True))
     w /= w.sum(-1, keepdims=True)
-    v0, v1 = unpack_coeffs(v_packed, v_scales)
+    v0, v1 = unpack_coeffs(v_packed, v_scales, coeff_bits)
     out = np.zeros((B, QH, D), np.float64)
     for b in range(B):
         for qh in range(QH):

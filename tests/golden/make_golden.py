@@ -160,6 +160,34 @@ def tri():
          out_far=out_far, scores_far=sc_far)
 
 
+def tri_modes():
+    """The encoder's other coefficient formats (8-bit codes, plain fp16) and post-RoPE scoring, on the
+    inputs of tri_f12_int4.npz (keys, values, query and positions are read from there): encodings, one decode step far from the keys, and the pre-softmax scores."""
+    g = torch.Generator().manual_seed(2)
+    B, S, H = 2, 200, 2
+    s_i = torch.exp(-torch.arange(64, dtype=torch.float32) / 16.0)
+    scale = torch.stack([s_i[torch.randperm(64, generator=g)] for _ in range(H)])
+    keys = (torch.randn(B, S, H, 64, 2, generator=g) * scale[None, None, :, :, None]).reshape(B, S, H, 128).half()
+    values = torch.randn(B, S, H, 128, generator=g).half()
+    q = torch.randn(B, 8, 128, generator=g).half()
+    qpos = torch.tensor([131072, 70000])
+    kpos = torch.stack([torch.arange(131072 - S, 131072), torch.arange(0, 3 * S, 3)])
+    out = {}
+    for name, bits, pre in (("c8", 8, True), ("c16", 16, True), ("post4", 4, False), ("post8", 8, False)):
+        cfg = TriAttentionConfig(head_dim=128, num_freqs=12, coeff_bits=bits, num_kv_heads=2,
+                                 num_query_heads=8, rope_base=1_000_000.0, pre_rope=pre)
+        tri = TriAttention(cfg, device="cpu")
+        k_enc, v_enc = tri.encode_kv(keys, values)
+        out.update({f"{name}_k_indices": k_enc.indices, f"{name}_k_packed": k_enc.packed, f"{name}_k_scales": k_enc.scales,
+                    f"{name}_v_indices": v_enc.indices, f"{name}_v_packed": v_enc.packed, f"{name}_v_scales": v_enc.scales,
+                    f"{name}_out_far": tri.decode_step(q, k_enc, v_enc, qpos, kpos),
+                    f"{name}_out_default": tri.decode_step(q, k_enc, v_enc),
+                    f"{name}_scores_far": tri.scorer.score(q, k_enc, qpos, kpos)})
+    base = np.load(os.path.join(HERE, "tri_f12_int4.npz"))      # same seeded inputs: stored once, there
+    assert np.array_equal(base["keys"], keys.numpy()) and np.array_equal(base["query"], q.numpy())
+    save("tri_f12_modes.npz", **out)
+
+
 def block_select():
     """The reference's BlockSelector on a seeded paged cache: representatives from the packed keys,
     scores, filtered tables (ties are improbable with random data)."""
@@ -211,3 +239,4 @@ if __name__ == "__main__":
     paged_attention()
     hybrid()
     tri()
+    tri_modes()

@@ -228,3 +228,57 @@ def test_paged_decode_query_positions_and_block_ops():
     assert torch.equal(out3[0], out[0]) and not torch.equal(out3[1], out[1])
     stats = cache.memory_stats()
     assert stats["total_tokens"] == 364 and stats["used_blocks"] == 19 + 4
+
+
+@pytest.mark.parametrize("name,bits,pre", (("c8", 8, True), ("c16", 16, True), ("post4", 4, False), ("post8", 8, False)))
+def test_coefficient_modes_and_post_rope_match_reference(name, bits, pre):
+    """8-bit and fp16 coefficients, post-RoPE scoring: encoder, decode step and scorer against reference fixtures."""
+    from aitherkvcache_b200.triattention import SpectralEncoding, TriAttention, TriAttentionConfig, TrigSeriesScorer
+    base, g = load_golden("tri_f12_int4.npz"), load_golden("tri_f12_modes.npz")
+    cfg = TriAttentionConfig(head_dim=128, num_freqs=12, coeff_bits=bits, num_kv_heads=2, num_query_heads=8,
+                             rope_base=1_000_000.0, pre_rope=pre)
+    tri = TriAttention(cfg, device="cuda")
+    k_enc, v_enc = tri.encode_kv(torch.from_numpy(base["keys"]).cuda(), torch.from_numpy(base["values"]).cuda())
+    for side, enc, x in (("k", k_enc, base["keys"]), ("v", v_enc, base["values"])):
+        clear = otri.rank_gap(x, 12) > 0
+        assert enc.packed.shape == g[f"{name}_{side}_packed"].shape
+        assert np.array_equal(enc.indices.cpu().numpy()[clear], g[f"{name}_{side}_indices"][clear])
+        assert np.array_equal(enc.packed.cpu().numpy()[clear].view(np.uint8), g[f"{name}_{side}_packed"][clear].view(np.uint8))
+        assert np.array_equal(enc.scales.cpu().numpy()[clear].view(np.uint16), g[f"{name}_{side}_scales"][clear].view(np.uint16))
+    gk = SpectralEncoding(*[torch.from_numpy(g[f"{name}_k_{f}"]).cuda() for f in ("indices", "packed", "scales")])
+    gv = SpectralEncoding(*[torch.from_numpy(g[f"{name}_v_{f}"]).cuda() for f in ("indices", "packed", "scales")])
+    q = torch.from_numpy(base["query"]).cuda()
+    qpos, kpos = torch.from_numpy(base["query_pos"]).cuda(), torch.from_numpy(base["key_positions"]).cuda()
+    assert np.abs(tri.decode_step(q, gk, gv).cpu().numpy() - g[f"{name}_out_default"]).max() < 2e-3
+    assert np.abs(tri.decode_step(q, gk, gv, qpos, kpos).cpu().numpy() - g[f"{name}_out_far"]).max() < 2e-3
+    sc = TrigSeriesScorer(cfg, device="cuda").score(q, gk, qpos, kpos)
+    assert np.abs(sc.cpu().numpy() - g[f"{name}_scores_far"]).max() < 5e-3
+    # the dense reconstruction of the encoder agrees with the oracle's coefficients
+    dense = tri.encoder.decode(gk).cpu().numpy()
+    k0, k1 = otri.unpack_coeffs(g[f"{name}_k_packed"], g[f"{name}_k_scales"], bits)
+    ids = g[f"{name}_k_indices"].astype(np.int64)
+    assert np.allclose(np.take_along_axis(dense[..., 0::2], ids, -1), k0, rtol=1e-6, atol=1e-6)     # torch's device division is 1 ulp off before the subtraction
+    assert np.allclose(np.take_along_axis(dense[..., 1::2], ids, -1), k1, rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("bits,pre", ((8, True), (16, True), (4, False), (16, False)))
+def test_coefficient_modes_benchmark_heads_vs_oracle(bits, pre):
+    """32Q/8KV heads, 1500 keys at the far end of a 128K context, every coefficient format, against the oracle
+    (4-bit post-RoPE goes through the record-lane kernel, the others through the dense-tile kernel)."""
+    from aitherkvcache_b200.triattention import TriAttention, TriAttentionConfig
+    B, S, H, QH = 2, 1500, 8, 32
+    cfg = TriAttentionConfig(head_dim=128, num_freqs=12, coeff_bits=bits, num_kv_heads=H, num_query_heads=QH,
+                             rope_base=1_000_000.0, pre_rope=pre)
+    tri = TriAttention(cfg, device="cuda")
+    keys, values, g = _synthetic(B, S, H, seed=21)
+    q = torch.randn(B, QH, 128, generator=g).half()
+    k_enc, v_enc = tri.encode_kv(keys.cuda(), values.cuda())
+    kpos = torch.arange(131072 - S, 131072).unsqueeze(0).expand(B, -1).contiguous()
+    qpos = torch.full((B,), 131072)
+    out = tri.decode_step(q.cuda(), k_enc, v_enc, qpos.cuda(), kpos.cuda()).cpu().numpy()
+    k_np, v_np = tuple(t.cpu().numpy() for t in k_enc), tuple(t.cpu().numpy() for t in v_enc)
+    ref = otri.decode_step(q.numpy(), k_np, v_np, tri._theta.cpu().numpy(), qpos.numpy(), kpos.numpy(), bits, pre)
+    assert np.abs(out - ref).max() < 2e-3
+    oi, op, osc = otri.encode(keys.numpy(), 12, bits)
+    clear = otri.rank_gap(keys.numpy(), 12) > 0
+    assert np.array_equal(k_np[0][clear], oi[clear]) and np.array_equal(k_np[1][clear].view(np.uint8), op[clear].view(np.uint8))

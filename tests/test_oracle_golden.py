@@ -215,3 +215,25 @@ def test_block_select_oracle_matches_the_reference():
     for s in range(fbt.shape[0]):
         n = (int(fcl[s]) + 15) // 16
         assert np.array_equal(fbt[s, :n], g["filtered_bt"][s, :n])
+
+
+@pytest.mark.parametrize("name,bits,pre", (("c8", 8, True), ("c16", 16, True), ("post4", 4, False), ("post8", 8, False)))
+def test_tri_oracle_coefficient_modes_and_post_rope(name, bits, pre):
+    """oracle/tri.py against the reference's 8-bit / fp16 coefficient formats and post-RoPE scoring."""
+    from oracle import tri as otri
+    base, g = load_golden("tri_f12_int4.npz"), load_golden("tri_f12_modes.npz")
+    for side, x in (("k", base["keys"]), ("v", base["values"])):
+        idx, packed, scales = otri.encode(x, 12, bits)
+        clear = otri.rank_gap(x, 12) > 0
+        assert np.array_equal(idx[clear], g[f"{name}_{side}_indices"][clear])
+        assert np.array_equal(packed[clear].view(np.uint8), g[f"{name}_{side}_packed"][clear].view(np.uint8))
+        assert np.array_equal(scales[clear].view(np.uint16), g[f"{name}_{side}_scales"][clear].view(np.uint16))
+    k_enc = tuple(g[f"{name}_k_{f}"] for f in ("indices", "packed", "scales"))
+    v_enc = tuple(g[f"{name}_v_{f}"] for f in ("indices", "packed", "scales"))
+    theta = base["theta"]
+    sc = otri.scores(base["query"], *k_enc, theta, base["query_pos"], base["key_positions"], bits, pre)
+    assert np.abs(sc - g[f"{name}_scores_far"]).max() < 2e-4
+    out = otri.decode_step(base["query"], k_enc, v_enc, theta, base["query_pos"], base["key_positions"], bits, pre)
+    assert np.abs(out - g[f"{name}_out_far"]).max() < 2e-5
+    out = otri.decode_step(base["query"], k_enc, v_enc, theta, coeff_bits=bits, pre_rope=pre)
+    assert np.abs(out - g[f"{name}_out_default"]).max() < 2e-5
