@@ -10,7 +10,7 @@
 // to a few float32 ulps, i.e. the fp16 outputs differ only where a value sits on a rounding tie.
 //
 // One persistent CTA of 16 warps per SM.  Thread (row, q) owns the 32 codes 32q..32q+31 of a row:
-// it prefetches their 4*BITS bytes two tiles ahead into registers, turns them into the two fp16
+// it prefetches their 4*BITS bytes two tiles ahead into registers (one 16-byte load for 4-bit rows), turns them into the two fp16
 // operand rows (per-lane table: code -> (c1, c2)) in the 128-byte-swizzled K-major layout, and
 // the MMAs of tile t run while the warps unpack tile t+1 and write out tile t-1 from the other
 // half of tensor memory (tcgen05.ld: one thread per vector, 32 consecutive outputs = 64 bytes).
@@ -140,14 +140,21 @@ tq_decode_tc_kernel(const uint8_t* __restrict__ packed, int64_t p_stride_row, co
   const int w4 = warp & 3, colq = warp >> 2, erow = w4 * 32 + lane;
 
   uint32_t cw[BITS];      // packed bytes of the tile to unpack next
-  auto prefetch = [&](int t) {
+  uint32_t cw_nx[BITS];   // ... and of the tile after it, in flight while this one is unpacked
+  const bool vec_rows = BITS == 4 && (p_stride_row & 15) == 0 && (reinterpret_cast<uintptr_t>(packed) & 15) == 0;
+  auto prefetch = [&](int t, uint32_t (&dst)[BITS]) {
     const int64_t n = tile_row0(t) + urow;
 #pragma unroll
-    for (int k = 0; k < BITS; ++k) cw[k] = 0u;
+    for (int k = 0; k < BITS; ++k) dst[k] = 0u;
     if (t < n_my && n < n_rows) {
       const uint32_t* src = reinterpret_cast<const uint32_t*>(packed + n * p_stride_row + 4 * BITS * uq);
+      if (BITS == 4 && vec_rows) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(src));
+        dst[0] = v.x; dst[1] = v.y; dst[2 % BITS] = v.z; dst[3 % BITS] = v.w;
+      } else {
 #pragma unroll
-      for (int k = 0; k < BITS; ++k) cw[k] = __ldg(src + k);
+        for (int k = 0; k < BITS; ++k) dst[k] = __ldg(src + k);
+      }
     }
   };
   auto unpack = [&](int t) {      // registers cw -> operand buffers of stage t & 1
@@ -166,10 +173,14 @@ tq_decode_tc_kernel(const uint8_t* __restrict__ packed, int64_t p_stride_row, co
     sts128(a1 + (((u_chunk0 + 3) ^ u_swz) << 4), c1); sts128(a2 + (((u_chunk0 + 3) ^ u_swz) << 4), c2);
   };
 
-  prefetch(0);
+  prefetch(0, cw);
   if (n_my > 0) unpack(0);
-  prefetch(1);
+  prefetch(1, cw);
   float nrm_cur = 0.f;
+  // 16-bit outputs leave through a transpose in shared memory, so that a store instruction of the warp covers
+  // eight 64-byte row segments instead of thirty-two 16-byte pieces.  The staging space is the part of the idle
+  // operand stage that this warp itself fills next (operand rows 8 warp .. 8 warp + 7, both K halves = 2 KB).
+  const uint32_t stg_lane = (uint32_t)((lane >> 4) * TC_HALF_BYTES + (lane & 15) * 64), stg_swz = (uint32_t)((lane >> 1) & 3);
 
   int gave_up = 0;
   for (int t = 0; t <= n_my; ++t) {
@@ -195,6 +206,7 @@ tq_decode_tc_kernel(const uint8_t* __restrict__ packed, int64_t p_stride_row, co
       }
       umma_commit(mbar_s + 8u * (uint32_t)(t & 1));
     }
+    prefetch(t + 2, cw_nx);
     float nrm_next = 0.f;
     if (have) {
       const int64_t n = tile_row0(t) + erow;
@@ -205,41 +217,55 @@ tq_decode_tc_kernel(const uint8_t* __restrict__ packed, int64_t p_stride_row, co
       if (!mbar_wait(mbar_s + 8u * (uint32_t)((t - 1) & 1), (uint32_t)(((t - 1) >> 1) & 1))) gave_up = 1;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     }
-    if (t + 1 < n_my && !gave_up) unpack(t + 1);
-    prefetch(t + 2);
     // ---- tile t-1: scale by the norm, convert, store ----
     if (t >= 1 && !gave_up) {
       uint32_t v[32];
       tmem_ld32(tmem_base + ((uint32_t)(w4 * 32) << 16) + (uint32_t)(((t - 1) & 1) * 128 + colq * 32), v);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       const int64_t n = tile_row0(t - 1) + erow;
-      if (n < n_rows) {
-        const float sc = nrm_cur * (1.0f / 1048576.0f);
-        if (out_dtype == AKV_F32) {
+      const float sc = nrm_cur * (1.0f / 1048576.0f);
+      if (out_dtype == AKV_F32) {
+        if (n < n_rows) {
           float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + n * 128 + colq * 32);
 #pragma unroll
           for (int k = 0; k < 8; ++k)
             dst[k] = make_float4(__uint_as_float(v[4 * k]) * sc, __uint_as_float(v[4 * k + 1]) * sc,
                                  __uint_as_float(v[4 * k + 2]) * sc, __uint_as_float(v[4 * k + 3]) * sc);
-        } else {
-          uint32_t h[16];
-#pragma unroll
-          for (int k = 0; k < 16; ++k) {
-            const float lo = __uint_as_float(v[2 * k]) * sc, hi = __uint_as_float(v[2 * k + 1]) * sc;
-            if (out_dtype == AKV_F16) {
-              __half2 p = __floats2half2_rn(lo, hi);
-              h[k] = *reinterpret_cast<uint32_t*>(&p);
-            } else {
-              __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
-              h[k] = *reinterpret_cast<uint32_t*>(&p);
-            }
-          }
-          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out) + n * 128 + colq * 32);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) dst[k] = make_uint4(h[4 * k], h[4 * k + 1], h[4 * k + 2], h[4 * k + 3]);
         }
+      } else {
+        uint32_t h[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+          const float lo = __uint_as_float(v[2 * k]) * sc, hi = __uint_as_float(v[2 * k + 1]) * sc;
+          if (out_dtype == AKV_F16) {
+            __half2 p = __floats2half2_rn(lo, hi);
+            h[k] = *reinterpret_cast<uint32_t*>(&p);
+          } else {
+            __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+            h[k] = *reinterpret_cast<uint32_t*>(&p);
+          }
+        }
+        const uint32_t stg = abuf_s + (uint32_t)((t + 1) & 1) * 2 * TC_OPER_BYTES + (uint32_t)warp * 1024u;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          sts128(stg + stg_lane + ((((uint32_t)c) ^ stg_swz) << 4), make_uint4(h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]));
+        __syncwarp();
+        const int64_t n0 = tile_row0(t - 1) + w4 * 32;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int r = 8 * k + (lane >> 2), c = lane & 3;       // row of the warp's 32, 16-byte piece of its 64 bytes
+          uint4 q;
+          const uint32_t a = stg + (uint32_t)((r >> 4) * TC_HALF_BYTES + (r & 15) * 64) + ((((uint32_t)c) ^ (uint32_t)((r >> 1) & 3)) << 4);
+          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "r"(a) : "memory");
+          if (n0 + r < n_rows)
+            *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out) + (n0 + r) * 128 + colq * 32 + c * 8) = q;
+        }
+        __syncwarp();        // the staging rows are this warp's to overwrite in unpack below
       }
     }
+    if (t + 1 < n_my && !gave_up) unpack(t + 1);
+#pragma unroll
+    for (int k = 0; k < BITS; ++k) cw[k] = cw_nx[k];
     nrm_cur = nrm_next;
   }
 
