@@ -9,13 +9,19 @@
 // result); the factor 2^-20 is folded into the norm.  Results agree with the float32 FMA kernel
 // to a few float32 ulps, i.e. the fp16 outputs differ only where a value sits on a rounding tie.
 //
-// One persistent CTA of 16 warps per SM.  Thread (row, q) owns the 32 codes 32q..32q+31 of a row:
-// it prefetches their 4*BITS bytes two tiles ahead into registers (one 16-byte load for 4-bit rows), turns them into the two fp16
-// operand rows (per-lane table: code -> (c1, c2)) in the 128-byte-swizzled K-major layout, and
-// the MMAs of tile t run while the warps unpack tile t+1 and write out tile t-1 from the other
-// half of tensor memory (tcgen05.ld: one thread per vector, 32 consecutive outputs = 64 bytes).
-// The wait on the MMA barrier is bounded; a wait that gives up sets g_tc_decode_status and the
-// CTA leaves after releasing its tensor memory.
+// One persistent CTA per SM: 16 worker warps and one warp whose first lane issues the MMAs.  Worker thread
+// (row, q) owns the 32 codes 32q..32q+31 of a row: it prefetches their 4*BITS bytes a tile ahead into registers
+// (one 16-byte load for 4-bit rows), turns them into the two fp16 operand rows (per-lane table: code -> (c1, c2))
+// in the 128-byte-swizzled K-major layout of operand stage t % 2, and writes out tile t-1 from its half of
+// tensor memory (tcgen05.ld: one thread per vector, 32 consecutive outputs).  Nothing in the loop is a CTA-wide
+// barrier; the hand-overs are mbarriers:
+//   full[s]      16 warp arrivals: the operand rows of stage s are written          -> the MMA warp may issue
+//   mma_done[s]  tcgen05.commit: the tile's MMAs are complete                       -> stage s may be refilled,
+//                                                                                      accumulator s may be read
+//   acc_free[s]  16 warp arrivals: accumulator s has been loaded into registers     -> the MMA warp may reuse it
+// so warps drift apart and their unpack, load, convert and store phases overlap.
+// Every wait is bounded; a wait that gives up sets g_tc_decode_status and a shared flag that ends all loops,
+// and the CTA leaves after releasing its tensor memory.
 #include "tq_rowmap.cuh"
 #include "umma.cuh"
 
@@ -25,6 +31,7 @@ namespace {
 __device__ int g_tc_decode_status;          // 1: a wait on the MMA barrier gave up
 __device__ int g_tc_decode_withhold = -1;   // test hook: CTA 0 issues neither the MMAs nor the commit of this tile
 
+constexpr int DT_THREADS = 17 * 32;                    // 16 worker warps + the MMA warp
 constexpr int DT_TERMS_R = 0;                          // R1, R2: 2 operands
 constexpr int DT_ABUF = 2 * TC_OPER_BYTES;             // 2 stages x (c1, c2) operands
 constexpr int DT_LUT = DT_ABUF + 4 * TC_OPER_BYTES;    // 16 entries x 128 B
@@ -62,7 +69,7 @@ __device__ __forceinline__ void sts128(uint32_t addr, const uint4& v) {
 }
 
 template <int BITS>
-__global__ void __launch_bounds__(512, 1)
+__global__ void __launch_bounds__(DT_THREADS, 1)
 tq_decode_tc_kernel(const uint8_t* __restrict__ packed, int64_t p_stride_row, const float* __restrict__ norms,
                     int64_t n_rows, const float* __restrict__ rot, const float* __restrict__ centroids,
                     void* __restrict__ out, int out_dtype) {
@@ -71,17 +78,23 @@ tq_decode_tc_kernel(const uint8_t* __restrict__ packed, int64_t p_stride_row, co
   const uint32_t base_s = (raw_s + 1023u) & ~1023u;
   uint8_t* base = smem_raw + (base_s - raw_s);
   uint8_t* rterms = base + DT_TERMS_R;
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(base + DT_MISC);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mbar + 3);   // mbar[2]: drain barrier
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(base + DT_MISC);   // full[2], mma_done[2], acc_free[2], drain
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mbar + 7);
+  const uint32_t failed_s = base_s + DT_MISC + 60;
   const uint32_t abuf_s = base_s + DT_ABUF, lut_s = base_s + DT_LUT, mbar_s = base_s + DT_MISC;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
   // ---------------- one-time setup ----------------
   if (tid == 0) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(mbar_s));
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(mbar_s + 8));
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(mbar_s + 16));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 16;" :: "r"(mbar_s));          // full[0]
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 16;" :: "r"(mbar_s + 8));      // full[1]
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(mbar_s + 16));      // mma_done[0]
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(mbar_s + 24));      // mma_done[1]
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 16;" :: "r"(mbar_s + 32));     // acc_free[0]
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 16;" :: "r"(mbar_s + 40));     // acc_free[1]
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(mbar_s + 48));      // drain
+    asm volatile("st.shared.u32 [%0], %1;" :: "r"(failed_s), "r"(0u) : "memory");
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   const int withhold = blockIdx.x == 0 ? g_tc_decode_withhold : -1;
@@ -96,12 +109,12 @@ tq_decode_tc_kernel(const uint8_t* __restrict__ packed, int64_t p_stride_row, co
   // XOR on the staging column keeps both passes free of bank conflicts.
   {
     float* stg = reinterpret_cast<float*>(base + DT_ABUF);
-    for (int e = tid; e < 128 * 128; e += 512) {
+    for (int e = tid; e < 128 * 128; e += DT_THREADS) {
       const int i = e >> 7, j = e & 127;
       stg[i * 128 + (j ^ (i & 31))] = rot[e];
     }
     __syncthreads();
-    for (int e = tid; e < 128 * 128; e += 512) {
+    for (int e = tid; e < 128 * 128; e += DT_THREADS) {
       const int j = e >> 7, i = e & 127;
       const float r = stg[i * 128 + (j ^ (i & 31))] * 1024.0f;
       const uint32_t off = tc_operand_offset(j, i);
@@ -111,7 +124,7 @@ tq_decode_tc_kernel(const uint8_t* __restrict__ packed, int64_t p_stride_row, co
     }
   }
   // table: code -> half2(c1, c2), one copy per lane
-  for (int e = tid; e < (1 << BITS) * 32; e += 512) {
+  for (int e = tid; e < (1 << BITS) * 32; e += DT_THREADS) {
     const float c = centroids[e >> 5] * 1024.0f;
     const __half h1 = __float2half_rn(c), h2 = __float2half_rn(c - __half2float(h1));
     *reinterpret_cast<uint32_t*>(base + DT_LUT + (e >> 5) * 128 + (e & 31) * 4) =
@@ -173,110 +186,137 @@ tq_decode_tc_kernel(const uint8_t* __restrict__ packed, int64_t p_stride_row, co
     sts128(a1 + (((u_chunk0 + 3) ^ u_swz) << 4), c1); sts128(a2 + (((u_chunk0 + 3) ^ u_swz) << 4), c2);
   };
 
-  prefetch(0, cw);
-  if (n_my > 0) unpack(0);
-  prefetch(1, cw);
-  float nrm_cur = 0.f;
-  // 16-bit outputs leave through a transpose in shared memory, so that a store instruction of the warp covers
-  // eight 64-byte row segments instead of thirty-two 16-byte pieces.  The staging space is the part of the idle
-  // operand stage that this warp itself fills next (operand rows 8 warp .. 8 warp + 7, both K halves = 2 KB).
-  const uint32_t stg_lane = (uint32_t)((lane >> 4) * TC_HALF_BYTES + (lane & 15) * 64), stg_swz = (uint32_t)((lane >> 1) & 3);
+  // Bounded wait; once one wait of the CTA has run out, the others return at once.
+  auto wait = [&](uint32_t bar, uint32_t parity) -> bool {
+    if (lds_u32(failed_s) != 0u) return false;
+    if (mbar_wait(bar, parity)) return true;
+    g_tc_decode_status = 1;
+    asm volatile("st.shared.u32 [%0], %1;" :: "r"(failed_s), "r"(1u) : "memory");
+    return false;
+  };
+  // the same for a whole warp, with one answer for all its lanes
+  auto wait_warp = [&](uint32_t bar, uint32_t parity) -> bool { return __all_sync(0xffffffffu, wait(bar, parity)); };
+  const uint32_t full_s = mbar_s, done_s = mbar_s + 16, free_s = mbar_s + 32, drain_s = mbar_s + 48;
 
-  int gave_up = 0;
-  for (int t = 0; t <= n_my; ++t) {
-    const bool have = t < n_my;
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // this thread's operand stores
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    if (__syncthreads_or(gave_up)) { gave_up = 1; break; }
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-
-    // ---- tile t: c1 R1 + c1 R2 + c2 R1, issued by one thread ----
-    if (have && tid == 0 && t != withhold) {
-      const uint32_t a_s = abuf_s + (uint32_t)(t & 1) * 2 * TC_OPER_BYTES;
-      const uint32_t d0 = tmem_base + (uint32_t)(t & 1) * 128;
+  if (warp == 16) {
+    // ---- MMA warp: tile t = c1 R1 + c1 R2 + c2 R1 as soon as its operand rows are there and its accumulator is free ----
+    if (lane == 0) {
+      for (int t = 0; t < n_my; ++t) {
+        const uint32_t s = (uint32_t)(t & 1), ph = (uint32_t)((t >> 1) & 1);
+        if (!wait(full_s + 8u * s, ph)) break;
+        if (t >= 2 && !wait(free_s + 8u * s, (uint32_t)(((t - 2) >> 1) & 1))) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (t == withhold) continue;
+        const uint32_t a_s = abuf_s + s * 2 * TC_OPER_BYTES;
+        const uint32_t d0 = tmem_base + s * 128;
 #pragma unroll
-      for (int pass = 0; pass < 3; ++pass) {
-        const uint32_t ao = pass == 2 ? TC_OPER_BYTES : 0u, bo = pass == 1 ? TC_OPER_BYTES : 0u;
+        for (int pass = 0; pass < 3; ++pass) {
+          const uint32_t ao = pass == 2 ? TC_OPER_BYTES : 0u, bo = pass == 1 ? TC_OPER_BYTES : 0u;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t koff = (uint32_t)((kk >> 2) * TC_HALF_BYTES + (kk & 3) * 32);
-          umma_f16(d0, umma_desc(a_s + ao + koff), umma_desc(base_s + DT_TERMS_R + bo + koff), IDESC,
-                   (uint32_t)((pass | kk) != 0));
-        }
-      }
-      umma_commit(mbar_s + 8u * (uint32_t)(t & 1));
-    }
-    prefetch(t + 2, cw_nx);
-    float nrm_next = 0.f;
-    if (have) {
-      const int64_t n = tile_row0(t) + erow;
-      if (n < n_rows) nrm_next = __ldg(norms + n);
-    }
-    // ---- tile t-1: wait for its MMAs (frees its operand stage, fills its accumulator) ----
-    if (t >= 1) {
-      if (!mbar_wait(mbar_s + 8u * (uint32_t)((t - 1) & 1), (uint32_t)(((t - 1) >> 1) & 1))) gave_up = 1;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    }
-    // ---- tile t-1: scale by the norm, convert, store ----
-    if (t >= 1 && !gave_up) {
-      uint32_t v[32];
-      tmem_ld32(tmem_base + ((uint32_t)(w4 * 32) << 16) + (uint32_t)(((t - 1) & 1) * 128 + colq * 32), v);
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      const int64_t n = tile_row0(t - 1) + erow;
-      const float sc = nrm_cur * (1.0f / 1048576.0f);
-      if (out_dtype == AKV_F32) {
-        if (n < n_rows) {
-          float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + n * 128 + colq * 32);
-#pragma unroll
-          for (int k = 0; k < 8; ++k)
-            dst[k] = make_float4(__uint_as_float(v[4 * k]) * sc, __uint_as_float(v[4 * k + 1]) * sc,
-                                 __uint_as_float(v[4 * k + 2]) * sc, __uint_as_float(v[4 * k + 3]) * sc);
-        }
-      } else {
-        uint32_t h[16];
-#pragma unroll
-        for (int k = 0; k < 16; ++k) {
-          const float lo = __uint_as_float(v[2 * k]) * sc, hi = __uint_as_float(v[2 * k + 1]) * sc;
-          if (out_dtype == AKV_F16) {
-            __half2 p = __floats2half2_rn(lo, hi);
-            h[k] = *reinterpret_cast<uint32_t*>(&p);
-          } else {
-            __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
-            h[k] = *reinterpret_cast<uint32_t*>(&p);
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t koff = (uint32_t)((kk >> 2) * TC_HALF_BYTES + (kk & 3) * 32);
+            umma_f16(d0, umma_desc(a_s + ao + koff), umma_desc(base_s + DT_TERMS_R + bo + koff), IDESC,
+                     (uint32_t)((pass | kk) != 0));
           }
         }
-        const uint32_t stg = abuf_s + (uint32_t)((t + 1) & 1) * 2 * TC_OPER_BYTES + (uint32_t)warp * 1024u;
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-          sts128(stg + stg_lane + ((((uint32_t)c) ^ stg_swz) << 4), make_uint4(h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]));
-        __syncwarp();
-        const int64_t n0 = tile_row0(t - 1) + w4 * 32;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int r = 8 * k + (lane >> 2), c = lane & 3;       // row of the warp's 32, 16-byte piece of its 64 bytes
-          uint4 q;
-          const uint32_t a = stg + (uint32_t)((r >> 4) * TC_HALF_BYTES + (r & 15) * 64) + ((((uint32_t)c) ^ (uint32_t)((r >> 1) & 3)) << 4);
-          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "r"(a) : "memory");
-          if (n0 + r < n_rows)
-            *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out) + (n0 + r) * 128 + colq * 32 + c * 8) = q;
-        }
-        __syncwarp();        // the staging rows are this warp's to overwrite in unpack below
+        umma_commit(done_s + 8u * s);
       }
     }
-    if (t + 1 < n_my && !gave_up) unpack(t + 1);
+    __syncwarp();
+  } else {
+    // ---- worker warps ----
+    // 16-bit outputs leave through a transpose in shared memory, so that a store instruction of the warp covers
+    // eight 64-byte row segments instead of thirty-two 16-byte pieces.  The staging space is the part of the idle
+    // operand stage that this warp itself fills next (operand rows 8 warp .. 8 warp + 7, both K halves = 2 KB).
+    const uint32_t stg_lane = (uint32_t)((lane >> 4) * TC_HALF_BYTES + (lane & 15) * 64), stg_swz = (uint32_t)((lane >> 1) & 3);
+    prefetch(0, cw);
+    float nrm_cur = 0.f;
+    for (int t = 0; t <= n_my; ++t) {
+      const bool have = t < n_my;
+      prefetch(t + 1, cw_nx);
+      float nrm_next = 0.f;
+      if (have) {
+        const int64_t n = tile_row0(t) + erow;
+        if (n < n_rows) nrm_next = __ldg(norms + n);
+        // ---- tile t: operand rows into stage t % 2, free once the MMAs of tile t-2 are complete ----
+        if (t >= 2 && !wait_warp(done_s + 8u * (uint32_t)(t & 1), (uint32_t)(((t - 2) >> 1) & 1))) break;
+        unpack(t);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(full_s + 8u * (uint32_t)(t & 1)) : "memory");
+      }
+      // ---- tile t-1: out of tensor memory, scale by the norm, convert, store ----
+      if (t >= 1) {
+        const uint32_t s1 = (uint32_t)((t - 1) & 1);
+        if (!wait_warp(done_s + 8u * s1, (uint32_t)(((t - 1) >> 1) & 1))) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        uint32_t v[32];
+        tmem_ld32(tmem_base + ((uint32_t)(w4 * 32) << 16) + (uint32_t)(s1 * 128 + colq * 32), v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(free_s + 8u * s1) : "memory");
+        const int64_t n = tile_row0(t - 1) + erow;
+        const float sc = nrm_cur * (1.0f / 1048576.0f);
+        if (out_dtype == AKV_F32) {
+          if (n < n_rows) {
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + n * 128 + colq * 32);
 #pragma unroll
-    for (int k = 0; k < BITS; ++k) cw[k] = cw_nx[k];
-    nrm_cur = nrm_next;
+            for (int k = 0; k < 8; ++k)
+              dst[k] = make_float4(__uint_as_float(v[4 * k]) * sc, __uint_as_float(v[4 * k + 1]) * sc,
+                                   __uint_as_float(v[4 * k + 2]) * sc, __uint_as_float(v[4 * k + 3]) * sc);
+          }
+        } else {
+          uint32_t h[16];
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {
+            const float lo = __uint_as_float(v[2 * k]) * sc, hi = __uint_as_float(v[2 * k + 1]) * sc;
+            if (out_dtype == AKV_F16) {
+              __half2 p = __floats2half2_rn(lo, hi);
+              h[k] = *reinterpret_cast<uint32_t*>(&p);
+            } else {
+              __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+              h[k] = *reinterpret_cast<uint32_t*>(&p);
+            }
+          }
+          // stage (t + 1) % 2 is idle: the MMAs of tile t-1 are complete and this warp refills its rows only in
+          // the next iteration
+          const uint32_t stg = abuf_s + (uint32_t)((t + 1) & 1) * 2 * TC_OPER_BYTES + (uint32_t)warp * 1024u;
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            sts128(stg + stg_lane + ((((uint32_t)c) ^ stg_swz) << 4), make_uint4(h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]));
+          __syncwarp();
+          const int64_t n0 = tile_row0(t - 1) + w4 * 32;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int r = 8 * k + (lane >> 2), c = lane & 3;       // row of the warp's 32, 16-byte piece of its 64 bytes
+            uint4 q;
+            const uint32_t a = stg + (uint32_t)((r >> 4) * TC_HALF_BYTES + (r & 15) * 64) + ((((uint32_t)c) ^ (uint32_t)((r >> 1) & 3)) << 4);
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "r"(a) : "memory");
+            if (n0 + r < n_rows)
+              *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out) + (n0 + r) * 128 + colq * 32 + c * 8) = q;
+          }
+          __syncwarp();        // the staging rows are this warp's to overwrite in the next unpack
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < BITS; ++k) cw[k] = cw_nx[k];
+      nrm_cur = nrm_next;
+    }
   }
 
-  // as in the encoder: drain whatever this thread did issue before the columns are released
-  int leak = 0;
-  if (gave_up && tid == 0) {
-    umma_commit(mbar_s + 16);
-    leak = mbar_wait(mbar_s + 16, 0u) ? 0 : 1;
-    g_tc_decode_status = 1 + leak;
-  }
+  // A CTA in which a wait gave up may still have MMAs in flight: before the columns go back, the issuing thread
+  // commits once more on the drain barrier (it completes when every MMA that thread issued has) and waits,
+  // bounded.  Only if that wait gives up too are the columns kept (status 2): lost to this SM until the context
+  // ends, which is better than freeing them under an MMA.
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  int leak = 0;
+  if (warp == 16 && lane == 0 && lds_u32(failed_s) != 0u) {
+    umma_commit(drain_s);
+    leak = mbar_wait(drain_s, 0u) ? 0 : 1;
+    if (leak) g_tc_decode_status = 2;
+  }
   leak = __syncthreads_or(leak);
   if (warp == 0 && !leak) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" :: "r"(tmem_base) : "memory");
@@ -291,7 +331,7 @@ int launch_dtc(const uint8_t* packed, int64_t ps, const float* norms, int64_t n_
   if (e != cudaSuccess) return fail((int)e, "decode: smem attribute: %s", cudaGetErrorString(e));
   int64_t tiles = (n_rows + 127) / 128;
   int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  kern<<<grid, 512, DT_SMEM, st>>>(packed, ps, norms, n_rows, rot, cent, out, out_dtype);
+  kern<<<grid, DT_THREADS, DT_SMEM, st>>>(packed, ps, norms, n_rows, rot, cent, out, out_dtype);
   return check_launch("tq_decode_tc_kernel");
 }
 
