@@ -24,6 +24,9 @@
 // and the CTA leaves after releasing its tensor memory.
 #include "tq_rowmap.cuh"
 #include "umma.cuh"
+#include <cuda.h>
+#include <stdlib.h>
+#include <string.h>
 
 namespace akv {
 namespace {
@@ -72,7 +75,7 @@ template <int BITS>
 __global__ void __launch_bounds__(DT_THREADS, 1)
 tq_decode_tc_kernel(const uint8_t* __restrict__ packed, int64_t p_stride_row, const float* __restrict__ norms,
                     int64_t n_rows, const float* __restrict__ rot, const float* __restrict__ centroids,
-                    void* __restrict__ out, int out_dtype) {
+                    void* __restrict__ out, int out_dtype, const __grid_constant__ CUtensorMap out_map, int tma_store) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_s = smem_u32(smem_raw);
   const uint32_t base_s = (raw_s + 1023u) & ~1023u;
@@ -240,6 +243,10 @@ tq_decode_tc_kernel(const uint8_t* __restrict__ packed, int64_t p_stride_row, co
         if (n < n_rows) nrm_next = __ldg(norms + n);
         // ---- tile t: operand rows into stage t % 2, free once the MMAs of tile t-2 are complete ----
         if (t >= 2 && !wait_warp(done_s + 8u * (uint32_t)(t & 1), (uint32_t)(((t - 2) >> 1) & 1))) break;
+        if (tma_store) {      // the bulk stores of tile t-2 have read this warp's staging rows (issued an iteration ago)
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          __syncwarp();
+        }
         unpack(t);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
@@ -285,24 +292,42 @@ tq_decode_tc_kernel(const uint8_t* __restrict__ packed, int64_t p_stride_row, co
 #pragma unroll
           for (int c = 0; c < 4; ++c)
             sts128(stg + stg_lane + ((((uint32_t)c) ^ stg_swz) << 4), make_uint4(h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]));
-          __syncwarp();
           const int64_t n0 = tile_row0(t - 1) + w4 * 32;
+          if (tma_store) {
+            // the staged rows are in the 64-byte-swizzled layout of the output map: two bulk tensor stores of 16 rows
+            // x 64 bytes (rows past the end of the output are dropped by the copy engine), no load / store instructions
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+              const int x = colq * 32, y = (int)n0;
+              if (n0 < n_rows)
+                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                             :: "l"(&out_map), "r"(x), "r"(y), "r"(stg) : "memory");
+              if (n0 + 16 < n_rows)
+                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                             :: "l"(&out_map), "r"(x), "r"(y + 16), "r"(stg + (uint32_t)TC_HALF_BYTES) : "memory");
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+          } else {
+            __syncwarp();
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const int r = 8 * k + (lane >> 2), c = lane & 3;       // row of the warp's 32, 16-byte piece of its 64 bytes
-            uint4 q;
-            const uint32_t a = stg + (uint32_t)((r >> 4) * TC_HALF_BYTES + (r & 15) * 64) + ((((uint32_t)c) ^ (uint32_t)((r >> 1) & 3)) << 4);
-            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "r"(a) : "memory");
-            if (n0 + r < n_rows)
-              *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out) + (n0 + r) * 128 + colq * 32 + c * 8) = q;
+            for (int k = 0; k < 4; ++k) {
+              const int r = 8 * k + (lane >> 2), c = lane & 3;       // row of the warp's 32, 16-byte piece of its 64 bytes
+              uint4 q;
+              const uint32_t a = stg + (uint32_t)((r >> 4) * TC_HALF_BYTES + (r & 15) * 64) + ((((uint32_t)c) ^ (uint32_t)((r >> 1) & 3)) << 4);
+              asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "r"(a) : "memory");
+              if (n0 + r < n_rows)
+                *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out) + (n0 + r) * 128 + colq * 32 + c * 8) = q;
+            }
+            __syncwarp();        // the staging rows are this warp's to overwrite in the next unpack
           }
-          __syncwarp();        // the staging rows are this warp's to overwrite in the next unpack
         }
       }
 #pragma unroll
       for (int k = 0; k < BITS; ++k) cw[k] = cw_nx[k];
       nrm_cur = nrm_next;
     }
+    if (tma_store && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");    // before the CTA's shared memory goes
   }
 
   // A CTA in which a wait gave up may still have MMAs in flight: before the columns go back, the issuing thread
@@ -323,6 +348,39 @@ tq_decode_tc_kernel(const uint8_t* __restrict__ packed, int64_t p_stride_row, co
   }
 }
 
+typedef CUresult (*dt_encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                       const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                       CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+dt_encode_tiled_fn dt_encoder() {
+  static dt_encode_tiled_fn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<dt_encode_tiled_fn>(p);
+    else
+      cudaGetLastError();
+  }
+  return fn;
+}
+
+// Map of a 16-bit output [n_rows][128] for stores of 16 rows x 32 elements out of 64-byte-swizzled shared memory.
+bool dt_out_map(void* out, int64_t n_rows, CUtensorMap* map) {
+  static const bool off = getenv("AKV_NO_TMA_STORE") != nullptr;
+  if (off || (reinterpret_cast<uintptr_t>(out) & 15) != 0 || n_rows >= (1ll << 31)) return false;
+  dt_encode_tiled_fn enc = dt_encoder();
+  if (enc == nullptr) return false;
+  const cuuint64_t dims[2] = {128, (cuuint64_t)n_rows};
+  const cuuint64_t strides[1] = {256};
+  const cuuint32_t box[2] = {32, 16}, ones[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, out, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int BITS>
 int launch_dtc(const uint8_t* packed, int64_t ps, const float* norms, int64_t n_rows, const float* rot,
                const float* cent, void* out, int out_dtype, cudaStream_t st) {
@@ -331,7 +389,10 @@ int launch_dtc(const uint8_t* packed, int64_t ps, const float* norms, int64_t n_
   if (e != cudaSuccess) return fail((int)e, "decode: smem attribute: %s", cudaGetErrorString(e));
   int64_t tiles = (n_rows + 127) / 128;
   int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  kern<<<grid, DT_THREADS, DT_SMEM, st>>>(packed, ps, norms, n_rows, rot, cent, out, out_dtype);
+  CUtensorMap map;
+  memset(&map, 0, sizeof(map));
+  const int tma_store = (out_dtype != AKV_F32 && dt_out_map(out, n_rows, &map)) ? 1 : 0;
+  kern<<<grid, DT_THREADS, DT_SMEM, st>>>(packed, ps, norms, n_rows, rot, cent, out, out_dtype, map, tma_store);
   return check_launch("tq_decode_tc_kernel");
 }
 
