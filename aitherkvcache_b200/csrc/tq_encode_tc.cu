@@ -16,13 +16,20 @@
 //     differs from the scalar kernels' value by a few float32 ulps; a code can differ only for
 //     a coordinate within ~2e-7 of a boundary.  Norms are bit-equal (same eight-lane order).
 //
-// One persistent CTA of 16 warps per SM.  Per tile: 16-byte cp.async copies fill a 32 KB
-// operand buffer in the 128-byte-swizzled K-major layout the MMA descriptors name; the
-// MMAs of tile t run while the warps compute the norms of tile t, start the copies of tile
-// t+1 and quantise tile t-1 out of its own tensor-memory columns (tcgen05.ld, one thread
-// per vector, 32 consecutive coordinates per load, so packing needs no exchange).
-// Every wait on the MMA barrier is bounded; a wait that gives up sets g_tc_status and the
-// CTA leaves after releasing its tensor memory.
+// One persistent CTA per SM: 16 worker warps and one warp whose first lane issues the MMAs.  Worker warp w owns
+// rows 8w .. 8w+7 of every tile on the input side: 16-byte cp.async copies bring them into a 32 KB operand buffer in the
+// 128-byte-swizzled K-major layout the MMA descriptors name (AHEAD tiles ahead), and four of its threads per row
+// compute the norm out of that buffer.  On the output side thread (row, quarter) quantises 32 consecutive coordinates
+// of its row out of tensor memory (tcgen05.ld, so packing needs no exchange).  No CTA-wide barrier in the loop; the
+// hand-overs are mbarriers:
+//   full[b]        16 warp arrivals: the rows of operand buffer b have landed            -> the MMA warp may issue
+//   norm_ready[i]  16 warp arrivals: norms, reciprocals and destinations of tile t's rows    -> quantisers of tile t
+//                  (i = t % 4) stored
+//   mma_done[s]    tcgen05.commit: the tile's MMAs are complete                           -> its operand buffer may be
+//                                                                                            refilled, accumulator s read
+//   acc_free[s]    16 warp arrivals: accumulator s has been loaded into registers         -> the MMA warp may reuse it
+// Every wait is bounded; a wait that gives up sets g_tc_status and a shared flag that ends all loops, and the CTA
+// leaves after releasing its tensor memory.
 #include "tq_rowmap.cuh"
 #include "umma.cuh"
 
@@ -31,8 +38,8 @@ namespace {
 
 constexpr int TC_CELLS = 128;
 constexpr int TC_LUT_BYTES = TC_CELLS * 32 * 8;   // every cell replicated once per lane
-constexpr int TC_RING = 8;                          // tiles whose destination rows are remembered
-constexpr int TC_TAIL_BYTES = TC_LUT_BYTES + 2 * 128 * 8 + TC_RING * 128 * 16 + 2 * 2 * 128 * 4 + 64 + 16 + 16;
+constexpr int TC_THREADS = 17 * 32;                 // 16 worker warps + the MMA warp
+constexpr int TC_TAIL_BYTES = TC_LUT_BYTES + 2 * 4 * 128 * 8 + 2 * 4 * 128 * 4 + 64 + 16 * 8 + 16 + 16;
 
 struct TcRow {
   int64_t src_off;   // element offset of the vector; < 0: beyond the last row
@@ -56,16 +63,61 @@ __device__ __forceinline__ float bits16_to_float(uint32_t h) {
   return __half2float(__ushort_as_half((unsigned short)h));
 }
 
-__device__ __forceinline__ TcRow make_row(const RowMap& m, int64_t n, int64_t n_rows) {
+// Position of a row that a thread follows from tile to tile: rows advance by a fixed step, so the (token, head)
+// split of the paged mode is kept by additions instead of a division per tile.
+struct TcCursor {
+  int64_t n, tok;
+  int head;
+};
+
+__device__ __forceinline__ TcCursor cursor_at(const RowMap& m, int64_t n) {
+  TcCursor c;
+  c.n = n;
+  if (m.slot_mapping == nullptr) { c.tok = n; c.head = 0; return c; }
+  c.tok = n / m.num_heads;
+  c.head = (int)(n - c.tok * m.num_heads);
+  return c;
+}
+
+__device__ __forceinline__ void cursor_advance(const RowMap& m, TcCursor& c, int64_t step, int64_t step_tok, int step_head) {
+  c.n += step;
+  if (m.slot_mapping == nullptr) { c.tok = c.n; return; }
+  c.tok += step_tok;
+  c.head += step_head;
+  if (c.head >= m.num_heads) { c.head -= m.num_heads; ++c.tok; }
+}
+
+// Element offset of the row's source vector; < 0: beyond the last row.
+__device__ __forceinline__ int64_t cursor_src(const RowMap& m, const TcCursor& c, int64_t n_rows) {
+  if (c.n >= n_rows) return -1;
+  return m.slot_mapping == nullptr ? c.n * m.x_stride_row : c.tok * m.x_stride_tok + c.head * m.x_stride_head;
+}
+
+// Where the row's codes and norm go (nullptr: skipped slot or beyond the last row).
+__device__ __forceinline__ TcRow cursor_dst(const RowMap& m, const TcCursor& c, int64_t n_rows) {
   TcRow r;
-  if (n >= n_rows) { r.src_off = -1; r.dst = nullptr; r.dst_norm = nullptr; return r; }
-  RowAddr a = map_row(m, n);
-  r.src_off = a.src_off; r.dst = a.dst; r.dst_norm = a.dst_norm;
+  r.src_off = -1; r.dst = nullptr; r.dst_norm = nullptr;
+  if (c.n >= n_rows) return r;
+  if (m.slot_mapping == nullptr) {
+    r.dst = m.packed + c.n * m.p_stride_row;
+    r.dst_norm = m.norms + c.n;
+    return r;
+  }
+  const int64_t slot = m.slot_mapping[c.tok];
+  if (slot < 0) return r;
+  int64_t blk;
+  if (slot < (1ll << 32)) blk = (int64_t)((uint32_t)slot / (uint32_t)m.block_size);     // no 64-bit division on the usual path
+  else blk = slot / m.block_size;
+  const int pos = (int)(slot - blk * m.block_size);
+  if (blk < m.max_blocks) {
+    r.dst = m.packed + blk * m.p_stride_blk + pos * m.p_stride_pos + c.head * m.p_stride_head;
+    r.dst_norm = m.norms + blk * m.n_stride_blk + pos * m.n_stride_pos + c.head * m.n_stride_head;
+  }
   return r;
 }
 
 template <int BITS, bool BF16>
-__global__ void __launch_bounds__(512, 1)
+__global__ void __launch_bounds__(TC_THREADS, 1)
 tq_encode_tc_kernel(RowMap m, int64_t n_rows, const float* __restrict__ rot_t,
                     const float* __restrict__ boundaries) {
   constexpr int TERMS = BF16 ? 3 : 2;
@@ -83,15 +135,15 @@ tq_encode_tc_kernel(RowMap m, int64_t n_rows, const float* __restrict__ rot_t,
   constexpr int AHEAD = NBUF - 1;
   uint8_t* tail = abuf + NBUF * TC_OPER_BYTES;
   float2* lut = reinterpret_cast<float2*>(tail);                 // [cells][32 lanes]
-  int64_t* src_ring = reinterpret_cast<int64_t*>(tail + TC_LUT_BYTES);            // [2][128]
-  uint8_t** dst_ring = reinterpret_cast<uint8_t**>(src_ring + 2 * 128);           // [TC_RING][128]
-  float** dstn_ring = reinterpret_cast<float**>(dst_ring + TC_RING * 128);        // [TC_RING][128]
-  float* rinv_s = reinterpret_cast<float*>(dstn_ring + TC_RING * 128);            // [2][128]
-  float* nrm_s = rinv_s + 256;                                   // [2][128]
-  float* bnd = nrm_s + 256;                                      // [16]
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(bnd + 16);        // [2] tile barriers, [1] drain barrier
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mbar + 3);
+  uint8_t** dstp_s = reinterpret_cast<uint8_t**>(tail + TC_LUT_BYTES);   // [4][128] where the codes of a row go
+  float** dstn_s = reinterpret_cast<float**>(dstp_s + 4 * 128);          // [4][128] ... and its norm
+  float* rinv_s = reinterpret_cast<float*>(dstn_s + 4 * 128);    // [4][128]
+  float* nrm_s = rinv_s + 4 * 128;                               // [4][128]
+  float* bnd = nrm_s + 4 * 128;                                  // [16]
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(bnd + 16);        // full[3], norm_ready[4], mma_done[2], acc_free[2], drain
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mbar + 16);
   int* simple_flag = reinterpret_cast<int*>(tmem_slot + 1);
+  uint32_t* failed_flag = tmem_slot + 2;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t terms_s = base_s;
@@ -101,9 +153,11 @@ tq_encode_tc_kernel(RowMap m, int64_t n_rows, const float* __restrict__ rot_t,
   // ---------------- one-time setup ----------------
   if (tid == 0) {
     *simple_flag = 1;
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(mbar_s));
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(mbar_s + 8));
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(mbar_s + 16));
+    *failed_flag = 0u;
+    for (int i = 0; i < 12; ++i) {     // full[0..2], norm_ready[0..3], mma_done[0..1], acc_free[0..1], drain
+      const uint32_t count = (i == 7 || i == 8 || i == 11) ? 1u : 16u;
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(mbar_s + 8u * (uint32_t)i), "r"(count));
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   const int withhold = blockIdx.x == 0 ? g_tc_withhold : -1;
@@ -119,12 +173,12 @@ tq_encode_tc_kernel(RowMap m, int64_t n_rows, const float* __restrict__ rot_t,
   // with j fastest; the XOR on the staging column keeps both passes free of bank conflicts.
   {
     float* stg = reinterpret_cast<float*>(abuf);
-    for (int e = tid; e < 128 * 128; e += 512) {
+    for (int e = tid; e < 128 * 128; e += TC_THREADS) {
       int j = e >> 7, i = e & 127;
       stg[j * 128 + (i ^ (j & 31))] = rot_t[e];
     }
     __syncthreads();
-    for (int e = tid; e < 128 * 128; e += 512) {
+    for (int e = tid; e < 128 * 128; e += TC_THREADS) {
       int i = e >> 7, j = e & 127;       // operand row i, K index j
       float r = stg[j * 128 + (i ^ (j & 31))] * PRESCALE;
       uint32_t off = (uint32_t)((j >> 6) * TC_HALF_BYTES + i * 128 + (((((j & 63) >> 3) ^ (i & 7)) << 4) | ((j & 7) << 1)));
@@ -168,7 +222,7 @@ tq_encode_tc_kernel(RowMap m, int64_t n_rows, const float* __restrict__ rot_t,
     }
     __syncthreads();
     // one copy per lane, 8 bytes apart: a warp's 32 lookups never share a bank
-    for (int e = tid; e < TC_CELLS * 32; e += 512) lut[e] = cells[e >> 5];
+    for (int e = tid; e < TC_CELLS * 32; e += TC_THREADS) lut[e] = cells[e >> 5];
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -184,120 +238,142 @@ tq_encode_tc_kernel(RowMap m, int64_t n_rows, const float* __restrict__ rot_t,
   const int64_t num_tiles = (n_rows + 127) >> 7;
   const int n_my = (int)((num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
 
-  auto issue_loads = [&](int t) {
-    const int64_t* rs = src_ring + (t & 1) * 128;
-    const uint32_t dst0 = abuf_s + (uint32_t)(t % NBUF) * TC_OPER_BYTES;
-#pragma unroll
-    for (int pass = 0; pass < 2; ++pass) {
-      const int r = (tid >> 3) + 64 * pass, c = tid & 7;
-      const int64_t off = rs[r];
-      const uint32_t nbytes = off >= 0 ? 16u : 0u;
-      const uint16_t* src = reinterpret_cast<const uint16_t*>(m.x) + (off >= 0 ? off : 0) + c * 8;
-      const uint32_t dst = dst0 + (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4));
-#pragma unroll
-      for (int h = 0; h < 2; ++h)
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
-                     :: "r"(dst + h * TC_HALF_BYTES), "l"(src + h * 64), "r"(nbytes) : "memory");
-    }
+  const uint32_t failed_s = smem_u32(failed_flag);
+  const uint32_t full_s = mbar_s, nready_s = mbar_s + 24, done_s = mbar_s + 56, free_s = mbar_s + 72, drain_s = mbar_s + 88;
+  // Bounded wait; once one wait of the CTA has run out, the others return at once.
+  auto wait = [&](uint32_t bar, uint32_t parity) -> bool {
+    if (lds_u32(failed_s) != 0u) return false;
+    if (mbar_wait(bar, parity)) return true;
+    g_tc_status = 1;
+    asm volatile("st.shared.u32 [%0], %1;" :: "r"(failed_s), "r"(1u) : "memory");
+    return false;
   };
-  // Row addresses of tile t, worked out by the last four warps one iteration before the
-  // tile's copies start (a barrier lies between): source offsets live for one iteration
-  // (2 slots), destinations until the tile's epilogue AHEAD + 2 iterations later.
-  auto note_rows = [&](int t) {
-    if (tid >= 384) {
-      const int r = tid - 384;
-      TcRow row = make_row(m, ((int64_t)blockIdx.x + (int64_t)t * gridDim.x) * 128 + r, n_rows);
-      src_ring[(t & 1) * 128 + r] = row.src_off;
-      dst_ring[(t & (TC_RING - 1)) * 128 + r] = row.dst;
-      dstn_ring[(t & (TC_RING - 1)) * 128 + r] = row.dst_norm;
-    }
-  };
+  auto wait_warp = [&](uint32_t bar, uint32_t parity) -> bool { return __all_sync(0xffffffffu, wait(bar, parity)); };
+  auto tile_row0 = [&](int t) { return ((int64_t)blockIdx.x + (int64_t)t * gridDim.x) * 128; };
 
-  // one commit group per tile slot, empty past the last tile, so that "all but the newest
-  // AHEAD - 1 groups" always means "up to tile t"
-  for (int t = 0; t < AHEAD; ++t) {
-    if (t < n_my) note_rows(t);
-    __syncthreads();
-    if (t < n_my) issue_loads(t);
-    asm volatile("cp.async.commit_group;" ::: "memory");
-  }
-  if (AHEAD < n_my) note_rows(AHEAD);
-
-  int gave_up = 0;
-  for (int t = 0; t <= n_my; ++t) {
-    const bool have = t < n_my;
-    if (have) {
-      asm volatile("cp.async.wait_group %0;" :: "n"(AHEAD - 1) : "memory");
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    if (__syncthreads_or(gave_up)) { gave_up = 1; break; }
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-
-    // ---- tile t: the whole rotation, issued by one thread ----
-    if (have && tid == 0 && t != withhold) {
-      const uint32_t a_s = abuf_s + (uint32_t)(t % NBUF) * TC_OPER_BYTES;
-      const uint32_t d0 = tmem_base + (uint32_t)(t & 1) * ACC_COLS;
+  if (warp == 16) {
+    // ---- MMA warp: the whole rotation of tile t, as soon as its rows are there and its accumulator is free ----
+    if (lane == 0) {
+      for (int t = 0; t < n_my; ++t) {
+        const uint32_t b = (uint32_t)(t % NBUF), s = (uint32_t)(t & 1);
+        if (!wait(full_s + 8u * b, (uint32_t)((t / NBUF) & 1))) break;
+        if (t >= 2 && !wait(free_s + 8u * s, (uint32_t)(((t - 2) >> 1) & 1))) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (t == withhold) continue;
+        const uint32_t a_s = abuf_s + b * TC_OPER_BYTES;
+        const uint32_t d0 = tmem_base + s * ACC_COLS;
 #pragma unroll
-      for (int tm = 0; tm < TERMS; ++tm) {
+        for (int tm = 0; tm < TERMS; ++tm) {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t koff = (uint32_t)((kk >> 2) * TC_HALF_BYTES + (kk & 3) * 32);
-          umma_f16(d0, umma_desc(a_s + koff),
-                   umma_desc(terms_s + (uint32_t)tm * TC_OPER_BYTES + koff), IDESC, (uint32_t)((tm | kk) != 0));
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t koff = (uint32_t)((kk >> 2) * TC_HALF_BYTES + (kk & 3) * 32);
+            umma_f16(d0, umma_desc(a_s + koff),
+                     umma_desc(terms_s + (uint32_t)tm * TC_OPER_BYTES + koff), IDESC, (uint32_t)((tm | kk) != 0));
+          }
         }
+        umma_commit(done_s + 8u * s);
       }
-      umma_commit(mbar_s + 8u * (uint32_t)(t & 1));
     }
-    // ---- tile t-1: wait for its MMAs (frees its operand buffer, fills its accumulators) ----
-    if (t >= 1) {
-      if (!mbar_wait(mbar_s + 8u * (uint32_t)((t - 1) & 1), (uint32_t)(((t - 1) >> 1) & 1))) gave_up = 1;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    }
-    if (t + AHEAD < n_my && !gave_up) issue_loads(t + AHEAD);
-    asm volatile("cp.async.commit_group;" ::: "memory");
-    if (t + AHEAD + 1 < n_my) note_rows(t + AHEAD + 1);
-    // ---- tile t: norms, four threads per vector, in the reference's summation order ----
-    if (have) {
-      const int row = tid >> 2, qs = tid & 3;
-      const uint8_t* rp = abuf + (t % NBUF) * TC_OPER_BYTES + row * 128 + qs * 4;
-      float s0 = 0.f, s1 = 0.f;          // partial sums of lanes 2 qs and 2 qs + 1
+    __syncwarp();
+  } else {
+    // ---- worker warps ----
+    // input side: row 8 warp + (lane >> 3) (+ 4), 16-byte piece lane & 7 of both K halves
+    const int64_t step = (int64_t)gridDim.x * 128;
+    const int64_t step_tok = m.slot_mapping ? step / m.num_heads : 0;
+    const int step_head = m.slot_mapping ? (int)(step - step_tok * m.num_heads) : 0;
+    TcCursor lc[2];         // the rows this thread loads, at the tile whose copies are issued next
+    lc[0] = cursor_at(m, tile_row0(0) + 8 * warp + (lane >> 3));
+    lc[1] = cursor_at(m, tile_row0(0) + 8 * warp + (lane >> 3) + 4);
+    auto issue_loads = [&](int t) {         // called for t = 0, 1, 2, ... in order
+      const uint32_t dst0 = abuf_s + (uint32_t)(t % NBUF) * TC_OPER_BYTES;
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        uint32_t w = *reinterpret_cast<const uint32_t*>(rp + (c >> 3) * TC_HALF_BYTES + (((c & 7) ^ (row & 7)) << 4));
-        float x0 = bits16_to_float<BF16>(w & 0xffffu), x1 = bits16_to_float<BF16>(w >> 16);
-        if (BF16) {
-          s0 = __fadd_rn(s0, __fmul_rn(x0, x0));
-          s1 = __fadd_rn(s1, __fmul_rn(x1, x1));
-        } else {     // the square of an fp16 value is exact in float32: one rounding either way
-          s0 = __fmaf_rn(x0, x0, s0);
-          s1 = __fmaf_rn(x1, x1, s1);
+      for (int pass = 0; pass < 2; ++pass) {
+        const int r = 8 * warp + (lane >> 3) + 4 * pass, c = lane & 7;
+        const int64_t off = cursor_src(m, lc[pass], n_rows);
+        cursor_advance(m, lc[pass], step, step_tok, step_head);
+        const uint32_t nbytes = off >= 0 ? 16u : 0u;
+        const uint16_t* src = reinterpret_cast<const uint16_t*>(m.x) + (off >= 0 ? off : 0) + c * 8;
+        const uint32_t dst = dst0 + (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4));
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                       :: "r"(dst + h * TC_HALF_BYTES), "l"(src + h * 64), "r"(nbytes) : "memory");
+      }
+    };
+    // one commit group per tile slot, empty past the last tile, so that "all but the newest AHEAD - 1 groups"
+    // always means "up to tile t"
+    for (int t = 0; t < AHEAD; ++t) {
+      if (t < n_my) issue_loads(t);
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    const int w4 = warp & 3, colq = warp >> 2;
+    const int qrow = w4 * 32 + lane;                  // output side: this thread's row, coordinates 32 colq ..
+    TcCursor nc = cursor_at(m, tile_row0(0) + (tid >> 2));      // the row whose norm this thread's quad computes
+    for (int t = 0; t <= n_my; ++t) {
+      const bool have = t < n_my;
+      TcRow nrow;                                     // where that row goes: worked out early, its slot load has time
+      nrow.src_off = -1; nrow.dst = nullptr; nrow.dst_norm = nullptr;
+      if (have && (tid & 3) == 3) nrow = cursor_dst(m, nc, n_rows);
+      if (have) cursor_advance(m, nc, step, step_tok, step_head);
+      if (have) {
+        // ---- tile t: this warp's rows have landed -> MMA warp ----
+        asm volatile("cp.async.wait_group %0;" :: "n"(AHEAD - 1) : "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(full_s + 8u * (uint32_t)(t % NBUF)) : "memory");
+        // ---- tile t: norms, four threads per vector, in the reference's summation order ----
+        const int row = tid >> 2, qs = tid & 3;
+        const uint8_t* rp = abuf + (t % NBUF) * TC_OPER_BYTES + row * 128 + qs * 4;
+        float s0 = 0.f, s1 = 0.f;          // partial sums of lanes 2 qs and 2 qs + 1
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          uint32_t w = *reinterpret_cast<const uint32_t*>(rp + (c >> 3) * TC_HALF_BYTES + (((c & 7) ^ (row & 7)) << 4));
+          float x0 = bits16_to_float<BF16>(w & 0xffffu), x1 = bits16_to_float<BF16>(w >> 16);
+          if (BF16) {
+            s0 = __fadd_rn(s0, __fmul_rn(x0, x0));
+            s1 = __fadd_rn(s1, __fmul_rn(x1, x1));
+          } else {     // the square of an fp16 value is exact in float32: one rounding either way
+            s0 = __fmaf_rn(x0, x0, s0);
+            s1 = __fmaf_rn(x1, x1, s1);
+          }
         }
-      }
-      float acc = __fadd_rn(s0, s1);     // right for qs == 0; the others chain on below
+        float acc = __fadd_rn(s0, s1);     // right for qs == 0; the others chain on below
 #pragma unroll
-      for (int step = 1; step < 4; ++step) {
-        float prev = __shfl_sync(0xffffffffu, acc, (lane & ~3) + step - 1);
-        if (qs == step) acc = __fadd_rn(__fadd_rn(prev, s0), s1);
+        for (int step = 1; step < 4; ++step) {
+          float prev = __shfl_sync(0xffffffffu, acc, (lane & ~3) + step - 1);
+          if (qs == step) acc = __fadd_rn(__fadd_rn(prev, s0), s1);
+        }
+        if (qs == 3) {
+          float nrm = __fsqrt_rn(acc);
+          nrm_s[(t & 3) * 128 + row] = nrm;
+          rinv_s[(t & 3) * 128 + row] = __frcp_rn(__fadd_rn(nrm, 1e-10f)) * (1.0f / PRESCALE);
+          dstp_s[(t & 3) * 128 + row] = nrow.dst;
+          dstn_s[(t & 3) * 128 + row] = nrow.dst_norm;
+        }
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(nready_s + 8u * (uint32_t)(t & 3)) : "memory");
       }
-      if (qs == 3) {
-        float nrm = __fsqrt_rn(acc);
-        nrm_s[(t & 1) * 128 + row] = nrm;
-        rinv_s[(t & 1) * 128 + row] = __frcp_rn(__fadd_rn(nrm, 1e-10f)) * (1.0f / PRESCALE);
-      }
-    }
-    // ---- tile t-1: quantise and pack out of tensor memory ----
-    if (t >= 1 && !gave_up) {
-      const int p = (t - 1) & 1;
-      const int w4 = warp & 3, colq = warp >> 2;
-      const int row = w4 * 32 + lane;
-      uint8_t* const dst = dst_ring[((t - 1) & (TC_RING - 1)) * 128 + row];
-      const float rinv = rinv_s[p * 128 + row];
-      const bool store = dst != nullptr;
-      {
+      // ---- tile t-1: its MMAs are complete: its operand buffer takes the rows of tile t + AHEAD ----
+      bool ok = true;
+      if (t >= 1) ok = wait_warp(done_s + 8u * (uint32_t)((t - 1) & 1), (uint32_t)(((t - 1) >> 1) & 1));
+      if (ok && t + AHEAD < n_my) issue_loads(t + AHEAD);
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      if (!ok) break;
+      // ---- tile t-1: quantise and pack out of tensor memory ----
+      if (t >= 1) {
+        const int p = (t - 1) & 1, pn = (t - 1) & 3;
+        if (!wait_warp(nready_s + 8u * (uint32_t)pn, (uint32_t)(((t - 1) >> 2) & 1))) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         uint32_t v1[32];
         tmem_ld32(tmem_base + ((uint32_t)(w4 * 32) << 16) + (uint32_t)(p * ACC_COLS + colq * 32), v1);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(free_s + 8u * (uint32_t)p) : "memory");
+        const int row = qrow;
+        uint8_t* const dst = dstp_s[pn * 128 + row];
+        const float rinv = rinv_s[pn * 128 + row];
+        const bool store = dst != nullptr;
         float y[32];
 #pragma unroll
         for (int k = 0; k < 32; ++k) y[k] = __fmul_rn(__uint_as_float(v1[k]), rinv);
@@ -359,23 +435,25 @@ tq_encode_tc_kernel(RowMap m, int64_t n_rows, const float* __restrict__ rot_t,
 #pragma unroll
             for (int b = 0; b < CHUNK_BYTES; ++b) dp[b] = (uint8_t)(pw[b >> 2] >> (8 * (b & 3)));
           }
+          if (colq == 0) *dstn_s[pn * 128 + row] = nrm_s[pn * 128 + row];
         }
       }
-      if (store && colq == 0) *dstn_ring[((t - 1) & (TC_RING - 1)) * 128 + row] = nrm_s[p * 128 + row];
     }
+    asm volatile("cp.async.wait_all;" ::: "memory");      // nothing of this thread may still be landing when the CTA leaves
   }
 
-  // A CTA that gave up may still have MMAs of a later tile in flight: before its columns go back,
-  // one more commit on the drain barrier (it completes when every MMA this thread issued has) and
-  // one more bounded wait.  Only if that wait gives up too are the columns kept (status 2): they
-  // are lost to this SM until the context ends, which is better than freeing them under an MMA.
-  int leak = 0;
-  if (gave_up && tid == 0) {
-    umma_commit(mbar_s + 16);
-    leak = mbar_wait(mbar_s + 16, 0u) ? 0 : 1;
-    g_tc_status = 1 + leak;
-  }
+  // A CTA in which a wait gave up may still have MMAs in flight: before the columns go back, the issuing thread
+  // commits once more on the drain barrier (it completes when every MMA that thread issued has) and waits,
+  // bounded.  Only if that wait gives up too are the columns kept (status 2): they are lost to this SM until the
+  // context ends, which is better than freeing them under an MMA.
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  int leak = 0;
+  if (warp == 16 && lane == 0 && lds_u32(failed_s) != 0u) {
+    umma_commit(drain_s);
+    leak = mbar_wait(drain_s, 0u) ? 0 : 1;
+    if (leak) g_tc_status = 2;
+  }
   leak = __syncthreads_or(leak);
   if (warp == 0 && !leak) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" :: "r"(tmem_base) : "memory");
@@ -390,7 +468,7 @@ int launch_tc(const RowMap& m, int64_t n_rows, const float* rot_t, const float* 
   if (e != cudaSuccess) return fail((int)e, "encode: smem attribute: %s", cudaGetErrorString(e));
   int64_t tiles = (n_rows + 127) / 128;
   int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  kern<<<grid, 512, SMEM, st>>>(m, n_rows, rot_t, bnd);
+  kern<<<grid, TC_THREADS, SMEM, st>>>(m, n_rows, rot_t, bnd);
   return check_launch("tq_encode_tc_kernel");
 }
 
