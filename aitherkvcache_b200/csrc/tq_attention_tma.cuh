@@ -45,6 +45,7 @@ __device__ __forceinline__ void t4_arrive_tx(uint32_t bar, uint32_t bytes) {
 // Bounded wait: about a second of SM cycles at most.  After the first wait of a CTA that runs out, the
 // shared word T4_FAILED makes every later wait of the CTA return at once, so a broken run ends quickly.
 constexpr uint32_t T4_FAILED = T4_BAR + 64;
+constexpr uint32_t T4_PLAN = T4_BAR + 256;     // copy of the stage plan (4 S + 2 words) for up to 64 sequences
 __device__ __forceinline__ bool t4_wait(uint32_t bar, uint32_t parity) {
   if (lds32(T4_FAILED) != 0u) return false;
   const long long t0 = clock64();
@@ -143,37 +144,43 @@ tq_attn_tma_kernel(AttnArgs a, const __grid_constant__ T4Maps maps) {
     for (int i = 4; i < 8; ++i) t4_bar_init(T4_BAR + 8 * i, 8);          // emptyK[0..1], emptyV[0..1]: eight consumer warps
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  // The plan written by the query-rotation launch ([0..S] stage prefix, [S] total, [S+1] stages per CTA, then three
+  // words per sequence) comes into shared memory with one round of loads; every later look-up is a shared load.
+  const int* __restrict__ Pg = a.sk;
+  const bool plan_local = S <= 64;
+  if (plan_local)
+    for (int i = tid; i < 4 * S + 2; i += T4_THREADS)
+      asm volatile("st.shared.u32 [%0], %1;" :: "r"(T4_PLAN + 4 * i), "r"((uint32_t)Pg[i]) : "memory");
   __syncthreads();
+  auto P = [&](int i) -> int { return plan_local ? (int)lds32(T4_PLAN + 4 * i) : Pg[i]; };
 
-  // this CTA's range of stages (plan written by the query-rotation launch).  The first sequence of the
-  // range is the last one whose stage prefix is <= u_begin: found with one round of parallel loads and a
-  // ballot for up to 64 sequences, by bisection beyond that.
-  const int* __restrict__ P = a.sk;                 // [0..S] stage prefix, [S] total, [S+1] stages per CTA
-  const int T = P[S], chunk = P[S + 1];
+  // this CTA's range of stages.  The first sequence of the range is the last one whose stage prefix is
+  // <= u_begin: found with a ballot for up to 64 sequences, by bisection beyond that.
+  const int T = P(S), chunk = P(S + 1);
   const int u_begin = b * chunk;
   const int u_end = (u_begin + chunk < T) ? u_begin + chunk : T;
   if (u_begin >= u_end) return;                      // uniform for the CTA
   const int n_it = u_end - u_begin;
   int seq0;
   if (S <= 64) {
-    const int c0 = (lane < S && P[lane] <= u_begin) ? 1 : 0, c1 = (lane + 32 < S && P[lane + 32] <= u_begin) ? 1 : 0;
+    const int c0 = (lane < S && P(lane) <= u_begin) ? 1 : 0, c1 = (lane + 32 < S && P(lane + 32) <= u_begin) ? 1 : 0;
     seq0 = __popc(__ballot_sync(0xffffffffu, c0)) + __popc(__ballot_sync(0xffffffffu, c1)) - 1;
   } else {
     int lo = 0, hi = S - 1;
     while (lo < hi) {
       const int mid = (lo + hi + 1) >> 1;
-      if (P[mid] <= u_begin) lo = mid; else hi = mid - 1;
+      if (P(mid) <= u_begin) lo = mid; else hi = mid - 1;
     }
     seq0 = lo;
   }
-  while (seq0 < S - 1 && u_begin >= P[seq0 + 1]) ++seq0;      // skip sequences without stages
+  while (seq0 < S - 1 && u_begin >= P(seq0 + 1)) ++seq0;      // skip sequences without stages
 
   if (warp < 8) {        // the consumers fill the lookup table while the producer already issues copies
     if constexpr (BITS == 4) {          // byte -> half2(c[hi nibble], c[lo nibble])
-      for (int i = tid; i < 256 * 32; i += 256) {
-        const int e = i >> 5, l = i & 31;
+      for (int i = tid; i < 256 * 8; i += 256) {          // entry e, lanes 4 q .. 4 q + 3: one 16-byte store
+        const int e = i >> 3, q4 = i & 7;
         const uint32_t v = pack_half2(s_cent[e >> 4], s_cent[e & 15]);
-        asm volatile("st.shared.u32 [%0], %1;\n" :: "r"(SK_LUT + e * LUT_STRIDE + l * 4), "r"(v));
+        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" :: "r"(SK_LUT + e * LUT_STRIDE + q4 * 16), "r"(v));
       }
     } else if constexpr (BITS == 3) {   // 6 bits -> half2(c[hi 3 bits], c[lo 3 bits])
       for (int i = tid; i < 64 * 32; i += 256) {
@@ -182,11 +189,11 @@ tq_attn_tma_kernel(AttnArgs a, const __grid_constant__ T4Maps maps) {
         asm volatile("st.shared.u32 [%0], %1;\n" :: "r"(SK_LUT + e * LUT3_STRIDE + l * 4), "r"(v));
       }
     } else {                            // byte -> four halves
-      for (int i = tid; i < 256 * 32; i += 256) {
-        const int e = i >> 5, l = i & 31;
+      for (int i = tid; i < 256 * 16; i += 256) {         // entry e, lanes 2 q, 2 q + 1: one 16-byte store
+        const int e = i >> 4, q2 = i & 15;
         const uint32_t v0 = pack_half2(s_cent[e >> 6], s_cent[(e >> 4) & 3]);
         const uint32_t v1 = pack_half2(s_cent[(e >> 2) & 3], s_cent[e & 3]);
-        asm volatile("st.shared.v2.u32 [%0], {%1,%2};\n" :: "r"(SK_LUT + e * LUT_STRIDE + l * 8), "r"(v0), "r"(v1));
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%1,%2};\n" :: "r"(SK_LUT + e * LUT_STRIDE + q2 * 16), "r"(v0), "r"(v1));
       }
     }
     asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -196,13 +203,13 @@ tq_attn_tma_kernel(AttnArgs a, const __grid_constant__ T4Maps maps) {
     // ------------------------------ producer ------------------------------
     const bool bt64 = a.bt_dtype == AKV_I64;
     const int nblocks = (int)a.num_blocks;
-    int p_seq = seq0, p_base = P[seq0], p_end = P[seq0 + 1], p_nb = P[3 * S + 2 + seq0];
+    int p_seq = seq0, p_base = P(seq0), p_end = P(seq0 + 1), p_nb = P(3 * S + 2 + seq0);
     const char* bt_row = reinterpret_cast<const char*>(a.block_tables) + (int64_t)p_seq * a.bt_stride * (bt64 ? 8 : 4);
     for (int it = 0; it < n_it; ++it) {
       const int u = u_begin + it;
       if (u >= p_end) {
-        while (p_seq < S - 1 && u >= P[p_seq + 1]) ++p_seq;
-        p_base = P[p_seq]; p_end = P[p_seq + 1]; p_nb = P[3 * S + 2 + p_seq];
+        while (p_seq < S - 1 && u >= P(p_seq + 1)) ++p_seq;
+        p_base = P(p_seq); p_end = P(p_seq + 1); p_nb = P(3 * S + 2 + p_seq);
         bt_row = reinterpret_cast<const char*>(a.block_tables) + (int64_t)p_seq * a.bt_stride * (bt64 ? 8 : 4);
       }
       const int bi = 4 * (u - p_base);
@@ -270,7 +277,7 @@ tq_attn_tma_kernel(AttnArgs a, const __grid_constant__ T4Maps maps) {
   int seq_c = -1, c_base = 0, c_end = 0, ctx_c = 0;
   auto begin_seq = [&](int seq) {
     seq_c = seq;
-    c_base = P[seq]; c_end = P[seq + 1];
+    c_base = P(seq); c_end = P(seq + 1);
     ctx_c = (int)load_ctx(a.context_lens, a.cl_dtype, seq, (int64_t)a.max_blocks_per_seq * a.block_size);
     const int qg = g & 3;
     const float* qp = a.qrot + ((int64_t)seq * a.num_q_heads + h * G + (qg < G ? qg : 0)) * 128 + 32 * t;
@@ -294,7 +301,7 @@ tq_attn_tma_kernel(AttnArgs a, const __grid_constant__ T4Maps maps) {
       l0 += __shfl_xor_sync(0xffffffffu, l0, offs);
       l1 += __shfl_xor_sync(0xffffffffu, l1, offs);
     }
-    const int part = b - P[S + 2 + seq_c];
+    const int part = b - P(S + 2 + seq_c);
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int n = 2 * t + e, qg = n & 3, ep = n >> 2;      // column -> (query head, dim parity)
@@ -434,7 +441,7 @@ tq_attn_tma_kernel(AttnArgs a, const __grid_constant__ T4Maps maps) {
     end_seq();
     if (it < n_it) {
       seq_next = seq_c;
-      while (seq_next < S - 1 && u_begin + it >= P[seq_next + 1]) ++seq_next;
+      while (seq_next < S - 1 && u_begin + it >= P(seq_next + 1)) ++seq_next;
     }
   }
 }
