@@ -958,6 +958,108 @@ hybrid_attn_kernel(HybridAttnArgs a) {
 }
 
 // ---------------------------------------------------------------------------
+// The same computation for tq25 records (44 bytes: group 0 = 32 coordinates with 2-bit codes, group 1 = 96
+// coordinates with 1-bit codes, a sign bit per coordinate in both).  The 256 virtual coordinates are
+//   [0, 32) group-0 centroids, [32, 64) group-0 signs, [64, 160) group-1 centroids, [160, 256) group-1 signs;
+// a lane holds coordinate `lane` of the first two segments and `lane`, `lane + 32`, `lane + 64` of the others.
+// ---------------------------------------------------------------------------
+struct Hy25Vals { float c0, s0, c1[3], s1[3], n0, r0, n1, r1; };
+
+__device__ __forceinline__ Hy25Vals hy25_load(const uint8_t* rec, int lane, const float* cent) {
+  Hy25Vals v;
+  v.c0 = cent[(rec[lane >> 2] >> (6 - 2 * (lane & 3))) & 3];
+  v.s0 = ((rec[8 + (lane >> 3)] >> (7 - (lane & 7))) & 1) ? 1.f : -1.f;
+#pragma unroll
+  for (int j = 0; j < 3; ++j) {
+    const int d = lane + 32 * j;
+    v.c1[j] = cent[8 + ((rec[16 + (d >> 3)] >> (7 - (d & 7))) & 1)];
+    v.s1[j] = ((rec[28 + (d >> 3)] >> (7 - (d & 7))) & 1) ? 1.f : -1.f;
+  }
+  const __half2 n0 = *reinterpret_cast<const __half2*>(rec + 12);
+  const __half2 n1 = *reinterpret_cast<const __half2*>(rec + 40);
+  v.n0 = __low2float(n0); v.r0 = __high2float(n0);
+  v.n1 = __low2float(n1); v.r1 = __high2float(n1);
+  return v;
+}
+
+// virtual coordinate of a lane's slot k (0..7)
+__device__ __forceinline__ int hy25_coord(int k, int lane) {
+  return k == 0 ? lane : k == 1 ? 32 + lane : k < 5 ? 64 + lane + 32 * (k - 2) : 160 + lane + 32 * (k - 5);
+}
+
+__global__ void __launch_bounds__(HA_WARPS * 32)
+hybrid_attn25_kernel(HybridAttnArgs a) {
+  const int split = blockIdx.x, h = blockIdx.y, seq = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = a.num_q_heads / a.num_kv_heads;
+  const int64_t ctx = load_ctx(a.context_lens, a.cl_dtype, seq, (int64_t)a.max_blocks_per_seq * a.block_size);
+  const int bs = a.block_size;
+  const int64_t nblk = (ctx + bs - 1) / bs;
+  const int64_t blk_begin = (int64_t)split * a.blocks_per_split;
+  if (blk_begin >= nblk) return;
+  const int64_t blk_end = (blk_begin + a.blocks_per_split < nblk) ? blk_begin + a.blocks_per_split : nblk;
+  __shared__ float cent[16];
+  if (threadIdx.x < 16) cent[threadIdx.x] = a.centroids[threadIdx.x];
+  __syncthreads();
+  const int part = split * HA_WARPS + warp;
+
+  for (int g0 = 0; g0 < G; g0 += 4) {
+    const int ng = (G - g0 < 4) ? G - g0 : 4;
+    float q[4][8], acc[4][8], m[4], l[4];
+#pragma unroll
+    for (int gi = 0; gi < 4; ++gi) {
+      m[gi] = -CUDART_INF_F; l[gi] = 0.f;
+      const float* qp = a.qprime + ((int64_t)seq * a.num_q_heads + h * G + g0 + (gi < ng ? gi : 0)) * 256;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        q[gi][k] = (gi < ng) ? qp[hy25_coord(k, lane)] : 0.f;
+        acc[gi][k] = 0.f;
+      }
+    }
+    for (int64_t blk = blk_begin + warp; blk < blk_end; blk += HA_WARPS) {
+      int64_t pb = load_index(a.block_tables, a.bt_dtype, (int64_t)seq * a.bt_stride + blk);
+      if (pb < 0) pb = 0;
+      if (pb >= a.num_blocks) pb = a.num_blocks - 1;
+      const int ntok = (int)((ctx - blk * bs < bs) ? ctx - blk * bs : bs);
+      for (int t = 0; t < ntok; ++t) {
+        const Hy25Vals k = hy25_load(a.k_cache + pb * a.k_sb + t * a.k_sp + h * a.k_sh, lane, cent);
+        const Hy25Vals v = hy25_load(a.v_cache + pb * a.v_sb + t * a.v_sp + h * a.v_sh, lane, cent);
+        const float kw0 = k.n0, kw1 = k.n0 * k.r0, kw2 = k.n1, kw3 = k.n1 * k.r1;
+        const float vw0 = v.n0, vw1 = v.n0 * v.r0, vw2 = v.n1, vw3 = v.n1 * v.r1;
+        const float vv[8] = {v.c0 * vw0, v.s0 * vw1, v.c1[0] * vw2, v.c1[1] * vw2, v.c1[2] * vw2,
+                             v.s1[0] * vw3, v.s1[1] * vw3, v.s1[2] * vw3};
+#pragma unroll
+        for (int gi = 0; gi < 4; ++gi) {
+          if (gi >= ng) continue;
+          float d = kw0 * (q[gi][0] * k.c0) + kw1 * (q[gi][1] * k.s0) +
+                    kw2 * (q[gi][2] * k.c1[0] + q[gi][3] * k.c1[1] + q[gi][4] * k.c1[2]) +
+                    kw3 * (q[gi][5] * k.s1[0] + q[gi][6] * k.s1[1] + q[gi][7] * k.s1[2]);
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+          const float mn = fmaxf(m[gi], d);
+          const float alpha = exp2f(m[gi] - mn);
+          const float p = exp2f(d - mn);
+          l[gi] = l[gi] * alpha + p;
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) acc[gi][kk] = __fmaf_rn(p, vv[kk], acc[gi][kk] * alpha);
+          m[gi] = mn;
+        }
+      }
+    }
+    for (int gi = 0; gi < ng; ++gi) {
+      const int64_t row = (int64_t)seq * a.num_q_heads + h * G + g0 + gi;
+      float* pa = a.part_acc + (row * a.num_parts + part) * 256;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) pa[hy25_coord(k, lane)] = acc[gi][k];
+      if (lane == 0) {
+        a.part_ml[(row * a.num_parts + part) * 2] = m[gi];
+        a.part_ml[(row * a.num_parts + part) * 2 + 1] = l[gi];
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Tensor-core version of the same computation (same grid, same partials).
 //
 // A warp owns one part (one KV head, every HA_WARPS-th 16-token tile of the split) and all
@@ -1427,6 +1529,57 @@ hybrid_qprime_kernel(const void* __restrict__ q, int q_dtype, int64_t q_ss, int6
   hybrid_qprime_row(q, q_dtype, q_ss, q_sh, num_q_heads, t, premul, qprime, blockIdx.x, threadIdx.x, w);
 }
 
+// In-place Walsh-Hadamard transform of n = 32 or 64 shared floats by one warp (stages h = 1, 2, 4, ...).
+__device__ __forceinline__ void fwht_warp_smem(float* w, int n, int lane) {
+  for (int h = 1; h < n; h <<= 1) {
+    __syncwarp();
+    for (int l = lane; l < n / 2; l += 32) {
+      const int j = ((l & ~(h - 1)) << 1) | (l & (h - 1));
+      const float x = w[j], y = w[j + h];
+      w[j] = x + y;
+      w[j + h] = x - y;
+    }
+  }
+  __syncwarp();
+}
+
+// The transforms of the 256 virtual coordinates of tq25: blocks of 32, 32, 64 + 32 (the 96-coordinate group is
+// block diagonal, hybrid_quantizer.py:130-193) and again 64 + 32.
+__device__ __forceinline__ void hy25_transforms(float* w, int warp, int nwarps, int lane) {
+  const int off[6] = {0, 32, 64, 128, 160, 224}, len[6] = {32, 32, 64, 32, 64, 32};
+  for (int b = warp; b < 6; b += nwarps) fwht_warp_smem(w + off[b], len[b], lane);
+}
+
+// Query side of tq25 attention: q'(virtual) = transform(q gathered by group, times the sign vectors) / sqrt(group size),
+// scale * log2(e) and the sketch factor kappa folded in.  One warp per (sequence, query head).
+__global__ void __launch_bounds__(32)
+hybrid_qprime25_kernel(const void* __restrict__ q, int q_dtype, int64_t q_ss, int64_t q_sh, int num_q_heads,
+                       HybridTables t, float premul, float* __restrict__ qprime) {
+  __shared__ float w[256];
+  const int row = blockIdx.x, lane = threadIdx.x;
+  const int seq = row / num_q_heads, qh = row % num_q_heads;
+  {
+    const float a = load_as_float(q, q_dtype, seq * q_ss + qh * q_sh + t.group_index[lane]);
+    w[lane] = a * t.had_signs[lane];
+    w[32 + lane] = a * t.qjl_signs[lane];
+  }
+  for (int k = lane; k < 96; k += 32) {
+    const float b = load_as_float(q, q_dtype, seq * q_ss + qh * q_sh + t.group_index[32 + k]);
+    w[64 + k] = b * t.had_signs[32 + k];
+    w[160 + k] = b * t.qjl_signs[32 + k];
+  }
+  __syncwarp();
+  hy25_transforms(w, 0, 1, lane);
+  const float r0 = 0.17677669529663687f * premul, r1 = 0.10206207261596577f * premul;     // 1/sqrt(32), 1/sqrt(96)
+  float* o = qprime + (int64_t)row * 256;
+  o[lane] = w[lane] * r0;
+  o[32 + lane] = w[32 + lane] * r0 * t.qjl_scale0;
+  for (int k = lane; k < 96; k += 32) {
+    o[64 + k] = w[64 + k] * r1;
+    o[160 + k] = w[160 + k] * r1 * t.qjl_scale1;
+  }
+}
+
 // The new token's K and V vectors of a serving step (16-bit, rows readable in 16-byte pieces), written
 // into the paged record cache by extra blocks of the query-transform launch.
 struct HyStepWrite {
@@ -1479,6 +1632,7 @@ __device__ __forceinline__ float block_reduce_256(float v, bool is_max, float* s
   return r;
 }
 
+template <int MODE>       // 35: four 64-coordinate segments; 25: segments of 32, 32, 96, 96
 __global__ void __launch_bounds__(256)
 hybrid_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml, int num_parts,
                     const void* context_lens, int cl_dtype, int tokens_per_split, int num_q_heads,
@@ -1520,23 +1674,40 @@ hybrid_merge_kernel(const float* __restrict__ part_acc, const float* __restrict_
   const float L = block_reduce_256(ls, false, scratch);
   const float inv = L > 0.f ? 1.f / L : 0.f;
   w[tid >> 6][tid & 63] = acc * inv;
-  // four 64-point transforms: 128 butterflies per stage, one per thread of the first half
-  for (int h = 1; h < 64; h <<= 1) {
+  if (MODE == 25) {
+    float* wf = &w[0][0];
+    __syncthreads();
+    hy25_transforms(wf, tid >> 5, 8, tid & 31);
     __syncthreads();
     if (tid < 128) {
-      const int sg = tid >> 5, l = tid & 31;
-      const int j = ((l & ~(h - 1)) << 1) | (l & (h - 1));
-      const float a = w[sg][j], b = w[sg][j + h];
-      w[sg][j] = a + b;
-      w[sg][j + h] = a - b;
+      float o;
+      if (tid < 32) {
+        o = (wf[tid] * t.had_signs[tid] + wf[32 + tid] * t.qjl_scale0 * t.qjl_signs[tid]) * 0.17677669529663687f;
+      } else {
+        const int k = tid - 32;
+        o = (wf[64 + k] * t.had_signs[tid] + wf[160 + k] * t.qjl_scale1 * t.qjl_signs[tid]) * 0.10206207261596577f;
+      }
+      store_from_float(out, out_dtype, seq * out_ss + qh * out_sh + t.group_index[tid], o);
     }
-  }
-  __syncthreads();
-  if (tid < 128) {
-    const int grp = tid >> 6, k = tid & 63;
-    const float o = (w[2 * grp][k] * t.had_signs[64 * grp + k] +
-                     w[2 * grp + 1][k] * (grp ? t.qjl_scale1 : t.qjl_scale0) * t.qjl_signs[64 * grp + k]) * 0.125f;
-    store_from_float(out, out_dtype, seq * out_ss + qh * out_sh + t.group_index[64 * grp + k], o);
+  } else {
+    // four 64-point transforms: 128 butterflies per stage, one per thread of the first half
+    for (int h = 1; h < 64; h <<= 1) {
+      __syncthreads();
+      if (tid < 128) {
+        const int sg = tid >> 5, l = tid & 31;
+        const int j = ((l & ~(h - 1)) << 1) | (l & (h - 1));
+        const float a = w[sg][j], b = w[sg][j + h];
+        w[sg][j] = a + b;
+        w[sg][j + h] = a - b;
+      }
+    }
+    __syncthreads();
+    if (tid < 128) {
+      const int grp = tid >> 6, k = tid & 63;
+      const float o = (w[2 * grp][k] * t.had_signs[64 * grp + k] +
+                       w[2 * grp + 1][k] * (grp ? t.qjl_scale1 : t.qjl_scale0) * t.qjl_signs[64 * grp + k]) * 0.125f;
+      store_from_float(out, out_dtype, seq * out_ss + qh * out_sh + t.group_index[64 * grp + k], o);
+    }
   }
 }
 
@@ -1716,7 +1887,8 @@ static int run_hybrid_attn(const akv_hybrid_attn_params* p, const HyStepWrite* w
   if (!p) return fail(AKV_ERR_ARG, "null params");
   HybridTables t; int mode;
   if (int rc = tables_from(p->tables, &t, &mode)) return rc;
-  if (mode != 35) return fail(AKV_ERR_UNSUPPORTED, "hybrid paged attention is built for tq35 (64-byte records)");
+  if (mode == 25 && wr != nullptr && wr->n_rows > 0)
+    return fail(AKV_ERR_UNSUPPORTED, "hybrid paged attention: the fused record write is built for tq35");
   if (t.num_index_heads != 1)
     return fail(AKV_ERR_UNSUPPORTED, "hybrid paged attention needs one dim split shared by all heads");
   if (p->num_seqs < 0 || p->num_q_heads <= 0 || p->num_kv_heads <= 0 || p->num_q_heads % p->num_kv_heads ||
@@ -1749,6 +1921,10 @@ static int run_hybrid_attn(const akv_hybrid_attn_params* p, const HyStepWrite* w
       hybrid_step_prologue_kernel<false><<<grid0, HC_THREADS, 0, st>>>(p->query, p->q_dtype, p->q_stride_seq,
           p->q_stride_head, p->num_q_heads, t, p->scale * 1.4426950408889634f, qprime, rows, q_blocks, *wr);
     if (int rc = check_launch("hybrid_step_prologue_kernel")) return rc;
+  } else if (mode == 25) {
+    hybrid_qprime25_kernel<<<rows, 32, 0, st>>>(p->query, p->q_dtype, p->q_stride_seq, p->q_stride_head,
+                                                p->num_q_heads, t, p->scale * 1.4426950408889634f, qprime);
+    if (int rc = check_launch("hybrid_qprime25_kernel")) return rc;
   } else {
     hybrid_qprime_kernel<<<rows, 32, 0, st>>>(p->query, p->q_dtype, p->q_stride_seq, p->q_stride_head,
                                               p->num_q_heads, t, p->scale * 1.4426950408889634f, qprime);
@@ -1773,7 +1949,10 @@ static int run_hybrid_attn(const akv_hybrid_attn_params* p, const HyStepWrite* w
                              p->v_stride_pos | p->v_stride_head) & 15) == 0;
     // the tensor-core kernel keeps its tables at fixed shared addresses: its dynamic window must start below them
     static const bool window_ok = dyn_smem_window_start(reinterpret_cast<const void*>(hybrid_attn_mma_kernel)) <= HM_LUT2;
-    if (!force_scalar && window_ok && aligned16 && p->block_size % 16 == 0 && p->num_q_heads / p->num_kv_heads <= 8) {
+    if (mode == 25) {
+      hybrid_attn25_kernel<<<grid, HA_WARPS * 32, 0, st>>>(a);
+      if (int rc = check_launch("hybrid_attn25_kernel")) return rc;
+    } else if (!force_scalar && window_ok && aligned16 && p->block_size % 16 == 0 && p->num_q_heads / p->num_kv_heads <= 8) {
       cudaError_t e = cudaFuncSetAttribute(hybrid_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, HM_SMEM);
       if (e != cudaSuccess) return fail((int)e, "hybrid attention: smem attribute: %s", cudaGetErrorString(e));
       hybrid_attn_mma_kernel<<<grid, HA_WARPS * 32, HM_SMEM, st>>>(a);
@@ -1783,9 +1962,14 @@ static int run_hybrid_attn(const akv_hybrid_attn_params* p, const HyStepWrite* w
       if (int rc = check_launch("hybrid_attn_kernel")) return rc;
     }
   }
-  hybrid_merge_kernel<<<rows, 256, 0, st>>>(part_acc, part_ml, p->max_blocks_per_seq > 0 ? parts : 0,
-                                           p->context_lens, p->cl_dtype, bps * p->block_size, p->num_q_heads, t,
-                                           p->out, p->out_dtype, p->out_stride_seq, p->out_stride_head);
+  if (mode == 25)
+    hybrid_merge_kernel<25><<<rows, 256, 0, st>>>(part_acc, part_ml, p->max_blocks_per_seq > 0 ? parts : 0,
+                                                 p->context_lens, p->cl_dtype, bps * p->block_size, p->num_q_heads, t,
+                                                 p->out, p->out_dtype, p->out_stride_seq, p->out_stride_head);
+  else
+    hybrid_merge_kernel<35><<<rows, 256, 0, st>>>(part_acc, part_ml, p->max_blocks_per_seq > 0 ? parts : 0,
+                                                 p->context_lens, p->cl_dtype, bps * p->block_size, p->num_q_heads, t,
+                                                 p->out, p->out_dtype, p->out_stride_seq, p->out_stride_head);
   return check_launch("hybrid_merge_kernel");
 }
 

@@ -284,17 +284,18 @@ class HybridTurboQuant:
 
 
 class HybridPagedAttention:
-    """Paged decode attention directly over tq35 records (no K/V reconstruction).
+    """Paged decode attention directly over tq35 or tq25 records (no K/V reconstruction).
 
     Stands in for the decompress-everything + SDPA body of the reference's
     ``tq::hybrid_decode_step`` (``vllm/hooks.py:297-345``).
-    ``k_cache`` / ``v_cache``: uint8 ``[num_blocks, block_size, num_kv_heads, 64]`` (views allowed).
+    ``k_cache`` / ``v_cache``: uint8 ``[num_blocks, block_size, num_kv_heads, 64]`` (tq35; 44 for tq25; views allowed).
+    tq35 runs on the tensor-core kernel, tq25 on the scalar one.
     """
 
     def __init__(self, htq: HybridTurboQuant, num_query_heads: int):
         htq._ensure_calibrated()
-        if htq.mode != "tq35" or htq.head_dim != 128:
-            raise NotImplementedError("hybrid paged attention is built for tq35 at head_dim 128")
+        if htq.head_dim != 128:
+            raise NotImplementedError("hybrid paged attention is built for head_dim 128")
         self.htq, self.num_query_heads = htq, num_query_heads
         self.scale = 1.0 / math.sqrt(htq.head_dim)
         self._workspace: Optional[torch.Tensor] = None
@@ -315,8 +316,8 @@ class HybridPagedAttention:
         if query.stride(-1) != 1:
             query = query.contiguous()
         for name, t in (("k_cache", k_cache), ("v_cache", v_cache)):
-            if t.dtype != torch.uint8 or t.stride(-1) != 1 or t.shape[-1] < 64:
-                raise ValueError(f"{name} must be uint8 [..., >=64] with a contiguous last dimension")
+            if t.dtype != torch.uint8 or t.stride(-1) != 1 or t.shape[-1] < self.htq.layout.packed_dim:
+                raise ValueError(f"{name} must be uint8 [..., >={self.htq.layout.packed_dim}] with a contiguous last dimension")
         if block_tables.stride(-1) != 1:
             block_tables = block_tables.contiguous()
         context_lens = context_lens.contiguous()

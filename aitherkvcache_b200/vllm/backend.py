@@ -26,7 +26,7 @@ from typing import Dict, Optional, Tuple
 import torch
 
 KV_DTYPE_BITS = {"tq-t4nc": 4, "tq-t3nc": 3, "tq-t2nc": 2}
-KV_DTYPE_HYBRID = {"tq-t35nc": "tq35"}
+KV_DTYPE_HYBRID = {"tq-t35nc": "tq35", "tq-t25nc": "tq25"}
 
 
 def bits_from_env_or_dtype(cache_dtype_str: Optional[str] = None) -> int:
@@ -36,17 +36,14 @@ def bits_from_env_or_dtype(cache_dtype_str: Optional[str] = None) -> int:
 
 
 def codec_from_env_or_dtype(cache_dtype_str: Optional[str] = None) -> Tuple[str, object]:
-    """``("uniform", bits)`` or ``("hybrid", "tq35")``."""
+    """``("uniform", bits)`` or ``("hybrid", "tq35" | "tq25")``."""
     if cache_dtype_str in KV_DTYPE_HYBRID:
         return "hybrid", KV_DTYPE_HYBRID[cache_dtype_str]
     if cache_dtype_str in KV_DTYPE_BITS:
         return "uniform", KV_DTYPE_BITS[cache_dtype_str]
     mode = os.environ.get("AITHER_TQ_MODE", "")
-    if mode == "tq35":
+    if mode in ("tq35", "tq25"):
         return "hybrid", mode
-    if mode == "tq25":
-        raise NotImplementedError("AITHER_TQ_MODE=tq25: the tq25 codec exists (HybridTurboQuant), its paged "
-                                  "attention kernel does not; use tq35")
     return "uniform", bits_from_env_or_dtype(cache_dtype_str)
 
 

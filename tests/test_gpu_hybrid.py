@@ -101,12 +101,13 @@ def test_per_head_calibration_and_errors():
     assert r["cosine_similarity"] > 0.9
 
 
-@pytest.mark.parametrize("H,QH,ctx", [(8, 32, [700, 33, 1, 0]), (2, 4, [100, 48])])
-def test_paged_attention_vs_oracle(H, QH, ctx):
+@pytest.mark.parametrize("mode", ("tq35", "tq25"))
+@pytest.mark.parametrize("H,QH,ctx", [(8, 32, [700, 33, 1, 0]), (2, 4, [100, 48]), (2, 16, [257])])
+def test_paged_attention_vs_oracle(H, QH, ctx, mode):
     from aitherkvcache_b200.hybrid_quantizer import HybridPagedAttention
-    g = load_golden("hybrid_tq35.npz")
-    h = _htq("tq35", g, heads=1)
-    t = _oracle_tables(g, "tq35")
+    g = load_golden(f"hybrid_{mode}.npz")
+    h = _htq(mode, g, heads=1)
+    t = _oracle_tables(g, mode)
     gen = torch.Generator().manual_seed(12)
     bs = 16
     nblk = [(c + bs - 1) // bs for c in ctx]
