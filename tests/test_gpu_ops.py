@@ -305,19 +305,20 @@ def test_backend_mixed_batch_attends_over_the_packed_cache():
     assert (np.abs(got - ref) <= 2e-3 * np.maximum(1.0, np.abs(ref))).all()
 
 
-def test_backend_hybrid_mode_from_environment(monkeypatch):
-    """AITHER_TQ_MODE=tq35 selects the hybrid codec in the backend impl: records (norms inside) written by
+@pytest.mark.parametrize("mode,PD", (("tq35", 64), ("tq25", 44)))
+def test_backend_hybrid_mode_from_environment(monkeypatch, mode, PD):
+    """AITHER_TQ_MODE=tq35 / tq25 selects the hybrid codec in the backend impl: records (norms inside) written by
     do_kv_cache_update equal the oracle's, decode and prefill rows match the oracle's decode -> attention."""
     from aitherkvcache_b200.vllm.backend import TurboQuantImplBase
-    monkeypatch.setenv("AITHER_TQ_MODE", "tq35")
-    g = load_golden("hybrid_tq35.npz")
-    t = ohy.Tables(128, "tq35", g["had0"], g["had1"], g["qjl0"], g["qjl1"],
+    monkeypatch.setenv("AITHER_TQ_MODE", mode)
+    g = load_golden(f"hybrid_{mode}.npz")
+    t = ohy.Tables(128, mode, g["had0"], g["had1"], g["qjl0"], g["qjl1"],
                    codebooks=[(g["cent0"], g["bnd0"]), (g["cent1"], g["bnd1"])])
     H, QH, bs = 8, 32, 16
     impl = TurboQuantImplBase()
     impl._tq_setup(QH, 128, 1.0 / math.sqrt(128), H, "auto")
-    assert impl.tq_codec == "hybrid" and impl.packed_dim == 64
-    layer = types.SimpleNamespace(layer_name="hy.layers.0.attn")
+    assert impl.tq_codec == "hybrid" and impl.packed_dim == PD
+    layer = types.SimpleNamespace(layer_name=f"hy{PD}.layers.0.attn")
     lens = [45, 130]
     bt = torch.tensor([[3, 7, 1, 0, 0, 0, 0, 0, 0], [2, 4, 5, 6, 8, 9, 10, 11, 12]], dtype=torch.int32)
     kv = torch.zeros(14, 2, bs, H, 128, dtype=torch.uint8, device="cuda")
@@ -328,9 +329,9 @@ def test_backend_hybrid_mode_from_environment(monkeypatch):
     slots = torch.cat([(bt[s, :(n + bs - 1) // bs].long()[:, None] * bs + torch.arange(bs)[None]).reshape(-1)[:n]
                        for s, n in enumerate(lens)])
     impl.do_kv_cache_update(layer, key.cuda(), val.cuda(), kv, slots.cuda())
-    kc = kv[:, 0, ..., :64].cpu().numpy()
-    vc = kv[:, 1, ..., :64].cpu().numpy()
-    assert np.array_equal(kc.reshape(-1, H, 64)[slots.numpy()], ohy.encode(key.numpy(), t))
+    kc = kv[:, 0, ..., :PD].cpu().numpy()
+    vc = kv[:, 1, ..., :PD].cpu().numpy()
+    assert np.array_equal(kc.reshape(-1, H, PD)[slots.numpy()], ohy.encode(key.numpy(), t))
     q = torch.randn(2, QH * 128, generator=gen).half()
     md1 = types.SimpleNamespace(num_actual_tokens=2, max_query_len=1, block_table=bt.cuda(),
                                 seq_lens=torch.tensor(lens, dtype=torch.int32, device="cuda"))
