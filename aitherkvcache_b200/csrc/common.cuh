@@ -156,6 +156,6 @@ __device__ __forceinline__ int64_t merge_half_offset(const MergeArgs& a) {
 
 int p2p_status(int* host_out, int reset);
 
-int launch_merge(const MergeArgs& a, int rows, cudaStream_t st);
+int launch_merge(const MergeArgs& a, int rows, cudaStream_t st, bool pdl = false);
 
 }  // namespace akv

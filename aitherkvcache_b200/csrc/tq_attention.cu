@@ -51,6 +51,7 @@ struct AttnArgs {
   int num_seqs, num_q_heads, num_kv_heads, head_dim, block_size, max_blocks_per_seq;
   int64_t num_blocks;            // physical blocks in the cache (for clamping)
   int bits;
+  int pdl;        // launched as a programmatic dependent of the query-rotation launch
   int blocks_per_split, num_splits, warps_per_head, num_parts;
   const float* qrot;             // [S][QH][D] float32, already multiplied by scale*log2(e)
   const float* centroids;
@@ -287,6 +288,9 @@ akv_qrot128_kernel(const void* __restrict__ q, int q_dtype, int64_t q_ss, int64_
                    int rot_blocks, int plan_blocks, StreamKPlanArgs plan, NewTokenWrite nt) {
   extern __shared__ __align__(16) float qs[];
   constexpr int D = 128;
+  // the attention launch that follows may be scheduled already: it waits (griddepcontrol.wait) for this whole
+  // grid before it reads the plan or the rotated queries
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // block order: the new token's vectors first (the longest-running blocks, so they start at once), then
   // the plan block, then the rotation blocks
   const int enc_blocks = (int)(2 * nt.n_rows);
@@ -344,6 +348,9 @@ akv_merge128_kernel(MergeArgs a, int rows, int np_alloc) {
   float* wall = vec + 4 * D;                // [4][np_alloc] weights
   float* red = wall + 4 * np_alloc;         // [4][2]  M, L
   stage_matrix128(mat, a.rot);
+  // launched as a programmatic dependent, this grid may start while the attention kernel still runs: the
+  // partials are complete only after this wait (a no-op for an ordinary launch)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int g = threadIdx.x >> 7, d = threadIdx.x & 127;
   float* wts = wall + g * np_alloc;
   bool first = true;
@@ -450,7 +457,7 @@ akv_merge128_kernel(MergeArgs a, int rows, int np_alloc) {
   asm volatile("cp.async.wait_group 0;\n" ::: "memory");
 }
 
-int launch_merge(const MergeArgs& a, int rows, cudaStream_t st) {
+int launch_merge(const MergeArgs& a, int rows, cudaStream_t st, bool pdl) {
   const int np_alloc = a.np > 0 ? a.np : 1;
   static const bool no_rot128 = getenv("AKV_NO_ROT128") != nullptr;
   const size_t smem128 = (size_t)ROT128_MAT_BYTES + (size_t)(4 * 128 + 4 * np_alloc + 8) * sizeof(float);
@@ -459,7 +466,17 @@ int launch_merge(const MergeArgs& a, int rows, cudaStream_t st) {
     if (e != cudaSuccess) return fail((int)e, "merge: smem attribute: %s", cudaGetErrorString(e));
     const int quads = (rows + 3) / 4;
     const int grid = quads < 2 * sm_count() ? quads : 2 * sm_count();
-    akv_merge128_kernel<<<grid, ROT128_THREADS, smem128, st>>>(a, rows, np_alloc);
+    if (pdl) {
+      cudaLaunchConfig_t cfg{};
+      cfg.gridDim = dim3(grid); cfg.blockDim = dim3(ROT128_THREADS); cfg.dynamicSmemBytes = smem128; cfg.stream = st;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      at[0].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = at; cfg.numAttrs = 1;
+      cudaLaunchKernelEx(&cfg, akv_merge128_kernel, a, rows, np_alloc);
+    } else {
+      akv_merge128_kernel<<<grid, ROT128_THREADS, smem128, st>>>(a, rows, np_alloc);
+    }
     return check_launch("akv_merge128_kernel");
   }
   akv_merge_kernel<<<rows, a.D < 128 ? (a.D < 32 ? 32 : a.D) : 128, (a.D + np_alloc) * sizeof(float), st>>>(a);
@@ -2465,6 +2482,10 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
                    p->num_q_heads / p->num_kv_heads <= 4 && p->kp_stride_pos % 16 == 0 && p->vp_stride_pos % 16 == 0 &&
                    p->kp_stride_blk % 16 == 0 && p->vp_stride_blk % 16 == 0 && t4_make_maps(a, &maps);
 
+  // The three launches of a step overlap their ends and beginnings (programmatic dependent launch) unless the
+  // caller brackets the attention kernel with events, which have to sit between whole launches.
+  static const bool no_pdl = getenv("AKV_NO_PDL") != nullptr;
+  const bool pdl = tma && !no_pdl && D == 128 && !no_rot128 && !p->ev_kernel_start && !p->ev_kernel_stop;
   if (p->ev_kernel_start) cudaEventRecord((cudaEvent_t)p->ev_kernel_start, st);
   if (p->max_blocks_per_seq > 0) {
     if (tma) {
@@ -2474,7 +2495,20 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T4_DYN_SMEM);
       if (e != cudaSuccess) return fail((int)e, "attention: smem attribute: %s", cudaGetErrorString(e));
       dim3 grid(plan.sk_grid, p->num_kv_heads / 8);
-      kern<<<grid, T4_THREADS, T4_DYN_SMEM, st>>>(a, maps);
+      if (pdl) {
+        // programmatic dependent launch: the grid may be scheduled while the query-rotation launch drains; the
+        // kernel fills its lookup table and then waits for that launch before reading anything it produced
+        a.pdl = 1;
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = grid; cfg.blockDim = dim3(T4_THREADS); cfg.dynamicSmemBytes = T4_DYN_SMEM; cfg.stream = st;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        cudaLaunchKernelEx(&cfg, kern, a, maps);
+      } else {
+        kern<<<grid, T4_THREADS, T4_DYN_SMEM, st>>>(a, maps);
+      }
       if (int rc = check_launch(p->bits == 4 ? "tq4_attn_tma_kernel" : "tq_lowbit_attn_tma_kernel")) return rc;
     } else if (persist && sk4) {
       a.num_parts = plan.sk_grid;
@@ -2538,7 +2572,7 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
   mg.rot = p->rotation;
   mg.out = p->out; mg.out_dtype = p->out_dtype; mg.out_ss = p->out_stride_seq; mg.out_sh = p->out_stride_head;
   mg.raw_out = p->raw_out;
-  return launch_merge(mg, rows, st);
+  return launch_merge(mg, rows, st, pdl && p->max_blocks_per_seq > 0);
 }
 
 AKV_EXPORT int akv_tq_paged_attn(const akv_tq_attn_params* p) {

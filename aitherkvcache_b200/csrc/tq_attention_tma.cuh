@@ -117,6 +117,32 @@ __device__ __forceinline__ void t4_scores(uint32_t lanebase, const uint32_t (&bq
   }
 }
 
+// The per-lane lookup table of the consumers (entry stride LUT_STRIDE / LUT3_STRIDE, one copy per lane), written by
+// `nthr` threads with 16-byte stores.
+template <int BITS>
+__device__ __forceinline__ void t4_fill_lut(const float* s_cent, int tid, int nthr) {
+  if constexpr (BITS == 4) {          // byte -> half2(c[hi nibble], c[lo nibble])
+    for (int i = tid; i < 256 * 8; i += nthr) {          // entry e, lanes 4 q .. 4 q + 3: one 16-byte store
+      const int e = i >> 3, q4 = i & 7;
+      const uint32_t v = pack_half2(s_cent[e >> 4], s_cent[e & 15]);
+      asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" :: "r"(SK_LUT + e * LUT_STRIDE + q4 * 16), "r"(v));
+    }
+  } else if constexpr (BITS == 3) {   // 6 bits -> half2(c[hi 3 bits], c[lo 3 bits])
+    for (int i = tid; i < 64 * 32; i += nthr) {
+      const int e = i >> 5, l = i & 31;
+      const uint32_t v = pack_half2(s_cent[e >> 3], s_cent[e & 7]);
+      asm volatile("st.shared.u32 [%0], %1;\n" :: "r"(SK_LUT + e * LUT3_STRIDE + l * 4), "r"(v));
+    }
+  } else {                            // byte -> four halves
+    for (int i = tid; i < 256 * 16; i += nthr) {         // entry e, lanes 2 q, 2 q + 1: one 16-byte store
+      const int e = i >> 4, q2 = i & 15;
+      const uint32_t v0 = pack_half2(s_cent[e >> 6], s_cent[(e >> 4) & 3]);
+      const uint32_t v1 = pack_half2(s_cent[(e >> 2) & 3], s_cent[e & 3]);
+      asm volatile("st.shared.v4.u32 [%0], {%1,%2,%1,%2};\n" :: "r"(SK_LUT + e * LUT_STRIDE + q2 * 16), "r"(v0), "r"(v1));
+    }
+  }
+}
+
 // BITS = 4: the layouts above.  BITS = 3, 2 (48 / 32 packed bytes per token and head): K and V codes both as
 // [head][token][PD] boxes without swizzle, the lookup tables and the natural-order fragment helpers of the
 // low-bit kernels (lowbit_k_fragments, lowbit_v_fragments); block slots keep their 8 KB spacing.
@@ -135,6 +161,8 @@ tq_attn_tma_kernel(AttnArgs a, const __grid_constant__ T4Maps maps) {
     if (tid == 0) g_attn_window_status = 1;
     return;
   }
+  // the merge launch that follows may be scheduled already; it waits for this whole grid before it reads partials
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (tid < 16) s_cent[tid] = tid < (1 << BITS) ? a.centroids[tid] : 0.f;
   if (tid == 0) {
     asm volatile("st.shared.u32 [%0], %1;" :: "r"(T4_FAILED), "r"(0u) : "memory");
@@ -143,6 +171,14 @@ tq_attn_tma_kernel(AttnArgs a, const __grid_constant__ T4Maps maps) {
 #pragma unroll
     for (int i = 4; i < 8; ++i) t4_bar_init(T4_BAR + 8 * i, 8);          // emptyK[0..1], emptyV[0..1]: eight consumer warps
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // Launched as a programmatic dependent of the query-rotation launch (a.pdl), this grid may start while that one
+  // still runs: the lookup table, which needs nothing of it, is filled first, then the grid waits for it.
+  const bool lut_first = a.pdl != 0;
+  if (lut_first) {
+    __syncthreads();                 // centroids
+    t4_fill_lut<BITS>(s_cent, tid, T4_THREADS);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
   }
   // The plan written by the query-rotation launch ([0..S] stage prefix, [S] total, [S+1] stages per CTA, then three
   // words per sequence) comes into shared memory with one round of loads; every later look-up is a shared load.
@@ -176,26 +212,7 @@ tq_attn_tma_kernel(AttnArgs a, const __grid_constant__ T4Maps maps) {
   while (seq0 < S - 1 && u_begin >= P(seq0 + 1)) ++seq0;      // skip sequences without stages
 
   if (warp < 8) {        // the consumers fill the lookup table while the producer already issues copies
-    if constexpr (BITS == 4) {          // byte -> half2(c[hi nibble], c[lo nibble])
-      for (int i = tid; i < 256 * 8; i += 256) {          // entry e, lanes 4 q .. 4 q + 3: one 16-byte store
-        const int e = i >> 3, q4 = i & 7;
-        const uint32_t v = pack_half2(s_cent[e >> 4], s_cent[e & 15]);
-        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" :: "r"(SK_LUT + e * LUT_STRIDE + q4 * 16), "r"(v));
-      }
-    } else if constexpr (BITS == 3) {   // 6 bits -> half2(c[hi 3 bits], c[lo 3 bits])
-      for (int i = tid; i < 64 * 32; i += 256) {
-        const int e = i >> 5, l = i & 31;
-        const uint32_t v = pack_half2(s_cent[e >> 3], s_cent[e & 7]);
-        asm volatile("st.shared.u32 [%0], %1;\n" :: "r"(SK_LUT + e * LUT3_STRIDE + l * 4), "r"(v));
-      }
-    } else {                            // byte -> four halves
-      for (int i = tid; i < 256 * 16; i += 256) {         // entry e, lanes 2 q, 2 q + 1: one 16-byte store
-        const int e = i >> 4, q2 = i & 15;
-        const uint32_t v0 = pack_half2(s_cent[e >> 6], s_cent[(e >> 4) & 3]);
-        const uint32_t v1 = pack_half2(s_cent[(e >> 2) & 3], s_cent[e & 3]);
-        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%1,%2};\n" :: "r"(SK_LUT + e * LUT_STRIDE + q2 * 16), "r"(v0), "r"(v1));
-      }
-    }
+    if (!lut_first) t4_fill_lut<BITS>(s_cent, tid, 256);
     asm volatile("bar.sync 1, 256;" ::: "memory");
   }
 
