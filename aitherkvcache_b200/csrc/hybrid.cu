@@ -1172,6 +1172,10 @@ __device__ __forceinline__ uint2 hm_quad2(uint32_t w, uint32_t lane8) {
   return hm_lds64c<HM_LUT2>(__byte_perm(w, lane8, 0x7604 + (K << 4)));
 }
 
+// PAR (at most four query heads per KV head): the eight MMA columns of the value products are (query head, parity of
+// the coordinate), so a table entry (two neighbouring coordinates of one token) is a complete A register and the
+// accumulators halve; score columns 4..7 repeat heads 0..3 so that every column finds its weights.
+template <bool PAR>
 __global__ void __launch_bounds__(HA_WARPS * 32, 2)
 hybrid_attn_mma_kernel(HybridAttnArgs a) {
   extern __shared__ __align__(16) unsigned char hm_smem[];
@@ -1222,13 +1226,14 @@ hybrid_attn_mma_kernel(HybridAttnArgs a) {
   // ---- query fragments: thread (g, t) holds q'[q head g][segment][16t .. 16t+15] ----
   uint32_t bq[4][4][2];
   {
-    const float* qp = a.qprime + ((int64_t)seq * a.num_q_heads + h * G + (g < G ? g : 0)) * 256 + 16 * t;
+    const int qcol = PAR ? (g & 3) : g;        // query head of score column g
+    const float* qp = a.qprime + ((int64_t)seq * a.num_q_heads + h * G + (qcol < G ? qcol : 0)) * 256 + 16 * t;
 #pragma unroll
     for (int sg = 0; sg < 4; ++sg)
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk) {
         float4 f = *reinterpret_cast<const float4*>(qp + 64 * sg + 4 * kk);
-        if (g >= G) f = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (qcol >= G) f = make_float4(0.f, 0.f, 0.f, 0.f);
         bq[sg][kk][0] = hm_pack(f.x, f.y);
         bq[sg][kk][1] = hm_pack(f.z, f.w);
       }
@@ -1252,11 +1257,33 @@ hybrid_attn_mma_kernel(HybridAttnArgs a) {
   const uint32_t oVs0 = vRow + swz(24 + g, sV), oVc1 = vRow + swz(36 + 2 * g, sV), oVs1 = vRow + swz(52 + g, sV);
   const uint32_t selV0 = (vo << 12) | ((vo + 1) << 8) | ((vo + 2) << 4) | (vo + 3);
 
-  float o[4][4][4];
+  constexpr int NT = PAR ? 2 : 4;        // accumulator tiles per segment
+  float o[4][NT][4];
 #pragma unroll
   for (int sg = 0; sg < 4; ++sg)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) { o[sg][j][0] = o[sg][j][1] = o[sg][j][2] = o[sg][j][3] = 0.f; }
+    for (int j = 0; j < NT; ++j) { o[sg][j][0] = o[sg][j][1] = o[sg][j][2] = o[sg][j][3] = 0.f; }
+  // PAR: B operand of a value product from the transposed weights x = (P[token 2t], P[token 2t+1]) of column g's head:
+  // the weight goes into the half that matches the column's parity, the other half is zero
+  const uint32_t selA = (g >> 2) ? 0x1044u : 0x4410u, selB = (g >> 2) ? 0x3244u : 0x4432u;
+  auto value_mmas = [&](float (&acc)[NT][4], const uint32_t (&n)[4][4], uint32_t pa_, uint32_t pb_) {
+    if constexpr (PAR) {
+      // rows g / g+8 of tile mt are coordinate pairs 4g + 2mt / 4g + 2mt + 1; k-step 0 holds tokens 2t, 2t+1, k-step 1 tokens 2t+8, 2t+9
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        hm_mma(acc[mt], n[0][2 * mt], n[0][2 * mt + 1], n[1][2 * mt], n[1][2 * mt + 1],
+               __byte_perm(pa_, 0u, selA), __byte_perm(pa_, 0u, selB));
+        hm_mma(acc[mt], n[2][2 * mt], n[2][2 * mt + 1], n[3][2 * mt], n[3][2 * mt + 1],
+               __byte_perm(pb_, 0u, selA), __byte_perm(pb_, 0u, selB));
+      }
+    } else {
+      // M-tile j pairs the same coordinate of two tokens: rows g / g+8 of the tile are coordinates 8g+2j / 8g+2j+1
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        hm_mma(acc[j], __byte_perm(n[0][j], n[1][j], 0x5410), __byte_perm(n[0][j], n[1][j], 0x7632),
+               __byte_perm(n[2][j], n[3][j], 0x5410), __byte_perm(n[2][j], n[3][j], 0x7632), pa_, pb_);
+    }
+  };
   float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
 
   const int64_t first = tile_begin + warp;
@@ -1390,7 +1417,7 @@ hybrid_attn_mma_kernel(HybridAttnArgs a) {
 #pragma unroll
       for (int sg = 0; sg < 4; ++sg)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) { o[sg][j][0] *= al0; o[sg][j][1] *= al1; o[sg][j][2] *= al0; o[sg][j][3] *= al1; }
+        for (int j = 0; j < NT; ++j) { o[sg][j][0] *= al0; o[sg][j][1] *= al1; o[sg][j][2] *= al0; o[sg][j][3] *= al1; }
       m0 = mn0; m1 = mn1;
     }
     const float p0 = hm_ex2(s0 - mn0), p1 = hm_ex2(s1 - mn1), p2 = hm_ex2(s2 - mn0), p3 = hm_ex2(s3 - mn1);
@@ -1418,10 +1445,7 @@ hybrid_attn_mma_kernel(HybridAttnArgs a) {
       }
       HM_FOUR_TOKENS(HM_V0)
 #undef HM_V0
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-        hm_mma(o[0][j], __byte_perm(n[0][j], n[1][j], 0x5410), __byte_perm(n[0][j], n[1][j], 0x7632),
-               __byte_perm(n[2][j], n[3][j], 0x5410), __byte_perm(n[2][j], n[3][j], 0x7632), pbA[0], pbB[0]);
+      value_mmas(o[0], n, pbA[0], pbB[0]);
     }
 #pragma unroll
     for (int sgn = 0; sgn < 2; ++sgn) {   // segments 1 and 3
@@ -1436,10 +1460,7 @@ hybrid_attn_mma_kernel(HybridAttnArgs a) {
       }
       HM_FOUR_TOKENS(HM_VS)
 #undef HM_VS
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-        hm_mma(o[sg][j], __byte_perm(n[0][j], n[1][j], 0x5410), __byte_perm(n[0][j], n[1][j], 0x7632),
-               __byte_perm(n[2][j], n[3][j], 0x5410), __byte_perm(n[2][j], n[3][j], 0x7632), pbA[sg], pbB[sg]);
+      value_mmas(o[sg], n, pbA[sg], pbB[sg]);
     }
     {   // segment 2
       uint32_t n[4][4];
@@ -1452,10 +1473,7 @@ hybrid_attn_mma_kernel(HybridAttnArgs a) {
       HM_FOUR_TOKENS(HM_V2)
 #undef HM_V2
 #undef HM_FOUR_TOKENS
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-        hm_mma(o[2][j], __byte_perm(n[0][j], n[1][j], 0x5410), __byte_perm(n[0][j], n[1][j], 0x7632),
-               __byte_perm(n[2][j], n[3][j], 0x5410), __byte_perm(n[2][j], n[3][j], 0x7632), pbA[2], pbB[2]);
+      value_mmas(o[2], n, pbA[2], pbB[2]);
     }
     __syncwarp();   // every lane is done with this buffer before the copy after next lands in it
   }
@@ -1468,6 +1486,29 @@ hybrid_attn_mma_kernel(HybridAttnArgs a) {
     l1 += __shfl_xor_sync(0xffffffffu, l1, offs);
   }
   const int part = split * HA_WARPS + warp;
+  if constexpr (PAR) {
+    // accumulator columns 2t, 2t+1 are query heads 2 (t & 1), 2 (t & 1) + 1 at coordinate parity t >> 1
+    const int par = t >> 1;
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int qg = 2 * (t & 1) + e;
+      if (qg >= G) continue;
+      const int64_t row = (int64_t)seq * a.num_q_heads + h * G + qg;
+      float* pa = a.part_acc + (row * a.num_parts + part) * 256;
+#pragma unroll
+      for (int sg = 0; sg < 4; ++sg)
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          pa[64 * sg + 8 * g + 4 * mt + par] = o[sg][mt][e];
+          pa[64 * sg + 8 * g + 4 * mt + 2 + par] = o[sg][mt][2 + e];
+        }
+      if (g == 0 && t < 2) {
+        a.part_ml[(row * a.num_parts + part) * 2] = e ? m1 : m0;
+        a.part_ml[(row * a.num_parts + part) * 2 + 1] = e ? l1 : l0;
+      }
+    }
+    return;
+  }
 #pragma unroll
   for (int e = 0; e < 2; ++e) {
     const int qg = 2 * t + e;
@@ -1477,7 +1518,7 @@ hybrid_attn_mma_kernel(HybridAttnArgs a) {
 #pragma unroll
     for (int sg = 0; sg < 4; ++sg)
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
+      for (int j = 0; j < NT; ++j)
         *reinterpret_cast<float2*>(pa + 64 * sg + 8 * g + 2 * j) = make_float2(o[sg][j][e], o[sg][j][2 + e]);
     if (g == 0) {
       a.part_ml[(row * a.num_parts + part) * 2] = e ? m1 : m0;
@@ -1948,14 +1989,17 @@ static int run_hybrid_attn(const akv_hybrid_attn_params* p, const HyStepWrite* w
                              p->k_stride_blk | p->k_stride_pos | p->k_stride_head | p->v_stride_blk |
                              p->v_stride_pos | p->v_stride_head) & 15) == 0;
     // the tensor-core kernel keeps its tables at fixed shared addresses: its dynamic window must start below them
-    static const bool window_ok = dyn_smem_window_start(reinterpret_cast<const void*>(hybrid_attn_mma_kernel)) <= HM_LUT2;
+    static const bool window_ok = dyn_smem_window_start(reinterpret_cast<const void*>(hybrid_attn_mma_kernel<false>)) <= HM_LUT2 &&
+        dyn_smem_window_start(reinterpret_cast<const void*>(hybrid_attn_mma_kernel<true>)) <= HM_LUT2;
     if (mode == 25) {
       hybrid_attn25_kernel<<<grid, HA_WARPS * 32, 0, st>>>(a);
       if (int rc = check_launch("hybrid_attn25_kernel")) return rc;
     } else if (!force_scalar && window_ok && aligned16 && p->block_size % 16 == 0 && p->num_q_heads / p->num_kv_heads <= 8) {
-      cudaError_t e = cudaFuncSetAttribute(hybrid_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, HM_SMEM);
+      static const bool no_par = getenv("AKV_HYBRID_NO_PAR") != nullptr;
+      auto kern = (p->num_q_heads / p->num_kv_heads <= 4 && !no_par) ? hybrid_attn_mma_kernel<true> : hybrid_attn_mma_kernel<false>;
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, HM_SMEM);
       if (e != cudaSuccess) return fail((int)e, "hybrid attention: smem attribute: %s", cudaGetErrorString(e));
-      hybrid_attn_mma_kernel<<<grid, HA_WARPS * 32, HM_SMEM, st>>>(a);
+      kern<<<grid, HA_WARPS * 32, HM_SMEM, st>>>(a);
       if (int rc = check_launch("hybrid_attn_mma_kernel")) return rc;
     } else {
       hybrid_attn_kernel<<<grid, HA_WARPS * 32, 0, st>>>(a);

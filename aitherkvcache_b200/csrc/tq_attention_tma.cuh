@@ -163,6 +163,10 @@ tq_attn_tma_kernel(AttnArgs a, const __grid_constant__ T4Maps maps) {
   }
   // the merge launch that follows may be scheduled already; it waits for this whole grid before it reads partials
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (warp == 8 && lane < 4) {       // the producer's four tensor maps into the descriptor cache, ahead of the first copy
+    const CUtensorMap* mp = lane == 0 ? &maps.k : lane == 1 ? &maps.v : lane == 2 ? &maps.kn : &maps.vn;
+    asm volatile("prefetch.tensormap [%0];" :: "l"(mp) : "memory");
+  }
   if (tid < 16) s_cent[tid] = tid < (1 << BITS) ? a.centroids[tid] : 0.f;
   if (tid == 0) {
     asm volatile("st.shared.u32 [%0], %1;" :: "r"(T4_FAILED), "r"(0u) : "memory");
