@@ -132,6 +132,30 @@ def test_decode_large_batch_vs_oracle(bits, out_dtype):
     assert (dec[3] == 0).all()
 
 
+@pytest.mark.parametrize("bits,dt", ((4, torch.float16), (3, torch.bfloat16), (2, torch.float16)))
+def test_codec_pipelines_many_tiles_per_cta(bits, dt):
+    """Several 128-vector tiles per CTA (3 x 148 tiles and a ragged one): the steady state of the tensor-core
+    encoder and decoder (operand stages and accumulators reused, barrier phases wrapping) against the oracle."""
+    g = load_golden(f"tq_d128_b{bits}.npz")
+    tq = _tq(128, bits, g, dtype=dt)
+    n = 3 * 148 * 128 + 45
+    x = torch.randn(n, 128, generator=torch.Generator().manual_seed(77 + bits)).to(dt)
+    packed, norms = tq.encode(x.cuda())
+    op, on, margin = otq.encode(x.float().numpy(), g["rotation"], g["boundaries"], bits, return_margin=True)
+    assert np.array_equal(norms.cpu().numpy().view(np.uint32), on.view(np.uint32))
+    diff = otq.unpack(packed.cpu().numpy(), 128, bits) != otq.unpack(op, 128, bits)
+    assert not (diff & ~(margin < 1e-6)).any() and diff.mean() < 1e-5
+    dec = tq.decode(torch.from_numpy(op).cuda(), torch.from_numpy(on).cuda())
+    assert dec.dtype == dt and dec.shape == (n, 128)
+    ref = otq.decode_f32(op, on, g["rotation"], g["centroids"], bits)
+    tol = 2.0 ** (-10 if dt == torch.float16 else -7)
+    d_abs = (dec.float().cpu() - torch.from_numpy(ref).to(dt).float()).abs().numpy()
+    assert (d_abs <= tol * np.abs(ref) + 1e-6 * on[:, None]).all()
+    assert (dec.cpu() != torch.from_numpy(ref).to(dt)).float().mean().item() < 2e-3
+    from aitherkvcache_b200 import _lib
+    assert _lib.device_status()["tc_encode"] == 0 and _lib.device_status()["tc_decode"] == 0
+
+
 @pytest.mark.parametrize("d,bits", [(256, 4), (32, 3), (16, 2), (512, 4)])
 def test_generic_head_dims_vs_oracle(d, bits):
     tq = _tq(d, bits)
