@@ -41,9 +41,11 @@ def codec_from_env_or_dtype(cache_dtype_str: Optional[str] = None) -> Tuple[str,
         return "hybrid", KV_DTYPE_HYBRID[cache_dtype_str]
     if cache_dtype_str in KV_DTYPE_BITS:
         return "uniform", KV_DTYPE_BITS[cache_dtype_str]
-    mode = os.environ.get("AITHER_TQ_MODE", "")
+    mode = os.environ.get("AITHER_TQ_MODE", "").replace("-primary", "")
     if mode in ("tq35", "tq25"):
         return "hybrid", mode
+    if mode in ("tq4", "tq3", "tq2"):
+        return "uniform", int(mode[2])
     return "uniform", bits_from_env_or_dtype(cache_dtype_str)
 
 
@@ -109,6 +111,12 @@ class TurboQuantImplBase:
             self.packed_dim = head_size * self.tq_bits // 8
 
     def _norms(self, layer_name: str, kv_cache: torch.Tensor):
+        pd = self.packed_dim
+        if kv_cache.shape[-1] == pd + 4 and pd % 4 == 0:
+            # primary-mode records: the norm is the float32 behind the codes of the same row
+            # (reference page layout, vllm/engine.py:125-133); strided views, nothing is copied
+            n = kv_cache[..., pd:pd + 4].view(torch.float32).squeeze(-1)       # [blocks, 2, block_size, kv_heads]
+            return n[:, 0], n[:, 1]
         kn = _LayerState.k_norms.get(layer_name)
         shape = (kv_cache.shape[0], kv_cache.shape[2], kv_cache.shape[3])
         if kn is None or kn.shape != shape or kn.device != kv_cache.device:
@@ -236,6 +244,9 @@ def _make_backend_class():
 
         @staticmethod
         def get_kv_cache_shape(num_blocks, block_size, num_kv_heads, head_size, cache_dtype_str="auto"):
+            from .engine import is_primary_mode, tq_dim_for_head
+            if is_primary_mode():      # the cache is the packed cache: one record per (token, KV head)
+                return (num_blocks, 2, block_size, num_kv_heads, tq_dim_for_head(head_size))
             return (num_blocks, 2, block_size, num_kv_heads, head_size)
 
         @staticmethod

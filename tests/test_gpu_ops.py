@@ -172,7 +172,7 @@ def test_backend_impl_cache_update_decode_and_prefill():
     impl.forward(layer, qry[last], None, None, kv, md1, output=out1)
     assert (out1.float() - out[last].float()).abs().max().item() < 2e-3
     tq = next(iter(_LayerState.quantizers.values()))
-    kn = _LayerState.k_norms[layer.layer_name]
+    kn = impl._norms(layer.layer_name, kv)[0]          # 68-byte rows: the norms live behind the codes
     op, on = otq.encode(key.cpu().numpy(), tq.rotation.cpu().numpy(), tq.boundaries_inner.cpu().numpy(), bits)
     got_n = kn.reshape(-1, H)[slots.cuda()].cpu().numpy()
     assert np.array_equal(got_n.view(np.uint32), on.view(np.uint32))
@@ -297,7 +297,7 @@ def test_backend_mixed_batch_attends_over_the_packed_cache():
     out = torch.zeros(nq, QH * 128, dtype=torch.float16, device="cuda")
     impl.forward(layer, qry.cuda(), None, None, kv, md, output=out)
     tq = _LayerState.quantizers[(128, 4, "cuda:0")]
-    kn, vn = _LayerState.k_norms[layer.layer_name], _LayerState.v_norms[layer.layer_name]
+    kn, vn = impl._norms(layer.layer_name, kv)
     ref = _causal_oracle(qry.reshape(nq, QH, 128).numpy(), kv[:, 0, ..., :64].cpu().numpy(), kn.cpu().numpy(),
                          kv[:, 1, ..., :64].cpu().numpy(), vn.cpu().numpy(), bt.numpy(), lens, qlens,
                          tq.rotation.cpu().numpy(), tq.centroids.cpu().numpy(), bits)
@@ -398,3 +398,42 @@ def test_backend_decode_step_replays_from_a_cuda_graph():
         impl.forward(layer, q, None, None, kv, md, output=out)
         torch.cuda.synchronize()
         assert torch.equal(got, out)
+
+
+@pytest.mark.parametrize("bits", (4, 3))
+def test_backend_primary_records_keep_norms_in_the_row(monkeypatch, bits):
+    """Primary-mode cache [blocks, 2, block_size, heads, packed_dim + 4]: the float32 norm of a vector sits behind
+    its codes in the same row.  Writes and attention over this layout equal the separate-norm layout bit for bit."""
+    from aitherkvcache_b200.vllm.backend import TurboQuantBackend, TurboQuantImplBase, _LayerState
+    monkeypatch.setenv("AITHER_TQ_MODE", f"tq{bits}-primary")
+    H, QH, bs, pd = 8, 32, 16, 128 * bits // 8
+    assert TurboQuantBackend.get_kv_cache_shape(14, bs, H, 128) == (14, 2, bs, H, pd + 4)
+    impl = TurboQuantImplBase()
+    impl._tq_setup(QH, 128, 1.0 / math.sqrt(128), H, "auto")
+    assert impl.tq_codec == "uniform" and impl.tq_bits == bits and impl.packed_dim == pd
+    lens = [45, 130]
+    bt = torch.tensor([[3, 7, 1, 0, 0, 0, 0, 0, 0], [2, 4, 5, 6, 8, 9, 10, 11, 12]], dtype=torch.int32)
+    gen = torch.Generator().manual_seed(31)
+    T = sum(lens)
+    key = torch.randn(T, H, 128, generator=gen).half().cuda()
+    val = torch.randn(T, H, 128, generator=gen).half().cuda()
+    slots = torch.cat([(bt[s, :(n + bs - 1) // bs].long()[:, None] * bs + torch.arange(bs)[None]).reshape(-1)[:n]
+                       for s, n in enumerate(lens)]).cuda()
+    q = torch.randn(2, QH * 128, generator=gen).half().cuda()
+    md = types.SimpleNamespace(num_actual_tokens=2, max_query_len=1, block_table=bt.cuda(),
+                               seq_lens=torch.tensor(lens, dtype=torch.int32, device="cuda"))
+    outs, caches = [], []
+    for width, name in ((pd + 4, "prim.layers.0.attn"), (128, "sep.layers.0.attn")):
+        layer = types.SimpleNamespace(layer_name=name)
+        kv = torch.zeros(14, 2, bs, H, width, dtype=torch.uint8, device="cuda")
+        impl.do_kv_cache_update(layer, key, val, kv, slots)
+        out = torch.zeros(2, QH * 128, dtype=torch.float16, device="cuda")
+        impl.forward(layer, q, None, None, kv, md, output=out)
+        outs.append(out)
+        caches.append(kv)
+    prim, sep = caches
+    assert torch.equal(prim[..., :pd], sep[..., :pd])
+    assert "prim.layers.0.attn" not in _LayerState.k_norms            # no side tensors for the record layout
+    kn = prim[:, 0, :, :, pd:].contiguous().view(torch.float32).squeeze(-1)
+    assert torch.equal(kn, _LayerState.k_norms["sep.layers.0.attn"])
+    assert torch.equal(outs[0], outs[1])

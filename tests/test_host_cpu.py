@@ -177,3 +177,39 @@ def test_spectral_kv_cache_host_semantics():
     assert torch.equal(cache.k_packed[2], cache.k_packed[5]) and int(cache._block_fill[2]) == 5
     cache.clear_block(5)
     assert cache.k_scales[5].abs().sum() == 0 and cache.memory_stats()["total_tokens"] == 37
+
+
+def test_primary_mode_page_sizes_and_vllm_patch(monkeypatch):
+    """Page sizing of the primary (packed) cache: the reference's formulas (vllm/engine.py:110-154), and the
+    page-size patch on the installed vLLM's KV-cache specs."""
+    from aitherkvcache_b200.vllm import engine
+    monkeypatch.delenv("AITHER_TQ_MODE", raising=False)
+    monkeypatch.setenv("AITHER_TQ_BITS", "4")
+    assert not engine.is_primary_mode()
+    assert engine.tq_dim_for_head(128) == 68 and engine.tq_page_size_bytes(16, 8, 128) == 2 * 16 * 8 * 68
+    assert engine.tq_dim_for_head(128, bits=3) == 52 and engine.tq_dim_for_head(128, bits=2) == 36
+    assert engine.align_page_size(17408) == 32768 and engine.align_page_size(16384) == 16384 and engine.align_page_size(0) == 0
+    monkeypatch.setenv("AITHER_TQ_MODE", "tq35-primary")
+    assert engine.is_primary_mode() and engine.tq_dim_for_head(128) == 64
+    assert engine.tq_page_size_bytes(16, 8, 128) == 2 * 16 * 8 * 64
+    monkeypatch.setenv("AITHER_TQ_MODE", "tq25")
+    assert not engine.is_primary_mode() and engine.tq_dim_for_head(128) == 44
+    monkeypatch.setenv("AITHER_TQ_MODE", "tq3-primary")
+    assert engine.tq_dim_for_head(128) == 52
+    vllm_spec = pytest.importorskip("vllm.v1.kv_cache_interface")
+    import torch
+    monkeypatch.setenv("AITHER_TQ_MODE", "tq4-primary")
+    spec = vllm_spec.FullAttentionSpec(block_size=16, num_kv_heads=8, head_size=128, dtype=torch.uint8)
+    stock = spec.real_page_size_bytes
+    assert stock == 2 * 16 * 8 * 128
+    try:
+        assert engine.apply_tq_patches(bits=4)
+        assert spec.real_page_size_bytes == 17408 and spec.page_size_bytes == 17408        # 16 x 8 x 2 records of 68 bytes
+        from aitherkvcache_b200.vllm.backend import TurboQuantBackend
+        assert TurboQuantBackend.get_kv_cache_shape(10, 16, 8, 128) == (10, 2, 16, 8, 68)
+    finally:
+        engine.remove_tq_patches()
+    assert spec.real_page_size_bytes == stock
+    monkeypatch.delenv("AITHER_TQ_MODE")
+    from aitherkvcache_b200.vllm.backend import TurboQuantBackend
+    assert TurboQuantBackend.get_kv_cache_shape(10, 16, 8, 128) == (10, 2, 16, 8, 128)
