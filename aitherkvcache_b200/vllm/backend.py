@@ -115,8 +115,11 @@ class TurboQuantImplBase:
         if kv_cache.shape[-1] == pd + 4 and pd % 4 == 0:
             # primary-mode records: the norm is the float32 behind the codes of the same row
             # (reference page layout, vllm/engine.py:125-133); strided views, nothing is copied
-            n = kv_cache[..., pd:pd + 4].view(torch.float32).squeeze(-1)       # [blocks, 2, block_size, kv_heads]
-            return n[:, 0], n[:, 1]
+            try:
+                n = kv_cache[..., pd:pd + 4].view(torch.float32).squeeze(-1)   # [blocks, 2, block_size, kv_heads]
+                return n[:, 0], n[:, 1]
+            except RuntimeError:       # rows that are not 4-byte aligned views: side tensors below
+                pass
         kn = _LayerState.k_norms.get(layer_name)
         shape = (kv_cache.shape[0], kv_cache.shape[2], kv_cache.shape[3])
         if kn is None or kn.shape != shape or kn.device != kv_cache.device:
