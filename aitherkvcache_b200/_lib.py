@@ -47,6 +47,29 @@ class TQAttnParams(C.Structure):
     ]
 
 
+class TQPrefillParams(C.Structure):
+    """Mirror of ``akv_tq_prefill_params``."""
+    _fields_ = [
+        ("query", c_vp), ("q_dtype", c_int), ("q_stride_tok", c_i64), ("q_stride_head", c_i64),
+        ("k_packed", c_vp), ("kp_stride_blk", c_i64), ("kp_stride_pos", c_i64), ("kp_stride_head", c_i64),
+        ("k_norms", c_vp), ("kn_stride_blk", c_i64), ("kn_stride_pos", c_i64), ("kn_stride_head", c_i64),
+        ("v_packed", c_vp), ("vp_stride_blk", c_i64), ("vp_stride_pos", c_i64), ("vp_stride_head", c_i64),
+        ("v_norms", c_vp), ("vn_stride_blk", c_i64), ("vn_stride_pos", c_i64), ("vn_stride_head", c_i64),
+        ("block_tables", c_vp), ("bt_dtype", c_int), ("bt_stride_seq", c_i64),
+        ("seq_lens", c_vp), ("sl_dtype", c_int),
+        ("query_start_loc", c_vp), ("qs_dtype", c_int),
+        ("num_seqs", c_int), ("num_tokens", c_int), ("num_q_heads", c_int), ("num_kv_heads", c_int),
+        ("head_dim", c_int), ("block_size", c_int), ("max_blocks_per_seq", c_int),
+        ("num_blocks", c_i64),
+        ("bits", c_int),
+        ("rotation", c_vp), ("rotation_t", c_vp), ("centroids", c_vp),
+        ("scale", c_f),
+        ("out", c_vp), ("out_dtype", c_int), ("out_stride_tok", c_i64), ("out_stride_head", c_i64),
+        ("workspace", c_vp), ("workspace_bytes", C.c_size_t),
+        ("stream", c_vp),
+    ]
+
+
 class TQDecodeStepParams(C.Structure):
     """Mirror of ``akv_tq_decode_step_params``."""
     _fields_ = [
@@ -155,6 +178,8 @@ _SIGNATURES = {
                                  c_i64, c_vp, c_i64, c_i64, c_i64, c_int, c_vp, c_vp, c_int, c_i64, c_vp]),
     "akv_tq_paged_attn_workspace_bytes": (C.c_size_t, [c_int] * 8),
     "akv_tq_paged_attn": (c_int, [C.POINTER(TQAttnParams)]),
+    "akv_tq_prefill_attn_workspace_bytes": (C.c_size_t, [c_int, c_int]),
+    "akv_tq_prefill_attn": (c_int, [C.POINTER(TQPrefillParams)]),
     "akv_tq_decode_step": (c_int, [C.POINTER(TQDecodeStepParams)]),
     "akv_tq_paged_attn_static_scratch_bytes": (C.c_size_t, []),
     "akv_tq_paged_attn_static": (c_int, [C.POINTER(TQAttnParams)]),

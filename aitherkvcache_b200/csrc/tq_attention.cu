@@ -2253,6 +2253,7 @@ tq_attn_streamk4_lowbit_kernel(AttnArgs a) {
 
 }  // namespace akv
 #include "tq_attention_tma.cuh"
+#include "tq_prefill.cuh"
 namespace akv {
 
 int attn_window_status(int* host_out, int reset) {
@@ -2689,6 +2690,120 @@ static int static_scratch_ptr(void** out) {
   return AKV_OK;
 }
 }  // namespace akv
+
+// Mirror of akv_tq_prefill_params in include/akv_b200.h.
+struct akv_tq_prefill_params {
+  const void* query; int q_dtype; int64_t q_stride_tok, q_stride_head;
+  const uint8_t* k_packed; int64_t kp_stride_blk, kp_stride_pos, kp_stride_head;
+  const float* k_norms; int64_t kn_stride_blk, kn_stride_pos, kn_stride_head;
+  const uint8_t* v_packed; int64_t vp_stride_blk, vp_stride_pos, vp_stride_head;
+  const float* v_norms; int64_t vn_stride_blk, vn_stride_pos, vn_stride_head;
+  const void* block_tables; int bt_dtype; int64_t bt_stride_seq;
+  const void* seq_lens; int sl_dtype;
+  const void* query_start_loc; int qs_dtype;
+  int num_seqs, num_tokens, num_q_heads, num_kv_heads, head_dim, block_size, max_blocks_per_seq;
+  int64_t num_blocks;
+  int bits;
+  const float* rotation; const float* rotation_t; const float* centroids;
+  float scale;
+  void* out; int out_dtype; int64_t out_stride_tok, out_stride_head;
+  void* workspace; size_t workspace_bytes;
+  void* stream;
+};
+
+static void prefill_plan(int num_tokens, int num_q_heads, size_t* off_acc, size_t* off_ml, size_t* total) {
+  const size_t rows = (size_t)num_tokens * num_q_heads;
+  auto al = [](size_t v) { return (v + 255) & ~(size_t)255; };
+  *off_acc = al(rows * 128 * sizeof(float));
+  *off_ml = *off_acc + al(rows * 128 * sizeof(float));
+  *total = *off_ml + al(rows * 2 * sizeof(float));
+}
+
+AKV_EXPORT size_t akv_tq_prefill_attn_workspace_bytes(int num_tokens, int num_q_heads) {
+  if (num_tokens <= 0 || num_q_heads <= 0) return 0;
+  size_t a, m, total;
+  prefill_plan(num_tokens, num_q_heads, &a, &m, &total);
+  return total;
+}
+
+// Returns AKV_ERR_UNSUPPORTED (without touching anything) for shapes the kernel is not built for; the caller
+// then attends row by row with akv_tq_paged_attn.
+AKV_EXPORT int akv_tq_prefill_attn(const akv_tq_prefill_params* p) {
+  if (!p) return fail(AKV_ERR_ARG, "null params");
+  if (p->num_tokens < 0 || p->num_seqs < 0 || p->num_q_heads <= 0 || p->num_kv_heads <= 0 ||
+      p->num_q_heads % p->num_kv_heads || p->block_size <= 0 || p->max_blocks_per_seq < 0 || p->num_blocks <= 0)
+    return fail(AKV_ERR_ARG, "prefill attention: bad sizes");
+  const int G = p->num_q_heads / p->num_kv_heads;
+  auto al16 = [](const void* q, int64_t a, int64_t b, int64_t c) {
+    return ((reinterpret_cast<uintptr_t>(q) | (uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) == 0;
+  };
+  if (p->head_dim != 128 || p->bits != 4 || (G != 1 && G != 2 && G != 4 && G != 8) || p->block_size % 16 != 0 ||
+      !al16(p->k_packed, p->kp_stride_blk, p->kp_stride_pos, p->kp_stride_head) ||
+      !al16(p->v_packed, p->vp_stride_blk, p->vp_stride_pos, p->vp_stride_head))
+    return fail(AKV_ERR_UNSUPPORTED, "prefill attention is built for head_dim 128, 4-bit codes, 1/2/4/8 query heads per KV "
+                                     "head, block sizes that are multiples of 16 and caches readable in 16-byte pieces");
+  if (p->num_tokens == 0 || p->num_seqs == 0) return AKV_OK;
+  if (!p->query || !p->k_packed || !p->v_packed || !p->k_norms || !p->v_norms || !p->block_tables || !p->seq_lens ||
+      !p->query_start_loc || !p->rotation || !p->rotation_t || !p->centroids || !p->out)
+    return fail(AKV_ERR_ARG, "prefill attention: null pointer");
+  size_t off_acc, off_ml, total;
+  prefill_plan(p->num_tokens, p->num_q_heads, &off_acc, &off_ml, &total);
+  if (!p->workspace || p->workspace_bytes < total)
+    return fail(AKV_ERR_WORKSPACE, "workspace too small: need %zu bytes, got %zu", total, p->workspace_bytes);
+  char* ws = reinterpret_cast<char*>(p->workspace);
+  float* qrot = reinterpret_cast<float*>(ws);
+  float* part_acc = reinterpret_cast<float*>(ws + off_acc);
+  float* part_ml = reinterpret_cast<float*>(ws + off_ml);
+  cudaStream_t st = (cudaStream_t)p->stream;
+  const int rows = p->num_tokens * p->num_q_heads;
+  {   // rotated, scaled queries of every token
+    const size_t smem128 = (size_t)ROT128_MAT_BYTES + 4 * 128 * sizeof(float);
+    cudaError_t e = cudaFuncSetAttribute(akv_qrot128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem128);
+    if (e != cudaSuccess) return fail((int)e, "prefill attention: smem attribute: %s", cudaGetErrorString(e));
+    const int quads = (rows + 3) / 4;
+    const int rot_blocks = quads < 2 * sm_count() ? quads : 2 * sm_count();
+    StreamKPlanArgs no_plan{};
+    NewTokenWrite no_write{};
+    akv_qrot128_kernel<<<rot_blocks, ROT128_THREADS, smem128, st>>>(
+        p->query, p->q_dtype, p->q_stride_tok, p->q_stride_head, p->num_q_heads, p->rotation_t,
+        p->scale * 1.4426950408889634f, qrot, rows, rot_blocks, 0, no_plan, no_write);
+    if (int rc = check_launch("akv_qrot128_kernel")) return rc;
+  }
+  // rows that no sequence of the chunk owns (padding) stay at l = 0 and come out as zeros
+  cudaMemsetAsync(part_ml, 0, (size_t)rows * 2 * sizeof(float), st);
+  PrefillArgs a{};
+  a.qrot = qrot;
+  a.k_packed = p->k_packed; a.kp_sb = p->kp_stride_blk; a.kp_sp = p->kp_stride_pos; a.kp_sh = p->kp_stride_head;
+  a.k_norms = p->k_norms; a.kn_sb = p->kn_stride_blk; a.kn_sp = p->kn_stride_pos; a.kn_sh = p->kn_stride_head;
+  a.v_packed = p->v_packed; a.vp_sb = p->vp_stride_blk; a.vp_sp = p->vp_stride_pos; a.vp_sh = p->vp_stride_head;
+  a.v_norms = p->v_norms; a.vn_sb = p->vn_stride_blk; a.vn_sp = p->vn_stride_pos; a.vn_sh = p->vn_stride_head;
+  a.block_tables = p->block_tables; a.bt_dtype = p->bt_dtype; a.bt_stride = p->bt_stride_seq;
+  a.seq_lens = p->seq_lens; a.sl_dtype = p->sl_dtype;
+  a.query_start_loc = p->query_start_loc; a.qs_dtype = p->qs_dtype;
+  a.num_seqs = p->num_seqs; a.n_tokens = p->num_tokens; a.num_q_heads = p->num_q_heads; a.num_kv_heads = p->num_kv_heads;
+  a.block_size = p->block_size; a.max_blocks_per_seq = p->max_blocks_per_seq; a.num_blocks = p->num_blocks;
+  a.centroids = p->centroids; a.part_acc = part_acc; a.part_ml = part_ml;
+  const int TT = 64 / G;
+  dim3 grid((p->num_tokens + TT - 1) / TT + p->num_seqs, p->num_kv_heads);
+  cudaError_t e = cudaSuccess;
+#define AKV_PF(GG)                                                                                                  \
+  e = cudaFuncSetAttribute(tq_prefill_attn_kernel<GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);         \
+  if (e == cudaSuccess) tq_prefill_attn_kernel<GG><<<grid, PF_THREADS, PF_SMEM, st>>>(a);
+  if (G == 1) { AKV_PF(1) } else if (G == 2) { AKV_PF(2) } else if (G == 4) { AKV_PF(4) } else { AKV_PF(8) }
+#undef AKV_PF
+  if (e != cudaSuccess) return fail((int)e, "prefill attention: smem attribute: %s", cudaGetErrorString(e));
+  if (int rc = check_launch("tq_prefill_attn_kernel")) return rc;
+  MergeArgs mg{};
+  mg.acc = part_acc; mg.acc_row = 128; mg.acc_part = 128;
+  mg.ml = part_ml; mg.ml_row = 2; mg.ml_part = 2;
+  mg.np = 1;
+  mg.num_q_heads = p->num_q_heads;
+  mg.D = 128;
+  mg.mode = MERGE_ROTATE;
+  mg.rot = p->rotation;
+  mg.out = p->out; mg.out_dtype = p->out_dtype; mg.out_ss = p->out_stride_tok; mg.out_sh = p->out_stride_head;
+  return launch_merge(mg, rows, st);
+}
 
 AKV_EXPORT size_t akv_tq_paged_attn_static_scratch_bytes(void) { return AKV_STATIC_SCRATCH_BYTES; }
 

@@ -44,6 +44,7 @@ class TQPagedAttention:
         self.packed_dim = tq._packed_dim
         self.num_query_heads = num_query_heads
         self._workspace: Optional[torch.Tensor] = None
+        self._prefill_ws: Optional[torch.Tensor] = None
         self._params = None
         self._params_key = None
 
@@ -103,6 +104,65 @@ class TQPagedAttention:
             self._params_key = None
         self._workspace = ws
         return ws
+
+    def prefill(self, query, k_packed, k_norms, v_packed, v_norms, block_tables, seq_lens, query_start_loc,
+                block_size: int = 16, num_kv_heads: Optional[int] = None, out: Optional[torch.Tensor] = None,
+                scale: Optional[float] = None) -> Optional[torch.Tensor]:
+        """Chunked-prefill attention: ``query`` [tokens, query_heads, head_dim] holds the last
+        ``query_start_loc[s+1] - query_start_loc[s]`` tokens of every sequence s; token i of a sequence attends
+        causally over the cached tokens up to its own position (``seq_lens`` counts the chunk's tokens, whose K/V
+        are already in the cache).  The query tokens of a sequence share one pass over its packed blocks
+        (``akv_tq_prefill_attn``); the reference decompresses the blocks and calls vLLM's unified attention
+        (``vllm/backend.py:1093-1244``).  Returns None when the kernel is not built for the shapes (the caller
+        then attends row by row with ``forward``)."""
+        if num_kv_heads is None:
+            num_kv_heads = k_packed.shape[2]
+        dev = _lib.require_cuda(query, k_packed, k_norms, v_packed, v_norms, block_tables, seq_lens, query_start_loc)
+        n_tok, num_q_heads, head_dim = query.shape
+        G = num_q_heads // num_kv_heads
+        aligned = all((t.data_ptr() | t.stride(0) | t.stride(1) | t.stride(2)) % 16 == 0 for t in (k_packed, v_packed))
+        if (self.bits != 4 or head_dim != 128 or G not in (1, 2, 4, 8) or block_size % 16 or not aligned
+                or k_norms.dtype != torch.float32 or v_norms.dtype != torch.float32):
+            return None
+        assert num_q_heads == self.num_query_heads and k_packed.shape[1] == block_size
+        num_seqs = query_start_loc.numel() - 1
+        if block_tables.dim() != 2 or block_tables.shape[0] < num_seqs or seq_lens.numel() < num_seqs:
+            raise ValueError(f"block_tables {tuple(block_tables.shape)} / seq_lens {tuple(seq_lens.shape)} do not cover "
+                             f"{num_seqs} sequences")
+        if query.dtype not in _lib._FLOAT_CODES:
+            query = query.float()
+        if query.stride(-1) != 1:
+            query = query.contiguous()
+        if block_tables.stride(-1) != 1:
+            block_tables = block_tables.contiguous()
+        seq_lens, query_start_loc = seq_lens.contiguous(), query_start_loc.contiguous()
+        if out is None:
+            out = torch.empty(n_tok, num_q_heads, head_dim, dtype=query.dtype, device=dev)
+        L = _lib.lib()
+        nbytes = L.akv_tq_prefill_attn_workspace_bytes(n_tok, num_q_heads)
+        if self._prefill_ws is None or self._prefill_ws.numel() < nbytes or self._prefill_ws.device != dev:
+            self._prefill_ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=dev)
+        p = _lib.TQPrefillParams()
+        p.query, p.q_dtype, p.q_stride_tok, p.q_stride_head = query.data_ptr(), _lib.float_code(query), query.stride(0), query.stride(1)
+        p.k_packed, p.kp_stride_blk, p.kp_stride_pos, p.kp_stride_head = k_packed.data_ptr(), k_packed.stride(0), k_packed.stride(1), k_packed.stride(2)
+        p.k_norms, p.kn_stride_blk, p.kn_stride_pos, p.kn_stride_head = k_norms.data_ptr(), k_norms.stride(0), k_norms.stride(1), k_norms.stride(2)
+        p.v_packed, p.vp_stride_blk, p.vp_stride_pos, p.vp_stride_head = v_packed.data_ptr(), v_packed.stride(0), v_packed.stride(1), v_packed.stride(2)
+        p.v_norms, p.vn_stride_blk, p.vn_stride_pos, p.vn_stride_head = v_norms.data_ptr(), v_norms.stride(0), v_norms.stride(1), v_norms.stride(2)
+        p.block_tables, p.bt_dtype, p.bt_stride_seq = block_tables.data_ptr(), _lib.index_code(block_tables), block_tables.stride(0)
+        p.seq_lens, p.sl_dtype = seq_lens.data_ptr(), _lib.index_code(seq_lens)
+        p.query_start_loc, p.qs_dtype = query_start_loc.data_ptr(), _lib.index_code(query_start_loc)
+        p.num_seqs, p.num_tokens, p.num_q_heads, p.num_kv_heads = num_seqs, n_tok, num_q_heads, num_kv_heads
+        p.head_dim, p.block_size, p.max_blocks_per_seq, p.num_blocks = head_dim, block_size, block_tables.shape[1], k_packed.shape[0]
+        p.bits = self.bits
+        p.rotation, p.rotation_t, p.centroids = self.rotation.data_ptr(), self.rotation_T.data_ptr(), self.centroids.data_ptr()
+        p.scale = self.scale if scale is None else float(scale)
+        p.out, p.out_dtype, p.out_stride_tok, p.out_stride_head = out.data_ptr(), _lib.float_code(out), out.stride(0), out.stride(1)
+        p.workspace, p.workspace_bytes = self._prefill_ws.data_ptr(), self._prefill_ws.numel()
+        p.stream = _lib.stream_ptr(dev)
+        with torch.cuda.device(dev):
+            rc = L.akv_tq_prefill_attn(ctypes.byref(p))
+        _lib.check(rc, "akv_tq_prefill_attn")
+        return out
 
     def forward(
         self,

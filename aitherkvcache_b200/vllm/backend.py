@@ -166,6 +166,22 @@ class TurboQuantImplBase:
         attn.forward(q, kc, kn, vc, vn, block_table, context_lens, block_size=bs, num_kv_heads=self.num_kv_heads,
                      out=out, scale=self.scale)
 
+    def _prefill(self, layer, q, out, kv_cache, md) -> bool:
+        """Prefill chunks and mixed batches through the chunked-prefill kernel (the query tokens of a sequence share
+        one pass over its packed blocks); False when that kernel is not built for the layout (3- / 2-bit codes,
+        68-byte rows), in which case every token becomes a row of the decode kernels."""
+        pd, bs = self.packed_dim, kv_cache.shape[2]
+        key_ = (self.head_size, self.tq_codec, self.tq_bits, self.num_heads, str(kv_cache.device))
+        attn = _LayerState.attention.get(key_)
+        if attn is None:
+            from ..fused_attention import TQPagedAttention
+            attn = TQPagedAttention(_quantizer(self.head_size, self.tq_bits, kv_cache.device), self.num_heads)
+            _LayerState.attention[key_] = attn
+        kn, vn = self._norms(getattr(layer, "layer_name", "layer"), kv_cache)
+        res = attn.prefill(q, kv_cache[:, 0, :, :, :pd], kn, kv_cache[:, 1, :, :, :pd], vn, md.block_table, md.seq_lens,
+                           md.query_start_loc, block_size=bs, num_kv_heads=self.num_kv_heads, out=out, scale=self.scale)
+        return res is not None
+
     def forward(self, layer, query, key, value, kv_cache, attn_metadata, output=None, output_scale=None,
                 output_block_scale=None):
         if output is None:
@@ -177,6 +193,8 @@ class TurboQuantImplBase:
         out = output[:n].view(n, self.num_heads, self.head_size)
         if attn_metadata.max_query_len == 1:      # one token per sequence: rows are the sequences
             self._attend(layer, q, out, kv_cache, attn_metadata.block_table, attn_metadata.seq_lens)
+            return output
+        if self.tq_codec == "uniform" and self._prefill(layer, q, out, kv_cache, attn_metadata):
             return output
         bt, ctx = token_rows(attn_metadata.query_start_loc, attn_metadata.seq_lens, attn_metadata.block_table, n)
         # the split-K workspace grows with the number of rows of a call: a chunk goes through in slices

@@ -145,6 +145,40 @@ size_t akv_tq_paged_attn_workspace_bytes(int num_seqs, int num_q_heads, int num_
                                          int max_blocks_per_seq, int blocks_per_split);
 int akv_tq_paged_attn(const akv_tq_attn_params* params);
 
+/* Chunked-prefill attention over the packed cache: replaces the prefill body of the reference's backend,
+ * which decompresses every active block to bf16 and calls vLLM's unified attention
+ * (vllm/backend.py:1093-1244, vllm/hooks.py:726-850).  Query token i of sequence s (rows
+ * query_start_loc[s] .. query_start_loc[s+1]-1 of `query`, the last tokens of the sequence) attends causally
+ * over the first seq_lens[s] - (query_len_s - 1 - i) cached tokens; the chunk's own K/V must already be in the
+ * cache.  The query tokens of a sequence share one pass over its blocks.
+ *   query [num_tokens, num_q_heads, 128]; caches, block tables as for akv_tq_paged_attn (4-bit codes);
+ *   seq_lens [num_seqs], query_start_loc [num_seqs + 1] int32 (dtype 0) or int64 (1);
+ *   out [num_tokens, num_q_heads, 128]; rows beyond query_start_loc[num_seqs] come out as zeros.
+ * Built for head_dim 128, bits 4, 1 / 2 / 4 / 8 query heads per KV head, block_size % 16 == 0 and code rows that
+ * are readable in 16-byte pieces; anything else returns AKV_ERR_UNSUPPORTED before any launch (attend row by
+ * row with akv_tq_paged_attn then). */
+typedef struct akv_tq_prefill_params {
+  const void* query; int q_dtype; int64_t q_stride_tok, q_stride_head;
+  const uint8_t* k_packed; int64_t kp_stride_blk, kp_stride_pos, kp_stride_head;
+  const float* k_norms; int64_t kn_stride_blk, kn_stride_pos, kn_stride_head;
+  const uint8_t* v_packed; int64_t vp_stride_blk, vp_stride_pos, vp_stride_head;
+  const float* v_norms; int64_t vn_stride_blk, vn_stride_pos, vn_stride_head;
+  const void* block_tables; int bt_dtype; int64_t bt_stride_seq;
+  const void* seq_lens; int sl_dtype;
+  const void* query_start_loc; int qs_dtype;
+  int num_seqs, num_tokens, num_q_heads, num_kv_heads, head_dim, block_size, max_blocks_per_seq;
+  int64_t num_blocks;
+  int bits;
+  const float* rotation; const float* rotation_t; const float* centroids;
+  float scale;
+  void* out; int out_dtype; int64_t out_stride_tok, out_stride_head;
+  void* workspace; size_t workspace_bytes;   /* akv_tq_prefill_attn_workspace_bytes(num_tokens, num_q_heads) */
+  void* stream;
+} akv_tq_prefill_params;
+
+size_t akv_tq_prefill_attn_workspace_bytes(int num_tokens, int num_q_heads);
+int akv_tq_prefill_attn(const akv_tq_prefill_params* params);
+
 /* One decode step of the serving path in a single call: encode the new tokens'
  * key and value ([num_tokens, num_kv_heads, head_dim], one dtype) into the packed
  * cache named by attn.k_packed / k_norms / v_packed / v_norms (akv_tq_kv_update

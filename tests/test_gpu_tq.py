@@ -659,3 +659,48 @@ def test_device_status_is_clean_and_reports_a_wait_that_gave_up():
     y3 = tq.decode(packed, norms)
     assert torch.equal(p3, packed) and torch.equal(n3, norms) and torch.equal(y3, y)
     assert not any(_lib.device_status().values())
+
+
+@pytest.mark.parametrize("H,QH,bs", ((8, 32, 16), (2, 16, 32), (4, 4, 16), (2, 4, 16)))
+def test_chunked_prefill_kernel_equals_row_by_row_attention(H, QH, bs):
+    """akv_tq_prefill_attn (query tokens of a sequence share one pass over its packed blocks) against the decode
+    kernels run with one row per query token and its causal context length, and against the oracle on one row."""
+    g = load_golden("tq_d128_b4.npz")
+    tq = _tq(128, 4, g)
+    attn = _attn(tq, QH)
+    gen = torch.Generator().manual_seed(900 + H + QH + bs)
+    # (tokens already cached before the chunk, chunk length) per sequence
+    seqs = [(0, 37), (300, 1), (129, 64), (511, 130), (5, 16)]
+    lens = [p + q for p, q in seqs]
+    nblk = [(n + bs - 1) // bs for n in lens]
+    total = sum(nblk) + 2
+    perm = torch.randperm(total, generator=gen)
+    bt = torch.zeros(len(seqs), max(nblk) + 1, dtype=torch.int32)
+    o = 0
+    for s, n in enumerate(nblk):
+        bt[s, :n] = perm[o:o + n].to(torch.int32)
+        o += n
+    k = torch.randn(total, bs, H, 128, generator=gen).half()
+    v = torch.randn(total, bs, H, 128, generator=gen).half()
+    kp, kn = tq.encode(k.cuda())
+    vp, vn = tq.encode(v.cuda())
+    nq = sum(q for _, q in seqs)
+    qsl = torch.tensor([0] + list(np.cumsum([q for _, q in seqs])), dtype=torch.int32)
+    query = torch.randn(nq + 3, QH, 128, generator=gen).half().cuda()          # three padding rows at the end
+    out = torch.full((nq + 3, QH, 128), 7.0, dtype=torch.float16, device="cuda")
+    res = attn.prefill(query, kp, kn, vp, vn, bt.cuda(), torch.tensor(lens, dtype=torch.int32).cuda(), qsl.cuda(),
+                       block_size=bs, num_kv_heads=H, out=out)
+    assert res is out
+    assert (out[nq:] == 0).all()
+    # one row per query token
+    rows_bt = torch.cat([bt[s:s + 1].expand(q, -1) for s, (_, q) in enumerate(seqs)])
+    rows_ctx = torch.cat([torch.arange(p + 1, p + q + 1) for p, q in seqs]).to(torch.int32)
+    ref = attn.forward(query[:nq], kp, kn, vp, vn, rows_bt.contiguous().cuda(), rows_ctx.cuda(), block_size=bs, num_kv_heads=H)
+    assert (out[:nq].float() - ref.float()).abs().max().item() < 2e-3
+    # the last token of the longest chunk against the oracle
+    s = 3
+    row = int(qsl[s + 1]) - 1
+    want = otq.paged_attention_decode_sdpa(query[row:row + 1].cpu().numpy(), kp.cpu().numpy(), kn.cpu().numpy(),
+                                           vp.cpu().numpy(), vn.cpu().numpy(), bt[s:s + 1].numpy(), np.asarray([lens[s]]),
+                                           g["rotation"], g["centroids"], 4, 1.0 / math.sqrt(128), bs)
+    assert np.abs(out[row].float().cpu().numpy() - want[0]).max() < 2e-3
