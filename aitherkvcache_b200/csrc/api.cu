@@ -48,7 +48,8 @@ AKV_EXPORT int akv_device_arch(void) {
 //          gave up and the CTA left its tile unwritten, 2 = it also kept its tensor-memory columns
 //   out[2] packed-cache attention, out[3] hybrid attention: 1 = a fixed-address kernel found its shared
 //          window taken and returned without writing partials; out[2] = 2: a bounded wait for a bulk copy
-//          ran out in a packed-cache attention kernel or in the TriAttention decode kernel
+//          ran out in a packed-cache attention kernel, in the TriAttention decode kernel or in the tensor-core
+//          prefill kernel
 //   out[4] akv_p2p_lse_merge: 1 = the bounded wait for the peers' partials ran out (a peer is late or gone)
 // reset != 0 clears the words after reading them.
 AKV_EXPORT int akv_device_status(int* out, int reset) {
@@ -61,16 +62,21 @@ AKV_EXPORT int akv_device_status(int* out, int reset) {
   int tri = 0;
   if (int rc = akv::tri_status(&tri, reset)) return rc;
   if (tri > out[2]) out[2] = tri;
+  int pre = 0;
+  if (int rc = akv::prefill_tc_status(&pre, reset)) return rc;
+  if (pre != 0 && out[2] < 2) out[2] = 2;
   if (int rc = akv::hybrid_window_status(out + 3, reset)) return rc;
   return akv::p2p_status(out + 4, reset);
 }
 
 // Test hook for the bounded waits of the tensor-core codec kernels: CTA 0 of the next launches of the
-// encoder (which = 0) or decoder (which = 1) issues neither the MMAs nor the commit of its tile number
+// encoder (which = 0), decoder (which = 1) or prefill attention kernel (which = 2; CTA (0, 0), score MMAs of key tile
+// `tile`) issues neither the MMAs nor the commit of its tile number
 // `tile`, so the wait on that tile's barrier runs out with no tensor work in flight, the CTA leaves
 // through its give-up path and akv_device_status reports 1.  tile < 0 switches the hook off (the default).
 AKV_EXPORT int akv_debug_tc_withhold(int which, int tile) {
   if (which == 0) return akv::tc_encode_withhold(tile);
   if (which == 1) return akv::tc_decode_withhold(tile);
-  return akv::fail(AKV_ERR_ARG, "akv_debug_tc_withhold: which must be 0 (encode) or 1 (decode)");
+  if (which == 2) return akv::prefill_tc_withhold(tile);
+  return akv::fail(AKV_ERR_ARG, "akv_debug_tc_withhold: which must be 0 (encode), 1 (decode) or 2 (prefill attention)");
 }

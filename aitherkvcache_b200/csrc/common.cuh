@@ -89,6 +89,8 @@ int tc_encode_status(int* host_out, int reset);
 int tc_decode_status(int* host_out, int reset);
 int attn_window_status(int* host_out, int reset);
 int tri_status(int* host_out, int reset);
+int prefill_tc_status(int* host_out, int reset);
+int prefill_tc_withhold(int tile);
 int hybrid_window_status(int* host_out, int reset);
 int tc_encode_withhold(int tile);
 int tc_decode_withhold(int tile);

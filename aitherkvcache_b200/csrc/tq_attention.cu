@@ -2783,6 +2783,16 @@ AKV_EXPORT int akv_tq_prefill_attn(const akv_tq_prefill_params* p) {
   a.num_seqs = p->num_seqs; a.n_tokens = p->num_tokens; a.num_q_heads = p->num_q_heads; a.num_kv_heads = p->num_kv_heads;
   a.block_size = p->block_size; a.max_blocks_per_seq = p->max_blocks_per_seq; a.num_blocks = p->num_blocks;
   a.centroids = p->centroids; a.part_acc = part_acc; a.part_ml = part_ml;
+  // tcgen05 kernel (128 rows per CTA) when its row tiles would be at least half full - chunks of prefill tokens, not a
+  // batch of single decode tokens (the host cannot see query_start_loc: a sequence adds at most one ragged tile);
+  // AKV_PREFILL_TC=0 / 1 forces one or the other
+  static const char* tc_env = getenv("AKV_PREFILL_TC");
+  const int64_t tc_rows = (int64_t)p->num_tokens * G;
+  const int64_t tc_tiles = (tc_rows + 127) / 128 + p->num_seqs - 1;
+  const bool use_tc = tc_env ? tc_env[0] == '1' : tc_rows >= 64 * tc_tiles;
+  if (use_tc) {
+    if (int rc = launch_prefill_tc(a, G, st)) return rc;
+  } else {
   const int TT = 64 / G;
   dim3 grid((p->num_tokens + TT - 1) / TT + p->num_seqs, p->num_kv_heads);
   cudaError_t e = cudaSuccess;
@@ -2793,6 +2803,7 @@ AKV_EXPORT int akv_tq_prefill_attn(const akv_tq_prefill_params* p) {
 #undef AKV_PF
   if (e != cudaSuccess) return fail((int)e, "prefill attention: smem attribute: %s", cudaGetErrorString(e));
   if (int rc = check_launch("tq_prefill_attn_kernel")) return rc;
+  }
   MergeArgs mg{};
   mg.acc = part_acc; mg.acc_row = 128; mg.acc_part = 128;
   mg.ml = part_ml; mg.ml_row = 2; mg.ml_part = 2;

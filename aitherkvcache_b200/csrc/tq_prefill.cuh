@@ -17,23 +17,9 @@
 // the un-normalised result (m, l, acc) of every row goes to the LSE merge kernel, which divides and rotates back.
 #pragma once
 
-namespace akv {
+#include "tq_prefill_args.cuh"
 
-struct PrefillArgs {
-  const float* qrot;                   // [n_tokens * num_q_heads][128], scale * log2(e) folded in
-  const uint8_t* k_packed; int64_t kp_sb, kp_sp, kp_sh;
-  const float* k_norms; int64_t kn_sb, kn_sp, kn_sh;
-  const uint8_t* v_packed; int64_t vp_sb, vp_sp, vp_sh;
-  const float* v_norms; int64_t vn_sb, vn_sp, vn_sh;
-  const void* block_tables; int bt_dtype; int64_t bt_stride;
-  const void* seq_lens; int sl_dtype;              // [num_seqs] tokens of each sequence, the chunk's included
-  const void* query_start_loc; int qs_dtype;       // [num_seqs + 1] first query row of each sequence
-  int num_seqs, n_tokens, num_q_heads, num_kv_heads, block_size, max_blocks_per_seq;
-  int64_t num_blocks;
-  const float* centroids;
-  float* part_acc;                     // [n_tokens * num_q_heads][128]
-  float* part_ml;                      // [n_tokens * num_q_heads][2]
-};
+namespace akv {
 
 constexpr int PF_THREADS = 128;
 constexpr int PF_LUT_BYTES = 256 * 128;                       // byte -> half2, one copy per lane

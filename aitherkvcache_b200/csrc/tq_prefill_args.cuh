@@ -1,0 +1,31 @@
+// Arguments shared by the chunked-prefill attention kernels (tq_prefill.cuh: mma.sync, tq_prefill_tc.cu: tcgen05).
+#pragma once
+
+#include "common.cuh"
+
+namespace akv {
+
+struct PrefillArgs {
+  const float* qrot;                   // [n_tokens * num_q_heads][128], scale * log2(e) folded in
+  const uint8_t* k_packed; int64_t kp_sb, kp_sp, kp_sh;
+  const float* k_norms; int64_t kn_sb, kn_sp, kn_sh;
+  const uint8_t* v_packed; int64_t vp_sb, vp_sp, vp_sh;
+  const float* v_norms; int64_t vn_sb, vn_sp, vn_sh;
+  const void* block_tables; int bt_dtype; int64_t bt_stride;
+  const void* seq_lens; int sl_dtype;              // [num_seqs] tokens of each sequence, the chunk's included
+  const void* query_start_loc; int qs_dtype;       // [num_seqs + 1] first query row of each sequence
+  int num_seqs, n_tokens, num_q_heads, num_kv_heads, block_size, max_blocks_per_seq;
+  int64_t num_blocks;
+  const float* centroids;
+  float* part_acc;                     // [n_tokens * num_q_heads][128]
+  float* part_ml;                      // [n_tokens * num_q_heads][2]
+};
+
+// tcgen05 kernel (tq_prefill_tc.cu): one CTA per 128 (token, query head) rows and KV head.  Returns AKV_OK after
+// the launch; AKV_ERR_UNSUPPORTED is never returned - the caller checks the shape (4-bit codes, head_dim 128,
+// G in {1, 2, 4, 8}, block_size % 16 == 0, 16-byte readable caches) before calling.
+int launch_prefill_tc(const PrefillArgs& a, int G, cudaStream_t st);
+int prefill_tc_status(int* host_out, int reset);
+int prefill_tc_withhold(int tile);
+
+}  // namespace akv

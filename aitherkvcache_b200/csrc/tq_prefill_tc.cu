@@ -1,0 +1,524 @@
+// Chunked-prefill attention over the packed 4-bit cache on the 5th-generation tensor cores (tcgen05 / TMEM).
+//
+// Same operation as tq_prefill_attn_kernel (tq_prefill.cuh); the reference decompresses every active block to
+// bf16 and calls vLLM's unified attention (vllm/backend.py:1093-1244, vllm/hooks.py:726-850).  A CTA owns 128
+// (token, query head) rows of one sequence and one KV head - 128 / G consecutive query tokens, G = query heads per
+// KV head - and walks over the causal key range in tiles of 64 keys.  Both products of a tile are tcgen05 MMAs with
+// float32 accumulators in tensor memory:
+//   S[128 rows][64 keys]  = Q K^T   A = the rotated queries (fp16, shared memory, written once),
+//                                   B = the tile's keys, codes -> fp16 centroids times the key norm;
+//   O[128 rows][144]      += P V    A = the probabilities (fp16, shared memory), B = the tile's values transposed,
+//                                   codes -> fp16 centroids times the value norm, plus a row of ones: column 128 of
+//                                   O is the row sum of the probabilities as the tensor cores saw them.
+// (Norms are folded in as fp16 factors: a key or value norm below 1e-2 loses bits to fp16's subnormal range.)
+// All operands are K-major in the 128-byte-swizzled layout of umma.cuh.  Thirteen warps, no CTA-wide barrier in the loop:
+//   warps 0-3   softmax: thread = row.  S out of tensor memory (tcgen05.ld), causal limit, running reference maximum
+//               (the accumulator O is rescaled only when the maximum grows by more than 2^8: tcgen05.ld / st of the
+//               thread's own lane), exp2, fp16 probabilities into the P operand.
+//   warps 4-11  decode: packed bytes and norms from global memory two tiles ahead in registers (block-table entries
+//               three tiles ahead), byte -> half2 by a per-lane lookup table; a thread writes 16-byte pieces of the K
+//               operand (32 dims of one key) and of the transposed V operand (8 keys of 4 dims).
+//   warp 12     one lane issues the MMAs: S of tile j+1 before P V of tile j, so the tensor cores compute the next
+//               scores while the softmax warps work on the current ones.
+// Hand-overs are mbarriers (tile j uses stage j % 2 of every operand and accumulator S):
+//   k_full / v_full  8 decode-warp arrivals: the operand stage is written          -> MMA warp
+//   s_full           tcgen05.commit after S: scores ready                          -> softmax warps; K stage free -> decode warps
+//   s_free           4 softmax-warp arrivals: S is in registers                    -> MMA warp may overwrite it
+//   p_full           4 arrivals: P written, O rescaled if need be                  -> MMA warp
+//   pv_done          tcgen05.commit after P V                                      -> V stage and P buffer free, O readable
+// Every wait is bounded; a wait that gives up sets g_prefill_tc_status and a shared flag that ends all loops; the
+// CTA then leaves after releasing its tensor memory, its rows unwritten (they come out as zeros).
+#include "tq_prefill_args.cuh"
+#include "umma.cuh"
+#include <math_constants.h>
+
+namespace akv {
+namespace {
+
+__device__ int g_prefill_tc_status;          // 1: a bounded wait gave up, 2: tensor-memory columns were kept
+__device__ int g_prefill_tc_withhold = -1;   // test hook: CTA (0, 0) issues neither the score MMAs nor the commit of this tile
+
+constexpr int PT_KT = 64;                            // keys per tile
+constexpr int PT_THREADS = 13 * 32;
+constexpr int PT_STAGE = 16384;                      // one operand stage: 64 x 128 or 128 x 64 fp16
+constexpr int PT_Q = 0;                              // A of S: [128 rows][128 dims], two halves of 64 dims
+constexpr int PT_K = PT_Q + 32768;                   // B of S: 2 stages x [64 keys][128 dims], two halves of 64 rows
+constexpr int PT_VSTAGE = 144 * 128;                 // value stage: 128 dims + the row of ones (+ 15 zero rows) x 64 keys
+constexpr int PT_V = PT_K + 2 * PT_STAGE;            // B of PV: 2 stages x [144 rows][64 keys]
+constexpr int PT_P = PT_V + 2 * PT_VSTAGE;           // A of PV: 2 buffers x [128 rows][64 keys]
+constexpr int PT_LUT = PT_P + 2 * PT_STAGE;          // byte -> half2, one copy per lane (256 x 128 B)
+constexpr int PT_BAR = PT_LUT + 32768;               // mbarriers, tensor-memory slot, failed flag
+constexpr int PT_SMEM = PT_BAR + 256 + 1024;         // + slack for the 1024-byte alignment
+constexpr uint32_t B_KFULL = 0, B_VFULL = 16, B_SFULL = 32, B_SFREE = 48, B_PFULL = 64, B_PVDONE = 80,
+                   B_DRAIN = 128, B_TMEM = 136, B_FAILED = 140;
+constexpr int PT_TMEM_COLS = 512;                    // S stages at columns 0 and 64, O at 128..271 (column 256 = row sum)
+constexpr float PT_RESCALE = 8.0f;                   // log2 units the row maximum may grow before O is rescaled
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      :: "r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+         "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+         "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+         "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+
+__device__ __forceinline__ void pt_sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" :: "r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint32_t pt_pack_half2(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ float pt_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void pt_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory");
+}
+
+template <int G>
+__global__ void __launch_bounds__(PT_THREADS, 1)
+tq_prefill_tc_kernel(PrefillArgs a) {
+  static_assert(G == 1 || G == 2 || G == 4 || G == 8, "query heads per KV head");
+  constexpr int TT = 128 / G;           // query tokens of a CTA
+  extern __shared__ uint8_t pt_smem_raw[];
+  const uint32_t raw_s = smem_u32(pt_smem_raw);
+  const uint32_t base_s = (raw_s + 1023u) & ~1023u;
+  uint8_t* base = pt_smem_raw + (base_s - raw_s);
+  const uint32_t bar_s = base_s + PT_BAR, failed_s = bar_s + B_FAILED;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int kvh = blockIdx.y;
+
+  // ---- which sequence and which of its query tiles (uniform for the CTA) ----
+  int tile = blockIdx.x, s = 0, q0 = 0, qlen = 0;
+  bool found = false;
+  for (s = 0; s < a.num_seqs; ++s) {
+    q0 = (int)load_index(a.query_start_loc, a.qs_dtype, s);
+    const int q1 = (int)load_index(a.query_start_loc, a.qs_dtype, s + 1);
+    qlen = q1 - q0;
+    if (qlen < 0) qlen = 0;
+    const int tiles = (qlen + TT - 1) / TT;
+    if (tile < tiles) { found = true; break; }
+    tile -= tiles;
+  }
+  if (!found) return;
+  const int64_t max_ctx = (int64_t)a.max_blocks_per_seq * a.block_size;
+  const int seq_len = (int)load_ctx(a.seq_lens, a.sl_dtype, s, max_ctx);
+  int past = seq_len - qlen;            // keys before the chunk
+  if (past < 0) past = 0;
+  const int tok_lo = tile * TT;
+  const int tok_hi = (tok_lo + TT < qlen) ? tok_lo + TT : qlen;
+  int kend = past + tok_hi;             // keys any row of this CTA may see
+  if (kend > seq_len) kend = seq_len;
+  const int n_ktiles = (kend + PT_KT - 1) / PT_KT;
+  if (n_ktiles <= 0) return;            // nothing to attend to: the rows keep l = 0
+
+  // ---------------- one-time setup ----------------
+  if (tid == 0) {
+    for (int i = 0; i < 2; ++i) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 8;" :: "r"(bar_s + B_KFULL + 8 * i));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 8;" :: "r"(bar_s + B_VFULL + 8 * i));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar_s + B_SFULL + 8 * i));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;" :: "r"(bar_s + B_SFREE + 8 * i));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;" :: "r"(bar_s + B_PFULL + 8 * i));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar_s + B_PVDONE + 8 * i));
+    }
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar_s + B_DRAIN));
+    asm volatile("st.shared.u32 [%0], %1;" :: "r"(failed_s), "r"(0u) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(bar_s + B_TMEM), "n"(PT_TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  // lookup table: byte -> half2(centroid[high nibble], centroid[low nibble]) = coordinates 2b, 2b+1; one copy per lane
+  {
+    __shared__ float s_cent[16];
+    if (tid < 16) s_cent[tid] = a.centroids[tid];
+    __syncthreads();
+    for (int i = tid; i < 256 * 8; i += PT_THREADS) {
+      const int e = i >> 3, q4 = i & 7;
+      const uint32_t v = pt_pack_half2(s_cent[e >> 4], s_cent[e & 15]);
+      *reinterpret_cast<uint4*>(base + PT_LUT + e * 128 + q4 * 16) = make_uint4(v, v, v, v);
+    }
+  }
+  // A operand of S: the CTA's query rows, row r = (token tok_lo + r / G, head r % G), zeros for rows without a token
+  for (int e = tid; e < 128 * 16; e += PT_THREADS) {
+    const int r = e >> 4, c = e & 15;
+    const int tok = tok_lo + r / G;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (tok < qlen && q0 + tok < a.n_tokens) {
+      const float4* src = reinterpret_cast<const float4*>(a.qrot + ((int64_t)(q0 + tok) * a.num_q_heads + kvh * G + r % G) * 128 + 8 * c);
+      const float4 f0 = src[0], f1 = src[1];
+      v = make_uint4(pt_pack_half2(f0.x, f0.y), pt_pack_half2(f0.z, f0.w), pt_pack_half2(f1.x, f1.y), pt_pack_half2(f1.z, f1.w));
+    }
+    *reinterpret_cast<uint4*>(base + PT_Q + (c >> 3) * 16384 + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+  }
+  // rows 128..143 of both value stages: a row of ones (output column 128 becomes the row sum of P) and zero rows
+  for (int e = tid; e < 2 * 16 * 8; e += PT_THREADS) {
+    const int stg = e >> 7, r = (e >> 3) & 15, c = e & 7;
+    const uint32_t v = r == 0 ? 0x3C003C00u : 0u;
+    *reinterpret_cast<uint4*>(base + PT_V + stg * PT_VSTAGE + (128 + r) * 128 + c * 16) = make_uint4(v, v, v, v);
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = lds_u32(bar_s + B_TMEM);
+  const uint32_t tmem_o = tmem_base + 128;                  // S stage s at column 64 s, O at columns 128..255
+
+  // Bounded wait.  Fast path: one try_wait (the hardware parks the thread for a while if the phase has not flipped).  Only
+  // a wait that comes back empty goes into the counted loop; once one wait of the CTA has run out, the others return
+  // at once.
+  auto wait = [&](uint32_t bar, uint32_t parity) -> bool {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) return true;
+    if (lds_u32(failed_s) != 0u) return false;
+    if (mbar_wait(bar, parity)) return true;
+    g_prefill_tc_status = 1;
+    asm volatile("st.shared.u32 [%0], %1;" :: "r"(failed_s), "r"(1u) : "memory");
+    return false;
+  };
+  auto wait_warp = [&](uint32_t bar, uint32_t parity) -> bool { return __all_sync(0xffffffffu, wait(bar, parity)); };
+  auto par2 = [](int j) -> uint32_t { return (uint32_t)((j >> 1) & 1); };      // phase parity of tile j on a two-stage barrier
+
+  if (warp == 12) {
+    // ================= MMA warp =================
+    if (lane == 0) {
+      // D = f32, A / B = f16, both K-major; N = 64 (scores) or 128 (values), M = 128
+      constexpr uint32_t IDESC_S = (1u << 4) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
+      constexpr uint32_t IDESC_O = (1u << 4) | ((144u >> 3) << 17) | ((128u >> 4) << 24);
+      const int withhold = (blockIdx.x | blockIdx.y) == 0 ? g_prefill_tc_withhold : -1;
+      auto issue_s = [&](int j) -> bool {
+        const uint32_t st = (uint32_t)(j & 1);
+        if (!wait(bar_s + B_KFULL + 8 * st, par2(j))) return false;
+        if (j >= 2 && !wait(bar_s + B_SFREE + 8 * st, par2(j - 2))) return false;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (j == withhold) return true;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_f16(tmem_base + st * 64, umma_desc(base_s + PT_Q + (uint32_t)((kk >> 2) * 16384 + (kk & 3) * 32)),
+                   umma_desc(base_s + PT_K + st * PT_STAGE + (uint32_t)((kk >> 2) * 8192 + (kk & 3) * 32)), IDESC_S,
+                   (uint32_t)(kk != 0));
+        umma_commit(bar_s + B_SFULL + 8 * st);
+        return true;
+      };
+      auto issue_pv = [&](int j) -> bool {
+        const uint32_t st = (uint32_t)(j & 1);
+        if (!wait(bar_s + B_PFULL + 8 * st, par2(j))) return false;
+        if (!wait(bar_s + B_VFULL + 8 * st, par2(j))) return false;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_f16(tmem_o, umma_desc(base_s + PT_P + st * PT_STAGE + (uint32_t)(kk * 32)),
+                   umma_desc(base_s + PT_V + st * PT_VSTAGE + (uint32_t)(kk * 32)), IDESC_O, (uint32_t)((j | kk) != 0));
+        umma_commit(bar_s + B_PVDONE + 8 * st);
+        return true;
+      };
+      if (issue_s(0)) {
+        for (int j = 0; j < n_ktiles; ++j) {
+          if (j + 1 < n_ktiles && !issue_s(j + 1)) break;
+          if (!issue_pv(j)) break;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp >= 4) {
+    // ================= decode warps =================
+    const int d = tid - 128;
+    const int kr = d >> 2, kc = d & 3;                          // K: 16 bytes (32 dims) of key kr
+    const int kg = d & 7, vbyte = 4 * (d >> 4) + 2 * ((d >> 3) & 1);     // V: bytes vbyte, vbyte + 1 of keys 8 kg .. 8 kg + 7
+    const uint32_t lut = base_s + PT_LUT + lane * 4;
+    const int n_table = a.max_blocks_per_seq, bs = a.block_size;
+    // Addressing without divisions or 64-bit products in the loop: (block index, position in block) of the thread's K key
+    // and of its first V key advance by one tile per step; a block-table entry is read two tiles ahead of its use.
+    // the entry comes back as loaded (nothing waits for it here); phys() turns it into a block number at its use
+    const bool bt64 = a.bt_dtype == AKV_I64;
+    const char* bt_row = reinterpret_cast<const char*>(a.block_tables) + (int64_t)s * a.bt_stride * (bt64 ? 8 : 4);
+    auto entry = [&](int blk) -> uint64_t {
+      if (blk >= n_table) blk = n_table - 1;
+      if (blk < 0) blk = 0;
+      if (n_table <= 0) return 0ull;
+      return bt64 ? (uint64_t)__ldg(reinterpret_cast<const long long*>(bt_row) + blk)
+                  : (uint64_t)(uint32_t)__ldg(reinterpret_cast<const int*>(bt_row) + blk);
+    };
+    auto phys = [&](uint64_t raw) -> int64_t {
+      const int64_t pb = bt64 ? (int64_t)raw : (int64_t)(int32_t)(uint32_t)raw;
+      return pb < 0 ? 0 : (pb >= a.num_blocks ? a.num_blocks - 1 : pb);
+    };
+    const int adv_blk = PT_KT / bs, adv_pos = PT_KT - adv_blk * bs;       // 64 keys = adv_blk blocks + adv_pos positions
+    auto advance = [&](int& blk, int& pos) {
+      blk += adv_blk;
+      pos += adv_pos;
+      if (pos >= bs) { pos -= bs; ++blk; }
+    };
+    const uint8_t* kbase = a.k_packed + (int64_t)kvh * a.kp_sh + kc * 16;
+    const float* knbase = a.k_norms + (int64_t)kvh * a.kn_sh;
+    const uint8_t* vbase = a.v_packed + (int64_t)kvh * a.vp_sh + vbyte;
+    const float* vnbase = a.v_norms + (int64_t)kvh * a.vn_sh;
+    const uint32_t kp_sp = (uint32_t)a.kp_sp, kn_sp = (uint32_t)a.kn_sp, vn_sp = (uint32_t)a.vn_sp;     // strides inside a block
+    const int64_t vp_sp = a.vp_sp;
+    // raw bytes and norms of three tiles: tile j is decoded out of set j % 3 while the loads of tiles j + 1 and j + 2 are
+    // in flight (a load from a cold block takes longer than one tile's work)
+    struct Raw { uint4 k; float kn; uint32_t v[8]; float vn[8]; };
+    Raw R0, R1, R2;
+    R0.k = R1.k = R2.k = make_uint4(0u, 0u, 0u, 0u);
+    R0.kn = R1.kn = R2.kn = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { R0.v[i] = R1.v[i] = R2.v[i] = 0u; R0.vn[i] = R1.vn[i] = R2.vn[i] = 0.f; }
+    auto load = [&](int j, uint64_t rawk, int posk, uint64_t rawv, int posv, Raw& R) {
+      uint4& k4 = R.k; float& knorm = R.kn; uint32_t (&v2)[8] = R.v; float (&vnorm)[8] = R.vn;
+      if (j >= n_ktiles) return;
+      const int64_t pbk = phys(rawk), pbv = phys(rawv);
+      k4 = __ldg(reinterpret_cast<const uint4*>(kbase + pbk * a.kp_sb + (uint32_t)posk * kp_sp));
+      knorm = __ldg(knbase + pbk * a.kn_sb + (uint32_t)posk * kn_sp);
+      const uint8_t* vp = vbase + pbv * a.vp_sb + (int64_t)posv * vp_sp;
+      const float* np = vnbase + pbv * a.vn_sb + (uint32_t)posv * vn_sp;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        v2[i] = (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(vp));
+        vnorm[i] = __ldg(np);
+        vp += vp_sp;
+        np += vn_sp;
+      }
+      if (j == n_ktiles - 1) {      // a key past the range carries any norm: its score is masked, its value row becomes zero
+        const int key8 = PT_KT * j + 8 * kg;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) vnorm[i] = key8 + i < kend ? vnorm[i] : 0.f;
+        if (PT_KT * j + kr >= kend) knorm = 0.f;
+      }
+    };
+    int blk_k = kr / bs, pos_k = kr - blk_k * bs, blk_v = (8 * kg) / bs, pos_v = 8 * kg - blk_v * bs;
+    load(0, entry(blk_k), pos_k, entry(blk_v), pos_v, R0);
+    advance(blk_k, pos_k);
+    advance(blk_v, pos_v);
+    load(1, entry(blk_k), pos_k, entry(blk_v), pos_v, R1);
+    advance(blk_k, pos_k);
+    advance(blk_v, pos_v);
+    uint64_t pbk_nx = entry(blk_k), pbv_nx = entry(blk_v);      // tile 2
+    int posk_nx = pos_k, posv_nx = pos_v;
+    auto tile_step = [&](int j, Raw& cur, Raw& tgt) -> bool {
+      const uint32_t st = (uint32_t)(j & 1);
+      const uint4 kw = cur.k;
+      const float kn = cur.kn;
+      const uint32_t (&vw)[8] = cur.v;
+      const float (&vn)[8] = cur.vn;
+      load(j + 2, pbk_nx, posk_nx, pbv_nx, posv_nx, tgt);
+      advance(blk_k, pos_k);
+      advance(blk_v, pos_v);
+      if (j + 3 < n_ktiles) { pbk_nx = entry(blk_k); pbv_nx = entry(blk_v); }       // tile j + 3
+      posk_nx = pos_k;
+      posv_nx = pos_v;
+      // ---- K operand of tile j: free once the scores of tile j-2 are complete ----
+      if (j >= 2 && !wait_warp(bar_s + B_SFULL + 8 * st, par2(j - 2))) return false;
+      {
+        // words 2, 3 first for the upper chunks: the eight threads of a quarter warp then store to eight different
+        // bank groups
+        const uint32_t hi = (uint32_t)(kc >> 1);
+        const __half2 knh = __float2half2_rn(kn);
+        const uint32_t ws[4] = {hi ? kw.z : kw.x, hi ? kw.w : kw.y, hi ? kw.x : kw.z, hi ? kw.y : kw.w};
+        const uint32_t row = base_s + PT_K + st * PT_STAGE + hi * 8192u + (uint32_t)kr * 128u;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint32_t h[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const uint32_t x = lds_u32(lut + (((ws[i] >> (8 * e)) & 0xffu) << 7));
+            const __half2 y = __hmul2(*reinterpret_cast<const __half2*>(&x), knh);
+            h[e] = *reinterpret_cast<const uint32_t*>(&y);
+          }
+          const uint32_t chunk = (uint32_t)(4 * (kc & 1)) + ((uint32_t)i ^ (hi << 1));
+          pt_sts128(row + ((chunk ^ (uint32_t)(kr & 7)) << 4), h[0], h[1], h[2], h[3]);
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) pt_arrive(bar_s + B_KFULL + 8 * st);
+      // ---- transposed V operand of tile j: free once P V of tile j-2 is complete ----
+      if (j >= 2 && !wait_warp(bar_s + B_PVDONE + 8 * st, par2(j - 2))) return false;
+      {
+        uint32_t e0[8], e1[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const __half2 nh = __float2half2_rn(vn[i]);
+          const uint32_t x0 = lds_u32(lut + ((vw[i] & 0xffu) << 7)), x1 = lds_u32(lut + (((vw[i] >> 8) & 0xffu) << 7));
+          const __half2 y0 = __hmul2(*reinterpret_cast<const __half2*>(&x0), nh), y1 = __hmul2(*reinterpret_cast<const __half2*>(&x1), nh);
+          e0[i] = *reinterpret_cast<const uint32_t*>(&y0);
+          e1[i] = *reinterpret_cast<const uint32_t*>(&y1);
+        }
+        const uint32_t vst = base_s + PT_V + st * PT_VSTAGE;
+        const int r0 = 2 * vbyte;            // dims 2 vbyte, + 1 (first byte), + 2, + 3 (second byte)
+        auto put = [&](int row, const uint32_t (&e)[8], uint32_t sel) {
+          pt_sts128(vst + (uint32_t)row * 128u + (((uint32_t)kg ^ (uint32_t)(row & 7)) << 4),
+                    __byte_perm(e[0], e[1], sel), __byte_perm(e[2], e[3], sel), __byte_perm(e[4], e[5], sel), __byte_perm(e[6], e[7], sel));
+        };
+        put(r0, e0, 0x5410u);
+        put(r0 + 1, e0, 0x7632u);
+        put(r0 + 2, e1, 0x5410u);
+        put(r0 + 3, e1, 0x7632u);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) pt_arrive(bar_s + B_VFULL + 8 * st);
+      return true;
+    };
+    for (int j = 0; j < n_ktiles; j += 3) {
+      if (!tile_step(j, R0, R2)) break;
+      if (j + 1 < n_ktiles && !tile_step(j + 1, R1, R0)) break;
+      if (j + 2 < n_ktiles && !tile_step(j + 2, R2, R1)) break;
+    }
+  } else {
+    // ================= softmax warps: thread = row =================
+    const int r = tid;
+    const int tok = tok_lo + r / G;
+    const bool live = tok < qlen && q0 + tok < a.n_tokens;
+    int lim = live ? past + tok + 1 : 0;          // keys the row may see
+    if (lim > seq_len) lim = seq_len;
+    const uint32_t t_lane = ((uint32_t)(warp * 32)) << 16;
+    float m_ref = -CUDART_INF_F;
+    bool ok = true;
+    for (int j = 0; j < n_ktiles && ok; ++j) {
+      const uint32_t st = (uint32_t)(j & 1);
+      if (!wait_warp(bar_s + B_SFULL + 8 * st, par2(j))) { ok = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      uint32_t v0[32], v1[32];
+      tmem_ld32(tmem_base + t_lane + st * 64, v0);
+      tmem_ld32(tmem_base + t_lane + st * 64 + 32, v1);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) pt_arrive(bar_s + B_SFREE + 8 * st);
+      // causal limit, maximum (the key norms are inside the K operand)
+      const int vis = lim - PT_KT * j;            // keys of this tile the row may see (<= 0: none, >= 64: all)
+      if (vis < PT_KT) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          v0[i] = i < vis ? v0[i] : 0xff800000u;
+          v1[i] = i + 32 < vis ? v1[i] : 0xff800000u;
+        }
+      }
+      float mx = -CUDART_INF_F;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(v0[i]), __uint_as_float(v1[i])));
+      // the reference maximum moves only when the row maximum has grown by more than PT_RESCALE; tcgen05.ld / st are
+      // warp-wide, so the rows of a warp rescale together (factor 1 for rows that keep their reference).  Column 128
+      // of O is the row sum and is rescaled with the rest.
+      const bool grow = mx > m_ref + PT_RESCALE;
+      if (__any_sync(0xffffffffu, grow)) {
+        const float alpha = grow ? pt_ex2(m_ref - mx) : 1.0f;      // m_ref = -inf: 0
+        if (grow) m_ref = mx;
+        if (j > 0) {
+          if (!wait_warp(bar_s + B_PVDONE + 8 * (uint32_t)((j - 1) & 1), par2(j - 1))) { ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+          for (int c = 0; c < 5; ++c) {
+            uint32_t o[32];
+            tmem_ld32(tmem_o + t_lane + 32 * c, o);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(tmem_o + t_lane + 32 * c, o);
+          }
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        }
+      }
+      const float ref = m_ref == -CUDART_INF_F ? 0.f : m_ref;
+      uint32_t ph[32];                            // probabilities as fp16 pairs: keys 2i, 2i + 1
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        ph[i] = pt_pack_half2(pt_ex2(__uint_as_float(v0[2 * i]) - ref), pt_ex2(__uint_as_float(v0[2 * i + 1]) - ref));
+        ph[16 + i] = pt_pack_half2(pt_ex2(__uint_as_float(v1[2 * i]) - ref), pt_ex2(__uint_as_float(v1[2 * i + 1]) - ref));
+      }
+      // P buffer of this stage: free once P V of tile j-2 is complete
+      if (j >= 2 && !wait_warp(bar_s + B_PVDONE + 8 * st, par2(j - 2))) { ok = false; break; }
+      const uint32_t prow = base_s + PT_P + st * PT_STAGE + (uint32_t)r * 128u;
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        pt_sts128(prow + (((uint32_t)c ^ (uint32_t)(r & 7)) << 4), ph[4 * c], ph[4 * c + 1], ph[4 * c + 2], ph[4 * c + 3]);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) pt_arrive(bar_s + B_PFULL + 8 * st);
+    }
+    // ---- un-normalised rows for the merge kernel ----
+    if (ok && wait_warp(bar_s + B_PVDONE + 8 * (uint32_t)((n_ktiles - 1) & 1), par2(n_ktiles - 1))) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int64_t row = (int64_t)(q0 + tok) * a.num_q_heads + kvh * G + r % G;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        tmem_ld32(tmem_o + t_lane + 32 * c, o);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (live) {
+          float4* dst = reinterpret_cast<float4*>(a.part_acc + row * 128 + 32 * c);
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            dst[i] = make_float4(__uint_as_float(o[4 * i]), __uint_as_float(o[4 * i + 1]), __uint_as_float(o[4 * i + 2]),
+                                 __uint_as_float(o[4 * i + 3]));
+        }
+      }
+      {
+        uint32_t o[32];
+        tmem_ld32(tmem_o + t_lane + 128, o);      // column 128: the row sum of the fp16 probabilities
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (live) { a.part_ml[row * 2] = m_ref; a.part_ml[row * 2 + 1] = __uint_as_float(o[0]); }
+      }
+    }
+  }
+
+  // A CTA in which a wait gave up may still have MMAs in flight: before the columns go back, the issuing thread
+  // commits once more on the drain barrier (it completes when every MMA that thread issued has) and waits, bounded.
+  // Only if that wait gives up too are the columns kept (status 2).
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  int leak = 0;
+  if (warp == 12 && lane == 0 && lds_u32(failed_s) != 0u) {
+    umma_commit(bar_s + B_DRAIN);
+    leak = mbar_wait(bar_s + B_DRAIN, 0u) ? 0 : 1;
+    if (leak) g_prefill_tc_status = 2;
+  }
+  leak = __syncthreads_or(leak);
+  if (warp == 0 && !leak) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "n"(PT_TMEM_COLS) : "memory");
+  }
+}
+
+}  // namespace
+
+int prefill_tc_status(int* host_out, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(host_out, g_prefill_tc_status, sizeof(int));
+  if (e == cudaSuccess && reset) { const int z = 0; e = cudaMemcpyToSymbol(g_prefill_tc_status, &z, sizeof(int)); }
+  return e == cudaSuccess ? AKV_OK : fail((int)e, "prefill status: %s", cudaGetErrorString(e));
+}
+
+int prefill_tc_withhold(int tile) {
+  cudaError_t e = cudaMemcpyToSymbol(g_prefill_tc_withhold, &tile, sizeof(int));
+  return e == cudaSuccess ? AKV_OK : fail((int)e, "prefill test hook: %s", cudaGetErrorString(e));
+}
+
+int launch_prefill_tc(const PrefillArgs& a, int G, cudaStream_t st) {
+  const int TT = 128 / G;
+  dim3 grid((a.n_tokens + TT - 1) / TT + a.num_seqs, a.num_kv_heads);
+  cudaError_t e = cudaSuccess;
+#define AKV_PT(GG)                                                                                                \
+  e = cudaFuncSetAttribute(tq_prefill_tc_kernel<GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, PT_SMEM);         \
+  if (e == cudaSuccess) tq_prefill_tc_kernel<GG><<<grid, PT_THREADS, PT_SMEM, st>>>(a);
+  if (G == 1) { AKV_PT(1) } else if (G == 2) { AKV_PT(2) } else if (G == 4) { AKV_PT(4) } else { AKV_PT(8) }
+#undef AKV_PT
+  if (e != cudaSuccess) return fail((int)e, "prefill attention: smem attribute: %s", cudaGetErrorString(e));
+  return check_launch("tq_prefill_attn_tc_kernel");
+}
+
+}  // namespace akv

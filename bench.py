@@ -331,7 +331,8 @@ def _event_time(fn, steps, warmup):
 def secondary_kernels(steps, warmup, dev):
     """The other configured kernels on their shapes (configs 0, 2, 3 of the benchmark specification), device-resident,
     CUDA events, inputs larger than L2: encode / decode / fused paged prefill write at 4, 3, 2 bits on
-    524 288 vectors, decode attention at 3 and 2 bits and with the hybrid tq35 layout on the headline shapes."""
+    524 288 vectors, decode attention at 3 and 2 bits and with the hybrid tq35 layout on the headline shapes,
+    chunked prefill attention over the packed 4-bit cache."""
     from aitherkvcache_b200 import TQPagedAttention, TurboQuant, fused_tq4_kv_update
     from aitherkvcache_b200.hybrid_quantizer import HybridPagedAttention, HybridTurboQuant
     peak, _ = peak_hbm()
@@ -378,6 +379,27 @@ def secondary_kernels(steps, warmup, dev):
         by = total_ctx * H_KV * 2 * (pd + 4)
         res[f"tq{bits}_decode_attn"] = {"KV-tokens/s": total_ctx / ms * 1e3, "GB/s": by / ms / 1e6,
                                         "frac_of_measured_peak": by / ms / 1e6 / peak, "ms": ms}
+    # chunked prefill over the packed 4-bit cache: a 2048-token chunk of one sequence with 30 000 tokens before it
+    tq = TurboQuant(head_dim=D, bits=4, device=str(dev))
+    attn = TQPagedAttention(tq, H_Q)
+    past, chunk = 30000, 2048
+    pnb = (past + chunk + BS - 1) // BS
+    kp = torch.randint(0, 256, (pnb, BS, H_KV, D // 2), dtype=torch.uint8, device=dev)
+    vp = torch.randint(0, 256, (pnb, BS, H_KV, D // 2), dtype=torch.uint8, device=dev)
+    kn = torch.rand(pnb, BS, H_KV, device=dev) + 0.5
+    vn = torch.rand(pnb, BS, H_KV, device=dev) + 0.5
+    pbt = torch.randperm(pnb, generator=torch.Generator().manual_seed(2)).to(torch.int32).reshape(1, pnb).to(dev)
+    qp = torch.randn(chunk, H_Q, D, generator=g, device=dev).half()
+    sl = torch.tensor([past + chunk], dtype=torch.int32, device=dev)
+    qsl = torch.tensor([0, chunk], dtype=torch.int32, device=dev)
+    outp = torch.empty_like(qp)
+    if attn.prefill(qp, kp, kn, vp, vn, pbt, sl, qsl, block_size=BS, num_kv_heads=H_KV, out=outp) is None:
+        raise RuntimeError("the chunked-prefill kernel refused the benchmark shape")
+    ms = _event_time(lambda: attn.prefill(qp, kp, kn, vp, vn, pbt, sl, qsl, block_size=BS, num_kv_heads=H_KV, out=outp),
+                     max(3, steps // 8), 2)
+    pairs = chunk * past + chunk * (chunk + 1) // 2            # (query token, key) pairs under the causal mask
+    res["tq4_chunked_prefill"] = {"ms": ms, "query_tokens": chunk, "past_tokens": past,
+                                  "TFLOP/s": pairs * H_Q * D * 4 / ms / 1e9, "query-tokens/s": chunk / ms * 1e3}
     htq = HybridTurboQuant(D, "tq35", device=str(dev))
     htq.calibrate_uniform()
     xh = torch.randn(8 * 4096 * 8, D, generator=g, device=dev).half()

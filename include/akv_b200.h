@@ -62,10 +62,11 @@ const char* akv_last_split_kernel(void);
  * A diagnostic call for health checks and tests, not part of a serving step. */
 int akv_device_status(int* out, int reset);
 
-/* Test hook for those bounded waits: CTA 0 of later encoder (which = 0) or decoder (which = 1)
- * launches issues neither the MMAs nor the commit of its tile number `tile`, so the wait on that tile
- * runs out with no tensor work in flight and the CTA leaves through its give-up path.  tile < 0
- * (the default) switches the hook off. */
+/* Test hook for those bounded waits: CTA 0 of later encoder (which = 0), decoder (which = 1) or
+ * tensor-core prefill attention (which = 2: the score MMAs of key tile `tile`) launches issues neither
+ * the MMAs nor the commit of its tile number `tile`, so the wait on that tile runs out with no tensor
+ * work in flight and the CTA leaves through its give-up path.  tile < 0 (the default) switches the
+ * hook off. */
 int akv_debug_tc_withhold(int which, int tile);
 
 /* ------------------------------------------------------------------------

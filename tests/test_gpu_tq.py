@@ -704,3 +704,72 @@ def test_chunked_prefill_kernel_equals_row_by_row_attention(H, QH, bs):
                                            vp.cpu().numpy(), vn.cpu().numpy(), bt[s:s + 1].numpy(), np.asarray([lens[s]]),
                                            g["rotation"], g["centroids"], 4, 1.0 / math.sqrt(128), bs)
     assert np.abs(out[row].float().cpu().numpy() - want[0]).max() < 2e-3
+
+
+def test_chunked_prefill_long_context_against_oracle_rows():
+    """A 512-token chunk behind 30 000 cached tokens (the headline cache geometry): three rows of the chunk against the
+    oracle, 64 rows against the decode kernels run with one row per query token."""
+    g = load_golden("tq_d128_b4.npz")
+    tq = _tq(128, 4, g)
+    H, QH, bs, past, chunk = 8, 32, 16, 30000, 512
+    attn = _attn(tq, QH)
+    gen = torch.Generator(device="cuda").manual_seed(77)
+    n = past + chunk
+    nb = (n + bs - 1) // bs
+    kp = torch.randint(0, 256, (nb, bs, H, 64), dtype=torch.uint8, device="cuda", generator=gen)
+    vp = torch.randint(0, 256, (nb, bs, H, 64), dtype=torch.uint8, device="cuda", generator=gen)
+    kn = torch.rand(nb, bs, H, device="cuda", generator=gen) + 0.5
+    vn = torch.rand(nb, bs, H, device="cuda", generator=gen) + 0.5
+    bt = torch.randperm(nb, device="cuda", generator=gen).to(torch.int32).reshape(1, nb)
+    query = (0.3 * torch.randn(chunk, QH, 128, device="cuda", generator=gen)).half()
+    sl = torch.tensor([n], dtype=torch.int32, device="cuda")
+    qsl = torch.tensor([0, chunk], dtype=torch.int32, device="cuda")
+    out = attn.prefill(query, kp, kn, vp, vn, bt, sl, qsl, block_size=bs, num_kv_heads=H)
+    assert out is not None
+    rows = torch.arange(0, chunk, 8, device="cuda")
+    ref = attn.forward(query[rows], kp, kn, vp, vn, bt.expand(len(rows), -1).contiguous(),
+                       (past + rows + 1).to(torch.int32), block_size=bs, num_kv_heads=H)
+    assert (out[rows].float() - ref.float()).abs().max().item() < 2e-3
+    kp_h, kn_h, vp_h, vn_h, bt_h = kp.cpu().numpy(), kn.cpu().numpy(), vp.cpu().numpy(), vn.cpu().numpy(), bt.cpu().numpy()
+    for row in (0, 257, chunk - 1):
+        want = otq.paged_attention_decode_sdpa(query[row:row + 1].cpu().numpy(), kp_h, kn_h, vp_h, vn_h, bt_h,
+                                               np.asarray([past + row + 1]), g["rotation"], g["centroids"], 4,
+                                               1.0 / math.sqrt(128), bs)
+        assert np.abs(out[row].float().cpu().numpy() - want[0]).max() < 2e-3
+
+
+def test_prefill_tensor_core_kernel_bounded_wait_gives_up_and_reports():
+    """The tensor-core prefill kernel with the score MMAs of one key tile withheld (test hook): the softmax warps' bounded
+    wait for that tile runs out, the CTA leaves through its give-up path and releases its tensor memory, the status word
+    reports it; afterwards the same call works again.  Nothing hangs or traps: the wait gives up by itself."""
+    g = load_golden("tq_d128_b4.npz")
+    tq = _tq(128, 4, g)
+    H, QH, bs, past, chunk = 2, 8, 16, 200, 64
+    attn = _attn(tq, QH)
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    n = past + chunk
+    nb = (n + bs - 1) // bs
+    kp = torch.randint(0, 256, (nb, bs, H, 64), dtype=torch.uint8, device="cuda", generator=gen)
+    vp = torch.randint(0, 256, (nb, bs, H, 64), dtype=torch.uint8, device="cuda", generator=gen)
+    kn = torch.rand(nb, bs, H, device="cuda", generator=gen) + 0.5
+    vn = torch.rand(nb, bs, H, device="cuda", generator=gen) + 0.5
+    bt = torch.arange(nb, device="cuda", dtype=torch.int32).reshape(1, nb)
+    query = torch.randn(chunk, QH, 128, device="cuda", generator=gen).half()
+    sl = torch.tensor([n], dtype=torch.int32, device="cuda")
+    qsl = torch.tensor([0, chunk], dtype=torch.int32, device="cuda")
+    from aitherkvcache_b200 import _lib
+    L = _lib.lib()
+    _lib.device_status(reset=True)
+    good = attn.prefill(query, kp, kn, vp, vn, bt, sl, qsl, block_size=bs, num_kv_heads=H)
+    assert good is not None and not any(_lib.device_status().values())
+    assert L.akv_last_split_kernel() == b"tq_prefill_attn_tc_kernel"
+    try:
+        assert L.akv_debug_tc_withhold(2, 1) == 0
+        attn.prefill(query, kp, kn, vp, vn, bt, sl, qsl, block_size=bs, num_kv_heads=H)
+        st = _lib.device_status(reset=True)
+        assert st["attn_window"] == 2
+    finally:
+        L.akv_debug_tc_withhold(2, -1)
+    again = attn.prefill(query, kp, kn, vp, vn, bt, sl, qsl, block_size=bs, num_kv_heads=H)
+    assert torch.equal(again, good)
+    assert not any(_lib.device_status().values())
