@@ -67,6 +67,7 @@ class TQPrefillParams(C.Structure):
         ("out", c_vp), ("out_dtype", c_int), ("out_stride_tok", c_i64), ("out_stride_head", c_i64),
         ("workspace", c_vp), ("workspace_bytes", C.c_size_t),
         ("stream", c_vp),
+        ("max_seq_len", c_int),
     ]
 
 
@@ -179,6 +180,7 @@ _SIGNATURES = {
     "akv_tq_paged_attn_workspace_bytes": (C.c_size_t, [c_int] * 8),
     "akv_tq_paged_attn": (c_int, [C.POINTER(TQAttnParams)]),
     "akv_tq_prefill_attn_workspace_bytes": (C.c_size_t, [c_int, c_int]),
+    "akv_tq_prefill_attn_workspace_bytes_staged": (C.c_size_t, [c_int] * 5),
     "akv_tq_prefill_attn": (c_int, [C.POINTER(TQPrefillParams)]),
     "akv_tq_decode_step": (c_int, [C.POINTER(TQDecodeStepParams)]),
     "akv_tq_paged_attn_static_scratch_bytes": (C.c_size_t, []),

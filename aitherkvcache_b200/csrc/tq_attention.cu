@@ -2709,6 +2709,7 @@ struct akv_tq_prefill_params {
   void* out; int out_dtype; int64_t out_stride_tok, out_stride_head;
   void* workspace; size_t workspace_bytes;
   void* stream;
+  int max_seq_len;
 };
 
 static void prefill_plan(int num_tokens, int num_q_heads, size_t* off_acc, size_t* off_ml, size_t* total) {
@@ -2728,6 +2729,14 @@ AKV_EXPORT size_t akv_tq_prefill_attn_workspace_bytes(int num_tokens, int num_q_
 
 // Returns AKV_ERR_UNSUPPORTED (without touching anything) for shapes the kernel is not built for; the caller
 // then attends row by row with akv_tq_paged_attn.
+AKV_EXPORT size_t akv_tq_prefill_attn_workspace_bytes_staged(int num_tokens, int num_q_heads, int num_kv_heads, int num_seqs,
+                                                             int max_seq_len) {
+  size_t a, m, total;
+  prefill_plan(num_tokens, num_q_heads, &a, &m, &total);
+  const size_t staged = prefill_staged_bytes(num_seqs, num_kv_heads, max_seq_len);
+  return staged ? ((total + 1023) & ~(size_t)1023) + staged : total;
+}
+
 AKV_EXPORT int akv_tq_prefill_attn(const akv_tq_prefill_params* p) {
   if (!p) return fail(AKV_ERR_ARG, "null params");
   if (p->num_tokens < 0 || p->num_seqs < 0 || p->num_q_heads <= 0 || p->num_kv_heads <= 0 ||
@@ -2791,6 +2800,16 @@ AKV_EXPORT int akv_tq_prefill_attn(const akv_tq_prefill_params* p) {
   const int64_t tc_tiles = (tc_rows + 127) / 128 + p->num_seqs - 1;
   const bool use_tc = tc_env ? tc_env[0] == '1' : tc_rows >= 64 * tc_tiles;
   if (use_tc) {
+    // with the longest sequence known on the host and room in the workspace, the codes are turned into fp16 operand
+    // images once (instead of once per row tile) and the tensor-core kernel is fed by bulk copies; AKV_PREFILL_STAGED=0
+    // keeps the decode inside the kernel
+    static const bool no_staged = getenv("AKV_PREFILL_STAGED") != nullptr && getenv("AKV_PREFILL_STAGED")[0] == '0';
+    const size_t staged = no_staged ? 0 : prefill_staged_bytes(p->num_seqs, p->num_kv_heads, p->max_seq_len);
+    const size_t staged_off = (total + 1023) & ~(size_t)1023;
+    if (staged != 0 && p->workspace_bytes >= staged_off + staged && (reinterpret_cast<uintptr_t>(ws) & 15) == 0) {
+      a.staged = reinterpret_cast<uint8_t*>(ws + staged_off);
+      a.tiles_per_seq = (p->max_seq_len + 63) / 64;
+    }
     if (int rc = launch_prefill_tc(a, G, st)) return rc;
   } else {
   const int TT = 64 / G;

@@ -19,12 +19,18 @@ struct PrefillArgs {
   const float* centroids;
   float* part_acc;                     // [n_tokens * num_q_heads][128]
   float* part_ml;                      // [n_tokens * num_q_heads][2]
+  // staged variant of the tensor-core kernel: [num_seqs][tiles_per_seq][num_kv_heads] operand images of 32 KB, or null
+  uint8_t* staged;
+  int tiles_per_seq;
 };
 
 // tcgen05 kernel (tq_prefill_tc.cu): one CTA per 128 (token, query head) rows and KV head.  Returns AKV_OK after
 // the launch; AKV_ERR_UNSUPPORTED is never returned - the caller checks the shape (4-bit codes, head_dim 128,
 // G in {1, 2, 4, 8}, block_size % 16 == 0, 16-byte readable caches) before calling.
+// With a.staged set, a pre-pass (tq_prefill_stage_kernel) first writes every key tile's fp16 operand images there and the
+// attention kernel is fed by bulk copies instead of decoding the codes itself.
 int launch_prefill_tc(const PrefillArgs& a, int G, cudaStream_t st);
+size_t prefill_staged_bytes(int num_seqs, int num_kv_heads, int max_seq_len);
 int prefill_tc_status(int* host_out, int reset);
 int prefill_tc_withhold(int tile);
 

@@ -39,18 +39,27 @@ __device__ int g_prefill_tc_status;          // 1: a bounded wait gave up, 2: te
 __device__ int g_prefill_tc_withhold = -1;   // test hook: CTA (0, 0) issues neither the score MMAs nor the commit of this tile
 
 constexpr int PT_KT = 64;                            // keys per tile
-constexpr int PT_THREADS = 13 * 32;
 constexpr int PT_STAGE = 16384;                      // one operand stage: 64 x 128 or 128 x 64 fp16
-constexpr int PT_Q = 0;                              // A of S: [128 rows][128 dims], two halves of 64 dims
-constexpr int PT_K = PT_Q + 32768;                   // B of S: 2 stages x [64 keys][128 dims], two halves of 64 rows
 constexpr int PT_VSTAGE = 144 * 128;                 // value stage: 128 dims + the row of ones (+ 15 zero rows) x 64 keys
-constexpr int PT_V = PT_K + 2 * PT_STAGE;            // B of PV: 2 stages x [144 rows][64 keys]
-constexpr int PT_P = PT_V + 2 * PT_VSTAGE;           // A of PV: 2 buffers x [128 rows][64 keys]
-constexpr int PT_LUT = PT_P + 2 * PT_STAGE;          // byte -> half2, one copy per lane (256 x 128 B)
-constexpr int PT_BAR = PT_LUT + 32768;               // mbarriers, tensor-memory slot, failed flag
-constexpr int PT_SMEM = PT_BAR + 256 + 1024;         // + slack for the 1024-byte alignment
-constexpr uint32_t B_KFULL = 0, B_VFULL = 16, B_SFULL = 32, B_SFREE = 48, B_PFULL = 64, B_PVDONE = 80,
-                   B_DRAIN = 128, B_TMEM = 136, B_FAILED = 140;
+constexpr int PT_IMAGE = 2 * PT_STAGE;               // a staged tile in global memory: K operand image, then V operand image
+
+// Shared-memory layout and warp roles of the two variants: codes decoded in the kernel (13 warps, two operand stages, the
+// lookup table) or operand images staged in global memory by tq_prefill_stage_kernel (6 warps, three stages fed by bulk copies).
+template <bool STAGED> struct PtL {
+  static constexpr int NST = STAGED ? 3 : 2;          // K / V operand stages
+  static constexpr int WARPS = STAGED ? 6 : 13;
+  static constexpr int THREADS = WARPS * 32;
+  static constexpr int MMA_WARP = STAGED ? 4 : 12;
+  static constexpr int Q = 0;                         // A of S: [128 rows][128 dims], two halves of 64 dims
+  static constexpr int K = Q + 32768;                 // B of S: NST x [64 keys][128 dims], two halves of 64 rows
+  static constexpr int V = K + NST * PT_STAGE;        // B of PV: NST x [144 rows][64 keys]
+  static constexpr int P = V + NST * PT_VSTAGE;       // A of PV: 2 buffers x [128 rows][64 keys]
+  static constexpr int LUT = P + 2 * PT_STAGE;        // byte -> half2, one copy per lane (256 x 128 B); not staged only
+  static constexpr int BAR = LUT + (STAGED ? 0 : 32768);      // mbarriers, tensor-memory slot, failed flag
+  static constexpr int SMEM = BAR + 256 + 1024;       // + slack for the 1024-byte alignment
+};
+constexpr uint32_t B_KFULL = 0, B_VFULL = 24, B_SFULL = 48, B_SFREE = 64, B_PFULL = 80, B_PVDONE = 96, B_KFREE = 112,
+                   B_VFREE = 136, B_DRAIN = 160, B_TMEM = 168, B_FAILED = 172;
 constexpr int PT_TMEM_COLS = 512;                    // S stages at columns 0 and 64, O at 128..271 (column 256 = row sum)
 constexpr float PT_RESCALE = 8.0f;                   // log2 units the row maximum may grow before O is rescaled
 
@@ -82,9 +91,70 @@ __device__ __forceinline__ void pt_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory");
 }
 
-template <int G>
-__global__ void __launch_bounds__(PT_THREADS, 1)
+// K operand rows: thread (key kr, chunk kc) turns its 16 packed bytes (32 dims) into four 16-byte pieces of row kr, times
+// the key norm.  Words 2, 3 first for the upper chunks: the eight threads of a quarter warp then store to eight
+// different bank groups.  `stage` is the shared address of a [64 keys][128 dims] operand (two halves of 64 rows).
+__device__ __forceinline__ void pt_decode_k(uint32_t stage, uint32_t lut, int kr, int kc, const uint4& kw, float kn) {
+  const uint32_t hi = (uint32_t)(kc >> 1);
+  const __half2 knh = __float2half2_rn(kn);
+  const uint32_t ws[4] = {hi ? kw.z : kw.x, hi ? kw.w : kw.y, hi ? kw.x : kw.z, hi ? kw.y : kw.w};
+  const uint32_t row = stage + hi * 8192u + (uint32_t)kr * 128u;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t h[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const uint32_t x = lds_u32(lut + (((ws[i] >> (8 * e)) & 0xffu) << 7));
+      const __half2 y = __hmul2(*reinterpret_cast<const __half2*>(&x), knh);
+      h[e] = *reinterpret_cast<const uint32_t*>(&y);
+    }
+    const uint32_t chunk = (uint32_t)(4 * (kc & 1)) + ((uint32_t)i ^ (hi << 1));
+    pt_sts128(row + ((chunk ^ (uint32_t)(kr & 7)) << 4), h[0], h[1], h[2], h[3]);
+  }
+}
+
+// Transposed V operand: thread (key group kg, bytes vbyte, vbyte + 1) turns two bytes of each of the keys 8 kg .. 8 kg + 7
+// into the 16-byte pieces (8 keys) of the four dim rows 2 vbyte .. 2 vbyte + 3, times the value norms.
+__device__ __forceinline__ void pt_decode_v(uint32_t stage, uint32_t lut, int kg, int vbyte, const uint32_t (&vw)[8],
+                                            const float (&vn)[8]) {
+  uint32_t e0[8], e1[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const __half2 nh = __float2half2_rn(vn[i]);
+    const uint32_t x0 = lds_u32(lut + ((vw[i] & 0xffu) << 7)), x1 = lds_u32(lut + (((vw[i] >> 8) & 0xffu) << 7));
+    const __half2 y0 = __hmul2(*reinterpret_cast<const __half2*>(&x0), nh), y1 = __hmul2(*reinterpret_cast<const __half2*>(&x1), nh);
+    e0[i] = *reinterpret_cast<const uint32_t*>(&y0);
+    e1[i] = *reinterpret_cast<const uint32_t*>(&y1);
+  }
+  const int r0 = 2 * vbyte;            // dims 2 vbyte, + 1 (first byte), + 2, + 3 (second byte)
+  auto put = [&](int row, const uint32_t (&e)[8], uint32_t sel) {
+    pt_sts128(stage + (uint32_t)row * 128u + (((uint32_t)kg ^ (uint32_t)(row & 7)) << 4),
+              __byte_perm(e[0], e[1], sel), __byte_perm(e[2], e[3], sel), __byte_perm(e[4], e[5], sel), __byte_perm(e[6], e[7], sel));
+  };
+  put(r0, e0, 0x5410u);
+  put(r0 + 1, e0, 0x7632u);
+  put(r0 + 2, e1, 0x5410u);
+  put(r0 + 3, e1, 0x7632u);
+}
+
+__device__ __forceinline__ void pt_fill_lut(uint8_t* lut, const float* centroids, int tid, int threads) {
+  // byte -> half2(centroid[high nibble], centroid[low nibble]) = coordinates 2b, 2b+1; one copy per lane
+  __shared__ float s_cent[16];
+  if (tid < 16) s_cent[tid] = centroids[tid];
+  __syncthreads();
+  for (int i = tid; i < 256 * 8; i += threads) {
+    const int e = i >> 3, q4 = i & 7;
+    const uint32_t v = pt_pack_half2(s_cent[e >> 4], s_cent[e & 15]);
+    *reinterpret_cast<uint4*>(lut + e * 128 + q4 * 16) = make_uint4(v, v, v, v);
+  }
+}
+
+template <int G, bool STAGED>
+__global__ void __launch_bounds__(PtL<STAGED>::THREADS, 1)
 tq_prefill_tc_kernel(PrefillArgs a) {
+  using L = PtL<STAGED>;
+  constexpr int PT_THREADS = L::THREADS, PT_Q = L::Q, PT_K = L::K, PT_V = L::V, PT_P = L::P, PT_LUT = L::LUT, PT_BAR = L::BAR;
+  constexpr int NST = L::NST;
   static_assert(G == 1 || G == 2 || G == 4 || G == 8, "query heads per KV head");
   constexpr int TT = 128 / G;           // query tokens of a CTA
   extern __shared__ uint8_t pt_smem_raw[];
@@ -116,14 +186,20 @@ tq_prefill_tc_kernel(PrefillArgs a) {
   const int tok_hi = (tok_lo + TT < qlen) ? tok_lo + TT : qlen;
   int kend = past + tok_hi;             // keys any row of this CTA may see
   if (kend > seq_len) kend = seq_len;
-  const int n_ktiles = (kend + PT_KT - 1) / PT_KT;
+  int n_ktiles = (kend + PT_KT - 1) / PT_KT;
+  if (STAGED && n_ktiles > a.tiles_per_seq) n_ktiles = a.tiles_per_seq;      // a caller that understated max_seq_len: no read past the images
   if (n_ktiles <= 0) return;            // nothing to attend to: the rows keep l = 0
 
   // ---------------- one-time setup ----------------
   if (tid == 0) {
+    for (int i = 0; i < NST; ++i) {
+      // decoded in the kernel: 8 decode-warp arrivals; staged: the producer's arrive.expect_tx + the copy's bytes
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar_s + B_KFULL + 8 * i), "r"(STAGED ? 1 : 8));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar_s + B_VFULL + 8 * i), "r"(STAGED ? 1 : 8));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar_s + B_KFREE + 8 * i));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar_s + B_VFREE + 8 * i));
+    }
     for (int i = 0; i < 2; ++i) {
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 8;" :: "r"(bar_s + B_KFULL + 8 * i));
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 8;" :: "r"(bar_s + B_VFULL + 8 * i));
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar_s + B_SFULL + 8 * i));
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;" :: "r"(bar_s + B_SFREE + 8 * i));
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;" :: "r"(bar_s + B_PFULL + 8 * i));
@@ -138,17 +214,7 @@ tq_prefill_tc_kernel(PrefillArgs a) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(bar_s + B_TMEM), "n"(PT_TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  // lookup table: byte -> half2(centroid[high nibble], centroid[low nibble]) = coordinates 2b, 2b+1; one copy per lane
-  {
-    __shared__ float s_cent[16];
-    if (tid < 16) s_cent[tid] = a.centroids[tid];
-    __syncthreads();
-    for (int i = tid; i < 256 * 8; i += PT_THREADS) {
-      const int e = i >> 3, q4 = i & 7;
-      const uint32_t v = pt_pack_half2(s_cent[e >> 4], s_cent[e & 15]);
-      *reinterpret_cast<uint4*>(base + PT_LUT + e * 128 + q4 * 16) = make_uint4(v, v, v, v);
-    }
-  }
+  if constexpr (!STAGED) pt_fill_lut(base + PT_LUT, a.centroids, tid, PT_THREADS);
   // A operand of S: the CTA's query rows, row r = (token tok_lo + r / G, head r % G), zeros for rows without a token
   for (int e = tid; e < 128 * 16; e += PT_THREADS) {
     const int r = e >> 4, c = e & 15;
@@ -162,7 +228,7 @@ tq_prefill_tc_kernel(PrefillArgs a) {
     *reinterpret_cast<uint4*>(base + PT_Q + (c >> 3) * 16384 + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
   }
   // rows 128..143 of both value stages: a row of ones (output column 128 becomes the row sum of P) and zero rows
-  for (int e = tid; e < 2 * 16 * 8; e += PT_THREADS) {
+  for (int e = tid; e < NST * 16 * 8; e += PT_THREADS) {
     const int stg = e >> 7, r = (e >> 3) & 15, c = e & 7;
     const uint32_t v = r == 0 ? 0x3C003C00u : 0u;
     *reinterpret_cast<uint4*>(base + PT_V + stg * PT_VSTAGE + (128 + r) * 128 + c * 16) = make_uint4(v, v, v, v);
@@ -193,8 +259,10 @@ tq_prefill_tc_kernel(PrefillArgs a) {
   };
   auto wait_warp = [&](uint32_t bar, uint32_t parity) -> bool { return __all_sync(0xffffffffu, wait(bar, parity)); };
   auto par2 = [](int j) -> uint32_t { return (uint32_t)((j >> 1) & 1); };      // phase parity of tile j on a two-stage barrier
+  auto kst = [](int j) -> uint32_t { return (uint32_t)(j % NST); };             // operand stage of tile j ...
+  auto kpar = [](int j) -> uint32_t { return (uint32_t)((j / NST) & 1); };      // ... and its phase parity
 
-  if (warp == 12) {
+  if (warp == L::MMA_WARP) {
     // ================= MMA warp =================
     if (lane == 0) {
       // D = f32, A / B = f16, both K-major; N = 64 (scores) or 128 (values), M = 128
@@ -202,29 +270,31 @@ tq_prefill_tc_kernel(PrefillArgs a) {
       constexpr uint32_t IDESC_O = (1u << 4) | ((144u >> 3) << 17) | ((128u >> 4) << 24);
       const int withhold = (blockIdx.x | blockIdx.y) == 0 ? g_prefill_tc_withhold : -1;
       auto issue_s = [&](int j) -> bool {
-        const uint32_t st = (uint32_t)(j & 1);
-        if (!wait(bar_s + B_KFULL + 8 * st, par2(j))) return false;
+        const uint32_t st = (uint32_t)(j & 1), ks = kst(j);
+        if (!wait(bar_s + B_KFULL + 8 * ks, kpar(j))) return false;
         if (j >= 2 && !wait(bar_s + B_SFREE + 8 * st, par2(j - 2))) return false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (j == withhold) return true;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
           umma_f16(tmem_base + st * 64, umma_desc(base_s + PT_Q + (uint32_t)((kk >> 2) * 16384 + (kk & 3) * 32)),
-                   umma_desc(base_s + PT_K + st * PT_STAGE + (uint32_t)((kk >> 2) * 8192 + (kk & 3) * 32)), IDESC_S,
+                   umma_desc(base_s + PT_K + ks * PT_STAGE + (uint32_t)((kk >> 2) * 8192 + (kk & 3) * 32)), IDESC_S,
                    (uint32_t)(kk != 0));
         umma_commit(bar_s + B_SFULL + 8 * st);
+        if constexpr (STAGED) umma_commit(bar_s + B_KFREE + 8 * ks);
         return true;
       };
       auto issue_pv = [&](int j) -> bool {
-        const uint32_t st = (uint32_t)(j & 1);
+        const uint32_t st = (uint32_t)(j & 1), ks = kst(j);
         if (!wait(bar_s + B_PFULL + 8 * st, par2(j))) return false;
-        if (!wait(bar_s + B_VFULL + 8 * st, par2(j))) return false;
+        if (!wait(bar_s + B_VFULL + 8 * ks, kpar(j))) return false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           umma_f16(tmem_o, umma_desc(base_s + PT_P + st * PT_STAGE + (uint32_t)(kk * 32)),
-                   umma_desc(base_s + PT_V + st * PT_VSTAGE + (uint32_t)(kk * 32)), IDESC_O, (uint32_t)((j | kk) != 0));
+                   umma_desc(base_s + PT_V + ks * PT_VSTAGE + (uint32_t)(kk * 32)), IDESC_O, (uint32_t)((j | kk) != 0));
         umma_commit(bar_s + B_PVDONE + 8 * st);
+        if constexpr (STAGED) umma_commit(bar_s + B_VFREE + 8 * ks);
         return true;
       };
       if (issue_s(0)) {
@@ -235,7 +305,34 @@ tq_prefill_tc_kernel(PrefillArgs a) {
       }
     }
     __syncwarp();
-  } else if (warp >= 4) {
+  } else if (STAGED && warp == 5) {
+    // ================= producer: operand images of tile j by two bulk copies =================
+    if (lane == 0) {
+      const uint8_t* src = a.staged + ((int64_t)s * a.tiles_per_seq * a.num_kv_heads + kvh) * PT_IMAGE;
+      const int64_t step = (int64_t)a.num_kv_heads * PT_IMAGE;
+      int issued = 0;
+      for (int j = 0; j < n_ktiles; ++j) {
+        const uint32_t ks = kst(j);
+        if (j >= NST && !wait(bar_s + B_KFREE + 8 * ks, kpar(j - NST))) break;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar_s + B_KFULL + 8 * ks), "r"(PT_STAGE) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     :: "r"(base_s + PT_K + ks * PT_STAGE), "l"(src + j * step), "r"(PT_STAGE), "r"(bar_s + B_KFULL + 8 * ks) : "memory");
+        if (j >= NST && !wait(bar_s + B_VFREE + 8 * ks, kpar(j - NST))) { issued = -(j + 1); break; }
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar_s + B_VFULL + 8 * ks), "r"(PT_STAGE) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     :: "r"(base_s + PT_V + ks * PT_VSTAGE), "l"(src + j * step + PT_STAGE), "r"(PT_STAGE), "r"(bar_s + B_VFULL + 8 * ks) : "memory");
+        issued = j + 1;
+      }
+      // a CTA that gives up must not leave while copies into its shared memory are in flight: the last copies of every
+      // stage are waited for here (bounded); in the regular flow the MMA warp has consumed them all already
+      if (lds_u32(failed_s) != 0u) {
+        const int nk = issued < 0 ? -issued : issued, nv = issued < 0 ? -issued - 1 : issued;
+        for (int j = nk - NST < 0 ? 0 : nk - NST; j < nk; ++j) mbar_wait(bar_s + B_KFULL + 8 * kst(j), kpar(j));
+        for (int j = nv - NST < 0 ? 0 : nv - NST; j < nv; ++j) mbar_wait(bar_s + B_VFULL + 8 * kst(j), kpar(j));
+      }
+    }
+    __syncwarp();
+  } else if (!STAGED && warp >= 4) {
     // ================= decode warps =================
     const int d = tid - 128;
     const int kr = d >> 2, kc = d & 3;                          // K: 16 bytes (32 dims) of key kr
@@ -323,52 +420,13 @@ tq_prefill_tc_kernel(PrefillArgs a) {
       posv_nx = pos_v;
       // ---- K operand of tile j: free once the scores of tile j-2 are complete ----
       if (j >= 2 && !wait_warp(bar_s + B_SFULL + 8 * st, par2(j - 2))) return false;
-      {
-        // words 2, 3 first for the upper chunks: the eight threads of a quarter warp then store to eight different
-        // bank groups
-        const uint32_t hi = (uint32_t)(kc >> 1);
-        const __half2 knh = __float2half2_rn(kn);
-        const uint32_t ws[4] = {hi ? kw.z : kw.x, hi ? kw.w : kw.y, hi ? kw.x : kw.z, hi ? kw.y : kw.w};
-        const uint32_t row = base_s + PT_K + st * PT_STAGE + hi * 8192u + (uint32_t)kr * 128u;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint32_t h[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const uint32_t x = lds_u32(lut + (((ws[i] >> (8 * e)) & 0xffu) << 7));
-            const __half2 y = __hmul2(*reinterpret_cast<const __half2*>(&x), knh);
-            h[e] = *reinterpret_cast<const uint32_t*>(&y);
-          }
-          const uint32_t chunk = (uint32_t)(4 * (kc & 1)) + ((uint32_t)i ^ (hi << 1));
-          pt_sts128(row + ((chunk ^ (uint32_t)(kr & 7)) << 4), h[0], h[1], h[2], h[3]);
-        }
-      }
+      pt_decode_k(base_s + PT_K + st * PT_STAGE, lut, kr, kc, kw, kn);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) pt_arrive(bar_s + B_KFULL + 8 * st);
       // ---- transposed V operand of tile j: free once P V of tile j-2 is complete ----
       if (j >= 2 && !wait_warp(bar_s + B_PVDONE + 8 * st, par2(j - 2))) return false;
-      {
-        uint32_t e0[8], e1[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const __half2 nh = __float2half2_rn(vn[i]);
-          const uint32_t x0 = lds_u32(lut + ((vw[i] & 0xffu) << 7)), x1 = lds_u32(lut + (((vw[i] >> 8) & 0xffu) << 7));
-          const __half2 y0 = __hmul2(*reinterpret_cast<const __half2*>(&x0), nh), y1 = __hmul2(*reinterpret_cast<const __half2*>(&x1), nh);
-          e0[i] = *reinterpret_cast<const uint32_t*>(&y0);
-          e1[i] = *reinterpret_cast<const uint32_t*>(&y1);
-        }
-        const uint32_t vst = base_s + PT_V + st * PT_VSTAGE;
-        const int r0 = 2 * vbyte;            // dims 2 vbyte, + 1 (first byte), + 2, + 3 (second byte)
-        auto put = [&](int row, const uint32_t (&e)[8], uint32_t sel) {
-          pt_sts128(vst + (uint32_t)row * 128u + (((uint32_t)kg ^ (uint32_t)(row & 7)) << 4),
-                    __byte_perm(e[0], e[1], sel), __byte_perm(e[2], e[3], sel), __byte_perm(e[4], e[5], sel), __byte_perm(e[6], e[7], sel));
-        };
-        put(r0, e0, 0x5410u);
-        put(r0 + 1, e0, 0x7632u);
-        put(r0 + 2, e1, 0x5410u);
-        put(r0 + 3, e1, 0x7632u);
-      }
+      pt_decode_v(base_s + PT_V + st * PT_VSTAGE, lut, kg, vbyte, vw, vn);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) pt_arrive(bar_s + B_VFULL + 8 * st);
@@ -379,7 +437,7 @@ tq_prefill_tc_kernel(PrefillArgs a) {
       if (j + 1 < n_ktiles && !tile_step(j + 1, R1, R0)) break;
       if (j + 2 < n_ktiles && !tile_step(j + 2, R2, R1)) break;
     }
-  } else {
+  } else if (warp < 4) {
     // ================= softmax warps: thread = row =================
     const int r = tid;
     const int tok = tok_lo + r / G;
@@ -484,7 +542,7 @@ tq_prefill_tc_kernel(PrefillArgs a) {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   int leak = 0;
-  if (warp == 12 && lane == 0 && lds_u32(failed_s) != 0u) {
+  if (warp == L::MMA_WARP && lane == 0 && lds_u32(failed_s) != 0u) {
     umma_commit(bar_s + B_DRAIN);
     leak = mbar_wait(bar_s + B_DRAIN, 0u) ? 0 : 1;
     if (leak) g_prefill_tc_status = 2;
@@ -492,6 +550,74 @@ tq_prefill_tc_kernel(PrefillArgs a) {
   leak = __syncthreads_or(leak);
   if (warp == 0 && !leak) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "n"(PT_TMEM_COLS) : "memory");
+  }
+}
+
+// Pre-pass of the staged variant: every 64-key tile of every sequence and KV head becomes the 32 KB pair of operand
+// images (K rows, transposed V rows, norms folded in, keys past the sequence zero) that tq_prefill_tc_kernel<G, true>
+// pulls into shared memory with two bulk copies.  A CTA takes PS_TILES consecutive tiles of one (sequence, KV head).
+constexpr int PS_THREADS = 256, PS_TILES = 4, PS_SMEM = 32768 + PT_IMAGE;
+
+__global__ void __launch_bounds__(PS_THREADS, 3)
+tq_prefill_stage_kernel(PrefillArgs a) {
+  extern __shared__ __align__(128) uint8_t ps_smem[];
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int s = blockIdx.y, kvh = blockIdx.z;
+  const int64_t max_ctx = (int64_t)a.max_blocks_per_seq * a.block_size;
+  const int seq_len = (int)load_ctx(a.seq_lens, a.sl_dtype, s, max_ctx);
+  int n_tiles = (seq_len + PT_KT - 1) / PT_KT;
+  if (n_tiles > a.tiles_per_seq) n_tiles = a.tiles_per_seq;
+  const int t_begin = blockIdx.x * PS_TILES;
+  if (t_begin >= n_tiles) return;
+  const int t_end = t_begin + PS_TILES < n_tiles ? t_begin + PS_TILES : n_tiles;
+  pt_fill_lut(ps_smem, a.centroids, tid, PS_THREADS);
+  __syncthreads();
+  const uint32_t lut = smem_u32(ps_smem) + lane * 4, img = smem_u32(ps_smem) + 32768;
+  const int kr = tid >> 2, kc = tid & 3;
+  const int kg = tid & 7, vbyte = 4 * (tid >> 4) + 2 * ((tid >> 3) & 1);
+  const int bs = a.block_size;
+  auto phys = [&](int key) -> int64_t {
+    int blk = key / bs;
+    if (blk >= a.max_blocks_per_seq) blk = a.max_blocks_per_seq - 1;
+    const int64_t pb = load_index(a.block_tables, a.bt_dtype, (int64_t)s * a.bt_stride + blk);
+    return pb < 0 ? 0 : (pb >= a.num_blocks ? a.num_blocks - 1 : pb);
+  };
+  for (int t = t_begin; t < t_end; ++t) {
+    uint4 kw;
+    float kn;
+    uint32_t vw[8];
+    float vn[8];
+    {
+      const int key = PT_KT * t + kr;
+      const int64_t pb = phys(key);
+      const int pos = key - (key / bs) * bs;
+      kw = __ldg(reinterpret_cast<const uint4*>(a.k_packed + pb * a.kp_sb + (int64_t)pos * a.kp_sp + (int64_t)kvh * a.kp_sh + kc * 16));
+      kn = key < seq_len ? __ldg(a.k_norms + pb * a.kn_sb + (int64_t)pos * a.kn_sp + (int64_t)kvh * a.kn_sh) : 0.f;
+    }
+    {
+      const int key8 = PT_KT * t + 8 * kg;
+      const int64_t pb = phys(key8);
+      const int pos8 = key8 - (key8 / bs) * bs;
+      const uint8_t* vp = a.v_packed + pb * a.vp_sb + (int64_t)pos8 * a.vp_sp + (int64_t)kvh * a.vp_sh + vbyte;
+      const float* np = a.v_norms + pb * a.vn_sb + (int64_t)pos8 * a.vn_sp + (int64_t)kvh * a.vn_sh;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        vw[i] = (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(vp + (int64_t)i * a.vp_sp));
+        vn[i] = key8 + i < seq_len ? __ldg(np + (int64_t)i * a.vn_sp) : 0.f;
+      }
+    }
+    pt_decode_k(img, lut, kr, kc, kw, kn);
+    pt_decode_v(img + PT_STAGE, lut, kg, vbyte, vw, vn);
+    __syncthreads();
+    uint4* dst = reinterpret_cast<uint4*>(a.staged + (((int64_t)s * a.tiles_per_seq + t) * a.num_kv_heads + kvh) * PT_IMAGE);
+#pragma unroll
+    for (int i = 0; i < PT_IMAGE / 16 / PS_THREADS; ++i) {
+      const int idx = i * PS_THREADS + tid;
+      uint4 v;
+      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(img + idx * 16));
+      dst[idx] = v;
+    }
+    __syncthreads();
   }
 }
 
@@ -512,13 +638,30 @@ int launch_prefill_tc(const PrefillArgs& a, int G, cudaStream_t st) {
   const int TT = 128 / G;
   dim3 grid((a.n_tokens + TT - 1) / TT + a.num_seqs, a.num_kv_heads);
   cudaError_t e = cudaSuccess;
-#define AKV_PT(GG)                                                                                                \
-  e = cudaFuncSetAttribute(tq_prefill_tc_kernel<GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, PT_SMEM);         \
-  if (e == cudaSuccess) tq_prefill_tc_kernel<GG><<<grid, PT_THREADS, PT_SMEM, st>>>(a);
-  if (G == 1) { AKV_PT(1) } else if (G == 2) { AKV_PT(2) } else if (G == 4) { AKV_PT(4) } else { AKV_PT(8) }
+  if (a.staged != nullptr) {
+    // operand images first (ordered before the attention kernel by the stream), then the bulk-copy-fed kernel
+    e = cudaFuncSetAttribute(tq_prefill_stage_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PS_SMEM);
+    if (e != cudaSuccess) return fail((int)e, "prefill attention: smem attribute: %s", cudaGetErrorString(e));
+    dim3 sgrid((a.tiles_per_seq + PS_TILES - 1) / PS_TILES, a.num_seqs, a.num_kv_heads);
+    tq_prefill_stage_kernel<<<sgrid, PS_THREADS, PS_SMEM, st>>>(a);
+    if (int rc = check_launch("tq_prefill_stage_kernel")) return rc;
+  }
+#define AKV_PT(GG, ST)                                                                                                  \
+  e = cudaFuncSetAttribute(tq_prefill_tc_kernel<GG, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, PtL<ST>::SMEM);     \
+  if (e == cudaSuccess) tq_prefill_tc_kernel<GG, ST><<<grid, PtL<ST>::THREADS, PtL<ST>::SMEM, st>>>(a);
+  if (a.staged != nullptr) {
+    if (G == 1) { AKV_PT(1, true) } else if (G == 2) { AKV_PT(2, true) } else if (G == 4) { AKV_PT(4, true) } else { AKV_PT(8, true) }
+  } else {
+    if (G == 1) { AKV_PT(1, false) } else if (G == 2) { AKV_PT(2, false) } else if (G == 4) { AKV_PT(4, false) } else { AKV_PT(8, false) }
+  }
 #undef AKV_PT
   if (e != cudaSuccess) return fail((int)e, "prefill attention: smem attribute: %s", cudaGetErrorString(e));
-  return check_launch("tq_prefill_attn_tc_kernel");
+  return check_launch(a.staged != nullptr ? "tq_prefill_attn_tc_staged_kernel" : "tq_prefill_attn_tc_kernel");
+}
+
+size_t prefill_staged_bytes(int num_seqs, int num_kv_heads, int max_seq_len) {
+  if (num_seqs <= 0 || num_kv_heads <= 0 || max_seq_len <= 0) return 0;
+  return (size_t)num_seqs * (size_t)((max_seq_len + PT_KT - 1) / PT_KT) * (size_t)num_kv_heads * PT_IMAGE;
 }
 
 }  // namespace akv

@@ -28,6 +28,8 @@ class TQPagedAttention:
     SPLITK_NUM_SPLITS = int(os.environ.get("AITHER_TQ_SPLITK_SPLITS", "16"))
     SPLITK_BLOCKS = int(os.environ.get("AITHER_TQ_SPLITK_BLOCKS", "0"))
 
+    STAGED_WORKSPACE_LIMIT = 4 << 30     # bytes of scratch the staged prefill kernel may ask for
+
     def __init__(self, tq, num_query_heads: int, block_selector=None):
         # optional BlockSelector (block_selector.py): filters block_tables / context_lens per query on the
         # device before the attention kernels run (hook of the reference: fused_attention.py:664-668)
@@ -107,14 +109,19 @@ class TQPagedAttention:
 
     def prefill(self, query, k_packed, k_norms, v_packed, v_norms, block_tables, seq_lens, query_start_loc,
                 block_size: int = 16, num_kv_heads: Optional[int] = None, out: Optional[torch.Tensor] = None,
-                scale: Optional[float] = None) -> Optional[torch.Tensor]:
+                scale: Optional[float] = None, max_seq_len: Optional[int] = None) -> Optional[torch.Tensor]:
         """Chunked-prefill attention: ``query`` [tokens, query_heads, head_dim] holds the last
         ``query_start_loc[s+1] - query_start_loc[s]`` tokens of every sequence s; token i of a sequence attends
         causally over the cached tokens up to its own position (``seq_lens`` counts the chunk's tokens, whose K/V
         are already in the cache).  The query tokens of a sequence share one pass over its packed blocks
         (``akv_tq_prefill_attn``); the reference decompresses the blocks and calls vLLM's unified attention
         (``vllm/backend.py:1093-1244``).  Returns None when the kernel is not built for the shapes (the caller
-        then attends row by row with ``forward``)."""
+        then attends row by row with ``forward``).
+
+        ``max_seq_len``: the longest entry of ``seq_lens`` when the host knows it (vLLM's metadata carries it; it is
+        never read back from the device here).  With it, large chunks take the staged tensor-core kernel: the codes of
+        every key tile become fp16 operand images once, in a scratch buffer of 512 bytes per (token, KV head) of
+        ``num_seqs x max_seq_len`` (up to ``STAGED_WORKSPACE_LIMIT`` bytes), instead of once per 128 query rows."""
         if num_kv_heads is None:
             num_kv_heads = k_packed.shape[2]
         dev = _lib.require_cuda(query, k_packed, k_norms, v_packed, v_norms, block_tables, seq_lens, query_start_loc)
@@ -140,6 +147,10 @@ class TQPagedAttention:
             out = torch.empty(n_tok, num_q_heads, head_dim, dtype=query.dtype, device=dev)
         L = _lib.lib()
         nbytes = L.akv_tq_prefill_attn_workspace_bytes(n_tok, num_q_heads)
+        if max_seq_len is not None and max_seq_len > 0:
+            staged = L.akv_tq_prefill_attn_workspace_bytes_staged(n_tok, num_q_heads, num_kv_heads, num_seqs, int(max_seq_len))
+            if staged <= self.STAGED_WORKSPACE_LIMIT:
+                nbytes = staged
         if self._prefill_ws is None or self._prefill_ws.numel() < nbytes or self._prefill_ws.device != dev:
             self._prefill_ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=dev)
         p = _lib.TQPrefillParams()
@@ -159,6 +170,7 @@ class TQPagedAttention:
         p.out, p.out_dtype, p.out_stride_tok, p.out_stride_head = out.data_ptr(), _lib.float_code(out), out.stride(0), out.stride(1)
         p.workspace, p.workspace_bytes = self._prefill_ws.data_ptr(), self._prefill_ws.numel()
         p.stream = _lib.stream_ptr(dev)
+        p.max_seq_len = int(max_seq_len) if max_seq_len else 0
         with torch.cuda.device(dev):
             rc = L.akv_tq_prefill_attn(ctypes.byref(p))
         _lib.check(rc, "akv_tq_prefill_attn")

@@ -175,9 +175,17 @@ typedef struct akv_tq_prefill_params {
   void* out; int out_dtype; int64_t out_stride_tok, out_stride_head;
   void* workspace; size_t workspace_bytes;   /* akv_tq_prefill_attn_workspace_bytes(num_tokens, num_q_heads) */
   void* stream;
+  int max_seq_len;   /* longest entry of seq_lens if the host knows it (vLLM's metadata does), else 0 */
 } akv_tq_prefill_params;
 
+/* Workspace: the first function gives what every call needs.  With max_seq_len set and a workspace of at least
+ * akv_tq_prefill_attn_workspace_bytes_staged(...) bytes (32 KB per 64 keys, sequence and KV head more), chunks large
+ * enough for the tensor-core kernel are served by its staged variant: one pre-pass turns the codes of every key
+ * tile into fp16 operand images in the workspace, and the attention kernel pulls them in with bulk copies instead
+ * of decoding them once per 128 query rows. */
 size_t akv_tq_prefill_attn_workspace_bytes(int num_tokens, int num_q_heads);
+size_t akv_tq_prefill_attn_workspace_bytes_staged(int num_tokens, int num_q_heads, int num_kv_heads, int num_seqs,
+                                                  int max_seq_len);
 int akv_tq_prefill_attn(const akv_tq_prefill_params* params);
 
 /* One decode step of the serving path in a single call: encode the new tokens'

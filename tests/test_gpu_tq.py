@@ -661,8 +661,9 @@ def test_device_status_is_clean_and_reports_a_wait_that_gave_up():
     assert not any(_lib.device_status().values())
 
 
+@pytest.mark.parametrize("staged", (False, True))
 @pytest.mark.parametrize("H,QH,bs", ((8, 32, 16), (2, 16, 32), (4, 4, 16), (2, 4, 16)))
-def test_chunked_prefill_kernel_equals_row_by_row_attention(H, QH, bs):
+def test_chunked_prefill_kernel_equals_row_by_row_attention(H, QH, bs, staged):
     """akv_tq_prefill_attn (query tokens of a sequence share one pass over its packed blocks) against the decode
     kernels run with one row per query token and its causal context length, and against the oracle on one row."""
     g = load_golden("tq_d128_b4.npz")
@@ -688,8 +689,10 @@ def test_chunked_prefill_kernel_equals_row_by_row_attention(H, QH, bs):
     qsl = torch.tensor([0] + list(np.cumsum([q for _, q in seqs])), dtype=torch.int32)
     query = torch.randn(nq + 3, QH, 128, generator=gen).half().cuda()          # three padding rows at the end
     out = torch.full((nq + 3, QH, 128), 7.0, dtype=torch.float16, device="cuda")
+    # staged: the longest sequence is known on the host, so chunks large enough for the tensor-core kernel get their
+    # operand images from the pre-pass
     res = attn.prefill(query, kp, kn, vp, vn, bt.cuda(), torch.tensor(lens, dtype=torch.int32).cuda(), qsl.cuda(),
-                       block_size=bs, num_kv_heads=H, out=out)
+                       block_size=bs, num_kv_heads=H, out=out, max_seq_len=max(lens) if staged else None)
     assert res is out
     assert (out[nq:] == 0).all()
     # one row per query token
@@ -706,7 +709,8 @@ def test_chunked_prefill_kernel_equals_row_by_row_attention(H, QH, bs):
     assert np.abs(out[row].float().cpu().numpy() - want[0]).max() < 2e-3
 
 
-def test_chunked_prefill_long_context_against_oracle_rows():
+@pytest.mark.parametrize("staged", (False, True))
+def test_chunked_prefill_long_context_against_oracle_rows(staged):
     """A 512-token chunk behind 30 000 cached tokens (the headline cache geometry): three rows of the chunk against the
     oracle, 64 rows against the decode kernels run with one row per query token."""
     g = load_golden("tq_d128_b4.npz")
@@ -724,8 +728,10 @@ def test_chunked_prefill_long_context_against_oracle_rows():
     query = (0.3 * torch.randn(chunk, QH, 128, device="cuda", generator=gen)).half()
     sl = torch.tensor([n], dtype=torch.int32, device="cuda")
     qsl = torch.tensor([0, chunk], dtype=torch.int32, device="cuda")
-    out = attn.prefill(query, kp, kn, vp, vn, bt, sl, qsl, block_size=bs, num_kv_heads=H)
+    out = attn.prefill(query, kp, kn, vp, vn, bt, sl, qsl, block_size=bs, num_kv_heads=H, max_seq_len=n if staged else None)
     assert out is not None
+    from aitherkvcache_b200 import _lib
+    assert _lib.lib().akv_last_split_kernel() == (b"tq_prefill_attn_tc_staged_kernel" if staged else b"tq_prefill_attn_tc_kernel")
     rows = torch.arange(0, chunk, 8, device="cuda")
     ref = attn.forward(query[rows], kp, kn, vp, vn, bt.expand(len(rows), -1).contiguous(),
                        (past + rows + 1).to(torch.int32), block_size=bs, num_kv_heads=H)
