@@ -35,6 +35,12 @@
 namespace akv {
 namespace {
 
+#ifdef PT_PROFILE
+__device__ long long g_pt_prof[64];
+#define PT_T(i) do { const long long now_ = clock64(); acc_[i] += now_ - tprev_; tprev_ = now_; } while (0)
+#else
+#define PT_T(i)
+#endif
 __device__ int g_prefill_tc_status;          // 1: a bounded wait gave up, 2: tensor-memory columns were kept
 __device__ int g_prefill_tc_withhold = -1;   // test hook: CTA (0, 0) issues neither the score MMAs nor the commit of this tile
 
@@ -46,20 +52,20 @@ constexpr int PT_IMAGE = 2 * PT_STAGE;               // a staged tile in global 
 // Shared-memory layout and warp roles of the two variants: codes decoded in the kernel (13 warps, two operand stages, the
 // lookup table) or operand images staged in global memory by tq_prefill_stage_kernel (6 warps, three stages fed by bulk copies).
 template <bool STAGED> struct PtL {
-  static constexpr int NST = STAGED ? 3 : 2;          // K / V operand stages
+  static constexpr int NST = STAGED ? 4 : 2;          // K / V operand stages (the barrier block has room for four)
+  static_assert(NST <= 4, "barrier slots");
   static constexpr int WARPS = STAGED ? 6 : 13;
   static constexpr int THREADS = WARPS * 32;
   static constexpr int MMA_WARP = STAGED ? 4 : 12;
-  static constexpr int Q = 0;                         // A of S: [128 rows][128 dims], two halves of 64 dims
-  static constexpr int K = Q + 32768;                 // B of S: NST x [64 keys][128 dims], two halves of 64 rows
+  static constexpr int K = 0;                         // B of S: NST x [64 keys][128 dims], two halves of 64 rows
   static constexpr int V = K + NST * PT_STAGE;        // B of PV: NST x [144 rows][64 keys]
-  static constexpr int P = V + NST * PT_VSTAGE;       // A of PV: 2 buffers x [128 rows][64 keys]
-  static constexpr int LUT = P + 2 * PT_STAGE;        // byte -> half2, one copy per lane (256 x 128 B); not staged only
+  static constexpr int LUT = V + NST * PT_VSTAGE;     // byte -> half2, one copy per lane (256 x 128 B); not staged only
   static constexpr int BAR = LUT + (STAGED ? 0 : 32768);      // mbarriers, tensor-memory slot, failed flag
   static constexpr int SMEM = BAR + 256 + 1024;       // + slack for the 1024-byte alignment
 };
-constexpr uint32_t B_KFULL = 0, B_VFULL = 24, B_SFULL = 48, B_SFREE = 64, B_PFULL = 80, B_PVDONE = 96, B_KFREE = 112,
-                   B_VFREE = 136, B_DRAIN = 160, B_TMEM = 168, B_FAILED = 172;
+// barrier slots (8 bytes each; up to four operand stages)
+constexpr uint32_t B_KFULL = 0, B_VFULL = 32, B_SFULL = 64, B_PFULL = 96, B_PVDONE = 112,
+                   B_VFREE = 160, B_DRAIN = 192, B_TMEM = 200, B_FAILED = 204;
 constexpr int PT_TMEM_COLS = 512;                    // S stages at columns 0 and 64, O at 128..271 (column 256 = row sum)
 constexpr float PT_RESCALE = 8.0f;                   // log2 units the row maximum may grow before O is rescaled
 
@@ -73,6 +79,15 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32
          "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
          "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
       : "memory");
+}
+
+// MMA with the A operand in tensor memory: row i of A is lane i, its K elements are packed two per 32-bit column
+// (a 16-element K step = 8 columns) - the layout a thread's tcgen05.st of packed half2 registers produces.
+__device__ __forceinline__ void umma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
+      :: "r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
 __device__ __forceinline__ void pt_sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
@@ -153,7 +168,7 @@ template <int G, bool STAGED>
 __global__ void __launch_bounds__(PtL<STAGED>::THREADS, 1)
 tq_prefill_tc_kernel(PrefillArgs a) {
   using L = PtL<STAGED>;
-  constexpr int PT_THREADS = L::THREADS, PT_Q = L::Q, PT_K = L::K, PT_V = L::V, PT_P = L::P, PT_LUT = L::LUT, PT_BAR = L::BAR;
+  constexpr int PT_THREADS = L::THREADS, PT_K = L::K, PT_V = L::V, PT_LUT = L::LUT, PT_BAR = L::BAR;
   constexpr int NST = L::NST;
   static_assert(G == 1 || G == 2 || G == 4 || G == 8, "query heads per KV head");
   constexpr int TT = 128 / G;           // query tokens of a CTA
@@ -196,12 +211,10 @@ tq_prefill_tc_kernel(PrefillArgs a) {
       // decoded in the kernel: 8 decode-warp arrivals; staged: the producer's arrive.expect_tx + the copy's bytes
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar_s + B_KFULL + 8 * i), "r"(STAGED ? 1 : 8));
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar_s + B_VFULL + 8 * i), "r"(STAGED ? 1 : 8));
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar_s + B_KFREE + 8 * i));
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar_s + B_VFREE + 8 * i));
     }
     for (int i = 0; i < 2; ++i) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar_s + B_SFULL + 8 * i));
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;" :: "r"(bar_s + B_SFREE + 8 * i));
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;" :: "r"(bar_s + B_PFULL + 8 * i));
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar_s + B_PVDONE + 8 * i));
     }
@@ -215,18 +228,6 @@ tq_prefill_tc_kernel(PrefillArgs a) {
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   if constexpr (!STAGED) pt_fill_lut(base + PT_LUT, a.centroids, tid, PT_THREADS);
-  // A operand of S: the CTA's query rows, row r = (token tok_lo + r / G, head r % G), zeros for rows without a token
-  for (int e = tid; e < 128 * 16; e += PT_THREADS) {
-    const int r = e >> 4, c = e & 15;
-    const int tok = tok_lo + r / G;
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (tok < qlen && q0 + tok < a.n_tokens) {
-      const float4* src = reinterpret_cast<const float4*>(a.qrot + ((int64_t)(q0 + tok) * a.num_q_heads + kvh * G + r % G) * 128 + 8 * c);
-      const float4 f0 = src[0], f1 = src[1];
-      v = make_uint4(pt_pack_half2(f0.x, f0.y), pt_pack_half2(f0.z, f0.w), pt_pack_half2(f1.x, f1.y), pt_pack_half2(f1.z, f1.w));
-    }
-    *reinterpret_cast<uint4*>(base + PT_Q + (c >> 3) * 16384 + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
-  }
   // rows 128..143 of both value stages: a row of ones (output column 128 becomes the row sum of P) and zero rows
   for (int e = tid; e < NST * 16 * 8; e += PT_THREADS) {
     const int stg = e >> 7, r = (e >> 3) & 15, c = e & 7;
@@ -238,7 +239,31 @@ tq_prefill_tc_kernel(PrefillArgs a) {
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = lds_u32(bar_s + B_TMEM);
-  const uint32_t tmem_o = tmem_base + 128;                  // S stage s at column 64 s, O at columns 128..255
+  const uint32_t tmem_o = tmem_base + 128;                  // S stage s at column 64 s, O at columns 128..271
+  const uint32_t tmem_p = tmem_base + 288;                  // P buffer s at columns 288 + 32 s: 64 fp16 probabilities per row
+  const uint32_t tmem_q = tmem_base + 352;                  // Q: 128 fp16 coordinates per row in 64 columns
+  // A operand of S: the CTA's query rows, row r = (token tok_lo + r / G, head r % G), zeros for rows without a token;
+  // thread r of the softmax warps writes its row into its lane of tensor memory
+  if (warp < 4) {
+    const int r = tid, tok = tok_lo + r / G;
+    const bool have = tok < qlen && q0 + tok < a.n_tokens;
+    const float4* src = reinterpret_cast<const float4*>(a.qrot + ((int64_t)(q0 + (have ? tok : 0)) * a.num_q_heads + kvh * G + r % G) * 128);
+#pragma unroll 1
+    for (int c = 0; c < 2; ++c) {
+      uint32_t w[32];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float4 f = have ? src[16 * c + i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        w[2 * i] = pt_pack_half2(f.x, f.y);
+        w[2 * i + 1] = pt_pack_half2(f.z, f.w);
+      }
+      tmem_st32(tmem_q + (((uint32_t)(warp * 32)) << 16) + 32 * c, w);
+    }
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
   // Bounded wait.  Fast path: one try_wait (the hardware parks the thread for a while if the phase has not flipped).  Only
   // a wait that comes back empty goes into the counted loop; once one wait of the CTA has run out, the others return
@@ -269,32 +294,48 @@ tq_prefill_tc_kernel(PrefillArgs a) {
       constexpr uint32_t IDESC_S = (1u << 4) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
       constexpr uint32_t IDESC_O = (1u << 4) | ((144u >> 3) << 17) | ((128u >> 4) << 24);
       const int withhold = (blockIdx.x | blockIdx.y) == 0 ? g_prefill_tc_withhold : -1;
+#ifdef PT_PROFILE
+      long long acc_[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      long long tprev_ = clock64();
+#endif
+      // Descriptors differ only in their 14-bit address field: one constant upper half, lower halves by 32-bit adds.
+      const uint64_t d_hi = umma_desc(0u) & 0xffffffff00000000ull;
+      const uint32_t d_lo = (uint32_t)umma_desc(0u);
+      auto desc = [&](uint32_t saddr) -> uint64_t { return d_hi | (uint64_t)(d_lo + ((saddr & 0x3FFFFu) >> 4)); };
+      const uint32_t k_lo = base_s + PT_K, v_lo = base_s + PT_V;
+      // S buffer (j & 1) was last read by the softmax warps for tile j-2, whose p_full this lane has waited for before
+      // it issued P V of tile j-2: no separate "scores read" barrier is needed.
       auto issue_s = [&](int j) -> bool {
         const uint32_t st = (uint32_t)(j & 1), ks = kst(j);
         if (!wait(bar_s + B_KFULL + 8 * ks, kpar(j))) return false;
-        if (j >= 2 && !wait(bar_s + B_SFREE + 8 * st, par2(j - 2))) return false;
+        PT_T(0);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (j == withhold) return true;
+        const uint32_t kb = k_lo + ks * PT_STAGE;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_f16(tmem_base + st * 64, umma_desc(base_s + PT_Q + (uint32_t)((kk >> 2) * 16384 + (kk & 3) * 32)),
-                   umma_desc(base_s + PT_K + ks * PT_STAGE + (uint32_t)((kk >> 2) * 8192 + (kk & 3) * 32)), IDESC_S,
-                   (uint32_t)(kk != 0));
+          umma_f16_ta(tmem_base + st * 64, tmem_q + (uint32_t)(kk * 8), desc(kb + (uint32_t)((kk >> 2) * 8192 + (kk & 3) * 32)),
+                      IDESC_S, (uint32_t)(kk != 0));
         umma_commit(bar_s + B_SFULL + 8 * st);
-        if constexpr (STAGED) umma_commit(bar_s + B_KFREE + 8 * ks);
+        PT_T(2);
         return true;
       };
       auto issue_pv = [&](int j) -> bool {
         const uint32_t st = (uint32_t)(j & 1), ks = kst(j);
         if (!wait(bar_s + B_PFULL + 8 * st, par2(j))) return false;
-        if (!wait(bar_s + B_VFULL + 8 * ks, kpar(j))) return false;
+        PT_T(3);
+        if constexpr (!STAGED) {       // staged: the value image arrived on the same barrier as the key image
+          if (!wait(bar_s + B_VFULL + 8 * ks, kpar(j))) return false;
+        }
+        PT_T(4);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t vb = v_lo + ks * PT_VSTAGE;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_f16(tmem_o, umma_desc(base_s + PT_P + st * PT_STAGE + (uint32_t)(kk * 32)),
-                   umma_desc(base_s + PT_V + ks * PT_VSTAGE + (uint32_t)(kk * 32)), IDESC_O, (uint32_t)((j | kk) != 0));
+          umma_f16_ta(tmem_o, tmem_p + st * 32 + (uint32_t)(kk * 8), desc(vb + (uint32_t)(kk * 32)), IDESC_O, (uint32_t)((j | kk) != 0));
         umma_commit(bar_s + B_PVDONE + 8 * st);
         if constexpr (STAGED) umma_commit(bar_s + B_VFREE + 8 * ks);
+        PT_T(5);
         return true;
       };
       if (issue_s(0)) {
@@ -303,6 +344,9 @@ tq_prefill_tc_kernel(PrefillArgs a) {
           if (!issue_pv(j)) break;
         }
       }
+#ifdef PT_PROFILE
+      if ((blockIdx.x | blockIdx.y) == 0) for (int i = 0; i < 8; ++i) g_pt_prof[i] = acc_[i];
+#endif
     }
     __syncwarp();
   } else if (STAGED && warp == 5) {
@@ -313,23 +357,19 @@ tq_prefill_tc_kernel(PrefillArgs a) {
       int issued = 0;
       for (int j = 0; j < n_ktiles; ++j) {
         const uint32_t ks = kst(j);
-        if (j >= NST && !wait(bar_s + B_KFREE + 8 * ks, kpar(j - NST))) break;
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar_s + B_KFULL + 8 * ks), "r"(PT_STAGE) : "memory");
+        // P V of tile j - NST complete: its value stage is free, and so is its key stage (the scores came first)
+        if (j >= NST && !wait(bar_s + B_VFREE + 8 * ks, kpar(j - NST))) break;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar_s + B_KFULL + 8 * ks), "r"(2 * PT_STAGE) : "memory");
         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                      :: "r"(base_s + PT_K + ks * PT_STAGE), "l"(src + j * step), "r"(PT_STAGE), "r"(bar_s + B_KFULL + 8 * ks) : "memory");
-        if (j >= NST && !wait(bar_s + B_VFREE + 8 * ks, kpar(j - NST))) { issued = -(j + 1); break; }
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar_s + B_VFULL + 8 * ks), "r"(PT_STAGE) : "memory");
         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                     :: "r"(base_s + PT_V + ks * PT_VSTAGE), "l"(src + j * step + PT_STAGE), "r"(PT_STAGE), "r"(bar_s + B_VFULL + 8 * ks) : "memory");
+                     :: "r"(base_s + PT_V + ks * PT_VSTAGE), "l"(src + j * step + PT_STAGE), "r"(PT_STAGE), "r"(bar_s + B_KFULL + 8 * ks) : "memory");
         issued = j + 1;
       }
       // a CTA that gives up must not leave while copies into its shared memory are in flight: the last copies of every
       // stage are waited for here (bounded); in the regular flow the MMA warp has consumed them all already
-      if (lds_u32(failed_s) != 0u) {
-        const int nk = issued < 0 ? -issued : issued, nv = issued < 0 ? -issued - 1 : issued;
-        for (int j = nk - NST < 0 ? 0 : nk - NST; j < nk; ++j) mbar_wait(bar_s + B_KFULL + 8 * kst(j), kpar(j));
-        for (int j = nv - NST < 0 ? 0 : nv - NST; j < nv; ++j) mbar_wait(bar_s + B_VFULL + 8 * kst(j), kpar(j));
-      }
+      if (lds_u32(failed_s) != 0u)
+        for (int j = issued - NST < 0 ? 0 : issued - NST; j < issued; ++j) mbar_wait(bar_s + B_KFULL + 8 * kst(j), kpar(j));
     }
     __syncwarp();
   } else if (!STAGED && warp >= 4) {
@@ -447,17 +487,22 @@ tq_prefill_tc_kernel(PrefillArgs a) {
     const uint32_t t_lane = ((uint32_t)(warp * 32)) << 16;
     float m_ref = -CUDART_INF_F;
     bool ok = true;
+#ifdef PT_PROFILE
+    long long acc_[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    long long tprev_ = clock64();
+#endif
     for (int j = 0; j < n_ktiles && ok; ++j) {
       const uint32_t st = (uint32_t)(j & 1);
+      PT_T(0);
       if (!wait_warp(bar_s + B_SFULL + 8 * st, par2(j))) { ok = false; break; }
+      PT_T(1);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       uint32_t v0[32], v1[32];
       tmem_ld32(tmem_base + t_lane + st * 64, v0);
       tmem_ld32(tmem_base + t_lane + st * 64 + 32, v1);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) pt_arrive(bar_s + B_SFREE + 8 * st);
+      PT_T(2);
       // causal limit, maximum (the key norms are inside the K operand)
       const int vis = lim - PT_KT * j;            // keys of this tile the row may see (<= 0: none, >= 64: all)
       if (vis < PT_KT) {
@@ -493,23 +538,33 @@ tq_prefill_tc_kernel(PrefillArgs a) {
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         }
       }
+      PT_T(3);
       const float ref = m_ref == -CUDART_INF_F ? 0.f : m_ref;
       uint32_t ph[32];                            // probabilities as fp16 pairs: keys 2i, 2i + 1
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
+#ifdef PT_EXP_SKIP
+        ph[i] = v0[2 * i] & 0x3C003C00u; ph[16 + i] = v1[2 * i] & 0x3C003C00u;
+#else
         ph[i] = pt_pack_half2(pt_ex2(__uint_as_float(v0[2 * i]) - ref), pt_ex2(__uint_as_float(v0[2 * i + 1]) - ref));
         ph[16 + i] = pt_pack_half2(pt_ex2(__uint_as_float(v1[2 * i]) - ref), pt_ex2(__uint_as_float(v1[2 * i + 1]) - ref));
+#endif
       }
-      // P buffer of this stage: free once P V of tile j-2 is complete
-      if (j >= 2 && !wait_warp(bar_s + B_PVDONE + 8 * st, par2(j - 2))) { ok = false; break; }
-      const uint32_t prow = base_s + PT_P + st * PT_STAGE + (uint32_t)r * 128u;
-#pragma unroll
-      for (int c = 0; c < 8; ++c)
-        pt_sts128(prow + (((uint32_t)c ^ (uint32_t)(r & 7)) << 4), ph[4 * c], ph[4 * c + 1], ph[4 * c + 2], ph[4 * c + 3]);
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      PT_T(4);
+      // P buffer (j & 1) is free: P V of tile j-2 was issued before the scores of tile j, the tensor cores work in issue
+      // order, and this tile's s_full - a commit - completes only when everything issued before it has
+      PT_T(5);
+      // the probabilities go to tensor memory as the A operand of P V: the thread's lane, 32 columns of fp16 pairs
+      tmem_st32(tmem_p + t_lane + st * 32, ph);
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) pt_arrive(bar_s + B_PFULL + 8 * st);
+      PT_T(6);
     }
+#ifdef PT_PROFILE
+    if ((blockIdx.x | blockIdx.y) == 0 && tid == 0) for (int i = 0; i < 8; ++i) g_pt_prof[32 + i] = acc_[i];
+#endif
     // ---- un-normalised rows for the merge kernel ----
     if (ok && wait_warp(bar_s + B_PVDONE + 8 * (uint32_t)((n_ktiles - 1) & 1), par2(n_ktiles - 1))) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -622,6 +677,13 @@ tq_prefill_stage_kernel(PrefillArgs a) {
 }
 
 }  // namespace
+
+#ifdef PT_PROFILE
+extern "C" __attribute__((visibility("default"))) int akv_debug_prefill_profile(long long* out) {
+  cudaDeviceSynchronize();
+  return (int)cudaMemcpyFromSymbol(out, g_pt_prof, sizeof(long long) * 64);
+}
+#endif
 
 int prefill_tc_status(int* host_out, int reset) {
   cudaError_t e = cudaMemcpyFromSymbol(host_out, g_prefill_tc_status, sizeof(int));
