@@ -2808,7 +2808,7 @@ AKV_EXPORT int akv_tq_prefill_attn(const akv_tq_prefill_params* p) {
     const size_t staged_off = (total + 1023) & ~(size_t)1023;
     if (staged != 0 && p->workspace_bytes >= staged_off + staged && (reinterpret_cast<uintptr_t>(ws) & 15) == 0) {
       a.staged = reinterpret_cast<uint8_t*>(ws + staged_off);
-      a.tiles_per_seq = (p->max_seq_len + 63) / 64;
+      a.tiles_per_seq = (p->max_seq_len + prefill_staged_tile_keys() - 1) / prefill_staged_tile_keys();
     }
     if (int rc = launch_prefill_tc(a, G, st)) return rc;
   } else {

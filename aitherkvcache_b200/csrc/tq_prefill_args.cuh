@@ -19,7 +19,7 @@ struct PrefillArgs {
   const float* centroids;
   float* part_acc;                     // [n_tokens * num_q_heads][128]
   float* part_ml;                      // [n_tokens * num_q_heads][2]
-  // staged variant of the tensor-core kernel: [num_seqs][tiles_per_seq][num_kv_heads] operand images of 32 KB, or null
+  // staged variant of the tensor-core kernel: [num_seqs][tiles_per_seq][num_kv_heads] operand images (512 B per key), or null
   uint8_t* staged;
   int tiles_per_seq;
 };
@@ -31,6 +31,7 @@ struct PrefillArgs {
 // attention kernel is fed by bulk copies instead of decoding the codes itself.
 int launch_prefill_tc(const PrefillArgs& a, int G, cudaStream_t st);
 size_t prefill_staged_bytes(int num_seqs, int num_kv_heads, int max_seq_len);
+int prefill_staged_tile_keys();
 int prefill_tc_status(int* host_out, int reset);
 int prefill_tc_withhold(int tile);
 

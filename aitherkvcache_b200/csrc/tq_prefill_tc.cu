@@ -44,29 +44,37 @@ __device__ long long g_pt_prof[64];
 __device__ int g_prefill_tc_status;          // 1: a bounded wait gave up, 2: tensor-memory columns were kept
 __device__ int g_prefill_tc_withhold = -1;   // test hook: CTA (0, 0) issues neither the score MMAs nor the commit of this tile
 
-constexpr int PT_KT = 64;                            // keys per tile
-constexpr int PT_STAGE = 16384;                      // one operand stage: 64 x 128 or 128 x 64 fp16
-constexpr int PT_VSTAGE = 144 * 128;                 // value stage: 128 dims + the row of ones (+ 15 zero rows) x 64 keys
-constexpr int PT_IMAGE = 2 * PT_STAGE;               // a staged tile in global memory: K operand image, then V operand image
+constexpr int PT_VHALF = 144 * 128;                  // 64 keys of a value operand: 128 dims + the row of ones (+ 15 zero rows)
 
-// Shared-memory layout and warp roles of the two variants: codes decoded in the kernel (13 warps, two operand stages, the
-// lookup table) or operand images staged in global memory by tq_prefill_stage_kernel (6 warps, three stages fed by bulk copies).
+// Shared-memory layout and warp roles of the two variants: codes decoded in the kernel (13 warps, tiles of 64 keys, two
+// operand stages, the lookup table) or operand images staged in global memory by tq_prefill_stage_kernel (6 warps, tiles
+// of 128 keys - half as many MMA instructions per key -, three stages fed by bulk copies).
 template <bool STAGED> struct PtL {
-  static constexpr int NST = STAGED ? 4 : 2;          // K / V operand stages (the barrier block has room for four)
+  static constexpr int KT = STAGED ? 128 : 64;        // keys per tile
+  static constexpr int NST = STAGED ? 3 : 2;          // K / V operand stages (the barrier block has room for four)
   static_assert(NST <= 4, "barrier slots");
   static constexpr int WARPS = STAGED ? 6 : 13;
   static constexpr int THREADS = WARPS * 32;
   static constexpr int MMA_WARP = STAGED ? 4 : 12;
-  static constexpr int K = 0;                         // B of S: NST x [64 keys][128 dims], two halves of 64 rows
-  static constexpr int V = K + NST * PT_STAGE;        // B of PV: NST x [144 rows][64 keys]
-  static constexpr int LUT = V + NST * PT_VSTAGE;     // byte -> half2, one copy per lane (256 x 128 B); not staged only
+  static constexpr int KHALF = KT * 128;              // 64 dims of a key operand: KT rows x 128 B
+  static constexpr int KSTAGE = 2 * KHALF;            // B of S: [KT keys][128 dims], two halves of 64 dims
+  static constexpr int VSTAGE = (KT / 64) * PT_VHALF; // B of PV: [144 rows][KT keys], one half per 64 keys
+  static constexpr int K = 0;
+  static constexpr int V = K + NST * KSTAGE;
+  static constexpr int LUT = V + NST * VSTAGE;        // byte -> half2, one copy per lane (256 x 128 B); not staged only
   static constexpr int BAR = LUT + (STAGED ? 0 : 32768);      // mbarriers, tensor-memory slot, failed flag
   static constexpr int SMEM = BAR + 256 + 1024;       // + slack for the 1024-byte alignment
+  // tensor memory (512 columns): S stage s at column KT s - its first KT / 2 columns are reused for the fp16 P of the same
+  // tile -, O at 2 KT (144 columns, column 128 = row sum), Q (64 columns of fp16 pairs) behind it
+  static constexpr int T_O = 2 * KT, T_Q = 2 * KT + 160;
+  static_assert(T_Q + 64 <= 512, "tensor memory");
 };
+constexpr int PS_KT = PtL<true>::KT;                 // keys per staged tile
+constexpr int PT_IMAGE = PS_KT * 512;                // a staged tile in global memory: K operand image, then V operand halves
 // barrier slots (8 bytes each; up to four operand stages)
 constexpr uint32_t B_KFULL = 0, B_VFULL = 32, B_SFULL = 64, B_PFULL = 96, B_PVDONE = 112,
                    B_VFREE = 160, B_DRAIN = 192, B_TMEM = 200, B_FAILED = 204;
-constexpr int PT_TMEM_COLS = 512;                    // S stages at columns 0 and 64, O at 128..271 (column 256 = row sum)
+constexpr int PT_TMEM_COLS = 512;
 constexpr float PT_RESCALE = 8.0f;                   // log2 units the row maximum may grow before O is rescaled
 
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
@@ -108,12 +116,14 @@ __device__ __forceinline__ void pt_arrive(uint32_t bar) {
 
 // K operand rows: thread (key kr, chunk kc) turns its 16 packed bytes (32 dims) into four 16-byte pieces of row kr, times
 // the key norm.  Words 2, 3 first for the upper chunks: the eight threads of a quarter warp then store to eight
-// different bank groups.  `stage` is the shared address of a [64 keys][128 dims] operand (two halves of 64 rows).
-__device__ __forceinline__ void pt_decode_k(uint32_t stage, uint32_t lut, int kr, int kc, const uint4& kw, float kn) {
+// different bank groups.  `stage` is the shared address of a [keys][128 dims] operand: two halves of 64 dims,
+// `half_stride` bytes apart; the key is row row0 + kr.
+__device__ __forceinline__ void pt_decode_k(uint32_t stage, uint32_t half_stride, int row0, uint32_t lut, int kr, int kc,
+                                            const uint4& kw, float kn) {
   const uint32_t hi = (uint32_t)(kc >> 1);
   const __half2 knh = __float2half2_rn(kn);
   const uint32_t ws[4] = {hi ? kw.z : kw.x, hi ? kw.w : kw.y, hi ? kw.x : kw.z, hi ? kw.y : kw.w};
-  const uint32_t row = stage + hi * 8192u + (uint32_t)kr * 128u;
+  const uint32_t row = stage + hi * half_stride + (uint32_t)(row0 + kr) * 128u;     // row0 is a multiple of 8
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     uint32_t h[4];
@@ -169,7 +179,7 @@ __global__ void __launch_bounds__(PtL<STAGED>::THREADS, 1)
 tq_prefill_tc_kernel(PrefillArgs a) {
   using L = PtL<STAGED>;
   constexpr int PT_THREADS = L::THREADS, PT_K = L::K, PT_V = L::V, PT_LUT = L::LUT, PT_BAR = L::BAR;
-  constexpr int NST = L::NST;
+  constexpr int NST = L::NST, PT_KT = L::KT, PT_STAGE = L::KSTAGE, PT_VSTAGE = L::VSTAGE;
   static_assert(G == 1 || G == 2 || G == 4 || G == 8, "query heads per KV head");
   constexpr int TT = 128 / G;           // query tokens of a CTA
   extern __shared__ uint8_t pt_smem_raw[];
@@ -229,19 +239,17 @@ tq_prefill_tc_kernel(PrefillArgs a) {
   }
   if constexpr (!STAGED) pt_fill_lut(base + PT_LUT, a.centroids, tid, PT_THREADS);
   // rows 128..143 of both value stages: a row of ones (output column 128 becomes the row sum of P) and zero rows
-  for (int e = tid; e < NST * 16 * 8; e += PT_THREADS) {
-    const int stg = e >> 7, r = (e >> 3) & 15, c = e & 7;
+  for (int e = tid; e < NST * (PT_KT / 64) * 16 * 8; e += PT_THREADS) {
+    const int half = e >> 7, r = (e >> 3) & 15, c = e & 7;         // the halves of all stages lie back to back
     const uint32_t v = r == 0 ? 0x3C003C00u : 0u;
-    *reinterpret_cast<uint4*>(base + PT_V + stg * PT_VSTAGE + (128 + r) * 128 + c * 16) = make_uint4(v, v, v, v);
+    *reinterpret_cast<uint4*>(base + PT_V + half * PT_VHALF + (128 + r) * 128 + c * 16) = make_uint4(v, v, v, v);
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = lds_u32(bar_s + B_TMEM);
-  const uint32_t tmem_o = tmem_base + 128;                  // S stage s at column 64 s, O at columns 128..271
-  const uint32_t tmem_p = tmem_base + 288;                  // P buffer s at columns 288 + 32 s: 64 fp16 probabilities per row
-  const uint32_t tmem_q = tmem_base + 352;                  // Q: 128 fp16 coordinates per row in 64 columns
+  const uint32_t tmem_o = tmem_base + L::T_O, tmem_q = tmem_base + L::T_Q;
   // A operand of S: the CTA's query rows, row r = (token tok_lo + r / G, head r % G), zeros for rows without a token;
   // thread r of the softmax warps writes its row into its lane of tensor memory
   if (warp < 4) {
@@ -290,8 +298,8 @@ tq_prefill_tc_kernel(PrefillArgs a) {
   if (warp == L::MMA_WARP) {
     // ================= MMA warp =================
     if (lane == 0) {
-      // D = f32, A / B = f16, both K-major; N = 64 (scores) or 128 (values), M = 128
-      constexpr uint32_t IDESC_S = (1u << 4) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
+      // D = f32, A / B = f16, B K-major; N = keys per tile (scores) or 144 (values), M = 128
+      constexpr uint32_t IDESC_S = (1u << 4) | (((uint32_t)PT_KT >> 3) << 17) | ((128u >> 4) << 24);
       constexpr uint32_t IDESC_O = (1u << 4) | ((144u >> 3) << 17) | ((128u >> 4) << 24);
       const int withhold = (blockIdx.x | blockIdx.y) == 0 ? g_prefill_tc_withhold : -1;
 #ifdef PT_PROFILE
@@ -314,7 +322,7 @@ tq_prefill_tc_kernel(PrefillArgs a) {
         const uint32_t kb = k_lo + ks * PT_STAGE;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_f16_ta(tmem_base + st * 64, tmem_q + (uint32_t)(kk * 8), desc(kb + (uint32_t)((kk >> 2) * 8192 + (kk & 3) * 32)),
+          umma_f16_ta(tmem_base + st * PT_KT, tmem_q + (uint32_t)(kk * 8), desc(kb + (uint32_t)((kk >> 2) * L::KHALF + (kk & 3) * 32)),
                       IDESC_S, (uint32_t)(kk != 0));
         umma_commit(bar_s + B_SFULL + 8 * st);
         PT_T(2);
@@ -331,8 +339,9 @@ tq_prefill_tc_kernel(PrefillArgs a) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t vb = v_lo + ks * PT_VSTAGE;
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_f16_ta(tmem_o, tmem_p + st * 32 + (uint32_t)(kk * 8), desc(vb + (uint32_t)(kk * 32)), IDESC_O, (uint32_t)((j | kk) != 0));
+        for (int kk = 0; kk < PT_KT / 16; ++kk)      // P of the tile: fp16 pairs in the first columns of its S stage
+          umma_f16_ta(tmem_o, tmem_base + st * PT_KT + (uint32_t)(kk * 8), desc(vb + (uint32_t)((kk >> 2) * PT_VHALF + (kk & 3) * 32)),
+                      IDESC_O, (uint32_t)((j | kk) != 0));
         umma_commit(bar_s + B_PVDONE + 8 * st);
         if constexpr (STAGED) umma_commit(bar_s + B_VFREE + 8 * ks);
         PT_T(5);
@@ -359,11 +368,14 @@ tq_prefill_tc_kernel(PrefillArgs a) {
         const uint32_t ks = kst(j);
         // P V of tile j - NST complete: its value stage is free, and so is its key stage (the scores came first)
         if (j >= NST && !wait(bar_s + B_VFREE + 8 * ks, kpar(j - NST))) break;
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar_s + B_KFULL + 8 * ks), "r"(2 * PT_STAGE) : "memory");
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar_s + B_KFULL + 8 * ks), "r"(PT_IMAGE) : "memory");
         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                      :: "r"(base_s + PT_K + ks * PT_STAGE), "l"(src + j * step), "r"(PT_STAGE), "r"(bar_s + B_KFULL + 8 * ks) : "memory");
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                     :: "r"(base_s + PT_V + ks * PT_VSTAGE), "l"(src + j * step + PT_STAGE), "r"(PT_STAGE), "r"(bar_s + B_KFULL + 8 * ks) : "memory");
+#pragma unroll
+        for (int h = 0; h < PT_KT / 64; ++h)       // the value halves leave room for their rows of ones in shared memory
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                       :: "r"(base_s + PT_V + ks * PT_VSTAGE + h * PT_VHALF), "l"(src + j * step + PT_STAGE + h * 16384), "r"(16384),
+                          "r"(bar_s + B_KFULL + 8 * ks) : "memory");
         issued = j + 1;
       }
       // a CTA that gives up must not leave while copies into its shared memory are in flight: the last copies of every
@@ -460,7 +472,7 @@ tq_prefill_tc_kernel(PrefillArgs a) {
       posv_nx = pos_v;
       // ---- K operand of tile j: free once the scores of tile j-2 are complete ----
       if (j >= 2 && !wait_warp(bar_s + B_SFULL + 8 * st, par2(j - 2))) return false;
-      pt_decode_k(base_s + PT_K + st * PT_STAGE, lut, kr, kc, kw, kn);
+      pt_decode_k(base_s + PT_K + st * PT_STAGE, L::KHALF, 0, lut, kr, kc, kw, kn);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) pt_arrive(bar_s + B_KFULL + 8 * st);
@@ -497,24 +509,21 @@ tq_prefill_tc_kernel(PrefillArgs a) {
       if (!wait_warp(bar_s + B_SFULL + 8 * st, par2(j))) { ok = false; break; }
       PT_T(1);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      uint32_t v0[32], v1[32];
-      tmem_ld32(tmem_base + t_lane + st * 64, v0);
-      tmem_ld32(tmem_base + t_lane + st * 64 + 32, v1);
+      uint32_t v[PT_KT];
+#pragma unroll
+      for (int c = 0; c < PT_KT / 32; ++c) tmem_ld32(tmem_base + t_lane + st * PT_KT + 32 * c, *reinterpret_cast<uint32_t (*)[32]>(&v[32 * c]));
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       PT_T(2);
       // causal limit, maximum (the key norms are inside the K operand)
-      const int vis = lim - PT_KT * j;            // keys of this tile the row may see (<= 0: none, >= 64: all)
+      const int vis = lim - PT_KT * j;            // keys of this tile the row may see (<= 0: none, >= PT_KT: all)
       if (vis < PT_KT) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          v0[i] = i < vis ? v0[i] : 0xff800000u;
-          v1[i] = i + 32 < vis ? v1[i] : 0xff800000u;
-        }
+        for (int i = 0; i < PT_KT; ++i) v[i] = i < vis ? v[i] : 0xff800000u;
       }
       float mx = -CUDART_INF_F;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(v0[i]), __uint_as_float(v1[i])));
+      for (int i = 0; i < PT_KT; i += 2) mx = fmaxf(mx, fmaxf(__uint_as_float(v[i]), __uint_as_float(v[i + 1])));
       // the reference maximum moves only when the row maximum has grown by more than PT_RESCALE; tcgen05.ld / st are
       // warp-wide, so the rows of a warp rescale together (factor 1 for rows that keep their reference).  Column 128
       // of O is the row sum and is rescaled with the rest.
@@ -540,22 +549,20 @@ tq_prefill_tc_kernel(PrefillArgs a) {
       }
       PT_T(3);
       const float ref = m_ref == -CUDART_INF_F ? 0.f : m_ref;
-      uint32_t ph[32];                            // probabilities as fp16 pairs: keys 2i, 2i + 1
+      // probabilities as fp16 pairs (keys 2i, 2i + 1) into the first columns of the S stage they came from: the A
+      // operand of P V.  P V of tile j-2, the last reader of these columns, was issued before the scores of tile j; the
+      // tensor cores work in issue order, and this tile's s_full - a commit - completes only when everything issued
+      // before it has.
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-#ifdef PT_EXP_SKIP
-        ph[i] = v0[2 * i] & 0x3C003C00u; ph[16 + i] = v1[2 * i] & 0x3C003C00u;
-#else
-        ph[i] = pt_pack_half2(pt_ex2(__uint_as_float(v0[2 * i]) - ref), pt_ex2(__uint_as_float(v0[2 * i + 1]) - ref));
-        ph[16 + i] = pt_pack_half2(pt_ex2(__uint_as_float(v1[2 * i]) - ref), pt_ex2(__uint_as_float(v1[2 * i + 1]) - ref));
-#endif
+      for (int c = 0; c < PT_KT / 64; ++c) {
+        uint32_t ph[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          ph[i] = pt_pack_half2(pt_ex2(__uint_as_float(v[64 * c + 2 * i]) - ref), pt_ex2(__uint_as_float(v[64 * c + 2 * i + 1]) - ref));
+        tmem_st32(tmem_base + t_lane + st * PT_KT + 32 * c, ph);
       }
       PT_T(4);
-      // P buffer (j & 1) is free: P V of tile j-2 was issued before the scores of tile j, the tensor cores work in issue
-      // order, and this tile's s_full - a commit - completes only when everything issued before it has
       PT_T(5);
-      // the probabilities go to tensor memory as the A operand of P V: the thread's lane, 32 columns of fp16 pairs
-      tmem_st32(tmem_p + t_lane + st * 32, ph);
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
@@ -608,19 +615,20 @@ tq_prefill_tc_kernel(PrefillArgs a) {
   }
 }
 
-// Pre-pass of the staged variant: every 64-key tile of every sequence and KV head becomes the 32 KB pair of operand
-// images (K rows, transposed V rows, norms folded in, keys past the sequence zero) that tq_prefill_tc_kernel<G, true>
-// pulls into shared memory with two bulk copies.  A CTA takes PS_TILES consecutive tiles of one (sequence, KV head).
-constexpr int PS_THREADS = 256, PS_TILES = 4, PS_SMEM = 32768 + PT_IMAGE;
+// Pre-pass of the staged variant: every 128-key tile of every sequence and KV head becomes the 64 KB set of operand
+// images (K rows, then the transposed V rows of its two 64-key halves; norms folded in, keys past the sequence zero)
+// that tq_prefill_tc_kernel<G, true> pulls into shared memory with three bulk copies.  A CTA takes PS_TILES consecutive
+// tiles of one (sequence, KV head) and decodes a tile in two passes of 64 keys.
+constexpr int PS_THREADS = 256, PS_TILES = 2, PS_SMEM = 32768 + PT_IMAGE;
 
-__global__ void __launch_bounds__(PS_THREADS, 3)
+__global__ void __launch_bounds__(PS_THREADS, 2)
 tq_prefill_stage_kernel(PrefillArgs a) {
   extern __shared__ __align__(128) uint8_t ps_smem[];
   const int tid = threadIdx.x, lane = tid & 31;
   const int s = blockIdx.y, kvh = blockIdx.z;
   const int64_t max_ctx = (int64_t)a.max_blocks_per_seq * a.block_size;
   const int seq_len = (int)load_ctx(a.seq_lens, a.sl_dtype, s, max_ctx);
-  int n_tiles = (seq_len + PT_KT - 1) / PT_KT;
+  int n_tiles = (seq_len + PS_KT - 1) / PS_KT;
   if (n_tiles > a.tiles_per_seq) n_tiles = a.tiles_per_seq;
   const int t_begin = blockIdx.x * PS_TILES;
   if (t_begin >= n_tiles) return;
@@ -638,31 +646,34 @@ tq_prefill_stage_kernel(PrefillArgs a) {
     return pb < 0 ? 0 : (pb >= a.num_blocks ? a.num_blocks - 1 : pb);
   };
   for (int t = t_begin; t < t_end; ++t) {
-    uint4 kw;
-    float kn;
-    uint32_t vw[8];
-    float vn[8];
-    {
-      const int key = PT_KT * t + kr;
-      const int64_t pb = phys(key);
-      const int pos = key - (key / bs) * bs;
-      kw = __ldg(reinterpret_cast<const uint4*>(a.k_packed + pb * a.kp_sb + (int64_t)pos * a.kp_sp + (int64_t)kvh * a.kp_sh + kc * 16));
-      kn = key < seq_len ? __ldg(a.k_norms + pb * a.kn_sb + (int64_t)pos * a.kn_sp + (int64_t)kvh * a.kn_sh) : 0.f;
-    }
-    {
-      const int key8 = PT_KT * t + 8 * kg;
-      const int64_t pb = phys(key8);
-      const int pos8 = key8 - (key8 / bs) * bs;
-      const uint8_t* vp = a.v_packed + pb * a.vp_sb + (int64_t)pos8 * a.vp_sp + (int64_t)kvh * a.vp_sh + vbyte;
-      const float* np = a.v_norms + pb * a.vn_sb + (int64_t)pos8 * a.vn_sp + (int64_t)kvh * a.vn_sh;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        vw[i] = (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(vp + (int64_t)i * a.vp_sp));
-        vn[i] = key8 + i < seq_len ? __ldg(np + (int64_t)i * a.vn_sp) : 0.f;
+#pragma unroll 1
+    for (int u = 0; u < PS_KT / 64; ++u) {       // 64 keys at a time with the thread roles of the decode warps
+      uint4 kw;
+      float kn;
+      uint32_t vw[8];
+      float vn[8];
+      {
+        const int key = PS_KT * t + 64 * u + kr;
+        const int64_t pb = phys(key);
+        const int pos = key - (key / bs) * bs;
+        kw = __ldg(reinterpret_cast<const uint4*>(a.k_packed + pb * a.kp_sb + (int64_t)pos * a.kp_sp + (int64_t)kvh * a.kp_sh + kc * 16));
+        kn = key < seq_len ? __ldg(a.k_norms + pb * a.kn_sb + (int64_t)pos * a.kn_sp + (int64_t)kvh * a.kn_sh) : 0.f;
       }
+      {
+        const int key8 = PS_KT * t + 64 * u + 8 * kg;
+        const int64_t pb = phys(key8);
+        const int pos8 = key8 - (key8 / bs) * bs;
+        const uint8_t* vp = a.v_packed + pb * a.vp_sb + (int64_t)pos8 * a.vp_sp + (int64_t)kvh * a.vp_sh + vbyte;
+        const float* np = a.v_norms + pb * a.vn_sb + (int64_t)pos8 * a.vn_sp + (int64_t)kvh * a.vn_sh;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          vw[i] = (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(vp + (int64_t)i * a.vp_sp));
+          vn[i] = key8 + i < seq_len ? __ldg(np + (int64_t)i * a.vn_sp) : 0.f;
+        }
+      }
+      pt_decode_k(img, PtL<true>::KHALF, 64 * u, lut, kr, kc, kw, kn);
+      pt_decode_v(img + PtL<true>::KSTAGE + u * 16384, lut, kg, vbyte, vw, vn);
     }
-    pt_decode_k(img, lut, kr, kc, kw, kn);
-    pt_decode_v(img + PT_STAGE, lut, kg, vbyte, vw, vn);
     __syncthreads();
     uint4* dst = reinterpret_cast<uint4*>(a.staged + (((int64_t)s * a.tiles_per_seq + t) * a.num_kv_heads + kvh) * PT_IMAGE);
 #pragma unroll
@@ -696,6 +707,8 @@ int prefill_tc_withhold(int tile) {
   return e == cudaSuccess ? AKV_OK : fail((int)e, "prefill test hook: %s", cudaGetErrorString(e));
 }
 
+int prefill_staged_tile_keys() { return PS_KT; }
+
 int launch_prefill_tc(const PrefillArgs& a, int G, cudaStream_t st) {
   const int TT = 128 / G;
   dim3 grid((a.n_tokens + TT - 1) / TT + a.num_seqs, a.num_kv_heads);
@@ -723,7 +736,7 @@ int launch_prefill_tc(const PrefillArgs& a, int G, cudaStream_t st) {
 
 size_t prefill_staged_bytes(int num_seqs, int num_kv_heads, int max_seq_len) {
   if (num_seqs <= 0 || num_kv_heads <= 0 || max_seq_len <= 0) return 0;
-  return (size_t)num_seqs * (size_t)((max_seq_len + PT_KT - 1) / PT_KT) * (size_t)num_kv_heads * PT_IMAGE;
+  return (size_t)num_seqs * (size_t)((max_seq_len + PS_KT - 1) / PS_KT) * (size_t)num_kv_heads * PT_IMAGE;
 }
 
 }  // namespace akv
