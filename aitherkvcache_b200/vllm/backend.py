@@ -179,7 +179,8 @@ class TurboQuantImplBase:
             _LayerState.attention[key_] = attn
         kn, vn = self._norms(getattr(layer, "layer_name", "layer"), kv_cache)
         res = attn.prefill(q, kv_cache[:, 0, :, :, :pd], kn, kv_cache[:, 1, :, :, :pd], vn, md.block_table, md.seq_lens,
-                           md.query_start_loc, block_size=bs, num_kv_heads=self.num_kv_heads, out=out, scale=self.scale)
+                           md.query_start_loc, block_size=bs, num_kv_heads=self.num_kv_heads, out=out, scale=self.scale,
+                           max_seq_len=getattr(md, "max_seq_len", None))      # host-side bound from vLLM's metadata: staged kernel
         return res is not None
 
     def forward(self, layer, query, key, value, kv_cache, attn_metadata, output=None, output_scale=None,

@@ -393,13 +393,16 @@ def secondary_kernels(steps, warmup, dev):
     sl = torch.tensor([past + chunk], dtype=torch.int32, device=dev)
     qsl = torch.tensor([0, chunk], dtype=torch.int32, device=dev)
     outp = torch.empty_like(qp)
-    if attn.prefill(qp, kp, kn, vp, vn, pbt, sl, qsl, block_size=BS, num_kv_heads=H_KV, out=outp) is None:
-        raise RuntimeError("the chunked-prefill kernel refused the benchmark shape")
-    ms = _event_time(lambda: attn.prefill(qp, kp, kn, vp, vn, pbt, sl, qsl, block_size=BS, num_kv_heads=H_KV, out=outp),
-                     max(3, steps // 8), 2)
     pairs = chunk * past + chunk * (chunk + 1) // 2            # (query token, key) pairs under the causal mask
-    res["tq4_chunked_prefill"] = {"ms": ms, "query_tokens": chunk, "past_tokens": past,
-                                  "TFLOP/s": pairs * H_Q * D * 4 / ms / 1e9, "query-tokens/s": chunk / ms * 1e3}
+    # "staged": the longest sequence is known on the host (as in vLLM's metadata), so the codes become fp16 operand images
+    # once per call; "in_kernel": they are decoded inside the attention kernel, once per 128 query rows
+    for name, msl in (("tq4_chunked_prefill", past + chunk), ("tq4_chunked_prefill_in_kernel_decode", None)):
+        if attn.prefill(qp, kp, kn, vp, vn, pbt, sl, qsl, block_size=BS, num_kv_heads=H_KV, out=outp, max_seq_len=msl) is None:
+            raise RuntimeError("the chunked-prefill kernel refused the benchmark shape")
+        ms = _event_time(lambda: attn.prefill(qp, kp, kn, vp, vn, pbt, sl, qsl, block_size=BS, num_kv_heads=H_KV, out=outp,
+                                              max_seq_len=msl), max(3, steps // 8), 2)
+        res[name] = {"ms": ms, "query_tokens": chunk, "past_tokens": past,
+                     "TFLOP/s": pairs * H_Q * D * 4 / ms / 1e9, "query-tokens/s": chunk / ms * 1e3}
     htq = HybridTurboQuant(D, "tq35", device=str(dev))
     htq.calibrate_uniform()
     xh = torch.randn(8 * 4096 * 8, D, generator=g, device=dev).half()

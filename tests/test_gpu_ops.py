@@ -292,7 +292,8 @@ def test_backend_mixed_batch_attends_over_the_packed_cache():
     nq = sum(qlens)
     qry = torch.randn(nq, QH * 128, generator=gen).half()
     qsl = torch.tensor([0, 50, 51, 111], dtype=torch.int32, device="cuda")
-    md = types.SimpleNamespace(num_actual_tokens=nq, max_query_len=max(qlens), block_table=bt.cuda(),
+    # max_seq_len as vLLM's metadata carries it: the prefill kernel may then stage its operand images
+    md = types.SimpleNamespace(num_actual_tokens=nq, max_query_len=max(qlens), block_table=bt.cuda(), max_seq_len=max(lens),
                                seq_lens=torch.tensor(lens, dtype=torch.int32, device="cuda"), query_start_loc=qsl)
     out = torch.zeros(nq, QH * 128, dtype=torch.float16, device="cuda")
     impl.forward(layer, qry.cuda(), None, None, kv, md, output=out)
