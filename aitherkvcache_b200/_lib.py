@@ -231,6 +231,9 @@ def lib() -> C.CDLL:
     return _lib
 
 
+AKV_ERR_ARG, AKV_ERR_UNSUPPORTED, AKV_ERR_WORKSPACE = -1, -2, -3
+
+
 class AkvError(RuntimeError):
     pass
 

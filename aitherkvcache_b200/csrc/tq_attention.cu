@@ -2746,11 +2746,13 @@ AKV_EXPORT int akv_tq_prefill_attn(const akv_tq_prefill_params* p) {
   auto al16 = [](const void* q, int64_t a, int64_t b, int64_t c) {
     return ((reinterpret_cast<uintptr_t>(q) | (uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) == 0;
   };
-  if (p->head_dim != 128 || p->bits != 4 || (G != 1 && G != 2 && G != 4 && G != 8) || p->block_size % 16 != 0 ||
-      !al16(p->k_packed, p->kp_stride_blk, p->kp_stride_pos, p->kp_stride_head) ||
-      !al16(p->v_packed, p->vp_stride_blk, p->vp_stride_pos, p->vp_stride_head))
-    return fail(AKV_ERR_UNSUPPORTED, "prefill attention is built for head_dim 128, 4-bit codes, 1/2/4/8 query heads per KV "
-                                     "head, block sizes that are multiples of 16 and caches readable in 16-byte pieces");
+  const bool low_bits = p->bits == 3 || p->bits == 2;      // served by the staged tensor-core kernel only
+  if (p->head_dim != 128 || (p->bits != 4 && !low_bits) || (G != 1 && G != 2 && G != 4 && G != 8) || p->block_size % 16 != 0 ||
+      (!low_bits && (!al16(p->k_packed, p->kp_stride_blk, p->kp_stride_pos, p->kp_stride_head) ||
+                     !al16(p->v_packed, p->vp_stride_blk, p->vp_stride_pos, p->vp_stride_head))))
+    return fail(AKV_ERR_UNSUPPORTED, "prefill attention is built for head_dim 128, 1/2/4/8 query heads per KV head, block sizes "
+                                     "that are multiples of 16 and 4-bit caches readable in 16-byte pieces (3- and 2-bit "
+                                     "caches: staged kernel only)");
   if (p->num_tokens == 0 || p->num_seqs == 0) return AKV_OK;
   if (!p->query || !p->k_packed || !p->v_packed || !p->k_norms || !p->v_norms || !p->block_tables || !p->seq_lens ||
       !p->query_start_loc || !p->rotation || !p->rotation_t || !p->centroids || !p->out)
@@ -2765,6 +2767,21 @@ AKV_EXPORT int akv_tq_prefill_attn(const akv_tq_prefill_params* p) {
   float* part_ml = reinterpret_cast<float*>(ws + off_ml);
   cudaStream_t st = (cudaStream_t)p->stream;
   const int rows = p->num_tokens * p->num_q_heads;
+  // tcgen05 kernel (128 rows per CTA) when its row tiles would be at least half full - chunks of prefill tokens, not a
+  // batch of single decode tokens (the host cannot see query_start_loc: a sequence adds at most one ragged tile);
+  // AKV_PREFILL_TC=0 / 1 forces one or the other
+  static const char* tc_env = getenv("AKV_PREFILL_TC");
+  const int64_t tc_rows = (int64_t)p->num_tokens * G;
+  const int64_t tc_tiles = (tc_rows + 127) / 128 + p->num_seqs - 1;
+  const bool use_tc = tc_env ? tc_env[0] == '1' : tc_rows >= 64 * tc_tiles;
+  // 3- and 2-bit caches: only the staged tensor-core kernel reads them; say so before anything is launched
+  {
+    static const bool no_staged_env = getenv("AKV_PREFILL_STAGED") != nullptr && getenv("AKV_PREFILL_STAGED")[0] == '0';
+    const size_t need = prefill_staged_bytes(p->num_seqs, p->num_kv_heads, p->max_seq_len);
+    if (low_bits && (!use_tc || no_staged_env || need == 0 || p->workspace_bytes < ((total + 1023) & ~(size_t)1023) + need))
+      return fail(AKV_ERR_UNSUPPORTED, "prefill attention over 3- / 2-bit codes needs a chunk that fills 128-row tiles, "
+                                       "max_seq_len and the staged workspace");
+  }
   {   // rotated, scaled queries of every token
     const size_t smem128 = (size_t)ROT128_MAT_BYTES + 4 * 128 * sizeof(float);
     cudaError_t e = cudaFuncSetAttribute(akv_qrot128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem128);
@@ -2792,13 +2809,6 @@ AKV_EXPORT int akv_tq_prefill_attn(const akv_tq_prefill_params* p) {
   a.num_seqs = p->num_seqs; a.n_tokens = p->num_tokens; a.num_q_heads = p->num_q_heads; a.num_kv_heads = p->num_kv_heads;
   a.block_size = p->block_size; a.max_blocks_per_seq = p->max_blocks_per_seq; a.num_blocks = p->num_blocks;
   a.centroids = p->centroids; a.part_acc = part_acc; a.part_ml = part_ml;
-  // tcgen05 kernel (128 rows per CTA) when its row tiles would be at least half full - chunks of prefill tokens, not a
-  // batch of single decode tokens (the host cannot see query_start_loc: a sequence adds at most one ragged tile);
-  // AKV_PREFILL_TC=0 / 1 forces one or the other
-  static const char* tc_env = getenv("AKV_PREFILL_TC");
-  const int64_t tc_rows = (int64_t)p->num_tokens * G;
-  const int64_t tc_tiles = (tc_rows + 127) / 128 + p->num_seqs - 1;
-  const bool use_tc = tc_env ? tc_env[0] == '1' : tc_rows >= 64 * tc_tiles;
   if (use_tc) {
     // with the longest sequence known on the host and room in the workspace, the codes are turned into fp16 operand
     // images once (instead of once per row tile) and the tensor-core kernel is fed by bulk copies; AKV_PREFILL_STAGED=0
@@ -2806,12 +2816,16 @@ AKV_EXPORT int akv_tq_prefill_attn(const akv_tq_prefill_params* p) {
     static const bool no_staged = getenv("AKV_PREFILL_STAGED") != nullptr && getenv("AKV_PREFILL_STAGED")[0] == '0';
     const size_t staged = no_staged ? 0 : prefill_staged_bytes(p->num_seqs, p->num_kv_heads, p->max_seq_len);
     const size_t staged_off = (total + 1023) & ~(size_t)1023;
+    a.bits = p->bits;
     if (staged != 0 && p->workspace_bytes >= staged_off + staged && (reinterpret_cast<uintptr_t>(ws) & 15) == 0) {
       a.staged = reinterpret_cast<uint8_t*>(ws + staged_off);
       a.tiles_per_seq = (p->max_seq_len + prefill_staged_tile_keys() - 1) / prefill_staged_tile_keys();
     }
+    if (low_bits && a.staged == nullptr)
+      return fail(AKV_ERR_UNSUPPORTED, "prefill attention over 3- / 2-bit codes needs max_seq_len and the staged workspace");
     if (int rc = launch_prefill_tc(a, G, st)) return rc;
   } else {
+  if (low_bits) return fail(AKV_ERR_UNSUPPORTED, "prefill attention over 3- / 2-bit codes: chunk too ragged for the staged kernel");
   const int TT = 64 / G;
   dim3 grid((p->num_tokens + TT - 1) / TT + p->num_seqs, p->num_kv_heads);
   cudaError_t e = cudaSuccess;

@@ -22,6 +22,7 @@ struct PrefillArgs {
   // staged variant of the tensor-core kernel: [num_seqs][tiles_per_seq][num_kv_heads] operand images (512 B per key), or null
   uint8_t* staged;
   int tiles_per_seq;
+  int bits;                            // 4; 3 or 2 only with staged images
 };
 
 // tcgen05 kernel (tq_prefill_tc.cu): one CTA per 128 (token, query head) rows and KV head.  Returns AKV_OK after

@@ -35,12 +35,6 @@
 namespace akv {
 namespace {
 
-#ifdef PT_PROFILE
-__device__ long long g_pt_prof[64];
-#define PT_T(i) do { const long long now_ = clock64(); acc_[i] += now_ - tprev_; tprev_ = now_; } while (0)
-#else
-#define PT_T(i)
-#endif
 __device__ int g_prefill_tc_status;          // 1: a bounded wait gave up, 2: tensor-memory columns were kept
 __device__ int g_prefill_tc_withhold = -1;   // test hook: CTA (0, 0) issues neither the score MMAs nor the commit of this tile
 
@@ -302,10 +296,6 @@ tq_prefill_tc_kernel(PrefillArgs a) {
       constexpr uint32_t IDESC_S = (1u << 4) | (((uint32_t)PT_KT >> 3) << 17) | ((128u >> 4) << 24);
       constexpr uint32_t IDESC_O = (1u << 4) | ((144u >> 3) << 17) | ((128u >> 4) << 24);
       const int withhold = (blockIdx.x | blockIdx.y) == 0 ? g_prefill_tc_withhold : -1;
-#ifdef PT_PROFILE
-      long long acc_[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      long long tprev_ = clock64();
-#endif
       // Descriptors differ only in their 14-bit address field: one constant upper half, lower halves by 32-bit adds.
       const uint64_t d_hi = umma_desc(0u) & 0xffffffff00000000ull;
       const uint32_t d_lo = (uint32_t)umma_desc(0u);
@@ -316,7 +306,6 @@ tq_prefill_tc_kernel(PrefillArgs a) {
       auto issue_s = [&](int j) -> bool {
         const uint32_t st = (uint32_t)(j & 1), ks = kst(j);
         if (!wait(bar_s + B_KFULL + 8 * ks, kpar(j))) return false;
-        PT_T(0);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (j == withhold) return true;
         const uint32_t kb = k_lo + ks * PT_STAGE;
@@ -325,17 +314,14 @@ tq_prefill_tc_kernel(PrefillArgs a) {
           umma_f16_ta(tmem_base + st * PT_KT, tmem_q + (uint32_t)(kk * 8), desc(kb + (uint32_t)((kk >> 2) * L::KHALF + (kk & 3) * 32)),
                       IDESC_S, (uint32_t)(kk != 0));
         umma_commit(bar_s + B_SFULL + 8 * st);
-        PT_T(2);
         return true;
       };
       auto issue_pv = [&](int j) -> bool {
         const uint32_t st = (uint32_t)(j & 1), ks = kst(j);
         if (!wait(bar_s + B_PFULL + 8 * st, par2(j))) return false;
-        PT_T(3);
         if constexpr (!STAGED) {       // staged: the value image arrived on the same barrier as the key image
           if (!wait(bar_s + B_VFULL + 8 * ks, kpar(j))) return false;
         }
-        PT_T(4);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t vb = v_lo + ks * PT_VSTAGE;
 #pragma unroll
@@ -344,7 +330,6 @@ tq_prefill_tc_kernel(PrefillArgs a) {
                       IDESC_O, (uint32_t)((j | kk) != 0));
         umma_commit(bar_s + B_PVDONE + 8 * st);
         if constexpr (STAGED) umma_commit(bar_s + B_VFREE + 8 * ks);
-        PT_T(5);
         return true;
       };
       if (issue_s(0)) {
@@ -353,9 +338,6 @@ tq_prefill_tc_kernel(PrefillArgs a) {
           if (!issue_pv(j)) break;
         }
       }
-#ifdef PT_PROFILE
-      if ((blockIdx.x | blockIdx.y) == 0) for (int i = 0; i < 8; ++i) g_pt_prof[i] = acc_[i];
-#endif
     }
     __syncwarp();
   } else if (STAGED && warp == 5) {
@@ -499,22 +481,15 @@ tq_prefill_tc_kernel(PrefillArgs a) {
     const uint32_t t_lane = ((uint32_t)(warp * 32)) << 16;
     float m_ref = -CUDART_INF_F;
     bool ok = true;
-#ifdef PT_PROFILE
-    long long acc_[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    long long tprev_ = clock64();
-#endif
     for (int j = 0; j < n_ktiles && ok; ++j) {
       const uint32_t st = (uint32_t)(j & 1);
-      PT_T(0);
       if (!wait_warp(bar_s + B_SFULL + 8 * st, par2(j))) { ok = false; break; }
-      PT_T(1);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       uint32_t v[PT_KT];
 #pragma unroll
       for (int c = 0; c < PT_KT / 32; ++c) tmem_ld32(tmem_base + t_lane + st * PT_KT + 32 * c, *reinterpret_cast<uint32_t (*)[32]>(&v[32 * c]));
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      PT_T(2);
       // causal limit, maximum (the key norms are inside the K operand)
       const int vis = lim - PT_KT * j;            // keys of this tile the row may see (<= 0: none, >= PT_KT: all)
       if (vis < PT_KT) {
@@ -547,7 +522,6 @@ tq_prefill_tc_kernel(PrefillArgs a) {
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         }
       }
-      PT_T(3);
       const float ref = m_ref == -CUDART_INF_F ? 0.f : m_ref;
       // probabilities as fp16 pairs (keys 2i, 2i + 1) into the first columns of the S stage they came from: the A
       // operand of P V.  P V of tile j-2, the last reader of these columns, was issued before the scores of tile j; the
@@ -561,17 +535,11 @@ tq_prefill_tc_kernel(PrefillArgs a) {
           ph[i] = pt_pack_half2(pt_ex2(__uint_as_float(v[64 * c + 2 * i]) - ref), pt_ex2(__uint_as_float(v[64 * c + 2 * i + 1]) - ref));
         tmem_st32(tmem_base + t_lane + st * PT_KT + 32 * c, ph);
       }
-      PT_T(4);
-      PT_T(5);
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) pt_arrive(bar_s + B_PFULL + 8 * st);
-      PT_T(6);
     }
-#ifdef PT_PROFILE
-    if ((blockIdx.x | blockIdx.y) == 0 && tid == 0) for (int i = 0; i < 8; ++i) g_pt_prof[32 + i] = acc_[i];
-#endif
     // ---- un-normalised rows for the merge kernel ----
     if (ok && wait_warp(bar_s + B_PVDONE + 8 * (uint32_t)((n_ktiles - 1) & 1), par2(n_ktiles - 1))) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -687,14 +655,82 @@ tq_prefill_stage_kernel(PrefillArgs a) {
   }
 }
 
-}  // namespace
-
-#ifdef PT_PROFILE
-extern "C" __attribute__((visibility("default"))) int akv_debug_prefill_profile(long long* out) {
-  cudaDeviceSynchronize();
-  return (int)cudaMemcpyFromSymbol(out, g_pt_prof, sizeof(long long) * 64);
+// The same images from 3- and 2-bit codes (MSB-first streams of 48 / 32 bytes per key and head): nothing downstream
+// depends on the code width.  Plain code - the pre-pass is a few percent of a call: a thread turns 8 dims of one key
+// into one 16-byte piece of the K image, then 8 dims of 8 keys into eight pieces of the transposed V image.
+template <int BITS>
+__global__ void __launch_bounds__(PS_THREADS, 2)
+tq_prefill_stage_bits_kernel(PrefillArgs a) {
+  constexpr int CB = BITS;          // bytes per 8 codes
+  extern __shared__ __align__(128) uint8_t ps_smem[];
+  __shared__ float cent[1 << BITS];
+  const int tid = threadIdx.x;
+  const int s = blockIdx.y, kvh = blockIdx.z;
+  const int64_t max_ctx = (int64_t)a.max_blocks_per_seq * a.block_size;
+  const int seq_len = (int)load_ctx(a.seq_lens, a.sl_dtype, s, max_ctx);
+  int n_tiles = (seq_len + PS_KT - 1) / PS_KT;
+  if (n_tiles > a.tiles_per_seq) n_tiles = a.tiles_per_seq;
+  const int t_begin = blockIdx.x * PS_TILES;
+  if (t_begin >= n_tiles) return;
+  const int t_end = t_begin + PS_TILES < n_tiles ? t_begin + PS_TILES : n_tiles;
+  if (tid < (1 << BITS)) cent[tid] = a.centroids[tid];
+  __syncthreads();
+  const int bs = a.block_size;
+  auto phys = [&](int key) -> int64_t {
+    int blk = key / bs;
+    if (blk >= a.max_blocks_per_seq) blk = a.max_blocks_per_seq - 1;
+    const int64_t pb = load_index(a.block_tables, a.bt_dtype, (int64_t)s * a.bt_stride + blk);
+    return pb < 0 ? 0 : (pb >= a.num_blocks ? a.num_blocks - 1 : pb);
+  };
+  // eight codes = CB whole bytes -> eight centroids times the norm
+  auto decode8 = [&](const uint8_t* src, float norm, float (&out)[8]) {
+    uint32_t w = 0;
+#pragma unroll
+    for (int i = 0; i < CB; ++i) w = (w << 8) | src[i];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] = cent[(w >> (BITS * (7 - i))) & ((1u << BITS) - 1u)] * norm;
+  };
+  for (int t = t_begin; t < t_end; ++t) {
+    // K image: [half = dims 0..63 | 64..127][key][128 B], 16-byte chunk c of key r at chunk c ^ (r & 7)
+    for (int e = tid; e < PS_KT * 16; e += PS_THREADS) {
+      const int r = e >> 4, c = e & 15;
+      const int key = PS_KT * t + r;
+      const int64_t pb = phys(key);
+      const int pos = key - (key / bs) * bs;
+      const float norm = key < seq_len ? a.k_norms[pb * a.kn_sb + (int64_t)pos * a.kn_sp + (int64_t)kvh * a.kn_sh] : 0.f;
+      float v[8];
+      decode8(a.k_packed + pb * a.kp_sb + (int64_t)pos * a.kp_sp + (int64_t)kvh * a.kp_sh + c * CB, norm, v);
+      *reinterpret_cast<uint4*>(ps_smem + (c >> 3) * PtL<true>::KHALF + r * 128 + (((c & 7) ^ (r & 7)) << 4)) =
+          make_uint4(pt_pack_half2(v[0], v[1]), pt_pack_half2(v[2], v[3]), pt_pack_half2(v[4], v[5]), pt_pack_half2(v[6], v[7]));
+    }
+    // V image: [half = keys 0..63 | 64..127][dim][128 B], the chunk of key group g (8 keys) of dim d at chunk g ^ (d & 7)
+    for (int e = tid; e < (PS_KT / 8) * 16; e += PS_THREADS) {
+      const int g = e >> 4, c = e & 15;              // keys 8 g .. 8 g + 7, dims 8 c .. 8 c + 7
+      const int key8 = PS_KT * t + 8 * g;
+      const int64_t pb = phys(key8);
+      const int pos8 = key8 - (key8 / bs) * bs;
+      float v[8][8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float norm = key8 + i < seq_len ? a.v_norms[pb * a.vn_sb + (int64_t)(pos8 + i) * a.vn_sp + (int64_t)kvh * a.vn_sh] : 0.f;
+        decode8(a.v_packed + pb * a.vp_sb + (int64_t)(pos8 + i) * a.vp_sp + (int64_t)kvh * a.vp_sh + c * CB, norm, v[i]);
+      }
+#pragma unroll
+      for (int dd = 0; dd < 8; ++dd) {
+        const int d = 8 * c + dd;
+        *reinterpret_cast<uint4*>(ps_smem + PtL<true>::KSTAGE + (g >> 3) * 16384 + d * 128 + ((((g & 7) ^ (d & 7))) << 4)) =
+            make_uint4(pt_pack_half2(v[0][dd], v[1][dd]), pt_pack_half2(v[2][dd], v[3][dd]), pt_pack_half2(v[4][dd], v[5][dd]),
+                       pt_pack_half2(v[6][dd], v[7][dd]));
+      }
+    }
+    __syncthreads();
+    uint4* dst = reinterpret_cast<uint4*>(a.staged + (((int64_t)s * a.tiles_per_seq + t) * a.num_kv_heads + kvh) * PT_IMAGE);
+    for (int i = tid; i < PT_IMAGE / 16; i += PS_THREADS) dst[i] = reinterpret_cast<const uint4*>(ps_smem)[i];
+    __syncthreads();
+  }
 }
-#endif
+
+}  // namespace
 
 int prefill_tc_status(int* host_out, int reset) {
   cudaError_t e = cudaMemcpyFromSymbol(host_out, g_prefill_tc_status, sizeof(int));
@@ -715,10 +751,18 @@ int launch_prefill_tc(const PrefillArgs& a, int G, cudaStream_t st) {
   cudaError_t e = cudaSuccess;
   if (a.staged != nullptr) {
     // operand images first (ordered before the attention kernel by the stream), then the bulk-copy-fed kernel
-    e = cudaFuncSetAttribute(tq_prefill_stage_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PS_SMEM);
-    if (e != cudaSuccess) return fail((int)e, "prefill attention: smem attribute: %s", cudaGetErrorString(e));
     dim3 sgrid((a.tiles_per_seq + PS_TILES - 1) / PS_TILES, a.num_seqs, a.num_kv_heads);
-    tq_prefill_stage_kernel<<<sgrid, PS_THREADS, PS_SMEM, st>>>(a);
+    if (a.bits == 4) {
+      e = cudaFuncSetAttribute(tq_prefill_stage_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PS_SMEM);
+      if (e == cudaSuccess) tq_prefill_stage_kernel<<<sgrid, PS_THREADS, PS_SMEM, st>>>(a);
+    } else if (a.bits == 3) {
+      e = cudaFuncSetAttribute(tq_prefill_stage_bits_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, PT_IMAGE);
+      if (e == cudaSuccess) tq_prefill_stage_bits_kernel<3><<<sgrid, PS_THREADS, PT_IMAGE, st>>>(a);
+    } else {
+      e = cudaFuncSetAttribute(tq_prefill_stage_bits_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PT_IMAGE);
+      if (e == cudaSuccess) tq_prefill_stage_bits_kernel<2><<<sgrid, PS_THREADS, PT_IMAGE, st>>>(a);
+    }
+    if (e != cudaSuccess) return fail((int)e, "prefill attention: smem attribute: %s", cudaGetErrorString(e));
     if (int rc = check_launch("tq_prefill_stage_kernel")) return rc;
   }
 #define AKV_PT(GG, ST)                                                                                                  \

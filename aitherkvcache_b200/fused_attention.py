@@ -128,8 +128,10 @@ class TQPagedAttention:
         n_tok, num_q_heads, head_dim = query.shape
         G = num_q_heads // num_kv_heads
         aligned = all((t.data_ptr() | t.stride(0) | t.stride(1) | t.stride(2)) % 16 == 0 for t in (k_packed, v_packed))
-        if (self.bits != 4 or head_dim != 128 or G not in (1, 2, 4, 8) or block_size % 16 or not aligned
+        if (head_dim != 128 or G not in (1, 2, 4, 8) or block_size % 16 or (self.bits == 4 and not aligned)
                 or k_norms.dtype != torch.float32 or v_norms.dtype != torch.float32):
+            return None
+        if self.bits != 4 and not max_seq_len:      # 3- and 2-bit codes: staged tensor-core kernel only
             return None
         assert num_q_heads == self.num_query_heads and k_packed.shape[1] == block_size
         num_seqs = query_start_loc.numel() - 1
@@ -173,6 +175,8 @@ class TQPagedAttention:
         p.max_seq_len = int(max_seq_len) if max_seq_len else 0
         with torch.cuda.device(dev):
             rc = L.akv_tq_prefill_attn(ctypes.byref(p))
+        if rc == _lib.AKV_ERR_UNSUPPORTED:          # e.g. a ragged batch of 3-bit sequences: nothing was launched
+            return None
         _lib.check(rc, "akv_tq_prefill_attn")
         return out
 

@@ -167,9 +167,10 @@ class TurboQuantImplBase:
                      out=out, scale=self.scale)
 
     def _prefill(self, layer, q, out, kv_cache, md) -> bool:
-        """Prefill chunks and mixed batches through the chunked-prefill kernel (the query tokens of a sequence share
-        one pass over its packed blocks); False when that kernel is not built for the layout (3- / 2-bit codes,
-        68-byte rows), in which case every token becomes a row of the decode kernels."""
+        """Prefill chunks and mixed batches through the chunked-prefill kernels (the query tokens of a sequence share
+        one pass over its packed blocks); False when they are not built for the case (3- / 2-bit codes in a batch too
+        ragged for the staged tensor-core kernel, rows that are not readable in 16-byte pieces), in which case every
+        token becomes a row of the decode kernels."""
         pd, bs = self.packed_dim, kv_cache.shape[2]
         key_ = (self.head_size, self.tq_codec, self.tq_bits, self.num_heads, str(kv_cache.device))
         attn = _LayerState.attention.get(key_)

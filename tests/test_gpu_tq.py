@@ -779,3 +779,44 @@ def test_prefill_tensor_core_kernel_bounded_wait_gives_up_and_reports():
     again = attn.prefill(query, kp, kn, vp, vn, bt, sl, qsl, block_size=bs, num_kv_heads=H)
     assert torch.equal(again, good)
     assert not any(_lib.device_status().values())
+
+
+@pytest.mark.parametrize("bits", (3, 2))
+def test_chunked_prefill_low_bit_caches_through_staged_images(bits):
+    """3- and 2-bit caches in chunked prefill: the pre-pass turns their codes into the same fp16 operand images, the
+    tensor-core kernel does not know the difference.  Against the decode kernels row by row and the oracle on one row."""
+    g = load_golden(f"tq_d128_b{bits}.npz")
+    tq = _tq(128, bits, g)
+    H, QH, bs = 4, 16, 16
+    attn = _attn(tq, QH)
+    gen = torch.Generator().manual_seed(300 + bits)
+    seqs = [(700, 90), (0, 150), (257, 64)]            # (cached before the chunk, chunk length)
+    lens = [p + q for p, q in seqs]
+    nblk = [(n + bs - 1) // bs for n in lens]
+    total = sum(nblk) + 1
+    perm = torch.randperm(total, generator=gen)
+    bt = torch.zeros(len(seqs), max(nblk), dtype=torch.int32)
+    o = 0
+    for s_, n in enumerate(nblk):
+        bt[s_, :n] = perm[o:o + n].to(torch.int32)
+        o += n
+    kp, kn = tq.encode(torch.randn(total, bs, H, 128, generator=gen).half().cuda())
+    vp, vn = tq.encode(torch.randn(total, bs, H, 128, generator=gen).half().cuda())
+    nq = sum(q for _, q in seqs)
+    qsl = torch.tensor([0] + list(np.cumsum([q for _, q in seqs])), dtype=torch.int32)
+    query = torch.randn(nq, QH, 128, generator=gen).half().cuda()
+    sl = torch.tensor(lens, dtype=torch.int32).cuda()
+    assert attn.prefill(query, kp, kn, vp, vn, bt.cuda(), sl, qsl.cuda(), block_size=bs, num_kv_heads=H) is None   # no bound, no scratch
+    out = attn.prefill(query, kp, kn, vp, vn, bt.cuda(), sl, qsl.cuda(), block_size=bs, num_kv_heads=H, max_seq_len=max(lens))
+    assert out is not None
+    from aitherkvcache_b200 import _lib
+    assert _lib.lib().akv_last_split_kernel() == b"tq_prefill_attn_tc_staged_kernel"
+    rows_bt = torch.cat([bt[s_:s_ + 1].expand(q, -1) for s_, (_, q) in enumerate(seqs)])
+    rows_ctx = torch.cat([torch.arange(p + 1, p + q + 1) for p, q in seqs]).to(torch.int32)
+    ref = attn.forward(query, kp, kn, vp, vn, rows_bt.contiguous().cuda(), rows_ctx.cuda(), block_size=bs, num_kv_heads=H)
+    assert (out.float() - ref.float()).abs().max().item() < 2e-3
+    row = int(qsl[1]) - 1                              # last token of the first chunk
+    want = otq.paged_attention_decode_sdpa(query[row:row + 1].cpu().numpy(), kp.cpu().numpy(), kn.cpu().numpy(),
+                                           vp.cpu().numpy(), vn.cpu().numpy(), bt[0:1].numpy(), np.asarray([lens[0]]),
+                                           g["rotation"], g["centroids"], bits, 1.0 / math.sqrt(128), bs)
+    assert np.abs(out[row].float().cpu().numpy() - want[0]).max() < 2e-3
