@@ -20,6 +20,7 @@ classes are created on first attribute access so that importing this module does
 from __future__ import annotations
 
 import inspect
+import types
 import os
 from typing import Dict, Optional, Tuple
 
@@ -184,6 +185,32 @@ class TurboQuantImplBase:
                            max_seq_len=getattr(md, "max_seq_len", None))      # host-side bound from vLLM's metadata: staged kernel
         return res is not None
 
+    def _mixed(self, layer, q, out, kv_cache, md, n) -> bool:
+        """A batch with chunks: the sequences that contribute more than one token go through the chunked-prefill kernels,
+        the single-token ones through the decode kernels, which stream a context once per sequence instead of once per
+        mostly empty row tile.  The split is made on the device (no host copy of ``query_start_loc``): each side sees a
+        length of zero for the other side's sequences and returns at once for them."""
+        qsl, seq_lens = md.query_start_loc, md.seq_lens
+        num_seqs = qsl.numel() - 1
+        if n == num_seqs * md.max_query_len:       # every sequence brings max_query_len > 1 tokens: no decode side
+            return self._prefill(layer, q, out, kv_cache, md)
+        qlen = qsl[1:] - qsl[:-1]
+        single = qlen == 1
+        zero = torch.zeros_like(seq_lens[:num_seqs])
+        chunk_md = types.SimpleNamespace(block_table=md.block_table, query_start_loc=qsl,
+                                         seq_lens=torch.where(single, zero, seq_lens[:num_seqs]),
+                                         max_seq_len=getattr(md, "max_seq_len", None))
+        if not self._prefill(layer, q, out, kv_cache, chunk_md):
+            return False
+        rows = qsl[:-1].long().clamp_(max=n - 1)                      # the one query row of a single-token sequence
+        dec_out = torch.empty(num_seqs, self.num_heads, self.head_size, dtype=out.dtype, device=out.device)
+        self._attend(layer, q.index_select(0, rows), dec_out, kv_cache, md.block_table,
+                     torch.where(single, seq_lens[:num_seqs], zero))
+        # rows of the other sequences are written back unchanged (a sequence without tokens would share its row index
+        # with its neighbour; vLLM schedules no such sequence)
+        out.index_copy_(0, rows, torch.where(single[:, None, None], dec_out, out.index_select(0, rows)))
+        return True
+
     def forward(self, layer, query, key, value, kv_cache, attn_metadata, output=None, output_scale=None,
                 output_block_scale=None):
         if output is None:
@@ -196,7 +223,7 @@ class TurboQuantImplBase:
         if attn_metadata.max_query_len == 1:      # one token per sequence: rows are the sequences
             self._attend(layer, q, out, kv_cache, attn_metadata.block_table, attn_metadata.seq_lens)
             return output
-        if self.tq_codec == "uniform" and self._prefill(layer, q, out, kv_cache, attn_metadata):
+        if self.tq_codec == "uniform" and self._mixed(layer, q, out, kv_cache, attn_metadata, n):
             return output
         bt, ctx = token_rows(attn_metadata.query_start_loc, attn_metadata.seq_lens, attn_metadata.block_table, n)
         # the split-K workspace grows with the number of rows of a call: a chunk goes through in slices
