@@ -89,6 +89,12 @@ int tc_encode_status(int* host_out, int reset);
 int tc_decode_status(int* host_out, int reset);
 int attn_window_status(int* host_out, int reset);
 int tri_status(int* host_out, int reset);
+// rot_rows.cu: out[r] = scale * (src[r] / l_r) M for many rows at once (tensor cores, float32 accuracy); row r = (r / inner, r % inner)
+bool rot_rows_ok(const void* src, int src_dtype, int64_t src_outer, int64_t src_inner, const void* out, int out_dtype,
+                 int64_t out_outer, int64_t out_inner);
+int launch_rot_rows(const void* src, int src_dtype, int64_t src_outer, int64_t src_inner, int inner, const float* inv_l,
+                    int64_t inv_stride, const float* mat, float scale, void* out, int out_dtype, int64_t out_outer,
+                    int64_t out_inner, int64_t rows, cudaStream_t st);
 int prefill_tc_status(int* host_out, int reset);
 int prefill_tc_withhold(int tile);
 int hybrid_window_status(int* host_out, int reset);

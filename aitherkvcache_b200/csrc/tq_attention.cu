@@ -2782,7 +2782,18 @@ AKV_EXPORT int akv_tq_prefill_attn(const akv_tq_prefill_params* p) {
       return fail(AKV_ERR_UNSUPPORTED, "prefill attention over 3- / 2-bit codes needs a chunk that fills 128-row tiles, "
                                        "max_seq_len and the staged workspace");
   }
-  {   // rotated, scaled queries of every token
+  // Many rows: both rotations are [rows, 128] x [128, 128] products on the tensor cores (rot_rows.cu); a few rows: the
+  // kernels of the decode path
+  const bool gemm_q = rows >= 1024 && rot_rows_ok(p->query, p->q_dtype, p->q_stride_tok, p->q_stride_head, qrot, AKV_F32,
+                                                    (int64_t)p->num_q_heads * 128, 128);
+  const bool gemm_o = rows >= 1024 && rot_rows_ok(part_acc, AKV_F32, (int64_t)p->num_q_heads * 128, 128, p->out, p->out_dtype,
+                                                    p->out_stride_tok, p->out_stride_head);
+  if (gemm_q) {
+    if (int rc = launch_rot_rows(p->query, p->q_dtype, p->q_stride_tok, p->q_stride_head, p->num_q_heads, nullptr, 0,
+                                 p->rotation_t, p->scale * 1.4426950408889634f, qrot, AKV_F32,
+                                 (int64_t)p->num_q_heads * 128, 128, rows, st))
+      return rc;
+  } else {   // rotated, scaled queries of every token
     const size_t smem128 = (size_t)ROT128_MAT_BYTES + 4 * 128 * sizeof(float);
     cudaError_t e = cudaFuncSetAttribute(akv_qrot128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem128);
     if (e != cudaSuccess) return fail((int)e, "prefill attention: smem attribute: %s", cudaGetErrorString(e));
@@ -2837,6 +2848,9 @@ AKV_EXPORT int akv_tq_prefill_attn(const akv_tq_prefill_params* p) {
   if (e != cudaSuccess) return fail((int)e, "prefill attention: smem attribute: %s", cudaGetErrorString(e));
   if (int rc = check_launch("tq_prefill_attn_kernel")) return rc;
   }
+  if (gemm_o)      // out = R^T (acc / l): one partial per row, nothing to merge
+    return launch_rot_rows(part_acc, AKV_F32, (int64_t)p->num_q_heads * 128, 128, p->num_q_heads, part_ml + 1, 2, p->rotation,
+                           1.0f, p->out, p->out_dtype, p->out_stride_tok, p->out_stride_head, rows, st);
   MergeArgs mg{};
   mg.acc = part_acc; mg.acc_row = 128; mg.acc_part = 128;
   mg.ml = part_ml; mg.ml_row = 2; mg.ml_part = 2;
