@@ -820,3 +820,31 @@ def test_chunked_prefill_low_bit_caches_through_staged_images(bits):
                                            vp.cpu().numpy(), vn.cpu().numpy(), bt[0:1].numpy(), np.asarray([lens[0]]),
                                            g["rotation"], g["centroids"], bits, 1.0 / math.sqrt(128), bs)
     assert np.abs(out[row].float().cpu().numpy() - want[0]).max() < 2e-3
+
+
+@pytest.mark.parametrize("staged", (False, True))
+@pytest.mark.parametrize("H,QH", ((4, 4), (2, 4), (1, 8)))
+def test_chunked_prefill_tensor_core_kernels_group_sizes(H, QH, staged):
+    """One and two query heads per KV head (128 and 64 query tokens per row tile) and eight (16 tokens) through both
+    tensor-core variants: one sequence whose chunk fills its row tiles, against the decode kernels row by row."""
+    g = load_golden("tq_d128_b4.npz")
+    tq = _tq(128, 4, g)
+    attn = _attn(tq, QH)
+    bs, past, chunk = 16, 100, 300
+    gen = torch.Generator().manual_seed(40 + H + QH)
+    n = past + chunk
+    nb = (n + bs - 1) // bs
+    bt = torch.randperm(nb + 3, generator=gen)[:nb].to(torch.int32).reshape(1, nb)
+    kp, kn = tq.encode(torch.randn(nb + 3, bs, H, 128, generator=gen).half().cuda())
+    vp, vn = tq.encode(torch.randn(nb + 3, bs, H, 128, generator=gen).half().cuda())
+    query = torch.randn(chunk, QH, 128, generator=gen).half().cuda()
+    sl = torch.tensor([n], dtype=torch.int32).cuda()
+    qsl = torch.tensor([0, chunk], dtype=torch.int32).cuda()
+    out = attn.prefill(query, kp, kn, vp, vn, bt.cuda(), sl, qsl, block_size=bs, num_kv_heads=H, max_seq_len=n if staged else None)
+    assert out is not None
+    from aitherkvcache_b200 import _lib
+    assert _lib.lib().akv_last_split_kernel() == (b"tq_prefill_attn_tc_staged_kernel" if staged else b"tq_prefill_attn_tc_kernel")
+    ref = attn.forward(query, kp, kn, vp, vn, bt.expand(chunk, -1).contiguous().cuda(),
+                       torch.arange(past + 1, n + 1, dtype=torch.int32).cuda(), block_size=bs, num_kv_heads=H)
+    assert (out.float() - ref.float()).abs().max().item() < 2e-3
+    assert not any(_lib.device_status().values())
