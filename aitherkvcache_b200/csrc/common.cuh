@@ -156,6 +156,9 @@ struct MergeArgs {
   // written earlier in the stream) says which, half_stride floats apart
   const unsigned int* half_select;
   int64_t half_stride;
+  // optional float32 [rows][128] scratch: with it, MERGE_ROTATE of 2048+ rows normalises into the scratch and rotates
+  // all rows as one tensor-core product (rot_rows.cu) instead of one matrix-vector product per row
+  float* gemm_scratch;
 };
 
 __device__ __forceinline__ int64_t merge_half_offset(const MergeArgs& a) {

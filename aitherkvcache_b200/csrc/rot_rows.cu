@@ -8,7 +8,9 @@
 // out of fp16's subnormal range), a float32 source row into two fp16 terms as well, and the product is accumulated as
 // a1 M1 + a1 M2 + a2 M1 in float32 (the dropped a2 M2 term is 2^-22 of the result).  A 16-bit source needs one term.
 // CTA = 8 warps = a tile of 128 rows (16 per warp), persistent over the tiles; both operands come from shared memory
-// (rows padded to 272 bytes: conflict-free 4-byte fragment loads).
+// (rows padded to 272 bytes: conflict-free 4-byte fragment loads).  With few row tiles the 128 output columns are
+// split over 2 or 4 CTAs (gridDim.y), each staging and using only its columns of the matrix, so that a call of a
+// few thousand rows still spreads over the GPU.
 #include "common.cuh"
 
 namespace akv {
@@ -35,6 +37,7 @@ __device__ __forceinline__ void rr_mma(float (&d)[4], uint32_t a0, uint32_t a1, 
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+template <int NJ>        // n-tiles (8 columns each) of this CTA: 16, 8 or 4
 __global__ void __launch_bounds__(RR_THREADS, 1)
 akv_rot_rows_kernel(RotRowsArgs a) {
   extern __shared__ __align__(16) unsigned char rr_smem[];
@@ -43,21 +46,42 @@ akv_rot_rows_kernel(RotRowsArgs a) {
   __half* a1 = m2 + 128 * RR_LD;
   __half* a2 = a1 + 128 * RR_LD;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int j0 = blockIdx.y * (8 * NJ);          // first column of this CTA
 
   // B operand: element (k = i, n = j) is M[i][j]; stored as [j][i] so that a fragment register is two neighbouring i
-  for (int e = tid; e < 128 * 128; e += RR_THREADS) {
-    const int i = e >> 7, j = e & 127;
-    const float v = a.mat[e] * 1024.0f;
-    const __half h = __float2half_rn(v);
-    m1[j * RR_LD + i] = h;
-    m2[j * RR_LD + i] = __float2half_rn(v - __half2float(h));
+  // (128 x 8 NJ values as 16-byte loads, up to eight per thread in flight at a time; local column jl = j - j0)
+  constexpr int QUADS = 128 * 8 * NJ / 4, PER = QUADS / RR_THREADS;       // 16, 8 or 4 loads per thread
+#pragma unroll 1
+  for (int b = 0; b < PER; b += 8) {
+    float4 x[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (b + u < PER) {
+        const int qd = (b + u) * RR_THREADS + tid, i = qd / (2 * NJ), jl = (qd % (2 * NJ)) * 4;
+        x[u] = __ldg(reinterpret_cast<const float4*>(a.mat + i * 128 + j0 + jl));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (b + u < PER) {
+        const int qd = (b + u) * RR_THREADS + tid, i = qd / (2 * NJ), jl = (qd % (2 * NJ)) * 4;
+        const float v[4] = {x[u].x * 1024.0f, x[u].y * 1024.0f, x[u].z * 1024.0f, x[u].w * 1024.0f};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const __half h = __float2half_rn(v[q]);
+          m1[(jl + q) * RR_LD + i] = h;
+          m2[(jl + q) * RR_LD + i] = __float2half_rn(v[q] - __half2float(h));
+        }
+      }
+    }
   }
   const bool two_terms = a.src_dtype == AKV_F32;
   const float out_scale = a.scale * (1.0f / 1024.0f);
   const int64_t tiles = (a.rows + 127) >> 7;
   for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
     __syncthreads();                    // the matrix is in place; the previous tile's fragments have been read
-    // ---- A operand: 128 rows x 128, eight elements per thread and pass ----
+    // ---- A operand: 128 rows x 128, eight elements per thread and pass (eight passes, unrolled: loads in flight together) ----
+#pragma unroll
     for (int e = tid; e < 128 * 16; e += RR_THREADS) {
       const int r = e >> 4, c = e & 15;
       const int64_t row = tile * 128 + r;
@@ -105,9 +129,9 @@ akv_rot_rows_kernel(RotRowsArgs a) {
     }
     __syncthreads();
     // ---- warp: rows 16 warp .. 16 warp + 15, all 128 columns ----
-    float acc[16][4];
+    float acc[NJ][4];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    for (int j = 0; j < NJ; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
     const __half* ra1 = a1 + (16 * warp + g) * RR_LD + 2 * t;
     const __half* ra2 = a2 + (16 * warp + g) * RR_LD + 2 * t;
 #pragma unroll
@@ -120,7 +144,7 @@ akv_rot_rows_kernel(RotRowsArgs a) {
         y2 = *reinterpret_cast<const uint32_t*>(ra2 + 16 * kk + 8); y3 = *reinterpret_cast<const uint32_t*>(ra2 + 8 * RR_LD + 16 * kk + 8);
       }
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
+      for (int j = 0; j < NJ; ++j) {
         const __half* rb1 = m1 + (8 * j + g) * RR_LD + 16 * kk + 2 * t;
         const __half* rb2 = m2 + (8 * j + g) * RR_LD + 16 * kk + 2 * t;
         const uint32_t b0 = *reinterpret_cast<const uint32_t*>(rb1), b1 = *reinterpret_cast<const uint32_t*>(rb1 + 8);
@@ -135,9 +159,9 @@ akv_rot_rows_kernel(RotRowsArgs a) {
     for (int half = 0; half < 2; ++half) {
       const int64_t row = tile * 128 + 16 * warp + g + 8 * half;
       if (row >= a.rows) continue;
-      const int64_t off = (row / a.inner) * a.out_outer + (row % a.inner) * a.out_inner + 2 * t;
+      const int64_t off = (row / a.inner) * a.out_outer + (row % a.inner) * a.out_inner + j0 + 2 * t;
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
+      for (int j = 0; j < NJ; ++j) {
         const float lo = acc[j][2 * half] * out_scale, hi = acc[j][2 * half + 1] * out_scale;
         if (a.out_dtype == AKV_F32) {
           *reinterpret_cast<float2*>(reinterpret_cast<float*>(a.out) + off + 8 * j) = make_float2(lo, hi);
@@ -170,11 +194,22 @@ int launch_rot_rows(const void* src, int src_dtype, int64_t src_outer, int64_t s
   a.src = src; a.src_dtype = src_dtype; a.src_outer = src_outer; a.src_inner = src_inner; a.inner = inner;
   a.inv_l = inv_l; a.inv_stride = inv_stride; a.mat = mat; a.scale = scale;
   a.out = out; a.out_dtype = out_dtype; a.out_outer = out_outer; a.out_inner = out_inner; a.rows = rows;
-  cudaError_t e = cudaFuncSetAttribute(akv_rot_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RR_SMEM);
-  if (e != cudaSuccess) return fail((int)e, "row rotation: smem attribute: %s", cudaGetErrorString(e));
   const int64_t tiles = (rows + 127) / 128;
-  const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  akv_rot_rows_kernel<<<grid, RR_THREADS, RR_SMEM, st>>>(a);
+  const int split = 4 * tiles <= sm_count() ? 4 : (2 * tiles <= sm_count() ? 2 : 1);      // column split: CTAs <= SMs
+  const int per = sm_count() / split;
+  dim3 grid((unsigned)(tiles < per ? tiles : per), split);
+  cudaError_t e;
+  if (split == 4) {
+    e = cudaFuncSetAttribute(akv_rot_rows_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, RR_SMEM);
+    if (e == cudaSuccess) akv_rot_rows_kernel<4><<<grid, RR_THREADS, RR_SMEM, st>>>(a);
+  } else if (split == 2) {
+    e = cudaFuncSetAttribute(akv_rot_rows_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, RR_SMEM);
+    if (e == cudaSuccess) akv_rot_rows_kernel<8><<<grid, RR_THREADS, RR_SMEM, st>>>(a);
+  } else {
+    e = cudaFuncSetAttribute(akv_rot_rows_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, RR_SMEM);
+    if (e == cudaSuccess) akv_rot_rows_kernel<16><<<grid, RR_THREADS, RR_SMEM, st>>>(a);
+  }
+  if (e != cudaSuccess) return fail((int)e, "row rotation: smem attribute: %s", cudaGetErrorString(e));
   return check_launch("akv_rot_rows_kernel");
 }
 

@@ -460,6 +460,19 @@ akv_merge128_kernel(MergeArgs a, int rows, int np_alloc) {
 int launch_merge(const MergeArgs& a, int rows, cudaStream_t st, bool pdl) {
   const int np_alloc = a.np > 0 ? a.np : 1;
   static const bool no_rot128 = getenv("AKV_NO_ROT128") != nullptr;
+  static const bool no_rot_gemm = getenv("AKV_NO_ROT_GEMM") != nullptr;
+  if (a.D == 128 && a.mode == MERGE_ROTATE && a.gemm_scratch != nullptr && rows >= 2048 && !no_rot_gemm &&
+      rot_rows_ok(a.gemm_scratch, AKV_F32, (int64_t)a.num_q_heads * 128, 128, a.out, a.out_dtype, a.out_ss, a.out_sh)) {
+    MergeArgs n = a;                       // LSE merge and division only, float32 rows into the scratch ...
+    n.mode = MERGE_NORMALIZE;
+    n.out = a.gemm_scratch; n.out_dtype = AKV_F32; n.out_ss = (int64_t)a.num_q_heads * 128; n.out_sh = 128;
+    n.gemm_scratch = nullptr;
+    akv_merge_kernel<<<rows, 128, (128 + np_alloc) * sizeof(float), st>>>(n);
+    if (int rc = check_launch("akv_merge_kernel")) return rc;
+    // ... then out = R^T x for all rows at once
+    return launch_rot_rows(a.gemm_scratch, AKV_F32, (int64_t)a.num_q_heads * 128, 128, a.num_q_heads, nullptr, 0, a.rot, 1.0f,
+                           a.out, a.out_dtype, a.out_ss, a.out_sh, rows, st);
+  }
   const size_t smem128 = (size_t)ROT128_MAT_BYTES + (size_t)(4 * 128 + 4 * np_alloc + 8) * sizeof(float);
   if (a.D == 128 && a.mode == MERGE_ROTATE && !no_rot128 && rows > 0 && smem128 <= 200 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(akv_merge128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem128);
@@ -2434,16 +2447,30 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
   }
   const int plan_blocks = persist ? 1 : 0;
   static const bool no_rot128 = getenv("AKV_NO_ROT128") != nullptr;
+  // Large batches (2048+ rows; below that the per-row kernels are as fast): the query rotation is one tensor-core product over all rows (rot_rows.cu); the
+  // plan block and the new token's vectors keep their launch
+  static const bool no_rot_gemm = getenv("AKV_NO_ROT_GEMM") != nullptr;
+  const bool gemm_q = D == 128 && rows >= 2048 && !no_rot_gemm && !no_rot128 &&
+                      rot_rows_ok(p->query, p->q_dtype, p->q_stride_seq, p->q_stride_head, qrot, AKV_F32,
+                                  (int64_t)p->num_q_heads * 128, 128);
+  if (gemm_q) {
+    if (int rc = launch_rot_rows(p->query, p->q_dtype, p->q_stride_seq, p->q_stride_head, p->num_q_heads, nullptr, 0,
+                                 p->rotation_t, p->scale * 1.4426950408889634f, qrot, AKV_F32,
+                                 (int64_t)p->num_q_heads * 128, 128, rows, st))
+      return rc;
+  }
   if (D == 128 && !no_rot128) {            // rotation matrix staged in shared memory, four rows per CTA pass
     const size_t smem128 = (size_t)ROT128_MAT_BYTES + 4 * 128 * sizeof(float);
     cudaError_t e = cudaFuncSetAttribute(akv_qrot128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem128);
     if (e != cudaSuccess) return fail((int)e, "attention: smem attribute: %s", cudaGetErrorString(e));
-    const int quads = (rows + 3) / 4;
+    const int quads = gemm_q ? 0 : (rows + 3) / 4;
     const int rot_blocks = quads < 2 * sm_count() ? quads : 2 * sm_count();
-    akv_qrot128_kernel<<<rot_blocks + plan_blocks + (unsigned)(2 * nt.n_rows), ROT128_THREADS, smem128, st>>>(
-        p->query, p->q_dtype, p->q_stride_seq, p->q_stride_head, p->num_q_heads, p->rotation_t,
-        p->scale * 1.4426950408889634f, qrot, rows, rot_blocks, plan_blocks, pl, nt);
-    if (int rc = check_launch("akv_qrot128_kernel")) return rc;
+    if (rot_blocks + plan_blocks + (unsigned)(2 * nt.n_rows) > 0) {
+      akv_qrot128_kernel<<<rot_blocks + plan_blocks + (unsigned)(2 * nt.n_rows), ROT128_THREADS, smem128, st>>>(
+          p->query, p->q_dtype, p->q_stride_seq, p->q_stride_head, p->num_q_heads, p->rotation_t,
+          p->scale * 1.4426950408889634f, qrot, rows, rot_blocks, plan_blocks, pl, nt);
+      if (int rc = check_launch("akv_qrot128_kernel")) return rc;
+    }
   } else {
     const int qrot_threads = D < 128 ? D : 128;
     akv_qrot_kernel<<<rows + plan_blocks + (unsigned)(2 * nt.n_rows), qrot_threads, qrot_smem, st>>>(
@@ -2573,6 +2600,7 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
   mg.rot = p->rotation;
   mg.out = p->out; mg.out_dtype = p->out_dtype; mg.out_ss = p->out_stride_seq; mg.out_sh = p->out_stride_head;
   mg.raw_out = p->raw_out;
+  mg.gemm_scratch = qrot;        // the rotated queries are dead once the attention kernel has run
   return launch_merge(mg, rows, st, pdl && p->max_blocks_per_seq > 0);
 }
 
@@ -2784,9 +2812,9 @@ AKV_EXPORT int akv_tq_prefill_attn(const akv_tq_prefill_params* p) {
   }
   // Many rows: both rotations are [rows, 128] x [128, 128] products on the tensor cores (rot_rows.cu); a few rows: the
   // kernels of the decode path
-  const bool gemm_q = rows >= 1024 && rot_rows_ok(p->query, p->q_dtype, p->q_stride_tok, p->q_stride_head, qrot, AKV_F32,
+  const bool gemm_q = rows >= 2048 && rot_rows_ok(p->query, p->q_dtype, p->q_stride_tok, p->q_stride_head, qrot, AKV_F32,
                                                     (int64_t)p->num_q_heads * 128, 128);
-  const bool gemm_o = rows >= 1024 && rot_rows_ok(part_acc, AKV_F32, (int64_t)p->num_q_heads * 128, 128, p->out, p->out_dtype,
+  const bool gemm_o = rows >= 2048 && rot_rows_ok(part_acc, AKV_F32, (int64_t)p->num_q_heads * 128, 128, p->out, p->out_dtype,
                                                     p->out_stride_tok, p->out_stride_head);
   if (gemm_q) {
     if (int rc = launch_rot_rows(p->query, p->q_dtype, p->q_stride_tok, p->q_stride_head, p->num_q_heads, nullptr, 0,

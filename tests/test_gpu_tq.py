@@ -848,3 +848,26 @@ def test_chunked_prefill_tensor_core_kernels_group_sizes(H, QH, staged):
                        torch.arange(past + 1, n + 1, dtype=torch.int32).cuda(), block_size=bs, num_kv_heads=H)
     assert (out.float() - ref.float()).abs().max().item() < 2e-3
     assert not any(_lib.device_status().values())
+
+
+@pytest.mark.parametrize("dtype", (torch.float16, torch.bfloat16, torch.float32))
+def test_paged_attention_large_batch_rotations_as_one_product(dtype):
+    """From 2048 (sequence, query head) rows on, the query rotation and the final rotate-back are tensor-core products
+    over all rows (two-term fp16 split): 72 sequences x 32 heads against the oracle, for every query / output type."""
+    t = load_golden("tq_d128_b4.npz")
+    tq = _tq(128, 4, t)
+    H, QH = 8, 32
+    gen = np.random.default_rng(77)
+    ctx = [0, 1, 300] + [int(v) for v in gen.integers(1, 200, 69)]
+    d = make_paged_cache(4242, ctx, H, 128, 4, t["rotation"], t["boundaries"])
+    q = torch.randn(len(ctx), QH, 128, generator=torch.Generator().manual_seed(3)).to(dtype)
+    c = to_cuda(d, ["k_packed", "k_norms", "v_packed", "v_norms", "block_tables", "context_lens"])
+    out = _attn(tq, QH).forward(q.cuda(), c["k_packed"], c["k_norms"], c["v_packed"], c["v_norms"],
+                                c["block_tables"], c["context_lens"])
+    assert out.dtype == dtype
+    ref = otq.paged_attention_rotated(q.float().numpy(), d["k_packed"], d["k_norms"], d["v_packed"], d["v_norms"],
+                                      d["block_tables"], d["context_lens"], t["rotation"], t["centroids"], 4, 1.0 / math.sqrt(128))
+    out = out.float().cpu().numpy()
+    assert (out[0] == 0).all()
+    tol = 2e-3 if dtype != torch.bfloat16 else 2e-2
+    assert (np.abs(out - ref) <= tol * np.maximum(1.0, np.abs(ref))).all()
