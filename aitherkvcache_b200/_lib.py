@@ -68,6 +68,7 @@ class TQPrefillParams(C.Structure):
         ("workspace", c_vp), ("workspace_bytes", C.c_size_t),
         ("stream", c_vp),
         ("max_seq_len", c_int),
+        ("hybrid_tables", c_vp),
     ]
 
 

@@ -12,6 +12,7 @@
 // Record of one vector: [g0: codes | sign bits | fp16 norm | fp16 residual norm][g1: same]
 //   tq35 (d=128): 24+8+2+2 | 16+8+2+2 = 64 bytes;  tq25: 8+4+2+2 | 12+12+2+2 = 44 bytes.
 #include "common.cuh"
+#include "tq_prefill_args.cuh"
 #include <math_constants.h>
 #include <stdlib.h>
 
@@ -1875,6 +1876,98 @@ AKV_EXPORT int akv_hybrid_decode(const uint8_t* packed, int64_t packed_row_strid
   else
     hybrid_decode_kernel<32, 2, 96, 1><<<grid, HY_THREADS, 0, st>>>(packed, packed_row_stride, n_rows, t, out, out_dtype);
   return check_launch("hybrid_decode_kernel");
+}
+
+// ---------------------------------------------------------------------------
+// Pre-pass of the staged chunked-prefill kernel for tq35 caches (tq_prefill_tc.cu): every 128-key tile of every
+// sequence and KV head is decoded once - exactly as hybrid_decode35_coop_kernel decodes, four lanes per record - and
+// written as the fp16 operand images the tensor-core attention kernel copies into shared memory (layout: PFI_* in
+// tq_prefill_args.cuh).  The decoded vectors are in the original domain: that attention runs without rotations.
+// The reference decodes the active blocks to bf16 and calls vLLM's unified attention (vllm/hooks.py:726-850).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(HC_THREADS, 2)
+hybrid_prefill_stage35_kernel(PrefillArgs a, HybridTables t) {
+  extern __shared__ __align__(16) uint8_t hp_image[];            // PFI_BYTES
+  __shared__ uint32_t recs[32 * 17];
+  __shared__ __align__(16) float outs[32 * HD_ROW];
+  __shared__ float s_had[128], s_qjl[128], s_cent[16];
+  __shared__ int s_idx[128];
+  const int tid = threadIdx.x;
+  const int s = blockIdx.y, kvh = blockIdx.z, tile = blockIdx.x;
+  const int64_t max_ctx = (int64_t)a.max_blocks_per_seq * a.block_size;
+  const int seq_len = (int)load_ctx(a.seq_lens, a.sl_dtype, s, max_ctx);
+  int n_tiles = (seq_len + PFI_KEYS - 1) / PFI_KEYS;
+  if (n_tiles > a.tiles_per_seq) n_tiles = a.tiles_per_seq;
+  if (tile >= n_tiles) return;
+  const int* gsrc = t.group_index + (t.num_index_heads > 1 ? (kvh % t.num_index_heads) * 128 : 0);
+  if (tid < 128) { s_had[tid] = t.had_signs[tid]; s_qjl[tid] = t.qjl_signs[tid]; s_idx[tid] = gsrc[tid]; }
+  if (tid < 16) s_cent[tid] = t.centroids[tid];
+  const int bs = a.block_size;
+  for (int side = 0; side < 2; ++side) {
+    const uint8_t* cache = side ? a.v_packed : a.k_packed;
+    const int64_t sb = side ? a.vp_sb : a.kp_sb, sp = side ? a.vp_sp : a.kp_sp, sh = side ? a.vp_sh : a.kp_sh;
+    for (int pass = 0; pass < PFI_KEYS / 32; ++pass) {
+      __syncthreads();                 // tables staged; the previous pass's rows have been read
+      {   // 32 records x 16 words, one 16-byte piece per thread
+        const int r = tid >> 2, c = tid & 3;
+        const int key = PFI_KEYS * tile + 32 * pass + r;
+        int blk = key / bs;
+        if (blk >= a.max_blocks_per_seq) blk = a.max_blocks_per_seq - 1;
+        int64_t pb = load_index(a.block_tables, a.bt_dtype, (int64_t)s * a.bt_stride + blk);
+        pb = pb < 0 ? 0 : (pb >= a.num_blocks ? a.num_blocks - 1 : pb);
+        const uint4 v = *reinterpret_cast<const uint4*>(cache + pb * sb + (int64_t)(key - (key / bs) * bs) * sp + (int64_t)kvh * sh + c * 16);
+        uint32_t* d = recs + r * 17 + 4 * c;
+        d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
+      }
+      __syncthreads();
+      const int vec = tid >> 2, q = tid & 3;
+      hc_decode_group<3>(recs + vec * 17, s_idx, s_had, s_qjl, s_cent, t.qjl_scale0, q, outs + vec * HD_ROW);
+      hc_decode_group<2>(recs + vec * 17 + 9, s_idx + 64, s_had + 64, s_qjl + 64, s_cent + 8, t.qjl_scale1, q,
+                         outs + vec * HD_ROW);
+      __syncthreads();
+      const int key0 = PFI_KEYS * tile + 32 * pass;
+      if (side == 0) {
+        // K image: 32 rows x 16 chunks of 8 dims
+        for (int e = tid; e < 32 * 16; e += HC_THREADS) {
+          const int r = e >> 4, c = e & 15;
+          const bool live = key0 + r < seq_len;
+          const float4 x = *reinterpret_cast<const float4*>(outs + r * HD_ROW + 8 * c);
+          const float4 y = *reinterpret_cast<const float4*>(outs + r * HD_ROW + 8 * c + 4);
+          __half2 h[4] = {__floats2half2_rn(x.x, x.y), __floats2half2_rn(x.z, x.w), __floats2half2_rn(y.x, y.y), __floats2half2_rn(y.z, y.w)};
+          uint4 w = *reinterpret_cast<uint4*>(h);
+          if (!live) w = make_uint4(0u, 0u, 0u, 0u);
+          const int row = 32 * pass + r;
+          *reinterpret_cast<uint4*>(hp_image + (c >> 3) * PFI_KHALF + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = w;
+        }
+      } else {
+        // transposed V image: 4 key groups of 8 keys x 128 dims
+        for (int e = tid; e < 4 * 128; e += HC_THREADS) {
+          const int gl = e >> 7, d = e & 127;
+          float v[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = key0 + 8 * gl + i < seq_len ? outs[(8 * gl + i) * HD_ROW + d] : 0.f;
+          __half2 h[4] = {__floats2half2_rn(v[0], v[1]), __floats2half2_rn(v[2], v[3]), __floats2half2_rn(v[4], v[5]), __floats2half2_rn(v[6], v[7])};
+          const int g = 4 * pass + gl;
+          *reinterpret_cast<uint4*>(hp_image + PFI_VOFF + (g >> 3) * PFI_VHALF + d * 128 + (((g & 7) ^ (d & 7)) << 4)) =
+              *reinterpret_cast<uint4*>(h);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  uint4* dst = reinterpret_cast<uint4*>(a.staged + (((int64_t)s * a.tiles_per_seq + tile) * a.num_kv_heads + kvh) * PFI_BYTES);
+  for (int i = tid; i < PFI_BYTES / 16; i += HC_THREADS) dst[i] = reinterpret_cast<const uint4*>(hp_image)[i];
+}
+
+int akv::launch_hybrid_prefill_stage(const PrefillArgs& a, cudaStream_t st) {
+  HybridTables t; int mode;
+  if (int rc = tables_from(reinterpret_cast<const akv_hybrid_tables*>(a.hybrid_tables), &t, &mode)) return rc;
+  if (mode != 35) return fail(AKV_ERR_UNSUPPORTED, "staged prefill attention reads tq35 records only");
+  cudaError_t e = cudaFuncSetAttribute(hybrid_prefill_stage35_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PFI_BYTES);
+  if (e != cudaSuccess) return fail((int)e, "prefill attention: smem attribute: %s", cudaGetErrorString(e));
+  dim3 grid(a.tiles_per_seq, a.num_seqs, a.num_kv_heads);
+  hybrid_prefill_stage35_kernel<<<grid, HC_THREADS, PFI_BYTES, st>>>(a, t);
+  return check_launch("hybrid_prefill_stage35_kernel");
 }
 
 // Mirror of akv_hybrid_attn_params in include/akv_b200.h.

@@ -2738,6 +2738,7 @@ struct akv_tq_prefill_params {
   void* workspace; size_t workspace_bytes;
   void* stream;
   int max_seq_len;
+  const void* hybrid_tables;
 };
 
 static void prefill_plan(int num_tokens, int num_q_heads, size_t* off_acc, size_t* off_ml, size_t* total) {
@@ -2774,7 +2775,12 @@ AKV_EXPORT int akv_tq_prefill_attn(const akv_tq_prefill_params* p) {
   auto al16 = [](const void* q, int64_t a, int64_t b, int64_t c) {
     return ((reinterpret_cast<uintptr_t>(q) | (uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) == 0;
   };
-  const bool low_bits = p->bits == 3 || p->bits == 2;      // served by the staged tensor-core kernel only
+  const bool hybrid = p->hybrid_tables != nullptr;         // tq35 records: staged tensor-core kernel only, like ...
+  const bool low_bits = p->bits == 3 || p->bits == 2 || hybrid;      // ... 3- and 2-bit codes
+  if (hybrid && ((reinterpret_cast<uintptr_t>(p->k_packed) | reinterpret_cast<uintptr_t>(p->v_packed) | (uintptr_t)p->kp_stride_blk |
+                  (uintptr_t)p->kp_stride_pos | (uintptr_t)p->kp_stride_head | (uintptr_t)p->vp_stride_blk |
+                  (uintptr_t)p->vp_stride_pos | (uintptr_t)p->vp_stride_head) & 15) != 0)
+    return fail(AKV_ERR_UNSUPPORTED, "prefill attention over tq35 records needs records readable in 16-byte pieces");
   if (p->head_dim != 128 || (p->bits != 4 && !low_bits) || (G != 1 && G != 2 && G != 4 && G != 8) || p->block_size % 16 != 0 ||
       (!low_bits && (!al16(p->k_packed, p->kp_stride_blk, p->kp_stride_pos, p->kp_stride_head) ||
                      !al16(p->v_packed, p->vp_stride_blk, p->vp_stride_pos, p->vp_stride_head))))
@@ -2782,8 +2788,8 @@ AKV_EXPORT int akv_tq_prefill_attn(const akv_tq_prefill_params* p) {
                                      "that are multiples of 16 and 4-bit caches readable in 16-byte pieces (3- and 2-bit "
                                      "caches: staged kernel only)");
   if (p->num_tokens == 0 || p->num_seqs == 0) return AKV_OK;
-  if (!p->query || !p->k_packed || !p->v_packed || !p->k_norms || !p->v_norms || !p->block_tables || !p->seq_lens ||
-      !p->query_start_loc || !p->rotation || !p->rotation_t || !p->centroids || !p->out)
+  if (!p->query || !p->k_packed || !p->v_packed || (!hybrid && (!p->k_norms || !p->v_norms || !p->centroids)) ||
+      !p->block_tables || !p->seq_lens || !p->query_start_loc || !p->rotation || !p->rotation_t || !p->out)
     return fail(AKV_ERR_ARG, "prefill attention: null pointer");
   size_t off_acc, off_ml, total;
   prefill_plan(p->num_tokens, p->num_q_heads, &off_acc, &off_ml, &total);
@@ -2807,8 +2813,8 @@ AKV_EXPORT int akv_tq_prefill_attn(const akv_tq_prefill_params* p) {
     static const bool no_staged_env = getenv("AKV_PREFILL_STAGED") != nullptr && getenv("AKV_PREFILL_STAGED")[0] == '0';
     const size_t need = prefill_staged_bytes(p->num_seqs, p->num_kv_heads, p->max_seq_len);
     if (low_bits && (!use_tc || no_staged_env || need == 0 || p->workspace_bytes < ((total + 1023) & ~(size_t)1023) + need))
-      return fail(AKV_ERR_UNSUPPORTED, "prefill attention over 3- / 2-bit codes needs a chunk that fills 128-row tiles, "
-                                       "max_seq_len and the staged workspace");
+      return fail(AKV_ERR_UNSUPPORTED, "prefill attention over 3- / 2-bit codes or tq35 records needs a chunk that fills "
+                                       "128-row tiles, max_seq_len and the staged workspace");
   }
   // Many rows: both rotations are [rows, 128] x [128, 128] products on the tensor cores (rot_rows.cu); a few rows: the
   // kernels of the decode path
@@ -2856,6 +2862,7 @@ AKV_EXPORT int akv_tq_prefill_attn(const akv_tq_prefill_params* p) {
     const size_t staged = no_staged ? 0 : prefill_staged_bytes(p->num_seqs, p->num_kv_heads, p->max_seq_len);
     const size_t staged_off = (total + 1023) & ~(size_t)1023;
     a.bits = p->bits;
+    a.hybrid_tables = p->hybrid_tables;
     if (staged != 0 && p->workspace_bytes >= staged_off + staged && (reinterpret_cast<uintptr_t>(ws) & 15) == 0) {
       a.staged = reinterpret_cast<uint8_t*>(ws + staged_off);
       a.tiles_per_seq = (p->max_seq_len + prefill_staged_tile_keys() - 1) / prefill_staged_tile_keys();

@@ -23,7 +23,23 @@ struct PrefillArgs {
   uint8_t* staged;
   int tiles_per_seq;
   int bits;                            // 4; 3 or 2 only with staged images
+  // tq35 records instead of TurboQuant codes (staged images only): host pointer to the akv_hybrid_tables of the call;
+  // k_packed / v_packed are the 64-byte records, the norm arrays are unused
+  const void* hybrid_tables;
 };
+
+// Layout of a staged tile in global memory (what the pre-pass kernels write and tq_prefill_tc_kernel<G, true> copies):
+// 128 keys of one KV head = the K operand [128 keys][128 dims] as two halves of 64 dims (128 rows x 128 B each, the
+// 16-byte chunk c of row r at chunk c ^ (r & 7)), then the transposed V operand as two halves of 64 keys
+// ([128 dims] rows x 128 B each, the chunk of key group g of dim d at chunk g ^ (d & 7)).
+constexpr int PFI_KEYS = 128;
+constexpr int PFI_KHALF = PFI_KEYS * 128;
+constexpr int PFI_VOFF = 2 * PFI_KHALF;
+constexpr int PFI_VHALF = 128 * 128;
+constexpr int PFI_BYTES = PFI_VOFF + 2 * PFI_VHALF;
+
+// hybrid.cu: the pre-pass for tq35 records
+int launch_hybrid_prefill_stage(const PrefillArgs& a, cudaStream_t st);
 
 // tcgen05 kernel (tq_prefill_tc.cu): one CTA per 128 (token, query head) rows and KV head.  Returns AKV_OK after
 // the launch; AKV_ERR_UNSUPPORTED is never returned - the caller checks the shape (4-bit codes, head_dim 128,

@@ -65,6 +65,8 @@ template <bool STAGED> struct PtL {
 };
 constexpr int PS_KT = PtL<true>::KT;                 // keys per staged tile
 constexpr int PT_IMAGE = PS_KT * 512;                // a staged tile in global memory: K operand image, then V operand halves
+static_assert(PS_KT == PFI_KEYS && PT_IMAGE == PFI_BYTES && PtL<true>::KHALF == PFI_KHALF && PtL<true>::KSTAGE == PFI_VOFF,
+              "image layout shared with the other pre-pass kernels");
 // barrier slots (8 bytes each; up to four operand stages)
 constexpr uint32_t B_KFULL = 0, B_VFULL = 32, B_SFULL = 64, B_PFULL = 96, B_PVDONE = 112,
                    B_VFREE = 160, B_DRAIN = 192, B_TMEM = 200, B_FAILED = 204;
@@ -752,7 +754,9 @@ int launch_prefill_tc(const PrefillArgs& a, int G, cudaStream_t st) {
   if (a.staged != nullptr) {
     // operand images first (ordered before the attention kernel by the stream), then the bulk-copy-fed kernel
     dim3 sgrid((a.tiles_per_seq + PS_TILES - 1) / PS_TILES, a.num_seqs, a.num_kv_heads);
-    if (a.bits == 4) {
+    if (a.hybrid_tables != nullptr) {
+      if (int rc = launch_hybrid_prefill_stage(a, st)) return rc;
+    } else if (a.bits == 4) {
       e = cudaFuncSetAttribute(tq_prefill_stage_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PS_SMEM);
       if (e == cudaSuccess) tq_prefill_stage_kernel<<<sgrid, PS_THREADS, PS_SMEM, st>>>(a);
     } else if (a.bits == 3) {
@@ -763,7 +767,8 @@ int launch_prefill_tc(const PrefillArgs& a, int G, cudaStream_t st) {
       if (e == cudaSuccess) tq_prefill_stage_bits_kernel<2><<<sgrid, PS_THREADS, PT_IMAGE, st>>>(a);
     }
     if (e != cudaSuccess) return fail((int)e, "prefill attention: smem attribute: %s", cudaGetErrorString(e));
-    if (int rc = check_launch("tq_prefill_stage_kernel")) return rc;
+    if (a.hybrid_tables == nullptr)
+      if (int rc = check_launch("tq_prefill_stage_kernel")) return rc;
   }
 #define AKV_PT(GG, ST)                                                                                                  \
   e = cudaFuncSetAttribute(tq_prefill_tc_kernel<GG, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, PtL<ST>::SMEM);     \

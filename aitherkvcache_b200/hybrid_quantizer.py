@@ -300,6 +300,71 @@ class HybridPagedAttention:
         self.scale = 1.0 / math.sqrt(htq.head_dim)
         self._workspace: Optional[torch.Tensor] = None
 
+    STAGED_WORKSPACE_LIMIT = 4 << 30     # bytes of scratch the staged prefill kernel may ask for
+
+    def prefill(self, query, k_cache, v_cache, block_tables, seq_lens, query_start_loc, block_size: int = 16,
+                num_kv_heads: Optional[int] = None, out: Optional[torch.Tensor] = None, scale: Optional[float] = None,
+                max_seq_len: Optional[int] = None) -> Optional[torch.Tensor]:
+        """Chunked-prefill attention over tq35 records (arguments as ``TQPagedAttention.prefill``): the records of every
+        128-key tile are decoded once into fp16 operand images, then the tensor-core attention kernel runs over them
+        (``akv_tq_prefill_attn`` with ``hybrid_tables``).  The reference decompresses the active blocks and calls vLLM's
+        unified attention (``vllm/hooks.py:726-850``).  Returns None when that kernel does not serve the case (tq25, no
+        host-side ``max_seq_len``, a batch too ragged for 128-row tiles, scratch beyond ``STAGED_WORKSPACE_LIMIT``): the
+        caller then attends row by row with ``forward``."""
+        if num_kv_heads is None:
+            num_kv_heads = k_cache.shape[2]
+        dev = _lib.require_cuda(query, k_cache, v_cache, block_tables, seq_lens, query_start_loc)
+        n_tok, num_q_heads, head_dim = query.shape
+        G = num_q_heads // num_kv_heads
+        aligned = all((t.data_ptr() | t.stride(0) | t.stride(1) | t.stride(2)) % 16 == 0 for t in (k_cache, v_cache))
+        if (self.htq.mode != "tq35" or head_dim != 128 or G not in (1, 2, 4, 8) or block_size % 16 or not aligned
+                or not max_seq_len or k_cache.shape[-1] < 64 or v_cache.shape[-1] < 64):
+            return None
+        assert num_q_heads == self.num_query_heads and k_cache.shape[1] == block_size
+        num_seqs = query_start_loc.numel() - 1
+        if query.dtype not in _lib._FLOAT_CODES:
+            query = query.float()
+        if query.stride(-1) != 1:
+            query = query.contiguous()
+        if block_tables.stride(-1) != 1:
+            block_tables = block_tables.contiguous()
+        seq_lens, query_start_loc = seq_lens.contiguous(), query_start_loc.contiguous()
+        if out is None:
+            out = torch.empty(n_tok, num_q_heads, head_dim, dtype=query.dtype, device=dev)
+        L = _lib.lib()
+        nbytes = L.akv_tq_prefill_attn_workspace_bytes_staged(n_tok, num_q_heads, num_kv_heads, num_seqs, int(max_seq_len))
+        if nbytes > self.STAGED_WORKSPACE_LIMIT:
+            return None
+        if getattr(self, "_prefill_ws", None) is None or self._prefill_ws.numel() < nbytes or self._prefill_ws.device != dev:
+            self._prefill_ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=dev)
+        if getattr(self, "_eye", None) is None or self._eye.device != dev:
+            self._eye = torch.eye(128, dtype=torch.float32, device=dev)      # the records decode into the original domain
+        tables = self.htq._kernel_tables(1)
+        p = _lib.TQPrefillParams()
+        p.query, p.q_dtype, p.q_stride_tok, p.q_stride_head = query.data_ptr(), _lib.float_code(query), query.stride(0), query.stride(1)
+        p.k_packed, p.kp_stride_blk, p.kp_stride_pos, p.kp_stride_head = k_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1), k_cache.stride(2)
+        p.v_packed, p.vp_stride_blk, p.vp_stride_pos, p.vp_stride_head = v_cache.data_ptr(), v_cache.stride(0), v_cache.stride(1), v_cache.stride(2)
+        p.k_norms = p.v_norms = None
+        p.block_tables, p.bt_dtype, p.bt_stride_seq = block_tables.data_ptr(), _lib.index_code(block_tables), block_tables.stride(0)
+        p.seq_lens, p.sl_dtype = seq_lens.data_ptr(), _lib.index_code(seq_lens)
+        p.query_start_loc, p.qs_dtype = query_start_loc.data_ptr(), _lib.index_code(query_start_loc)
+        p.num_seqs, p.num_tokens, p.num_q_heads, p.num_kv_heads = num_seqs, n_tok, num_q_heads, num_kv_heads
+        p.head_dim, p.block_size, p.max_blocks_per_seq, p.num_blocks = head_dim, block_size, block_tables.shape[1], k_cache.shape[0]
+        p.bits = 4
+        p.rotation, p.rotation_t, p.centroids = self._eye.data_ptr(), self._eye.data_ptr(), None
+        p.scale = self.scale if scale is None else float(scale)
+        p.out, p.out_dtype, p.out_stride_tok, p.out_stride_head = out.data_ptr(), _lib.float_code(out), out.stride(0), out.stride(1)
+        p.workspace, p.workspace_bytes = self._prefill_ws.data_ptr(), self._prefill_ws.numel()
+        p.stream = _lib.stream_ptr(dev)
+        p.max_seq_len = int(max_seq_len)
+        p.hybrid_tables = ctypes.cast(ctypes.pointer(tables), ctypes.c_void_p)
+        with torch.cuda.device(dev):
+            rc = L.akv_tq_prefill_attn(ctypes.byref(p))
+        if rc == _lib.AKV_ERR_UNSUPPORTED:
+            return None
+        _lib.check(rc, "akv_tq_prefill_attn")
+        return out
+
     def forward(self, query, k_cache, v_cache, block_tables, context_lens, block_size: int = 16,
                 num_kv_heads: Optional[int] = None, out: Optional[torch.Tensor] = None,
                 scale: Optional[float] = None, new_kv=None) -> torch.Tensor:

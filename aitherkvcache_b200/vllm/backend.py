@@ -173,6 +173,17 @@ class TurboQuantImplBase:
         ragged for the staged tensor-core kernel, rows that are not readable in 16-byte pieces), in which case every
         token becomes a row of the decode kernels."""
         pd, bs = self.packed_dim, kv_cache.shape[2]
+        if self.tq_codec == "hybrid":      # tq35 records: staged tensor-core kernel over decoded operand images
+            key_ = (self.head_size, self.tq_codec, self.tq_mode or self.tq_bits, self.num_heads, str(kv_cache.device))
+            attn = _LayerState.attention.get(key_)
+            if attn is None:
+                from ..hybrid_quantizer import HybridPagedAttention
+                attn = HybridPagedAttention(_hybrid_quantizer(self.head_size, self.tq_mode, kv_cache.device), self.num_heads)
+                _LayerState.attention[key_] = attn
+            res = attn.prefill(q, kv_cache[:, 0, :, :, :pd], kv_cache[:, 1, :, :, :pd], md.block_table, md.seq_lens,
+                               md.query_start_loc, block_size=bs, num_kv_heads=self.num_kv_heads, out=out, scale=self.scale,
+                               max_seq_len=getattr(md, "max_seq_len", None))
+            return res is not None
         key_ = (self.head_size, self.tq_codec, self.tq_bits, self.num_heads, str(kv_cache.device))
         attn = _LayerState.attention.get(key_)
         if attn is None:
@@ -223,7 +234,7 @@ class TurboQuantImplBase:
         if attn_metadata.max_query_len == 1:      # one token per sequence: rows are the sequences
             self._attend(layer, q, out, kv_cache, attn_metadata.block_table, attn_metadata.seq_lens)
             return output
-        if self.tq_codec == "uniform" and self._mixed(layer, q, out, kv_cache, attn_metadata, n):
+        if self._mixed(layer, q, out, kv_cache, attn_metadata, n):
             return output
         bt, ctx = token_rows(attn_metadata.query_start_loc, attn_metadata.seq_lens, attn_metadata.block_table, n)
         # the split-K workspace grows with the number of rows of a call: a chunk goes through in slices

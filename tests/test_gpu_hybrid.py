@@ -201,3 +201,52 @@ def test_paged_attention_full_size_random_values_vs_oracle():
     ref = ohy.paged_attention_decode_sdpa(q.cpu().numpy()[pick], kc.cpu().numpy(), vc.cpu().numpy(), bt.numpy()[pick],
                                           ctx.numpy()[pick], t, 1.0 / math.sqrt(D), BS, kv_dtype=np.float32)
     assert np.abs(out[pick] - ref).max() < 2e-3
+
+
+@pytest.mark.parametrize("H,QH", [(8, 32), (2, 16), (2, 2)])
+def test_chunked_prefill_over_tq35_records(H, QH):
+    """Chunked prefill over a tq35 cache: the pre-pass decodes every 128-key tile of records into fp16 operand images, the
+    tensor-core attention kernel runs over them in the original domain.  Against the record-domain decode kernel row by
+    row (all rows) and the oracle (decode -> fp16 -> attention) on the last row of each chunk."""
+    from aitherkvcache_b200 import _lib
+    from aitherkvcache_b200.hybrid_quantizer import HybridPagedAttention
+    g = load_golden("hybrid_tq35.npz")
+    h = _htq("tq35", g, heads=1)
+    t = _oracle_tables(g, "tq35")
+    gen = torch.Generator().manual_seed(21 + H)
+    bs = 16
+    seqs = [(500, 140), (0, 200), (130, 128)]          # (cached before the chunk, chunk length)
+    lens = [p + q for p, q in seqs]
+    nblk = [(n + bs - 1) // bs for n in lens]
+    total = sum(nblk) + 2
+    perm = torch.randperm(total, generator=gen)
+    bt = torch.zeros(len(seqs), max(nblk), dtype=torch.int32)
+    o = 0
+    for s, n in enumerate(nblk):
+        bt[s, :n] = perm[o:o + n].to(torch.int32)
+        o += n
+    kc = h.encode(torch.randn(total, bs, H, 128, generator=gen).half().cuda())
+    vc = h.encode(torch.randn(total, bs, H, 128, generator=gen).half().cuda())
+    nq = sum(q for _, q in seqs)
+    qsl = torch.tensor([0] + list(np.cumsum([q for _, q in seqs])), dtype=torch.int32)
+    query = torch.randn(nq, QH, 128, generator=gen).half().cuda()
+    attn = HybridPagedAttention(h, QH)
+    sl = torch.tensor(lens, dtype=torch.int32).cuda()
+    assert attn.prefill(query, kc, vc, bt.cuda(), sl, qsl.cuda(), block_size=bs) is None          # no host-side bound
+    out = attn.prefill(query, kc, vc, bt.cuda(), sl, qsl.cuda(), block_size=bs, max_seq_len=max(lens))
+    assert out is not None and out.dtype == torch.float16
+    assert _lib.lib().akv_last_split_kernel() == b"tq_prefill_attn_tc_staged_kernel"
+    rows_bt = torch.cat([bt[s:s + 1].expand(q, -1) for s, (_, q) in enumerate(seqs)])
+    rows_ctx = torch.cat([torch.arange(p + 1, p + q + 1) for p, q in seqs]).to(torch.int32)
+    ref = torch.cat([attn.forward(query[lo:lo + 64], kc, vc, rows_bt[lo:lo + 64].contiguous().cuda(), rows_ctx[lo:lo + 64].cuda())
+                     for lo in range(0, nq, 64)])
+    # rows with a handful of keys return value vectors of magnitude 2..4, where one fp16 step (the staged values are
+    # fp16) is 2e-3 already: the tolerance scales with the magnitude
+    assert ((out.float() - ref.float()).abs() <= 2e-3 * ref.float().abs().clamp(min=1.0)).all()
+    for s in range(len(seqs)):
+        row = int(qsl[s + 1]) - 1
+        want = ohy.paged_attention_decode_sdpa(query[row:row + 1].cpu().numpy(), kc.cpu().numpy(), vc.cpu().numpy(),
+                                               bt[s:s + 1].numpy(), np.asarray([lens[s]]), t, 1.0 / math.sqrt(128), bs,
+                                               kv_dtype=np.float16)
+        assert np.abs(out[row].float().cpu().numpy() - want[0]).max() < 2e-3
+    assert not any(_lib.device_status().values())

@@ -352,6 +352,22 @@ def test_backend_hybrid_mode_from_environment(monkeypatch, mode, PD):
     ref0 = ohy.paged_attention_decode_sdpa(q3[:1].reshape(1, QH, 128).numpy(), kc, vc, bt.numpy()[1:2],
                                            np.asarray([lens[1] - 2]), t, 1.0 / math.sqrt(128), bs)
     assert np.abs(out3[0].float().cpu().numpy().reshape(QH, 128) - ref0[0]).max() < 2e-3
+    # a mixed batch with the host-side length bound of vLLM's metadata: sequence 0 brings one token (decode kernel),
+    # sequence 1 its last 64 (tq35: staged tensor-core prefill over decoded operand images; tq25: rows)
+    qm = torch.cat([q[0:1], torch.randn(63, QH * 128, generator=gen).half(), q[1:2]])
+    mdm = types.SimpleNamespace(num_actual_tokens=65, max_query_len=64, block_table=bt.cuda(), max_seq_len=max(lens),
+                                seq_lens=torch.tensor(lens, dtype=torch.int32, device="cuda"),
+                                query_start_loc=torch.tensor([0, 1, 65], dtype=torch.int32, device="cuda"))
+    outm = torch.zeros(65, QH * 128, dtype=torch.float16, device="cuda")
+    impl.forward(layer, qm.cuda(), None, None, kv, mdm, output=outm)
+    if mode == "tq35":
+        from aitherkvcache_b200 import _lib
+        assert _lib.lib().akv_last_split_kernel() != b"tq_prefill_attn_tc_staged_kernel"      # the decode side ran last ...
+    assert (outm[0].float() - out1[0].float()).abs().max().item() < 1e-3
+    assert (outm[64].float() - out1[1].float()).abs().max().item() < 2e-3
+    refm = ohy.paged_attention_decode_sdpa(qm[1:2].reshape(1, QH, 128).numpy(), kc, vc, bt.numpy()[1:2],
+                                           np.asarray([lens[1] - 63]), t, 1.0 / math.sqrt(128), bs, kv_dtype=np.float16)
+    assert np.abs(outm[1].float().cpu().numpy().reshape(QH, 128) - refm[0]).max() < 2e-3
 
 
 def test_backend_decode_step_replays_from_a_cuda_graph():
