@@ -418,6 +418,13 @@ def secondary_kernels(steps, warmup, dev):
     by = total_ctx * H_KV * 128
     res["tq35_decode_attn"] = {"KV-tokens/s": total_ctx / ms * 1e3, "GB/s": by / ms / 1e6,
                                "frac_of_measured_peak": by / ms / 1e6 / peak, "ms": ms}
+    # the same prefill chunk over tq35 records (records decoded into the staged operand images, attention in the original domain)
+    if hattn.prefill(qp, kc, kc, pbt, sl, qsl, block_size=BS, num_kv_heads=H_KV, out=outp, max_seq_len=past + chunk) is None:
+        raise RuntimeError("the chunked-prefill kernel refused the tq35 benchmark shape")
+    ms = _event_time(lambda: hattn.prefill(qp, kc, kc, pbt, sl, qsl, block_size=BS, num_kv_heads=H_KV, out=outp,
+                                           max_seq_len=past + chunk), max(3, steps // 8), 2)
+    res["tq35_chunked_prefill"] = {"ms": ms, "query_tokens": chunk, "past_tokens": past,
+                                   "TFLOP/s": pairs * H_Q * D * 4 / ms / 1e9, "query-tokens/s": chunk / ms * 1e3}
     return res
 
 
