@@ -871,3 +871,44 @@ def test_paged_attention_large_batch_rotations_as_one_product(dtype):
     assert (out[0] == 0).all()
     tol = 2e-3 if dtype != torch.bfloat16 else 2e-2
     assert (np.abs(out - ref) <= tol * np.maximum(1.0, np.abs(ref))).all()
+
+
+def test_chunked_prefill_staged_edge_cases():
+    """Staged tensor-core prefill with awkward batches: a sequence that contributes no token, a length bound larger than
+    any sequence (scratch sized for it), padding query rows, int64 index tensors; and an understated bound, which
+    must neither fault nor read past the staged images (its long sequences are simply cut at the bound)."""
+    g = load_golden("tq_d128_b4.npz")
+    tq = _tq(128, 4, g)
+    H, QH, bs = 2, 8, 16
+    attn = _attn(tq, QH)
+    gen = torch.Generator().manual_seed(77)
+    seqs = [(60, 200), (40, 0), (0, 129)]              # (cached before the chunk, chunk length); the middle one brings nothing
+    lens = [p + q for p, q in seqs]
+    nblk = [(n + bs - 1) // bs for n in lens]
+    total = sum(nblk) + 1
+    perm = torch.randperm(total, generator=gen)
+    bt = torch.zeros(len(seqs), max(nblk), dtype=torch.int64)
+    o = 0
+    for s_, n in enumerate(nblk):
+        bt[s_, :n] = perm[o:o + n]
+        o += n
+    kp, kn = tq.encode(torch.randn(total, bs, H, 128, generator=gen).half().cuda())
+    vp, vn = tq.encode(torch.randn(total, bs, H, 128, generator=gen).half().cuda())
+    nq = sum(q for _, q in seqs)
+    qsl = torch.tensor([0] + list(np.cumsum([q for _, q in seqs])), dtype=torch.int64)
+    query = torch.randn(nq + 5, QH, 128, generator=gen).half().cuda()
+    sl = torch.tensor(lens, dtype=torch.int64).cuda()
+    out = torch.full_like(query, 3.0)
+    res = attn.prefill(query, kp, kn, vp, vn, bt.cuda(), sl, qsl.cuda(), block_size=bs, num_kv_heads=H, out=out, max_seq_len=1000)
+    assert res is out and (out[nq:] == 0).all()
+    rows_bt = torch.cat([bt[s_:s_ + 1].expand(q, -1) for s_, (_, q) in enumerate(seqs) if q])
+    rows_ctx = torch.cat([torch.arange(p + 1, p + q + 1) for p, q in seqs if q])
+    ref = attn.forward(query[:nq], kp, kn, vp, vn, rows_bt.contiguous().cuda(), rows_ctx.cuda(), block_size=bs, num_kv_heads=H)
+    assert ((out[:nq].float() - ref.float()).abs() <= 2e-3 * ref.float().abs().clamp(min=1.0)).all()
+    # understated bound: rows that fit below it are still right, nothing faults
+    low = attn.prefill(query, kp, kn, vp, vn, bt.cuda(), sl, qsl.cuda(), block_size=bs, num_kv_heads=H, max_seq_len=128)
+    assert low is not None and torch.isfinite(low.float()).all()
+    short = slice(200, 200 + 128)                      # the third sequence: its first 128 tokens see keys 0..127 only
+    assert ((low[short].float() - ref[short].float()).abs() <= 2e-3 * ref[short].float().abs().clamp(min=1.0)).all()
+    from aitherkvcache_b200 import _lib
+    assert not any(_lib.device_status().values())
