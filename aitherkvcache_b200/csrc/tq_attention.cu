@@ -2741,12 +2741,17 @@ struct akv_tq_prefill_params {
   const void* hybrid_tables;
 };
 
+// Short chunks get room for PREFILL_MAX_SPLITS partials per row (key-range splits of the tensor-core kernels).
+constexpr int PREFILL_MAX_SPLITS = 4;
+constexpr size_t PREFILL_SPLIT_ROWS = 16384;
+static int prefill_parts(size_t rows) { return rows <= PREFILL_SPLIT_ROWS ? PREFILL_MAX_SPLITS : 1; }
+
 static void prefill_plan(int num_tokens, int num_q_heads, size_t* off_acc, size_t* off_ml, size_t* total) {
-  const size_t rows = (size_t)num_tokens * num_q_heads;
+  const size_t rows = (size_t)num_tokens * num_q_heads, parts = (size_t)prefill_parts(rows);
   auto al = [](size_t v) { return (v + 255) & ~(size_t)255; };
   *off_acc = al(rows * 128 * sizeof(float));
-  *off_ml = *off_acc + al(rows * 128 * sizeof(float));
-  *total = *off_ml + al(rows * 2 * sizeof(float));
+  *off_ml = *off_acc + al(rows * parts * 128 * sizeof(float));
+  *total = *off_ml + al(rows * parts * 2 * sizeof(float));
 }
 
 AKV_EXPORT size_t akv_tq_prefill_attn_workspace_bytes(int num_tokens, int num_q_heads) {
@@ -2808,6 +2813,14 @@ AKV_EXPORT int akv_tq_prefill_attn(const akv_tq_prefill_params* p) {
   const int64_t tc_rows = (int64_t)p->num_tokens * G;
   const int64_t tc_tiles = (tc_rows + 127) / 128 + p->num_seqs - 1;
   const bool use_tc = tc_env ? tc_env[0] == '1' : tc_rows >= 64 * tc_tiles;
+  // few row tiles (a short chunk, possibly on a long context): the key range of every tile is split over up to four
+  // CTAs, whose partials the merge kernel combines
+  int splits = 1;
+  if (use_tc && prefill_parts((size_t)rows) > 1) {
+    const int64_t ctas = tc_tiles * p->num_kv_heads;
+    splits = (int)(sm_count() / (ctas > 0 ? ctas : 1));
+    splits = splits < 1 ? 1 : (splits > PREFILL_MAX_SPLITS ? PREFILL_MAX_SPLITS : splits);
+  }
   // 3- and 2-bit caches: only the staged tensor-core kernel reads them; say so before anything is launched
   {
     static const bool no_staged_env = getenv("AKV_PREFILL_STAGED") != nullptr && getenv("AKV_PREFILL_STAGED")[0] == '0';
@@ -2820,7 +2833,7 @@ AKV_EXPORT int akv_tq_prefill_attn(const akv_tq_prefill_params* p) {
   // kernels of the decode path
   const bool gemm_q = rows >= 2048 && rot_rows_ok(p->query, p->q_dtype, p->q_stride_tok, p->q_stride_head, qrot, AKV_F32,
                                                     (int64_t)p->num_q_heads * 128, 128);
-  const bool gemm_o = rows >= 2048 && rot_rows_ok(part_acc, AKV_F32, (int64_t)p->num_q_heads * 128, 128, p->out, p->out_dtype,
+  const bool gemm_o = splits == 1 && rows >= 2048 && rot_rows_ok(part_acc, AKV_F32, (int64_t)p->num_q_heads * 128, 128, p->out, p->out_dtype,
                                                     p->out_stride_tok, p->out_stride_head);
   if (gemm_q) {
     if (int rc = launch_rot_rows(p->query, p->q_dtype, p->q_stride_tok, p->q_stride_head, p->num_q_heads, nullptr, 0,
@@ -2841,7 +2854,7 @@ AKV_EXPORT int akv_tq_prefill_attn(const akv_tq_prefill_params* p) {
     if (int rc = check_launch("akv_qrot128_kernel")) return rc;
   }
   // rows that no sequence of the chunk owns (padding) stay at l = 0 and come out as zeros
-  cudaMemsetAsync(part_ml, 0, (size_t)rows * 2 * sizeof(float), st);
+  cudaMemsetAsync(part_ml, 0, (size_t)rows * splits * 2 * sizeof(float), st);
   PrefillArgs a{};
   a.qrot = qrot;
   a.k_packed = p->k_packed; a.kp_sb = p->kp_stride_blk; a.kp_sp = p->kp_stride_pos; a.kp_sh = p->kp_stride_head;
@@ -2863,6 +2876,7 @@ AKV_EXPORT int akv_tq_prefill_attn(const akv_tq_prefill_params* p) {
     const size_t staged_off = (total + 1023) & ~(size_t)1023;
     a.bits = p->bits;
     a.hybrid_tables = p->hybrid_tables;
+    a.splits = splits;
     if (staged != 0 && p->workspace_bytes >= staged_off + staged && (reinterpret_cast<uintptr_t>(ws) & 15) == 0) {
       a.staged = reinterpret_cast<uint8_t*>(ws + staged_off);
       a.tiles_per_seq = (p->max_seq_len + prefill_staged_tile_keys() - 1) / prefill_staged_tile_keys();
@@ -2887,14 +2901,15 @@ AKV_EXPORT int akv_tq_prefill_attn(const akv_tq_prefill_params* p) {
     return launch_rot_rows(part_acc, AKV_F32, (int64_t)p->num_q_heads * 128, 128, p->num_q_heads, part_ml + 1, 2, p->rotation,
                            1.0f, p->out, p->out_dtype, p->out_stride_tok, p->out_stride_head, rows, st);
   MergeArgs mg{};
-  mg.acc = part_acc; mg.acc_row = 128; mg.acc_part = 128;
-  mg.ml = part_ml; mg.ml_row = 2; mg.ml_part = 2;
-  mg.np = 1;
+  mg.acc = part_acc; mg.acc_row = (int64_t)splits * 128; mg.acc_part = 128;
+  mg.ml = part_ml; mg.ml_row = (int64_t)splits * 2; mg.ml_part = 2;
+  mg.np = splits;
   mg.num_q_heads = p->num_q_heads;
   mg.D = 128;
   mg.mode = MERGE_ROTATE;
   mg.rot = p->rotation;
   mg.out = p->out; mg.out_dtype = p->out_dtype; mg.out_ss = p->out_stride_tok; mg.out_sh = p->out_stride_head;
+  mg.gemm_scratch = qrot;        // the rotated queries are dead by now
   return launch_merge(mg, rows, st);
 }
 

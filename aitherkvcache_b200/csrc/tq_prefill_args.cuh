@@ -17,8 +17,8 @@ struct PrefillArgs {
   int num_seqs, n_tokens, num_q_heads, num_kv_heads, block_size, max_blocks_per_seq;
   int64_t num_blocks;
   const float* centroids;
-  float* part_acc;                     // [n_tokens * num_q_heads][128]
-  float* part_ml;                      // [n_tokens * num_q_heads][2]
+  float* part_acc;                     // [n_tokens * num_q_heads][splits][128]
+  float* part_ml;                      // [n_tokens * num_q_heads][splits][2]
   // staged variant of the tensor-core kernel: [num_seqs][tiles_per_seq][num_kv_heads] operand images (512 B per key), or null
   uint8_t* staged;
   int tiles_per_seq;
@@ -26,6 +26,7 @@ struct PrefillArgs {
   // tq35 records instead of TurboQuant codes (staged images only): host pointer to the akv_hybrid_tables of the call;
   // k_packed / v_packed are the 64-byte records, the norm arrays are unused
   const void* hybrid_tables;
+  int splits;                          // tensor-core kernels: key-range splits = partials per row (1: part_acc [rows][128])
 };
 
 // Layout of a staged tile in global memory (what the pre-pass kernels write and tq_prefill_tc_kernel<G, true> copies):

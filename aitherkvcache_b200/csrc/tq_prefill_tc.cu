@@ -36,7 +36,7 @@ namespace akv {
 namespace {
 
 __device__ int g_prefill_tc_status;          // 1: a bounded wait gave up, 2: tensor-memory columns were kept
-__device__ int g_prefill_tc_withhold = -1;   // test hook: CTA (0, 0) issues neither the score MMAs nor the commit of this tile
+__device__ int g_prefill_tc_withhold = -1;   // test hook: CTAs (0, 0, z) issue neither the score MMAs nor the commit of this tile of their share
 
 constexpr int PT_VHALF = 144 * 128;                  // 64 keys of a value operand: 128 dims + the row of ones (+ 15 zero rows)
 
@@ -207,9 +207,13 @@ tq_prefill_tc_kernel(PrefillArgs a) {
   const int tok_hi = (tok_lo + TT < qlen) ? tok_lo + TT : qlen;
   int kend = past + tok_hi;             // keys any row of this CTA may see
   if (kend > seq_len) kend = seq_len;
-  int n_ktiles = (kend + PT_KT - 1) / PT_KT;
-  if (STAGED && n_ktiles > a.tiles_per_seq) n_ktiles = a.tiles_per_seq;      // a caller that understated max_seq_len: no read past the images
-  if (n_ktiles <= 0) return;            // nothing to attend to: the rows keep l = 0
+  int n_all = (kend + PT_KT - 1) / PT_KT;
+  if (STAGED && n_all > a.tiles_per_seq) n_all = a.tiles_per_seq;      // a caller that understated max_seq_len: no read past the images
+  // split z of gridDim.z takes an even share of the CTA's key tiles and writes partial z of its rows (short chunks on
+  // long contexts: more CTAs than row tiles); tile indices below are local to the share, jbase + j is the tile itself
+  const int jbase = (int)((int64_t)n_all * blockIdx.z / gridDim.z);
+  const int n_ktiles = (int)((int64_t)n_all * (blockIdx.z + 1) / gridDim.z) - jbase;
+  if (n_ktiles <= 0) return;            // nothing to attend to: the partial keeps l = 0
 
   // ---------------- one-time setup ----------------
   if (tid == 0) {
@@ -345,7 +349,7 @@ tq_prefill_tc_kernel(PrefillArgs a) {
   } else if (STAGED && warp == 5) {
     // ================= producer: operand images of tile j by two bulk copies =================
     if (lane == 0) {
-      const uint8_t* src = a.staged + ((int64_t)s * a.tiles_per_seq * a.num_kv_heads + kvh) * PT_IMAGE;
+      const uint8_t* src = a.staged + (((int64_t)s * a.tiles_per_seq + jbase) * a.num_kv_heads + kvh) * PT_IMAGE;
       const int64_t step = (int64_t)a.num_kv_heads * PT_IMAGE;
       int issued = 0;
       for (int j = 0; j < n_ktiles; ++j) {
@@ -427,13 +431,14 @@ tq_prefill_tc_kernel(PrefillArgs a) {
         np += vn_sp;
       }
       if (j == n_ktiles - 1) {      // a key past the range carries any norm: its score is masked, its value row becomes zero
-        const int key8 = PT_KT * j + 8 * kg;
+        const int key8 = PT_KT * (jbase + j) + 8 * kg;
 #pragma unroll
         for (int i = 0; i < 8; ++i) vnorm[i] = key8 + i < kend ? vnorm[i] : 0.f;
-        if (PT_KT * j + kr >= kend) knorm = 0.f;
+        if (PT_KT * (jbase + j) + kr >= kend) knorm = 0.f;
       }
     };
-    int blk_k = kr / bs, pos_k = kr - blk_k * bs, blk_v = (8 * kg) / bs, pos_v = 8 * kg - blk_v * bs;
+    const int key_k0 = PT_KT * jbase + kr, key_v0 = PT_KT * jbase + 8 * kg;      // this thread's keys in the share's first tile
+    int blk_k = key_k0 / bs, pos_k = key_k0 - blk_k * bs, blk_v = key_v0 / bs, pos_v = key_v0 - blk_v * bs;
     load(0, entry(blk_k), pos_k, entry(blk_v), pos_v, R0);
     advance(blk_k, pos_k);
     advance(blk_v, pos_v);
@@ -493,7 +498,7 @@ tq_prefill_tc_kernel(PrefillArgs a) {
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       // causal limit, maximum (the key norms are inside the K operand)
-      const int vis = lim - PT_KT * j;            // keys of this tile the row may see (<= 0: none, >= PT_KT: all)
+      const int vis = lim - PT_KT * (jbase + j);  // keys of this tile the row may see (<= 0: none, >= PT_KT: all)
       if (vis < PT_KT) {
 #pragma unroll
         for (int i = 0; i < PT_KT; ++i) v[i] = i < vis ? v[i] : 0xff800000u;
@@ -545,7 +550,7 @@ tq_prefill_tc_kernel(PrefillArgs a) {
     // ---- un-normalised rows for the merge kernel ----
     if (ok && wait_warp(bar_s + B_PVDONE + 8 * (uint32_t)((n_ktiles - 1) & 1), par2(n_ktiles - 1))) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int64_t row = (int64_t)(q0 + tok) * a.num_q_heads + kvh * G + r % G;
+      const int64_t row = ((int64_t)(q0 + tok) * a.num_q_heads + kvh * G + r % G) * gridDim.z + blockIdx.z;      // (row, partial)
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t o[32];
@@ -749,7 +754,7 @@ int prefill_staged_tile_keys() { return PS_KT; }
 
 int launch_prefill_tc(const PrefillArgs& a, int G, cudaStream_t st) {
   const int TT = 128 / G;
-  dim3 grid((a.n_tokens + TT - 1) / TT + a.num_seqs, a.num_kv_heads);
+  dim3 grid((a.n_tokens + TT - 1) / TT + a.num_seqs, a.num_kv_heads, a.splits > 0 ? a.splits : 1);
   cudaError_t e = cudaSuccess;
   if (a.staged != nullptr) {
     // operand images first (ordered before the attention kernel by the stream), then the bulk-copy-fed kernel

@@ -770,7 +770,7 @@ def test_prefill_tensor_core_kernel_bounded_wait_gives_up_and_reports():
     assert good is not None and not any(_lib.device_status().values())
     assert L.akv_last_split_kernel() == b"tq_prefill_attn_tc_kernel"
     try:
-        assert L.akv_debug_tc_withhold(2, 1) == 0
+        assert L.akv_debug_tc_withhold(2, 0) == 0      # the first key tile of every share of CTA (0, 0)
         attn.prefill(query, kp, kn, vp, vn, bt, sl, qsl, block_size=bs, num_kv_heads=H)
         st = _lib.device_status(reset=True)
         assert st["attn_window"] == 2
