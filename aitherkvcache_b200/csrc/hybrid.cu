@@ -1959,10 +1959,103 @@ hybrid_prefill_stage35_kernel(PrefillArgs a, HybridTables t) {
   for (int i = tid; i < PFI_BYTES / 16; i += HC_THREADS) dst[i] = reinterpret_cast<const uint4*>(hp_image)[i];
 }
 
+// The same for any dim split (tq25: 32 + 96 dims, 44-byte records): one thread per record, the decode of
+// hybrid_decode_kernel, 64 records per pass.
+template <int G0, int B0, int G1, int B1>
+__global__ void __launch_bounds__(HY_THREADS)
+hybrid_prefill_stage_kernel(PrefillArgs a, HybridTables t) {
+  constexpr int D = G0 + G1;
+  static_assert(D == 128, "head_dim 128");
+  constexpr int BYTES0 = (G0 * B0 + 7) / 8 + (G0 + 7) / 8 + 4;
+  constexpr int BYTES1 = (G1 * B1 + 7) / 8 + (G1 + 7) / 8 + 4;
+  extern __shared__ __align__(16) uint8_t hp_image[];            // PFI_BYTES
+  __shared__ float xs[HY_THREADS * HY_LD];
+  __shared__ float s_had[D], s_qjl[D], s_cent[16];
+  __shared__ int s_idx[D];
+  const int tid = threadIdx.x;
+  const int s = blockIdx.y, kvh = blockIdx.z, tile = blockIdx.x;
+  const int64_t max_ctx = (int64_t)a.max_blocks_per_seq * a.block_size;
+  const int seq_len = (int)load_ctx(a.seq_lens, a.sl_dtype, s, max_ctx);
+  int n_tiles = (seq_len + PFI_KEYS - 1) / PFI_KEYS;
+  if (n_tiles > a.tiles_per_seq) n_tiles = a.tiles_per_seq;
+  if (tile >= n_tiles) return;
+  const int* gsrc = t.group_index + (t.num_index_heads > 1 ? (kvh % t.num_index_heads) * D : 0);
+  for (int i = tid; i < D; i += HY_THREADS) { s_had[i] = t.had_signs[i]; s_qjl[i] = t.qjl_signs[i]; s_idx[i] = gsrc[i]; }
+  if (tid < 16) s_cent[tid] = t.centroids[tid];
+  const int bs = a.block_size;
+  for (int side = 0; side < 2; ++side) {
+    const uint8_t* cache = side ? a.v_packed : a.k_packed;
+    const int64_t sb = side ? a.vp_sb : a.kp_sb, sp = side ? a.vp_sp : a.kp_sp, sh = side ? a.vp_sh : a.kp_sh;
+    for (int pass = 0; pass < PFI_KEYS / HY_THREADS; ++pass) {
+      __syncthreads();                 // tables staged; the previous pass's rows have been read
+      const int key0 = PFI_KEYS * tile + HY_THREADS * pass;
+      {
+        const int key = key0 + tid;
+        int blk = key / bs;
+        if (blk >= a.max_blocks_per_seq) blk = a.max_blocks_per_seq - 1;
+        int64_t pb = load_index(a.block_tables, a.bt_dtype, (int64_t)s * a.bt_stride + blk);
+        pb = pb < 0 ? 0 : (pb >= a.num_blocks ? a.num_blocks - 1 : pb);
+        const uint8_t* src = cache + pb * sb + (int64_t)(key - (key / bs) * bs) * sp + (int64_t)kvh * sh;
+        uint8_t rec[BYTES0 + BYTES1];
+#pragma unroll
+        for (int wd = 0; wd < (BYTES0 + BYTES1) / 4; ++wd) {      // records are 4-byte aligned (checked by the host)
+          const uint32_t v = reinterpret_cast<const uint32_t*>(src)[wd];
+          rec[4 * wd] = (uint8_t)v; rec[4 * wd + 1] = (uint8_t)(v >> 8);
+          rec[4 * wd + 2] = (uint8_t)(v >> 16); rec[4 * wd + 3] = (uint8_t)(v >> 24);
+        }
+        decode_group<G0, B0>(rec, s_idx, s_had, s_qjl, s_cent, t.qjl_scale0, xs + tid * HY_LD);
+        decode_group<G1, B1>(rec + BYTES0, s_idx + G0, s_had + G0, s_qjl + G0, s_cent + 8, t.qjl_scale1, xs + tid * HY_LD);
+      }
+      __syncthreads();
+      if (side == 0) {
+        for (int e = tid; e < HY_THREADS * 16; e += HY_THREADS) {
+          const int r = e >> 4, c = e & 15;
+          const bool live = key0 + r < seq_len;
+          const float* x = xs + r * HY_LD + 8 * c;
+          __half2 h[4] = {__floats2half2_rn(x[0], x[1]), __floats2half2_rn(x[2], x[3]), __floats2half2_rn(x[4], x[5]), __floats2half2_rn(x[6], x[7])};
+          uint4 w = *reinterpret_cast<uint4*>(h);
+          if (!live) w = make_uint4(0u, 0u, 0u, 0u);
+          const int row = HY_THREADS * pass + r;
+          *reinterpret_cast<uint4*>(hp_image + (c >> 3) * PFI_KHALF + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = w;
+        }
+      } else {
+        for (int e = tid; e < (HY_THREADS / 8) * 128; e += HY_THREADS) {
+          const int gl = e >> 7, d = e & 127;
+          float v[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = key0 + 8 * gl + i < seq_len ? xs[(8 * gl + i) * HY_LD + d] : 0.f;
+          __half2 h[4] = {__floats2half2_rn(v[0], v[1]), __floats2half2_rn(v[2], v[3]), __floats2half2_rn(v[4], v[5]), __floats2half2_rn(v[6], v[7])};
+          const int g = (HY_THREADS / 8) * pass + gl;
+          *reinterpret_cast<uint4*>(hp_image + PFI_VOFF + (g >> 3) * PFI_VHALF + d * 128 + (((g & 7) ^ (d & 7)) << 4)) =
+              *reinterpret_cast<uint4*>(h);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  uint4* dst = reinterpret_cast<uint4*>(a.staged + (((int64_t)s * a.tiles_per_seq + tile) * a.num_kv_heads + kvh) * PFI_BYTES);
+  for (int i = tid; i < PFI_BYTES / 16; i += HY_THREADS) dst[i] = reinterpret_cast<const uint4*>(hp_image)[i];
+}
+
 int akv::launch_hybrid_prefill_stage(const PrefillArgs& a, cudaStream_t st) {
   HybridTables t; int mode;
   if (int rc = tables_from(reinterpret_cast<const akv_hybrid_tables*>(a.hybrid_tables), &t, &mode)) return rc;
-  if (mode != 35) return fail(AKV_ERR_UNSUPPORTED, "staged prefill attention reads tq35 records only");
+  const uintptr_t al = reinterpret_cast<uintptr_t>(a.k_packed) | reinterpret_cast<uintptr_t>(a.v_packed) | (uintptr_t)a.kp_sb |
+                       (uintptr_t)a.kp_sp | (uintptr_t)a.kp_sh | (uintptr_t)a.vp_sb | (uintptr_t)a.vp_sp | (uintptr_t)a.vp_sh;
+  if (mode != 35 || (al & 15) != 0) {      // tq25, or tq35 records that cannot be read in 16-byte pieces
+    if ((al & 3) != 0) return fail(AKV_ERR_UNSUPPORTED, "staged prefill attention needs records readable in 4-byte pieces");
+    dim3 grid(a.tiles_per_seq, a.num_seqs, a.num_kv_heads);
+    cudaError_t e;
+    if (mode == 35) {
+      e = cudaFuncSetAttribute(hybrid_prefill_stage_kernel<64, 3, 64, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PFI_BYTES);
+      if (e == cudaSuccess) hybrid_prefill_stage_kernel<64, 3, 64, 2><<<grid, HY_THREADS, PFI_BYTES, st>>>(a, t);
+    } else {
+      e = cudaFuncSetAttribute(hybrid_prefill_stage_kernel<32, 2, 96, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PFI_BYTES);
+      if (e == cudaSuccess) hybrid_prefill_stage_kernel<32, 2, 96, 1><<<grid, HY_THREADS, PFI_BYTES, st>>>(a, t);
+    }
+    if (e != cudaSuccess) return fail((int)e, "prefill attention: smem attribute: %s", cudaGetErrorString(e));
+    return check_launch("hybrid_prefill_stage_kernel");
+  }
   cudaError_t e = cudaFuncSetAttribute(hybrid_prefill_stage35_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PFI_BYTES);
   if (e != cudaSuccess) return fail((int)e, "prefill attention: smem attribute: %s", cudaGetErrorString(e));
   dim3 grid(a.tiles_per_seq, a.num_seqs, a.num_kv_heads);

@@ -2784,8 +2784,8 @@ AKV_EXPORT int akv_tq_prefill_attn(const akv_tq_prefill_params* p) {
   const bool low_bits = p->bits == 3 || p->bits == 2 || hybrid;      // ... 3- and 2-bit codes
   if (hybrid && ((reinterpret_cast<uintptr_t>(p->k_packed) | reinterpret_cast<uintptr_t>(p->v_packed) | (uintptr_t)p->kp_stride_blk |
                   (uintptr_t)p->kp_stride_pos | (uintptr_t)p->kp_stride_head | (uintptr_t)p->vp_stride_blk |
-                  (uintptr_t)p->vp_stride_pos | (uintptr_t)p->vp_stride_head) & 15) != 0)
-    return fail(AKV_ERR_UNSUPPORTED, "prefill attention over tq35 records needs records readable in 16-byte pieces");
+                  (uintptr_t)p->vp_stride_pos | (uintptr_t)p->vp_stride_head) & 3) != 0)
+    return fail(AKV_ERR_UNSUPPORTED, "prefill attention over hybrid records needs records readable in 4-byte pieces");
   if (p->head_dim != 128 || (p->bits != 4 && !low_bits) || (G != 1 && G != 2 && G != 4 && G != 8) || p->block_size % 16 != 0 ||
       (!low_bits && (!al16(p->k_packed, p->kp_stride_blk, p->kp_stride_pos, p->kp_stride_head) ||
                      !al16(p->v_packed, p->vp_stride_blk, p->vp_stride_pos, p->vp_stride_head))))

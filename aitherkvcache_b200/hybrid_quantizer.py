@@ -305,10 +305,10 @@ class HybridPagedAttention:
     def prefill(self, query, k_cache, v_cache, block_tables, seq_lens, query_start_loc, block_size: int = 16,
                 num_kv_heads: Optional[int] = None, out: Optional[torch.Tensor] = None, scale: Optional[float] = None,
                 max_seq_len: Optional[int] = None) -> Optional[torch.Tensor]:
-        """Chunked-prefill attention over tq35 records (arguments as ``TQPagedAttention.prefill``): the records of every
+        """Chunked-prefill attention over tq35 / tq25 records (arguments as ``TQPagedAttention.prefill``): the records of every
         128-key tile are decoded once into fp16 operand images, then the tensor-core attention kernel runs over them
         (``akv_tq_prefill_attn`` with ``hybrid_tables``).  The reference decompresses the active blocks and calls vLLM's
-        unified attention (``vllm/hooks.py:726-850``).  Returns None when that kernel does not serve the case (tq25, no
+        unified attention (``vllm/hooks.py:726-850``).  Returns None when that kernel does not serve the case (no
         host-side ``max_seq_len``, a batch too ragged for 128-row tiles, scratch beyond ``STAGED_WORKSPACE_LIMIT``): the
         caller then attends row by row with ``forward``."""
         if num_kv_heads is None:
@@ -316,9 +316,10 @@ class HybridPagedAttention:
         dev = _lib.require_cuda(query, k_cache, v_cache, block_tables, seq_lens, query_start_loc)
         n_tok, num_q_heads, head_dim = query.shape
         G = num_q_heads // num_kv_heads
-        aligned = all((t.data_ptr() | t.stride(0) | t.stride(1) | t.stride(2)) % 16 == 0 for t in (k_cache, v_cache))
-        if (self.htq.mode != "tq35" or head_dim != 128 or G not in (1, 2, 4, 8) or block_size % 16 or not aligned
-                or not max_seq_len or k_cache.shape[-1] < 64 or v_cache.shape[-1] < 64):
+        aligned = all((t.data_ptr() | t.stride(0) | t.stride(1) | t.stride(2)) % 4 == 0 for t in (k_cache, v_cache))
+        pd = self.htq.layout.packed_dim
+        if (head_dim != 128 or G not in (1, 2, 4, 8) or block_size % 16 or not aligned
+                or not max_seq_len or k_cache.shape[-1] < pd or v_cache.shape[-1] < pd):
             return None
         assert num_q_heads == self.num_query_heads and k_cache.shape[1] == block_size
         num_seqs = query_start_loc.numel() - 1

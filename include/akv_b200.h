@@ -177,8 +177,8 @@ typedef struct akv_tq_prefill_params {
   void* workspace; size_t workspace_bytes;   /* akv_tq_prefill_attn_workspace_bytes(num_tokens, num_q_heads) */
   void* stream;
   int max_seq_len;   /* longest entry of seq_lens if the host knows it (vLLM's metadata does), else 0 */
-  /* NULL, or the tables of a tq35 cache (HOST pointer, see akv_hybrid_tables below): k_packed / v_packed are then the
-   * 64-byte records [num_blocks, block_size, num_kv_heads, 64], the norm arrays, bits and centroids are ignored, and
+  /* NULL, or the tables of a tq35 / tq25 cache (HOST pointer, see akv_hybrid_tables below): k_packed / v_packed are then
+   * the 64- / 44-byte records [num_blocks, block_size, num_kv_heads, packed_dim], the norm arrays, bits and centroids are ignored, and
    * the attention runs in the original domain - pass identity matrices as rotation and rotation_t.  Staged kernel
    * only (max_seq_len and the staged workspace).  Replaces the decompress-then-attend prefill of the hybrid modes
    * (vllm/hooks.py:726-850). */

@@ -203,16 +203,17 @@ def test_paged_attention_full_size_random_values_vs_oracle():
     assert np.abs(out[pick] - ref).max() < 2e-3
 
 
+@pytest.mark.parametrize("mode", ("tq35", "tq25"))
 @pytest.mark.parametrize("H,QH", [(8, 32), (2, 16), (2, 2)])
-def test_chunked_prefill_over_tq35_records(H, QH):
-    """Chunked prefill over a tq35 cache: the pre-pass decodes every 128-key tile of records into fp16 operand images, the
-    tensor-core attention kernel runs over them in the original domain.  Against the record-domain decode kernel row by
-    row (all rows) and the oracle (decode -> fp16 -> attention) on the last row of each chunk."""
+def test_chunked_prefill_over_hybrid_records(H, QH, mode):
+    """Chunked prefill over a tq35 / tq25 cache: the pre-pass decodes every 128-key tile of records into fp16 operand
+    images, the tensor-core attention kernel runs over them in the original domain.  Against the record-domain decode
+    kernel row by row (all rows) and the oracle (decode -> fp16 -> attention) on the last row of each chunk."""
     from aitherkvcache_b200 import _lib
     from aitherkvcache_b200.hybrid_quantizer import HybridPagedAttention
-    g = load_golden("hybrid_tq35.npz")
-    h = _htq("tq35", g, heads=1)
-    t = _oracle_tables(g, "tq35")
+    g = load_golden(f"hybrid_{mode}.npz")
+    h = _htq(mode, g, heads=1)
+    t = _oracle_tables(g, mode)
     gen = torch.Generator().manual_seed(21 + H)
     bs = 16
     seqs = [(500, 140), (0, 200), (130, 128)]          # (cached before the chunk, chunk length)
