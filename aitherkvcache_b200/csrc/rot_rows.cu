@@ -19,7 +19,8 @@ namespace {
 constexpr int RR_THREADS = 256;
 constexpr int RR_LD = 136;                                   // halves per padded row
 constexpr int RR_MAT = 128 * RR_LD * 2;                      // one fp16 term of a 128 x 128 operand
-constexpr int RR_SMEM = 4 * RR_MAT;                          // M1, M2 (as [j][i]), A1, A2 (as [row][i])
+// M1, M2 (as [j][i], the CTA's 8 NJ columns), A1, A2 (as [row][i]); a column-split CTA leaves room for a second one per SM
+constexpr int rr_smem(int nj) { return 2 * (8 * nj) * RR_LD * 2 + 2 * RR_MAT; }
 
 struct RotRowsArgs {
   const void* src; int src_dtype; int64_t src_outer, src_inner; int inner;   // row r = (r / inner, r % inner); strides in elements
@@ -38,12 +39,12 @@ __device__ __forceinline__ void rr_mma(float (&d)[4], uint32_t a0, uint32_t a1, 
 }
 
 template <int NJ>        // n-tiles (8 columns each) of this CTA: 16, 8 or 4
-__global__ void __launch_bounds__(RR_THREADS, 1)
+__global__ void __launch_bounds__(RR_THREADS, NJ == 16 ? 1 : 2)
 akv_rot_rows_kernel(RotRowsArgs a) {
-  extern __shared__ __align__(16) unsigned char rr_smem[];
-  __half* m1 = reinterpret_cast<__half*>(rr_smem);
-  __half* m2 = m1 + 128 * RR_LD;
-  __half* a1 = m2 + 128 * RR_LD;
+  extern __shared__ __align__(16) unsigned char rr_smem_raw[];
+  __half* m1 = reinterpret_cast<__half*>(rr_smem_raw);
+  __half* m2 = m1 + 8 * NJ * RR_LD;
+  __half* a1 = m2 + 8 * NJ * RR_LD;
   __half* a2 = a1 + 128 * RR_LD;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int j0 = blockIdx.y * (8 * NJ);          // first column of this CTA
@@ -195,19 +196,21 @@ int launch_rot_rows(const void* src, int src_dtype, int64_t src_outer, int64_t s
   a.inv_l = inv_l; a.inv_stride = inv_stride; a.mat = mat; a.scale = scale;
   a.out = out; a.out_dtype = out_dtype; a.out_outer = out_outer; a.out_inner = out_inner; a.rows = rows;
   const int64_t tiles = (rows + 127) / 128;
-  const int split = 4 * tiles <= sm_count() ? 4 : (2 * tiles <= sm_count() ? 2 : 1);      // column split: CTAs <= SMs
-  const int per = sm_count() / split;
+  // column split 4, 2 or 1: the largest that keeps the CTAs within what the GPU holds at once (two split CTAs per SM)
+  const int64_t room = 2 * (int64_t)sm_count();
+  const int split = 4 * tiles <= room ? 4 : (2 * tiles <= room ? 2 : 1);
+  const int64_t per = split == 1 ? sm_count() : room / split;
   dim3 grid((unsigned)(tiles < per ? tiles : per), split);
   cudaError_t e;
   if (split == 4) {
-    e = cudaFuncSetAttribute(akv_rot_rows_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, RR_SMEM);
-    if (e == cudaSuccess) akv_rot_rows_kernel<4><<<grid, RR_THREADS, RR_SMEM, st>>>(a);
+    e = cudaFuncSetAttribute(akv_rot_rows_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, rr_smem(4));
+    if (e == cudaSuccess) akv_rot_rows_kernel<4><<<grid, RR_THREADS, rr_smem(4), st>>>(a);
   } else if (split == 2) {
-    e = cudaFuncSetAttribute(akv_rot_rows_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, RR_SMEM);
-    if (e == cudaSuccess) akv_rot_rows_kernel<8><<<grid, RR_THREADS, RR_SMEM, st>>>(a);
+    e = cudaFuncSetAttribute(akv_rot_rows_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, rr_smem(8));
+    if (e == cudaSuccess) akv_rot_rows_kernel<8><<<grid, RR_THREADS, rr_smem(8), st>>>(a);
   } else {
-    e = cudaFuncSetAttribute(akv_rot_rows_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, RR_SMEM);
-    if (e == cudaSuccess) akv_rot_rows_kernel<16><<<grid, RR_THREADS, RR_SMEM, st>>>(a);
+    e = cudaFuncSetAttribute(akv_rot_rows_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, rr_smem(16));
+    if (e == cudaSuccess) akv_rot_rows_kernel<16><<<grid, RR_THREADS, rr_smem(16), st>>>(a);
   }
   if (e != cudaSuccess) return fail((int)e, "row rotation: smem attribute: %s", cudaGetErrorString(e));
   return check_launch("akv_rot_rows_kernel");
