@@ -457,6 +457,63 @@ akv_merge128_kernel(MergeArgs a, int rows, int np_alloc) {
   asm volatile("cp.async.wait_group 0;\n" ::: "memory");
 }
 
+// Normalise-only LSE merge for many rows, D = 128: one warp per row (lane = four dims), eight rows per CTA, grid-stride.
+// Same arithmetic and order of operations per element as akv_merge_kernel (weights 2^(m_p - M) for parts with l_p > 0,
+// four accumulation chains by part number modulo 4, one division by L); float32 rows out.
+__global__ void __launch_bounds__(256)
+akv_merge_norm_rows_kernel(MergeArgs a, int rows) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int row = blockIdx.x * 8 + warp; row < rows; row += gridDim.x * 8) {
+    const int seq = row / a.num_q_heads, qh = row % a.num_q_heads;
+    int np = a.np;
+    if (a.part_counts != nullptr) {
+      np = a.part_counts[seq] < np ? a.part_counts[seq] : np;
+    } else if (a.context_lens != nullptr) {
+      const int64_t ctx = load_index(a.context_lens, a.cl_dtype, seq);
+      const int64_t splits = (ctx + a.tokens_per_split - 1) / a.tokens_per_split;
+      const int64_t v = splits * a.warps_per_head;
+      np = (int)(v < np ? v : np);
+    }
+    const float* ml = a.ml + merge_half_offset(a) + (int64_t)row * a.ml_row;
+    const float* acc = a.acc + merge_half_offset(a) + (int64_t)row * a.acc_row + 4 * lane;
+    float M = -CUDART_INF_F;
+    for (int p = lane; p < np; p += 32) {
+      const float m = ml[(int64_t)p * a.ml_part], l = ml[(int64_t)p * a.ml_part + 1];
+      if (l > 0.f) M = fmaxf(M, m);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    float L = 0.f;
+    for (int p = lane; p < np; p += 32) {
+      const float l = ml[(int64_t)p * a.ml_part + 1];
+      const float w = (l > 0.f) ? exp2f(ml[(int64_t)p * a.ml_part] - M) : 0.f;
+      L += l * w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+    float o4[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o4[i][0] = o4[i][1] = o4[i][2] = o4[i][3] = 0.f;
+    for (int p = 0; p < np; ++p) {
+      const float l = ml[(int64_t)p * a.ml_part + 1];                 // the same address in all lanes: one broadcast load
+      const float w = (l > 0.f) ? exp2f(ml[(int64_t)p * a.ml_part] - M) : 0.f;
+      if (w != 0.f) {
+        const float4 x = *reinterpret_cast<const float4*>(acc + (int64_t)p * a.acc_part);
+        o4[0][p & 3] = __fmaf_rn(x.x, w, o4[0][p & 3]); o4[1][p & 3] = __fmaf_rn(x.y, w, o4[1][p & 3]);
+        o4[2][p & 3] = __fmaf_rn(x.z, w, o4[2][p & 3]); o4[3][p & 3] = __fmaf_rn(x.w, w, o4[3][p & 3]);
+      }
+    }
+    float v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float o = (o4[i][0] + o4[i][1]) + (o4[i][2] + o4[i][3]);
+      v[i] = (L > 0.f) ? o / L : 0.f;
+    }
+    *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + (int64_t)seq * a.out_ss + (int64_t)qh * a.out_sh + 4 * lane) =
+        make_float4(v[0], v[1], v[2], v[3]);
+  }
+}
+
 int launch_merge(const MergeArgs& a, int rows, cudaStream_t st, bool pdl) {
   const int np_alloc = a.np > 0 ? a.np : 1;
   static const bool no_rot128 = getenv("AKV_NO_ROT128") != nullptr;
@@ -467,8 +524,16 @@ int launch_merge(const MergeArgs& a, int rows, cudaStream_t st, bool pdl) {
     n.mode = MERGE_NORMALIZE;
     n.out = a.gemm_scratch; n.out_dtype = AKV_F32; n.out_ss = (int64_t)a.num_q_heads * 128; n.out_sh = 128;
     n.gemm_scratch = nullptr;
-    akv_merge_kernel<<<rows, 128, (128 + np_alloc) * sizeof(float), st>>>(n);
-    if (int rc = check_launch("akv_merge_kernel")) return rc;
+    const bool vec = ((reinterpret_cast<uintptr_t>(a.acc) | (uintptr_t)(a.acc_row * 4) | (uintptr_t)(a.acc_part * 4) |
+                       (uintptr_t)(a.half_stride * 4)) & 15) == 0;
+    if (vec) {
+      const int ctas = (rows + 7) / 8;
+      akv_merge_norm_rows_kernel<<<ctas < 8 * sm_count() ? ctas : 8 * sm_count(), 256, 0, st>>>(n, rows);
+      if (int rc = check_launch("akv_merge_norm_rows_kernel")) return rc;
+    } else {
+      akv_merge_kernel<<<rows, 128, (128 + np_alloc) * sizeof(float), st>>>(n);
+      if (int rc = check_launch("akv_merge_kernel")) return rc;
+    }
     // ... then out = R^T x for all rows at once
     return launch_rot_rows(a.gemm_scratch, AKV_F32, (int64_t)a.num_q_heads * 128, 128, a.num_q_heads, nullptr, 0, a.rot, 1.0f,
                            a.out, a.out_dtype, a.out_ss, a.out_sh, rows, st);
