@@ -65,12 +65,15 @@ def test_decode_step_op(bits):
     assert np.abs(out[:S].float().cpu().numpy() - ref).max() < 2e-3
 
 
-def test_decode_step_single_call_matches_stepwise_path():
+@pytest.mark.parametrize("nseq", (3, 72))
+def test_decode_step_single_call_matches_stepwise_path(nseq):
     """The one-call entry point and the step-by-step path (taken here through an int32 slot mapping)
     write the same cache bytes and return the same output; the cached argument block survives a
-    second step with different inputs."""
+    second step with different inputs.  72 sequences x 32 heads = 2304 rows: both rotations run as
+    tensor-core products while the new token's vectors keep their blocks of the plan launch."""
     from aitherkvcache_b200.vllm import ops
-    H, QH, ctx = 8, 32, [300, 17, 64]
+    H, QH = 8, 32
+    ctx = [300, 17, 64] + [int(v) for v in np.random.default_rng(5).integers(1, 120, nseq - 3)]
     outs, caches = [], []
     for slot_dtype in (torch.int64, torch.int32):
         t, d, kv, kn, vn, q, key, val, slots = _setup_decode(4, H, QH, ctx, 77)
