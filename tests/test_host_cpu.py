@@ -213,3 +213,46 @@ def test_primary_mode_page_sizes_and_vllm_patch(monkeypatch):
     monkeypatch.delenv("AITHER_TQ_MODE")
     from aitherkvcache_b200.vllm.backend import TurboQuantBackend
     assert TurboQuantBackend.get_kv_cache_shape(10, 16, 8, 128) == (10, 2, 16, 8, 128)
+
+
+def test_backend_mixed_batch_routing_on_the_host():
+    """TurboQuantImplBase.forward on a batch with chunks and single tokens, kernels replaced by recording fakes (no
+    GPU): the prefill side sees length zero for the single-token sequences, the decode side for the others, every query
+    row is written exactly once and by the right side; a batch of equal chunks skips the decode side."""
+    import types
+    from aitherkvcache_b200.vllm.backend import TurboQuantImplBase
+    impl = TurboQuantImplBase()
+    impl._tq_setup(4, 128, 0.1, 2, "auto")
+    calls = {}
+
+    def fake_prefill(layer, q, out, kv_cache, md):
+        calls["prefill"] = (md.seq_lens.clone(), md.query_start_loc.clone(), getattr(md, "max_seq_len", None))
+        qsl = md.query_start_loc.tolist()
+        for s, n in enumerate(md.seq_lens.tolist()):
+            out[qsl[s]:qsl[s + 1]] = 100.0 + s if n > 0 else 0.0      # the kernels write zeros for rows of empty sequences
+        return True
+
+    def fake_attend(layer, q, out, kv_cache, block_table, context_lens):
+        calls["attend"] = (context_lens.clone(), q.clone())
+        for s, n in enumerate(context_lens.tolist()):
+            out[s] = 200.0 + s if n > 0 else 0.0
+
+    impl._prefill, impl._attend = fake_prefill, fake_attend
+    qsl = torch.tensor([0, 5, 6, 9, 10], dtype=torch.int32)            # chunk lengths 5, 1, 3, 1
+    seq_lens = torch.tensor([50, 7, 3, 90], dtype=torch.int32)
+    md = types.SimpleNamespace(num_actual_tokens=10, max_query_len=5, block_table=torch.zeros(4, 8, dtype=torch.int32),
+                               seq_lens=seq_lens, query_start_loc=qsl, max_seq_len=90)
+    query = torch.arange(10, dtype=torch.float32)[:, None].expand(10, 4 * 128).contiguous()
+    out = torch.full((10, 4 * 128), -1.0)
+    impl.forward(None, query, None, None, torch.zeros(1), md, output=out)
+    assert calls["prefill"][0].tolist() == [50, 0, 3, 0] and calls["prefill"][2] == 90
+    assert calls["attend"][0].tolist() == [0, 7, 0, 90]
+    assert calls["attend"][1][:, 0, 0].tolist() == [0.0, 5.0, 6.0, 9.0]      # the first query row of every sequence
+    rows = out[:, 0].tolist()
+    assert rows == [100.0] * 5 + [201.0] + [102.0] * 3 + [203.0]
+    # four equal chunks: nothing for the decode kernels to do
+    calls.clear()
+    md2 = types.SimpleNamespace(num_actual_tokens=8, max_query_len=2, block_table=torch.zeros(4, 8, dtype=torch.int32),
+                                seq_lens=seq_lens, query_start_loc=torch.tensor([0, 2, 4, 6, 8], dtype=torch.int32))
+    impl.forward(None, query[:8].contiguous(), None, None, torch.zeros(1), md2, output=torch.zeros(8, 4 * 128))
+    assert "attend" not in calls and calls["prefill"][0].tolist() == [50, 7, 3, 90]
