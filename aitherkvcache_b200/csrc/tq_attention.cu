@@ -2846,14 +2846,15 @@ AKV_EXPORT int akv_tq_prefill_attn(const akv_tq_prefill_params* p) {
     return ((reinterpret_cast<uintptr_t>(q) | (uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) == 0;
   };
   const bool hybrid = p->hybrid_tables != nullptr;         // tq35 records: staged tensor-core kernel only, like ...
-  const bool low_bits = p->bits == 3 || p->bits == 2 || hybrid;      // ... 3- and 2-bit codes
+  // ... 3- and 2-bit codes and 4-bit rows that cannot be read in 16-byte pieces (68-byte records with the norm inside)
+  const bool rows16 = al16(p->k_packed, p->kp_stride_blk, p->kp_stride_pos, p->kp_stride_head) &&
+                      al16(p->v_packed, p->vp_stride_blk, p->vp_stride_pos, p->vp_stride_head);
+  const bool low_bits = p->bits == 3 || p->bits == 2 || hybrid || (p->bits == 4 && !rows16);
   if (hybrid && ((reinterpret_cast<uintptr_t>(p->k_packed) | reinterpret_cast<uintptr_t>(p->v_packed) | (uintptr_t)p->kp_stride_blk |
                   (uintptr_t)p->kp_stride_pos | (uintptr_t)p->kp_stride_head | (uintptr_t)p->vp_stride_blk |
                   (uintptr_t)p->vp_stride_pos | (uintptr_t)p->vp_stride_head) & 3) != 0)
     return fail(AKV_ERR_UNSUPPORTED, "prefill attention over hybrid records needs records readable in 4-byte pieces");
-  if (p->head_dim != 128 || (p->bits != 4 && !low_bits) || (G != 1 && G != 2 && G != 4 && G != 8) || p->block_size % 16 != 0 ||
-      (!low_bits && (!al16(p->k_packed, p->kp_stride_blk, p->kp_stride_pos, p->kp_stride_head) ||
-                     !al16(p->v_packed, p->vp_stride_blk, p->vp_stride_pos, p->vp_stride_head))))
+  if (p->head_dim != 128 || (p->bits != 4 && !low_bits) || (G != 1 && G != 2 && G != 4 && G != 8) || p->block_size % 16 != 0)
     return fail(AKV_ERR_UNSUPPORTED, "prefill attention is built for head_dim 128, 1/2/4/8 query heads per KV head, block sizes "
                                      "that are multiples of 16 and 4-bit caches readable in 16-byte pieces (3- and 2-bit "
                                      "caches: staged kernel only)");
@@ -2940,6 +2941,7 @@ AKV_EXPORT int akv_tq_prefill_attn(const akv_tq_prefill_params* p) {
     const size_t staged = no_staged ? 0 : prefill_staged_bytes(p->num_seqs, p->num_kv_heads, p->max_seq_len);
     const size_t staged_off = (total + 1023) & ~(size_t)1023;
     a.bits = p->bits;
+    a.byte_rows = rows16 ? 0 : 1;
     a.hybrid_tables = p->hybrid_tables;
     a.splits = splits;
     if (staged != 0 && p->workspace_bytes >= staged_off + staged && (reinterpret_cast<uintptr_t>(ws) & 15) == 0) {

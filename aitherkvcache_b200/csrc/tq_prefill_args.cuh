@@ -23,6 +23,7 @@ struct PrefillArgs {
   uint8_t* staged;
   int tiles_per_seq;
   int bits;                            // 4; 3 or 2 only with staged images
+  int byte_rows;                       // 4-bit rows that are not readable in 16-byte pieces: pre-pass by byte loads
   // tq35 records instead of TurboQuant codes (staged images only): host pointer to the akv_hybrid_tables of the call;
   // k_packed / v_packed are the 64-byte records, the norm arrays are unused
   const void* hybrid_tables;

@@ -761,9 +761,12 @@ int launch_prefill_tc(const PrefillArgs& a, int G, cudaStream_t st) {
     dim3 sgrid((a.tiles_per_seq + PS_TILES - 1) / PS_TILES, a.num_seqs, a.num_kv_heads);
     if (a.hybrid_tables != nullptr) {
       if (int rc = launch_hybrid_prefill_stage(a, st)) return rc;
-    } else if (a.bits == 4) {
+    } else if (a.bits == 4 && !a.byte_rows) {
       e = cudaFuncSetAttribute(tq_prefill_stage_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PS_SMEM);
       if (e == cudaSuccess) tq_prefill_stage_kernel<<<sgrid, PS_THREADS, PS_SMEM, st>>>(a);
+    } else if (a.bits == 4) {
+      e = cudaFuncSetAttribute(tq_prefill_stage_bits_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, PT_IMAGE);
+      if (e == cudaSuccess) tq_prefill_stage_bits_kernel<4><<<sgrid, PS_THREADS, PT_IMAGE, st>>>(a);
     } else if (a.bits == 3) {
       e = cudaFuncSetAttribute(tq_prefill_stage_bits_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, PT_IMAGE);
       if (e == cudaSuccess) tq_prefill_stage_bits_kernel<3><<<sgrid, PS_THREADS, PT_IMAGE, st>>>(a);

@@ -128,11 +128,11 @@ class TQPagedAttention:
         n_tok, num_q_heads, head_dim = query.shape
         G = num_q_heads // num_kv_heads
         aligned = all((t.data_ptr() | t.stride(0) | t.stride(1) | t.stride(2)) % 16 == 0 for t in (k_packed, v_packed))
-        if (head_dim != 128 or G not in (1, 2, 4, 8) or block_size % 16 or (self.bits == 4 and not aligned)
+        if (head_dim != 128 or G not in (1, 2, 4, 8) or block_size % 16
                 or k_norms.dtype != torch.float32 or v_norms.dtype != torch.float32):
             return None
-        if self.bits != 4 and not max_seq_len:      # 3- and 2-bit codes: staged tensor-core kernel only
-            return None
+        if (self.bits != 4 or not aligned) and not max_seq_len:
+            return None      # 3- / 2-bit codes and rows that are not readable in 16-byte pieces: staged tensor-core kernel only
         assert num_q_heads == self.num_query_heads and k_packed.shape[1] == block_size
         num_seqs = query_start_loc.numel() - 1
         if block_tables.dim() != 2 or block_tables.shape[0] < num_seqs or seq_lens.numel() < num_seqs:

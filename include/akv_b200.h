@@ -156,8 +156,8 @@ int akv_tq_paged_attn(const akv_tq_attn_params* params);
  *   seq_lens [num_seqs], query_start_loc [num_seqs + 1] int32 (dtype 0) or int64 (1);
  *   out [num_tokens, num_q_heads, 128]; rows beyond query_start_loc[num_seqs] come out as zeros.
  * Built for head_dim 128, 1 / 2 / 4 / 8 query heads per KV head, block_size % 16 == 0 and 4-bit code rows that
- * are readable in 16-byte pieces; 3- and 2-bit caches are served when max_seq_len and the staged workspace are
- * given and the chunk fills 128-row tiles.  Anything else returns AKV_ERR_UNSUPPORTED before any launch (attend
+ * are readable in 16-byte pieces; 3- and 2-bit caches and 4-bit rows of any alignment (68-byte records with the
+ * norm inside) are served when max_seq_len and the staged workspace are given and the chunk fills 128-row tiles.  Anything else returns AKV_ERR_UNSUPPORTED before any launch (attend
  * row by row with akv_tq_paged_attn then). */
 typedef struct akv_tq_prefill_params {
   const void* query; int q_dtype; int64_t q_stride_tok, q_stride_head;

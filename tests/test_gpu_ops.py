@@ -457,3 +457,39 @@ def test_backend_primary_records_keep_norms_in_the_row(monkeypatch, bits):
     kn = prim[:, 0, :, :, pd:].contiguous().view(torch.float32).squeeze(-1)
     assert torch.equal(kn, _LayerState.k_norms["sep.layers.0.attn"])
     assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("bits", (4, 3))
+def test_backend_primary_records_chunked_prefill(monkeypatch, bits):
+    """A prefill chunk over the primary-mode record layout (68- / 52-byte rows, norm inside, not readable in 16-byte
+    pieces) with vLLM's host-side length bound: the staged tensor-core kernel serves it (pre-pass by byte loads); rows
+    equal the decode kernels run token by token over the same cache."""
+    from aitherkvcache_b200 import _lib
+    from aitherkvcache_b200.vllm.backend import TurboQuantImplBase
+    monkeypatch.setenv("AITHER_TQ_MODE", f"tq{bits}-primary")
+    H, QH, bs, pd = 8, 32, 16, 128 * bits // 8
+    impl = TurboQuantImplBase()
+    impl._tq_setup(QH, 128, 1.0 / math.sqrt(128), H, "auto")
+    layer = types.SimpleNamespace(layer_name=f"primchunk{bits}.layers.0.attn")
+    n, chunk = 330, 96
+    nb = (n + bs - 1) // bs
+    gen = torch.Generator().manual_seed(9)
+    bt = torch.randperm(nb + 2, generator=gen)[:nb].to(torch.int32).reshape(1, nb)
+    kv = torch.zeros(nb + 2, 2, bs, H, pd + 4, dtype=torch.uint8, device="cuda")
+    key = torch.randn(n, H, 128, generator=gen).half().cuda()
+    val = torch.randn(n, H, 128, generator=gen).half().cuda()
+    slots = (bt[0].long()[:, None] * bs + torch.arange(bs)[None]).reshape(-1)[:n].cuda()
+    impl.do_kv_cache_update(layer, key, val, kv, slots)
+    q = torch.randn(chunk, QH * 128, generator=gen).half().cuda()
+    md = types.SimpleNamespace(num_actual_tokens=chunk, max_query_len=chunk, block_table=bt.cuda(), max_seq_len=n,
+                               seq_lens=torch.tensor([n], dtype=torch.int32, device="cuda"),
+                               query_start_loc=torch.tensor([0, chunk], dtype=torch.int32, device="cuda"))
+    out = torch.zeros(chunk, QH * 128, dtype=torch.float16, device="cuda")
+    impl.forward(layer, q, None, None, kv, md, output=out)
+    assert _lib.lib().akv_last_split_kernel() == b"tq_prefill_attn_tc_staged_kernel"
+    # token by token: every query token as its own single-token sequence
+    md1 = types.SimpleNamespace(num_actual_tokens=chunk, max_query_len=1, block_table=bt.expand(chunk, -1).contiguous().cuda(),
+                                seq_lens=torch.arange(n - chunk + 1, n + 1, dtype=torch.int32, device="cuda"))
+    ref = torch.zeros_like(out)
+    impl.forward(layer, q, None, None, kv, md1, output=ref)
+    assert ((out.float() - ref.float()).abs() <= 2e-3 * ref.float().abs().clamp(min=1.0)).all()
