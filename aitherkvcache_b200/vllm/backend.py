@@ -111,8 +111,40 @@ class TurboQuantImplBase:
             self.tq_mode, self.tq_bits = "", int(what)
             self.packed_dim = head_size * self.tq_bits // 8
 
+    def _planar(self, kv_cache: torch.Tensor) -> bool:
+        """Primary-mode pages of the uniform codecs are laid out in planes unless ``AITHER_TQ_RECORD_PAGES`` is set: in
+        each of a block's K and V halves first the codes of all (position, head) rows, then their float32 norms.  The
+        bytes per block are those of the reference's pages (``vllm/engine.py:125-133`` puts the norm behind the codes
+        of the same row: 68-byte rows at 4 bits), but code rows start on 16-byte boundaries, which the TMA-fed decode
+        kernel and the vectorised prefill pre-pass need - attention over 68-byte rows runs at half the speed."""
+        pd = self.packed_dim
+        return (self.tq_codec == "uniform" and kv_cache.dim() == 5 and kv_cache.shape[-1] == pd + 4 and pd % 4 == 0
+                and kv_cache.is_contiguous() and (kv_cache.shape[2] * kv_cache.shape[3] * pd) % 16 == 0
+                and not os.environ.get("AITHER_TQ_RECORD_PAGES"))
+
+    def _planes(self, kv_cache: torch.Tensor):
+        """(codes [blocks, 2, block_size, heads, packed_dim] uint8, norms [blocks, 2, block_size, heads] float32): views
+        of a planar primary-mode cache, nothing is copied."""
+        nb, _, bs, H, W = kv_cache.shape
+        pd = self.packed_dim
+        flat = kv_cache.view(nb, 2, bs * H * W)
+        codes = flat[:, :, :bs * H * pd].view(nb, 2, bs, H, pd)
+        norms = flat[:, :, bs * H * pd:].view(torch.float32).view(nb, 2, bs, H)
+        return codes, norms
+
+    def _codes(self, kv_cache: torch.Tensor):
+        """The K and V code (or record) rows [blocks, block_size, heads, packed_dim] of a cache in any layout."""
+        if self._planar(kv_cache):
+            codes, _ = self._planes(kv_cache)
+            return codes[:, 0], codes[:, 1]
+        pd = self.packed_dim
+        return kv_cache[:, 0, :, :, :pd], kv_cache[:, 1, :, :, :pd]
+
     def _norms(self, layer_name: str, kv_cache: torch.Tensor):
         pd = self.packed_dim
+        if self._planar(kv_cache):
+            _, norms = self._planes(kv_cache)
+            return norms[:, 0], norms[:, 1]
         if kv_cache.shape[-1] == pd + 4 and pd % 4 == 0:
             # primary-mode records: the norm is the float32 behind the codes of the same row
             # (reference page layout, vllm/engine.py:125-133); strided views, nothing is copied
@@ -135,19 +167,19 @@ class TurboQuantImplBase:
         if self.tq_codec == "hybrid":
             from ..hybrid_quantizer import hybrid_kv_update
             htq = _hybrid_quantizer(self.head_size, self.tq_mode, kv_cache.device)
-            for x, side in ((key, 0), (value, 1)):
-                hybrid_kv_update(htq, x, slot_mapping, kv_cache[:, side, :, :, :pd], bs, kv_cache.shape[0])
+            for x, rows in zip((key, value), self._codes(kv_cache)):
+                hybrid_kv_update(htq, x, slot_mapping, rows, bs, kv_cache.shape[0])
             return
         from ..fused_kv_update import fused_tq4_kv_update
         tq = _quantizer(self.head_size, self.tq_bits, kv_cache.device)
         kn, vn = self._norms(getattr(layer, "layer_name", "layer"), kv_cache)
-        for x, side, norms in ((key, 0, kn), (value, 1, vn)):
-            fused_tq4_kv_update(x, slot_mapping, kv_cache[:, side, :, :, :pd], norms, tq.rotation,
+        for x, rows, norms in zip((key, value), self._codes(kv_cache), (kn, vn)):
+            fused_tq4_kv_update(x, slot_mapping, rows, norms, tq.rotation,
                                 tq.boundaries_inner, bs, kv_cache.shape[0], rotation_t=tq.rotation_T)
 
     def _attend(self, layer, q, out, kv_cache, block_table, context_lens) -> None:
         pd, bs = self.packed_dim, kv_cache.shape[2]
-        kc, vc = kv_cache[:, 0, :, :, :pd], kv_cache[:, 1, :, :, :pd]
+        kc, vc = self._codes(kv_cache)
         key_ = (self.head_size, self.tq_codec, self.tq_mode or self.tq_bits, self.num_heads, str(kv_cache.device))
         attn = _LayerState.attention.get(key_)
         if self.tq_codec == "hybrid":
@@ -180,7 +212,7 @@ class TurboQuantImplBase:
                 from ..hybrid_quantizer import HybridPagedAttention
                 attn = HybridPagedAttention(_hybrid_quantizer(self.head_size, self.tq_mode, kv_cache.device), self.num_heads)
                 _LayerState.attention[key_] = attn
-            res = attn.prefill(q, kv_cache[:, 0, :, :, :pd], kv_cache[:, 1, :, :, :pd], md.block_table, md.seq_lens,
+            res = attn.prefill(q, *self._codes(kv_cache), md.block_table, md.seq_lens,
                                md.query_start_loc, block_size=bs, num_kv_heads=self.num_kv_heads, out=out, scale=self.scale,
                                max_seq_len=getattr(md, "max_seq_len", None))
             return res is not None
@@ -191,7 +223,8 @@ class TurboQuantImplBase:
             attn = TQPagedAttention(_quantizer(self.head_size, self.tq_bits, kv_cache.device), self.num_heads)
             _LayerState.attention[key_] = attn
         kn, vn = self._norms(getattr(layer, "layer_name", "layer"), kv_cache)
-        res = attn.prefill(q, kv_cache[:, 0, :, :, :pd], kn, kv_cache[:, 1, :, :, :pd], vn, md.block_table, md.seq_lens,
+        kc, vc = self._codes(kv_cache)
+        res = attn.prefill(q, kc, kn, vc, vn, md.block_table, md.seq_lens,
                            md.query_start_loc, block_size=bs, num_kv_heads=self.num_kv_heads, out=out, scale=self.scale,
                            max_seq_len=getattr(md, "max_seq_len", None))      # host-side bound from vLLM's metadata: staged kernel
         return res is not None

@@ -4,9 +4,11 @@ Interface of the reference's ``vllm/engine.py`` (``apply_tq_patches`` :52-107, `
 ``_tq_dim_for_head`` :126-135, ``_align_page_size`` :138-154, ``_patch_page_size`` :157-193, ``_patch_max_memory``
 :196-220).  A row of the primary cache is one record of ``tq_dim`` bytes per (token, KV head):
 
-* uniform codecs: ``packed_dim`` code bytes followed by the float32 norm of the vector (``packed_dim + 4``; the
-  reference leaves these four bytes unused and keeps norms in separate tensors, ``vllm/backend.py:440-454``;
-  here the kernels read and write them in place through strided norm pointers);
+* uniform codecs: ``packed_dim + 4`` bytes per (token, KV head) as in the reference, which leaves four of them
+  unused and keeps norms in separate tensors (``vllm/backend.py:440-454``); here they hold the float32 norm.  Inside
+  a block's K half and V half the bytes are laid out in planes - all code rows, then all norms - so that code rows
+  start on 16-byte boundaries (TMA copies, 16-byte loads); ``AITHER_TQ_RECORD_PAGES=1`` keeps the norm behind the codes
+  of its own row (68-byte records), which the general kernels read through strided pointers at half the speed;
 * hybrid codecs: the 64 / 44-byte record, norms inside.
 
 With the installed vLLM the cache tensor is shaped by the backend's own ``get_kv_cache_shape`` (which returns the
