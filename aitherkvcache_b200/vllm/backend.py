@@ -112,13 +112,16 @@ class TurboQuantImplBase:
             self.packed_dim = head_size * self.tq_bits // 8
 
     def _planar(self, kv_cache: torch.Tensor) -> bool:
-        """Primary-mode pages of the uniform codecs are laid out in planes unless ``AITHER_TQ_RECORD_PAGES`` is set: in
-        each of a block's K and V halves first the codes of all (position, head) rows, then their float32 norms.  The
-        bytes per block are those of the reference's pages (``vllm/engine.py:125-133`` puts the norm behind the codes
-        of the same row: 68-byte rows at 4 bits), but code rows start on 16-byte boundaries, which the TMA-fed decode
-        kernel and the vectorised prefill pre-pass need - attention over 68-byte rows runs at half the speed."""
+        """Pages of the uniform codecs are laid out in planes unless ``AITHER_TQ_RECORD_PAGES`` is set: in each of a
+        block's K and V halves first the codes of all (position, head) rows back to back, then their float32 norms
+        (the rest of a page that vLLM sized for fp16 K/V stays unused).  The bytes per block are those of the
+        reference's pages - ``vllm/engine.py:125-133`` puts the norm behind the codes of the same row (68-byte rows at
+        4 bits) in primary mode, ``vllm/backend.py:440-454`` keeps the codes at the start of head_size-byte rows and the
+        norms in side tensors otherwise - but code rows are dense and start on 16-byte boundaries, which the TMA-fed
+        decode kernel and the vectorised prefill pre-pass need: attention over strided or 68-byte rows runs at half
+        the speed."""
         pd = self.packed_dim
-        return (self.tq_codec == "uniform" and kv_cache.dim() == 5 and kv_cache.shape[-1] == pd + 4 and pd % 4 == 0
+        return (self.tq_codec == "uniform" and kv_cache.dim() == 5 and kv_cache.shape[-1] >= pd + 4 and pd % 4 == 0
                 and kv_cache.is_contiguous() and (kv_cache.shape[2] * kv_cache.shape[3] * pd) % 16 == 0
                 and not os.environ.get("AITHER_TQ_RECORD_PAGES"))
 
@@ -129,7 +132,7 @@ class TurboQuantImplBase:
         pd = self.packed_dim
         flat = kv_cache.view(nb, 2, bs * H * W)
         codes = flat[:, :, :bs * H * pd].view(nb, 2, bs, H, pd)
-        norms = flat[:, :, bs * H * pd:].view(torch.float32).view(nb, 2, bs, H)
+        norms = flat[:, :, bs * H * pd:bs * H * (pd + 4)].view(torch.float32).view(nb, 2, bs, H)
         return codes, norms
 
     def _codes(self, kv_cache: torch.Tensor):

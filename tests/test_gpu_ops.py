@@ -302,8 +302,9 @@ def test_backend_mixed_batch_attends_over_the_packed_cache():
     impl.forward(layer, qry.cuda(), None, None, kv, md, output=out)
     tq = _LayerState.quantizers[(128, 4, "cuda:0")]
     kn, vn = impl._norms(layer.layer_name, kv)
-    ref = _causal_oracle(qry.reshape(nq, QH, 128).numpy(), kv[:, 0, ..., :64].cpu().numpy(), kn.cpu().numpy(),
-                         kv[:, 1, ..., :64].cpu().numpy(), vn.cpu().numpy(), bt.numpy(), lens, qlens,
+    kc_, vc_ = impl._codes(kv)
+    ref = _causal_oracle(qry.reshape(nq, QH, 128).numpy(), kc_.cpu().numpy(), kn.cpu().numpy(),
+                         vc_.cpu().numpy(), vn.cpu().numpy(), bt.numpy(), lens, qlens,
                          tq.rotation.cpu().numpy(), tq.centroids.cpu().numpy(), bits)
     got = out.float().cpu().numpy().reshape(nq, QH, 128)
     assert (np.abs(got - ref) <= 2e-3 * np.maximum(1.0, np.abs(ref))).all()
@@ -454,6 +455,8 @@ def test_backend_primary_records_keep_norms_in_the_row(monkeypatch, bits, layout
     for width, name in ((pd + 4, "prim.layers.0.attn"), (128, "sep.layers.0.attn")):
         layer = types.SimpleNamespace(layer_name=name)
         kv = torch.zeros(14, 2, bs, H, width, dtype=torch.uint8, device="cuda")
+        if width == 128:       # a strided view: codes at the start of 128-byte rows, norms in side tensors
+            kv = torch.zeros(14, 2, bs, H, 256, dtype=torch.uint8, device="cuda")[..., :128]
         impl.do_kv_cache_update(layer, key, val, kv, slots)
         out = torch.zeros(2, QH * 128, dtype=torch.float16, device="cuda")
         impl.forward(layer, q, None, None, kv, md, output=out)
