@@ -12,7 +12,7 @@
 //                                   O is the row sum of the probabilities as the tensor cores saw them.
 // (Norms are folded in as fp16 factors: a key or value norm below 1e-2 loses bits to fp16's subnormal range.)
 // All operands are K-major in the 128-byte-swizzled layout of umma.cuh.  Thirteen warps, no CTA-wide barrier in the loop:
-//   warps 0-3   softmax: thread = row.  S out of tensor memory (tcgen05.ld), causal limit, running reference maximum
+//   warps 0-3   softmax: thread = row (staged variant: warps 0-7, two threads per row with 64 keys of the tile each).  S out of tensor memory (tcgen05.ld), causal limit, running reference maximum
 //               (the accumulator O is rescaled only when the maximum grows by more than 2^8: tcgen05.ld / st of the
 //               thread's own lane), exp2, fp16 probabilities into the P operand.
 //   warps 4-11  decode: packed bytes and norms from global memory two tiles ahead in registers (block-table entries
@@ -41,15 +41,18 @@ __device__ int g_prefill_tc_withhold = -1;   // test hook: CTAs (0, 0, z) issue 
 constexpr int PT_VHALF = 144 * 128;                  // 64 keys of a value operand: 128 dims + the row of ones (+ 15 zero rows)
 
 // Shared-memory layout and warp roles of the two variants: codes decoded in the kernel (13 warps, tiles of 64 keys, two
-// operand stages, the lookup table) or operand images staged in global memory by tq_prefill_stage_kernel (6 warps, tiles
-// of 128 keys - half as many MMA instructions per key -, three stages fed by bulk copies).
+// operand stages, the lookup table) or operand images staged in global memory by tq_prefill_stage_kernel (10 warps, tiles
+// of 128 keys - half as many MMA instructions per key -, two softmax threads per row, three stages fed by bulk copies).
 template <bool STAGED> struct PtL {
   static constexpr int KT = STAGED ? 128 : 64;        // keys per tile
   static constexpr int NST = STAGED ? 3 : 2;          // K / V operand stages (the barrier block has room for four)
   static_assert(NST <= 4, "barrier slots");
-  static constexpr int WARPS = STAGED ? 6 : 13;
+  static constexpr int SW = STAGED ? 8 : 4;           // softmax warps: 4 = a thread per row, 8 = two threads per row (64 keys each)
+  static constexpr int WARPS = STAGED ? 10 : 13;
   static constexpr int THREADS = WARPS * 32;
-  static constexpr int MMA_WARP = STAGED ? 4 : 12;
+  static constexpr int MMA_WARP = STAGED ? 8 : 12;
+  static constexpr int LOAD_WARP = 9;                 // staged: the lane that issues the bulk copies
+  static_assert(KT / (SW / 4) == 64, "a softmax thread handles 64 keys of a tile");
   static constexpr int KHALF = KT * 128;              // 64 dims of a key operand: KT rows x 128 B
   static constexpr int KSTAGE = 2 * KHALF;            // B of S: [KT keys][128 dims], two halves of 64 dims
   static constexpr int VSTAGE = (KT / 64) * PT_VHALF; // B of PV: [144 rows][KT keys], one half per 64 keys
@@ -57,7 +60,7 @@ template <bool STAGED> struct PtL {
   static constexpr int V = K + NST * KSTAGE;
   static constexpr int LUT = V + NST * VSTAGE;        // byte -> half2, one copy per lane (256 x 128 B); not staged only
   static constexpr int BAR = LUT + (STAGED ? 0 : 32768);      // mbarriers, tensor-memory slot, failed flag
-  static constexpr int SMEM = BAR + 256 + 1024;       // + slack for the 1024-byte alignment
+  static constexpr int SMEM = BAR + 512 + 1024;       // + slack for the 1024-byte alignment
   // tensor memory (512 columns): S stage s at column KT s - its first KT / 2 columns are reused for the fp16 P of the same
   // tile -, O at 2 KT (144 columns, column 128 = row sum), Q (64 columns of fp16 pairs) behind it
   static constexpr int T_O = 2 * KT, T_Q = 2 * KT + 160;
@@ -69,7 +72,8 @@ static_assert(PS_KT == PFI_KEYS && PT_IMAGE == PFI_BYTES && PtL<true>::KHALF == 
               "image layout shared with the other pre-pass kernels");
 // barrier slots (8 bytes each; up to four operand stages)
 constexpr uint32_t B_KFULL = 0, B_VFULL = 32, B_SFULL = 64, B_PFULL = 96, B_PVDONE = 112,
-                   B_VFREE = 160, B_DRAIN = 192, B_TMEM = 200, B_FAILED = 204;
+                   B_VFREE = 160, B_DRAIN = 192, B_TMEM = 200, B_FAILED = 204,
+                   B_MX = 256;          // 4 row quadrants x 2 tile parities: both half-row warps have published their maxima
 constexpr int PT_TMEM_COLS = 512;
 constexpr float PT_RESCALE = 8.0f;                   // log2 units the row maximum may grow before O is rescaled
 
@@ -225,9 +229,10 @@ tq_prefill_tc_kernel(PrefillArgs a) {
     }
     for (int i = 0; i < 2; ++i) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar_s + B_SFULL + 8 * i));
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;" :: "r"(bar_s + B_PFULL + 8 * i));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar_s + B_PFULL + 8 * i), "r"(L::SW));
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar_s + B_PVDONE + 8 * i));
     }
+    for (int i = 0; i < 8; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 2;" :: "r"(bar_s + B_MX + 8 * i));
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar_s + B_DRAIN));
     asm volatile("st.shared.u32 [%0], %1;" :: "r"(failed_s), "r"(0u) : "memory");
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -346,7 +351,7 @@ tq_prefill_tc_kernel(PrefillArgs a) {
       }
     }
     __syncwarp();
-  } else if (STAGED && warp == 5) {
+  } else if (STAGED && warp == L::LOAD_WARP) {
     // ================= producer: operand images of tile j by two bulk copies =================
     if (lane == 0) {
       const uint8_t* src = a.staged + (((int64_t)s * a.tiles_per_seq + jbase) * a.num_kv_heads + kvh) * PT_IMAGE;
@@ -478,37 +483,50 @@ tq_prefill_tc_kernel(PrefillArgs a) {
       if (j + 1 < n_ktiles && !tile_step(j + 1, R1, R0)) break;
       if (j + 2 < n_ktiles && !tile_step(j + 2, R2, R1)) break;
     }
-  } else if (warp < 4) {
-    // ================= softmax warps: thread = row =================
-    const int r = tid;
+  } else if (warp < L::SW) {
+    // ================= softmax warps: thread = 64 keys of a row =================
+    // (warps 0-3: rows 32 warp .. + 31; with eight warps, warps 4-7 take the second 64 keys of the same rows - a warp
+    // may only touch the 32 tensor-memory lanes of its index modulo 4)
+    __shared__ float s_mx[2][2][128];             // [tile parity][half][row]: the half-row maxima of a tile
+    constexpr int SPLIT = L::SW / 4;
+    const int quad = warp & 3, hf = warp >> 2;
+    const int r = quad * 32 + lane;
     const int tok = tok_lo + r / G;
     const bool live = tok < qlen && q0 + tok < a.n_tokens;
     int lim = live ? past + tok + 1 : 0;          // keys the row may see
     if (lim > seq_len) lim = seq_len;
-    const uint32_t t_lane = ((uint32_t)(warp * 32)) << 16;
+    const uint32_t t_lane = ((uint32_t)(quad * 32)) << 16;
     float m_ref = -CUDART_INF_F;
     bool ok = true;
     for (int j = 0; j < n_ktiles && ok; ++j) {
       const uint32_t st = (uint32_t)(j & 1);
       if (!wait_warp(bar_s + B_SFULL + 8 * st, par2(j))) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      uint32_t v[PT_KT];
-#pragma unroll
-      for (int c = 0; c < PT_KT / 32; ++c) tmem_ld32(tmem_base + t_lane + st * PT_KT + 32 * c, *reinterpret_cast<uint32_t (*)[32]>(&v[32 * c]));
+      uint32_t v[64];
+      tmem_ld32(tmem_base + t_lane + st * PT_KT + 64 * hf, *reinterpret_cast<uint32_t (*)[32]>(&v[0]));
+      tmem_ld32(tmem_base + t_lane + st * PT_KT + 64 * hf + 32, *reinterpret_cast<uint32_t (*)[32]>(&v[32]));
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       // causal limit, maximum (the key norms are inside the K operand)
-      const int vis = lim - PT_KT * (jbase + j);  // keys of this tile the row may see (<= 0: none, >= PT_KT: all)
-      if (vis < PT_KT) {
+      const int vis = lim - PT_KT * (jbase + j) - 64 * hf;      // of this thread's 64 keys the row may see (<= 0: none, >= 64: all)
+      if (vis < 64) {
 #pragma unroll
-        for (int i = 0; i < PT_KT; ++i) v[i] = i < vis ? v[i] : 0xff800000u;
+        for (int i = 0; i < 64; ++i) v[i] = i < vis ? v[i] : 0xff800000u;
       }
       float mx = -CUDART_INF_F;
 #pragma unroll
-      for (int i = 0; i < PT_KT; i += 2) mx = fmaxf(mx, fmaxf(__uint_as_float(v[i]), __uint_as_float(v[i + 1])));
+      for (int i = 0; i < 64; i += 2) mx = fmaxf(mx, fmaxf(__uint_as_float(v[i]), __uint_as_float(v[i + 1])));
+      if constexpr (SPLIT == 2) {      // the other half of the row: maxima through shared memory, one mbarrier per quadrant and parity
+        s_mx[j & 1][hf][r] = mx;
+        __syncwarp();
+        const uint32_t xb = bar_s + B_MX + 8 * (uint32_t)(2 * quad + (j & 1));
+        if (lane == 0) pt_arrive(xb);
+        if (!wait_warp(xb, par2(j))) { ok = false; break; }
+        mx = fmaxf(mx, s_mx[j & 1][hf ^ 1][r]);
+      }
       // the reference maximum moves only when the row maximum has grown by more than PT_RESCALE; tcgen05.ld / st are
       // warp-wide, so the rows of a warp rescale together (factor 1 for rows that keep their reference).  Column 128
-      // of O is the row sum and is rescaled with the rest.
+      // of O is the row sum and is rescaled with the rest.  Two warps per row: each takes a share of the columns.
       const bool grow = mx > m_ref + PT_RESCALE;
       if (__any_sync(0xffffffffu, grow)) {
         const float alpha = grow ? pt_ex2(m_ref - mx) : 1.0f;      // m_ref = -inf: 0
@@ -516,8 +534,9 @@ tq_prefill_tc_kernel(PrefillArgs a) {
         if (j > 0) {
           if (!wait_warp(bar_s + B_PVDONE + 8 * (uint32_t)((j - 1) & 1), par2(j - 1))) { ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const int c_lo = SPLIT == 2 ? (hf ? 3 : 0) : 0, c_hi = SPLIT == 2 ? (hf ? 5 : 3) : 5;
 #pragma unroll 1
-          for (int c = 0; c < 5; ++c) {
+          for (int c = c_lo; c < c_hi; ++c) {
             uint32_t o[32];
             tmem_ld32(tmem_o + t_lane + 32 * c, o);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -533,14 +552,14 @@ tq_prefill_tc_kernel(PrefillArgs a) {
       // probabilities as fp16 pairs (keys 2i, 2i + 1) into the first columns of the S stage they came from: the A
       // operand of P V.  P V of tile j-2, the last reader of these columns, was issued before the scores of tile j; the
       // tensor cores work in issue order, and this tile's s_full - a commit - completes only when everything issued
-      // before it has.
-#pragma unroll
-      for (int c = 0; c < PT_KT / 64; ++c) {
+      // before it has.  With two warps per row, P of keys 64..127 lands on columns 32..63, which hold scores of the
+      // other warp's keys: that warp loaded them before it arrived on the maxima barrier this warp has passed.
+      {
         uint32_t ph[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i)
-          ph[i] = pt_pack_half2(pt_ex2(__uint_as_float(v[64 * c + 2 * i]) - ref), pt_ex2(__uint_as_float(v[64 * c + 2 * i + 1]) - ref));
-        tmem_st32(tmem_base + t_lane + st * PT_KT + 32 * c, ph);
+          ph[i] = pt_pack_half2(pt_ex2(__uint_as_float(v[2 * i]) - ref), pt_ex2(__uint_as_float(v[2 * i + 1]) - ref));
+        tmem_st32(tmem_base + t_lane + st * PT_KT + 32 * hf, ph);
       }
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -551,8 +570,9 @@ tq_prefill_tc_kernel(PrefillArgs a) {
     if (ok && wait_warp(bar_s + B_PVDONE + 8 * (uint32_t)((n_ktiles - 1) & 1), par2(n_ktiles - 1))) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int64_t row = ((int64_t)(q0 + tok) * a.num_q_heads + kvh * G + r % G) * gridDim.z + blockIdx.z;      // (row, partial)
+      const int c_lo = SPLIT == 2 ? 2 * hf : 0, c_hi = SPLIT == 2 ? 2 * hf + 2 : 4;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = c_lo; c < c_hi; ++c) {
         uint32_t o[32];
         tmem_ld32(tmem_o + t_lane + 32 * c, o);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -564,7 +584,7 @@ tq_prefill_tc_kernel(PrefillArgs a) {
                                  __uint_as_float(o[4 * i + 3]));
         }
       }
-      {
+      if (hf == SPLIT - 1) {
         uint32_t o[32];
         tmem_ld32(tmem_o + t_lane + 128, o);      // column 128: the row sum of the fp16 probabilities
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
