@@ -28,7 +28,8 @@ class TQPagedAttention:
     SPLITK_NUM_SPLITS = int(os.environ.get("AITHER_TQ_SPLITK_SPLITS", "16"))
     SPLITK_BLOCKS = int(os.environ.get("AITHER_TQ_SPLITK_BLOCKS", "0"))
 
-    STAGED_WORKSPACE_LIMIT = 4 << 30     # bytes of scratch the staged prefill kernel may ask for
+    # bytes of scratch the staged prefill kernel may ask for (AITHER_TQ_PREFILL_SCRATCH_MB overrides; 0 = never staged)
+    STAGED_WORKSPACE_LIMIT = int(os.environ.get("AITHER_TQ_PREFILL_SCRATCH_MB", "2048")) << 20
 
     def __init__(self, tq, num_query_heads: int, block_selector=None):
         # optional BlockSelector (block_selector.py): filters block_tables / context_lens per query on the

@@ -11,6 +11,7 @@ The kernels cover head_dim 128.
 """
 from __future__ import annotations
 
+import os
 import ctypes
 import functools
 import math
@@ -300,7 +301,8 @@ class HybridPagedAttention:
         self.scale = 1.0 / math.sqrt(htq.head_dim)
         self._workspace: Optional[torch.Tensor] = None
 
-    STAGED_WORKSPACE_LIMIT = 4 << 30     # bytes of scratch the staged prefill kernel may ask for
+    # bytes of scratch the staged prefill kernel may ask for (AITHER_TQ_PREFILL_SCRATCH_MB overrides; 0 = never staged)
+    STAGED_WORKSPACE_LIMIT = int(os.environ.get("AITHER_TQ_PREFILL_SCRATCH_MB", "2048")) << 20
 
     def prefill(self, query, k_cache, v_cache, block_tables, seq_lens, query_start_loc, block_size: int = 16,
                 num_kv_heads: Optional[int] = None, out: Optional[torch.Tensor] = None, scale: Optional[float] = None,
