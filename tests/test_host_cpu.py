@@ -256,3 +256,46 @@ def test_backend_mixed_batch_routing_on_the_host():
                                 seq_lens=seq_lens, query_start_loc=torch.tensor([0, 2, 4, 6, 8], dtype=torch.int32))
     impl.forward(None, query[:8].contiguous(), None, None, torch.zeros(1), md2, output=torch.zeros(8, 4 * 128))
     assert "attend" not in calls and calls["prefill"][0].tolist() == [50, 7, 3, 90]
+
+
+def test_ctypes_structures_match_the_header_layout(tmp_path):
+    """Every parameter struct of include/akv_b200.h against its ctypes mirror: the C compiler's sizeof and the offset
+    of every field, in order (gcc on the header itself; no library call)."""
+    import ctypes, re, subprocess
+    from aitherkvcache_b200 import _lib
+    root = os.path.join(os.path.dirname(__file__), "..")
+    header = open(os.path.join(root, "include", "akv_b200.h")).read()
+    pairs = {"akv_tq_attn_params": _lib.TQAttnParams, "akv_tq_prefill_params": _lib.TQPrefillParams,
+             "akv_tq_decode_step_params": _lib.TQDecodeStepParams, "akv_hybrid_tables": _lib.HybridTables,
+             "akv_hybrid_attn_params": _lib.HybridAttnParams, "akv_hybrid_decode_step_params": _lib.HybridDecodeStepParams,
+             "akv_p2p_merge_params": _lib.P2PMergeParams, "akv_tri_decode_params": _lib.TriDecodeParams}
+    lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "akv_b200.h"', 'int main(void) {']
+    names = {}
+    for cname in pairs:
+        body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (cname, cname), header, re.S).group(1)
+        body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+        fields = []
+        for decl in body.split(";"):
+            decl = decl.strip()
+            if not decl:
+                continue
+            # "const void* a" / "int64_t a, b, c" / "akv_tq_attn_params attn": the names are the last identifier of each part
+            first, *rest = decl.split(",")
+            fields.append(re.findall(r"[A-Za-z_][A-Za-z_0-9]*", first)[-1])
+            fields += [re.findall(r"[A-Za-z_][A-Za-z_0-9]*", part)[-1] for part in rest]
+        names[cname] = fields
+        lines.append('printf("%s %%zu", sizeof(%s));' % (cname, cname))
+        lines += ['printf(" %%zu", offsetof(%s, %s));' % (cname, f) for f in fields]
+        lines.append('printf("\\n");')
+    lines += ["return 0;", "}"]
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-std=c99", "-I", os.path.join(root, "include"), "-o", str(exe), str(src)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.strip().splitlines()
+    for line in out:
+        cname, size, *offs = line.split()
+        st = pairs[cname]
+        assert ctypes.sizeof(st) == int(size), cname
+        got = [getattr(st, f).offset for f, _ in st._fields_]
+        assert got == [int(o) for o in offs], (cname, names[cname], [f for f, _ in st._fields_])
