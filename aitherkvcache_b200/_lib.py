@@ -44,6 +44,7 @@ class TQAttnParams(C.Structure):
         ("blocks_per_split", c_int),
         ("stream", c_vp),
         ("ev_kernel_start", c_vp), ("ev_kernel_stop", c_vp),
+        ("out_copy", c_vp),
     ]
 
 

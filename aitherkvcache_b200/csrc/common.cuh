@@ -150,6 +150,7 @@ struct MergeArgs {
   int D;
   const float* rot;              // R row-major (MERGE_ROTATE only)
   void* out; int out_dtype; int64_t out_ss, out_sh;
+  void* out2;                    // optional second destination (MERGE_ROTATE): dense [rows][D] rows of out_dtype, same values
   float* raw_out;
   const int* part_counts;       // optional [num_seqs]: number of valid parts of each sequence
   // optional: the partials live in one of two halves of a double buffer; *half_select (a device word

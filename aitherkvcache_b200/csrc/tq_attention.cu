@@ -257,7 +257,9 @@ __global__ void akv_merge_kernel(MergeArgs a) {
 #pragma unroll
       for (int k = 0; k < 32; ++k) x4[k & 3] = __fmaf_rn(sm[i + k], r[k], x4[k & 3]);
     }
-    store_from_float(a.out, a.out_dtype, seq * a.out_ss + qh * a.out_sh + j, (x4[0] + x4[1]) + (x4[2] + x4[3]));
+    const float o = (x4[0] + x4[1]) + (x4[2] + x4[3]);
+    store_from_float(a.out, a.out_dtype, seq * a.out_ss + qh * a.out_sh + j, o);
+    if (a.out2 != nullptr) store_from_float(a.out2, a.out_dtype, (int64_t)row * a.D + j, o);
   }
 }
 
@@ -450,7 +452,9 @@ akv_merge128_kernel(MergeArgs a, int rows, int np_alloc) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) x4[k] = __fmaf_rn(vec[g * D + i + k], mat[(i + k) * D + d], x4[k]);
       }
-      store_from_float(a.out, a.out_dtype, seq * a.out_ss + qh * a.out_sh + d, (x4[0] + x4[1]) + (x4[2] + x4[3]));
+      const float o = (x4[0] + x4[1]) + (x4[2] + x4[3]);
+      store_from_float(a.out, a.out_dtype, seq * a.out_ss + qh * a.out_sh + d, o);
+      if (a.out2 != nullptr) store_from_float(a.out2, a.out_dtype, (int64_t)row * D + d, o);
     }
     group_sync(g);                          // vec[g], wts and red[g] are free again
   }
@@ -535,8 +539,18 @@ int launch_merge(const MergeArgs& a, int rows, cudaStream_t st, bool pdl) {
       if (int rc = check_launch("akv_merge_kernel")) return rc;
     }
     // ... then out = R^T x for all rows at once
+    if (int rc = launch_rot_rows(a.gemm_scratch, AKV_F32, (int64_t)a.num_q_heads * 128, 128, a.num_q_heads, nullptr, 0, a.rot,
+                                 1.0f, a.out, a.out_dtype, a.out_ss, a.out_sh, rows, st))
+      return rc;
+    if (a.out2 == nullptr) return AKV_OK;
+    // the second destination: a device copy when `out` is dense itself, else the product once more
+    if (a.out_sh == 128 && a.out_ss == (int64_t)a.num_q_heads * 128) {
+      const size_t bytes = (size_t)rows * 128 * (a.out_dtype == AKV_F32 ? 4 : 2);
+      cudaError_t e = cudaMemcpyAsync(a.out2, a.out, bytes, cudaMemcpyDeviceToDevice, st);
+      return e == cudaSuccess ? AKV_OK : fail((int)e, "merge: copy of the result: %s", cudaGetErrorString(e));
+    }
     return launch_rot_rows(a.gemm_scratch, AKV_F32, (int64_t)a.num_q_heads * 128, 128, a.num_q_heads, nullptr, 0, a.rot, 1.0f,
-                           a.out, a.out_dtype, a.out_ss, a.out_sh, rows, st);
+                           a.out2, a.out_dtype, (int64_t)a.num_q_heads * 128, 128, rows, st);
   }
   const size_t smem128 = (size_t)ROT128_MAT_BYTES + (size_t)(4 * 128 + 4 * np_alloc + 8) * sizeof(float);
   if (a.D == 128 && a.mode == MERGE_ROTATE && !no_rot128 && rows > 0 && smem128 <= 200 * 1024) {
@@ -2412,6 +2426,7 @@ struct akv_tq_attn_params {
   void* stream;
   void* ev_kernel_start;     // optional cudaEvent_t recorded right before / after the
   void* ev_kernel_stop;      // split-K kernel (for per-kernel timing); may be null
+  void* out_copy;            // optional dense [num_seqs][num_q_heads][head_dim] second copy of `out`
 };
 
 AKV_EXPORT size_t akv_tq_paged_attn_workspace_bytes(int num_seqs, int num_q_heads, int num_kv_heads,
@@ -2664,6 +2679,7 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
   mg.mode = p->raw_out ? MERGE_RAW : MERGE_ROTATE;
   mg.rot = p->rotation;
   mg.out = p->out; mg.out_dtype = p->out_dtype; mg.out_ss = p->out_stride_seq; mg.out_sh = p->out_stride_head;
+  mg.out2 = p->raw_out ? nullptr : p->out_copy;
   mg.raw_out = p->raw_out;
   mg.gemm_scratch = qrot;        // the rotated queries are dead once the attention kernel has run
   return launch_merge(mg, rows, st, pdl && p->max_blocks_per_seq > 0);

@@ -162,13 +162,19 @@ def decode_step(query, key, value, kv_cache, output, k_norms, v_norms, slot_mapp
     a.out, a.out_dtype = output.data_ptr(), _lib._FLOAT_CODES[output.dtype]
     a.out_stride_seq, a.out_stride_head = output.stride(0), output.stride(1)
     a.stream = torch.cuda.current_stream(dev).cuda_stream
+    # the op returns a copy of `output`: when every row of `output` is written by this call the merge kernel
+    # writes the copy itself (one launch less than a clone)
+    res = None
+    if num_actual == output.shape[0]:
+        res = torch.empty(output.shape, dtype=output.dtype, device=dev)
+    a.out_copy = res.data_ptr() if res is not None else None
     if torch.cuda.current_device() == dev.index:
         rc = _lib.lib().akv_tq_decode_step(ctypes.byref(p))
     else:
         with torch.cuda.device(dev):
             rc = _lib.lib().akv_tq_decode_step(ctypes.byref(p))
     _lib.check(rc, "akv_tq_decode_step")
-    return output.clone()
+    return res if res is not None else output.clone()
 
 
 _hybrid: Dict[int, object] = {}                # head_size -> HybridTurboQuant

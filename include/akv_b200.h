@@ -139,6 +139,9 @@ typedef struct akv_tq_attn_params {
   void* stream;
   void* ev_kernel_start;  /* optional cudaEvent_t pair recorded around the split-K kernel, */
   void* ev_kernel_stop;   /* so a caller can time that kernel alone; NULL = off */
+  void* out_copy;         /* optional second destination of the result: dense [num_seqs, num_q_heads, head_dim] of
+                           * out_dtype, written by the same kernel as `out` (the reference's op mutates `output` and
+                           * returns a copy of it, vllm/hooks.py:129-205); NULL = off; ignored with raw_out */
 } akv_tq_attn_params;
 
 size_t akv_tq_paged_attn_workspace_bytes(int num_seqs, int num_q_heads, int num_kv_heads,

@@ -101,6 +101,40 @@ def test_decode_step_single_call_matches_stepwise_path(nseq):
     assert not torch.equal(outs[0][0], outs[0][1])
 
 
+@pytest.mark.parametrize("dense", (True, False))
+@pytest.mark.parametrize("nseq", (3, 72))
+def test_decode_step_returned_copy_is_written_by_the_merge(nseq, dense):
+    """With num_actual == output rows the op's return value is a second destination of the merge kernel (no clone
+    launch): it must be a dense tensor of its own holding exactly `output`, for a dense and a strided `output`, on
+    the per-row merge (96 rows) and on the tensor-core rotation (2304 rows; dense: device copy, strided: the
+    product once more), and equal to what the clone path (padding rows in `output`) returns."""
+    from aitherkvcache_b200 import _lib
+    from aitherkvcache_b200.vllm import ops
+    H, QH = 8, 32
+    ctx = [300, 17, 64] + [int(v) for v in np.random.default_rng(6).integers(1, 120, nseq - 3)]
+    S = len(ctx)
+    results = []
+    for pad in (0, 2):
+        t, d, kv, kn, vn, q, key, val, slots = _setup_decode(4, H, QH, ctx, 78)
+        tq = ops.init_quantizer(128, bits=4)
+        tq.rotation = torch.from_numpy(t["rotation"]).cuda()
+        assert ops.register_custom_ops()
+        big = torch.zeros(S + pad, QH + (0 if dense else 1), 128, dtype=torch.float16, device="cuda")
+        out = big[:, :QH]
+        n0 = _lib.lib().akv_launch_count()
+        res = torch.ops.tq.decode_step(q.cuda()[:S + pad], key.cuda(), val.cuda(), kv, out, kn, vn, slots.cuda(),
+                                       torch.from_numpy(d["block_tables"]).cuda(),
+                                       torch.tensor(ctx, dtype=torch.int32, device="cuda"),
+                                       0, QH, H, 128, 1.0 / math.sqrt(128), S)
+        assert res.is_contiguous() and res.shape == out.shape and res.data_ptr() != out.data_ptr()
+        assert torch.equal(res, out)
+        results.append(res[:S].clone())
+        if not dense:
+            assert (big[:, QH] == 0).all(), "the strided output's gaps stay untouched"
+    assert torch.equal(results[0], results[1])
+    assert results[0].abs().max() > 0
+
+
 def test_hybrid_decode_step_op():
     from aitherkvcache_b200.vllm import ops
     g = load_golden("hybrid_tq35.npz")
