@@ -284,6 +284,73 @@ __device__ __forceinline__ void group_sync(int g) {      // the 128 threads of r
   asm volatile("bar.sync %0, 128;\n" :: "r"(g + 1) : "memory");
 }
 
+// The new token's vectors, four per CTA of 512 threads (head_dim 128): threads 128 g .. 128 g + 127 encode vector
+// 4 * quad + g (K rows first, then V rows), each group on its own named barrier.  Per vector the arithmetic and its order
+// are those of encode_generic_rows: norm by sumsq_8lane, exact division, one accumulation chain j = 0..127 per output.
+// `scratch`: 4 x 168 floats of shared memory.
+__device__ __forceinline__ void encode128_quad(const RowMap& mk, const RowMap& mv, int64_t n_rows, int64_t quad, int bits,
+                                               const float* __restrict__ rot_t, const float* __restrict__ boundaries,
+                                               float* scratch) {
+  constexpr int D = 128;
+  const int g = threadIdx.x >> 7, i = threadIdx.x & 127;
+  const int64_t e = quad * 4 + g;
+  if (e >= 2 * n_rows) return;              // the whole group leaves; the others only use their own barriers
+  const bool is_v = e >= n_rows;
+  const RowMap& m = is_v ? mv : mk;
+  float* u = scratch + g * 168;                              // [128]
+  uint8_t* codes = reinterpret_cast<uint8_t*>(u + D);        // [128]
+  float* s_nrm = u + D + 32;
+  const int nb = (1 << bits) - 1;
+  const int pd = D * bits / 8;
+  RowAddr a = map_row(m, is_v ? e - n_rows : e);
+  u[i] = load_as_float(a.src_base, m.x_dtype, a.src_off + i);
+  float r0[32];                             // the first round of matrix loads travels while the norm is computed
+#pragma unroll
+  for (int k = 0; k < 32; ++k) r0[k] = rot_t[(int64_t)k * D + i];
+  group_sync(g);
+  if (i < 32) {
+    const float tot = sumsq_8lane(u, D, i & 7, 0xffffffffu);
+    if (i == 0) *s_nrm = __fsqrt_rn(tot);
+  }
+  group_sync(g);
+  const float nrm = *s_nrm;
+  const float den = __fadd_rn(nrm, 1e-10f);
+  u[i] = __fdiv_rn(u[i], den);              // the first warp finished reading u before the barrier above
+  group_sync(g);
+  float y = 0.f;
+  float r1[32];
+#pragma unroll
+  for (int k = 0; k < 32; ++k) r1[k] = rot_t[(int64_t)(32 + k) * D + i];
+#pragma unroll
+  for (int k = 0; k < 32; ++k) y = __fmaf_rn(u[k], r0[k], y);
+#pragma unroll
+  for (int k = 0; k < 32; ++k) r0[k] = rot_t[(int64_t)(64 + k) * D + i];
+#pragma unroll
+  for (int k = 0; k < 32; ++k) y = __fmaf_rn(u[32 + k], r1[k], y);
+#pragma unroll
+  for (int k = 0; k < 32; ++k) r1[k] = rot_t[(int64_t)(96 + k) * D + i];
+#pragma unroll
+  for (int k = 0; k < 32; ++k) y = __fmaf_rn(u[64 + k], r0[k], y);
+#pragma unroll
+  for (int k = 0; k < 32; ++k) y = __fmaf_rn(u[96 + k], r1[k], y);
+  int c = 0;
+  for (int k = 0; k < nb; ++k) c += (boundaries[k] < y) ? 1 : 0;
+  codes[i] = (uint8_t)c;
+  group_sync(g);
+  if (a.dst != nullptr) {
+    if (i < pd) {
+      int val = 0;
+      for (int bit = 0; bit < 8; ++bit) {
+        const int pos = i * 8 + bit;
+        const int k = pos / bits, off = pos - k * bits;
+        val = (val << 1) | ((codes[k] >> (bits - 1 - off)) & 1);
+      }
+      a.dst[i] = (uint8_t)val;
+    }
+    if (i == 0) *a.dst_norm = nrm;
+  }
+}
+
 __global__ void __launch_bounds__(ROT128_THREADS)
 akv_qrot128_kernel(const void* __restrict__ q, int q_dtype, int64_t q_ss, int64_t q_sh, int num_q_heads,
                    const float* __restrict__ rot_t, float premul, float* __restrict__ qrot, int rows,
@@ -295,12 +362,9 @@ akv_qrot128_kernel(const void* __restrict__ q, int q_dtype, int64_t q_ss, int64_
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // block order: the new token's vectors first (the longest-running blocks, so they start at once), then
   // the plan block, then the rotation blocks
-  const int enc_blocks = (int)(2 * nt.n_rows);
-  if ((int)blockIdx.x < enc_blocks) {       // one K or V vector of the new token
-    const int64_t e = blockIdx.x;
-    const bool is_v = e >= nt.n_rows;
-    encode_generic_rows(is_v ? nt.v : nt.k, is_v ? e - nt.n_rows : e, nt.n_rows, nt.n_rows, D, nt.bits, rot_t,
-                        nt.boundaries);
+  const int enc_blocks = (int)((2 * nt.n_rows + 3) / 4);
+  if ((int)blockIdx.x < enc_blocks) {       // four K or V vectors of the new token
+    encode128_quad(nt.k, nt.v, nt.n_rows, blockIdx.x, nt.bits, rot_t, nt.boundaries, qs);
     return;
   }
   if ((int)blockIdx.x < enc_blocks + plan_blocks) {
@@ -2545,8 +2609,9 @@ int akv::run_tq_attn(const akv_tq_attn_params* p, void* workspace, size_t worksp
     if (e != cudaSuccess) return fail((int)e, "attention: smem attribute: %s", cudaGetErrorString(e));
     const int quads = gemm_q ? 0 : (rows + 3) / 4;
     const int rot_blocks = quads < 2 * sm_count() ? quads : 2 * sm_count();
-    if (rot_blocks + plan_blocks + (unsigned)(2 * nt.n_rows) > 0) {
-      akv_qrot128_kernel<<<rot_blocks + plan_blocks + (unsigned)(2 * nt.n_rows), ROT128_THREADS, smem128, st>>>(
+    const unsigned enc_blocks = (unsigned)((2 * nt.n_rows + 3) / 4);      // four vectors of the new token per block
+    if (rot_blocks + plan_blocks + enc_blocks > 0) {
+      akv_qrot128_kernel<<<rot_blocks + plan_blocks + enc_blocks, ROT128_THREADS, smem128, st>>>(
           p->query, p->q_dtype, p->q_stride_seq, p->q_stride_head, p->num_q_heads, p->rotation_t,
           p->scale * 1.4426950408889634f, qrot, rows, rot_blocks, plan_blocks, pl, nt);
       if (int rc = check_launch("akv_qrot128_kernel")) return rc;
