@@ -304,9 +304,6 @@ __device__ __forceinline__ void encode128_quad(const RowMap& mk, const RowMap& m
   const int pd = D * bits / 8;
   RowAddr a = map_row(m, is_v ? e - n_rows : e);
   u[i] = load_as_float(a.src_base, m.x_dtype, a.src_off + i);
-  float r0[32];                             // the first round of matrix loads travels while the norm is computed
-#pragma unroll
-  for (int k = 0; k < 32; ++k) r0[k] = rot_t[(int64_t)k * D + i];
   group_sync(g);
   if (i < 32) {
     const float tot = sumsq_8lane(u, D, i & 7, 0xffffffffu);
@@ -318,21 +315,13 @@ __device__ __forceinline__ void encode128_quad(const RowMap& mk, const RowMap& m
   u[i] = __fdiv_rn(u[i], den);              // the first warp finished reading u before the barrier above
   group_sync(g);
   float y = 0.f;
-  float r1[32];
+  for (int j0 = 0; j0 < D; j0 += 32) {      // 32 loads in flight per round: the matrix comes from L2
+    float r[32];
 #pragma unroll
-  for (int k = 0; k < 32; ++k) r1[k] = rot_t[(int64_t)(32 + k) * D + i];
+    for (int k = 0; k < 32; ++k) r[k] = rot_t[(int64_t)(j0 + k) * D + i];
 #pragma unroll
-  for (int k = 0; k < 32; ++k) y = __fmaf_rn(u[k], r0[k], y);
-#pragma unroll
-  for (int k = 0; k < 32; ++k) r0[k] = rot_t[(int64_t)(64 + k) * D + i];
-#pragma unroll
-  for (int k = 0; k < 32; ++k) y = __fmaf_rn(u[32 + k], r1[k], y);
-#pragma unroll
-  for (int k = 0; k < 32; ++k) r1[k] = rot_t[(int64_t)(96 + k) * D + i];
-#pragma unroll
-  for (int k = 0; k < 32; ++k) y = __fmaf_rn(u[64 + k], r0[k], y);
-#pragma unroll
-  for (int k = 0; k < 32; ++k) y = __fmaf_rn(u[96 + k], r1[k], y);
+    for (int k = 0; k < 32; ++k) y = __fmaf_rn(u[j0 + k], r[k], y);
+  }
   int c = 0;
   for (int k = 0; k < nb; ++k) c += (boundaries[k] < y) ? 1 : 0;
   codes[i] = (uint8_t)c;
