@@ -2876,10 +2876,34 @@ struct akv_tq_prefill_params {
   const void* hybrid_tables;
 };
 
-// Short chunks get room for PREFILL_MAX_SPLITS partials per row (key-range splits of the tensor-core kernels).
+// Chunks of up to PREFILL_SPLIT_ROWS rows get room for PREFILL_MAX_SPLITS partials per row (key-range splits of the
+// tensor-core kernels).
 constexpr int PREFILL_MAX_SPLITS = 4;
-constexpr size_t PREFILL_SPLIT_ROWS = 16384;
+constexpr size_t PREFILL_SPLIT_ROWS = 65536;
 static int prefill_parts(size_t rows) { return rows <= PREFILL_SPLIT_ROWS ? PREFILL_MAX_SPLITS : 1; }
+
+// Key-range splits of the tensor-core kernels: `ctas` CTAs of equal length run in ceil(ctas / SMs) rounds; s splits make
+// it ceil(s ctas / SMs) rounds of 1 / s the length.  The smallest s within 2 % of the best is taken (every split adds a
+// partial per row to the merge), with at least 16 key tiles per split when the caller gave max_seq_len.
+static int prefill_splits(int64_t ctas, int parts, int max_seq_len) {
+  if (ctas <= 0 || parts <= 1) return 1;
+  const int sms = sm_count();
+  int limit = parts;
+  if (max_seq_len > 0) {
+    const int by_len = (max_seq_len / 128) / 16;
+    limit = by_len < 1 ? 1 : (by_len < limit ? by_len : limit);
+  } else {            // lengths unknown: only the case of fewer CTAs than SMs
+    const int by_sms = (int)(sms / ctas);
+    limit = by_sms < 1 ? 1 : (by_sms < limit ? by_sms : limit);
+  }
+  int best = 1;
+  double best_cost = (double)((ctas + sms - 1) / sms);
+  for (int s = 2; s <= limit; ++s) {
+    const double cost = (double)((ctas * s + sms - 1) / sms) / s * (1.0 + 0.02 * (s - 1));
+    if (cost < best_cost * 0.98) { best = s; best_cost = cost; }
+  }
+  return best;
+}
 
 static void prefill_plan(int num_tokens, int num_q_heads, size_t* off_acc, size_t* off_ml, size_t* total) {
   const size_t rows = (size_t)num_tokens * num_q_heads, parts = (size_t)prefill_parts(rows);
@@ -2949,14 +2973,9 @@ AKV_EXPORT int akv_tq_prefill_attn(const akv_tq_prefill_params* p) {
   const int64_t tc_rows = (int64_t)p->num_tokens * G;
   const int64_t tc_tiles = (tc_rows + 127) / 128 + p->num_seqs - 1;
   const bool use_tc = tc_env ? tc_env[0] == '1' : tc_rows >= 64 * tc_tiles;
-  // few row tiles (a short chunk, possibly on a long context): the key range of every tile is split over up to four
-  // CTAs, whose partials the merge kernel combines
-  int splits = 1;
-  if (use_tc && prefill_parts((size_t)rows) > 1) {
-    const int64_t ctas = tc_tiles * p->num_kv_heads;
-    splits = (int)(sm_count() / (ctas > 0 ? ctas : 1));
-    splits = splits < 1 ? 1 : (splits > PREFILL_MAX_SPLITS ? PREFILL_MAX_SPLITS : splits);
-  }
+  // the key range of every row tile may be split over up to four CTAs, whose partials the merge kernel combines: few row
+  // tiles (a short chunk, possibly on a long context), or a CTA count that leaves the last round of CTAs half empty
+  const int splits = use_tc ? prefill_splits(tc_tiles * p->num_kv_heads, prefill_parts((size_t)rows), p->max_seq_len) : 1;
   // 3- and 2-bit caches: only the staged tensor-core kernel reads them; say so before anything is launched
   {
     static const bool no_staged_env = getenv("AKV_PREFILL_STAGED") != nullptr && getenv("AKV_PREFILL_STAGED")[0] == '0';

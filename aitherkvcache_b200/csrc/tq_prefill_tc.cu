@@ -610,6 +610,351 @@ tq_prefill_tc_kernel(PrefillArgs a) {
   }
 }
 
+// ---------------------------------------------------------------------------
+// Staged variant with two softmax groups in ping-pong over the key tiles.
+//
+// In tq_prefill_tc_kernel<G, true> the eight softmax warps work on one tile together: their exponentials (the MUFU
+// pipe, 1024 cycles per 128 x 128 tile) and everything else they do (loads from tensor memory, maxima, hand-overs)
+// follow each other, about 2000 cycles per tile, and the tensor pipe waits.  Here warps 0-3 take the even tiles of the
+// CTA's share and warps 4-7 the odd ones (thread = row, all 128 keys of a tile), so one group's exponentials run under
+// the other group's loads and hand-overs.  What that needs:
+//   * three score stages in tensor memory (tiles j and j+1 are in the softmax groups while S of tile j+2 is computed):
+//     3 x 128 columns + O (128 columns) = 512.  Q moves to shared memory (A operand by descriptor), and the value
+//     operand loses its row of ones: the row sums are accumulated by the softmax threads (float32, before rounding).
+//   * the row's reference maximum is shared by the two threads that own the row (shared memory, one mbarrier per 32 rows
+//     and tile parity): tile j+1's owner takes its decision after tile j's owner has published its own; only the
+//     decision is serial (loads + maximum), the exponentials are not.  A thread keeps the row sum of its own tiles and
+//     the reference it is relative to; the two are combined at the end.
+//   * K operands are needed two tiles before the matching V operands and are released much earlier: two K slots fed by
+//     one producer lane (slot free = scores of tile j-2 complete) and three V slots fed by another (value product of
+//     tile j-3 complete).
+// Barriers (index = tile modulo the ring size, phase parity = tile / ring size):
+//   k_full[2], v_full[3]  bulk-copy bytes        s_full[3]   commit after S      p_full[3]  4 warp arrivals
+//   pv_done[3]            commit after P V       ref[4][2]   the row quarter's reference of tile j is published
+// ---------------------------------------------------------------------------
+struct PpL {
+  static constexpr int KT = 128, NKS = 3, NVS = 3, NSS = 3;
+  static constexpr int WARPS = 11, THREADS = WARPS * 32, MMA_WARP = 8, K_WARP = 9, V_WARP = 10;
+  static constexpr int KSLOT = 32768, VSLOT = 32768, VHALF = 16384;
+  static constexpr int K = 0, V = K + NKS * KSLOT, Q = V + NVS * VSLOT, BAR = Q + 32768;
+  static constexpr int SMEM = BAR + 1536 + 1024;      // barriers and the per-row words, + slack for the 1024-byte alignment
+  static constexpr int T_O = 384;
+};
+static_assert(PpL::KSLOT == PFI_VOFF && PpL::VSLOT == 2 * PFI_VHALF && PpL::KSLOT + PpL::VSLOT == PFI_BYTES, "image layout");
+constexpr uint32_t Q_KFULL = 0, Q_VFULL = 24, Q_SFULL = 48, Q_PFULL = 72, Q_PVDONE = 96, Q_REF = 120, Q_DRAIN = 184,
+                   Q_TMEM = 192, Q_FAILED = 196, Q_SREF = 256, Q_SL = 768;      // s_ref [128] and s_l [128] floats
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      :: "r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+         "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
+  asm volatile("st.shared.f32 [%0], %1;" :: "r"(addr), "f"(v) : "memory");
+}
+
+template <int G>
+__global__ void __launch_bounds__(PpL::THREADS, 1)
+tq_prefill_pp_kernel(PrefillArgs a) {
+  using L = PpL;
+  static_assert(G == 1 || G == 2 || G == 4 || G == 8, "query heads per KV head");
+  constexpr int TT = 128 / G;
+  extern __shared__ uint8_t pt_smem_raw[];
+  const uint32_t raw_s = smem_u32(pt_smem_raw);
+  const uint32_t base_s = (raw_s + 1023u) & ~1023u;
+  uint8_t* base = pt_smem_raw + (base_s - raw_s);
+  const uint32_t bar_s = base_s + L::BAR, failed_s = bar_s + Q_FAILED;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int kvh = blockIdx.y;
+
+  int tile = blockIdx.x, s = 0, q0 = 0, qlen = 0;
+  bool found = false;
+  for (s = 0; s < a.num_seqs; ++s) {
+    q0 = (int)load_index(a.query_start_loc, a.qs_dtype, s);
+    const int q1 = (int)load_index(a.query_start_loc, a.qs_dtype, s + 1);
+    qlen = q1 - q0;
+    if (qlen < 0) qlen = 0;
+    const int tiles = (qlen + TT - 1) / TT;
+    if (tile < tiles) { found = true; break; }
+    tile -= tiles;
+  }
+  if (!found) return;
+  const int64_t max_ctx = (int64_t)a.max_blocks_per_seq * a.block_size;
+  const int seq_len = (int)load_ctx(a.seq_lens, a.sl_dtype, s, max_ctx);
+  int past = seq_len - qlen;
+  if (past < 0) past = 0;
+  const int tok_lo = tile * TT;
+  const int tok_hi = (tok_lo + TT < qlen) ? tok_lo + TT : qlen;
+  int kend = past + tok_hi;
+  if (kend > seq_len) kend = seq_len;
+  int n_all = (kend + L::KT - 1) / L::KT;
+  if (n_all > a.tiles_per_seq) n_all = a.tiles_per_seq;
+  const int jbase = (int)((int64_t)n_all * blockIdx.z / gridDim.z);
+  const int n_ktiles = (int)((int64_t)n_all * (blockIdx.z + 1) / gridDim.z) - jbase;
+  if (n_ktiles <= 0) return;
+
+  if (tid == 0) {
+    for (int i = 0; i < L::NKS; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar_s + Q_KFULL + 8 * i));
+    for (int i = 0; i < 3; ++i) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar_s + Q_VFULL + 8 * i));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar_s + Q_SFULL + 8 * i));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;" :: "r"(bar_s + Q_PFULL + 8 * i));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar_s + Q_PVDONE + 8 * i));
+    }
+    for (int i = 0; i < 8; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar_s + Q_REF + 8 * i));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar_s + Q_DRAIN));
+    asm volatile("st.shared.u32 [%0], %1;" :: "r"(failed_s), "r"(0u) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(bar_s + Q_TMEM), "n"(PT_TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  // A operand of S in shared memory: row r = (token tok_lo + r / G, head r % G), zeros for rows without a token
+  if (warp < 4) {
+    const int r = tid, tok = tok_lo + r / G;
+    const bool have = tok < qlen && q0 + tok < a.n_tokens;
+    const float4* src = reinterpret_cast<const float4*>(a.qrot + ((int64_t)(q0 + (have ? tok : 0)) * a.num_q_heads + kvh * G + r % G) * 128);
+#pragma unroll 4
+    for (int c = 0; c < 16; ++c) {           // 16-byte chunk c = dims 8c .. 8c + 7
+      const float4 f0 = have ? src[2 * c] : make_float4(0.f, 0.f, 0.f, 0.f);
+      const float4 f1 = have ? src[2 * c + 1] : make_float4(0.f, 0.f, 0.f, 0.f);
+      pt_sts128(base_s + L::Q + (uint32_t)(c >> 3) * 16384u + (uint32_t)r * 128u + ((((uint32_t)c & 7u) ^ ((uint32_t)r & 7u)) << 4),
+                pt_pack_half2(f0.x, f0.y), pt_pack_half2(f0.z, f0.w), pt_pack_half2(f1.x, f1.y), pt_pack_half2(f1.z, f1.w));
+    }
+    sts_f32(bar_s + Q_SREF + 4 * r, -CUDART_INF_F);
+    sts_f32(bar_s + Q_SL + 4 * r, 0.f);
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = lds_u32(bar_s + Q_TMEM);
+  const uint32_t tmem_o = tmem_base + L::T_O;
+
+  auto wait = [&](uint32_t bar, uint32_t parity) -> bool {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) return true;
+    if (lds_u32(failed_s) != 0u) return false;
+    if (mbar_wait(bar, parity)) return true;
+    g_prefill_tc_status = 1;
+    asm volatile("st.shared.u32 [%0], %1;" :: "r"(failed_s), "r"(1u) : "memory");
+    return false;
+  };
+  auto wait_warp = [&](uint32_t bar, uint32_t parity) -> bool { return __all_sync(0xffffffffu, wait(bar, parity)); };
+  auto par = [](int j, int ring) -> uint32_t { return (uint32_t)((j / ring) & 1); };
+
+  if (warp == L::MMA_WARP) {
+    if (lane == 0) {
+      constexpr uint32_t IDESC = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);      // M 128, N 128, f16 -> f32, K-major
+      const int withhold = (blockIdx.x | blockIdx.y) == 0 ? g_prefill_tc_withhold : -1;
+      const uint64_t d_hi = umma_desc(0u) & 0xffffffff00000000ull;
+      const uint32_t d_lo = (uint32_t)umma_desc(0u);
+      auto desc = [&](uint32_t saddr) -> uint64_t { return d_hi | (uint64_t)(d_lo + ((saddr & 0x3FFFFu) >> 4)); };
+      const uint32_t k_lo = base_s + L::K, v_lo = base_s + L::V, q_lo = base_s + L::Q;
+      auto issue_s = [&](int j) -> bool {
+        const uint32_t st = (uint32_t)(j % 3), ks = st;
+        if (!wait(bar_s + Q_KFULL + 8 * ks, par(j, 3))) return false;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (j == withhold) return true;
+        const uint32_t kb = k_lo + ks * L::KSLOT;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (uint32_t)((kk >> 2) * 16384 + (kk & 3) * 32);
+          umma_f16(tmem_base + st * 128u, desc(q_lo + off), desc(kb + off), IDESC, (uint32_t)(kk != 0));
+        }
+        umma_commit(bar_s + Q_SFULL + 8 * st);
+        return true;
+      };
+      auto issue_pv = [&](int j) -> bool {
+        const uint32_t st = (uint32_t)(j % 3);
+        if (!wait(bar_s + Q_PFULL + 8 * st, par(j, 3))) return false;
+        if (!wait(bar_s + Q_VFULL + 8 * st, par(j, 3))) return false;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t vb = v_lo + st * L::VSLOT;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_f16_ta(tmem_o, tmem_base + st * 128u + (uint32_t)(kk * 8), desc(vb + (uint32_t)((kk >> 2) * L::VHALF + (kk & 3) * 32)),
+                      IDESC, (uint32_t)((j | kk) != 0));
+        umma_commit(bar_s + Q_PVDONE + 8 * st);
+        return true;
+      };
+      bool go = issue_s(0);
+      if (go && n_ktiles > 1) go = issue_s(1);
+      if (go) {
+        for (int j = 0; j < n_ktiles; ++j) {
+          if (j + 2 < n_ktiles && !issue_s(j + 2)) break;
+          if (!issue_pv(j)) break;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == L::K_WARP || warp == L::V_WARP) {
+    if (lane == 0) {
+      const bool isk = warp == L::K_WARP;
+      constexpr int ring = 3;
+      const uint8_t* src = a.staged + (((int64_t)s * a.tiles_per_seq + jbase) * a.num_kv_heads + kvh) * PT_IMAGE + (isk ? 0 : L::KSLOT);
+      const int64_t step = (int64_t)a.num_kv_heads * PT_IMAGE;
+      const uint32_t full0 = bar_s + (isk ? Q_KFULL : Q_VFULL), dst0 = base_s + (isk ? L::K : L::V);
+      int issued = 0;
+      for (int j = 0; j < n_ktiles; ++j) {
+        const uint32_t slot = (uint32_t)(j % ring);
+        if (j >= ring) {
+          // K slot: the scores of tile j-3 are complete; V slot: the value product of tile j-3 is complete
+          const int jj = j - ring;
+          if (!wait(bar_s + (isk ? Q_SFULL : Q_PVDONE) + 8 * (uint32_t)(jj % 3), par(jj, 3))) break;
+        }
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(full0 + 8 * slot), "r"(32768) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     :: "r"(dst0 + slot * 32768u), "l"(src + j * step), "r"(32768), "r"(full0 + 8 * slot) : "memory");
+        issued = j + 1;
+      }
+      if (lds_u32(failed_s) != 0u)
+        for (int j = issued - ring < 0 ? 0 : issued - ring; j < issued; ++j) mbar_wait(full0 + 8 * (uint32_t)(j % ring), par(j, ring));
+    }
+    __syncwarp();
+  } else {
+    // ================= softmax groups: warps 0-3 even tiles, warps 4-7 odd tiles; thread = row =================
+    const int quad = warp & 3, grp = warp >> 2;
+    const int r = quad * 32 + lane;
+    const int tok = tok_lo + r / G;
+    const bool live = tok < qlen && q0 + tok < a.n_tokens;
+    int lim = live ? past + tok + 1 : 0;
+    if (lim > seq_len) lim = seq_len;
+    const uint32_t t_lane = ((uint32_t)(quad * 32)) << 16;
+    const uint32_t sref_s = bar_s + Q_SREF + 4 * r, sl_s = bar_s + Q_SL + 4 * r;
+    float l = 0.f, lref = -CUDART_INF_F;      // row sum of this thread's tiles and the reference it is relative to
+    bool ok = true;
+    for (int j = grp; j < n_ktiles && ok; j += 2) {
+      const uint32_t st = (uint32_t)(j % 3);
+      if (!wait_warp(bar_s + Q_SFULL + 8 * st, par(j, 3))) { ok = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t s_addr = tmem_base + t_lane + st * 128u;
+      const int vis = lim - L::KT * (jbase + j);      // keys of this tile the row may see (<= 0: none, >= 128: all)
+      // ---- pass 1: the row maximum ----
+      float mx = -CUDART_INF_F;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(s_addr + 32 * c, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (vis < 32 * c + 32) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 32 * c + i < vis ? v[i] : 0xff800000u;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) mx = fmaxf(mx, fmaxf(__uint_as_float(v[i]), __uint_as_float(v[i + 1])));
+      }
+      // ---- the row's reference: after the owner of tile j-1 has published its decision ----
+      if (j > 0 && !wait_warp(bar_s + Q_REF + 8 * (uint32_t)(2 * quad + ((j - 1) & 1)), par(j - 1, 2))) { ok = false; break; }
+      float m_ref = lds_f32(sref_s);
+      const bool grow = mx > m_ref + PT_RESCALE;
+      const bool any = __any_sync(0xffffffffu, grow);
+      const float alpha = grow ? pt_ex2(m_ref - mx) : 1.0f;      // m_ref = -inf: 0
+      if (grow) { m_ref = mx; sts_f32(sref_s, mx); }
+      __syncwarp();
+      if (lane == 0) pt_arrive(bar_s + Q_REF + 8 * (uint32_t)(2 * quad + (j & 1)));
+      if (lref != m_ref) {
+        l = l > 0.f ? l * pt_ex2(lref - m_ref) : 0.f;
+        lref = m_ref;
+      }
+      if (any && j > 0) {       // O holds the value products of tiles < j, all relative to the old reference
+        if (!wait_warp(bar_s + Q_PVDONE + 8 * (uint32_t)((j - 1) % 3), par(j - 1, 3))) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          tmem_ld32(tmem_o + t_lane + 32 * c, o);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(tmem_o + t_lane + 32 * c, o);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      }
+      // ---- pass 2: probabilities as fp16 pairs into the first 64 columns of the stage (chunk c lands on columns the
+      // thread has consumed already), row sum in float32 ----
+      const float ref = m_ref == -CUDART_INF_F ? 0.f : m_ref;
+      float ls0 = 0.f, ls1 = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(s_addr + 32 * c, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (vis < 32 * c + 32) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 32 * c + i < vis ? v[i] : 0xff800000u;
+        }
+        uint32_t ph[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = pt_ex2(__uint_as_float(v[2 * i]) - ref), p1 = pt_ex2(__uint_as_float(v[2 * i + 1]) - ref);
+          ls0 += p0;
+          ls1 += p1;
+          ph[i] = pt_pack_half2(p0, p1);
+        }
+        tmem_st16(s_addr + 16 * c, ph);
+      }
+      l += ls0 + ls1;
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) pt_arrive(bar_s + Q_PFULL + 8 * st);
+    }
+    // ---- the two owners of a row agree on its final reference and add their sums ----
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    const float fin = lds_f32(sref_s);
+    if (lref != fin) l = l > 0.f ? l * pt_ex2(lref - fin) : 0.f;
+    if (grp == 1) sts_f32(sl_s, l);
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (grp == 0) l += lds_f32(sl_s);
+    if (ok && wait_warp(bar_s + Q_PVDONE + 8 * (uint32_t)((n_ktiles - 1) % 3), par(n_ktiles - 1, 3))) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int64_t row = ((int64_t)(q0 + tok) * a.num_q_heads + kvh * G + r % G) * gridDim.z + blockIdx.z;
+#pragma unroll 1
+      for (int c = 2 * grp; c < 2 * grp + 2; ++c) {
+        uint32_t o[32];
+        tmem_ld32(tmem_o + t_lane + 32 * c, o);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (live) {
+          float4* dst = reinterpret_cast<float4*>(a.part_acc + row * 128 + 32 * c);
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            dst[i] = make_float4(__uint_as_float(o[4 * i]), __uint_as_float(o[4 * i + 1]), __uint_as_float(o[4 * i + 2]),
+                                 __uint_as_float(o[4 * i + 3]));
+        }
+      }
+      if (grp == 0 && live) { a.part_ml[row * 2] = fin; a.part_ml[row * 2 + 1] = l; }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  int leak = 0;
+  if (warp == L::MMA_WARP && lane == 0 && lds_u32(failed_s) != 0u) {
+    umma_commit(bar_s + Q_DRAIN);
+    leak = mbar_wait(bar_s + Q_DRAIN, 0u) ? 0 : 1;
+    if (leak) g_prefill_tc_status = 2;
+  }
+  leak = __syncthreads_or(leak);
+  if (warp == 0 && !leak) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "n"(PT_TMEM_COLS) : "memory");
+  }
+}
+
 // Pre-pass of the staged variant: every 128-key tile of every sequence and KV head becomes the 64 KB set of operand
 // images (K rows, then the transposed V rows of its two 64-key halves; norms folded in, keys past the sequence zero)
 // that tq_prefill_tc_kernel<G, true> pulls into shared memory with three bulk copies.  A CTA takes PS_TILES consecutive
@@ -801,12 +1146,19 @@ int launch_prefill_tc(const PrefillArgs& a, int G, cudaStream_t st) {
 #define AKV_PT(GG, ST)                                                                                                  \
   e = cudaFuncSetAttribute(tq_prefill_tc_kernel<GG, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, PtL<ST>::SMEM);     \
   if (e == cudaSuccess) tq_prefill_tc_kernel<GG, ST><<<grid, PtL<ST>::THREADS, PtL<ST>::SMEM, st>>>(a);
-  if (a.staged != nullptr) {
+  static const bool pingpong = getenv("AKV_PREFILL_PP") == nullptr || atoi(getenv("AKV_PREFILL_PP")) != 0;      // AKV_PREFILL_PP=0: the one-tile-at-a-time kernel
+#define AKV_PP(GG)                                                                                                       \
+  e = cudaFuncSetAttribute(tq_prefill_pp_kernel<GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, PpL::SMEM);             \
+  if (e == cudaSuccess) tq_prefill_pp_kernel<GG><<<grid, PpL::THREADS, PpL::SMEM, st>>>(a);
+  if (a.staged != nullptr && pingpong) {
+    if (G == 1) { AKV_PP(1) } else if (G == 2) { AKV_PP(2) } else if (G == 4) { AKV_PP(4) } else { AKV_PP(8) }
+  } else if (a.staged != nullptr) {
     if (G == 1) { AKV_PT(1, true) } else if (G == 2) { AKV_PT(2, true) } else if (G == 4) { AKV_PT(4, true) } else { AKV_PT(8, true) }
   } else {
     if (G == 1) { AKV_PT(1, false) } else if (G == 2) { AKV_PT(2, false) } else if (G == 4) { AKV_PT(4, false) } else { AKV_PT(8, false) }
   }
 #undef AKV_PT
+#undef AKV_PP
   if (e != cudaSuccess) return fail((int)e, "prefill attention: smem attribute: %s", cudaGetErrorString(e));
   return check_launch(a.staged != nullptr ? "tq_prefill_attn_tc_staged_kernel" : "tq_prefill_attn_tc_kernel");
 }
