@@ -1146,7 +1146,8 @@ int launch_prefill_tc(const PrefillArgs& a, int G, cudaStream_t st) {
 #define AKV_PT(GG, ST)                                                                                                  \
   e = cudaFuncSetAttribute(tq_prefill_tc_kernel<GG, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, PtL<ST>::SMEM);     \
   if (e == cudaSuccess) tq_prefill_tc_kernel<GG, ST><<<grid, PtL<ST>::THREADS, PtL<ST>::SMEM, st>>>(a);
-  static const bool pingpong = getenv("AKV_PREFILL_PP") == nullptr || atoi(getenv("AKV_PREFILL_PP")) != 0;      // AKV_PREFILL_PP=0: the one-tile-at-a-time kernel
+  const char* pp_env = getenv("AKV_PREFILL_PP");          // read per call; AKV_PREFILL_PP=0: the one-tile-at-a-time kernel
+  const bool pingpong = pp_env == nullptr || atoi(pp_env) != 0;
 #define AKV_PP(GG)                                                                                                       \
   e = cudaFuncSetAttribute(tq_prefill_pp_kernel<GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, PpL::SMEM);             \
   if (e == cudaSuccess) tq_prefill_pp_kernel<GG><<<grid, PpL::THREADS, PpL::SMEM, st>>>(a);
@@ -1160,7 +1161,8 @@ int launch_prefill_tc(const PrefillArgs& a, int G, cudaStream_t st) {
 #undef AKV_PT
 #undef AKV_PP
   if (e != cudaSuccess) return fail((int)e, "prefill attention: smem attribute: %s", cudaGetErrorString(e));
-  return check_launch(a.staged != nullptr ? "tq_prefill_attn_tc_staged_kernel" : "tq_prefill_attn_tc_kernel");
+  return check_launch(a.staged == nullptr ? "tq_prefill_attn_tc_kernel"
+                                          : (pingpong ? "tq_prefill_attn_tc_staged_kernel" : "tq_prefill_attn_tc_staged_onetile_kernel"));
 }
 
 size_t prefill_staged_bytes(int num_seqs, int num_kv_heads, int max_seq_len) {

@@ -709,10 +709,13 @@ def test_chunked_prefill_kernel_equals_row_by_row_attention(H, QH, bs, staged):
     assert np.abs(out[row].float().cpu().numpy() - want[0]).max() < 2e-3
 
 
-@pytest.mark.parametrize("staged", (False, True))
-def test_chunked_prefill_long_context_against_oracle_rows(staged):
+@pytest.mark.parametrize("staged", (False, True, "one_tile"))
+def test_chunked_prefill_long_context_against_oracle_rows(staged, monkeypatch):
     """A 512-token chunk behind 30 000 cached tokens (the headline cache geometry): three rows of the chunk against the
-    oracle, 64 rows against the decode kernels run with one row per query token."""
+    oracle, 64 rows against the decode kernels run with one row per query token.  Codes decoded in the kernel, staged
+    images with the two softmax groups in ping-pong (the default), staged images with one tile at a time."""
+    if staged == "one_tile":
+        monkeypatch.setenv("AKV_PREFILL_PP", "0")
     g = load_golden("tq_d128_b4.npz")
     tq = _tq(128, 4, g)
     H, QH, bs, past, chunk = 8, 32, 16, 30000, 512
@@ -731,7 +734,8 @@ def test_chunked_prefill_long_context_against_oracle_rows(staged):
     out = attn.prefill(query, kp, kn, vp, vn, bt, sl, qsl, block_size=bs, num_kv_heads=H, max_seq_len=n if staged else None)
     assert out is not None
     from aitherkvcache_b200 import _lib
-    assert _lib.lib().akv_last_split_kernel() == (b"tq_prefill_attn_tc_staged_kernel" if staged else b"tq_prefill_attn_tc_kernel")
+    assert _lib.lib().akv_last_split_kernel() == {False: b"tq_prefill_attn_tc_kernel", True: b"tq_prefill_attn_tc_staged_kernel",
+                                                  "one_tile": b"tq_prefill_attn_tc_staged_onetile_kernel"}[staged]
     rows = torch.arange(0, chunk, 8, device="cuda")
     ref = attn.forward(query[rows], kp, kn, vp, vn, bt.expand(len(rows), -1).contiguous(),
                        (past + rows + 1).to(torch.int32), block_size=bs, num_kv_heads=H)
@@ -822,11 +826,13 @@ def test_chunked_prefill_low_bit_caches_through_staged_images(bits):
     assert np.abs(out[row].float().cpu().numpy() - want[0]).max() < 2e-3
 
 
-@pytest.mark.parametrize("staged", (False, True))
+@pytest.mark.parametrize("staged", (False, True, "one_tile"))
 @pytest.mark.parametrize("H,QH", ((4, 4), (2, 4), (1, 8)))
-def test_chunked_prefill_tensor_core_kernels_group_sizes(H, QH, staged):
-    """One and two query heads per KV head (128 and 64 query tokens per row tile) and eight (16 tokens) through both
+def test_chunked_prefill_tensor_core_kernels_group_sizes(H, QH, staged, monkeypatch):
+    """One and two query heads per KV head (128 and 64 query tokens per row tile) and eight (16 tokens) through the
     tensor-core variants: one sequence whose chunk fills its row tiles, against the decode kernels row by row."""
+    if staged == "one_tile":
+        monkeypatch.setenv("AKV_PREFILL_PP", "0")
     g = load_golden("tq_d128_b4.npz")
     tq = _tq(128, 4, g)
     attn = _attn(tq, QH)
@@ -843,7 +849,8 @@ def test_chunked_prefill_tensor_core_kernels_group_sizes(H, QH, staged):
     out = attn.prefill(query, kp, kn, vp, vn, bt.cuda(), sl, qsl, block_size=bs, num_kv_heads=H, max_seq_len=n if staged else None)
     assert out is not None
     from aitherkvcache_b200 import _lib
-    assert _lib.lib().akv_last_split_kernel() == (b"tq_prefill_attn_tc_staged_kernel" if staged else b"tq_prefill_attn_tc_kernel")
+    assert _lib.lib().akv_last_split_kernel() == {False: b"tq_prefill_attn_tc_kernel", True: b"tq_prefill_attn_tc_staged_kernel",
+                                                  "one_tile": b"tq_prefill_attn_tc_staged_onetile_kernel"}[staged]
     ref = attn.forward(query, kp, kn, vp, vn, bt.expand(chunk, -1).contiguous().cuda(),
                        torch.arange(past + 1, n + 1, dtype=torch.int32).cuda(), block_size=bs, num_kv_heads=H)
     assert (out.float() - ref.float()).abs().max().item() < 2e-3
