@@ -28,6 +28,11 @@
 //   pv_done          tcgen05.commit after P V                                      -> V stage and P buffer free, O readable
 // Every wait is bounded; a wait that gives up sets g_prefill_tc_status and a shared flag that ends all loops; the
 // CTA then leaves after releasing its tensor memory, its rows unwritten (they come out as zeros).
+//
+// Three kernels live here: tq_prefill_tc_kernel<G, false> as described above (codes decoded in the kernel),
+// tq_prefill_tc_kernel<G, true> (operand images staged in global memory by a pre-pass, tiles of 128 keys, Q and P as
+// tensor-memory operands, all softmax warps on one tile) and tq_prefill_pp_kernel<G> (staged images, two softmax groups
+// in ping-pong over the key tiles: the default whenever images are staged; its own description is above it).
 #include "tq_prefill_args.cuh"
 #include "umma.cuh"
 #include <math_constants.h>
